@@ -1,0 +1,265 @@
+"""TEST INFRASTRUCTURE -- numpy front end over the CPU checkers in this directory.
+
+`libpluto_oracle.so` is this repository's C restatement of the reference arithmetic
+(pluto_oracle.c); `_ref/libpluto_ref.so` is the reference project's own
+AttentionLayerReference compiled from its sources (ref_shim.cc, Makefile).  Only tests, the
+smoke check and the benchmark's CPU-baseline leg import this package; the engine in
+`pluto_b200` never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ORACLE_SO = os.path.join(_HERE, "libpluto_oracle.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libpluto_ref.so")
+
+
+def build(quiet: bool = True) -> None:
+    """Compile the C restatement, and the reference's own layer when its tree is present."""
+    subprocess.run(["make", "-C", _HERE, "all"], check=True,
+                   stdout=subprocess.DEVNULL if quiet else None)
+
+
+_lib = None
+_ref = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_ORACLE_SO):
+            build()
+        _lib = C.CDLL(_ORACLE_SO)
+        _lib.oracle_gdn_decay.restype = C.c_float
+        _lib.oracle_gdn_decay.argtypes = [C.c_float] * 3
+        _lib.oracle_gdn_beta.restype = C.c_float
+        _lib.oracle_gdn_beta.argtypes = [C.c_float, C.c_int]
+    return _lib
+
+
+def have_ref() -> bool:
+    return os.path.exists(_REF_SO)
+
+
+def ref() -> C.CDLL:
+    global _ref
+    if _ref is None:
+        _ref = C.CDLL(_REF_SO)
+    return _ref
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+# ---------------------------------------------------------------------------- bf16 helpers
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """fp32 -> bf16 bit patterns (uint16), round to nearest even (reference_internal.h:109-115)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    b = b + 0x7FFF + ((b >> 16) & 1)
+    return (b >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(h: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(h, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    return from_bf16_bits(to_bf16_bits(x))
+
+
+# ---------------------------------------------------------------------------- causal MHA
+def attention_fwd(qkv, context, heads, embed, bf16, threads=1, want_probs=False, use_ref=False):
+    """qkv: [rows, 3E] float32 (fp32 policy) or uint16 bf16 bits.  Returns dict(out, maxima,
+    normalizers[, probs]).  use_ref=True runs the reference's own compiled layer (no stats)."""
+    rows = qkv.shape[0]
+    qkv = np.ascontiguousarray(qkv)
+    assert qkv.dtype == (np.uint16 if bf16 else np.float32) and qkv.shape[1] == 3 * embed
+    out = np.empty((rows, embed), dtype=qkv.dtype)
+    if use_ref:
+        code = ref().pluto_ref_attention(_p(qkv), None, rows, context, heads, embed, int(bf16),
+                                         threads, _p(out), None)
+        if code:
+            raise ValueError(f"reference status code {code}")
+        return {"out": out}
+    batch = rows // context if context > 0 and rows % context == 0 else 0
+    maxima = np.empty((batch * heads * context,), dtype=np.float32)
+    normalizers = np.empty_like(maxima)
+    probs = np.empty((batch, heads, context, context), np.float32) if want_probs else None
+    code = lib().oracle_attention_fwd(_p(qkv), rows, context, heads, embed, int(bf16), threads,
+                                      _p(out), _p(maxima), _p(normalizers), _p(probs))
+    if code:
+        raise ValueError(f"oracle status code {code}")
+    res = {"out": out, "maxima": maxima, "normalizers": normalizers}
+    if want_probs:
+        res["probs"] = probs
+    return res
+
+
+def attention_fwd_bwd(qkv, d_out, context, heads, embed, bf16, threads=1, use_ref=False):
+    """Forward then backward.  Returns (out, d_qkv fp32 [rows, 3E])."""
+    rows = qkv.shape[0]
+    qkv = np.ascontiguousarray(qkv)
+    d_out = np.ascontiguousarray(d_out, dtype=np.float32)
+    out = np.empty((rows, embed), dtype=qkv.dtype)
+    d_qkv = np.empty((rows, 3 * embed), dtype=np.float32)
+    if use_ref:
+        code = ref().pluto_ref_attention(_p(qkv), _p(d_out), rows, context, heads, embed,
+                                         int(bf16), threads, _p(out), _p(d_qkv))
+        if code:
+            raise ValueError(f"reference status code {code}")
+        return out, d_qkv
+    out = attention_fwd(qkv, context, heads, embed, bf16, threads)["out"]
+    code = lib().oracle_attention_bwd(_p(qkv), _p(out), _p(d_out), rows, context, heads, embed,
+                                      int(bf16), threads, _p(d_qkv))
+    if code:
+        raise ValueError(f"oracle status code {code}")
+    return out, d_qkv
+
+
+def attention_bwd(qkv, out, d_out, context, heads, embed, bf16, threads=1):
+    rows = qkv.shape[0]
+    d_qkv = np.empty((rows, 3 * embed), dtype=np.float32)
+    qkv, out = np.ascontiguousarray(qkv), np.ascontiguousarray(out)
+    d_out = np.ascontiguousarray(d_out, dtype=np.float32)
+    code = lib().oracle_attention_bwd(_p(qkv), _p(out), _p(d_out), rows, context, heads, embed,
+                                      int(bf16), threads, _p(d_qkv))
+    if code:
+        raise ValueError(f"oracle status code {code}")
+    return d_qkv
+
+
+# ---------------------------------------------------------------------------- Qwen GQA
+def qk_prepare(q_gate, k, v, q_norm, k_norm, position, rotary, eps, theta, rnd, keys, values):
+    """One token.  q_gate [Hq,2,D], k,v [Hkv,D] fp32; keys/values: fp32 cache [cap,Hkv,D] updated
+    in place at `position`.  Returns queries [Hq,D]."""
+    hq, _, d = q_gate.shape
+    hkv = k.shape[0]
+    queries = np.empty((hq, d), np.float32)
+    f = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    q_gate, k, v, q_norm, k_norm = map(f, (q_gate, k, v, q_norm, k_norm))
+    lib().oracle_qk_prepare(_p(q_gate), _p(k), _p(v), _p(q_norm), _p(k_norm), hq, hkv, d, rotary,
+                            position, C.c_float(eps), C.c_float(theta), int(rnd), _p(queries),
+                            _p(keys), _p(values))
+    return queries
+
+
+def gqa_decode(queries, q_gate, keys, values, length, rnd):
+    """queries [Hq,D] fp32, q_gate [Hq,2,D] or None, keys/values [>=length,Hkv,D] fp32 or uint16."""
+    hq, d = queries.shape
+    hkv = keys.shape[1]
+    out = np.empty((hq, d), np.float32)
+    queries = np.ascontiguousarray(queries, dtype=np.float32)
+    if q_gate is not None:
+        q_gate = np.ascontiguousarray(q_gate, dtype=np.float32)
+    assert keys.flags.c_contiguous and values.flags.c_contiguous
+    lib().oracle_gqa_decode(_p(queries), _p(q_gate), _p(keys), _p(values),
+                            int(keys.dtype == np.uint16), hq, hkv, d, length, int(rnd), _p(out))
+    return out
+
+
+def gqa_decode_batch(q, keys, values, lengths, rnd=True, threads=1):
+    """q [B,Hq,D] (uint16 bf16 bits or fp32); keys/values: lists of [L_b(or more),Hkv,D] arrays."""
+    b, hq, d = q.shape
+    hkv = keys[0].shape[1]
+    q = np.ascontiguousarray(q)
+    out = np.empty_like(q)
+    kp = (C.c_void_p * b)(*[k.ctypes.data for k in keys])
+    vp = (C.c_void_p * b)(*[v.ctypes.data for v in values])
+    lens = np.ascontiguousarray(lengths, dtype=np.int32)
+    lib().oracle_gqa_decode_batch(_p(q), kp, vp, _p(lens), b, int(q.dtype == np.uint16),
+                                  int(keys[0].dtype == np.uint16), hq, hkv, d, int(rnd), threads,
+                                  _p(out))
+    return out
+
+
+def gqa_probabilities(queries, keys, length):
+    hq, d = queries.shape
+    hkv = keys.shape[1]
+    probs = np.empty((hq, length), np.float32)
+    queries = np.ascontiguousarray(queries, dtype=np.float32)
+    lib().oracle_gqa_probabilities(_p(queries), _p(keys), int(keys.dtype == np.uint16), hq, hkv, d,
+                                   length, _p(probs))
+    return probs
+
+
+def gqa_prefill(q, k, v, gate=None, rnd=True, threads=1, rows=None, q_token_stride=None,
+                q_head_stride=None, want_core=False, want_lse=False, shape=None):
+    """q [T,Hq,D], k,v [T,Hkv,D] (uint16 bf16 bits or fp32).  `rows=(begin,end)` limits the query
+    rows computed (others left zero).  For a strided q view pass the base array plus strides and
+    shape=(T,Hq,D)."""
+    t, hq, d = shape if shape is not None else q.shape
+    hkv = k.shape[1]
+    bf16 = k.dtype == np.uint16
+    out = np.zeros((t, hq, d), dtype=k.dtype)
+    core = np.zeros((t, hq, d), np.float32) if want_core else None
+    lse = np.zeros((hq, t), np.float32) if want_lse else None
+    rb, re = rows if rows is not None else (0, t)
+    qts = q_token_stride if q_token_stride is not None else hq * d
+    qhs = q_head_stride if q_head_stride is not None else d
+    lib().oracle_gqa_prefill(_p(q), _p(gate), _p(np.ascontiguousarray(k)),
+                             _p(np.ascontiguousarray(v)), int(bf16), t, hq, hkv, d,
+                             C.c_size_t(qts), C.c_size_t(qhs), int(rnd), threads, rb, re, _p(out),
+                             _p(core), _p(lse))
+    res = {"out": out}
+    if want_core:
+        res["core"] = core
+    if want_lse:
+        res["lse"] = lse
+    return res
+
+
+# ---------------------------------------------------------------------------- gated delta-net
+def gdn_decay(a, dt_bias, a_log):
+    return np.array([lib().oracle_gdn_decay(float(x), float(y), float(z))
+                     for x, y, z in zip(np.ravel(a), np.ravel(dt_bias), np.ravel(a_log))],
+                    np.float32).reshape(np.shape(a))
+
+
+def gdn_beta(b, rnd):
+    return np.array([lib().oracle_gdn_beta(float(x), int(rnd)) for x in np.ravel(b)],
+                    np.float32).reshape(np.shape(b))
+
+
+def gdn_recurrence(q, k, v, g, beta, state, normalize_qk=True, q_scale=1.0, rnd=True, threads=1):
+    """q,k [B,T,Hk,dk]; v [B,T,Hv,dv] (uint16 bf16 bits or fp32); g,beta fp32 [B,T,Hv];
+    state fp32 [B,Hv,dk,dv] updated IN PLACE.  Returns out like v."""
+    b, t, hk, dk = q.shape
+    hv, dv = v.shape[2], v.shape[3]
+    q, k, v = map(np.ascontiguousarray, (q, k, v))
+    g = np.ascontiguousarray(g, dtype=np.float32)
+    beta = np.ascontiguousarray(beta, dtype=np.float32)
+    assert state.dtype == np.float32 and state.flags.c_contiguous
+    out = np.empty_like(v)
+    code = lib().oracle_gdn_recurrence(_p(q), _p(k), _p(v), _p(g), _p(beta),
+                                       int(v.dtype == np.uint16), b, t, hk, hv, dk, dv,
+                                       int(normalize_qk), C.c_float(q_scale), int(rnd), threads,
+                                       _p(state), _p(out))
+    if code:
+        raise ValueError(f"oracle status code {code}")
+    return out
+
+
+def gdn_conv_step(x, weight, state, rnd):
+    """x [channels] fp32, weight [channels,width], state [channels,width] updated in place."""
+    ch, width = weight.shape
+    out = np.empty((ch,), np.float32)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    weight = np.ascontiguousarray(weight, dtype=np.float32)
+    lib().oracle_gdn_conv_step(_p(x), _p(weight), ch, width, int(rnd), _p(state), _p(out))
+    return out
+
+
+def gdn_output(core, z, norm_weight, eps, rnd, final_round=True):
+    heads, dim = core.shape
+    out = np.empty((heads, dim), np.float32)
+    f = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    core, z, norm_weight = map(f, (core, z, norm_weight))
+    lib().oracle_gdn_output(_p(core), _p(z), _p(norm_weight), heads, dim, C.c_float(eps), int(rnd),
+                            int(final_round), _p(out))
+    return out

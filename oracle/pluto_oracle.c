@@ -1,0 +1,528 @@
+/*
+ * TEST INFRASTRUCTURE -- not part of the shipped engine.
+ *
+ * CPU restatement, in plain C, of the reference project's arithmetic for every layer on the
+ * attention hot path.  Only the test-suite, the smoke check and the benchmark's CPU-baseline leg
+ * may load this library; the CUDA engine never links or calls it.
+ *
+ * Pinning status (how each function is anchored to the reference):
+ *   oracle_attention_fwd / _bwd   restate AttentionLayerReference (src/llm/layers/
+ *       attention_reference.cc:36-114 and :116-230) with the same scalar operation order; the
+ *       tests require BIT equality with the reference's own compiled code (oracle/_ref) on the
+ *       reference test-suite's shapes and inputs (attention_reference_test.cc:35-44,148-197) and
+ *       reproduce its hand-computable answer (attention_test.cc:282-360).
+ *   oracle_qk_prepare, oracle_gqa_decode, oracle_gqa_probabilities   restate PrepareAttentionKernel,
+ *       FullAttentionKernel, AttentionProbabilitiesKernel (src/llm/layers/util/
+ *       cached_attention_ops.cc:30-79, :83-126, :131-178).  No compilable reference CPU code exists
+ *       for them; they are pinned by the reference tests' known answers
+ *       (cached_attention_ops_test.cc:364-398 exact gate products, :472-503 uniform 1/length rows,
+ *       cached_attention_test.cc:108-156) and cross-checked against an independent double-precision
+ *       statement of the same layer written from the equations in the tests' specification
+ *       (cached_attention_ops_test.cc:43-131).
+ *   oracle_gqa_prefill   restates the attention core of ForwardKernel
+ *       (src/llm/layers/qwen_attention.cc:68-119); pinned by equality with oracle_gqa_decode run
+ *       token by token (the reference's own cross-path check, qwen_attention_test.cc:155-228).
+ *   oracle_gdn_*   restate ConvolutionKernel/ConvForward, DeltaRecurrenceKernel/RecurrenceForward,
+ *       DeltaOutputKernel/OutputForward (cached_attention_ops.cc:180-272,
+ *       sequence_delta_net.cc:31-121); pinned by the a=+-100 softplus extremes and Reset-replay
+ *       properties of cached_attention_ops_test.cc:400-470 and a double-precision cross-check.
+ *
+ * All tensors are caller-owned; nothing here allocates except scratch rows on the stack/heap.
+ */
+#include <math.h>
+#include <pthread.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ---- bf16 helpers: round-to-nearest-even, as reference_internal.h:109-119 ---------------- */
+static inline uint16_t f2bf(float v) {
+  uint32_t b;
+  memcpy(&b, &v, 4);
+  if ((b & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((b >> 16) | 0x40u); /* quiet NaN */
+  b += 0x7fffu + ((b >> 16) & 1u);
+  return (uint16_t)(b >> 16);
+}
+static inline float bf2f(uint16_t h) {
+  uint32_t b = (uint32_t)h << 16;
+  float v;
+  memcpy(&v, &b, 4);
+  return v;
+}
+static inline float rnd(float v, int round) { return round ? bf2f(f2bf(v)) : v; }
+static inline float load_act(const void* p, size_t i, int bf16) {
+  return bf16 ? bf2f(((const uint16_t*)p)[i]) : ((const float*)p)[i];
+}
+static inline void store_act(void* p, size_t i, int bf16, float v) {
+  if (bf16) ((uint16_t*)p)[i] = f2bf(v);
+  else ((float*)p)[i] = v;
+}
+uint16_t oracle_float_to_bf16(float v) { return f2bf(v); }
+float oracle_bf16_to_float(uint16_t h) { return bf2f(h); }
+
+/* ---- tiny pthread parallel-for over independent units ------------------------------------ */
+typedef void (*unit_fn)(int unit, void* ctx);
+typedef struct { unit_fn fn; void* ctx; int begin, end; } span_t;
+static void* run_span(void* arg) {
+  span_t* s = (span_t*)arg;
+  for (int u = s->begin; u < s->end; ++u) s->fn(u, s->ctx);
+  return NULL;
+}
+static void parallel_units(int units, int threads, unit_fn fn, void* ctx) {
+  if (threads > units) threads = units;
+  if (threads <= 1) { for (int u = 0; u < units; ++u) fn(u, ctx); return; }
+  pthread_t* ids = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)threads);
+  span_t* spans = (span_t*)malloc(sizeof(span_t) * (size_t)threads);
+  for (int t = 0; t < threads; ++t) {
+    spans[t].fn = fn; spans[t].ctx = ctx;
+    spans[t].begin = (int)((long long)units * t / threads);
+    spans[t].end = (int)((long long)units * (t + 1) / threads);
+    pthread_create(&ids[t], NULL, run_span, &spans[t]);
+  }
+  for (int t = 0; t < threads; ++t) pthread_join(ids[t], NULL);
+  free(ids); free(spans);
+}
+
+/* ========================================================================================== *
+ * Causal multi-head attention over packed [rows, 3E]   (AttentionLayerReference)
+ * ========================================================================================== */
+typedef struct {
+  const void* qkv; const void* out_in; const float* d_out; void* out; float* maxima;
+  float* normalizers; float* d_qkv; float* probs; int rows, context, heads, embed, bf16;
+} mha_t;
+
+/* attention_reference.cc:61-110, one sequence per unit.  Also emits the statistics the GPU layer
+ * saves (row maximum of the scaled scores and the sum of exp(score - max), attention.cc:128-131,
+ * 160-169) in its [(b*H+h)*S + s] layout, and optionally the full causal probabilities
+ * [B,H,S,S] with zeros above the diagonal (attention.cc:176-230). */
+static void mha_fwd_sequence(int sequence, void* ctx) {
+  const mha_t* a = (const mha_t*)ctx;
+  const int S = a->context, H = a->heads, E = a->embed, D = E / H;
+  const float scale = 1.0f / sqrtf((float)D);
+  float* scores = (float*)malloc(sizeof(float) * (size_t)S);
+  for (int pos = 0; pos < S; ++pos) {
+    const size_t row = (size_t)sequence * S + pos;
+    for (int h = 0; h < H; ++h) {
+      const int c0 = h * D;
+      float maximum = -INFINITY;
+      for (int kp = 0; kp <= pos; ++kp) {
+        const size_t krow = (size_t)sequence * S + kp;
+        float score = 0.0f;
+        for (int d = 0; d < D; ++d)
+          score += load_act(a->qkv, row * 3 * E + c0 + d, a->bf16) *
+                   load_act(a->qkv, krow * 3 * E + E + c0 + d, a->bf16);
+        scores[kp] = score * scale;
+        maximum = fmaxf(maximum, scores[kp]);
+      }
+      float denominator = 0.0f;
+      for (int kp = 0; kp <= pos; ++kp) {
+        scores[kp] = expf(scores[kp] - maximum);
+        denominator += scores[kp];
+      }
+      if (a->maxima) a->maxima[((size_t)sequence * H + h) * S + pos] = maximum;
+      if (a->normalizers) a->normalizers[((size_t)sequence * H + h) * S + pos] = denominator;
+      if (a->probs) {
+        float* p = a->probs + (((size_t)sequence * H + h) * S + pos) * S;
+        for (int kp = 0; kp < S; ++kp) p[kp] = kp <= pos ? scores[kp] / denominator : 0.0f;
+      }
+      if (a->out) {
+        for (int d = 0; d < D; ++d) {
+          float value = 0.0f;
+          for (int kp = 0; kp <= pos; ++kp) {
+            const size_t krow = (size_t)sequence * S + kp;
+            value += (scores[kp] / denominator) *
+                     load_act(a->qkv, krow * 3 * E + 2 * E + c0 + d, a->bf16);
+          }
+          store_act(a->out, row * E + c0 + d, a->bf16, value);
+        }
+      }
+    }
+  }
+  free(scores);
+}
+
+int oracle_attention_fwd(const void* qkv, int rows, int context, int heads, int embed, int is_bf16,
+                         int threads, void* out, float* maxima, float* normalizers, float* probs) {
+  if (context <= 0 || heads <= 0 || embed <= 0 || embed % heads || rows <= 0 || rows % context)
+    return 3;
+  mha_t a = {qkv, NULL, NULL, out, maxima, normalizers, NULL, probs, rows, context, heads, embed,
+             is_bf16};
+  parallel_units(rows / context, threads, mha_fwd_sequence, &a);
+  return 0;
+}
+
+/* attention_reference.cc:151-228, one sequence per unit; d_qkv must be zero-filled by the caller
+ * (the reference clears it, :138-140) because keys/values accumulate across later queries. */
+static void mha_bwd_sequence(int sequence, void* ctx) {
+  const mha_t* a = (const mha_t*)ctx;
+  const int S = a->context, H = a->heads, E = a->embed, D = E / H;
+  const float scale = 1.0f / sqrtf((float)D);
+  float* p = (float*)malloc(sizeof(float) * (size_t)S);
+  for (int pos = 0; pos < S; ++pos) {
+    const size_t row = (size_t)sequence * S + pos;
+    for (int h = 0; h < H; ++h) {
+      const int c0 = h * D;
+      float maximum = -INFINITY;
+      for (int kp = 0; kp <= pos; ++kp) {
+        const size_t krow = (size_t)sequence * S + kp;
+        float score = 0.0f;
+        for (int d = 0; d < D; ++d)
+          score += load_act(a->qkv, row * 3 * E + c0 + d, a->bf16) *
+                   load_act(a->qkv, krow * 3 * E + E + c0 + d, a->bf16);
+        p[kp] = score * scale;
+        maximum = fmaxf(maximum, p[kp]);
+      }
+      float denominator = 0.0f;
+      for (int kp = 0; kp <= pos; ++kp) { p[kp] = expf(p[kp] - maximum); denominator += p[kp]; }
+      for (int kp = 0; kp <= pos; ++kp) p[kp] /= denominator;
+      float delta = 0.0f;
+      for (int d = 0; d < D; ++d)
+        delta += a->d_out[row * E + c0 + d] * load_act(a->out_in, row * E + c0 + d, a->bf16);
+      for (int kp = 0; kp <= pos; ++kp) {
+        const size_t krow = (size_t)sequence * S + kp;
+        float dp = 0.0f;
+        for (int d = 0; d < D; ++d)
+          dp += a->d_out[row * E + c0 + d] *
+                load_act(a->qkv, krow * 3 * E + 2 * E + c0 + d, a->bf16);
+        const float ds = p[kp] * (dp - delta);
+        for (int d = 0; d < D; ++d) {
+          const size_t q = row * 3 * E + c0 + d;
+          const size_t k = krow * 3 * E + E + c0 + d;
+          const size_t v = krow * 3 * E + 2 * E + c0 + d;
+          a->d_qkv[q] += ds * load_act(a->qkv, k, a->bf16) * scale;
+          a->d_qkv[k] += ds * load_act(a->qkv, q, a->bf16) * scale;
+          a->d_qkv[v] += p[kp] * a->d_out[row * E + c0 + d];
+        }
+      }
+    }
+  }
+  free(p);
+}
+
+int oracle_attention_bwd(const void* qkv, const void* out, const float* d_out, int rows,
+                         int context, int heads, int embed, int is_bf16, int threads,
+                         float* d_qkv) {
+  if (context <= 0 || heads <= 0 || embed <= 0 || embed % heads || rows <= 0 || rows % context)
+    return 3;
+  memset(d_qkv, 0, sizeof(float) * (size_t)rows * 3 * embed);
+  mha_t a = {qkv, out, d_out, NULL, NULL, NULL, d_qkv, NULL, rows, context, heads, embed, is_bf16};
+  parallel_units(rows / context, threads, mha_bwd_sequence, &a);
+  return 0;
+}
+
+/* ========================================================================================== *
+ * Qwen GQA attention: prepare (RMSNorm + partial RoPE), decode over a cache, sequence core
+ * ========================================================================================== */
+
+/* PrepareAttentionKernel, cached_attention_ops.cc:30-79 (sequence form: qwen_attention.cc:30-63).
+ * One head vector: x[dim] -> out[dim].  weight is zero-centred (multiplier 1+w). */
+void oracle_qk_prepare_head(const float* x, const float* weight, int dim, int rotary, int position,
+                            float epsilon, float theta, int round, float* out) {
+  float square = 0.0f;
+  for (int c = 0; c < dim; ++c) square += x[c] * x[c];
+  const float inverse = 1.0f / sqrtf(square / (float)dim + epsilon);
+  const float log_theta = logf(theta);
+  const int half = rotary / 2;
+  for (int c = 0; c < dim; ++c) {
+    const float n = rnd(x[c] * inverse * (1.0f + weight[c]), round);
+    if (c >= rotary) { out[c] = n; continue; }
+    const int partner = c < half ? c + half : c - half;
+    float rotated = rnd(x[partner] * inverse * (1.0f + weight[partner]), round);
+    if (c < half) rotated = -rotated;
+    const int f = c < half ? c : c - half;
+    const float angle = (float)position * expf((float)f * (-2.0f * log_theta / (float)rotary));
+    const float cosine = rnd(cosf(angle), round), sine = rnd(sinf(angle), round);
+    out[c] = rnd(rnd(n * cosine, round) + rnd(rotated * sine, round), round);
+  }
+}
+
+/* Whole-token prepare: q_gate [Hq,2,D] (query at h*2D), k,v [Hkv,D] -> queries [Hq,D] and the
+ * cache row at `position` of keys/values [capacity,Hkv,D] (fp32 cache as key_value_cache.h:25-57). */
+void oracle_qk_prepare(const float* q_gate, const float* k, const float* v, const float* q_norm,
+                       const float* k_norm, int q_heads, int kv_heads, int dim, int rotary,
+                       int position, float epsilon, float theta, int round, float* queries,
+                       float* keys, float* values) {
+  for (int h = 0; h < q_heads; ++h)
+    oracle_qk_prepare_head(q_gate + (size_t)h * 2 * dim, q_norm, dim, rotary, position, epsilon,
+                           theta, round, queries + (size_t)h * dim);
+  for (int h = 0; h < kv_heads; ++h) {
+    const size_t off = ((size_t)position * kv_heads + h) * dim;
+    oracle_qk_prepare_head(k + (size_t)h * dim, k_norm, dim, rotary, position, epsilon, theta,
+                           round, keys + off);
+    for (int c = 0; c < dim; ++c) values[off + c] = rnd(v[(size_t)h * dim + c], round);
+  }
+}
+
+/* FullAttentionKernel, cached_attention_ops.cc:83-126: one query head, online softmax over the
+ * cached rows 32 at a time in fp32, then the optional sigmoid gate with the reference's rounding
+ * sequence R(R(acc/l) * R(sigmoid(gate))).  K/V rows are `kv_is_bf16 ? bf16 : fp32`, laid out
+ * [length, kv_heads, dim] with `kv_row_stride` elements between rows.  gate may be NULL
+ * (then out = R(acc/l) when round, acc/l otherwise).  stats (optional) receives {max, sum}. */
+static void decode_head(const float* query, const float* gate, const void* keys, const void* values,
+                        int kv_is_bf16, size_t kv_row_stride, int kv_head, int dim, int length,
+                        float scale, int round, float* out, float* stats) {
+  float maximum = -3.402823466e+38f, denominator = 0.0f;
+  float result[256];
+  float score[32], prob[32];
+  for (int c = 0; c < dim; ++c) result[c] = 0.0f;
+  for (int start = 0; start < length; start += 32) {
+    const int n = length - start < 32 ? length - start : 32;
+    float tile_max = -3.402823466e+38f;
+    for (int r = 0; r < n; ++r) {
+      const size_t off = (size_t)(start + r) * kv_row_stride + (size_t)kv_head * dim;
+      float s = 0.0f;
+      for (int c = 0; c < dim; ++c) s += load_act(keys, off + c, kv_is_bf16) * query[c];
+      score[r] = s * scale;
+      tile_max = fmaxf(tile_max, score[r]);
+    }
+    const float next = fmaxf(maximum, tile_max);
+    const float correction = expf(maximum - next);
+    float psum = 0.0f;
+    for (int r = 0; r < n; ++r) { prob[r] = expf(score[r] - next); psum += prob[r]; }
+    for (int c = 0; c < dim; ++c) {
+      float acc = 0.0f;
+      for (int r = 0; r < n; ++r)
+        acc += prob[r] * load_act(values, (size_t)(start + r) * kv_row_stride +
+                                              (size_t)kv_head * dim + c, kv_is_bf16);
+      result[c] = result[c] * correction + acc;
+    }
+    denominator = denominator * correction + psum;
+    maximum = next;
+  }
+  if (stats) { stats[0] = maximum; stats[1] = denominator; }
+  for (int c = 0; c < dim; ++c) {
+    const float core = result[c] / denominator;
+    if (gate) {
+      const float sigmoid = rnd(1.0f / (1.0f + expf(-gate[c])), round);
+      out[c] = rnd(rnd(core, round) * sigmoid, round);
+    } else {
+      out[c] = rnd(core, round);
+    }
+  }
+}
+
+/* One token of one sequence: queries [Hq,D] fp32 (already prepared), gate pointer q_gate
+ * [Hq,2,D] or NULL, output [Hq,D] fp32. */
+void oracle_gqa_decode(const float* queries, const float* q_gate, const void* keys,
+                       const void* values, int kv_is_bf16, int q_heads, int kv_heads, int dim,
+                       int length, int round, float* output) {
+  const float scale = 1.0f / sqrtf((float)dim);
+  for (int h = 0; h < q_heads; ++h)
+    decode_head(queries + (size_t)h * dim, q_gate ? q_gate + ((size_t)h * 2 + 1) * dim : NULL,
+                keys, values, kv_is_bf16, (size_t)kv_heads * dim, h / (q_heads / kv_heads), dim,
+                length, scale, round, output + (size_t)h * dim, NULL);
+}
+
+/* Batched form used for the decode benchmark shape: sequence b has its own cache base pointers
+ * and length; q [B,Hq,D] and out [B,Hq,D] are bf16 bit patterns (q_is_bf16) or fp32. */
+typedef struct {
+  const void* q; const void* const* keys; const void* const* values; const int* lengths;
+  void* out; int q_bf16, kv_bf16, q_heads, kv_heads, dim, round;
+} decode_batch_t;
+static void decode_batch_unit(int unit, void* ctx) {
+  const decode_batch_t* a = (const decode_batch_t*)ctx;
+  const int b = unit / a->q_heads, h = unit % a->q_heads;
+  float query[256], out[256];
+  for (int c = 0; c < a->dim; ++c)
+    query[c] = load_act(a->q, ((size_t)b * a->q_heads + h) * a->dim + c, a->q_bf16);
+  decode_head(query, NULL, a->keys[b], a->values[b], a->kv_bf16, (size_t)a->kv_heads * a->dim,
+              h / (a->q_heads / a->kv_heads), a->dim, a->lengths[b],
+              1.0f / sqrtf((float)a->dim), a->round, out, NULL);
+  for (int c = 0; c < a->dim; ++c)
+    store_act(a->out, ((size_t)b * a->q_heads + h) * a->dim + c, a->q_bf16, out[c]);
+}
+void oracle_gqa_decode_batch(const void* q, const void* const* keys, const void* const* values,
+                             const int* lengths, int batch, int q_is_bf16, int kv_is_bf16,
+                             int q_heads, int kv_heads, int dim, int round, int threads,
+                             void* out) {
+  decode_batch_t a = {q, keys, values, lengths, out, q_is_bf16, kv_is_bf16, q_heads, kv_heads,
+                      dim, round};
+  parallel_units(batch * q_heads, threads, decode_batch_unit, &a);
+}
+
+/* AttentionProbabilitiesKernel, cached_attention_ops.cc:131-178: softmax row [Hq, length]. */
+void oracle_gqa_probabilities(const float* queries, const void* keys, int kv_is_bf16, int q_heads,
+                              int kv_heads, int dim, int length, float* probabilities) {
+  const float scale = 1.0f / sqrtf((float)dim);
+  for (int h = 0; h < q_heads; ++h) {
+    const int kv = h / (q_heads / kv_heads);
+    float* p = probabilities + (size_t)h * length;
+    float maximum = -3.402823466e+38f;
+    for (int t = 0; t < length; ++t) {
+      float s = 0.0f;
+      for (int c = 0; c < dim; ++c)
+        s += load_act(keys, ((size_t)t * kv_heads + kv) * dim + c, kv_is_bf16) *
+             queries[(size_t)h * dim + c];
+      p[t] = s * scale;
+      maximum = fmaxf(maximum, p[t]);
+    }
+    float denominator = 0.0f;
+    for (int t = 0; t < length; ++t) denominator += expf(p[t] - maximum);
+    for (int t = 0; t < length; ++t) p[t] = expf(p[t] - maximum) / denominator;
+  }
+}
+
+/* Attention core of ForwardKernel, qwen_attention.cc:68-119, for a whole sequence:
+ * q [T,Hq,D] with q_token_stride elements between tokens and q_head_stride between heads (so the
+ * stride-2D view into [T,Hq,2,D] works), k,v [T,Hkv,D]; causal; 32-key online tiles.  Storage is
+ * bf16 bit patterns when is_bf16.  gate (same indexing as q, or NULL).  out [T,Hq,D] (same
+ * storage type); core (optional fp32 [T,Hq,D]) receives the unrounded acc/l; lse (optional
+ * [Hq,T]) receives max + log(sum). */
+typedef struct {
+  const void* q; const void* gate; const void* k; const void* v; void* out; float* core;
+  float* lse; int bf16, T, q_heads, kv_heads, dim, round; size_t q_token_stride, q_head_stride;
+  int unit_base;
+} prefill_t;
+static void prefill_unit(int unit, void* ctx) {
+  const prefill_t* a = (const prefill_t*)ctx;
+  const int row = (unit + a->unit_base) / a->q_heads, h = (unit + a->unit_base) % a->q_heads;
+  const int D = a->dim;
+  float query[256], gate[256], out[256], stats[2];
+  const size_t qoff = (size_t)row * a->q_token_stride + (size_t)h * a->q_head_stride;
+  for (int c = 0; c < D; ++c) query[c] = load_act(a->q, qoff + c, a->bf16);
+  if (a->gate)
+    for (int c = 0; c < D; ++c) gate[c] = load_act(a->gate, qoff + c, a->bf16);
+  /* unrounded core first (round = 0, no gate), then the output rounding sequence */
+  decode_head(query, NULL, a->k, a->v, a->bf16, (size_t)a->kv_heads * D,
+              h / (a->q_heads / a->kv_heads), D, row + 1, 1.0f / sqrtf((float)D), 0, out, stats);
+  const size_t ooff = ((size_t)row * a->q_heads + h) * D;
+  if (a->core) for (int c = 0; c < D; ++c) a->core[ooff + c] = out[c];
+  if (a->lse) a->lse[(size_t)h * a->T + row] = stats[0] + logf(stats[1]);
+  for (int c = 0; c < D; ++c) {
+    float y;
+    if (a->gate) {
+      const float sigmoid = rnd(1.0f / (1.0f + expf(-gate[c])), a->round);
+      y = rnd(rnd(out[c], a->round) * sigmoid, a->round);
+    } else {
+      y = rnd(out[c], a->round);
+    }
+    store_act(a->out, ooff + c, a->bf16, y);
+  }
+}
+void oracle_gqa_prefill(const void* q, const void* gate, const void* k, const void* v, int is_bf16,
+                        int T, int q_heads, int kv_heads, int dim, size_t q_token_stride,
+                        size_t q_head_stride, int round, int threads, int row_begin, int row_end,
+                        void* out, float* core, float* lse) {
+  /* units are (row, head); a row range lets a caller check a sample of a long sequence */
+  if (row_begin < 0) row_begin = 0;
+  if (row_end > T) row_end = T;
+  if (row_end <= row_begin) return;
+  prefill_t a = {q, gate, k, v, out, core, lse, is_bf16, T, q_heads, kv_heads, dim, round,
+                 q_token_stride, q_head_stride, row_begin * q_heads};
+  parallel_units((row_end - row_begin) * q_heads, threads, prefill_unit, &a);
+}
+
+/* ========================================================================================== *
+ * Gated delta-net
+ * ========================================================================================== */
+
+/* decay gate of DeltaRecurrenceKernel, cached_attention_ops.cc:231-236:
+ * g = exp(-exp(A_log) * softplus(a + dt_bias)), softplus in its overflow-safe form. */
+float oracle_gdn_decay(float a, float dt_bias, float a_log) {
+  const float alpha = a + dt_bias;
+  const float softplus = fmaxf(alpha, 0.0f) + logf(1.0f + expf(-fabsf(alpha)));
+  return expf(-expf(a_log) * softplus);
+}
+float oracle_gdn_beta(float b, int round) { return rnd(1.0f / (1.0f + expf(-b)), round); }
+
+/* The recurrence of RecurrenceForward (sequence_delta_net.cc:55-102) / DeltaRecurrenceKernel
+ * (cached_attention_ops.cc:205-251) for one (batch, value head) over T tokens:
+ *     q^ = q * rsqrt(sum q^2 + 1e-6) / sqrt(dk),  k^ = k * rsqrt(sum k^2 + 1e-6)   [normalize_qk]
+ *     S <- g_t S ;  delta = (v_t - S^T k^) * beta_t ;  S <- S + k^ (x) delta ;  o_t = R(S^T q^)
+ * q,k: [B,T,Hk,dk]; v,out: [B,T,Hv,dv]; g,beta: fp32 [B,T,Hv]; state fp32 [B,Hv,dk,dv], updated
+ * in place (zero it for a prefill from scratch).  q,k,v,out are bf16 bit patterns when is_bf16.
+ * When normalize_qk == 0 the vectors are used as given and q is multiplied by q_scale. */
+typedef struct {
+  const void* q; const void* k; const void* v; const float* g; const float* beta; float* state;
+  void* out; int bf16, B, T, Hk, Hv, dk, dv, normalize, round; float q_scale;
+} gdn_t;
+static void gdn_unit(int unit, void* ctx) {
+  const gdn_t* a = (const gdn_t*)ctx;
+  const int b = unit / a->Hv, h = unit % a->Hv, kh = h / (a->Hv / a->Hk);
+  const int dk = a->dk, dv = a->dv;
+  float* S = a->state + ((size_t)b * a->Hv + h) * dk * dv;
+  float q[128], k[128];
+  for (int t = 0; t < a->T; ++t) {
+    const size_t qk = (((size_t)b * a->T + t) * a->Hk + kh) * dk;
+    const size_t vo = (((size_t)b * a->T + t) * a->Hv + h) * dv;
+    float qs = 0.0f, ks = 0.0f;
+    for (int i = 0; i < dk; ++i) {
+      q[i] = load_act(a->q, qk + i, a->bf16);
+      k[i] = load_act(a->k, qk + i, a->bf16);
+      qs += q[i] * q[i];
+      ks += k[i] * k[i];
+    }
+    if (a->normalize) {
+      const float qn = (1.0f / sqrtf(qs + 1e-6f)) / sqrtf((float)dk);
+      const float kn = 1.0f / sqrtf(ks + 1e-6f);
+      for (int i = 0; i < dk; ++i) { q[i] *= qn; k[i] *= kn; }
+    } else {
+      for (int i = 0; i < dk; ++i) q[i] *= a->q_scale;
+    }
+    const float decay = a->g[((size_t)b * a->T + t) * a->Hv + h];
+    const float beta = a->beta[((size_t)b * a->T + t) * a->Hv + h];
+    for (int j = 0; j < dv; ++j) {
+      float prediction = 0.0f;
+      for (int i = 0; i < dk; ++i) {
+        S[(size_t)i * dv + j] *= decay;
+        prediction += S[(size_t)i * dv + j] * k[i];
+      }
+      const float delta = (load_act(a->v, vo + j, a->bf16) - prediction) * beta;
+      float core = 0.0f;
+      for (int i = 0; i < dk; ++i) {
+        S[(size_t)i * dv + j] += k[i] * delta;
+        core += S[(size_t)i * dv + j] * q[i];
+      }
+      store_act(a->out, vo + j, a->bf16, rnd(core, a->round));
+    }
+  }
+}
+int oracle_gdn_recurrence(const void* q, const void* k, const void* v, const float* g,
+                          const float* beta, int is_bf16, int B, int T, int Hk, int Hv, int dk,
+                          int dv, int normalize_qk, float q_scale, int round, int threads,
+                          float* state, void* out) {
+  if (dk > 128 || dv > 256 || Hk <= 0 || Hv % Hk) return 3;
+  gdn_t a = {q, k, v, g, beta, state, out, is_bf16, B, T, Hk, Hv, dk, dv, normalize_qk, round,
+             q_scale};
+  parallel_units(B * Hv, threads, gdn_unit, &a);
+  return 0;
+}
+
+/* ConvolutionKernel (cached_attention_ops.cc:180-203): single-token causal depthwise conv over a
+ * shift-register state [channels, width] followed by SiLU.  ConvForward
+ * (sequence_delta_net.cc:31-51) is the same arithmetic with an explicit zero history. */
+void oracle_gdn_conv_step(const float* input, const float* weight, int channels, int width,
+                          int round, float* state, float* output) {
+  for (int c = 0; c < channels; ++c) {
+    float sum = 0.0f;
+    for (int tap = 0; tap < width - 1; ++tap) {
+      const float previous = state[(size_t)c * width + tap + 1];
+      sum += previous * weight[(size_t)c * width + tap];
+      state[(size_t)c * width + tap] = previous;
+    }
+    const float current = rnd(input[c], round);
+    state[(size_t)c * width + width - 1] = current;
+    sum = rnd(sum + current * weight[(size_t)c * width + width - 1], round);
+    output[c] = rnd(sum / (1.0f + expf(-sum)), round);
+  }
+}
+
+/* DeltaOutputKernel (cached_attention_ops.cc:253-272): per head RMSNorm * weight * SiLU(z) with
+ * a rounding after each product.  final_round = 0 reproduces OutputForward
+ * (sequence_delta_net.cc:104-121), which leaves the last product unrounded before its bf16 store. */
+void oracle_gdn_output(const float* core, const float* z, const float* norm_weight, int heads,
+                       int dim, float epsilon, int round, int final_round, float* output) {
+  for (int h = 0; h < heads; ++h) {
+    float square = 0.0f;
+    for (int c = 0; c < dim; ++c) square += core[(size_t)h * dim + c] * core[(size_t)h * dim + c];
+    const float inverse = 1.0f / sqrtf(square / (float)dim + epsilon);
+    for (int c = 0; c < dim; ++c) {
+      const float normalized = rnd(core[(size_t)h * dim + c] * inverse, round);
+      const float affine = rnd(normalized * norm_weight[c], round);
+      const float gate = z[(size_t)h * dim + c];
+      const float silu = gate / (1.0f + expf(-gate));
+      output[(size_t)h * dim + c] = rnd(affine * silu, round && final_round);
+    }
+  }
+}

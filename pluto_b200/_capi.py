@@ -1,0 +1,73 @@
+"""ctypes binding of the C ABI in include/pluto_b200.h.
+
+The shared library is built in-tree by `pluto_b200.build`; if it is missing this module raises
+immediately -- there is no CPU or PyTorch fallback for any operation of the engine.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libpluto_b200.so")
+
+
+class PlutoStatusError(RuntimeError):
+    """Non-OK return of a C entry point.  `code` uses absl::StatusCode names."""
+
+    def __init__(self, code: str, message: str, raw: int):
+        super().__init__(f"{code}: {message}")
+        self.code = code
+        self.message = message
+        self.raw = raw
+
+
+_CODES = {-1: "InvalidArgument", -2: "Unimplemented", -3: "ResourceExhausted", -4: "Internal"}
+
+_vp, _i, _sz, _fp = C.c_void_p, C.c_int, C.c_size_t, C.c_float
+_SIGNATURES = {
+    "pluto_last_error": (C.c_char_p, []),
+    "pluto_build_info": (C.c_char_p, []),
+    "pluto_kernel_status": (_i, [C.POINTER(C.c_uint32), _i]),
+    "pluto_attn_fwd": (_i, [_vp] * 5 + [_i] * 5),
+    "pluto_attn_bwd": (_i, [_vp] * 8 + [_i] * 5),
+    "pluto_attn_probs": (_i, [_vp] * 5 + [_i] * 5),
+    "pluto_gqa_prefill_fwd": (_i, [_vp] * 9 + [_i] * 5 + [_sz, _sz, _i]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build the CUDA engine with `python -m pluto_b200.build` "
+                "(there is no fallback path)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the library lacks a declared symbol
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def exported_symbols():
+    return sorted(_SIGNATURES)
+
+
+def check(code: int) -> None:
+    if code == 0:
+        return
+    message = lib().pluto_last_error().decode()
+    if code < 0:
+        raise PlutoStatusError(_CODES.get(code, "Unknown"), message, code)
+    raise PlutoStatusError("Internal", message, code)
+
+
+def kernel_status(clear: bool = True) -> int:
+    value = C.c_uint32(0)
+    check(lib().pluto_kernel_status(C.byref(value), int(clear)))
+    return value.value

@@ -1,0 +1,409 @@
+// Causal softmax attention forward on the Blackwell tensor cores (bf16 operands, fp32
+// accumulation), head width 64 or 128.  One kernel serves both layers on the hot path:
+//   * AttentionLayer forward over the packed [rows, 3E] activation
+//     (reference: src/llm/layers/attention.cc:98-170, 418-507), writing O plus the row maximum
+//     and row normaliser the backward pass reuses;
+//   * the attention core of QwenAttentionLayer's sequence forward with grouped query heads
+//     (reference: src/llm/layers/qwen_attention.cc:68-119), with the optional sigmoid output gate
+//     and its rounding sequence R(R(core) * R(sigmoid(gate))).
+//
+// Structure of one CTA (256 threads) = one 128-row query tile of one (sequence, query head):
+//   warp 0      TMA producer: Q once, then K_j / V_j tiles of 128 keys into a 2-stage ring
+//               (128-byte swizzled boxes of 64 columns; no multicast).
+//   warp 1      tcgen05.mma issuer: S_j = Q K_j^T into one of two 128-column TMEM buffers,
+//               then O += P_j V_j with P_j read straight from TMEM (it overwrites S_j in place
+//               as packed bf16) and V_j as an MN-major shared-memory operand.
+//   warps 4-7   one thread per query row (TMEM lane): tcgen05.ld the score row, online softmax
+//               in fp32 with exp2, lazy rescaling of the O accumulator (only when the running
+//               maximum grew by more than 2^8), tcgen05.st of P, final normalise and store.
+// QK^T of tile j+1 is issued before PV of tile j, so the tensor pipe works on the next score tile
+// while the softmax warps are busy with the current one.
+#include "common.cuh"
+#include "engine.h"
+
+namespace pluto {
+namespace {
+
+constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBN = 128;          // keys per tile
+constexpr int kStages = 2;        // K/V ring depth
+constexpr int kThreadsFwd = 256;
+constexpr int kSlabBytes = 128 * 64 * 2;  // one [128 rows x 64 bf16] swizzled slab
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct FwdParams {
+  // column (innermost) coordinate of head 0 in each tensor map, and per-head column step
+  int q_col0, k_col0, v_col0;
+  int q_head_cols, kv_head_cols;
+  int seq, heads, group;
+  float scale_log2;  // softmax scale * log2(e)
+  float scale;
+  // outputs
+  __nv_bfloat16* out;          // [batch*seq, heads, D] with out_token/out_head element strides
+  size_t out_token, out_head;
+  float* maxima;               // optional, [(b*H+h)*S + s]
+  float* normalizers;          // optional
+  float* core;                 // optional fp32 copy of the ungated result, same indexing as out
+  const __nv_bfloat16* gate;   // optional, indexed like q: token stride gate_token, head stride gate_head
+  size_t gate_token, gate_head;
+  int round_gate;              // apply bf16 rounding inside the gate product (reference behaviour)
+  uint32_t* status;
+};
+
+struct Barriers {
+  uint64_t q_full;
+  uint64_t k_full[kStages], k_empty[kStages];
+  uint64_t v_full[kStages], v_empty[kStages];
+  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint32_t tmem_base;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreadsFwd, 1)
+attn_fwd_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, FwdParams p) {
+  constexpr int kSlabs = D / 64;
+  constexpr int kTileBytes = kSlabs * kSlabBytes;  // one Q, K or V tile
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColO = 256;
+  constexpr uint32_t kIdescQK = umma_idesc_bf16(kBM, kBN, false);
+  constexpr uint32_t kIdescPV = umma_idesc_bf16(kBM, D, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* k_smem = q_smem + kTileBytes;
+  uint8_t* v_smem = k_smem + kStages * kTileBytes;
+  Barriers* bar = reinterpret_cast<Barriers*>(v_smem + kStages * kTileBytes);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int q_tile = gridDim.x - 1 - blockIdx.x;  // heaviest (latest) tiles first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int n_tiles = q_tile + 1;                 // causal: key tiles 0..q_tile
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bar->k_full[s], 1);
+      mbar_init(&bar->k_empty[s], 1);
+      mbar_init(&bar->v_full[s], 1);
+      mbar_init(&bar->v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar->s_full[s], 1);
+      mbar_init(&bar->p_full[s], 128);
+      mbar_init(&bar->pv_done[s], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      const int kv_head = head / p.group;
+      mbar_expect_tx(&bar->q_full, kTileBytes);
+      for (int s = 0; s < kSlabs; ++s)
+        tma_load_3d(q_smem + s * kSlabBytes, &map_q, p.q_col0 + head * p.q_head_cols + s * 64,
+                    q_tile * kBM, batch, &bar->q_full);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % kStages, use = j / kStages;
+        if (use > 0) ok = mbar_wait(&bar->k_empty[st], (use - 1) & 1, p.status, 1);
+        if (!ok) break;
+        mbar_expect_tx(&bar->k_full[st], kTileBytes);
+        for (int s = 0; s < kSlabs; ++s)
+          tma_load_3d(k_smem + st * kTileBytes + s * kSlabBytes, &map_k,
+                      p.k_col0 + kv_head * p.kv_head_cols + s * 64, j * kBN, batch,
+                      &bar->k_full[st]);
+        if (use > 0) ok = mbar_wait(&bar->v_empty[st], (use - 1) & 1, p.status, 2);
+        if (!ok) break;
+        mbar_expect_tx(&bar->v_full[st], kTileBytes);
+        for (int s = 0; s < kSlabs; ++s)
+          tma_load_3d(v_smem + st * kTileBytes + s * kSlabBytes, &map_v,
+                      p.v_col0 + kv_head * p.kv_head_cols + s * 64, j * kBN, batch,
+                      &bar->v_full[st]);
+      }
+      // Before leaving, make sure every copy this thread started has landed (bounded): nothing
+      // may still be writing this CTA's shared memory when it exits.
+      mbar_wait(&bar->q_full, 0, p.status, 3);
+      for (int j = max(0, n_tiles - kStages); j < n_tiles; ++j) {
+        mbar_wait(&bar->k_full[j % kStages], (j / kStages) & 1, p.status, 4);
+        mbar_wait(&bar->v_full[j % kStages], (j / kStages) & 1, p.status, 5);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(&bar->q_full, 0, p.status, 10);
+      tc_fence_after();
+      auto issue_pv = [&](int i) -> bool {
+        const int sb = i & 1, st = i % kStages;
+        if (!mbar_wait(&bar->p_full[sb], (i >> 1) & 1, p.status, 11)) return false;
+        if (!mbar_wait(&bar->v_full[st], (i / kStages) & 1, p.status, 12)) return false;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(v_smem + st * kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          // B = V tile, MN-major: 16 key rows per step (2048 bytes), 64-column slabs kBN*128 apart
+          const uint64_t b_desc = umma_desc_sw128(v_addr + ks * 2048, kSlabBytes, 1024);
+          umma_ts(tmem + kColO, tmem + kColS + sb * 128 + ks * 8, b_desc, kIdescPV,
+                  i > 0 || ks > 0);
+        }
+        tc_commit(&bar->pv_done[sb]);
+        tc_commit(&bar->v_empty[st]);
+        return true;
+      };
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int sb = j & 1, st = j % kStages;
+        ok = mbar_wait(&bar->k_full[st], (j / kStages) & 1, p.status, 13);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(q_smem);
+        const uint32_t k_addr = smem_u32(k_smem + st * kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * kSlabBytes + (ks % 4) * 32;
+          umma_ss(tmem + kColS + sb * 128, umma_desc_sw128(q_addr + off, 16, 1024),
+                  umma_desc_sw128(k_addr + off, 16, 1024), kIdescQK, ks > 0);
+        }
+        tc_commit(&bar->s_full[sb]);
+        tc_commit(&bar->k_empty[st]);
+        if (j > 0) ok = issue_pv(j - 1);
+      }
+      if (ok) issue_pv(n_tiles - 1);
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax / epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;             // row inside the query tile == TMEM lane
+    const int query = q_tile * kBM + row;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    float m_used = -INFINITY;   // maximum the accumulators are expressed against (raw scores)
+    float m_true = -INFINITY;   // true running maximum (raw scores)
+    float l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int sb = j & 1;
+      ok = mbar_wait(&bar->s_full[sb], (j >> 1) & 1, p.status, 20);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s[4][32];
+      const uint32_t s_addr = tmem + lane_base + kColS + sb * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
+      tmem_wait_ld();
+      float tile_max = -INFINITY;
+      if (j == q_tile) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (c * 32 + i > row) s[c][i] = 0xff800000u;  // -inf above the diagonal
+            tile_max = fmaxf(tile_max, __uint_as_float(s[c][i]));
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(s[c][i]));
+      }
+      m_true = fmaxf(m_true, tile_max);
+      const bool grow = (m_true - m_used) * p.scale_log2 > kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float factor = grow ? fast_exp2((m_used - m_true) * p.scale_log2) : 1.0f;
+        if (grow) m_used = m_true;
+        l *= factor;
+        if (j > 0) {
+          // the previous PV must have landed in O before O is rescaled
+          ok = mbar_wait(&bar->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, p.status, 21);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem + lane_base + kColO + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st32(tmem + lane_base + kColO + c * 32, o);
+          }
+        }
+      }
+      const float neg_m = -m_used * p.scale_log2;
+      float row_sum = 0.0f;
+      uint32_t packed[2][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), p.scale_log2, neg_m));
+          row_sum += p0 + p1;
+          packed[c / 2][(c % 2) * 16 + i / 2] = pack_bf16(p0, p1);
+        }
+      l += row_sum;
+      tmem_st32(s_addr, packed[0]);
+      tmem_st32(s_addr + 32, packed[1]);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->p_full[sb]);
+    }
+    if (ok) ok = mbar_wait(&bar->pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, p.status, 22);
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      const bool live = query < p.seq;
+      const size_t token = static_cast<size_t>(batch) * p.seq + query;
+      __nv_bfloat16* out = p.out + token * p.out_token + head * p.out_head;
+      float* core = p.core ? p.core + token * p.out_token + head * p.out_head : nullptr;
+      const __nv_bfloat16* gate =
+          p.gate ? p.gate + token * p.gate_token + head * p.gate_head : nullptr;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem + lane_base + kColO + c * 32, o);
+        tmem_wait_ld();
+        if (live) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float a = __uint_as_float(o[i]) * inv, b = __uint_as_float(o[i + 1]) * inv;
+            if (core) {
+              core[c * 32 + i] = a;
+              core[c * 32 + i + 1] = b;
+            }
+            if (gate) {
+              const float g0 = __bfloat162float(gate[c * 32 + i]);
+              const float g1 = __bfloat162float(gate[c * 32 + i + 1]);
+              float s0 = 1.0f / (1.0f + expf(-g0)), s1 = 1.0f / (1.0f + expf(-g1));
+              if (p.round_gate) {
+                s0 = bf16_round(s0);
+                s1 = bf16_round(s1);
+                a = bf16_round(a);
+                b = bf16_round(b);
+              }
+              a *= s0;
+              b *= s1;
+            }
+            w[i / 2] = pack_bf16(a, b);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(out + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      }
+      if (live && p.maxima) {
+        const size_t stat = (static_cast<size_t>(batch) * p.heads + head) * p.seq + query;
+        p.maxima[stat] = m_true * p.scale;
+        p.normalizers[stat] = l * fast_exp2((m_used - m_true) * p.scale_log2);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) !=
+            cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      return static_cast<EncodeTiled>(nullptr);
+    return reinterpret_cast<EncodeTiled>(sym);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+// bf16 tensor [batch][seq][cols] with `token_stride` elements between tokens; box = 64 columns x
+// `box_rows` tokens, 128-byte swizzle, out-of-range reads return zero.
+bool make_token_map(CUtensorMap* map, const void* base, int cols, int seq, int batch,
+                    size_t token_stride, int box_rows) {
+  EncodeTiled encode = encode_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(seq),
+                              static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[2] = {token_stride * 2, token_stride * 2 * static_cast<cuuint64_t>(seq)};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+         CUDA_SUCCESS;
+}
+
+// See engine.h for the contract.  Returns cudaErrorInvalidValue when a tensor map cannot be
+// encoded (misaligned base or stride).
+cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_token_map(&map_q, a.q, a.q_cols, a.seq, a.batch, a.q_token, kBM) ||
+      !make_token_map(&map_k, a.k, a.kv_cols, a.seq, a.batch, a.kv_token, kBN) ||
+      !make_token_map(&map_v, a.v, a.kv_cols, a.seq, a.batch, a.kv_token, kBN))
+    return cudaErrorInvalidValue;
+  FwdParams p;
+  p.q_col0 = a.q_col0;
+  p.k_col0 = a.k_col0;
+  p.v_col0 = a.v_col0;
+  p.q_head_cols = a.q_head_cols;
+  p.kv_head_cols = a.head_dim;
+  p.seq = a.seq;
+  p.heads = a.heads;
+  p.group = a.group;
+  p.scale = 1.0f / sqrtf(static_cast<float>(a.head_dim));
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.out = static_cast<__nv_bfloat16*>(a.out);
+  p.out_token = a.out_token;
+  p.out_head = a.out_head;
+  p.maxima = a.maxima;
+  p.normalizers = a.normalizers;
+  p.core = a.core;
+  p.gate = static_cast<const __nv_bfloat16*>(a.gate);
+  p.gate_token = a.gate_token;
+  p.gate_head = a.gate_head;
+  p.round_gate = a.round_gate;
+  p.status = a.status;
+  const dim3 grid((a.seq + kBM - 1) / kBM, a.heads, a.batch);
+  const size_t tile = static_cast<size_t>(a.head_dim / 64) * kSlabBytes;
+  const size_t smem = 1024 + tile * (1 + 2 * kStages) + sizeof(Barriers);
+  cudaError_t e;
+  if (a.head_dim == 128) {
+    e = cudaFuncSetAttribute(attn_fwd_sm100<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    attn_fwd_sm100<128><<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, p);
+  } else if (a.head_dim == 64) {
+    e = cudaFuncSetAttribute(attn_fwd_sm100<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    attn_fwd_sm100<64><<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, p);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace pluto
