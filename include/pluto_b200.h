@@ -109,6 +109,128 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
                           int head_dim, size_t q_token_stride, size_t q_head_stride,
                           int round_to_bf16);
 
+/* --------------------------------------------------------------------------------------------
+ * KV cache addressing shared by prepare and decode.  The reference keeps one KeyValueCache per
+ * sequence: two fp32 buffers [capacity, kv_heads, head_dim] plus a position counter
+ * (src/llm/key_value_cache.h:25-57).  Every value it stores is already rounded to bf16 when
+ * round_to_bfloat16 is set (cached_attention_ops.cc:48,64-67,76), so a bf16 cache holds the same
+ * numbers in half the bytes; both storage types are accepted.
+ * Token t of sequence b, kv head h starts at element
+ *     page(b, t) * page_stride + (t % page_size) * token_stride + h * head_dim
+ * with page(b, t) = block_table ? block_table[b * max_blocks + t / page_size] : b.
+ * One contiguous [capacity, kv_heads, head_dim] region per sequence is block_table = NULL,
+ * page_size = capacity, page_stride = capacity * kv_heads * head_dim,
+ * token_stride = kv_heads * head_dim.  The position counter stays with the caller. */
+typedef struct pluto_kv_cache {
+  void* k_base;
+  void* v_base;
+  const int32_t* block_table; /* device int32 [batch, max_blocks] or NULL */
+  int max_blocks;
+  int page_size;
+  size_t page_stride;  /* elements */
+  size_t token_stride; /* elements */
+  int dtype;           /* PLUTO_BF16 or PLUTO_FP32 */
+} pluto_kv_cache;
+
+/* Per-head RMSNorm(1+w) -> bf16 rounding -> split-half partial RoPE of queries and keys, and the
+ * append of the new K/V rows to the cache.  Stands in for PrepareAttentionKernel
+ * (src/llm/layers/util/cached_attention_ops.cc:30-79) and PrepareKernel
+ * (src/llm/layers/qwen_attention.cc:30-63).
+ *   q_in         token (b,t), head h at q_in + (b*tokens+t)*q_token_stride + h*q_head_stride;
+ *                [.., Hq, 2, D] query halves are (2*Hq*D, 2*D).  k_in, v_in [batch*tokens, Hkv, D].
+ *                in_dtype says whether these three are fp32 or bf16.
+ *   q_norm, k_norm   fp32 [head_dim], zero-centred (multiplier 1 + w)
+ *   positions    device int32 [batch] position of token 0 of each sequence (NULL = 0): the cache
+ *                row written and the RoPE angle use positions[b] + t
+ *   q_out        [batch*tokens, Hq, D] in q_out_dtype
+ *   rotary_dim even, <= head_dim; head_dim <= 256. */
+int pluto_qk_prepare(pluto_stream_t stream, const void* q_in, const void* k_in, const void* v_in,
+                     int in_dtype, size_t q_token_stride, size_t q_head_stride,
+                     const float* q_norm, const float* k_norm, const int32_t* positions,
+                     void* q_out, int q_out_dtype, const pluto_kv_cache* cache /* host */,
+                     int batch, int tokens, int q_heads, int kv_heads, int head_dim,
+                     int rotary_dim, float rms_norm_epsilon, float rope_theta, int round_to_bf16);
+
+/* Bytes of scratch pluto_gqa_decode needs for split-KV partial results (host-only query). */
+size_t pluto_gqa_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim,
+                                        int max_seq_len);
+
+/* One new query token per sequence against the cache.  Stands in for FullAttentionKernel and the
+ * launch sequence of CachedAttentionStep (src/llm/layers/util/cached_attention_ops.cc:83-126,
+ * :308-353) with a batch dimension added (the reference is batch one).
+ *   q            [batch, Hq, D] prepared queries (q_dtype)
+ *   gate         optional; element (b,h,d) at gate + b*gate_token_stride + h*gate_head_stride + d
+ *                ([B,Hq,2,D]: pass base + D, strides (2*Hq*D, 2*D)); out = R(R(core)*R(sigmoid))
+ *   seq_lens     device int32 [batch]: tokens to attend to (position + 1, each >= 1)
+ *   max_seq_len  host upper bound of seq_lens (sizes the grid; no device read-back)
+ *   out          [batch, Hq, D] (out_dtype);  lse optional fp32 [batch, Hq]
+ *   workspace    >= pluto_gqa_decode_workspace_bytes(...) bytes, 16-byte aligned
+ * bf16 cache with head_dim 64/128 takes the bandwidth-bound path (bulk copies + mma); anything
+ * else the exact fp32 path.  The result does not depend on which SM ran which chunk. */
+int pluto_gqa_decode(pluto_stream_t stream, const void* q, int q_dtype, const void* gate,
+                     int gate_dtype, size_t gate_token_stride, size_t gate_head_stride,
+                     const pluto_kv_cache* cache /* host */, const int32_t* seq_lens,
+                     int max_seq_len, void* out, int out_dtype, float* lse, void* workspace,
+                     size_t workspace_bytes, int batch, int q_heads, int kv_heads, int head_dim,
+                     int round_to_bf16);
+
+/* Softmax row of the current query for the inspection hook.  Stands in for the cached
+ * AttentionProbabilitiesKernel (cached_attention_ops.cc:131-178).  probs: fp32, row (b,h) at
+ * probs + (b*Hq + h)*probs_stride, seq_lens[b] entries written. */
+int pluto_gqa_decode_probs(pluto_stream_t stream, const void* q, int q_dtype,
+                           const pluto_kv_cache* cache /* host */, const int32_t* seq_lens,
+                           float* probs, size_t probs_stride, int batch, int q_heads,
+                           int kv_heads, int head_dim);
+
+/* --------------------------------------------------------------------------------------------
+ * Gated delta-net.
+ * pluto_gdn_gates: g = exp(-exp(A_log) * softplus(a + dt_bias)), beta = R(sigmoid(b)); the decay
+ * and write-strength arithmetic of DeltaRecurrenceKernel (cached_attention_ops.cc:231-238).
+ * a, b: [tokens, heads] (in_dtype); A_log, dt_bias fp32 [heads]; g, beta fp32 [tokens, heads]. */
+int pluto_gdn_gates(pluto_stream_t stream, const void* a, const void* b, const float* a_log,
+                    const float* dt_bias, int in_dtype, long long tokens, int heads,
+                    int round_to_bf16, float* g, float* beta);
+
+/* Causal depthwise convolution + SiLU.  Stands in for ConvolutionKernel
+ * (cached_attention_ops.cc:180-203; tokens = 1) and ConvForward (sequence_delta_net.cc:31-51).
+ * input/output [batch, tokens, channels]; weight fp32 [channels, width] oldest to newest;
+ * state fp32 [batch, channels, width]: the last `width` rounded inputs, updated in place (zero it
+ * for a fresh sequence).  width <= 32. */
+int pluto_gdn_conv_silu(pluto_stream_t stream, const void* input, const float* weight,
+                        int in_dtype, int batch, int tokens, int channels, int width,
+                        int round_to_bf16, float* state, void* output, int out_dtype);
+
+/* The recurrence over `tokens` tokens from the given state.  Stands in for RecurrenceForward
+ * (src/llm/layers/sequence_delta_net.cc:55-102) without its per-token state history; with
+ * tokens = 1 it is DeltaRecurrenceKernel (cached_attention_ops.cc:205-251).
+ *   q, k         [batch, tokens, key_heads, key_dim];  v, out [batch, tokens, value_heads, value_dim]
+ *   g, beta      fp32 [batch, tokens, value_heads]
+ *   state        fp32 [batch, value_heads, key_dim, value_dim], read and updated in place
+ *   normalize_qk 1: q^ = q*rsqrt(sum q^2 + 1e-6)/sqrt(key_dim), k^ = k*rsqrt(sum k^2 + 1e-6) as
+ *                the reference; 0: use k as given and q * q_scale
+ * key_dim <= 128, value_dim <= 256, value_heads % key_heads == 0. */
+int pluto_gdn_prefill(pluto_stream_t stream, const void* q, const void* k, const void* v,
+                      int in_dtype, const float* g, const float* beta, float* state, void* out,
+                      int out_dtype, int batch, int tokens, int key_heads, int value_heads,
+                      int key_dim, int value_dim, int normalize_qk, float q_scale,
+                      int round_to_bf16);
+
+/* Single-token form of pluto_gdn_prefill (tokens = 1): DeltaRecurrenceKernel as launched by
+ * DeltaNetState::Step (src/llm/layers/util/cached_attention_ops.cc:205-251, :401-431). */
+int pluto_gdn_step(pluto_stream_t stream, const void* q, const void* k, const void* v,
+                   int in_dtype, const float* g, const float* beta, float* state, void* out,
+                   int out_dtype, int batch, int key_heads, int value_heads, int key_dim,
+                   int value_dim, int normalize_qk, float q_scale, int round_to_bf16);
+
+/* Per (token, head) RMSNorm * weight * SiLU(z).  Stands in for DeltaOutputKernel
+ * (cached_attention_ops.cc:253-272; final_round = 1) and OutputForward
+ * (sequence_delta_net.cc:104-121; final_round = 0: last product stored without the extra
+ * rounding).  core, z, out: [rows, dim]; norm_weight fp32 [dim] (plain multiplier). */
+int pluto_gdn_out_norm_gate(pluto_stream_t stream, const void* core, int core_dtype, const void* z,
+                            int z_dtype, const float* norm_weight, long long rows, int dim,
+                            float rms_norm_epsilon, int round_to_bf16, int final_round, void* out,
+                            int out_dtype);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

@@ -33,7 +33,25 @@ _SIGNATURES = {
     "pluto_attn_bwd": (_i, [_vp] * 8 + [_i] * 5),
     "pluto_attn_probs": (_i, [_vp] * 5 + [_i] * 5),
     "pluto_gqa_prefill_fwd": (_i, [_vp] * 9 + [_i] * 5 + [_sz, _sz, _i]),
+    "pluto_qk_prepare": (_i, [_vp] * 4 + [_i, _sz, _sz] + [_vp] * 4 + [_i, _vp] + [_i] * 6
+                         + [_fp, _fp, _i]),
+    "pluto_gqa_decode_workspace_bytes": (_sz, [_i] * 5),
+    "pluto_gqa_decode": (_i, [_vp, _vp, _i, _vp, _i, _sz, _sz, _vp, _vp, _i, _vp, _i, _vp, _vp,
+                              _sz] + [_i] * 5),
+    "pluto_gqa_decode_probs": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _sz] + [_i] * 4),
+    "pluto_gdn_gates": (_i, [_vp] * 5 + [_i, C.c_longlong, _i, _i, _vp, _vp]),
+    "pluto_gdn_conv_silu": (_i, [_vp] * 3 + [_i] * 6 + [_vp, _vp, _i]),
+    "pluto_gdn_prefill": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 8 + [_fp, _i]),
+    "pluto_gdn_step": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 7 + [_fp, _i]),
+    "pluto_gdn_out_norm_gate": (_i, [_vp, _vp, _i, _vp, _i, _vp, C.c_longlong, _i, _fp, _i, _i,
+                                     _vp, _i]),
 }
+
+
+class KvCacheStruct(C.Structure):
+    """struct pluto_kv_cache of include/pluto_b200.h."""
+    _fields_ = [("k_base", _vp), ("v_base", _vp), ("block_table", _vp), ("max_blocks", _i),
+                ("page_size", _i), ("page_stride", _sz), ("token_stride", _sz), ("dtype", _i)]
 
 _lib = None
 

@@ -168,3 +168,218 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
 }
 
 }  // extern "C"
+
+namespace {
+
+bool dtype_ok(int d) { return d == PLUTO_FP32 || d == PLUTO_BF16; }
+
+int check_cache(const pluto_kv_cache* cache, int kv_heads, int head_dim) {
+  if (!cache || !cache->k_base || !cache->v_base)
+    return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
+  if (!dtype_ok(cache->dtype)) return fail(PLUTO_E_INVALID, "attention cache has an unknown dtype");
+  if (cache->page_size <= 0 || (cache->block_table && cache->max_blocks <= 0) ||
+      cache->token_stride < static_cast<size_t>(kv_heads) * head_dim ||
+      cache->page_stride < cache->token_stride)
+    return fail(PLUTO_E_INVALID, "attention cache shape or capacity does not match parameters");
+  return PLUTO_OK;
+}
+
+// Chunk length of the split-KV decode: the largest of {2048,...,256} tokens that still yields
+// at least 16 work items per SM, so ragged lengths balance across the 148 SMs.
+int decode_split_tokens(int batch, int kv_heads, int max_seq_len) {
+  for (int s : {2048, 1024, 512}) {
+    const long long items = static_cast<long long>(batch) * kv_heads * ((max_seq_len + s - 1) / s);
+    if (items >= 148 * 16) return s;
+  }
+  return 256;
+}
+
+int fill_decode(pluto::DecodeArgs* a, const void* q, int q_dtype, const pluto_kv_cache* cache,
+                const int32_t* seq_lens, int max_seq_len, int batch, int q_heads, int kv_heads,
+                int head_dim) {
+  if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || head_dim <= 0 ||
+      head_dim > 256 || max_seq_len <= 0 || batch > 65535 || q_heads > 65535 || !dtype_ok(q_dtype))
+    return fail(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
+  if (int c = check_cache(cache, kv_heads, head_dim)) return c;
+  if (!q || !seq_lens) return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
+  *a = pluto::DecodeArgs{};
+  a->q = q;
+  a->q_is_bf16 = q_dtype == PLUTO_BF16;
+  a->k_base = cache->k_base;
+  a->v_base = cache->v_base;
+  a->kv_is_bf16 = cache->dtype == PLUTO_BF16;
+  a->block_table = cache->block_table;
+  a->max_blocks = cache->max_blocks;
+  a->page_size = cache->page_size;
+  a->page_stride = cache->page_stride;
+  a->token_stride = cache->token_stride;
+  a->seq_lens = seq_lens;
+  a->batch = batch; a->q_heads = q_heads; a->kv_heads = kv_heads; a->head_dim = head_dim;
+  a->split_tokens = decode_split_tokens(batch, kv_heads, max_seq_len);
+  a->splits = (max_seq_len + a->split_tokens - 1) / a->split_tokens;
+  a->scale = 1.0f / sqrtf(static_cast<float>(head_dim));
+  a->status = pluto::kernel_status_word();
+  if (!a->status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
+  return PLUTO_OK;
+}
+
+int check_gdn(int batch, int tokens, int key_heads, int value_heads, int key_dim, int value_dim) {
+  // DeltaNetState::Create, src/llm/layers/util/cached_attention_ops.cc:370-376
+  if (batch <= 0 || tokens <= 0 || key_heads <= 0 || value_heads <= 0 ||
+      value_heads % key_heads != 0 || key_dim <= 0 || key_dim > 128 || value_dim <= 0 ||
+      value_dim > 256 || batch > 65535 || value_heads > 65535)
+    return fail(PLUTO_E_INVALID, "invalid DeltaNet dimensions or parameters");
+  return PLUTO_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pluto_qk_prepare(pluto_stream_t stream, const void* q_in, const void* k_in, const void* v_in,
+                     int in_dtype, size_t q_token_stride, size_t q_head_stride,
+                     const float* q_norm, const float* k_norm, const int32_t* positions,
+                     void* q_out, int q_out_dtype, const pluto_kv_cache* cache, int batch,
+                     int tokens, int q_heads, int kv_heads, int head_dim, int rotary_dim,
+                     float rms_norm_epsilon, float rope_theta, int round_to_bf16) {
+  // ValidateCachedAttention, src/llm/layers/util/cached_attention_ops.cc:283-306
+  if (batch <= 0 || tokens <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 ||
+      head_dim <= 0 || head_dim > 256 || rotary_dim <= 0 || rotary_dim > head_dim ||
+      rotary_dim % 2 != 0 || !isfinite(rope_theta) || rope_theta <= 0.0f ||
+      !isfinite(rms_norm_epsilon) || rms_norm_epsilon <= 0.0f || !dtype_ok(in_dtype) ||
+      !dtype_ok(q_out_dtype) ||
+      static_cast<long long>(batch) * tokens * (q_heads + kv_heads) > 0x7fffffffLL)
+    return fail(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
+  if (int c = check_cache(cache, kv_heads, head_dim)) return c;
+  if (!q_in || !k_in || !v_in || !q_norm || !k_norm || !q_out)
+    return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
+  pluto::PrepareArgs a{};
+  a.q_in = q_in; a.k_in = k_in; a.v_in = v_in; a.in_is_bf16 = in_dtype == PLUTO_BF16;
+  a.q_token = q_token_stride; a.q_head = q_head_stride;
+  a.q_norm = q_norm; a.k_norm = k_norm; a.positions = positions;
+  a.q_out = q_out; a.q_out_is_bf16 = q_out_dtype == PLUTO_BF16;
+  a.k_cache = cache->k_base; a.v_cache = cache->v_base; a.kv_is_bf16 = cache->dtype == PLUTO_BF16;
+  a.block_table = cache->block_table; a.max_blocks = cache->max_blocks;
+  a.page_size = cache->page_size; a.page_stride = cache->page_stride;
+  a.token_stride = cache->token_stride;
+  a.batch = batch; a.tokens = tokens; a.q_heads = q_heads; a.kv_heads = kv_heads;
+  a.head_dim = head_dim; a.rotary = rotary_dim;
+  a.epsilon = rms_norm_epsilon; a.log_theta = logf(rope_theta); a.round = round_to_bf16;
+  return from_cuda(pluto::qk_prepare(stream, a), "prepare Qwen attention");
+}
+
+size_t pluto_gqa_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim,
+                                        int max_seq_len) {
+  if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || max_seq_len <= 0) return 0;
+  const int s = decode_split_tokens(batch, kv_heads, max_seq_len);
+  const size_t splits = static_cast<size_t>((max_seq_len + s - 1) / s);
+  return static_cast<size_t>(batch) * q_heads * splits * (head_dim + 2) * sizeof(float);
+}
+
+int pluto_gqa_decode(pluto_stream_t stream, const void* q, int q_dtype, const void* gate,
+                     int gate_dtype, size_t gate_token_stride, size_t gate_head_stride,
+                     const pluto_kv_cache* cache, const int32_t* seq_lens, int max_seq_len,
+                     void* out, int out_dtype, float* lse, void* workspace, size_t workspace_bytes,
+                     int batch, int q_heads, int kv_heads, int head_dim, int round_to_bf16) {
+  pluto::DecodeArgs a;
+  if (int c = fill_decode(&a, q, q_dtype, cache, seq_lens, max_seq_len, batch, q_heads, kv_heads,
+                          head_dim))
+    return c;
+  if (!out || !workspace || !dtype_ok(out_dtype) || (gate && !dtype_ok(gate_dtype)))
+    return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
+  if (workspace_bytes <
+          pluto_gqa_decode_workspace_bytes(batch, q_heads, kv_heads, head_dim, max_seq_len) ||
+      !aligned16(workspace))
+    return fail(PLUTO_E_INVALID, "attention decode workspace is too small or misaligned");
+  a.gate = gate; a.gate_is_bf16 = gate_dtype == PLUTO_BF16;
+  a.gate_token = gate_token_stride; a.gate_head = gate_head_stride;
+  a.out = out; a.out_is_bf16 = out_dtype == PLUTO_BF16; a.lse = lse;
+  a.round = round_to_bf16;
+  a.partial_acc = static_cast<float*>(workspace);
+  a.partial_ml = a.partial_acc + static_cast<size_t>(batch) * q_heads * a.splits * head_dim;
+  return from_cuda(pluto::gqa_decode(stream, a), "Qwen full attention");
+}
+
+int pluto_gqa_decode_probs(pluto_stream_t stream, const void* q, int q_dtype,
+                           const pluto_kv_cache* cache, const int32_t* seq_lens, float* probs,
+                           size_t probs_stride, int batch, int q_heads, int kv_heads,
+                           int head_dim) {
+  pluto::DecodeArgs a;
+  if (int c = fill_decode(&a, q, q_dtype, cache, seq_lens, 1, batch, q_heads, kv_heads, head_dim))
+    return c;
+  if (!probs) return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
+  return from_cuda(pluto::gqa_decode_probabilities(stream, a, probs, probs_stride),
+                   "inspect cached attention probabilities");
+}
+
+int pluto_gdn_gates(pluto_stream_t stream, const void* a, const void* b, const float* a_log,
+                    const float* dt_bias, int in_dtype, long long tokens, int heads,
+                    int round_to_bf16, float* g, float* beta) {
+  if (tokens <= 0 || heads <= 0 || !dtype_ok(in_dtype) || tokens * heads > 0x7fffffff00LL)
+    return fail(PLUTO_E_INVALID, "invalid DeltaNet dimensions or parameters");
+  if (!a || !b || !a_log || !dt_bias || !g || !beta)
+    return fail(PLUTO_E_INVALID, "DeltaNet requires non-null device pointers");
+  return from_cuda(pluto::gdn_gates(stream, a, b, a_log, dt_bias, in_dtype == PLUTO_BF16, tokens,
+                                    heads, round_to_bf16, g, beta),
+                   "Qwen gated delta gates");
+}
+
+int pluto_gdn_conv_silu(pluto_stream_t stream, const void* input, const float* weight,
+                        int in_dtype, int batch, int tokens, int channels, int width,
+                        int round_to_bf16, float* state, void* output, int out_dtype) {
+  if (batch <= 0 || tokens <= 0 || channels <= 0 || width <= 0 || width > 32 ||
+      !dtype_ok(in_dtype) || !dtype_ok(out_dtype))
+    return fail(PLUTO_E_INVALID, "invalid DeltaNet dimensions or parameters");
+  if (!input || !weight || !state || !output)
+    return fail(PLUTO_E_INVALID, "DeltaNet requires non-null device pointers");
+  return from_cuda(pluto::gdn_conv(stream, input, weight, in_dtype == PLUTO_BF16, batch, tokens,
+                                   channels, width, round_to_bf16, state, output,
+                                   out_dtype == PLUTO_BF16),
+                   "Qwen causal convolution");
+}
+
+int pluto_gdn_prefill(pluto_stream_t stream, const void* q, const void* k, const void* v,
+                      int in_dtype, const float* g, const float* beta, float* state, void* out,
+                      int out_dtype, int batch, int tokens, int key_heads, int value_heads,
+                      int key_dim, int value_dim, int normalize_qk, float q_scale,
+                      int round_to_bf16) {
+  if (int c = check_gdn(batch, tokens, key_heads, value_heads, key_dim, value_dim)) return c;
+  if (!dtype_ok(in_dtype) || !dtype_ok(out_dtype))
+    return fail(PLUTO_E_INVALID, "invalid DeltaNet dimensions or parameters");
+  if (!q || !k || !v || !g || !beta || !state || !out)
+    return fail(PLUTO_E_INVALID, "DeltaNet requires non-null device pointers");
+  pluto::GdnArgs a{};
+  a.q = q; a.k = k; a.v = v; a.in_is_bf16 = in_dtype == PLUTO_BF16;
+  a.g = g; a.beta = beta; a.state = state; a.out = out; a.out_is_bf16 = out_dtype == PLUTO_BF16;
+  a.batch = batch; a.tokens = tokens; a.key_heads = key_heads; a.value_heads = value_heads;
+  a.key_dim = key_dim; a.value_dim = value_dim;
+  a.normalize_qk = normalize_qk; a.q_scale = q_scale; a.round = round_to_bf16;
+  return from_cuda(pluto::gdn_recurrent(stream, a), "Qwen gated delta recurrence");
+}
+
+int pluto_gdn_step(pluto_stream_t stream, const void* q, const void* k, const void* v,
+                   int in_dtype, const float* g, const float* beta, float* state, void* out,
+                   int out_dtype, int batch, int key_heads, int value_heads, int key_dim,
+                   int value_dim, int normalize_qk, float q_scale, int round_to_bf16) {
+  return pluto_gdn_prefill(stream, q, k, v, in_dtype, g, beta, state, out, out_dtype, batch, 1,
+                           key_heads, value_heads, key_dim, value_dim, normalize_qk, q_scale,
+                           round_to_bf16);
+}
+
+int pluto_gdn_out_norm_gate(pluto_stream_t stream, const void* core, int core_dtype, const void* z,
+                            int z_dtype, const float* norm_weight, long long rows, int dim,
+                            float rms_norm_epsilon, int round_to_bf16, int final_round, void* out,
+                            int out_dtype) {
+  if (rows <= 0 || rows > 0x7fffffffLL || dim <= 0 || dim > 256 || !dtype_ok(core_dtype) ||
+      !dtype_ok(z_dtype) || !dtype_ok(out_dtype) || !isfinite(rms_norm_epsilon) ||
+      rms_norm_epsilon <= 0.0f)
+    return fail(PLUTO_E_INVALID, "invalid DeltaNet dimensions or parameters");
+  if (!core || !z || !norm_weight || !out)
+    return fail(PLUTO_E_INVALID, "DeltaNet requires non-null device pointers");
+  return from_cuda(pluto::gdn_output(stream, core, z, norm_weight, core_dtype == PLUTO_BF16,
+                                     z_dtype == PLUTO_BF16, rows, dim, rms_norm_epsilon,
+                                     round_to_bf16, final_round, out, out_dtype == PLUTO_BF16),
+                   "Qwen gated delta output norm");
+}
+
+}  // extern "C"

@@ -54,4 +54,90 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& args);
 bool make_token_map(CUtensorMap* map, const void* base, int cols, int seq, int batch,
                     size_t token_stride, int box_rows);
 
+
+// ---- gqa_decode.cu ------------------------------------------------------------------------------
+// Cache addressing: token t of sequence b, kv head h starts at element
+//   page(b, t) * page_stride + (t % page_size) * token_stride + h * head_dim,
+// page(b, t) = block_table ? block_table[b * max_blocks + t / page_size] : b.
+struct DecodeArgs {
+  const void* q;            // [batch, q_heads, head_dim], already normalised/rotated
+  int q_is_bf16;
+  const void* gate;         // optional; element (b, h, d) at b*gate_token + h*gate_head + d
+  int gate_is_bf16;
+  size_t gate_token, gate_head;
+  const void* k_base;
+  const void* v_base;
+  int kv_is_bf16;
+  const int32_t* block_table;
+  int max_blocks, page_size;
+  size_t page_stride, token_stride;
+  const int32_t* seq_lens;  // [batch], number of cached tokens to attend to (>= 1)
+  void* out;                // [batch, q_heads, head_dim]
+  int out_is_bf16;
+  float* lse;               // optional [batch, q_heads]
+  float* partial_acc;       // workspace [batch, q_heads, splits, head_dim]
+  float* partial_ml;        // workspace [batch, q_heads, splits, 2]
+  int batch, q_heads, kv_heads, head_dim;
+  int splits, split_tokens;
+  float scale;
+  int round;
+  uint32_t* status;
+};
+bool gqa_decode_uses_tensor_cores(const DecodeArgs& args);
+cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args);
+cudaError_t gqa_decode_probabilities(cudaStream_t stream, const DecodeArgs& args, float* probs,
+                                     size_t probs_stride);
+
+// ---- qk_prepare.cu ------------------------------------------------------------------------------
+struct PrepareArgs {
+  const void* q_in;         // token/head element strides q_token, q_head
+  const void* k_in;         // [batch*tokens, kv_heads, head_dim]
+  const void* v_in;
+  int in_is_bf16;
+  size_t q_token, q_head;
+  const float* q_norm;      // [head_dim], zero-centred
+  const float* k_norm;
+  const int32_t* positions; // optional [batch]: position of token 0 of each sequence
+  void* q_out;              // [batch*tokens, q_heads, head_dim]
+  int q_out_is_bf16;
+  void* k_cache;            // cache addressing as in DecodeArgs
+  void* v_cache;
+  int kv_is_bf16;
+  const int32_t* block_table;
+  int max_blocks, page_size;
+  size_t page_stride, token_stride;
+  int batch, tokens, q_heads, kv_heads, head_dim, rotary;
+  float epsilon, log_theta;
+  int round;
+};
+cudaError_t qk_prepare(cudaStream_t stream, const PrepareArgs& args);
+
+// ---- gdn.cu -------------------------------------------------------------------------------------
+struct GdnArgs {
+  const void* q;            // [batch, tokens, key_heads, key_dim]
+  const void* k;
+  const void* v;            // [batch, tokens, value_heads, value_dim]
+  int in_is_bf16;
+  const float* g;           // [batch, tokens, value_heads] decay in (0, 1]
+  const float* beta;        // [batch, tokens, value_heads]
+  float* state;             // [batch, value_heads, key_dim, value_dim], updated in place
+  void* out;                // [batch, tokens, value_heads, value_dim]
+  int out_is_bf16;
+  int batch, tokens, key_heads, value_heads, key_dim, value_dim;
+  int normalize_qk;
+  float q_scale;
+  int round;
+};
+cudaError_t gdn_recurrent(cudaStream_t stream, const GdnArgs& args);
+cudaError_t gdn_gates(cudaStream_t stream, const void* a_in, const void* b_in, const float* a_log,
+                      const float* dt_bias, int in_is_bf16, long long tokens, int heads, int round,
+                      float* g, float* beta);
+cudaError_t gdn_conv(cudaStream_t stream, const void* input, const float* weight, int in_is_bf16,
+                     int batch, int tokens, int channels, int width, int round, float* state,
+                     void* output, int out_is_bf16);
+cudaError_t gdn_output(cudaStream_t stream, const void* core, const void* z,
+                       const float* norm_weight, int core_is_bf16, int z_is_bf16, long long rows,
+                       int dim, float epsilon, int round, int final_round, void* output,
+                       int out_is_bf16);
+
 }  // namespace pluto

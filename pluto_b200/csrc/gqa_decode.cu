@@ -180,7 +180,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) gqa_decode_tc(DecodeArgs a)
           s[nb][i] = token < end ? s[nb][i] * scale_log2 : -INFINITY;
           tile_max[i >> 1] = fmaxf(tile_max[i >> 1], s[nb][i]);
         }
-      uint32_t pf[4];
+      // P is split into a bf16 high part and a bf16 remainder so that P V keeps ~16 mantissa
+      // bits: the result then tracks the fp32 reference to ~1e-5 instead of a bf16 ulp, and the
+      // extra MMAs are free in a bandwidth-bound kernel.
+      uint32_t pf[4], pl[4];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
@@ -197,6 +200,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) gqa_decode_tc(DecodeArgs a)
         m_run[r] = m_new;
         pf[r] = pack_bf16(p00, p01);      // a0 / a1: tokens 0-7
         pf[2 + r] = pack_bf16(p10, p11);  // a2 / a3: tokens 8-15
+        pl[r] = pack_bf16(p00 - bf16_lo(pf[r]), p01 - bf16_hi(pf[r]));
+        pl[2 + r] = pack_bf16(p10 - bf16_lo(pf[2 + r]), p11 - bf16_hi(pf[2 + r]));
 #pragma unroll
         for (int nb = 0; nb < D / 8; ++nb) {
           o[nb][2 * r] *= correction;
@@ -210,7 +215,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) gqa_decode_tc(DecodeArgs a)
         ldmatrix_x4_trans(vf, v_tile + (warp * 16 + ((lane / 8) & 1) * 8 + lane % 8) * kRowBytes +
                                   (np * 16 + (lane / 16) * 8) * 2);
         mma_bf16(o[2 * np], pf, vf[0], vf[1]);
+        mma_bf16(o[2 * np], pl, vf[0], vf[1]);
         mma_bf16(o[2 * np + 1], pf, vf[2], vf[3]);
+        mma_bf16(o[2 * np + 1], pl, vf[2], vf[3]);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->empty[st]);

@@ -243,3 +243,292 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     if want_stats:
         result["maxima"], result["normalizers"] = maxima, normalizers
     return result
+
+
+# =================================================================================================
+# Qwen cached attention: KeyValueCache, FullAttentionParameters, CachedAttentionStep
+# =================================================================================================
+def _resource_exhausted(message: str) -> PlutoStatusError:
+    return PlutoStatusError("ResourceExhausted", message, -3)
+
+
+@dataclass
+class FullAttentionParameters:
+    """src/llm/layers/util/cached_attention_ops.h:13-22, field for field."""
+    query_heads: int = 24
+    key_value_heads: int = 4
+    head_dim: int = 256
+    rotary_dim: int = 64
+    capacity: int = 4096
+    rms_norm_epsilon: float = 1e-6
+    rope_theta: float = 10000000.0
+    round_to_bfloat16: bool = True
+
+
+class KeyValueCache:
+    """Per-sequence K/V storage [capacity, kv_heads, head_dim] with a position counter
+    (src/llm/key_value_cache.h:25-57).  The reference stores fp32; every value it writes is already
+    bf16-rounded when rounding is on, so `dtype=torch.bfloat16` (default) holds the same numbers
+    in half the bytes.  `torch.float32` keeps the reference's storage."""
+
+    def __init__(self, capacity, key_value_heads, head_dim, dtype, device):
+        self.capacity_ = capacity
+        self.key_value_heads_ = key_value_heads
+        self.head_dim_ = head_dim
+        self.keys_ = torch.zeros((capacity, key_value_heads, head_dim), dtype=dtype, device=device)
+        self.values_ = torch.zeros_like(self.keys_)
+        self.position_ = 0
+
+    @staticmethod
+    def Create(capacity: int, key_value_heads: int, head_dim: int,
+               dtype: torch.dtype = torch.bfloat16, device="cuda") -> "KeyValueCache":
+        # src/llm/key_value_cache.cc:20-36
+        if capacity <= 0 or key_value_heads <= 0 or head_dim <= 0:
+            raise _invalid("key-value cache dimensions must be positive")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise _invalid("key-value cache stores bf16 or fp32")
+        return KeyValueCache(capacity, key_value_heads, head_dim, dtype, device)
+
+    def capacity(self): return self.capacity_
+    def key_value_heads(self): return self.key_value_heads_
+    def head_dim(self): return self.head_dim_
+    def position(self): return self.position_
+    def keys(self): return self.keys_
+    def values(self): return self.values_
+
+    def Advance(self) -> None:
+        if self.position_ >= self.capacity_:
+            raise _resource_exhausted("key-value cache capacity reached")
+        self.position_ += 1
+
+    def Reset(self) -> None:
+        self.position_ = 0  # contents are not cleared, as in the reference
+
+    def layout(self) -> "_capi.KvCacheStruct":
+        return kv_layout(self.keys_, self.values_, None, self.capacity_,
+                         self.capacity_ * self.key_value_heads_ * self.head_dim_,
+                         self.key_value_heads_ * self.head_dim_)
+
+
+def kv_layout(k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: Optional[torch.Tensor],
+              page_size: int, page_stride: int, token_stride: int) -> "_capi.KvCacheStruct":
+    s = _capi.KvCacheStruct()
+    s.k_base, s.v_base = k_pool.data_ptr(), v_pool.data_ptr()
+    s.block_table = None if block_table is None else block_table.data_ptr()
+    s.max_blocks = 0 if block_table is None else block_table.shape[1]
+    s.page_size, s.page_stride, s.token_stride = page_size, page_stride, token_stride
+    s.dtype = 1 if k_pool.dtype == torch.bfloat16 else 0
+    return s
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise _invalid("tensor must be bf16 or fp32")
+
+
+def ValidateCachedAttention(p: FullAttentionParameters, cache: KeyValueCache) -> None:
+    """src/llm/layers/util/cached_attention_ops.cc:283-306.  No GPU work."""
+    import math
+    imax = 2 ** 31 - 1
+    if (p.query_heads <= 0 or p.key_value_heads <= 0 or p.query_heads % p.key_value_heads != 0
+            or p.head_dim <= 0 or p.head_dim > 256 or p.rotary_dim <= 0
+            or p.rotary_dim > p.head_dim or p.rotary_dim % 2 != 0 or p.capacity <= 0
+            or p.capacity > imax - 32 or not math.isfinite(p.rope_theta) or p.rope_theta <= 0.0
+            or not math.isfinite(p.rms_norm_epsilon) or p.rms_norm_epsilon <= 0.0
+            or p.query_heads > imax // (2 * p.head_dim)
+            or p.query_heads > imax - p.key_value_heads):
+        raise _invalid("invalid full-attention dimensions or parameters")
+    if (cache.capacity() != p.capacity or cache.key_value_heads() != p.key_value_heads
+            or cache.head_dim() != p.head_dim):
+        raise _invalid("attention cache shape or capacity does not match parameters")
+
+
+_decode_workspaces = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    key = (str(device), torch.cuda.current_stream().cuda_stream)
+    ws = _decode_workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty((max(nbytes, 1 << 20),), dtype=torch.uint8, device=device)
+        _decode_workspaces[key] = ws
+    return ws
+
+
+def CachedAttentionStep(p: FullAttentionParameters, cache: KeyValueCache, q_gate: torch.Tensor,
+                        k: torch.Tensor, v: torch.Tensor, q_norm: torch.Tensor,
+                        k_norm: torch.Tensor, output: torch.Tensor,
+                        probabilities: Optional[torch.Tensor] = None) -> None:
+    """One token of batch-one causal attention against `cache`
+    (src/llm/layers/util/cached_attention_ops.cc:308-353): validate everything, prepare
+    (norm + RoPE + append), attend, optional probabilities, then advance the cache -- the position
+    moves only after every launch succeeded.  q_gate [Hq,2,D], k,v [Hkv,D], output [Hq,D];
+    fp32 (the reference's pointer type) or bf16."""
+    ValidateCachedAttention(p, cache)
+    for t in (q_gate, k, v, q_norm, k_norm, output):
+        if t is None:
+            raise _invalid("attention requires non-null device pointers")
+    if cache.position() >= cache.capacity():
+        raise _resource_exhausted("full-attention cache capacity reached")
+    L = _capi.lib()
+    device = output.device
+    position = cache.position()
+    D, Hq, Hkv = p.head_dim, p.query_heads, p.key_value_heads
+    queries = torch.empty((Hq, D), dtype=torch.bfloat16 if p.round_to_bfloat16 else torch.float32,
+                          device=device)
+    positions = torch.tensor([position], dtype=torch.int32, device=device)
+    layout = cache.layout()
+    check(L.pluto_qk_prepare(_stream(), _ptr(q_gate), _ptr(k), _ptr(v), _dt(q_gate), 2 * Hq * D,
+                             2 * D, _ptr(q_norm), _ptr(k_norm), _ptr(positions), _ptr(queries),
+                             _dt(queries), C_byref(layout), 1, 1, Hq, Hkv, D, p.rotary_dim,
+                             p.rms_norm_epsilon, p.rope_theta, int(p.round_to_bfloat16)))
+    lens = positions + 1
+    nbytes = L.pluto_gqa_decode_workspace_bytes(1, Hq, Hkv, D, position + 1)
+    ws = _workspace(device, nbytes)
+    gate = q_gate.reshape(-1)[D:]
+    check(L.pluto_gqa_decode(_stream(), _ptr(queries), _dt(queries), _ptr(gate), _dt(q_gate),
+                             2 * Hq * D, 2 * D, C_byref(layout), _ptr(lens), position + 1,
+                             _ptr(output), _dt(output), None, _ptr(ws), ws.numel(), 1, Hq, Hkv, D,
+                             int(p.round_to_bfloat16)))
+    if probabilities is not None:
+        check(L.pluto_gqa_decode_probs(_stream(), _ptr(queries), _dt(queries), C_byref(layout),
+                                       _ptr(lens), _ptr(probabilities), position + 1, 1, Hq, Hkv,
+                                       D))
+    cache.Advance()
+
+
+def C_byref(struct):
+    import ctypes
+    return ctypes.cast(ctypes.pointer(struct), ctypes.c_void_p)
+
+
+def gqa_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, seq_lens: torch.Tensor,
+               max_seq_len: int, *, block_table: Optional[torch.Tensor] = None,
+               page_size: Optional[int] = None, gate: Optional[torch.Tensor] = None,
+               round_to_bfloat16: bool = True, out: Optional[torch.Tensor] = None,
+               workspace: Optional[torch.Tensor] = None, want_lse: bool = False):
+    """Batched decode over a page pool.  q [B,Hq,D] prepared queries; k_pool/v_pool
+    [pages, page_size, Hkv, D]; without a block table sequence b owns page b.  Returns out
+    [B,Hq,D] (and lse [B,Hq])."""
+    B, Hq, D = q.shape
+    pages, psize, Hkv, _ = k_pool.shape
+    page_size = psize if page_size is None else page_size
+    layout = kv_layout(k_pool, v_pool, block_table, page_size, k_pool.stride(0), k_pool.stride(1))
+    L = _capi.lib()
+    if out is None:
+        out = torch.empty_like(q)
+    nbytes = L.pluto_gqa_decode_workspace_bytes(B, Hq, Hkv, D, max_seq_len)
+    ws = workspace if workspace is not None else _workspace(q.device, nbytes)
+    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if want_lse else None
+    gts = ghs = 0
+    if gate is not None:
+        gts, ghs = gate.stride(0), gate.stride(1)
+    check(L.pluto_gqa_decode(_stream(), _ptr(q), _dt(q), _ptr(gate),
+                             _dt(gate) if gate is not None else 0, gts, ghs, C_byref(layout),
+                             _ptr(seq_lens), max_seq_len, _ptr(out), _dt(out), _ptr(lse), _ptr(ws),
+                             ws.numel(), B, Hq, Hkv, D, int(round_to_bfloat16)))
+    return (out, lse) if want_lse else out
+
+
+# =================================================================================================
+# Gated delta-net
+# =================================================================================================
+@dataclass
+class DeltaNetParameters:
+    """src/llm/layers/util/cached_attention_ops.h:49-57, field for field."""
+    key_heads: int = 16
+    value_heads: int = 48
+    key_head_dim: int = 128
+    value_head_dim: int = 128
+    conv_kernel_dim: int = 4
+    rms_norm_epsilon: float = 1e-6
+    round_to_bfloat16: bool = True
+
+
+class DeltaNetState:
+    """Single-token causal depthwise convolution + gated delta recurrence with an fp32 recurrent
+    matrix (src/llm/layers/util/cached_attention_ops.h:59-89, .cc:355-442)."""
+
+    def __init__(self, p: DeltaNetParameters, device):
+        self.parameters_ = p
+        self.channels_ = 2 * p.key_heads * p.key_head_dim + p.value_heads * p.value_head_dim
+        f32 = dict(dtype=torch.float32, device=device)
+        self.convolution_state_ = torch.empty((1, self.channels_, p.conv_kernel_dim), **f32)
+        self.recurrent_state_ = torch.empty((1, p.value_heads, p.key_head_dim, p.value_head_dim),
+                                            **f32)
+        self.convolved_qkv_ = torch.empty((self.channels_,), **f32)
+        self.core_output_ = torch.empty((p.value_heads, p.value_head_dim), **f32)
+        self.g_ = torch.empty((p.value_heads,), **f32)
+        self.beta_ = torch.empty((p.value_heads,), **f32)
+
+    @staticmethod
+    def Create(p: DeltaNetParameters, device="cuda") -> "DeltaNetState":
+        import math
+        if (p.key_heads <= 0 or p.value_heads <= 0 or p.value_heads % p.key_heads != 0
+                or p.key_head_dim <= 0 or p.key_head_dim > 128 or p.value_head_dim <= 0
+                or p.value_head_dim > 256 or p.conv_kernel_dim <= 0 or p.conv_kernel_dim > 32
+                or not math.isfinite(p.rms_norm_epsilon) or p.rms_norm_epsilon <= 0.0):
+            raise _invalid("invalid DeltaNet dimensions or parameters")
+        _capi.lib()
+        state = DeltaNetState(p, device)
+        state.Reset()
+        return state
+
+    def Reset(self) -> None:
+        self.convolution_state_.zero_()
+        self.recurrent_state_.zero_()
+
+    def Step(self, qkv, z, a, b, conv_weight, a_log, dt_bias, norm_weight, output) -> None:
+        """qkv packed [all Q, all K, all V]; z [Hv,dv]; a, b, A_log, dt_bias [Hv]; conv weights
+        [channels, kernel] oldest to newest; norm_weight [dv] plain multiplier; output [Hv,dv]."""
+        for t in (qkv, z, a, b, conv_weight, a_log, dt_bias, norm_weight, output):
+            if t is None:
+                raise _invalid("DeltaNet requires non-null device pointers")
+        p, L, rnd = self.parameters_, _capi.lib(), int(self.parameters_.round_to_bfloat16)
+        check(L.pluto_gdn_conv_silu(_stream(), _ptr(qkv), _ptr(conv_weight), _dt(qkv), 1, 1,
+                                    self.channels_, p.conv_kernel_dim, rnd,
+                                    _ptr(self.convolution_state_), _ptr(self.convolved_qkv_), 0))
+        check(L.pluto_gdn_gates(_stream(), _ptr(a), _ptr(b), _ptr(a_log), _ptr(dt_bias), _dt(a), 1,
+                                p.value_heads, rnd, _ptr(self.g_), _ptr(self.beta_)))
+        kq = p.key_heads * p.key_head_dim
+        conv = self.convolved_qkv_
+        check(L.pluto_gdn_step(_stream(), _ptr(conv[:kq]), _ptr(conv[kq:2 * kq]),
+                               _ptr(conv[2 * kq:]), 0, _ptr(self.g_), _ptr(self.beta_),
+                               _ptr(self.recurrent_state_), _ptr(self.core_output_), 0, 1,
+                               p.key_heads, p.value_heads, p.key_head_dim, p.value_head_dim, 1,
+                               1.0, rnd))
+        check(L.pluto_gdn_out_norm_gate(_stream(), _ptr(self.core_output_), 0, _ptr(z), _dt(z),
+                                        _ptr(norm_weight), p.value_heads, p.value_head_dim,
+                                        p.rms_norm_epsilon, rnd, 1, _ptr(output), _dt(output)))
+
+
+def gdn_prefill(q, k, v, g, beta, state, normalize_qk=True, q_scale=1.0, round_to_bfloat16=True,
+                out=None):
+    """Recurrence over a whole sequence from `state` (updated in place).  q,k [B,T,Hk,dk];
+    v [B,T,Hv,dv]; g,beta fp32 [B,T,Hv]; state fp32 [B,Hv,dk,dv].  Returns out like v."""
+    B, T, Hk, dk = q.shape
+    Hv, dv = v.shape[2], v.shape[3]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if out is None:
+        out = torch.empty_like(v)
+    check(_capi.lib().pluto_gdn_prefill(_stream(), _ptr(q), _ptr(k), _ptr(v), _dt(v), _ptr(g),
+                                        _ptr(beta), _ptr(state), _ptr(out), _dt(out), B, T, Hk, Hv,
+                                        dk, dv, int(normalize_qk), float(q_scale),
+                                        int(round_to_bfloat16)))
+    return out
+
+
+def gdn_step(q, k, v, g, beta, state, normalize_qk=True, q_scale=1.0, round_to_bfloat16=True,
+             out=None):
+    """Single-token update: q,k [B,Hk,dk]; v [B,Hv,dv]; g,beta [B,Hv]."""
+    B, Hk, dk = q.shape
+    Hv, dv = v.shape[1], v.shape[2]
+    if out is None:
+        out = torch.empty_like(v)
+    check(_capi.lib().pluto_gdn_step(_stream(), _ptr(q), _ptr(k), _ptr(v), _dt(v), _ptr(g),
+                                     _ptr(beta), _ptr(state), _ptr(out), _dt(out), B, Hk, Hv, dk,
+                                     dv, int(normalize_qk), float(q_scale), int(round_to_bfloat16)))
+    return out
