@@ -231,6 +231,17 @@ int pluto_gdn_out_norm_gate(pluto_stream_t stream, const void* core, int core_dt
                             float rms_norm_epsilon, int round_to_bf16, int final_round, void* out,
                             int out_dtype);
 
+/* --------------------------------------------------------------------------------------------
+ * Head-sharded multi-GPU support.  The reference is single-GPU (its only cudaSetDevice pins a
+ * thread pool to one device, src/cuda/thread_pool.h:19-22, src/cuda/thread_pool.cc:109), so this
+ * has no kernel to mirror: it is the local half of "all-gather the head-sharded output" for a
+ * caller that wants the concatenated [rows, E] activation the next reference layer expects
+ * (AttentionLayer output layout, src/llm/layers/attention.h:64-70).  The collective itself is the
+ * caller's ncclAllGather into `gathered` = [ranks][rows][local_bytes]; this kernel rewrites it to
+ * out = [rows][ranks * local_bytes].  Only local memory is touched. */
+int pluto_interleave_heads(pluto_stream_t stream, const void* gathered, void* out, int ranks,
+                           long long rows, size_t local_bytes);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

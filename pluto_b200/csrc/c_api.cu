@@ -383,3 +383,12 @@ int pluto_gdn_out_norm_gate(pluto_stream_t stream, const void* core, int core_dt
 }
 
 }  // extern "C"
+
+extern "C" int pluto_interleave_heads(pluto_stream_t stream, const void* gathered, void* out,
+                                      int ranks, long long rows, size_t local_bytes) {
+  if (ranks <= 0 || rows <= 0 || local_bytes == 0 || local_bytes > 0x7fffffffu)
+    return fail(PLUTO_E_INVALID, "invalid head-gather dimensions");
+  if (!gathered || !out) return fail(PLUTO_E_INVALID, "head gather requires non-null device pointers");
+  return from_cuda(pluto::interleave_heads(stream, gathered, out, ranks, rows, local_bytes),
+                   "head interleave launch");
+}

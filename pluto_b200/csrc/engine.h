@@ -140,4 +140,9 @@ cudaError_t gdn_output(cudaStream_t stream, const void* core, const void* z,
                        int dim, float epsilon, int round, int final_round, void* output,
                        int out_is_bf16);
 
+
+// ---- interleave.cu ------------------------------------------------------------------------------
+cudaError_t interleave_heads(cudaStream_t stream, const void* gathered, void* out, int ranks,
+                             long long rows, size_t local_bytes);
+
 }  // namespace pluto
