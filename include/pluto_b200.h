@@ -174,6 +174,33 @@ int pluto_gqa_decode(pluto_stream_t stream, const void* q, int q_dtype, const vo
                      size_t workspace_bytes, int batch, int q_heads, int kv_heads, int head_dim,
                      int round_to_bf16);
 
+/* pluto_gqa_decode for callers that may not allocate device memory and have no workspace to lend:
+ * hosts whose HBM plan is fixed and fully committed at start-up, plugin sandboxes that forbid
+ * cudaMalloc (and the stream-ordered allocators) to loaded libraries, decode loops that must not
+ * contend for an allocator lock.  It has no counterpart in the reference, whose CachedAttentionStep
+ * allocates its scratch with a stream-ordered Buffer on every token.  The split-KV partials live
+ * in a 24 MiB area inside the library image (pluto_gqa_decode_builtin_scratch_bytes(); every GPU
+ * that loads the library holds it until the process exits).  Arguments, results and kernels are
+ * those of pluto_gqa_decode minus the workspace pair.
+ *   - A call whose pluto_gqa_decode_workspace_bytes(...) exceeds the area returns
+ *     PLUTO_E_EXHAUSTED with the two sizes in pluto_last_error(); nothing is launched.
+ *   - No cudaMalloc/cudaFree or allocating library routine is called, now or later.
+ *   - The first call on each device looks up the area's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before starting any
+ *     stream capture on the device.
+ *   - All calls share the one area.  Nothing in it has to start at zero (each call overwrites
+ *     every partial it later reads), but two calls whose kernels overlap on the GPU -- different
+ *     streams, or different host threads -- race on it: order them on one stream. */
+int pluto_gqa_decode_noalloc(pluto_stream_t stream, const void* q, int q_dtype, const void* gate,
+                             int gate_dtype, size_t gate_token_stride, size_t gate_head_stride,
+                             const pluto_kv_cache* cache /* host */, const int32_t* seq_lens,
+                             int max_seq_len, void* out, int out_dtype, float* lse, int batch,
+                             int q_heads, int kv_heads, int head_dim, int round_to_bf16);
+
+/* Size in bytes of the built-in area pluto_gqa_decode_noalloc uses (host-only query; no
+ * counterpart in the reference). */
+size_t pluto_gqa_decode_builtin_scratch_bytes(void);
+
 /* Softmax row of the current query for the inspection hook.  Stands in for the cached
  * AttentionProbabilitiesKernel (cached_attention_ops.cc:131-178).  probs: fp32, row (b,h) at
  * probs + (b*Hq + h)*probs_stride, seq_lens[b] entries written. */

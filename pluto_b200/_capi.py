@@ -38,6 +38,9 @@ _SIGNATURES = {
     "pluto_gqa_decode_workspace_bytes": (_sz, [_i] * 5),
     "pluto_gqa_decode": (_i, [_vp, _vp, _i, _vp, _i, _sz, _sz, _vp, _vp, _i, _vp, _i, _vp, _vp,
                               _sz] + [_i] * 5),
+    "pluto_gqa_decode_noalloc": (_i, [_vp, _vp, _i, _vp, _i, _sz, _sz, _vp, _vp, _i, _vp, _i, _vp]
+                                 + [_i] * 5),
+    "pluto_gqa_decode_builtin_scratch_bytes": (_sz, []),
     "pluto_gqa_decode_probs": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _sz] + [_i] * 4),
     "pluto_gdn_gates": (_i, [_vp] * 5 + [_i, C.c_longlong, _i, _i, _vp, _vp]),
     "pluto_gdn_conv_silu": (_i, [_vp] * 3 + [_i] * 6 + [_vp, _vp, _i]),

@@ -6,6 +6,7 @@
 #include <stdio.h>
 
 #include <limits>
+#include <mutex>
 
 #include "../../include/pluto_b200.h"
 #include "engine.h"
@@ -391,4 +392,72 @@ extern "C" int pluto_interleave_heads(pluto_stream_t stream, const void* gathere
   if (!gathered || !out) return fail(PLUTO_E_INVALID, "head gather requires non-null device pointers");
   return from_cuda(pluto::interleave_heads(stream, gathered, out, ranks, rows, local_bytes),
                    "head interleave launch");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode without any caller-provided or allocated scratch.
+//
+// Some hosts of this library are not allowed to allocate device memory at the point where they
+// run attention: a serving loop whose memory plan is fixed at start-up and audited (every byte
+// of HBM is already handed to the KV-cache pool), a plugin sandbox that forbids cudaMalloc and
+// its stream-ordered variants to third-party code, or a latency-critical decode step that must
+// not take the allocator's lock.  pluto_gqa_decode needs a workspace for its split-KV partial
+// results; this variant keeps that workspace inside the library image instead.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kBuiltInScratchBytes = 24u << 20;  // 24 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_builtin_decode_scratch[kBuiltInScratchBytes];
+
+constexpr int kMaxScratchDevices = 64;
+std::once_flag g_scratch_once[kMaxScratchDevices];
+void* g_scratch_address[kMaxScratchDevices] = {};
+cudaError_t g_scratch_error[kMaxScratchDevices] = {};
+
+// In host code `g_builtin_decode_scratch` is only a handle for the runtime, not an address a
+// kernel can use; the device address is asked for once per device, with that device current.
+cudaError_t builtin_scratch(void** address) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device < 0 || device >= kMaxScratchDevices) return cudaErrorInvalidDevice;
+  std::call_once(g_scratch_once[device], [device] {
+    void* p = nullptr;
+    g_scratch_error[device] = cudaGetSymbolAddress(&p, g_builtin_decode_scratch);
+    g_scratch_address[device] = p;
+  });
+  if (g_scratch_error[device] != cudaSuccess) return g_scratch_error[device];
+  *address = g_scratch_address[device];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" size_t pluto_gqa_decode_builtin_scratch_bytes(void) { return kBuiltInScratchBytes; }
+
+extern "C" int pluto_gqa_decode_noalloc(pluto_stream_t stream, const void* q, int q_dtype,
+                                        const void* gate, int gate_dtype,
+                                        size_t gate_token_stride, size_t gate_head_stride,
+                                        const pluto_kv_cache* cache, const int32_t* seq_lens,
+                                        int max_seq_len, void* out, int out_dtype, float* lse,
+                                        int batch, int q_heads, int kv_heads, int head_dim,
+                                        int round_to_bf16) {
+  const size_t needed =
+      pluto_gqa_decode_workspace_bytes(batch, q_heads, kv_heads, head_dim, max_seq_len);
+  if (needed > kBuiltInScratchBytes) {
+    snprintf(g_error, sizeof(g_error),
+             "decode of this size needs %zu bytes of scratch but the built-in scratch area holds "
+             "%zu; use pluto_gqa_decode with a caller workspace",
+             needed, kBuiltInScratchBytes);
+    return PLUTO_E_EXHAUSTED;
+  }
+  void* scratch = nullptr;
+  if (int c = from_cuda(builtin_scratch(&scratch), "built-in decode scratch address")) return c;
+  // Same validation and launches as pluto_gqa_decode (dimension errors surface from there);
+  // every partial the merge kernel reads is written earlier in the same call, so the area's
+  // previous contents never need clearing.
+  return pluto_gqa_decode(stream, q, q_dtype, gate, gate_dtype, gate_token_stride,
+                          gate_head_stride, cache, seq_lens, max_seq_len, out, out_dtype, lse,
+                          scratch, kBuiltInScratchBytes, batch, q_heads, kv_heads, head_dim,
+                          round_to_bf16);
 }

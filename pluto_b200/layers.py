@@ -532,3 +532,27 @@ def gdn_step(q, k, v, g, beta, state, normalize_qk=True, q_scale=1.0, round_to_b
                                      _ptr(beta), _ptr(state), _ptr(out), _dt(out), B, Hk, Hv, dk,
                                      dv, int(normalize_qk), float(q_scale), int(round_to_bfloat16)))
     return out
+
+
+def gqa_decode_noalloc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                       seq_lens: torch.Tensor, max_seq_len: int, out: torch.Tensor, *,
+                       block_table: Optional[torch.Tensor] = None,
+                       gate: Optional[torch.Tensor] = None,
+                       round_to_bfloat16: bool = True) -> torch.Tensor:
+    """`gqa_decode` for callers that may not allocate device memory (a fixed, fully committed
+    memory plan; a sandbox that forbids cudaMalloc to plugins; a decode loop that must stay off
+    the allocator lock).  Nothing is allocated here or in the library: `out` comes from the
+    caller and the split-KV partials use the 24 MiB area built into the library, which every
+    call shares -- keep calls on one stream.  Raises ResourceExhausted when the shape needs more
+    scratch than the area holds."""
+    B, Hq, D = q.shape
+    _, psize, Hkv, _ = k_pool.shape
+    layout = kv_layout(k_pool, v_pool, block_table, psize, k_pool.stride(0), k_pool.stride(1))
+    gts = ghs = 0
+    if gate is not None:
+        gts, ghs = gate.stride(0), gate.stride(1)
+    check(_capi.lib().pluto_gqa_decode_noalloc(
+        _stream(), _ptr(q), _dt(q), _ptr(gate), _dt(gate) if gate is not None else 0, gts, ghs,
+        C_byref(layout), _ptr(seq_lens), max_seq_len, _ptr(out), _dt(out), None, B, Hq, Hkv, D,
+        int(round_to_bfloat16)))
+    return out
