@@ -130,6 +130,8 @@ typedef struct pluto_kv_cache {
   size_t page_stride;  /* elements */
   size_t token_stride; /* elements */
   int dtype;           /* PLUTO_BF16 or PLUTO_FP32 */
+  int num_pages;       /* pages in the pool when block_table is used (0 = unknown: decode then
+                          takes its plain-load path); ignored without a block table */
 } pluto_kv_cache;
 
 /* Per-head RMSNorm(1+w) -> bf16 rounding -> split-half partial RoPE of queries and keys, and the

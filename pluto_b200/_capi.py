@@ -55,7 +55,8 @@ _SIGNATURES = {
 class KvCacheStruct(C.Structure):
     """struct pluto_kv_cache of include/pluto_b200.h."""
     _fields_ = [("k_base", _vp), ("v_base", _vp), ("block_table", _vp), ("max_blocks", _i),
-                ("page_size", _i), ("page_stride", _sz), ("token_stride", _sz), ("dtype", _i)]
+                ("page_size", _i), ("page_stride", _sz), ("token_stride", _sz), ("dtype", _i),
+                ("num_pages", _i)]
 
 _lib = None
 

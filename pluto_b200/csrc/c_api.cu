@@ -214,6 +214,7 @@ int fill_decode(pluto::DecodeArgs* a, const void* q, int q_dtype, const pluto_kv
   a->page_size = cache->page_size;
   a->page_stride = cache->page_stride;
   a->token_stride = cache->token_stride;
+  a->num_pages = cache->num_pages;
   a->seq_lens = seq_lens;
   a->batch = batch; a->q_heads = q_heads; a->kv_heads = kv_heads; a->head_dim = head_dim;
   a->split_tokens = decode_split_tokens(batch, kv_heads, max_seq_len);

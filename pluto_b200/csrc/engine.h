@@ -71,6 +71,8 @@ struct DecodeArgs {
   const int32_t* block_table;
   int max_blocks, page_size;
   size_t page_stride, token_stride;
+  int num_pages;            // pages in the pool (needed for the TMA map when a block table is used)
+  int box_rows;             // filled by gqa_decode: tokens per TMA box
   const int32_t* seq_lens;  // [batch], number of cached tokens to attend to (>= 1)
   void* out;                // [batch, q_heads, head_dim]
   int out_is_bf16;

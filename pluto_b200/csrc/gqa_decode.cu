@@ -8,9 +8,11 @@
 //     partial (max, sum, accumulator), the four consumer warps of a CTA merge through shared
 //     memory, and a second kernel merges the chunks in a fixed order (deterministic, no atomics,
 //     no inter-CTA waits);
-//   * K/V rows travel global -> shared as 16-byte-aligned bulk copies (TMA, no multicast) issued
-//     by a producer warp into a 3-stage ring guarded by mbarriers; rows are padded by 16 bytes in
-//     shared memory so ldmatrix is bank-conflict free;
+//   * K/V tiles travel global -> shared as tiled TMA loads (no multicast) over a 4-D map of the
+//     page pool (column, kv head, token in page, page): one elected thread issues a handful of
+//     box copies per 64-token stage into a 3-stage ring guarded by mbarriers, 128-byte swizzled
+//     so ldmatrix is bank-conflict free.  (Per-row bulk copies were tried first: at 256 bytes
+//     per instruction the copy engine's per-instruction cost capped the kernel near 2 TB/s.)
 //   * the arithmetic is bf16 mma.sync (m16n8k16) with fp32 accumulation -- the kernel is bound by
 //     HBM bandwidth, the tensor path only has to stay out of the way.
 // The cache is a page pool: token t of sequence b lives in page block_table[b][t / page_size]
@@ -65,11 +67,16 @@ struct DecodeBarriers {
 
 // grid (splits, kv_heads, batch).  Partials: acc [B, Hq, splits, D], ml [B, Hq, splits, 2].
 template <int D>
-__global__ void __launch_bounds__(kDecodeThreads, 2) gqa_decode_tc(DecodeArgs a) {
-  constexpr int kRowBytes = D * 2 + 16;
-  constexpr int kTileBytes = kTile * kRowBytes;
-  constexpr int kStageBytes = 2 * kTileBytes;
-  extern __shared__ __align__(128) uint8_t smem[];
+__global__ void __launch_bounds__(kDecodeThreads, 2)
+gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+              DecodeArgs a) {
+  constexpr int kHalves = D / 64;                 // 64-column (128-byte) swizzled slabs per row
+  constexpr int kHalfBytes = kTile * 128;         // one slab of a tile
+  constexpr int kTileBytes = kHalves * kHalfBytes;
+  constexpr int kStageBytes = 2 * kTileBytes;     // K tile then V tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
   DecodeBarriers* bar = reinterpret_cast<DecodeBarriers*>(smem + kDecodeStages * kStageBytes);
 
   const int split = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
@@ -95,28 +102,39 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) gqa_decode_tc(DecodeArgs a)
 
   if (warp == kConsumerWarps) {
     // ---------------------------------------------------------------- producer warp
-    bool ok = true;
-    for (int it = 0; it < tiles && ok; ++it) {
-      const int st = it % kDecodeStages, use = it / kDecodeStages;
-      if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, a.status, 30);
-      if (!ok) break;
-      if (lane == 0) mbar_expect_tx(&bar->full[st], 2 * kTile * D * 2);
-      __syncwarp();
-      uint8_t* k_tile = smem + st * kStageBytes;
-      uint8_t* v_tile = k_tile + kTileBytes;
-      for (int r = lane; r < kTile; r += 32) {
-        // rows past the chunk end re-read the last valid token: finite data, masked to zero
-        const int t = min(begin + it * kTile + r, end - 1);
-        bulk_load(k_tile + r * kRowBytes, kv_row(a, a.k_base, b, t, kv_head, 2), D * 2,
-                  &bar->full[st]);
-        bulk_load(v_tile + r * kRowBytes, kv_row(a, a.v_base, b, t, kv_head, 2), D * 2,
-                  &bar->full[st]);
+    if (lane == 0) {
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      bool ok = true;
+      const int rows = a.box_rows;  // tokens per box: divides both the tile and the page size
+      for (int it = 0; it < tiles && ok; ++it) {
+        const int st = it % kDecodeStages, use = it / kDecodeStages;
+        if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, a.status, 30);
+        if (!ok) break;
+        const int t0 = begin + it * kTile;
+        const int boxes = min(kTile, end - t0 + rows - 1) / rows;  // boxes that hold a live token
+        mbar_expect_tx(&bar->full[st], static_cast<uint32_t>(boxes) * rows * D * 2 * 2);
+        uint8_t* k_tile = smem + st * kStageBytes;
+        uint8_t* v_tile = k_tile + kTileBytes;
+        for (int bx = 0; bx < boxes; ++bx) {
+          const int t = t0 + bx * rows;
+          const int page = a.block_table
+                               ? a.block_table[static_cast<size_t>(b) * a.max_blocks + t / a.page_size]
+                               : b;
+          const int in_page = t % a.page_size;
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h) {
+            tma_load_4d(k_tile + h * kHalfBytes + bx * rows * 128, &map_k, h * 64, kv_head, in_page,
+                        page, &bar->full[st]);
+            tma_load_4d(v_tile + h * kHalfBytes + bx * rows * 128, &map_v, h * 64, kv_head, in_page,
+                        page, &bar->full[st]);
+          }
+        }
       }
-    }
-    // all copies this warp started must have landed before the CTA may exit
-    if (lane == 0)
+      // all copies this thread started must have landed before the CTA may exit
       for (int it = max(0, tiles - kDecodeStages); it < tiles; ++it)
         mbar_wait(&bar->full[it % kDecodeStages], (it / kDecodeStages) & 1, a.status, 31);
+    }
   } else {
     // ---------------------------------------------------------------- consumer warps
     // A fragments of Q: rows = query heads of this KV head (rows >= group are zero).
@@ -156,6 +174,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) gqa_decode_tc(DecodeArgs a)
       if (!ok) break;
       const uint32_t k_tile = smem_u32(smem + st * kStageBytes);
       const uint32_t v_tile = k_tile + kTileBytes;
+      const int live = end - (begin + it * kTile);  // live tokens in this tile (may exceed kTile)
+      if (live < (warp + 1) * 16) {
+        // Rows past the sequence end hold whatever the page (or an earlier stage) held; their
+        // probabilities are zero, but 0 * NaN would poison P V, so this warp clears its own dead
+        // V rows first.  Only the last tile of a sequence takes this path.
+        for (int r = max(live, warp * 16); r < (warp + 1) * 16; ++r)
+          for (int c = lane; c < kHalves * 8; c += 32)
+            *reinterpret_cast<uint4*>(smem + st * kStageBytes + kTileBytes + (c / 8) * kHalfBytes +
+                                      r * 128 + (c % 8) * 16) = make_uint4(0, 0, 0, 0);
+        fence_proxy_async();
+        __syncwarp();
+      }
       // ---- S = Q K^T for this warp's 16 tokens: two n-blocks of 8 tokens
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -163,8 +193,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) gqa_decode_tc(DecodeArgs a)
 #pragma unroll
         for (int kp = 0; kp < D / 32; ++kp) {
           uint32_t kf[4];
-          ldmatrix_x4(kf, k_tile + (warp * 16 + nb * 8 + lane % 8) * kRowBytes +
-                              (kp * 32 + (lane / 8) * 8) * 2);
+          // element (row, col) of a tile sits in slab col/64 at row*128 + ((col%64)/8 ^ row%8)*16
+          const int row = warp * 16 + nb * 8 + lane % 8;
+          const int chunk = (kp * 4 + lane / 8) % 8;
+          ldmatrix_x4(kf, k_tile + (kp / 2) * kHalfBytes + row * 128 + ((chunk ^ (row % 8)) * 16));
           mma_bf16(s[nb], qf[2 * kp], kf[0], kf[1]);
           mma_bf16(s[nb], qf[2 * kp + 1], kf[2], kf[3]);
         }
@@ -212,8 +244,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) gqa_decode_tc(DecodeArgs a)
 #pragma unroll
       for (int np = 0; np < D / 16; ++np) {
         uint32_t vf[4];
-        ldmatrix_x4_trans(vf, v_tile + (warp * 16 + ((lane / 8) & 1) * 8 + lane % 8) * kRowBytes +
-                                  (np * 16 + (lane / 16) * 8) * 2);
+        const int row = warp * 16 + ((lane / 8) & 1) * 8 + lane % 8;
+        const int chunk = (np * 2 + lane / 16) % 8;
+        ldmatrix_x4_trans(vf, v_tile + (np / 4) * kHalfBytes + row * 128 + ((chunk ^ (row % 8)) * 16));
         mma_bf16(o[2 * np], pf, vf[0], vf[1]);
         mma_bf16(o[2 * np], pl, vf[0], vf[1]);
         mma_bf16(o[2 * np + 1], pf, vf[2], vf[3]);
@@ -427,33 +460,69 @@ __global__ void __launch_bounds__(256) gqa_decode_probs(DecodeArgs a, float* pro
 
 template <int D>
 constexpr size_t decode_smem() {
-  return kDecodeStages * 2 * kTile * (D * 2 + 16) + sizeof(DecodeBarriers);
+  return 1024 + kDecodeStages * 2 * kTile * D * 2 + sizeof(DecodeBarriers);
+}
+
+// 4-D map of a bf16 page pool: (column, kv head, token in page, page); box = 64 columns x
+// box_rows tokens of one kv head, 128-byte swizzle, zero fill outside the pool.
+bool make_pool_map(CUtensorMap* map, const void* base, const DecodeArgs& a, int pages) {
+  using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Encode encode = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) !=
+            cudaSuccess || result != cudaDriverEntryPointSuccess)
+      return static_cast<Encode>(nullptr);
+    return reinterpret_cast<Encode>(sym);
+  }();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(a.head_dim), static_cast<cuuint64_t>(a.kv_heads),
+                              static_cast<cuuint64_t>(a.page_size), static_cast<cuuint64_t>(pages)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(a.head_dim) * 2, a.token_stride * 2,
+                                 a.page_stride * 2};
+  const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(a.box_rows), 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides,
+                box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+         CUDA_SUCCESS;
 }
 
 }  // namespace
 
 bool gqa_decode_uses_tensor_cores(const DecodeArgs& a) {
   const int group = a.q_heads / a.kv_heads;
+  const int pages = a.block_table ? a.num_pages : a.batch;
   return a.kv_is_bf16 && (a.head_dim == 64 || a.head_dim == 128) && group <= 16 &&
          (a.round || a.q_is_bf16) && a.token_stride % 8 == 0 && a.page_stride % 8 == 0 &&
+         a.page_size % 16 == 0 && pages > 0 &&
          (reinterpret_cast<uintptr_t>(a.k_base) & 15u) == 0 &&
          (reinterpret_cast<uintptr_t>(a.v_base) & 15u) == 0;
 }
 
-cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& a) {
+cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args) {
+  DecodeArgs a = args;
   if (gqa_decode_uses_tensor_cores(a)) {
     const dim3 grid(a.splits, a.kv_heads, a.batch);
     cudaError_t e;
+    a.box_rows = a.page_size % kTile == 0 ? kTile : 16;
+    const int pages = a.block_table ? a.num_pages : a.batch;
+    CUtensorMap map_k, map_v;
+    if (!make_pool_map(&map_k, a.k_base, a, pages) || !make_pool_map(&map_v, a.v_base, a, pages))
+      return cudaErrorInvalidValue;
     if (a.head_dim == 128) {
       e = cudaFuncSetAttribute(gqa_decode_tc<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(decode_smem<128>()));
       if (e != cudaSuccess) return e;
-      gqa_decode_tc<128><<<grid, kDecodeThreads, decode_smem<128>(), stream>>>(a);
+      gqa_decode_tc<128><<<grid, kDecodeThreads, decode_smem<128>(), stream>>>(map_k, map_v, a);
     } else {
       e = cudaFuncSetAttribute(gqa_decode_tc<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(decode_smem<64>()));
       if (e != cudaSuccess) return e;
-      gqa_decode_tc<64><<<grid, kDecodeThreads, decode_smem<64>(), stream>>>(a);
+      gqa_decode_tc<64><<<grid, kDecodeThreads, decode_smem<64>(), stream>>>(map_k, map_v, a);
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;

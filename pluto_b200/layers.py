@@ -318,6 +318,7 @@ def kv_layout(k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: Optional[
     s.max_blocks = 0 if block_table is None else block_table.shape[1]
     s.page_size, s.page_stride, s.token_stride = page_size, page_stride, token_stride
     s.dtype = 1 if k_pool.dtype == torch.bfloat16 else 0
+    s.num_pages = k_pool.shape[0] if k_pool.dim() == 4 else 1
     return s
 
 
