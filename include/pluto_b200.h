@@ -229,6 +229,12 @@ int pluto_gdn_conv_silu(pluto_stream_t stream, const void* input, const float* w
                         int in_dtype, int batch, int tokens, int channels, int width,
                         int round_to_bf16, float* state, void* output, int out_dtype);
 
+/* Bytes of scratch the chunked prefill path of pluto_gdn_prefill needs (host-only query; 0 when
+ * the shape has no chunked path: it needs bf16 q/k/v, key_dim 128, value_dim a multiple of 32,
+ * tokens >= 64). */
+size_t pluto_gdn_prefill_workspace_bytes(int batch, int tokens, int key_heads, int value_heads,
+                                         int key_dim, int value_dim, int in_dtype);
+
 /* The recurrence over `tokens` tokens from the given state.  Stands in for RecurrenceForward
  * (src/llm/layers/sequence_delta_net.cc:55-102) without its per-token state history; with
  * tokens = 1 it is DeltaRecurrenceKernel (cached_attention_ops.cc:205-251).
@@ -237,12 +243,16 @@ int pluto_gdn_conv_silu(pluto_stream_t stream, const void* input, const float* w
  *   state        fp32 [batch, value_heads, key_dim, value_dim], read and updated in place
  *   normalize_qk 1: q^ = q*rsqrt(sum q^2 + 1e-6)/sqrt(key_dim), k^ = k*rsqrt(sum k^2 + 1e-6) as
  *                the reference; 0: use k as given and q * q_scale
+ *   workspace    NULL: token-sequential kernel (the reference's arithmetic, state on chip).
+ *                >= pluto_gdn_prefill_workspace_bytes(...) bytes, 256-byte aligned: chunked form
+ *                (64-token chunks, in-chunk products on the tensor cores, fp32 state carried
+ *                across chunks); same result within bf16 operand rounding.
  * key_dim <= 128, value_dim <= 256, value_heads % key_heads == 0. */
 int pluto_gdn_prefill(pluto_stream_t stream, const void* q, const void* k, const void* v,
                       int in_dtype, const float* g, const float* beta, float* state, void* out,
                       int out_dtype, int batch, int tokens, int key_heads, int value_heads,
                       int key_dim, int value_dim, int normalize_qk, float q_scale,
-                      int round_to_bf16);
+                      int round_to_bf16, void* workspace, size_t workspace_bytes);
 
 /* Single-token form of pluto_gdn_prefill (tokens = 1): DeltaRecurrenceKernel as launched by
  * DeltaNetState::Step (src/llm/layers/util/cached_attention_ops.cc:205-251, :401-431). */

@@ -44,7 +44,8 @@ _SIGNATURES = {
     "pluto_gqa_decode_probs": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _sz] + [_i] * 4),
     "pluto_gdn_gates": (_i, [_vp] * 5 + [_i, C.c_longlong, _i, _i, _vp, _vp]),
     "pluto_gdn_conv_silu": (_i, [_vp] * 3 + [_i] * 6 + [_vp, _vp, _i]),
-    "pluto_gdn_prefill": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 8 + [_fp, _i]),
+    "pluto_gdn_prefill": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 8 + [_fp, _i, _vp, _sz]),
+    "pluto_gdn_prefill_workspace_bytes": (_sz, [_i] * 7),
     "pluto_gdn_step": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 7 + [_fp, _i]),
     "pluto_interleave_heads": (_i, [_vp, _vp, _vp, _i, C.c_longlong, _sz]),
     "pluto_gdn_out_norm_gate": (_i, [_vp, _vp, _i, _vp, _i, _vp, C.c_longlong, _i, _fp, _i, _i,

@@ -344,7 +344,7 @@ int pluto_gdn_prefill(pluto_stream_t stream, const void* q, const void* k, const
                       int in_dtype, const float* g, const float* beta, float* state, void* out,
                       int out_dtype, int batch, int tokens, int key_heads, int value_heads,
                       int key_dim, int value_dim, int normalize_qk, float q_scale,
-                      int round_to_bf16) {
+                      int round_to_bf16, void* workspace, size_t workspace_bytes) {
   if (int c = check_gdn(batch, tokens, key_heads, value_heads, key_dim, value_dim)) return c;
   if (!dtype_ok(in_dtype) || !dtype_ok(out_dtype))
     return fail(PLUTO_E_INVALID, "invalid DeltaNet dimensions or parameters");
@@ -356,7 +356,27 @@ int pluto_gdn_prefill(pluto_stream_t stream, const void* q, const void* k, const
   a.batch = batch; a.tokens = tokens; a.key_heads = key_heads; a.value_heads = value_heads;
   a.key_dim = key_dim; a.value_dim = value_dim;
   a.normalize_qk = normalize_qk; a.q_scale = q_scale; a.round = round_to_bf16;
+  if (workspace != nullptr) {
+    if (!pluto::gdn_chunked_supported(a))
+      return fail(PLUTO_E_INVALID, "DeltaNet shape has no chunked prefill path; pass a null workspace");
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 ||
+        workspace_bytes < pluto::gdn_chunked_workspace_bytes(batch, tokens, value_heads, value_dim))
+      return fail(PLUTO_E_INVALID, "DeltaNet prefill workspace is too small or misaligned");
+    uint32_t* status = pluto::kernel_status_word();
+    if (!status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
+    return from_cuda(pluto::gdn_chunked(stream, a, workspace, status), "Qwen gated delta chunked prefill");
+  }
   return from_cuda(pluto::gdn_recurrent(stream, a), "Qwen gated delta recurrence");
+}
+
+size_t pluto_gdn_prefill_workspace_bytes(int batch, int tokens, int key_heads, int value_heads,
+                                         int key_dim, int value_dim, int in_dtype) {
+  if (batch <= 0 || tokens <= 0 || key_heads <= 0 || value_heads <= 0) return 0;
+  pluto::GdnArgs a{};
+  a.in_is_bf16 = in_dtype == PLUTO_BF16; a.key_dim = key_dim; a.value_dim = value_dim;
+  a.tokens = tokens;
+  if (!pluto::gdn_chunked_supported(a)) return 0;
+  return pluto::gdn_chunked_workspace_bytes(batch, tokens, value_heads, value_dim);
 }
 
 int pluto_gdn_step(pluto_stream_t stream, const void* q, const void* k, const void* v,
@@ -365,7 +385,7 @@ int pluto_gdn_step(pluto_stream_t stream, const void* q, const void* k, const vo
                    int value_dim, int normalize_qk, float q_scale, int round_to_bf16) {
   return pluto_gdn_prefill(stream, q, k, v, in_dtype, g, beta, state, out, out_dtype, batch, 1,
                            key_heads, value_heads, key_dim, value_dim, normalize_qk, q_scale,
-                           round_to_bf16);
+                           round_to_bf16, nullptr, 0);
 }
 
 int pluto_gdn_out_norm_gate(pluto_stream_t stream, const void* core, int core_dtype, const void* z,

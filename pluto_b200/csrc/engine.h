@@ -131,6 +131,10 @@ struct GdnArgs {
   int round;
 };
 cudaError_t gdn_recurrent(cudaStream_t stream, const GdnArgs& args);
+// gdn_chunked.cu: chunked (64-token) form for bf16 inputs with key_dim 128
+bool gdn_chunked_supported(const GdnArgs& args);
+size_t gdn_chunked_workspace_bytes(int batch, int tokens, int value_heads, int value_dim);
+cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& args, void* workspace, uint32_t* status);
 cudaError_t gdn_gates(cudaStream_t stream, const void* a_in, const void* b_in, const float* a_log,
                       const float* dt_bias, int in_is_bf16, long long tokens, int heads, int round,
                       float* g, float* beta);

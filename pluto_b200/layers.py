@@ -507,18 +507,30 @@ class DeltaNetState:
 
 
 def gdn_prefill(q, k, v, g, beta, state, normalize_qk=True, q_scale=1.0, round_to_bfloat16=True,
-                out=None):
+                out=None, chunked=None, workspace=None):
     """Recurrence over a whole sequence from `state` (updated in place).  q,k [B,T,Hk,dk];
-    v [B,T,Hv,dv]; g,beta fp32 [B,T,Hv]; state fp32 [B,Hv,dk,dv].  Returns out like v."""
+    v [B,T,Hv,dv]; g,beta fp32 [B,T,Hv]; state fp32 [B,Hv,dk,dv].  Returns out like v.
+    chunked=None picks the 64-token chunked tensor-core form when the shape has one (bf16 inputs,
+    key width 128, T >= 64) and the token-sequential kernel otherwise; False forces the latter."""
     B, T, Hk, dk = q.shape
     Hv, dv = v.shape[2], v.shape[3]
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     if out is None:
         out = torch.empty_like(v)
-    check(_capi.lib().pluto_gdn_prefill(_stream(), _ptr(q), _ptr(k), _ptr(v), _dt(v), _ptr(g),
-                                        _ptr(beta), _ptr(state), _ptr(out), _dt(out), B, T, Hk, Hv,
-                                        dk, dv, int(normalize_qk), float(q_scale),
-                                        int(round_to_bfloat16)))
+    L = _capi.lib()
+    ws_ptr, ws_bytes = None, 0
+    if chunked is None or chunked:
+        need = L.pluto_gdn_prefill_workspace_bytes(B, T, Hk, Hv, dk, dv, _dt(v))
+        if need == 0 and chunked:
+            raise _invalid("DeltaNet shape has no chunked prefill path")
+        if need:
+            ws = workspace if workspace is not None else _workspace(q.device, need + 256)
+            ws_ptr = (ws.data_ptr() + 255) // 256 * 256
+            ws_bytes = ws.numel() - (ws_ptr - ws.data_ptr())
+    check(L.pluto_gdn_prefill(_stream(), _ptr(q), _ptr(k), _ptr(v), _dt(v), _ptr(g), _ptr(beta),
+                              _ptr(state), _ptr(out), _dt(out), B, T, Hk, Hv, dk, dv,
+                              int(normalize_qk), float(q_scale), int(round_to_bfloat16), ws_ptr,
+                              ws_bytes))
     return out
 
 
