@@ -319,6 +319,314 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Two query tiles per CTA in ping-pong (sequences longer than one tile).
+//
+// A CTA owns the query tiles 2i and 2i+1 of one (sequence, head) and shares every K/V tile
+// between them.  Warps 4-7 run the softmax of tile A, warps 8-11 of tile B; the MMA warp issues
+//     ... PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), PV_A(j+1), ...
+// so while one tile's rows are in the exp2 unit the tensor pipe works on the other tile, and the
+// two units overlap instead of alternating.  Each tile has one score buffer in TMEM (P overwrites
+// S in place; the next QK^T of that tile is issued behind the PV that reads P, and the tensor pipe
+// runs its instructions in order) and its own O accumulator: 2 x 128 + 2 x D <= 512 columns.
+// The copy/MMA warpgroup hands registers to the softmax warpgroups (setmaxnreg), so a softmax
+// thread can hold its whole 128-entry score row and read TMEM once per tile.
+// ---------------------------------------------------------------------------------------------
+constexpr int kThreadsPair = 384;
+
+struct PairBarriers {
+  uint64_t q_full;
+  uint64_t k_full[kStages], k_empty[kStages];
+  uint64_t v_full[kStages], v_empty[kStages];
+  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint32_t tmem_base;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreadsPair, 1)
+attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
+                    const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, FwdParams p) {
+  constexpr int kSlabs = D / 64;
+  constexpr int kTileBytes = kSlabs * kSlabBytes;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kIdescQK = umma_idesc_bf16(kBM, kBN, false);
+  constexpr uint32_t kIdescPV = umma_idesc_bf16(kBM, D, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;                              // two query tiles
+  uint8_t* k_smem = q_smem + 2 * kTileBytes;
+  uint8_t* v_smem = k_smem + kStages * kTileBytes;
+  PairBarriers* bar = reinterpret_cast<PairBarriers*>(v_smem + kStages * kTileBytes);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int pair = gridDim.x - 1 - blockIdx.x;         // heaviest pairs first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int q_tiles = (p.seq + kBM - 1) / kBM;
+  const int tile_of[2] = {2 * pair, 2 * pair + 1};
+  const int n_of[2] = {tile_of[0] + 1, tile_of[1] < q_tiles ? tile_of[1] + 1 : 0};
+  const int n_max = max(n_of[0], n_of[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bar->k_full[s], 1);
+      mbar_init(&bar->k_empty[s], 1);
+      mbar_init(&bar->v_full[s], 1);
+      mbar_init(&bar->v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar->s_full[s], 1);
+      mbar_init(&bar->p_full[s], 128);
+      mbar_init(&bar->pv_done[s], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  // Register file: 384 threads x 168 at launch.  The warpgroup of the copy/MMA warps gives most of
+  // its registers back so that the two softmax warpgroups can keep a whole score row each.
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (lane == 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      const int kv_head = head / p.group;
+      mbar_expect_tx(&bar->q_full, 2 * kTileBytes);  // a tile past the sequence end reads zeros
+      for (int x = 0; x < 2; ++x)
+        for (int s = 0; s < kSlabs; ++s)
+          tma_load_3d(q_smem + x * kTileBytes + s * kSlabBytes, &map_q,
+                      p.q_col0 + head * p.q_head_cols + s * 64, tile_of[x] * kBM, batch,
+                      &bar->q_full);
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j % kStages, use = j / kStages;
+        if (use > 0) ok = mbar_wait(&bar->k_empty[st], (use - 1) & 1, p.status, 1);
+        if (!ok) break;
+        mbar_expect_tx(&bar->k_full[st], kTileBytes);
+        for (int s = 0; s < kSlabs; ++s)
+          tma_load_3d(k_smem + st * kTileBytes + s * kSlabBytes, &map_k,
+                      p.k_col0 + kv_head * p.kv_head_cols + s * 64, j * kBN, batch,
+                      &bar->k_full[st]);
+        if (use > 0) ok = mbar_wait(&bar->v_empty[st], (use - 1) & 1, p.status, 2);
+        if (!ok) break;
+        mbar_expect_tx(&bar->v_full[st], kTileBytes);
+        for (int s = 0; s < kSlabs; ++s)
+          tma_load_3d(v_smem + st * kTileBytes + s * kSlabBytes, &map_v,
+                      p.v_col0 + kv_head * p.kv_head_cols + s * 64, j * kBN, batch,
+                      &bar->v_full[st]);
+      }
+      mbar_wait(&bar->q_full, 0, p.status, 3);
+      for (int j = max(0, n_max - kStages); j < n_max; ++j) {
+        mbar_wait(&bar->k_full[j % kStages], (j / kStages) & 1, p.status, 4);
+        mbar_wait(&bar->v_full[j % kStages], (j / kStages) & 1, p.status, 5);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (lane == 0) {
+      bool ok = mbar_wait(&bar->q_full, 0, p.status, 10);
+      tc_fence_after();
+      auto issue_qk = [&](int x, int j) -> bool {
+        const int st = j % kStages;
+        if (!mbar_wait(&bar->k_full[st], (j / kStages) & 1, p.status, 13)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(q_smem + x * kTileBytes);
+        const uint32_t k_addr = smem_u32(k_smem + st * kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * kSlabBytes + (ks % 4) * 32;
+          umma_ss(tmem + x * 128, umma_desc_sw128(q_addr + off, 16, 1024),
+                  umma_desc_sw128(k_addr + off, 16, 1024), kIdescQK, ks > 0);
+        }
+        tc_commit(&bar->s_full[x]);
+        return true;
+      };
+      auto issue_pv = [&](int x, int j) -> bool {
+        const int st = j % kStages;
+        if (!mbar_wait(&bar->p_full[x], j & 1, p.status, 11)) return false;
+        if (!mbar_wait(&bar->v_full[st], (j / kStages) & 1, p.status, 12)) return false;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(v_smem + st * kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks)
+          umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8,
+                  umma_desc_sw128(v_addr + ks * 2048, kSlabBytes, 1024), kIdescPV, j > 0 || ks > 0);
+        tc_commit(&bar->pv_done[x]);
+        return true;
+      };
+      for (int x = 0; x < 2 && ok; ++x)
+        if (n_of[x] > 0) ok = issue_qk(x, 0);
+      if (ok) tc_commit(&bar->k_empty[0]);
+      for (int j = 0; j < n_max && ok; ++j) {
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (j >= n_of[x]) continue;
+          ok = issue_pv(x, j);
+          if (ok && j + 1 < n_of[x]) ok = issue_qk(x, j + 1);
+        }
+        if (!ok) break;
+        tc_commit(&bar->v_empty[j % kStages]);
+        if (j + 1 < n_max) tc_commit(&bar->k_empty[(j + 1) % kStages]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax / epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int x = (warp - 4) / 4;                    // which query tile this warpgroup serves
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int q_tile = tile_of[x];
+    const int query = q_tile * kBM + row;
+    const int n_tiles = n_of[x];
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem + lane_base + x * 128;
+    const uint32_t o_addr = tmem + lane_base + 256 + x * 128;
+    float m_used = -INFINITY, m_true = -INFINITY, l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      ok = mbar_wait(&bar->s_full[x], j & 1, p.status, 20);
+      if (!ok) break;
+      tc_fence_after();
+      const bool diagonal = j == q_tile;
+      // the whole score row in registers (this warpgroup raised its register allowance)
+      uint32_t s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
+      tmem_wait_ld();
+      float mx[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
+      if (diagonal) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (c * 32 + i > row) s[c][i] = 0xff800000u;  // -inf above the diagonal
+            mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(s[c][i]));
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(s[c][i]));
+      }
+      m_true = fmaxf(m_true, fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                   fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))));
+      const bool grow = (m_true - m_used) * p.scale_log2 > kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float factor = grow ? fast_exp2((m_used - m_true) * p.scale_log2) : 1.0f;
+        if (grow) m_used = m_true;
+        l *= factor;
+        if (j > 0) {
+          ok = mbar_wait(&bar->pv_done[x], (j - 1) & 1, p.status, 21);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st32(o_addr + c * 32, o);
+          }
+        }
+      }
+      const float neg_m = -m_used * p.scale_log2;
+      float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), p.scale_log2, neg_m));
+          sum[(i >> 1) & 3] += p0 + p1;
+          packed[i / 2] = pack_bf16(p0, p1);
+        }
+        tmem_st16(s_addr + c * 16, packed);
+      }
+      l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->p_full[x]);
+    }
+    if (ok && n_tiles > 0) ok = mbar_wait(&bar->pv_done[x], (n_tiles - 1) & 1, p.status, 22);
+    if (ok && n_tiles > 0) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      const bool live = query < p.seq;
+      const size_t token = static_cast<size_t>(batch) * p.seq + query;
+      __nv_bfloat16* out = p.out + token * p.out_token + head * p.out_head;
+      float* core = p.core ? p.core + token * p.out_token + head * p.out_head : nullptr;
+      const __nv_bfloat16* gate =
+          p.gate ? p.gate + token * p.gate_token + head * p.gate_head : nullptr;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + c * 32, o);
+        tmem_wait_ld();
+        if (live) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float a = __uint_as_float(o[i]) * inv, b = __uint_as_float(o[i + 1]) * inv;
+            if (core) {
+              core[c * 32 + i] = a;
+              core[c * 32 + i + 1] = b;
+            }
+            if (gate) {
+              const float g0 = __bfloat162float(gate[c * 32 + i]);
+              const float g1 = __bfloat162float(gate[c * 32 + i + 1]);
+              float s0 = 1.0f / (1.0f + expf(-g0)), s1 = 1.0f / (1.0f + expf(-g1));
+              if (p.round_gate) {
+                s0 = bf16_round(s0);
+                s1 = bf16_round(s1);
+                a = bf16_round(a);
+                b = bf16_round(b);
+              }
+              a *= s0;
+              b *= s1;
+            }
+            w[i / 2] = pack_bf16(a, b);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(out + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      }
+      if (live && p.maxima) {
+        const size_t stat = (static_cast<size_t>(batch) * p.heads + head) * p.seq + query;
+        p.maxima[stat] = m_true * p.scale;
+        p.normalizers[stat] = l * fast_exp2((m_used - m_true) * p.scale_log2);
+      }
+    }
+  } else {
+    // warps 2-3 idle, but every warp of a warpgroup has to give its registers back together
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -386,22 +694,25 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
   p.gate_head = a.gate_head;
   p.round_gate = a.round_gate;
   p.status = a.status;
-  const dim3 grid((a.seq + kBM - 1) / kBM, a.heads, a.batch);
+  const int q_tiles = (a.seq + kBM - 1) / kBM;
   const size_t tile = static_cast<size_t>(a.head_dim / 64) * kSlabBytes;
-  const size_t smem = 1024 + tile * (1 + 2 * kStages) + sizeof(Barriers);
   cudaError_t e;
-  if (a.head_dim == 128) {
-    e = cudaFuncSetAttribute(attn_fwd_sm100<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem));
+  if (a.head_dim != 128 && a.head_dim != 64) return cudaErrorInvalidValue;
+  if (q_tiles >= 2) {
+    // two query tiles per CTA in ping-pong
+    const dim3 grid((q_tiles + 1) / 2, a.heads, a.batch);
+    const size_t smem = 1024 + tile * (2 + 2 * kStages) + sizeof(PairBarriers);
+    auto kernel = a.head_dim == 128 ? attn_fwd_sm100_pair<128> : attn_fwd_sm100_pair<64>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    attn_fwd_sm100<128><<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, p);
-  } else if (a.head_dim == 64) {
-    e = cudaFuncSetAttribute(attn_fwd_sm100<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-    attn_fwd_sm100<64><<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, p);
+    kernel<<<grid, kThreadsPair, smem, stream>>>(map_q, map_k, map_v, p);
   } else {
-    return cudaErrorInvalidValue;
+    const dim3 grid(q_tiles, a.heads, a.batch);
+    const size_t smem = 1024 + tile * (1 + 2 * kStages) + sizeof(Barriers);
+    auto kernel = a.head_dim == 128 ? attn_fwd_sm100<128> : attn_fwd_sm100<64>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    kernel<<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, p);
   }
   return cudaGetLastError();
 }
