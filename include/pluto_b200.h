@@ -69,15 +69,24 @@ int pluto_kernel_status(uint32_t* value /* host */, int clear);
 int pluto_attn_fwd(pluto_stream_t stream, const void* qkv, void* out, float* maxima,
                    float* normalizers, int batch, int seq, int heads, int head_dim, int dtype);
 
+/* Bytes of scratch the tensor-core backward needs (host-only query; 0 when the shape has no
+ * tensor-core path: it needs bf16 activations and head_dim 64 or 128). */
+size_t pluto_attn_bwd_workspace_bytes(int batch, int seq, int heads, int head_dim, int dtype);
+
 /* Stands in for AttentionLayer::bwd_impl + FlashAttentionQueryBackwardKernel +
  * FlashAttentionKeyValueBackwardKernel (src/llm/layers/attention.cc:509-596, :235-314, :319-396).
  *   d_out        fp32 [batch*seq, heads*head_dim] (upstream gradient is always fp32)
  *   d_qkv        fp32 [batch*seq, 3*heads*head_dim]: dQ third, dK third, dV third (fully written)
  *   deltas       fp32 scratch [batch*heads*seq] (sum dO*O per row; written then read)
- * Deterministic: single-writer tiles, fixed-order reductions, no floating-point atomics. */
+ *   workspace    NULL: exact fp32 kernels (every shape).  >= pluto_attn_bwd_workspace_bytes(...)
+ *                bytes, 256-byte aligned: tcgen05 kernels (holds the gradient rounded to bf16 and
+ *                a padded per-row statistics record).
+ * Deterministic either way: single-writer tiles, fixed-order reductions, no floating-point
+ * atomics. */
 int pluto_attn_bwd(pluto_stream_t stream, const void* qkv, const void* out, const float* d_out,
                    const float* maxima, const float* normalizers, float* d_qkv, float* deltas,
-                   int batch, int seq, int heads, int head_dim, int dtype);
+                   int batch, int seq, int heads, int head_dim, int dtype, void* workspace,
+                   size_t workspace_bytes);
 
 /* Stands in for AttentionProbabilitiesKernel behind LayerHooks::attention_probabilities_hook
  * (src/llm/layers/attention.cc:176-230, :475-502).  probs: fp32 [batch, heads, seq, seq], zeros

@@ -30,7 +30,8 @@ _SIGNATURES = {
     "pluto_build_info": (C.c_char_p, []),
     "pluto_kernel_status": (_i, [C.POINTER(C.c_uint32), _i]),
     "pluto_attn_fwd": (_i, [_vp] * 5 + [_i] * 5),
-    "pluto_attn_bwd": (_i, [_vp] * 8 + [_i] * 5),
+    "pluto_attn_bwd": (_i, [_vp] * 8 + [_i] * 5 + [_vp, _sz]),
+    "pluto_attn_bwd_workspace_bytes": (_sz, [_i] * 5),
     "pluto_attn_probs": (_i, [_vp] * 5 + [_i] * 5),
     "pluto_gqa_prefill_fwd": (_i, [_vp] * 9 + [_i] * 5 + [_sz, _sz, _i]),
     "pluto_qk_prepare": (_i, [_vp] * 4 + [_i, _sz, _sz] + [_vp] * 4 + [_i, _vp] + [_i] * 6

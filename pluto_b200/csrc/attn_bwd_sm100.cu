@@ -1,0 +1,543 @@
+// Causal multi-head attention backward on the Blackwell tensor cores (bf16 operands, fp32
+// accumulation, head width 64 or 128) for the packed [rows, 3E] layout of AttentionLayer.
+//
+// Same decomposition as the reference (src/llm/layers/attention.cc:235-314 query-owned pass,
+// :319-396 key/value-owned pass): two passes that each own their output tile, so every dQ, dK
+// and dV element has one writer and a fixed summation order -- no floating-point atomics, runs
+// are bitwise repeatable.  Probabilities are rebuilt from the statistics the forward saved:
+//     P = exp(s*scale - max) / l,   dP = dO V^T,   dS = P (dP - delta) scale,   delta = sum dO.O
+//     dQ = dS K                     dK = dS^T Q,                                dV = P^T dO
+//
+//   attn_bwd_prep        delta per row (fp32, from the stored O like the reference), the upstream
+//                        gradient rounded to bf16 for the tensor cores, and a padded per-row
+//                        record (max*log2e, 1/l, delta) the other two kernels fetch.
+//   attn_bwd_dq_sm100    one CTA per 128-query tile; per 64-key step: S and dP by tcgen05.mma into
+//                        TMEM, one thread per query row turns them into dS (bf16, written over S in
+//                        TMEM), dQ += dS K with dS as the TMEM operand and K MN-major from smem.
+//   attn_bwd_dkv_sm100   one CTA per 128-key tile; per 64-query step: S^T = K Q^T and dP^T = V dO^T,
+//                        one thread per key row builds P^T and dS^T, then dV += P^T dO and
+//                        dK += dS^T Q.
+// TMEM budgets (<= 256 columns for head width 64) let two CTAs share an SM, so one CTA's
+// exponentials overlap the other's MMAs.  All copies are tiled TMA loads without multicast; all
+// waits are bounded.
+#include "common.cuh"
+#include "engine.h"
+
+namespace pluto {
+namespace {
+
+constexpr int kRowTile = 128;   // rows owned by a CTA (TMEM lanes)
+constexpr int kColTile = 64;    // opposite-side rows consumed per step
+constexpr int kBwdStages = 2;
+constexpr int kBwdThreads = 256;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdParams {
+  int seq, heads, head_dim;
+  float scale, scale_log2;
+  const float4* stats;   // [(b*H+h) * seq_pad + s] = (max*log2e, 1/l, delta, 0); zero past seq
+  int seq_pad;
+  float* d_qkv;          // fp32 [rows, 3E]
+  uint32_t* status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// prep: grid (rows), 128 threads; one row (all heads) per CTA
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d_out,
+              const float* __restrict__ maxima, const float* __restrict__ normalizers,
+              __nv_bfloat16* __restrict__ d_out_bf16, float4* __restrict__ stats,
+              float* __restrict__ deltas, int seq, int seq_pad, int heads, int head_dim) {
+  const int b = blockIdx.y, s = blockIdx.x;   // s runs over the padded length
+  const int E = heads * head_dim;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  for (int h = warp; h < heads; h += 4) {
+    const size_t record = (static_cast<size_t>(b) * heads + h) * seq_pad + s;
+    if (s >= seq) {
+      if (lane == 0) stats[record] = make_float4(0.f, 0.f, 0.f, 0.f);
+      continue;
+    }
+    const size_t row = static_cast<size_t>(b) * seq + s;
+    float part = 0.0f;
+    for (int d = lane; d < head_dim; d += 32) {
+      const float g = d_out[row * E + h * head_dim + d];
+      part = fmaf(g, __bfloat162float(out[row * E + h * head_dim + d]), part);
+      d_out_bf16[row * E + h * head_dim + d] = __float2bfloat16_rn(g);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) {
+      const size_t stat = (static_cast<size_t>(b) * heads + h) * seq + s;
+      deltas[stat] = part;
+      stats[record] = make_float4(maxima[stat] * kLog2e, 1.0f / normalizers[stat], part, 0.0f);
+    }
+  }
+}
+
+struct DqBarriers {
+  uint64_t qdo_full, k_full[kBwdStages], v_full[kBwdStages], kv_empty[kBwdStages];
+  uint64_t s_full, ds_full, dq_done;
+  uint32_t tmem_base;
+};
+
+// ---------------------------------------------------------------------------------------------
+// dQ: grid (query tiles of 128, heads, batch)
+// ---------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, D == 64 ? 2 : 1)
+attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
+                  const __grid_constant__ CUtensorMap map_qkv64,
+                  const __grid_constant__ CUtensorMap map_do128, BwdParams p) {
+  constexpr int kSlabs = D / 64;
+  constexpr int kRowTileBytes = kSlabs * kRowTile * 128;   // [128 x D] bf16
+  constexpr int kColTileBytes = kSlabs * kColTile * 128;   // [64 x D] bf16
+  constexpr uint32_t kTmemCols = 256;
+  constexpr uint32_t kColS = 0, kColDP = 64, kColDQ = 128;
+  constexpr uint32_t kIdescS = umma_idesc_bf16(kRowTile, kColTile, false);
+  constexpr uint32_t kIdescDQ = umma_idesc_bf16(kRowTile, D, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* do_smem = q_smem + kRowTileBytes;
+  uint8_t* k_smem = do_smem + kRowTileBytes;
+  uint8_t* v_smem = k_smem + kBwdStages * kColTileBytes;
+  DqBarriers* bar = reinterpret_cast<DqBarriers*>(v_smem + kBwdStages * kColTileBytes);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int q_tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int E = p.heads * D;
+  const int col_tiles = (p.seq + kColTile - 1) / kColTile;
+  const int n_steps = min(2 * q_tile + 2, col_tiles);   // key tiles that hold a visible key
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->qdo_full, 1);
+    for (int s = 0; s < kBwdStages; ++s) {
+      mbar_init(&bar->k_full[s], 1);
+      mbar_init(&bar->v_full[s], 1);
+      mbar_init(&bar->kv_empty[s], 1);
+    }
+    mbar_init(&bar->s_full, 1);
+    mbar_init(&bar->ds_full, 128);
+    mbar_init(&bar->dq_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_qkv128);
+      tma_prefetch_desc(&map_qkv64);
+      tma_prefetch_desc(&map_do128);
+      mbar_expect_tx(&bar->qdo_full, 2 * kRowTileBytes);
+      for (int s = 0; s < kSlabs; ++s) {
+        tma_load_3d(q_smem + s * kRowTile * 128, &map_qkv128, head * D + s * 64, q_tile * kRowTile,
+                    batch, &bar->qdo_full);
+        tma_load_3d(do_smem + s * kRowTile * 128, &map_do128, head * D + s * 64, q_tile * kRowTile,
+                    batch, &bar->qdo_full);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_steps && ok; ++j) {
+        const int st = j % kBwdStages, use = j / kBwdStages;
+        if (use > 0) ok = mbar_wait(&bar->kv_empty[st], (use - 1) & 1, p.status, 50);
+        if (!ok) break;
+        mbar_expect_tx(&bar->k_full[st], kColTileBytes);
+        mbar_expect_tx(&bar->v_full[st], kColTileBytes);
+        for (int s = 0; s < kSlabs; ++s) {
+          tma_load_3d(k_smem + st * kColTileBytes + s * kColTile * 128, &map_qkv64,
+                      E + head * D + s * 64, j * kColTile, batch, &bar->k_full[st]);
+          tma_load_3d(v_smem + st * kColTileBytes + s * kColTile * 128, &map_qkv64,
+                      2 * E + head * D + s * 64, j * kColTile, batch, &bar->v_full[st]);
+        }
+      }
+      mbar_wait(&bar->qdo_full, 0, p.status, 51);
+      for (int j = max(0, n_steps - kBwdStages); j < n_steps; ++j) {
+        mbar_wait(&bar->k_full[j % kBwdStages], (j / kBwdStages) & 1, p.status, 52);
+        mbar_wait(&bar->v_full[j % kBwdStages], (j / kBwdStages) & 1, p.status, 53);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(&bar->qdo_full, 0, p.status, 54);
+      const uint32_t q_addr = smem_u32(q_smem), do_addr = smem_u32(do_smem);
+      for (int j = 0; j < n_steps && ok; ++j) {
+        const int st = j % kBwdStages;
+        ok = mbar_wait(&bar->k_full[st], (j / kBwdStages) & 1, p.status, 55) &&
+             mbar_wait(&bar->v_full[st], (j / kBwdStages) & 1, p.status, 56);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(k_smem + st * kColTileBytes);
+        const uint32_t v_addr = smem_u32(v_smem + st * kColTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t a_off = (ks / 4) * kRowTile * 128 + (ks % 4) * 32;
+          const uint32_t b_off = (ks / 4) * kColTile * 128 + (ks % 4) * 32;
+          umma_ss(tmem + kColS, umma_desc_sw128(q_addr + a_off, 16, 1024),
+                  umma_desc_sw128(k_addr + b_off, 16, 1024), kIdescS, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t a_off = (ks / 4) * kRowTile * 128 + (ks % 4) * 32;
+          const uint32_t b_off = (ks / 4) * kColTile * 128 + (ks % 4) * 32;
+          umma_ss(tmem + kColDP, umma_desc_sw128(do_addr + a_off, 16, 1024),
+                  umma_desc_sw128(v_addr + b_off, 16, 1024), kIdescS, ks > 0);
+        }
+        tc_commit(&bar->s_full);
+        ok = mbar_wait(&bar->ds_full, j & 1, p.status, 57);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kColTile / 16; ++ks)   // dQ += dS K: 16 keys per step, K MN-major
+          umma_ts(tmem + kColDQ, tmem + kColS + ks * 8,
+                  umma_desc_sw128(k_addr + ks * 2048, kColTile * 128, 1024), kIdescDQ,
+                  j > 0 || ks > 0);
+        tc_commit(&bar->kv_empty[st]);
+      }
+      if (ok) tc_commit(&bar->dq_done);
+    }
+  } else if (warp >= 4) {
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const int query = q_tile * kRowTile + row;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float4 st4 = p.stats[(static_cast<size_t>(batch) * p.heads + head) * p.seq_pad +
+                               min(query, p.seq_pad - 1)];
+    const float neg_m = -st4.x, inv_l = st4.y, delta = st4.z;
+    bool ok = true;
+    for (int j = 0; j < n_steps && ok; ++j) {
+      ok = mbar_wait(&bar->s_full, j & 1, p.status, 58);
+      if (!ok) break;
+      tc_fence_after();
+      const bool masked = (j + 1) * kColTile - 1 > q_tile * kRowTile;  // tile may cross the diagonal
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[32], dp[32], packed[16];
+        tmem_ld32(tmem + lane_base + kColS + half * 32, s);
+        tmem_ld32(tmem + lane_base + kColDP + half * 32, dp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = j * kColTile + half * 32 + i + e;
+            float pr = fast_exp2(fmaf(__uint_as_float(s[i + e]), p.scale_log2, neg_m)) * inv_l;
+            if (masked && key > query) pr = 0.0f;
+            ds[e] = pr * (__uint_as_float(dp[i + e]) - delta) * p.scale;
+          }
+          packed[i / 2] = pack_bf16(ds[0], ds[1]);
+        }
+        tmem_st16(tmem + lane_base + kColS + half * 16, packed);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->ds_full);
+    }
+    if (ok) ok = mbar_wait(&bar->dq_done, 0, p.status, 59);
+    if (ok) {
+      tc_fence_after();
+      float* dst = p.d_qkv + (static_cast<size_t>(batch) * p.seq + query) * 3 * E + head * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem + lane_base + kColDQ + c * 32, o);
+        tmem_wait_ld();
+        if (query < p.seq) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+struct DkvBarriers {
+  uint64_t kv_full, q_full[kBwdStages], q_empty[kBwdStages];
+  uint64_t s_full, ds_full, done;
+  uint32_t tmem_base;
+};
+
+// ---------------------------------------------------------------------------------------------
+// dK, dV: grid (key tiles of 128, heads, batch)
+// ---------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, D == 64 ? 2 : 1)
+attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
+                   const __grid_constant__ CUtensorMap map_qkv64,
+                   const __grid_constant__ CUtensorMap map_do64, BwdParams p) {
+  constexpr int kSlabs = D / 64;
+  constexpr int kRowTileBytes = kSlabs * kRowTile * 128;
+  constexpr int kColTileBytes = kSlabs * kColTile * 128;
+  constexpr int kStatsBytes = kColTile * 16;
+  constexpr int kStageBytes = 2 * kColTileBytes + kStatsBytes;   // Q_i, dO_i, stats
+  constexpr uint32_t kTmemCols = D == 64 ? 256 : 512;
+  constexpr uint32_t kColS = 0, kColDP = 64, kColDV = 128, kColDK = 128 + D;
+  constexpr uint32_t kIdescS = umma_idesc_bf16(kRowTile, kColTile, false);
+  constexpr uint32_t kIdescAcc = umma_idesc_bf16(kRowTile, D, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* k_smem = smem;
+  uint8_t* v_smem = k_smem + kRowTileBytes;
+  uint8_t* stage_smem = v_smem + kRowTileBytes;   // per stage: Q_i | dO_i | stats
+  DkvBarriers* bar = reinterpret_cast<DkvBarriers*>(stage_smem + kBwdStages * kStageBytes);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int k_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int E = p.heads * D;
+  const int col_tiles = (p.seq + kColTile - 1) / kColTile;
+  const int first = 2 * k_tile;                    // first query tile that can see these keys
+  const int n_steps = max(0, col_tiles - first);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->kv_full, 1);
+    for (int s = 0; s < kBwdStages; ++s) {
+      mbar_init(&bar->q_full[s], 1);
+      mbar_init(&bar->q_empty[s], 1);
+    }
+    mbar_init(&bar->s_full, 1);
+    mbar_init(&bar->ds_full, 128);
+    mbar_init(&bar->done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  const float4* stats_row = p.stats + (static_cast<size_t>(batch) * p.heads + head) * p.seq_pad;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_qkv128);
+      tma_prefetch_desc(&map_qkv64);
+      tma_prefetch_desc(&map_do64);
+      mbar_expect_tx(&bar->kv_full, 2 * kRowTileBytes);
+      for (int s = 0; s < kSlabs; ++s) {
+        tma_load_3d(k_smem + s * kRowTile * 128, &map_qkv128, E + head * D + s * 64,
+                    k_tile * kRowTile, batch, &bar->kv_full);
+        tma_load_3d(v_smem + s * kRowTile * 128, &map_qkv128, 2 * E + head * D + s * 64,
+                    k_tile * kRowTile, batch, &bar->kv_full);
+      }
+      bool ok = true;
+      for (int i = 0; i < n_steps && ok; ++i) {
+        const int st = i % kBwdStages, use = i / kBwdStages, tile = first + i;
+        if (use > 0) ok = mbar_wait(&bar->q_empty[st], (use - 1) & 1, p.status, 60);
+        if (!ok) break;
+        uint8_t* dst = stage_smem + st * kStageBytes;
+        mbar_expect_tx(&bar->q_full[st], kStageBytes);
+        for (int s = 0; s < kSlabs; ++s) {
+          tma_load_3d(dst + s * kColTile * 128, &map_qkv64, head * D + s * 64, tile * kColTile,
+                      batch, &bar->q_full[st]);
+          tma_load_3d(dst + kColTileBytes + s * kColTile * 128, &map_do64, head * D + s * 64,
+                      tile * kColTile, batch, &bar->q_full[st]);
+        }
+        bulk_load(dst + 2 * kColTileBytes, stats_row + tile * kColTile, kStatsBytes, &bar->q_full[st]);
+      }
+      mbar_wait(&bar->kv_full, 0, p.status, 61);
+      for (int i = max(0, n_steps - kBwdStages); i < n_steps; ++i)
+        mbar_wait(&bar->q_full[i % kBwdStages], (i / kBwdStages) & 1, p.status, 62);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(&bar->kv_full, 0, p.status, 63);
+      const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
+      for (int i = 0; i < n_steps && ok; ++i) {
+        const int st = i % kBwdStages;
+        ok = mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 64);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(stage_smem + st * kStageBytes);
+        const uint32_t do_addr = q_addr + kColTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {   // S^T = K Q^T
+          const uint32_t a_off = (ks / 4) * kRowTile * 128 + (ks % 4) * 32;
+          const uint32_t b_off = (ks / 4) * kColTile * 128 + (ks % 4) * 32;
+          umma_ss(tmem + kColS, umma_desc_sw128(k_addr + a_off, 16, 1024),
+                  umma_desc_sw128(q_addr + b_off, 16, 1024), kIdescS, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {   // dP^T = V dO^T
+          const uint32_t a_off = (ks / 4) * kRowTile * 128 + (ks % 4) * 32;
+          const uint32_t b_off = (ks / 4) * kColTile * 128 + (ks % 4) * 32;
+          umma_ss(tmem + kColDP, umma_desc_sw128(v_addr + a_off, 16, 1024),
+                  umma_desc_sw128(do_addr + b_off, 16, 1024), kIdescS, ks > 0);
+        }
+        tc_commit(&bar->s_full);
+        ok = mbar_wait(&bar->ds_full, i & 1, p.status, 65);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kColTile / 16; ++ks) {   // 16 queries per step, operands MN-major
+          umma_ts(tmem + kColDV, tmem + kColS + ks * 8,
+                  umma_desc_sw128(do_addr + ks * 2048, kColTile * 128, 1024), kIdescAcc,
+                  i > 0 || ks > 0);
+          umma_ts(tmem + kColDK, tmem + kColDP + ks * 8,
+                  umma_desc_sw128(q_addr + ks * 2048, kColTile * 128, 1024), kIdescAcc,
+                  i > 0 || ks > 0);
+        }
+        tc_commit(&bar->q_empty[st]);
+      }
+      if (ok) tc_commit(&bar->done);
+    }
+  } else if (warp >= 4) {
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const int key = k_tile * kRowTile + row;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ok = true;
+    for (int i = 0; i < n_steps && ok; ++i) {
+      const int st = i % kBwdStages, tile = first + i;
+      ok = mbar_wait(&bar->s_full, i & 1, p.status, 66) &&
+           mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 68);  // stats landed (acquire)
+      if (!ok) break;
+      tc_fence_after();
+      const float4* st4 = reinterpret_cast<const float4*>(stage_smem + st * kStageBytes + 2 * kColTileBytes);
+      const bool masked = tile * kColTile < k_tile * kRowTile + kRowTile;  // some query may precede a key
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[32], dp[32], pp[16], dsp[16];
+        tmem_ld32(tmem + lane_base + kColS + half * 32, s);
+        tmem_ld32(tmem + lane_base + kColDP + half * 32, dp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float pr[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float4 q4 = st4[half * 32 + c + e];   // same address for the whole warp
+            const int query = tile * kColTile + half * 32 + c + e;
+            pr[e] = fast_exp2(fmaf(__uint_as_float(s[c + e]), p.scale_log2, -q4.x)) * q4.y;
+            if (masked && query < key) pr[e] = 0.0f;
+            ds[e] = pr[e] * (__uint_as_float(dp[c + e]) - q4.z) * p.scale;
+          }
+          pp[c / 2] = pack_bf16(pr[0], pr[1]);
+          dsp[c / 2] = pack_bf16(ds[0], ds[1]);
+        }
+        // P^T over the consumed part of S^T, dS^T over the consumed part of dP^T
+        tmem_st16(tmem + lane_base + kColS + half * 16, pp);
+        tmem_st16(tmem + lane_base + kColDP + half * 16, dsp);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->ds_full);
+    }
+    if (ok && n_steps > 0) ok = mbar_wait(&bar->done, 0, p.status, 67);
+    if (ok) {
+      tc_fence_after();
+      float* dst = p.d_qkv + (static_cast<size_t>(batch) * p.seq + key) * 3 * E + head * D;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {   // 0: dV at 2E, 1: dK at E
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (n_steps > 0) {
+            tmem_ld32(tmem + lane_base + (which == 0 ? kColDV : kColDK) + c * 32, o);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+          if (key < p.seq) {
+            float* out = dst + (which == 0 ? 2 * E : E) + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<uint4*>(out + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <int D>
+cudaError_t launch_bwd_tc(cudaStream_t stream, const CUtensorMap& qkv128, const CUtensorMap& qkv64,
+                          const CUtensorMap& do128, const CUtensorMap& do64, const BwdParams& p,
+                          int batch) {
+  constexpr int kSlabs = D / 64;
+  const size_t dq_smem = 1024 + 2 * kSlabs * kRowTile * 128 + 2 * kBwdStages * kSlabs * kColTile * 128 +
+                         sizeof(DqBarriers);
+  const size_t dkv_smem = 1024 + 2 * kSlabs * kRowTile * 128 +
+                          kBwdStages * (2 * kSlabs * kColTile * 128 + kColTile * 16) + sizeof(DkvBarriers);
+  cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(dq_smem));
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(attn_bwd_dkv_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(dkv_smem));
+  if (e != cudaSuccess) return e;
+  const dim3 grid((p.seq + kRowTile - 1) / kRowTile, p.heads, batch);
+  attn_bwd_dq_sm100<D><<<grid, kBwdThreads, dq_smem, stream>>>(qkv128, qkv64, do128, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  attn_bwd_dkv_sm100<D><<<grid, kBwdThreads, dkv_smem, stream>>>(qkv128, qkv64, do64, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t attn_bwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim) {
+  const size_t seq_pad = (static_cast<size_t>(seq) + kColTile - 1) / kColTile * kColTile + kColTile;
+  const size_t do_bytes = (static_cast<size_t>(batch) * seq * heads * head_dim * 2 + 255) / 256 * 256;
+  return do_bytes + static_cast<size_t>(batch) * heads * seq_pad * sizeof(float4);
+}
+
+cudaError_t attn_bwd_tc(cudaStream_t stream, const void* qkv, const void* out, const float* d_out,
+                        const float* maxima, const float* normalizers, float* d_qkv, float* deltas,
+                        void* workspace, int batch, int seq, int heads, int head_dim,
+                        uint32_t* status) {
+  const int E = heads * head_dim;
+  const int seq_pad = (seq + kColTile - 1) / kColTile * kColTile + kColTile;
+  const size_t do_bytes = (static_cast<size_t>(batch) * seq * E * 2 + 255) / 256 * 256;
+  auto* do_bf16 = static_cast<__nv_bfloat16*>(workspace);
+  auto* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(workspace) + do_bytes);
+  attn_bwd_prep<<<dim3(seq_pad, batch), 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(out), d_out, maxima, normalizers, do_bf16, stats, deltas, seq,
+      seq_pad, heads, head_dim);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  CUtensorMap qkv128, qkv64, do128, do64;
+  if (!make_token_map(&qkv128, qkv, 3 * E, seq, batch, 3 * static_cast<size_t>(E), kRowTile) ||
+      !make_token_map(&qkv64, qkv, 3 * E, seq, batch, 3 * static_cast<size_t>(E), kColTile) ||
+      !make_token_map(&do128, do_bf16, E, seq, batch, E, kRowTile) ||
+      !make_token_map(&do64, do_bf16, E, seq, batch, E, kColTile))
+    return cudaErrorInvalidValue;
+  BwdParams p;
+  p.seq = seq;
+  p.heads = heads;
+  p.head_dim = head_dim;
+  p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
+  p.scale_log2 = p.scale * kLog2e;
+  p.stats = stats;
+  p.seq_pad = seq_pad;
+  p.d_qkv = d_qkv;
+  p.status = status;
+  if (head_dim == 64) return launch_bwd_tc<64>(stream, qkv128, qkv64, do128, do64, p, batch);
+  if (head_dim == 128) return launch_bwd_tc<128>(stream, qkv128, qkv64, do128, do64, p, batch);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace pluto

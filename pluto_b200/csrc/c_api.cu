@@ -91,7 +91,8 @@ int pluto_attn_fwd(pluto_stream_t stream, const void* qkv, void* out, float* max
 
 int pluto_attn_bwd(pluto_stream_t stream, const void* qkv, const void* out, const float* d_out,
                    const float* maxima, const float* normalizers, float* d_qkv, float* deltas,
-                   int batch, int seq, int heads, int head_dim, int dtype) {
+                   int batch, int seq, int heads, int head_dim, int dtype, void* workspace,
+                   size_t workspace_bytes) {
   if (int c = check_mha(batch, seq, heads, head_dim, dtype)) return c;
   if (!qkv) return fail(PLUTO_E_INVALID, "attention backward requires the saved Q/K/V");
   if (!out) return fail(PLUTO_E_INVALID, "attention backward requires the saved output");
@@ -99,10 +100,28 @@ int pluto_attn_bwd(pluto_stream_t stream, const void* qkv, const void* out, cons
   if (!normalizers) return fail(PLUTO_E_INVALID, "attention backward requires the saved normalizers");
   if (!d_out || !d_qkv || !deltas)
     return fail(PLUTO_E_INVALID, "attention backward requires non-null gradient pointers");
+  if (workspace != nullptr) {
+    const size_t need = pluto_attn_bwd_workspace_bytes(batch, seq, heads, head_dim, dtype);
+    if (need == 0)
+      return fail(PLUTO_E_INVALID, "attention backward has no tensor-core path for this shape; pass a null workspace");
+    if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 ||
+        !aligned16(qkv) || !aligned16(d_qkv))
+      return fail(PLUTO_E_INVALID, "attention backward workspace is too small or misaligned");
+    uint32_t* status = pluto::kernel_status_word();
+    if (!status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
+    return from_cuda(pluto::attn_bwd_tc(stream, qkv, out, d_out, maxima, normalizers, d_qkv, deltas,
+                                        workspace, batch, seq, heads, head_dim, status),
+                     "attention backward (tcgen05) launch");
+  }
   return from_cuda(pluto::attn_generic_bwd(stream, qkv, out, d_out, maxima, normalizers, d_qkv,
                                            deltas, batch, seq, heads, head_dim,
                                            dtype == PLUTO_BF16),
                    "attention backward launch");
+}
+
+size_t pluto_attn_bwd_workspace_bytes(int batch, int seq, int heads, int head_dim, int dtype) {
+  if (batch <= 0 || seq <= 0 || heads <= 0 || !tensor_core_shape(head_dim, dtype)) return 0;
+  return pluto::attn_bwd_tc_workspace_bytes(batch, seq, heads, head_dim);
 }
 
 int pluto_attn_probs(pluto_stream_t stream, const void* qkv, const float* maxima,

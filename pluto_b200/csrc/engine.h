@@ -29,6 +29,13 @@ cudaError_t attn_generic_bwd(cudaStream_t stream, const void* qkv, const void* o
                              float* d_qkv, float* deltas, int batch, int seq, int heads,
                              int head_dim, bool bf16);
 
+// ---- attn_bwd_sm100.cu: tcgen05 backward, bf16, head_dim 64 or 128 -----------------------------
+size_t attn_bwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim);
+cudaError_t attn_bwd_tc(cudaStream_t stream, const void* qkv, const void* out, const float* d_out,
+                        const float* maxima, const float* normalizers, float* d_qkv, float* deltas,
+                        void* workspace, int batch, int seq, int heads, int head_dim,
+                        uint32_t* status);
+
 // ---- attn_fwd_sm100.cu: tcgen05 forward, bf16, head_dim 64 or 128 ------------------------------
 struct AttnFwdArgs {
   const void* q;      // bf16; token stride q_token elements; q_cols valid columns per token

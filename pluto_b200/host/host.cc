@@ -210,6 +210,10 @@ StatusOr<BufferVec> AttentionLayer::bwd_impl(cuda::Executor& executor,
   PLUTO_RETURN_IF_ERROR(ValidateBuffer(executor, state.intermediates[3], stats_bytes, "attention saved normalizers"));
   PLUTO_ASSIGN_OR_RETURN(Buffer gradient, Buffer::Allocate(executor, static_cast<size_t>(rows) * 3 * embedding_dim_ * sizeof(float)));
   PLUTO_ASSIGN_OR_RETURN(Buffer deltas, Buffer::Allocate(executor, stats_bytes));
+  const int dtype = output_type_ == DataType::BF16 ? PLUTO_BF16 : PLUTO_FP32;
+  const size_t workspace_bytes = pluto_attn_bwd_workspace_bytes(
+      rows / context_length_, context_length_, num_heads_, embedding_dim_ / num_heads_, dtype);
+  PLUTO_ASSIGN_OR_RETURN(Buffer workspace, Buffer::Allocate(executor, workspace_bytes));
   PLUTO_RETURN_IF_ERROR(FromEngine(
       pluto_attn_bwd(executor.stream(), state.intermediates[0].data(), state.intermediates[1].data(),
                      static_cast<const float*>(output_gradients[0].data()),
@@ -217,7 +221,7 @@ StatusOr<BufferVec> AttentionLayer::bwd_impl(cuda::Executor& executor,
                      static_cast<const float*>(state.intermediates[3].data()),
                      static_cast<float*>(gradient.data()), static_cast<float*>(deltas.data()),
                      rows / context_length_, context_length_, num_heads_,
-                     embedding_dim_ / num_heads_, output_type_ == DataType::BF16 ? PLUTO_BF16 : PLUTO_FP32),
+                     embedding_dim_ / num_heads_, dtype, workspace.data(), workspace_bytes),
       "attention backward launch"));
   return BufferVec{gradient};
 }

@@ -133,6 +133,9 @@ class AttentionLayer(Layer):
         self.num_heads_ = num_heads
         self.embedding_dim_ = embedding_dim
         self.output_type_ = data_type
+        # bf16 layers with head width 64/128 run backward on the tensor cores; set False to force
+        # the exact fp32 kernels (every shape has them)
+        self.tensor_core_backward = True
 
     @staticmethod
     def Create(context_length: int, num_heads: int, embedding_dim: int,
@@ -208,10 +211,16 @@ class AttentionLayer(Layer):
         _validate_buffer(normalizers, rows * H * 4, "attention saved normalizers")
         d_qkv = torch.empty((rows, 3 * E), dtype=torch.float32, device=d_out.device)
         deltas = torch.empty((rows * H,), dtype=torch.float32, device=d_out.device)
-        check(_capi.lib().pluto_attn_bwd(_stream(), _ptr(qkv), _ptr(out), _ptr(d_out),
-                                         _ptr(maxima), _ptr(normalizers), _ptr(d_qkv),
-                                         _ptr(deltas), rows // S, S, H, E // H,
-                                         self._dtype_code()))
+        L = _capi.lib()
+        ws_ptr, ws_bytes = None, 0
+        need = L.pluto_attn_bwd_workspace_bytes(rows // S, S, H, E // H, self._dtype_code())
+        if need and self.tensor_core_backward:
+            ws = torch.empty((need + 256,), dtype=torch.uint8, device=d_out.device)
+            ws_ptr = (ws.data_ptr() + 255) // 256 * 256
+            ws_bytes = need
+        check(L.pluto_attn_bwd(_stream(), _ptr(qkv), _ptr(out), _ptr(d_out), _ptr(maxima),
+                               _ptr(normalizers), _ptr(d_qkv), _ptr(deltas), rows // S, S, H, E // H,
+                               self._dtype_code(), ws_ptr, ws_bytes))
         return [d_qkv]
 
 

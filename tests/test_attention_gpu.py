@@ -187,6 +187,27 @@ def test_future_tokens_and_other_sequences_cannot_matter(bf16):
     assert np.all(new_g[cut:] == 0.0)
 
 
+@pytest.mark.parametrize("shape", [(300, 2, 128, 2), (1024, 2, 256, 1), (65, 3, 192, 2)])
+def test_tensor_core_backward_matches_exact_backward(shape):
+    """bf16, head width 64/128: the tcgen05 backward against the exact fp32 backward kernels on
+    the same saved state (max-abs 2e-2), and bit-identical across repeated runs."""
+    context, heads, width, sequences = shape
+    rng = np.random.default_rng(77)
+    qkv = to_device_bf16(oracle.to_bf16_bits(rng.standard_normal((context * sequences, 3 * width), dtype=np.float32)))
+    d_out = torch.from_numpy(rng.standard_normal((context * sequences, width), dtype=np.float32)).cuda()
+    layer = AttentionLayer.Create(context, heads, width, DataType.BF16)
+    fwd = layer.fwd([qkv])
+    fast = layer.bwd([d_out], fwd.state)[0]
+    again = layer.bwd([d_out], fwd.state)[0]
+    layer.tensor_core_backward = False
+    exact = layer.bwd([d_out], fwd.state)[0]
+    torch.cuda.synchronize()
+    assert torch.equal(fast, again)
+    assert (fast - exact).abs().max().item() <= 2e-2
+    assert torch.isfinite(fast).all()
+    assert _capi.kernel_status() == 0
+
+
 def test_validation_errors_launch_nothing():
     """attention_test.cc:549-626."""
     layer = AttentionLayer.Create(8, 2, 32, DataType.FP16)
@@ -241,6 +262,8 @@ def test_full_size_training_config_properties():
     assert torch.equal(out[:, 0], v[:, 0])
     dv_sum = grad.view(b, s, 3 * e)[:, :, 2 * e:].double().sum(1)
     do_sum = d_out.view(b, s, e).double().sum(1)
-    assert (dv_sum - do_sum).abs().max().item() < 2e-2
+    # the tensor-core backward rounds dO and P to bf16 (2^-9 each): allow 1 % of the summed magnitude
+    scale = d_out.view(b, s, e).abs().double().sum(1)
+    assert ((dv_sum - do_sum).abs() <= 2e-2 + 0.01 * scale).all()
     assert torch.isfinite(grad).all()
     assert _capi.kernel_status() == 0

@@ -34,6 +34,7 @@ def test_header_cites_the_reference_for_every_entry_point():
     for name in declared_functions():
         if name in ("pluto_last_error", "pluto_build_info", "pluto_kernel_status",
                     "pluto_gqa_decode_workspace_bytes", "pluto_gdn_prefill_workspace_bytes",
+                    "pluto_attn_bwd_workspace_bytes",
                     "pluto_gqa_decode_noalloc",
                     "pluto_gqa_decode_builtin_scratch_bytes"):
             continue
@@ -57,9 +58,9 @@ def test_attention_argument_validation_happens_before_gpu_work(engine):
     assert _code(engine, L.pluto_attn_fwd, None, one, one, one, one, 1, 8, 2, 64, 7)[0] == "Unimplemented"
     assert _code(engine, L.pluto_attn_fwd, None, one, one, one, one, 1, 8, 2, 300, 0)[0] == "Unimplemented"
     assert _code(engine, L.pluto_attn_fwd, None, None, one, one, one, 1, 8, 2, 64, 0)[0] == "InvalidArgument"
-    code, message = _code(engine, L.pluto_attn_bwd, None, one, one, one, None, one, one, one, 1, 8, 2, 64, 0)
+    code, message = _code(engine, L.pluto_attn_bwd, None, one, one, one, None, one, one, one, 1, 8, 2, 64, 0, None, 0)
     assert code == "InvalidArgument" and "saved maxima" in message
-    code, message = _code(engine, L.pluto_attn_bwd, None, one, one, one, one, None, one, one, 1, 8, 2, 64, 0)
+    code, message = _code(engine, L.pluto_attn_bwd, None, one, one, one, one, None, one, one, 1, 8, 2, 64, 0, None, 0)
     assert code == "InvalidArgument" and "saved normalizers" in message
 
 
