@@ -103,7 +103,8 @@ int pluto_attn_probs(pluto_stream_t stream, const void* qkv, const float* maxima
  *   q            bf16, token t / head h at q + (b*seq + t)*q_token_stride + h*q_head_stride
  *                (element strides; [T,Hq,D] is (Hq*D, D); the query half of [T,Hq,2,D] is
  *                (2*Hq*D, 2*D))
- *   gate         optional bf16, indexed with the same two strides (pass q + D for [T,Hq,2,D]);
+ *   gate         optional bf16; token t / head h at gate + (b*seq + t)*gate_token_stride +
+ *                h*gate_head_stride (for [T,Hq,2,D] pass base + D and strides (2*Hq*D, 2*D));
  *                when non-null out = R(R(core) * R(sigmoid(gate))), R = bf16 rounding when
  *                round_to_bf16, as the reference does
  *   k, v         bf16 [batch, seq, kv_heads, head_dim] contiguous
@@ -116,7 +117,7 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
                           const void* v, void* out, float* core, float* maxima,
                           float* normalizers, int batch, int seq, int q_heads, int kv_heads,
                           int head_dim, size_t q_token_stride, size_t q_head_stride,
-                          int round_to_bf16);
+                          size_t gate_token_stride, size_t gate_head_stride, int round_to_bf16);
 
 /* --------------------------------------------------------------------------------------------
  * KV cache addressing shared by prepare and decode.  The reference keeps one KeyValueCache per
@@ -214,11 +215,14 @@ size_t pluto_gqa_decode_builtin_scratch_bytes(void);
 
 /* Softmax row of the current query for the inspection hook.  Stands in for the cached
  * AttentionProbabilitiesKernel (cached_attention_ops.cc:131-178).  probs: fp32, row (b,h) at
- * probs + (b*Hq + h)*probs_stride, seq_lens[b] entries written. */
+ * probs + b*probs_batch_stride + h*probs_head_stride, seq_lens[b] entries written.  The
+ * reference's [Hq, length] is (anything, length); the [Hq, T, T] tensor of the sequence layer's
+ * hook is rows b = 0..T-1 with strides (T, T*T), seq_lens[b] = b + 1 and a block table that maps
+ * every row to the same page. */
 int pluto_gqa_decode_probs(pluto_stream_t stream, const void* q, int q_dtype,
                            const pluto_kv_cache* cache /* host */, const int32_t* seq_lens,
-                           float* probs, size_t probs_stride, int batch, int q_heads,
-                           int kv_heads, int head_dim);
+                           float* probs, size_t probs_batch_stride, size_t probs_head_stride,
+                           int batch, int q_heads, int kv_heads, int head_dim);
 
 /* --------------------------------------------------------------------------------------------
  * Gated delta-net.
@@ -248,6 +252,9 @@ size_t pluto_gdn_prefill_workspace_bytes(int batch, int tokens, int key_heads, i
  * (src/llm/layers/sequence_delta_net.cc:55-102) without its per-token state history; with
  * tokens = 1 it is DeltaRecurrenceKernel (cached_attention_ops.cc:205-251).
  *   q, k         [batch, tokens, key_heads, key_dim];  v, out [batch, tokens, value_heads, value_dim]
+ *   qk_token_stride, v_token_stride   elements between consecutive tokens of q/k and of v
+ *                (0 = dense).  The reference's packed [T, all Q | all K | all V] activation is
+ *                q = base, k = base + Hk*dk, v = base + 2*Hk*dk with both strides = channels.
  *   g, beta      fp32 [batch, tokens, value_heads]
  *   state        fp32 [batch, value_heads, key_dim, value_dim], read and updated in place
  *   normalize_qk 1: q^ = q*rsqrt(sum q^2 + 1e-6)/sqrt(key_dim), k^ = k*rsqrt(sum k^2 + 1e-6) as
@@ -260,8 +267,9 @@ size_t pluto_gdn_prefill_workspace_bytes(int batch, int tokens, int key_heads, i
 int pluto_gdn_prefill(pluto_stream_t stream, const void* q, const void* k, const void* v,
                       int in_dtype, const float* g, const float* beta, float* state, void* out,
                       int out_dtype, int batch, int tokens, int key_heads, int value_heads,
-                      int key_dim, int value_dim, int normalize_qk, float q_scale,
-                      int round_to_bf16, void* workspace, size_t workspace_bytes);
+                      int key_dim, int value_dim, size_t qk_token_stride, size_t v_token_stride,
+                      int normalize_qk, float q_scale, int round_to_bf16, void* workspace,
+                      size_t workspace_bytes);
 
 /* Single-token form of pluto_gdn_prefill (tokens = 1): DeltaRecurrenceKernel as launched by
  * DeltaNetState::Step (src/llm/layers/util/cached_attention_ops.cc:205-251, :401-431). */

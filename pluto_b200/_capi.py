@@ -33,7 +33,7 @@ _SIGNATURES = {
     "pluto_attn_bwd": (_i, [_vp] * 8 + [_i] * 5 + [_vp, _sz]),
     "pluto_attn_bwd_workspace_bytes": (_sz, [_i] * 5),
     "pluto_attn_probs": (_i, [_vp] * 5 + [_i] * 5),
-    "pluto_gqa_prefill_fwd": (_i, [_vp] * 9 + [_i] * 5 + [_sz, _sz, _i]),
+    "pluto_gqa_prefill_fwd": (_i, [_vp] * 9 + [_i] * 5 + [_sz, _sz, _sz, _sz, _i]),
     "pluto_qk_prepare": (_i, [_vp] * 4 + [_i, _sz, _sz] + [_vp] * 4 + [_i, _vp] + [_i] * 6
                          + [_fp, _fp, _i]),
     "pluto_gqa_decode_workspace_bytes": (_sz, [_i] * 5),
@@ -42,10 +42,11 @@ _SIGNATURES = {
     "pluto_gqa_decode_noalloc": (_i, [_vp, _vp, _i, _vp, _i, _sz, _sz, _vp, _vp, _i, _vp, _i, _vp]
                                  + [_i] * 5),
     "pluto_gqa_decode_builtin_scratch_bytes": (_sz, []),
-    "pluto_gqa_decode_probs": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _sz] + [_i] * 4),
+    "pluto_gqa_decode_probs": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _sz, _sz] + [_i] * 4),
     "pluto_gdn_gates": (_i, [_vp] * 5 + [_i, C.c_longlong, _i, _i, _vp, _vp]),
     "pluto_gdn_conv_silu": (_i, [_vp] * 3 + [_i] * 6 + [_vp, _vp, _i]),
-    "pluto_gdn_prefill": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 8 + [_fp, _i, _vp, _sz]),
+    "pluto_gdn_prefill": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 7 + [_sz, _sz, _i, _fp, _i, _vp,
+                                                                          _sz]),
     "pluto_gdn_prefill_workspace_bytes": (_sz, [_i] * 7),
     "pluto_gdn_step": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 7 + [_fp, _i]),
     "pluto_interleave_heads": (_i, [_vp, _vp, _vp, _i, C.c_longlong, _sz]),

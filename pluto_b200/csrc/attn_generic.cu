@@ -123,7 +123,7 @@ struct Dims {
 // Addressing of separate Q/K/V tensors for the forward kernel: element strides between tokens
 // and between heads, and how many query heads share one key/value head.
 struct Views {
-  size_t q_token, q_head, kv_token, kv_head, out_token, out_head;
+  size_t q_token, q_head, kv_token, kv_head, out_token, out_head, gate_token, gate_head;
   int group;
 };
 
@@ -204,7 +204,7 @@ attn_fwd_generic(const T* __restrict__ q, const T* __restrict__ k, const T* __re
     if (query >= S) continue;
     const float inv = 1.0f / l[i];
     const size_t o_off = (static_cast<size_t>(b) * S + query) * views.out_token + h * views.out_head;
-    const T* g = gate ? gate + (static_cast<size_t>(b) * S + query) * views.q_token + h * views.q_head
+    const T* g = gate ? gate + (static_cast<size_t>(b) * S + query) * views.gate_token + h * views.gate_head
                       : nullptr;
 #pragma unroll
     for (int c = 0; c < DC; ++c) {
@@ -503,10 +503,10 @@ cudaError_t attn_generic_fwd(cudaStream_t stream, const void* q, const void* k, 
                              void* out, float* maxima, float* normalizers, int batch, int seq,
                              int heads, int head_dim, size_t q_token, size_t q_head,
                              size_t kv_token, size_t kv_head, size_t out_token, size_t out_head,
-                             int group, const void* gate, float* core, int round_gate,
-                             bool bf16) {
+                             int group, const void* gate, size_t gate_token, size_t gate_head,
+                             float* core, int round_gate, bool bf16) {
   Dims dims{seq, heads, head_dim, 1.0f / sqrtf(static_cast<float>(head_dim))};
-  Views views{q_token, q_head, kv_token, kv_head, out_token, out_head, group};
+  Views views{q_token, q_head, kv_token, kv_head, out_token, out_head, gate_token, gate_head, group};
 #define CALL_FWD(T, DP, BM) \
   launch_fwd<T, DP, BM>(stream, q, k, v, out, maxima, normalizers, gate, core, round_gate, \
                         batch, dims, views)

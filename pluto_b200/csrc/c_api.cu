@@ -85,7 +85,8 @@ int pluto_attn_fwd(pluto_stream_t stream, const void* qkv, void* out, float* max
   return from_cuda(
       pluto::attn_generic_fwd(stream, base, base + E * es, base + 2 * E * es, out, maxima,
                               normalizers, batch, seq, heads, head_dim, 3 * E, head_dim, 3 * E,
-                              head_dim, E, head_dim, 1, nullptr, nullptr, 0, dtype == PLUTO_BF16),
+                              head_dim, E, head_dim, 1, nullptr, 0, 0, nullptr, 0,
+                              dtype == PLUTO_BF16),
       "attention forward launch");
 }
 
@@ -146,7 +147,7 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
                           const void* v, void* out, float* core, float* maxima,
                           float* normalizers, int batch, int seq, int q_heads, int kv_heads,
                           int head_dim, size_t q_token_stride, size_t q_head_stride,
-                          int round_to_bf16) {
+                          size_t gate_token_stride, size_t gate_head_stride, int round_to_bf16) {
   if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
       q_heads % kv_heads != 0 || head_dim > 256 || batch > 65535 || q_heads > 65535)
     return fail(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
@@ -162,7 +163,7 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
   const size_t out_token = static_cast<size_t>(q_heads) * head_dim;
   const bool tma_ok = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
                       q_token_stride % 8 == 0 && q_head_stride % 8 == 0 &&
-                      q_token_stride <= 0x7fffffffu && (!gate || aligned16(gate));
+                      q_token_stride <= 0x7fffffffu;
   if ((head_dim == 64 || head_dim == 128) && tma_ok) {
     pluto::AttnFwdArgs a{};
     a.q = q; a.k = k; a.v = v;
@@ -174,7 +175,7 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
     a.batch = batch; a.seq = seq; a.heads = q_heads; a.group = group; a.head_dim = head_dim;
     a.out = out; a.out_token = out_token; a.out_head = head_dim;
     a.maxima = maxima; a.normalizers = normalizers; a.core = core;
-    a.gate = gate; a.gate_token = q_token_stride; a.gate_head = q_head_stride;
+    a.gate = gate; a.gate_token = gate_token_stride; a.gate_head = gate_head_stride;
     a.round_gate = round_to_bf16;
     a.status = pluto::kernel_status_word();
     if (!a.status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
@@ -183,7 +184,8 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
   return from_cuda(
       pluto::attn_generic_fwd(stream, q, k, v, out, maxima, normalizers, batch, seq, q_heads,
                               head_dim, q_token_stride, q_head_stride, kv_token, head_dim,
-                              out_token, head_dim, group, gate, core, round_to_bf16, true),
+                              out_token, head_dim, group, gate, gate_token_stride, gate_head_stride,
+                              core, round_to_bf16, true),
       "GQA prefill launch");
 }
 
@@ -323,13 +325,14 @@ int pluto_gqa_decode(pluto_stream_t stream, const void* q, int q_dtype, const vo
 
 int pluto_gqa_decode_probs(pluto_stream_t stream, const void* q, int q_dtype,
                            const pluto_kv_cache* cache, const int32_t* seq_lens, float* probs,
-                           size_t probs_stride, int batch, int q_heads, int kv_heads,
-                           int head_dim) {
+                           size_t probs_batch_stride, size_t probs_head_stride, int batch,
+                           int q_heads, int kv_heads, int head_dim) {
   pluto::DecodeArgs a;
   if (int c = fill_decode(&a, q, q_dtype, cache, seq_lens, 1, batch, q_heads, kv_heads, head_dim))
     return c;
   if (!probs) return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
-  return from_cuda(pluto::gqa_decode_probabilities(stream, a, probs, probs_stride),
+  return from_cuda(pluto::gqa_decode_probabilities(stream, a, probs, probs_batch_stride,
+                                                   probs_head_stride),
                    "inspect cached attention probabilities");
 }
 
@@ -362,15 +365,23 @@ int pluto_gdn_conv_silu(pluto_stream_t stream, const void* input, const float* w
 int pluto_gdn_prefill(pluto_stream_t stream, const void* q, const void* k, const void* v,
                       int in_dtype, const float* g, const float* beta, float* state, void* out,
                       int out_dtype, int batch, int tokens, int key_heads, int value_heads,
-                      int key_dim, int value_dim, int normalize_qk, float q_scale,
-                      int round_to_bf16, void* workspace, size_t workspace_bytes) {
+                      int key_dim, int value_dim, size_t qk_token_stride, size_t v_token_stride,
+                      int normalize_qk, float q_scale, int round_to_bf16, void* workspace,
+                      size_t workspace_bytes) {
   if (int c = check_gdn(batch, tokens, key_heads, value_heads, key_dim, value_dim)) return c;
+  const size_t qk_dense = static_cast<size_t>(key_heads) * key_dim;
+  const size_t v_dense = static_cast<size_t>(value_heads) * value_dim;
+  if (qk_token_stride == 0) qk_token_stride = qk_dense;
+  if (v_token_stride == 0) v_token_stride = v_dense;
+  if (qk_token_stride < qk_dense || v_token_stride < v_dense)
+    return fail(PLUTO_E_INVALID, "DeltaNet token strides overlap");
   if (!dtype_ok(in_dtype) || !dtype_ok(out_dtype))
     return fail(PLUTO_E_INVALID, "invalid DeltaNet dimensions or parameters");
   if (!q || !k || !v || !g || !beta || !state || !out)
     return fail(PLUTO_E_INVALID, "DeltaNet requires non-null device pointers");
   pluto::GdnArgs a{};
   a.q = q; a.k = k; a.v = v; a.in_is_bf16 = in_dtype == PLUTO_BF16;
+  a.qk_token = qk_token_stride; a.v_token = v_token_stride;
   a.g = g; a.beta = beta; a.state = state; a.out = out; a.out_is_bf16 = out_dtype == PLUTO_BF16;
   a.batch = batch; a.tokens = tokens; a.key_heads = key_heads; a.value_heads = value_heads;
   a.key_dim = key_dim; a.value_dim = value_dim;
@@ -394,6 +405,7 @@ size_t pluto_gdn_prefill_workspace_bytes(int batch, int tokens, int key_heads, i
   pluto::GdnArgs a{};
   a.in_is_bf16 = in_dtype == PLUTO_BF16; a.key_dim = key_dim; a.value_dim = value_dim;
   a.tokens = tokens;
+  a.qk_token = 8; a.v_token = 8;  // alignment of the real strides is checked at launch
   if (!pluto::gdn_chunked_supported(a)) return 0;
   return pluto::gdn_chunked_workspace_bytes(batch, tokens, value_heads, value_dim);
 }
@@ -403,7 +415,7 @@ int pluto_gdn_step(pluto_stream_t stream, const void* q, const void* k, const vo
                    int out_dtype, int batch, int key_heads, int value_heads, int key_dim,
                    int value_dim, int normalize_qk, float q_scale, int round_to_bf16) {
   return pluto_gdn_prefill(stream, q, k, v, in_dtype, g, beta, state, out, out_dtype, batch, 1,
-                           key_heads, value_heads, key_dim, value_dim, normalize_qk, q_scale,
+                           key_heads, value_heads, key_dim, value_dim, 0, 0, normalize_qk, q_scale,
                            round_to_bf16, nullptr, 0);
 }
 

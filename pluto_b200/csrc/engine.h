@@ -19,8 +19,8 @@ cudaError_t attn_generic_fwd(cudaStream_t stream, const void* q, const void* k, 
                              void* out, float* maxima, float* normalizers, int batch, int seq,
                              int heads, int head_dim, size_t q_token, size_t q_head,
                              size_t kv_token, size_t kv_head, size_t out_token, size_t out_head,
-                             int group, const void* gate, float* core, int round_gate,
-                             bool bf16);
+                             int group, const void* gate, size_t gate_token, size_t gate_head,
+                             float* core, int round_gate, bool bf16);
 cudaError_t attn_generic_probs(cudaStream_t stream, const void* qkv, const float* maxima,
                                const float* normalizers, float* probs, int batch, int seq,
                                int heads, int head_dim, bool bf16);
@@ -95,7 +95,7 @@ struct DecodeArgs {
 bool gqa_decode_uses_tensor_cores(const DecodeArgs& args);
 cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args);
 cudaError_t gqa_decode_probabilities(cudaStream_t stream, const DecodeArgs& args, float* probs,
-                                     size_t probs_stride);
+                                     size_t batch_stride, size_t head_stride);
 
 // ---- qk_prepare.cu ------------------------------------------------------------------------------
 struct PrepareArgs {
@@ -127,6 +127,8 @@ struct GdnArgs {
   const void* k;
   const void* v;            // [batch, tokens, value_heads, value_dim]
   int in_is_bf16;
+  size_t qk_token;          // elements between tokens of q / k (key_heads*key_dim when dense)
+  size_t v_token;           // elements between tokens of v (value_heads*value_dim when dense)
   const float* g;           // [batch, tokens, value_heads] decay in (0, 1]
   const float* beta;        // [batch, tokens, value_heads]
   float* state;             // [batch, value_heads, key_dim, value_dim], updated in place

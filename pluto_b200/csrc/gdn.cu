@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(kRecThreads) gdn_recurrent_kernel(GdnArgs a) {
       const int tt = idx / 128, i = idx % 128, t = t0 + tt;
       float qv = 0.0f, kv = 0.0f;
       if (t < a.tokens && i < dk) {
-        const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.key_heads + kh) * dk + i;
+        const size_t off = (static_cast<size_t>(b) * a.tokens + t) * a.qk_token + static_cast<size_t>(kh) * dk + i;
         qv = load_any(a.q, off, a.in_is_bf16);
         kv = load_any(a.k, off, a.in_is_bf16);
       }
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(kRecThreads) gdn_recurrent_kernel(GdnArgs a) {
       const int tt = idx / kSlice, j = idx % kSlice, t = t0 + tt, c = slice * kSlice + j;
       float x = 0.0f;
       if (t < a.tokens && c < dv)
-        x = load_any(a.v, ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv + c,
+        x = load_any(a.v, (static_cast<size_t>(b) * a.tokens + t) * a.v_token + static_cast<size_t>(h) * dv + c,
                      a.in_is_bf16);
       sv[buf][tt][j] = x;
     }

@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare(GdnArgs a, uint8_t* wor
     const int t = t0 + rbase + 8 * i;
     qraw[i] = kraw[i] = make_uint4(0, 0, 0, 0);
     if (t < a.tokens) {
-      const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.key_heads + kh) * kDK + sub * 8;
+      const size_t off = (static_cast<size_t>(b) * a.tokens + t) * a.qk_token + static_cast<size_t>(kh) * kDK + sub * 8;
       qraw[i] = __ldg(reinterpret_cast<const uint4*>(qg + off));
       kraw[i] = __ldg(reinterpret_cast<const uint4*>(kg + off));
     }
@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare(GdnArgs a, uint8_t* wor
       vraw[i] = make_uint4(0, 0, 0, 0);
       if (t < a.tokens && j < dv)
         vraw[i] = __ldg(reinterpret_cast<const uint4*>(
-            vg + ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv + j));
+            vg + (static_cast<size_t>(b) * a.tokens + t) * a.v_token + static_cast<size_t>(h) * dv + j));
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -541,7 +541,9 @@ __global__ void __launch_bounds__(96) gdn_chunk_recurrence(GdnArgs a, const uint
 
 bool gdn_chunked_supported(const GdnArgs& a) {
   return a.in_is_bf16 && a.key_dim == kDK && a.value_dim % kSliceCols == 0 && a.value_dim <= 256 &&
-         a.tokens >= kC;
+         a.tokens >= kC && a.qk_token % 8 == 0 && a.v_token % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.k) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
 }
 
 size_t gdn_chunked_workspace_bytes(int batch, int tokens, int value_heads, int value_dim) {

@@ -414,14 +414,15 @@ __global__ void gqa_decode_merge(DecodeArgs a) {
   }
 }
 
-// Two-pass softmax row per (head, sequence) for the inspection hook: probs [B, Hq, max_len] rows
-// of `length` entries at stride probs_stride.  grid (q_heads, batch), 256 threads.
-__global__ void __launch_bounds__(256) gqa_decode_probs(DecodeArgs a, float* probs, size_t probs_stride) {
+// Two-pass softmax row per (head, sequence) for the inspection hook: row (b, h) of `length`
+// entries starts at probs + b*batch_stride + h*head_stride.  grid (q_heads, batch), 256 threads.
+__global__ void __launch_bounds__(256) gqa_decode_probs(DecodeArgs a, float* probs,
+                                                        size_t batch_stride, size_t head_stride) {
   const int head = blockIdx.x, b = blockIdx.y, D = a.head_dim;
   const int length = a.seq_lens[b];
   const int kv_head = head / (a.q_heads / a.kv_heads);
   const size_t element = a.kv_is_bf16 ? 2 : 4;
-  float* row = probs + (static_cast<size_t>(b) * a.q_heads + head) * probs_stride;
+  float* row = probs + static_cast<size_t>(b) * batch_stride + static_cast<size_t>(head) * head_stride;
   __shared__ float red[256];
   const size_t q0 = (static_cast<size_t>(b) * a.q_heads + head) * D;
   float local_max = -INFINITY;
@@ -536,8 +537,8 @@ cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args) {
 }
 
 cudaError_t gqa_decode_probabilities(cudaStream_t stream, const DecodeArgs& a, float* probs,
-                                     size_t probs_stride) {
-  gqa_decode_probs<<<dim3(a.q_heads, a.batch), 256, 0, stream>>>(a, probs, probs_stride);
+                                     size_t batch_stride, size_t head_stride) {
+  gqa_decode_probs<<<dim3(a.q_heads, a.batch), 256, 0, stream>>>(a, probs, batch_stride, head_stride);
   return cudaGetLastError();
 }
 

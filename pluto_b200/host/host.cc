@@ -320,8 +320,8 @@ Status CachedAttentionStep(cuda::Executor& executor, const FullAttentionParamete
   if (probabilities)
     PLUTO_RETURN_IF_ERROR(FromEngine(
         pluto_gqa_decode_probs(executor.stream(), queries.data(), PLUTO_FP32, &view,
-                               device_counters + 1, probabilities, position + 1, 1, p.query_heads,
-                               p.key_value_heads, p.head_dim),
+                               device_counters + 1, probabilities, 0, position + 1, 1,
+                               p.query_heads, p.key_value_heads, p.head_dim),
         "inspect cached attention probabilities"));
   return cache.Advance();
 }

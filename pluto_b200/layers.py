@@ -241,11 +241,15 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     if want_stats:
         maxima = torch.empty((B * Hq * T,), dtype=torch.float32, device=q.device)
         normalizers = torch.empty_like(maxima)
-    if gate is not None and (gate.stride(1) != q.stride(1) or gate.stride(2) != q.stride(2)):
-        raise _invalid("attention gate must share the query's strides")
+    gts = ghs = 0
+    if gate is not None:
+        if gate.stride(3) != 1 or gate.stride(0) != T * gate.stride(1):
+            raise _invalid("attention gate must have a contiguous head dimension and batch")
+        gts, ghs = gate.stride(1), gate.stride(2)
     check(_capi.lib().pluto_gqa_prefill_fwd(
         _stream(), _ptr(q), _ptr(gate), _ptr(k), _ptr(v), _ptr(out), _ptr(core), _ptr(maxima),
-        _ptr(normalizers), B, T, Hq, Hkv, D, q.stride(1), q.stride(2), int(round_to_bfloat16)))
+        _ptr(normalizers), B, T, Hq, Hkv, D, q.stride(1), q.stride(2), gts, ghs,
+        int(round_to_bfloat16)))
     result = {"out": out}
     if want_core:
         result["core"] = core
@@ -405,7 +409,7 @@ def CachedAttentionStep(p: FullAttentionParameters, cache: KeyValueCache, q_gate
                              int(p.round_to_bfloat16)))
     if probabilities is not None:
         check(L.pluto_gqa_decode_probs(_stream(), _ptr(queries), _dt(queries), C_byref(layout),
-                                       _ptr(lens), _ptr(probabilities), position + 1, 1, Hq, Hkv,
+                                       _ptr(lens), _ptr(probabilities), 0, position + 1, 1, Hq, Hkv,
                                        D))
     cache.Advance()
 
@@ -537,7 +541,7 @@ def gdn_prefill(q, k, v, g, beta, state, normalize_qk=True, q_scale=1.0, round_t
             ws_ptr = (ws.data_ptr() + 255) // 256 * 256
             ws_bytes = ws.numel() - (ws_ptr - ws.data_ptr())
     check(L.pluto_gdn_prefill(_stream(), _ptr(q), _ptr(k), _ptr(v), _dt(v), _ptr(g), _ptr(beta),
-                              _ptr(state), _ptr(out), _dt(out), B, T, Hk, Hv, dk, dv,
+                              _ptr(state), _ptr(out), _dt(out), B, T, Hk, Hv, dk, dv, 0, 0,
                               int(normalize_qk), float(q_scale), int(round_to_bfloat16), ws_ptr,
                               ws_bytes))
     return out
@@ -578,3 +582,296 @@ def gqa_decode_noalloc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
         C_byref(layout), _ptr(seq_lens), max_seq_len, _ptr(out), _dt(out), None, B, Hq, Hkv, D,
         int(round_to_bfloat16)))
     return out
+
+
+# =================================================================================================
+# Layer objects of the Qwen decoder: QwenAttentionLayer, DeltaNetLayer, SequenceDeltaNetLayer
+# =================================================================================================
+def _unimplemented(message: str) -> PlutoStatusError:
+    return PlutoStatusError("Unimplemented", message, -2)
+
+
+def _validate_bf16_inputs(inputs, counts, what: str) -> None:
+    """internal::ValidateBFloat16Inputs (src/llm/layers/util.cc): count and exact byte sizes."""
+    if len(inputs) != len(counts):
+        raise _invalid(f"{what} expects {len(counts)} inputs")
+    for tensor, count in zip(inputs, counts):
+        if not tensor.is_cuda:
+            raise _invalid(f"{what} input belongs to a different Executor")
+        if tensor.dtype != torch.bfloat16 or tensor.numel() != count:
+            raise _invalid(f"{what} input has {tensor.numel() * tensor.element_size()} bytes; "
+                           f"expected {2 * count}")
+
+
+class QwenAttentionLayer(Layer):
+    """Qwen grouped-query attention: per-head Q/K RMSNorm, partial RoPE, causal attention, sigmoid
+    output gate (src/llm/layers/qwen_attention.h:14-99, .cc:291-448).  Inputs are bf16
+    [T, query_heads, 2, head_dim] query/gate and [T, kv_heads, head_dim] K and V; the output is
+    bf16 [T, query_heads, head_dim].  A cache selects single-token inference (sequence_length 1,
+    backward rejected); without one the layer is the stateless sequence forward.  The reference
+    limits the sequence form to 128 positions because it materialises all probabilities; here any
+    length runs (the probabilities exist only when a hook asks for them)."""
+
+    kMaximumDimension = 1048576
+
+    def __init__(self, parameters, q_norm, k_norm, sequence_length, cache):
+        self.parameters_ = parameters
+        self.weights_ = [q_norm, k_norm]
+        self.sequence_length_ = sequence_length
+        self.cache_ = cache
+
+    @staticmethod
+    def Create(parameters: FullAttentionParameters, q_norm: torch.Tensor, k_norm: torch.Tensor,
+               sequence_length: int, cache: Optional[KeyValueCache] = None) -> "QwenAttentionLayer":
+        import math
+        p = parameters
+        if cache is not None:
+            if sequence_length != 1:
+                raise _invalid("cached Qwen attention requires sequence_length == 1")
+            if p.query_heads <= 0 or p.key_value_heads <= 0 or p.head_dim <= 0:
+                raise _invalid("QwenAttentionLayer dimensions must be positive")
+            if (p.query_heads * p.head_dim > QwenAttentionLayer.kMaximumDimension // 2
+                    or p.key_value_heads * p.head_dim > QwenAttentionLayer.kMaximumDimension):
+                raise _invalid("QwenAttentionLayer activation exceeds the layer dimension limit")
+            ValidateCachedAttention(p, cache)
+        else:
+            if (p.query_heads <= 0 or p.query_heads > 256 or p.key_value_heads <= 0
+                    or p.query_heads % p.key_value_heads or p.head_dim <= 0 or p.head_dim > 256
+                    or p.rotary_dim <= 0 or p.rotary_dim > p.head_dim or p.rotary_dim % 2
+                    or sequence_length <= 0 or not (p.rms_norm_epsilon > 0)
+                    or not math.isfinite(p.rms_norm_epsilon) or not (p.rope_theta > 0)
+                    or not math.isfinite(p.rope_theta)):
+                raise _invalid("sequence Qwen attention requires valid GQA dimensions and D<=256")
+        for norm in (q_norm, k_norm):
+            if norm is None or norm.dtype != torch.float32 or norm.numel() != p.head_dim or not norm.is_cuda:
+                raise _invalid("Qwen attention norms must be FP32 head-width parameters on its Executor")
+        _capi.lib()
+        return QwenAttentionLayer(p, q_norm, k_norm, sequence_length, cache)
+
+    def name(self) -> str:
+        return "QwenAttentionLayer"
+
+    def output_type(self) -> DataType:
+        return DataType.BF16
+
+    def weights(self):
+        return self.weights_
+
+    def input_types(self):
+        p, t = self.parameters_, self.sequence_length_
+        return [ActivationType(DataType.BF16, (-2, t, 2 * p.query_heads * p.head_dim)),
+                ActivationType(DataType.BF16, (-2, t, p.key_value_heads * p.head_dim)),
+                ActivationType(DataType.BF16, (-2, t, p.key_value_heads * p.head_dim))]
+
+    def output_types(self):
+        p = self.parameters_
+        return [ActivationType(DataType.BF16, (-2, self.sequence_length_, p.query_heads * p.head_dim))]
+
+    def fwd_impl(self, inputs, hooks) -> FwdResult:
+        return self._cached_forward(inputs, hooks) if self.cache_ is not None else \
+            self._sequence_forward(inputs, hooks)
+
+    def bwd_impl(self, output_gradients, state, hooks):
+        if self.cache_ is not None:
+            raise _unimplemented("QwenAttentionLayer with a KV cache supports inference only")
+        raise _unimplemented("QwenAttentionLayer sequence backward is not built in this engine yet")
+
+    def _cached_forward(self, inputs, hooks) -> FwdResult:
+        # src/llm/layers/qwen_attention.cc:370-412, minus the bf16<->fp32 cast launches
+        p = self.parameters_
+        width = p.query_heads * p.head_dim
+        kv = p.key_value_heads * p.head_dim
+        _validate_bf16_inputs(inputs, [2 * width, kv, kv], "QwenAttentionLayer")
+        if self.cache_.position() >= self.cache_.capacity():
+            raise _resource_exhausted("full-attention cache capacity reached")
+        output = torch.empty((1, width), dtype=torch.bfloat16, device=inputs[0].device)
+        length = self.cache_.position() + 1
+        inspect = hooks is not None and hooks.attention_probabilities_hook is not None
+        probabilities = torch.empty((p.query_heads, length), dtype=torch.float32,
+                                    device=inputs[0].device) if inspect else None
+        CachedAttentionStep(p, self.cache_, inputs[0].view(p.query_heads, 2, p.head_dim),
+                            inputs[1].view(p.key_value_heads, p.head_dim),
+                            inputs[2].view(p.key_value_heads, p.head_dim), self.weights_[0],
+                            self.weights_[1], output.view(p.query_heads, p.head_dim), probabilities)
+        if inspect:
+            hooks.attention_probabilities_hook(
+                self.name(), ActivationType(DataType.FP32, (1, p.query_heads, 1, length)), probabilities)
+        return FwdResult([output], BackwardState())
+
+    def _sequence_forward(self, inputs, hooks) -> FwdResult:
+        # src/llm/layers/qwen_attention.cc:414-448: PrepareKernel + ForwardKernel
+        p, t = self.parameters_, self.sequence_length_
+        hq, hkv, d = p.query_heads, p.key_value_heads, p.head_dim
+        _validate_bf16_inputs(inputs, [2 * t * hq * d, t * hkv * d, t * hkv * d], "QwenAttentionLayer")
+        if not p.round_to_bfloat16:
+            raise _unimplemented("sequence Qwen attention without bf16 rounding is not built")
+        L = _capi.lib()
+        device = inputs[0].device
+        q = torch.empty((1, t, hq, d), dtype=torch.bfloat16, device=device)
+        k = torch.empty((1, t, hkv, d), dtype=torch.bfloat16, device=device)
+        v = torch.empty_like(k)
+        layout = kv_layout(k, v, None, t, t * hkv * d, hkv * d)
+        check(L.pluto_qk_prepare(_stream(), _ptr(inputs[0]), _ptr(inputs[1]), _ptr(inputs[2]), 1,
+                                 2 * hq * d, 2 * d, _ptr(self.weights_[0]), _ptr(self.weights_[1]),
+                                 None, _ptr(q), 1, C_byref(layout), 1, t, hq, hkv, d, p.rotary_dim,
+                                 p.rms_norm_epsilon, p.rope_theta, 1))
+        qg = inputs[0].view(1, t, hq, 2, d)
+        result = gqa_prefill(q, k, v, gate=qg[:, :, :, 1], round_to_bfloat16=True, want_core=True)
+        output = result["out"].view(t, hq * d)
+        probabilities = torch.empty((0,), dtype=torch.float32, device=device)
+        if hooks is not None and hooks.attention_probabilities_hook is not None:
+            probabilities = torch.zeros((hq, t, t), dtype=torch.float32, device=device)
+            rows = torch.arange(1, t + 1, dtype=torch.int32, device=device)
+            table = torch.zeros((t, 1), dtype=torch.int32, device=device)
+            paged = kv_layout(k, v, table, t, t * hkv * d, hkv * d)
+            check(L.pluto_gqa_decode_probs(_stream(), _ptr(q), 1, C_byref(paged), _ptr(rows),
+                                           _ptr(probabilities), t, t * t, t, hq, hkv, d))
+            hooks.attention_probabilities_hook(
+                self.name(), ActivationType(DataType.FP32, (1, hq, t, t)), probabilities)
+        state = BackwardState(intermediates=[inputs[0], inputs[1], inputs[2], q, k, probabilities,
+                                             result["core"]])
+        return FwdResult([output], state)
+
+
+class DeltaNetLayer(Layer):
+    """Single-token gated delta-net layer over a DeltaNetState (src/llm/layers/delta_net.h:20-60,
+    .cc:38-110).  Inputs bf16 [1, QKV channels], [1, Hv*dv] (z), [1, Hv] (a), [1, Hv] (b); output
+    bf16 [1, Hv*dv].  Weights fp32: convolution [channels, kernel], A_log [Hv], dt_bias [Hv], RMS
+    multiplier [dv].  Inference only."""
+
+    kMaximumDimension = 1048576
+
+    def __init__(self, parameters, weights, state):
+        self.parameters_ = parameters
+        self.weights_ = weights
+        self.cache_ = state
+
+    @staticmethod
+    def Create(parameters: DeltaNetParameters, convolution, a_log, dt_bias, norm) -> "DeltaNetLayer":
+        p = parameters
+        if min(p.key_heads, p.value_heads, p.key_head_dim, p.value_head_dim, p.conv_kernel_dim) <= 0:
+            raise _invalid("DeltaNetLayer dimensions must be positive")
+        key_width, value_width = p.key_heads * p.key_head_dim, p.value_heads * p.value_head_dim
+        limit = DeltaNetLayer.kMaximumDimension
+        if key_width > limit // 2 or value_width > limit or 2 * key_width + value_width > limit:
+            raise _invalid("DeltaNetLayer activation exceeds the layer dimension limit")
+        channels = 2 * key_width + value_width
+        counts = [channels * p.conv_kernel_dim, p.value_heads, p.value_heads, p.value_head_dim]
+        for weight, count in zip((convolution, a_log, dt_bias, norm), counts):
+            if weight is None or not weight.is_cuda or weight.dtype != torch.float32 or weight.numel() != count:
+                raise _invalid("DeltaNetLayer weight has incorrect FP32 size or Executor")
+        return DeltaNetLayer(p, [convolution, a_log, dt_bias, norm], DeltaNetState.Create(p, convolution.device))
+
+    def name(self) -> str:
+        return "DeltaNetLayer"
+
+    def output_type(self) -> DataType:
+        return DataType.BF16
+
+    def weights(self):
+        return self.weights_
+
+    def Reset(self) -> None:
+        self.cache_.Reset()
+
+    def fwd_impl(self, inputs, hooks) -> FwdResult:
+        p = self.parameters_
+        width = p.value_heads * p.value_head_dim
+        channels = 2 * p.key_heads * p.key_head_dim + width
+        _validate_bf16_inputs(inputs, [channels, width, p.value_heads, p.value_heads], "DeltaNetLayer")
+        output = torch.empty((1, width), dtype=torch.bfloat16, device=inputs[0].device)
+        self.cache_.Step(inputs[0].view(-1), inputs[1].view(p.value_heads, p.value_head_dim),
+                         inputs[2].view(-1), inputs[3].view(-1), *self.weights_,
+                         output.view(p.value_heads, p.value_head_dim))
+        return FwdResult([output], BackwardState())
+
+    def bwd_impl(self, output_gradients, state, hooks):
+        raise _unimplemented("DeltaNetLayer supports cached inference only")
+
+
+class SequenceDeltaNetLayer(Layer):
+    """Full-sequence gated delta-net forward from a zero state
+    (src/llm/layers/sequence_delta_net.h:20-67, .cc:396-480): causal depthwise convolution + SiLU,
+    the recurrence, RMSNorm * weight * SiLU(z).  Inputs bf16 QKV [1,T,channels], Z [1,T,Hv*dv],
+    A and B [1,T,Hv]; output bf16 [1,T,Hv*dv].  The reference caps T at 128 because it stores every
+    intermediate state; here the recurrence is chunked and any T runs.  Backward is not built."""
+
+    def __init__(self, parameters, weights, sequence_length):
+        self.parameters_ = parameters
+        self.weights_ = weights
+        self.sequence_length_ = sequence_length
+
+    @staticmethod
+    def Create(parameters: DeltaNetParameters, convolution, a_log, dt_bias, norm,
+               sequence_length: int) -> "SequenceDeltaNetLayer":
+        import math
+        p = parameters
+        if (sequence_length < 1 or p.key_heads < 1 or p.value_heads < 1 or p.value_heads % p.key_heads
+                or p.key_head_dim < 1 or p.key_head_dim > 128 or p.value_head_dim < 1
+                or p.value_head_dim > 256 or p.conv_kernel_dim < 1 or p.conv_kernel_dim > 32
+                or not math.isfinite(p.rms_norm_epsilon) or p.rms_norm_epsilon <= 0):
+            raise _invalid("unsupported SequenceDeltaNetLayer shape")
+        channels = 2 * p.key_heads * p.key_head_dim + p.value_heads * p.value_head_dim
+        counts = [channels * p.conv_kernel_dim, p.value_heads, p.value_heads, p.value_head_dim]
+        for weight, count in zip((convolution, a_log, dt_bias, norm), counts):
+            if weight is None or weight.dtype != torch.float32:
+                raise _invalid("DeltaNet parameters must be FP32")
+            if not weight.is_cuda or weight.numel() != count:
+                raise _invalid(f"DeltaNet parameter has {weight.numel() * 4} bytes; expected {count * 4}")
+        _capi.lib()
+        return SequenceDeltaNetLayer(p, [convolution, a_log, dt_bias, norm], sequence_length)
+
+    def name(self) -> str:
+        return "SequenceDeltaNetLayer"
+
+    def output_type(self) -> DataType:
+        return DataType.BF16
+
+    def weights(self):
+        return self.weights_
+
+    def fwd_impl(self, inputs, hooks) -> FwdResult:
+        p, t = self.parameters_, self.sequence_length_
+        width = p.value_heads * p.value_head_dim
+        kq = p.key_heads * p.key_head_dim
+        channels = 2 * kq + width
+        if len(inputs) != 4:
+            raise _invalid("DeltaNet expects four inputs on its Executor")
+        _validate_bf16_inputs(inputs, [t * channels, t * width, t * p.value_heads, t * p.value_heads],
+                              "SequenceDeltaNetLayer")
+        L, rnd = _capi.lib(), int(p.round_to_bfloat16)
+        device = inputs[0].device
+        if not p.round_to_bfloat16:
+            raise _unimplemented("sequence delta-net without bf16 rounding is not built")
+        post = torch.empty((t, channels), dtype=torch.bfloat16, device=device)
+        conv_state = torch.zeros((1, channels, p.conv_kernel_dim), dtype=torch.float32, device=device)
+        check(L.pluto_gdn_conv_silu(_stream(), _ptr(inputs[0]), _ptr(self.weights_[0]), 1, 1, t,
+                                    channels, p.conv_kernel_dim, rnd, _ptr(conv_state), _ptr(post), 1))
+        g = torch.empty((t, p.value_heads), dtype=torch.float32, device=device)
+        beta = torch.empty_like(g)
+        check(L.pluto_gdn_gates(_stream(), _ptr(inputs[2]), _ptr(inputs[3]), _ptr(self.weights_[1]),
+                                _ptr(self.weights_[2]), 1, t, p.value_heads, rnd, _ptr(g), _ptr(beta)))
+        state = torch.zeros((1, p.value_heads, p.key_head_dim, p.value_head_dim), dtype=torch.float32,
+                            device=device)
+        core = torch.empty((t, width), dtype=torch.bfloat16, device=device)
+        flat = post.view(-1)
+        need = L.pluto_gdn_prefill_workspace_bytes(1, t, p.key_heads, p.value_heads, p.key_head_dim,
+                                                   p.value_head_dim, 1)
+        ws_ptr, ws_bytes = None, 0
+        if need and channels % 8 == 0 and kq % 8 == 0:
+            ws = _workspace(device, need + 256)
+            ws_ptr = (ws.data_ptr() + 255) // 256 * 256
+            ws_bytes = ws.numel() - (ws_ptr - ws.data_ptr())
+        check(L.pluto_gdn_prefill(_stream(), _ptr(flat), _ptr(flat[kq:]), _ptr(flat[2 * kq:]), 1,
+                                  _ptr(g), _ptr(beta), _ptr(state), _ptr(core), 1, 1, t, p.key_heads,
+                                  p.value_heads, p.key_head_dim, p.value_head_dim, channels, channels,
+                                  1, 1.0, rnd, ws_ptr, ws_bytes))
+        output = torch.empty((t, width), dtype=torch.bfloat16, device=device)
+        check(L.pluto_gdn_out_norm_gate(_stream(), _ptr(core), 1, _ptr(inputs[1]), 1,
+                                        _ptr(self.weights_[3]), t * p.value_heads, p.value_head_dim,
+                                        p.rms_norm_epsilon, rnd, 0, _ptr(output), 1))
+        saved = BackwardState(intermediates=[inputs[0], inputs[1], inputs[2], inputs[3], post, core, state])
+        return FwdResult([output], saved)
+
+    def bwd_impl(self, output_gradients, state, hooks):
+        raise _unimplemented("SequenceDeltaNetLayer backward is not built in this engine yet")

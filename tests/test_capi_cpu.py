@@ -89,16 +89,16 @@ def test_cached_attention_argument_validation(engine):
 def test_delta_net_argument_validation(engine):
     L = engine.lib()
     args = [None, 16, 16, 16, 0, 16, 16, 16, 16, 0, 1, 4]
-    assert _code(engine, L.pluto_gdn_prefill, *args, 2, 3, 8, 8, 1, 1.0, 1, None, 0)[0] == "InvalidArgument"  # 3 % 2
-    assert _code(engine, L.pluto_gdn_prefill, *args, 2, 4, 129, 8, 1, 1.0, 1, None, 0)[0] == "InvalidArgument"
-    assert _code(engine, L.pluto_gdn_prefill, *args, 2, 4, 8, 257, 1, 1.0, 1, None, 0)[0] == "InvalidArgument"
+    assert _code(engine, L.pluto_gdn_prefill, *args, 2, 3, 8, 8, 0, 0, 1, 1.0, 1, None, 0)[0] == "InvalidArgument"  # 3 % 2
+    assert _code(engine, L.pluto_gdn_prefill, *args, 2, 4, 129, 8, 0, 0, 1, 1.0, 1, None, 0)[0] == "InvalidArgument"
+    assert _code(engine, L.pluto_gdn_prefill, *args, 2, 4, 8, 257, 0, 0, 1, 1.0, 1, None, 0)[0] == "InvalidArgument"
     null_state = [None, 16, 16, 16, 0, 16, 16, None, 16, 0, 1, 4]
-    code, message = _code(engine, L.pluto_gdn_prefill, *null_state, 2, 4, 8, 8, 1, 1.0, 1, None, 0)
+    code, message = _code(engine, L.pluto_gdn_prefill, *null_state, 2, 4, 8, 8, 0, 0, 1, 1.0, 1, None, 0)
     assert code == "InvalidArgument" and "non-null" in message
     # a workspace for a shape without a chunked path, and a workspace that is too small
-    assert _code(engine, L.pluto_gdn_prefill, *args, 2, 4, 8, 8, 1, 1.0, 1, 256, 1 << 30)[0] == "InvalidArgument"
+    assert _code(engine, L.pluto_gdn_prefill, *args, 2, 4, 8, 8, 0, 0, 1, 1.0, 1, 256, 1 << 30)[0] == "InvalidArgument"
     big = [None, 16, 16, 16, 1, 16, 16, 16, 16, 1, 1, 128]
-    assert _code(engine, L.pluto_gdn_prefill, *big, 2, 4, 128, 128, 1, 1.0, 1, 256, 1024)[0] == "InvalidArgument"
+    assert _code(engine, L.pluto_gdn_prefill, *big, 2, 4, 128, 128, 0, 0, 1, 1.0, 1, 256, 1024)[0] == "InvalidArgument"
     assert L.pluto_gdn_prefill_workspace_bytes(2, 16384, 16, 16, 128, 128, 1) == 2 * 16 * 256 * 96512
     assert L.pluto_gdn_prefill_workspace_bytes(2, 16384, 16, 16, 64, 128, 1) == 0
     assert _code(engine, L.pluto_gdn_conv_silu, None, 16, 16, 0, 1, 1, 8, 33, 1, 16, 16, 0)[0] == "InvalidArgument"
