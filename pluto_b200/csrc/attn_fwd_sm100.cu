@@ -698,7 +698,18 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
   const size_t tile = static_cast<size_t>(a.head_dim / 64) * kSlabBytes;
   cudaError_t e;
   if (a.head_dim != 128 && a.head_dim != 64) return cudaErrorInvalidValue;
-  if (q_tiles >= 2) {
+  // Two query tiles per CTA (ping-pong) run each tile faster but make coarser work units: the
+  // longest unit of a causal sequence is then ~1/16 of one head's work.  With few heads per GPU
+  // (head-sharded across 8 GPUs) that unit alone would exceed an SM's fair share, so the
+  // single-tile kernel takes over when there are fewer than two units per SM.
+  int sms = 148;
+  {
+    int device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess)
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  }
+  const long long pair_units = static_cast<long long>((q_tiles + 1) / 2) * a.heads * a.batch;
+  if (q_tiles >= 2 && pair_units >= 2LL * sms) {
     // two query tiles per CTA in ping-pong
     const dim3 grid((q_tiles + 1) / 2, a.heads, a.batch);
     const size_t smem = 1024 + tile * (2 + 2 * kStages) + sizeof(PairBarriers);

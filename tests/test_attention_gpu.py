@@ -76,6 +76,14 @@ def test_subtile_head_widths(bf16):
         check(65, 3, 96, 2, True, 4.0)
 
 
+def test_many_heads_ragged_length_takes_the_two_tile_kernel():
+    """Enough (sequence, head) units for the two-tile ping-pong forward kernel at a length that
+    is not a multiple of its tiles (300 = 2 tiles + 44 rows: the last CTA has a lone tile), for
+    both head widths; smaller shapes elsewhere in this file exercise the single-tile kernel."""
+    check(300, 16, 1024, 10, True)     # head width 64
+    check(300, 10, 1280, 16, True)     # head width 128
+
+
 def test_golden_vectors_through_the_c_abi():
     """The committed outputs of the reference's CPU layer (tests/golden) against the CUDA path."""
     data = np.load(GOLDEN)
