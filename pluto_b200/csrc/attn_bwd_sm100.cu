@@ -28,7 +28,7 @@ namespace {
 
 constexpr int kRowTile = 128;   // rows owned by a CTA (TMEM lanes)
 constexpr int kColTile = 64;    // opposite-side rows consumed per step
-constexpr int kBwdStages = 2;
+constexpr int kBwdStages = 4;
 constexpr int kBwdThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -60,10 +60,18 @@ attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d
     }
     const size_t row = static_cast<size_t>(b) * seq + s;
     float part = 0.0f;
-    for (int d = lane; d < head_dim; d += 32) {
-      const float g = d_out[row * E + h * head_dim + d];
-      part = fmaf(g, __bfloat162float(out[row * E + h * head_dim + d]), part);
-      d_out_bf16[row * E + h * head_dim + d] = __float2bfloat16_rn(g);
+    const size_t base = row * E + static_cast<size_t>(h) * head_dim;
+    if (head_dim == 128) {          // four channels per lane: 16-byte gradient loads
+      const float4 g = *reinterpret_cast<const float4*>(d_out + base + lane * 4);
+      const uint2 o = *reinterpret_cast<const uint2*>(out + base + lane * 4);
+      part = g.x * bf16_lo(o.x) + g.y * bf16_hi(o.x) + g.z * bf16_lo(o.y) + g.w * bf16_hi(o.y);
+      *reinterpret_cast<uint2*>(d_out_bf16 + base + lane * 4) =
+          make_uint2(pack_bf16(g.x, g.y), pack_bf16(g.z, g.w));
+    } else {                        // head_dim 64: two channels per lane
+      const float2 g = *reinterpret_cast<const float2*>(d_out + base + lane * 2);
+      const uint32_t o = *reinterpret_cast<const uint32_t*>(out + base + lane * 2);
+      part = g.x * bf16_lo(o) + g.y * bf16_hi(o);
+      *reinterpret_cast<uint32_t*>(d_out_bf16 + base + lane * 2) = pack_bf16(g.x, g.y);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);

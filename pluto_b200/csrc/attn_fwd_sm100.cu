@@ -78,8 +78,10 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   Barriers* bar = reinterpret_cast<Barriers*>(v_smem + kStages * kTileBytes);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int q_tile = gridDim.x - 1 - blockIdx.x;  // heaviest (latest) tiles first
-  const int head = blockIdx.y, batch = blockIdx.z;
+  // (sequence, head) varies fastest, the tile index slowest: the longest tiles of every head start
+  // first and the shortest fill the tail.
+  const int q_tile = gridDim.y - 1 - blockIdx.y;
+  const int head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
   const int n_tiles = q_tile + 1;                 // causal: key tiles 0..q_tile
 
   if (threadIdx.x == 0) {
@@ -363,8 +365,11 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
   PairBarriers* bar = reinterpret_cast<PairBarriers*>(v_smem + kStages * kTileBytes);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int pair = gridDim.x - 1 - blockIdx.x;         // heaviest pairs first
-  const int head = blockIdx.y, batch = blockIdx.z;
+  // CTAs are handed to SMs in blockIdx.x-major order: (sequence, head) varies fastest and the pair
+  // index slowest, so every head's longest pairs start first and the shortest ones fill the tail
+  // (longest-processing-time-first over the whole grid, not per head).
+  const int pair = gridDim.y - 1 - blockIdx.y;
+  const int head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
   const int q_tiles = (p.seq + kBM - 1) / kBM;
   const int tile_of[2] = {2 * pair, 2 * pair + 1};
   const int n_of[2] = {tile_of[0] + 1, tile_of[1] < q_tiles ? tile_of[1] + 1 : 0};
@@ -380,7 +385,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bar->s_full[s], 1);
-      mbar_init(&bar->p_full[s], 128);
+      mbar_init(&bar->p_full[s], 4);  // one arrival per softmax warp
       mbar_init(&bar->pv_done[s], 1);
     }
     mbar_fence_init();
@@ -563,7 +568,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
       l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&bar->p_full[x]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->p_full[x]);
     }
     if (ok && n_tiles > 0) ok = mbar_wait(&bar->pv_done[x], (n_tiles - 1) & 1, p.status, 22);
     if (ok && n_tiles > 0) {
@@ -711,14 +717,14 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
   const long long pair_units = static_cast<long long>((q_tiles + 1) / 2) * a.heads * a.batch;
   if (q_tiles >= 2 && pair_units >= 2LL * sms) {
     // two query tiles per CTA in ping-pong
-    const dim3 grid((q_tiles + 1) / 2, a.heads, a.batch);
+    const dim3 grid(a.heads * a.batch, (q_tiles + 1) / 2);
     const size_t smem = 1024 + tile * (2 + 2 * kStages) + sizeof(PairBarriers);
     auto kernel = a.head_dim == 128 ? attn_fwd_sm100_pair<128> : attn_fwd_sm100_pair<64>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     kernel<<<grid, kThreadsPair, smem, stream>>>(map_q, map_k, map_v, p);
   } else {
-    const dim3 grid(q_tiles, a.heads, a.batch);
+    const dim3 grid(a.heads * a.batch, q_tiles);
     const size_t smem = 1024 + tile * (1 + 2 * kStages) + sizeof(Barriers);
     auto kernel = a.head_dim == 128 ? attn_fwd_sm100<128> : attn_fwd_sm100<64>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
