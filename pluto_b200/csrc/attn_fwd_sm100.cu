@@ -364,7 +364,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
   uint8_t* v_smem = k_smem + kStages * kTileBytes;
   PairBarriers* bar = reinterpret_cast<PairBarriers*>(v_smem + kStages * kTileBytes);
 
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   // CTAs are handed to SMs in blockIdx.x-major order: (sequence, head) varies fastest and the pair
   // index slowest, so every head's longest pairs start first and the shortest ones fill the tail
   // (longest-processing-time-first over the whole grid, not per head).
@@ -443,49 +443,65 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (lane == 0) {
-      bool ok = mbar_wait(&bar->q_full, 0, p.status, 10);
+    {
+      // The whole warp walks the schedule (uniform control flow); one elected lane issues.
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full, 0, p.status, 10));
       tc_fence_after();
+      const uint32_t q_base = smem_u32(q_smem), k_base = smem_u32(k_smem), v_base = smem_u32(v_smem);
       auto issue_qk = [&](int x, int j) -> bool {
         const int st = j % kStages;
-        if (!mbar_wait(&bar->k_full[st], (j / kStages) & 1, p.status, 13)) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[st], (j / kStages) & 1, p.status, 13)))
+          return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(q_smem + x * kTileBytes);
-        const uint32_t k_addr = smem_u32(k_smem + st * kTileBytes);
+        if (elect_one()) {
+          const uint64_t q_desc = umma_desc_sw128(q_base + x * kTileBytes, 16, 1024);
+          const uint64_t k_desc = umma_desc_sw128(k_base + st * kTileBytes, 16, 1024);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * kSlabBytes + (ks % 4) * 32;
-          umma_ss(tmem + x * 128, umma_desc_sw128(q_addr + off, 16, 1024),
-                  umma_desc_sw128(k_addr + off, 16, 1024), kIdescQK, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            // advancing the start-address field (bytes >> 4) of a descriptor is a 32-bit add
+            const uint32_t off = ((ks / 4) * kSlabBytes + (ks % 4) * 32) >> 4;
+            umma_ss(tmem + x * 128, q_desc + off, k_desc + off, kIdescQK, ks > 0);
+          }
+          tc_commit(&bar->s_full[x]);
         }
-        tc_commit(&bar->s_full[x]);
+        __syncwarp();
         return true;
       };
       auto issue_pv = [&](int x, int j) -> bool {
         const int st = j % kStages;
-        if (!mbar_wait(&bar->p_full[x], j & 1, p.status, 11)) return false;
-        if (!mbar_wait(&bar->v_full[st], (j / kStages) & 1, p.status, 12)) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[x], j & 1, p.status, 11))) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full[st], (j / kStages) & 1, p.status, 12)))
+          return false;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_smem + st * kTileBytes);
+        if (elect_one()) {
+          const uint64_t v_desc = umma_desc_sw128(v_base + st * kTileBytes, kSlabBytes, 1024);
 #pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks)
-          umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8,
-                  umma_desc_sw128(v_addr + ks * 2048, kSlabBytes, 1024), kIdescPV, j > 0 || ks > 0);
-        tc_commit(&bar->pv_done[x]);
+          for (int ks = 0; ks < kBN / 16; ++ks)
+            umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, v_desc + ks * (2048 >> 4),
+                    kIdescPV, j > 0 || ks > 0);
+          tc_commit(&bar->pv_done[x]);
+        }
+        __syncwarp();
         return true;
       };
-      for (int x = 0; x < 2 && ok; ++x)
-        if (n_of[x] > 0) ok = issue_qk(x, 0);
-      if (ok) tc_commit(&bar->k_empty[0]);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+        if (ok && n_of[x] > 0) ok = issue_qk(x, 0);
+      if (ok && elect_one()) tc_commit(&bar->k_empty[0]);
+      __syncwarp();
       for (int j = 0; j < n_max && ok; ++j) {
-        for (int x = 0; x < 2 && ok; ++x) {
-          if (j >= n_of[x]) continue;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (!ok || j >= n_of[x]) continue;
           ok = issue_pv(x, j);
           if (ok && j + 1 < n_of[x]) ok = issue_qk(x, j + 1);
         }
         if (!ok) break;
-        tc_commit(&bar->v_empty[j % kStages]);
-        if (j + 1 < n_max) tc_commit(&bar->k_empty[(j + 1) % kStages]);
+        if (elect_one()) {
+          tc_commit(&bar->v_empty[j % kStages]);
+          if (j + 1 < n_max) tc_commit(&bar->k_empty[(j + 1) % kStages]);
+        }
+        __syncwarp();
       }
     }
   } else if (warp >= 4) {

@@ -141,6 +141,22 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
+// One lane of a fully converged warp (always the same one).  Code that issues tcgen05.mma runs
+// with warp-uniform control flow and elects the issuer only around the instruction itself, so the
+// descriptors stay in the uniform datapath instead of being moved there per instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+// Warp index as a value the compiler knows to be uniform across the warp.
+__device__ __forceinline__ int uniform_warp_index() {
+  return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x / 32), 0);
+}
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
