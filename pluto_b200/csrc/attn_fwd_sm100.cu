@@ -336,12 +336,13 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // thread can hold its whole 128-entry score row and read TMEM once per tile.
 // ---------------------------------------------------------------------------------------------
 constexpr int kThreadsPair = 384;
+constexpr int kPolyOf4 = 1;  // pairs per four whose exp2 runs on the FMA pipe
 
 struct PairBarriers {
   uint64_t q_full;
   uint64_t k_full[kStages], k_empty[kStages];
   uint64_t v_full[kStages], v_empty[kStages];
-  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint64_t s_full[2], p_full[2], p_half[2], pv_done[2];
   uint32_t tmem_base;
 };
 
@@ -386,6 +387,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bar->s_full[s], 1);
       mbar_init(&bar->p_full[s], 4);  // one arrival per softmax warp
+      mbar_init(&bar->p_half[s], 4);
       mbar_init(&bar->pv_done[s], 1);
     }
     mbar_fence_init();
@@ -469,16 +471,27 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
       };
       auto issue_pv = [&](int x, int j) -> bool {
         const int st = j % kStages;
-        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[x], j & 1, p.status, 11))) return false;
+        // P arrives in two halves of 64 keys: the first four PV instructions run while the softmax
+        // warps still work on the second half of the row.
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_half[x], j & 1, p.status, 14))) return false;
         if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full[st], (j / kStages) & 1, p.status, 12)))
           return false;
         tc_fence_after();
+        const uint64_t v_desc = umma_desc_sw128(v_base + st * kTileBytes, kSlabBytes, 1024);
         if (elect_one()) {
-          const uint64_t v_desc = umma_desc_sw128(v_base + st * kTileBytes, kSlabBytes, 1024);
 #pragma unroll
-          for (int ks = 0; ks < kBN / 16; ++ks)
+          for (int ks = 0; ks < kBN / 32; ++ks)
             umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, v_desc + ks * (2048 >> 4),
                     kIdescPV, j > 0 || ks > 0);
+        }
+        __syncwarp();
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[x], j & 1, p.status, 11))) return false;
+        tc_fence_after();
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = kBN / 32; ks < kBN / 16; ++ks)
+            umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, v_desc + ks * (2048 >> 4),
+                    kIdescPV, true);
           tc_commit(&bar->pv_done[x]);
         }
         __syncwarp();
@@ -528,25 +541,23 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, s[c]);
       tmem_wait_ld();
-      float mx[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
       if (diagonal) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 32; ++i)
             if (c * 32 + i > row) s[c][i] = 0xff800000u;  // -inf above the diagonal
-            mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(s[c][i]));
-          }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(s[c][i]));
       }
-      m_true = fmaxf(m_true, fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                                   fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))));
+      float mx[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+      m_true = fmaxf(m_true, fmaxf(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5])));
+      m_true = max3(m_true, mx[6], mx[7]);
       const bool grow = (m_true - m_used) * p.scale_log2 > kRescaleThreshold;
       if (__any_sync(0xffffffffu, grow)) {
         const float factor = grow ? fast_exp2((m_used - m_true) * p.scale_log2) : 1.0f;
@@ -567,21 +578,47 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
           }
         }
       }
-      const float neg_m = -m_used * p.scale_log2;
-      float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      // exp2 of the row: the special-function unit (16 results per clock and SM) would need as
+      // long for the two tiles as the tensor pipe needs for their MMAs, so kPolyOf4 of every four
+      // pairs are evaluated on the FMA pipe instead.
+      const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
+      const uint64_t neg_m2 = f2_pack(-m_used * p.scale_log2, -m_used * p.scale_log2);
+      uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), p.scale_log2, neg_m));
-          sum[(i >> 1) & 3] += p0 + p1;
+          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])),
+                                     scale2, neg_m2);
+          uint64_t p2;
+          float p0, p1;
+          if (((i >> 1) & 3) < kPolyOf4) {
+            p2 = f2_exp2_poly(x2);
+            f2_unpack(p2, p0, p1);
+          } else {
+            f2_unpack(x2, p0, p1);
+            p0 = fast_exp2(p0);
+            p1 = fast_exp2(p1);
+            p2 = f2_pack(p0, p1);
+          }
+          sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], p2);
           packed[i / 2] = pack_bf16(p0, p1);
         }
         tmem_st16(s_addr + c * 16, packed);
+        if (c == 1) {
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar->p_half[x]);
+        }
       }
-      l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      {
+        float a0, a1, b0, b1;
+        f2_unpack(sum2[0], a0, a1);
+        f2_unpack(sum2[1], b0, b1);
+        l += (a0 + a1) + (b0 + b1);
+      }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();

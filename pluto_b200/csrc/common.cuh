@@ -269,6 +269,55 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two-lane fp32 arithmetic (one instruction per pair of values).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// 2^x for a pair of values on the FMA pipe instead of the special-function unit: x = n + f with
+// n = round(x) (taken from the mantissa of x + 1.5*2^23) and f in [-0.5, 0.5]; 2^f by a cubic
+// fitted to 7.5e-5 relative error (a bf16 result keeps 8 bits, 3.9e-3); n is added into the
+// exponent field.  Inputs below -120 (including -inf) are clamped, so they return ~1e-36, not 0.
+__device__ __forceinline__ uint64_t f2_exp2_poly(uint64_t x2) {
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x2 = f2_pack(fmaxf(x0, -120.0f), fmaxf(x1, -120.0f));
+  const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);
+  const uint64_t t2 = f2_add(x2, magic);
+  const uint64_t f2 = f2_sub(x2, f2_sub(t2, magic));
+  uint64_t p2 = f2_fma(f2_pack(0.0551716685f, 0.0551716685f), f2, f2_pack(0.2426111251f, 0.2426111251f));
+  p2 = f2_fma(p2, f2, f2_pack(0.6932609677f, 0.6932609677f));
+  p2 = f2_fma(p2, f2, f2_pack(0.9999280572f, 0.9999280572f));
+  float p0, p1, t0, t1;
+  f2_unpack(p2, p0, p1);
+  f2_unpack(t2, t0, t1);
+  return f2_pack(__int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23)),
+                 __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23)));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
