@@ -77,7 +77,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   uint8_t* v_smem = k_smem + kStages * kTileBytes;
   Barriers* bar = reinterpret_cast<Barriers*>(v_smem + kStages * kTileBytes);
 
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   // (sequence, head) varies fastest, the tile index slowest: the longest tiles of every head start
   // first and the shortest fill the tail.
   const int q_tile = gridDim.y - 1 - blockIdx.y;
@@ -147,41 +147,48 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      bool ok = mbar_wait(&bar->q_full, 0, p.status, 10);
+    {
+      // The whole warp walks the schedule (uniform control flow); one elected lane issues.
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full, 0, p.status, 10));
       tc_fence_after();
+      const uint32_t q_base = smem_u32(q_smem), k_base = smem_u32(k_smem), v_base = smem_u32(v_smem);
       auto issue_pv = [&](int i) -> bool {
         const int sb = i & 1, st = i % kStages;
-        if (!mbar_wait(&bar->p_full[sb], (i >> 1) & 1, p.status, 11)) return false;
-        if (!mbar_wait(&bar->v_full[st], (i / kStages) & 1, p.status, 12)) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[sb], (i >> 1) & 1, p.status, 11)))
+          return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full[st], (i / kStages) & 1, p.status, 12)))
+          return false;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_smem + st * kTileBytes);
-#pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
+        if (elect_one()) {
           // B = V tile, MN-major: 16 key rows per step (2048 bytes), 64-column slabs kBN*128 apart
-          const uint64_t b_desc = umma_desc_sw128(v_addr + ks * 2048, kSlabBytes, 1024);
-          umma_ts(tmem + kColO, tmem + kColS + sb * 128 + ks * 8, b_desc, kIdescPV,
-                  i > 0 || ks > 0);
+          const uint64_t v_desc = umma_desc_sw128(v_base + st * kTileBytes, kSlabBytes, 1024);
+#pragma unroll
+          for (int ks = 0; ks < kBN / 16; ++ks)
+            umma_ts(tmem + kColO, tmem + kColS + sb * 128 + ks * 8, v_desc + ks * (2048 >> 4),
+                    kIdescPV, i > 0 || ks > 0);
+          tc_commit(&bar->pv_done[sb]);
+          tc_commit(&bar->v_empty[st]);
         }
-        tc_commit(&bar->pv_done[sb]);
-        tc_commit(&bar->v_empty[st]);
+        __syncwarp();
         return true;
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int sb = j & 1, st = j % kStages;
-        ok = mbar_wait(&bar->k_full[st], (j / kStages) & 1, p.status, 13);
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->k_full[st], (j / kStages) & 1, p.status, 13));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(q_smem);
-        const uint32_t k_addr = smem_u32(k_smem + st * kTileBytes);
+        if (elect_one()) {
+          const uint64_t q_desc = umma_desc_sw128(q_base, 16, 1024);
+          const uint64_t k_desc = umma_desc_sw128(k_base + st * kTileBytes, 16, 1024);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * kSlabBytes + (ks % 4) * 32;
-          umma_ss(tmem + kColS + sb * 128, umma_desc_sw128(q_addr + off, 16, 1024),
-                  umma_desc_sw128(k_addr + off, 16, 1024), kIdescQK, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = ((ks / 4) * kSlabBytes + (ks % 4) * 32) >> 4;
+            umma_ss(tmem + kColS + sb * 128, q_desc + off, k_desc + off, kIdescQK, ks > 0);
+          }
+          tc_commit(&bar->s_full[sb]);
+          tc_commit(&bar->k_empty[st]);
         }
-        tc_commit(&bar->s_full[sb]);
-        tc_commit(&bar->k_empty[st]);
+        __syncwarp();
         if (j > 0) ok = issue_pv(j - 1);
       }
       if (ok) issue_pv(n_tiles - 1);
@@ -336,13 +343,14 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // thread can hold its whole 128-entry score row and read TMEM once per tile.
 // ---------------------------------------------------------------------------------------------
 constexpr int kThreadsPair = 384;
+constexpr int kEarly = 6;     // PV instructions (of 8) issued on the early hand-off of P
 constexpr int kPolyOf4 = 1;  // pairs per four whose exp2 runs on the FMA pipe
 
 struct PairBarriers {
   uint64_t q_full;
   uint64_t k_full[kStages], k_empty[kStages];
   uint64_t v_full[kStages], v_empty[kStages];
-  uint64_t s_full[2], p_full[2], p_half[2], pv_done[2];
+  uint64_t s_full[2], p_full[2], p_early[2], pv_done[2];
   uint32_t tmem_base;
 };
 
@@ -387,7 +395,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bar->s_full[s], 1);
       mbar_init(&bar->p_full[s], 4);  // one arrival per softmax warp
-      mbar_init(&bar->p_half[s], 4);
+      mbar_init(&bar->p_early[s], 4);
       mbar_init(&bar->pv_done[s], 1);
     }
     mbar_fence_init();
@@ -471,16 +479,16 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
       };
       auto issue_pv = [&](int x, int j) -> bool {
         const int st = j % kStages;
-        // P arrives in two halves of 64 keys: the first four PV instructions run while the softmax
-        // warps still work on the second half of the row.
-        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_half[x], j & 1, p.status, 14))) return false;
+        // P arrives in two parts (96 + 32 keys): the first kEarly PV instructions run while the
+        // softmax warps still work on the rest of the row.
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_early[x], j & 1, p.status, 14))) return false;
         if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full[st], (j / kStages) & 1, p.status, 12)))
           return false;
         tc_fence_after();
         const uint64_t v_desc = umma_desc_sw128(v_base + st * kTileBytes, kSlabBytes, 1024);
         if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < kBN / 32; ++ks)
+          for (int ks = 0; ks < kEarly; ++ks)
             umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, v_desc + ks * (2048 >> 4),
                     kIdescPV, j > 0 || ks > 0);
         }
@@ -489,7 +497,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
-          for (int ks = kBN / 32; ks < kBN / 16; ++ks)
+          for (int ks = kEarly; ks < kBN / 16; ++ks)
             umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, v_desc + ks * (2048 >> 4),
                     kIdescPV, true);
           tc_commit(&bar->pv_done[x]);
@@ -606,11 +614,11 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
           packed[i / 2] = pack_bf16(p0, p1);
         }
         tmem_st16(s_addr + c * 16, packed);
-        if (c == 1) {
+        if (c == kEarly / 2 - 1) {
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&bar->p_half[x]);
+          if (lane == 0) mbar_arrive(&bar->p_early[x]);
         }
       }
       {
