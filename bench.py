@@ -263,11 +263,11 @@ def run_engine(args):
         "clocks": clocks,
     }
     if rank == 0:
-        # roofline of the one kernel in the step (attn_fwd_sm100<128>): bf16 tensor-core bound.
+        # roofline of the one kernel in the step (attn_fwd_sm100_pair<128>): bf16 tensor-core bound.
         per_rank_flop = FLOP_PER_STEP / world
         achieved = per_rank_flop / (ms * 1e-3) / 1e12
         line["roofline"] = {
-            "bound": "tensor", "kernel": "attn_fwd_sm100<128>", "achieved": achieved,
+            "bound": "tensor", "kernel": "attn_fwd_sm100_pair<128>", "achieved": achieved,
             "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
             "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"]
                                   if peaks.get("bf16_tflops_sustained") else None),
@@ -290,9 +290,9 @@ def run_engine(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_sm100<128> launch on this
-# workload, from the ncu capture summarised in profiles/attn_fwd_sm100_d128_gqa_prefill_8192.md.
-TRAFFIC_BYTES_PER_LAUNCH = 166.6e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_sm100_pair<128> launch on this
+# workload, from the ncu capture summarised in profiles/attn_fwd_sm100_pair_d128_gqa_prefill_8192.md.
+TRAFFIC_BYTES_PER_LAUNCH = 164.5e6
 
 
 def other_workloads(peaks, only=None, decode_batch=64, steps_scale=1.0):
