@@ -114,8 +114,9 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
   uint8_t* v_smem = k_smem + kBwdStages * kColTileBytes;
   DqBarriers* bar = reinterpret_cast<DqBarriers*>(v_smem + kBwdStages * kColTileBytes);
 
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int q_tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  // (sequence, head) varies fastest and the tile index slowest: longest tiles start first
+  const int q_tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
   const int E = p.heads * D;
   const int col_tiles = (p.seq + kColTile - 1) / kColTile;
   const int n_steps = min(2 * q_tile + 2, col_tiles);   // key tiles that hold a visible key
@@ -128,7 +129,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
       mbar_init(&bar->kv_empty[s], 1);
     }
     mbar_init(&bar->s_full, 1);
-    mbar_init(&bar->ds_full, 128);
+    mbar_init(&bar->ds_full, 4);   // one arrival per warp
     mbar_init(&bar->dq_done, 1);
     mbar_fence_init();
   }
@@ -174,43 +175,52 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      bool ok = mbar_wait(&bar->qdo_full, 0, p.status, 54);
-      const uint32_t q_addr = smem_u32(q_smem), do_addr = smem_u32(do_smem);
+    {
+      // The whole warp walks the schedule (uniform control flow); one elected lane issues.
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->qdo_full, 0, p.status, 54));
+      const uint64_t q_desc = umma_desc_sw128(smem_u32(q_smem), 16, 1024);
+      const uint64_t do_desc = umma_desc_sw128(smem_u32(do_smem), 16, 1024);
       for (int j = 0; j < n_steps && ok; ++j) {
         const int st = j % kBwdStages;
-        ok = mbar_wait(&bar->k_full[st], (j / kBwdStages) & 1, p.status, 55) &&
-             mbar_wait(&bar->v_full[st], (j / kBwdStages) & 1, p.status, 56);
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->k_full[st], (j / kBwdStages) & 1, p.status, 55) &&
+                                         mbar_wait(&bar->v_full[st], (j / kBwdStages) & 1, p.status, 56));
         if (!ok) break;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(k_smem + st * kColTileBytes);
         const uint32_t v_addr = smem_u32(v_smem + st * kColTileBytes);
+        if (elect_one()) {
+          const uint64_t k_desc = umma_desc_sw128(k_addr, 16, 1024);
+          const uint64_t v_desc = umma_desc_sw128(v_addr, 16, 1024);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t a_off = (ks / 4) * kRowTile * 128 + (ks % 4) * 32;
-          const uint32_t b_off = (ks / 4) * kColTile * 128 + (ks % 4) * 32;
-          umma_ss(tmem + kColS, umma_desc_sw128(q_addr + a_off, 16, 1024),
-                  umma_desc_sw128(k_addr + b_off, 16, 1024), kIdescS, ks > 0);
-        }
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
+            const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
+            umma_ss(tmem + kColS, q_desc + a_off, k_desc + b_off, kIdescS, ks > 0);
+          }
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t a_off = (ks / 4) * kRowTile * 128 + (ks % 4) * 32;
-          const uint32_t b_off = (ks / 4) * kColTile * 128 + (ks % 4) * 32;
-          umma_ss(tmem + kColDP, umma_desc_sw128(do_addr + a_off, 16, 1024),
-                  umma_desc_sw128(v_addr + b_off, 16, 1024), kIdescS, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
+            const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
+            umma_ss(tmem + kColDP, do_desc + a_off, v_desc + b_off, kIdescS, ks > 0);
+          }
+          tc_commit(&bar->s_full);
         }
-        tc_commit(&bar->s_full);
-        ok = mbar_wait(&bar->ds_full, j & 1, p.status, 57);
+        __syncwarp();
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->ds_full, j & 1, p.status, 57));
         if (!ok) break;
         tc_fence_after();
+        if (elect_one()) {
+          const uint64_t k_mn = umma_desc_sw128(k_addr, kColTile * 128, 1024);
 #pragma unroll
-        for (int ks = 0; ks < kColTile / 16; ++ks)   // dQ += dS K: 16 keys per step, K MN-major
-          umma_ts(tmem + kColDQ, tmem + kColS + ks * 8,
-                  umma_desc_sw128(k_addr + ks * 2048, kColTile * 128, 1024), kIdescDQ,
-                  j > 0 || ks > 0);
-        tc_commit(&bar->kv_empty[st]);
+          for (int ks = 0; ks < kColTile / 16; ++ks)   // dQ += dS K: 16 keys per step, K MN-major
+            umma_ts(tmem + kColDQ, tmem + kColS + ks * 8, k_mn + ks * (2048 >> 4), kIdescDQ,
+                    j > 0 || ks > 0);
+          tc_commit(&bar->kv_empty[st]);
+        }
+        __syncwarp();
       }
-      if (ok) tc_commit(&bar->dq_done);
+      if (ok && elect_one()) tc_commit(&bar->dq_done);
+      __syncwarp();
     }
   } else if (warp >= 4) {
     const int quarter = warp & 3, row = quarter * 32 + lane;
@@ -247,7 +257,8 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&bar->ds_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->ds_full);
     }
     if (ok) ok = mbar_wait(&bar->dq_done, 0, p.status, 59);
     if (ok) {
@@ -306,8 +317,9 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
   uint8_t* stage_smem = v_smem + kRowTileBytes;   // per stage: Q_i | dO_i | stats
   DkvBarriers* bar = reinterpret_cast<DkvBarriers*>(stage_smem + kBwdStages * kStageBytes);
 
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int k_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  // key tile 0 is seen by every query tile: the lowest tile index is the longest, and it starts first
+  const int k_tile = blockIdx.y, head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
   const int E = p.heads * D;
   const int col_tiles = (p.seq + kColTile - 1) / kColTile;
   const int first = 2 * k_tile;                    // first query tile that can see these keys
@@ -320,7 +332,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
       mbar_init(&bar->q_empty[s], 1);
     }
     mbar_init(&bar->s_full, 1);
-    mbar_init(&bar->ds_full, 128);
+    mbar_init(&bar->ds_full, 4);   // one arrival per warp
     mbar_init(&bar->done, 1);
     mbar_fence_init();
   }
@@ -366,46 +378,54 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
         mbar_wait(&bar->q_full[i % kBwdStages], (i / kBwdStages) & 1, p.status, 62);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      bool ok = mbar_wait(&bar->kv_full, 0, p.status, 63);
-      const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
+    {
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->kv_full, 0, p.status, 63));
+      const uint64_t k_desc = umma_desc_sw128(smem_u32(k_smem), 16, 1024);
+      const uint64_t v_desc = umma_desc_sw128(smem_u32(v_smem), 16, 1024);
       for (int i = 0; i < n_steps && ok; ++i) {
         const int st = i % kBwdStages;
-        ok = mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 64);
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 64));
         if (!ok) break;
         tc_fence_after();
         const uint32_t q_addr = smem_u32(stage_smem + st * kStageBytes);
         const uint32_t do_addr = q_addr + kColTileBytes;
+        if (elect_one()) {
+          const uint64_t q_desc = umma_desc_sw128(q_addr, 16, 1024);
+          const uint64_t do_desc = umma_desc_sw128(do_addr, 16, 1024);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {   // S^T = K Q^T
-          const uint32_t a_off = (ks / 4) * kRowTile * 128 + (ks % 4) * 32;
-          const uint32_t b_off = (ks / 4) * kColTile * 128 + (ks % 4) * 32;
-          umma_ss(tmem + kColS, umma_desc_sw128(k_addr + a_off, 16, 1024),
-                  umma_desc_sw128(q_addr + b_off, 16, 1024), kIdescS, ks > 0);
-        }
+          for (int ks = 0; ks < D / 16; ++ks) {   // S^T = K Q^T
+            const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
+            const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
+            umma_ss(tmem + kColS, k_desc + a_off, q_desc + b_off, kIdescS, ks > 0);
+          }
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {   // dP^T = V dO^T
-          const uint32_t a_off = (ks / 4) * kRowTile * 128 + (ks % 4) * 32;
-          const uint32_t b_off = (ks / 4) * kColTile * 128 + (ks % 4) * 32;
-          umma_ss(tmem + kColDP, umma_desc_sw128(v_addr + a_off, 16, 1024),
-                  umma_desc_sw128(do_addr + b_off, 16, 1024), kIdescS, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {   // dP^T = V dO^T
+            const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
+            const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
+            umma_ss(tmem + kColDP, v_desc + a_off, do_desc + b_off, kIdescS, ks > 0);
+          }
+          tc_commit(&bar->s_full);
         }
-        tc_commit(&bar->s_full);
-        ok = mbar_wait(&bar->ds_full, i & 1, p.status, 65);
+        __syncwarp();
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->ds_full, i & 1, p.status, 65));
         if (!ok) break;
         tc_fence_after();
+        if (elect_one()) {
+          const uint64_t do_mn = umma_desc_sw128(do_addr, kColTile * 128, 1024);
+          const uint64_t q_mn = umma_desc_sw128(q_addr, kColTile * 128, 1024);
 #pragma unroll
-        for (int ks = 0; ks < kColTile / 16; ++ks) {   // 16 queries per step, operands MN-major
-          umma_ts(tmem + kColDV, tmem + kColS + ks * 8,
-                  umma_desc_sw128(do_addr + ks * 2048, kColTile * 128, 1024), kIdescAcc,
-                  i > 0 || ks > 0);
-          umma_ts(tmem + kColDK, tmem + kColDP + ks * 8,
-                  umma_desc_sw128(q_addr + ks * 2048, kColTile * 128, 1024), kIdescAcc,
-                  i > 0 || ks > 0);
+          for (int ks = 0; ks < kColTile / 16; ++ks) {   // 16 queries per step, operands MN-major
+            umma_ts(tmem + kColDV, tmem + kColS + ks * 8, do_mn + ks * (2048 >> 4), kIdescAcc,
+                    i > 0 || ks > 0);
+            umma_ts(tmem + kColDK, tmem + kColDP + ks * 8, q_mn + ks * (2048 >> 4), kIdescAcc,
+                    i > 0 || ks > 0);
+          }
+          tc_commit(&bar->q_empty[st]);
         }
-        tc_commit(&bar->q_empty[st]);
+        __syncwarp();
       }
-      if (ok) tc_commit(&bar->done);
+      if (ok && elect_one()) tc_commit(&bar->done);
+      __syncwarp();
     }
   } else if (warp >= 4) {
     const int quarter = warp & 3, row = quarter * 32 + lane;
@@ -446,7 +466,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&bar->ds_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->ds_full);
     }
     if (ok && n_steps > 0) ok = mbar_wait(&bar->done, 0, p.status, 67);
     if (ok) {
@@ -497,7 +518,7 @@ cudaError_t launch_bwd_tc(cudaStream_t stream, const CUtensorMap& qkv128, const 
   e = cudaFuncSetAttribute(attn_bwd_dkv_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(dkv_smem));
   if (e != cudaSuccess) return e;
-  const dim3 grid((p.seq + kRowTile - 1) / kRowTile, p.heads, batch);
+  const dim3 grid(p.heads * batch, (p.seq + kRowTile - 1) / kRowTile);
   attn_bwd_dq_sm100<D><<<grid, kBwdThreads, dq_smem, stream>>>(qkv128, qkv64, do128, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
