@@ -214,6 +214,30 @@ def gqa_prefill(q, k, v, gate=None, rnd=True, threads=1, rows=None, q_token_stri
     return res
 
 
+def gqa_sequence_bwd(qg, k, v, q_norm, k_norm, dy, rotary, eps, theta, rnd=True, dqw=None, dkw=None):
+    """QwenAttentionLayer sequence forward + backward (qwen_attention.cc:124-239, 450-499) for one
+    sequence.  fp32 arrays: qg [T,Hq,2,D], k,v [T,Hkv,D], norms [D], dy [T,Hq,D].  dqw / dkw are
+    fp32 [D] arrays accumulated into (None = frozen norm).  Returns dqg, dk, dv and the forward
+    output y."""
+    qg = np.ascontiguousarray(qg, np.float32)
+    k = np.ascontiguousarray(k, np.float32)
+    v = np.ascontiguousarray(v, np.float32)
+    dy = np.ascontiguousarray(dy, np.float32)
+    t, hq, _, d = qg.shape
+    hkv = k.shape[1]
+    dqg = np.zeros_like(qg)
+    dk = np.zeros_like(k)
+    dv = np.zeros_like(v)
+    y = np.zeros((t, hq, d), np.float32)
+    rc = lib().oracle_gqa_sequence_bwd(
+        _p(qg), _p(k), _p(v), _p(np.ascontiguousarray(q_norm, np.float32)),
+        _p(np.ascontiguousarray(k_norm, np.float32)), _p(dy), t, hq, hkv, d, int(rotary),
+        C.c_float(eps), C.c_float(theta), int(rnd), _p(dqg), _p(dk), _p(dv), _p(dqw), _p(dkw), _p(y))
+    if rc != 0:
+        raise MemoryError("oracle_gqa_sequence_bwd scratch allocation failed")
+    return {"dqg": dqg, "dk": dk, "dv": dv, "y": y}
+
+
 # ---------------------------------------------------------------------------- gated delta-net
 def gdn_decay(a, dt_bias, a_log):
     return np.array([lib().oracle_gdn_decay(float(x), float(y), float(z))

@@ -413,6 +413,197 @@ void oracle_gqa_prefill(const void* q, const void* gate, const void* k, const vo
   parallel_units((row_end - row_begin) * q_heads, threads, prefill_unit, &a);
 }
 
+/* SequenceBackward of QwenAttentionLayer, qwen_attention.cc:124-239 (kernels) and :450-499 (host
+ * order), for one sequence.  All tensors fp32 (values of bf16 inputs are bf16-exact):
+ *   qg [T,Hq,2,D] (query at h*2D, gate at (2h+1)*D), k_in,v [T,Hkv,D], q_norm,k_norm [D]
+ *   (zero-centred), dy [T,Hq,D].
+ * Runs the forward first (PrepareKernel :30-63, ForwardKernel :68-119: prepared q/k, unrounded
+ * core, probabilities P = exp(s - max)/denominator) and then, in the reference's order:
+ *   GateBackwardKernel      dc = dy * R(sigmoid(gate)); d_gate = dy * R(core) * sig * (1 - sig)
+ *   QueryBackwardKernel     delta = dc.core; dS = P * (dc.v - delta); dq_rope = scale * sum dS k
+ *   KeyValueBackwardKernel  dk_rope = scale * sum_{h in group, t >= row} dS q; dv = sum P dc
+ *   NormBackwardKernel      RoPE^-1 with the rounded cos/sin, then RMSNorm backward; per-row
+ *                           weight-gradient parts normalized_grad * x * inv
+ *   ReduceNormKernel        dw += sum of parts in row order
+ * Outputs: dqg [T,Hq,2,D], dk [T,Hkv,D], dv [T,Hkv,D]; dqw/dkw [D] are ACCUMULATED into (NULL =
+ * frozen norm); out_y (optional) [T,Hq,D] receives the forward output.  Returns 0, or -1 when a
+ * scratch allocation fails. */
+static void norm_backward_row(const float* x, const float* w, const float* grad, int d, int rotary,
+                              int row, float epsilon, float log_theta, int round, float* dx,
+                              float* dw_part) {
+  const int half = rotary / 2;
+  float square = 0.0f;
+  for (int c = 0; c < d; ++c) square += x[c] * x[c];
+  const float inv = 1.0f / sqrtf(square / (float)d + epsilon);
+  float ng[256], dot = 0.0f;
+  for (int c = 0; c < d; ++c) {
+    float g = grad[c];
+    if (c < rotary) {
+      const int partner = c < half ? c + half : c - half;
+      const int f = c < half ? c : c - half;
+      const float angle = (float)row * expf((float)f * (-2.0f * log_theta / (float)rotary));
+      const float co = rnd(cosf(angle), round), si = rnd(sinf(angle), round);
+      const float gp = grad[partner];
+      g = g * co + (c < half ? gp * si : -gp * si);
+    }
+    ng[c] = g;
+    dot += g * (1.0f + w[c]) * x[c];
+  }
+  for (int c = 0; c < d; ++c) {
+    const float weighted = ng[c] * (1.0f + w[c]);
+    dx[c] = inv * weighted - x[c] * (inv * inv * inv / (float)d) * dot;
+    if (dw_part) dw_part[c] = ng[c] * x[c] * inv;
+  }
+}
+
+int oracle_gqa_sequence_bwd(const float* qg, const float* k_in, const float* v, const float* q_norm,
+                            const float* k_norm, const float* dy, int T, int q_heads, int kv_heads,
+                            int d, int rotary, float epsilon, float theta, int round, float* dqg,
+                            float* dk, float* dv, float* dqw, float* dkw, float* out_y) {
+  const size_t qn = (size_t)T * q_heads * d, kn = (size_t)T * kv_heads * d;
+  const size_t pn = (size_t)q_heads * T * T;
+  float* q = (float*)malloc(qn * sizeof(float));
+  float* k = (float*)malloc(kn * sizeof(float));
+  float* core = (float*)malloc(qn * sizeof(float));
+  float* dc = (float*)malloc(qn * sizeof(float));
+  float* dq_rope = (float*)malloc(qn * sizeof(float));
+  float* dk_rope = (float*)malloc(kn * sizeof(float));
+  float* p = (float*)calloc(pn, sizeof(float));
+  float* ds = (float*)calloc(pn, sizeof(float));
+  float* parts = (float*)malloc((qn > kn ? qn : kn) * sizeof(float));
+  if (!q || !k || !core || !dc || !dq_rope || !dk_rope || !p || !ds || !parts) {
+    free(q); free(k); free(core); free(dc); free(dq_rope); free(dk_rope); free(p); free(ds);
+    free(parts);
+    return -1;
+  }
+  const int group = q_heads / kv_heads;
+  const float scale = 1.0f / sqrtf((float)d), log_theta = logf(theta);
+  /* forward: prepare */
+  for (int row = 0; row < T; ++row) {
+    for (int h = 0; h < q_heads; ++h)
+      oracle_qk_prepare_head(qg + ((size_t)row * q_heads + h) * 2 * d, q_norm, d, rotary, row,
+                             epsilon, theta, round, q + ((size_t)row * q_heads + h) * d);
+    for (int h = 0; h < kv_heads; ++h)
+      oracle_qk_prepare_head(k_in + ((size_t)row * kv_heads + h) * d, k_norm, d, rotary, row,
+                             epsilon, theta, round, k + ((size_t)row * kv_heads + h) * d);
+  }
+  /* forward: online softmax in 32-key tiles, core, probabilities, gated output */
+  for (int row = 0; row < T; ++row)
+    for (int h = 0; h < q_heads; ++h) {
+      const int kv = h / group;
+      const float* query = q + ((size_t)row * q_heads + h) * d;
+      float maximum = -3.402823466e38f, denominator = 0.0f, sum[256];
+      for (int c = 0; c < d; ++c) sum[c] = 0.0f;
+      for (int start = 0; start <= row; start += 32) {
+        float score[32], next_max = maximum;
+        const int count = row + 1 - start < 32 ? row + 1 - start : 32;
+        for (int r = 0; r < count; ++r) {
+          const float* key = k + ((size_t)(start + r) * kv_heads + kv) * d;
+          float dot = 0.0f;
+          for (int c = 0; c < d; ++c) dot += key[c] * query[c];
+          score[r] = dot * scale;
+          if (score[r] > next_max) next_max = score[r];
+        }
+        const float correction = expf(maximum - next_max);
+        float tile_sum = 0.0f;
+        for (int c = 0; c < d; ++c) sum[c] *= correction;
+        for (int r = 0; r < count; ++r) {
+          const float pr = expf(score[r] - next_max);
+          const float* value = v + ((size_t)(start + r) * kv_heads + kv) * d;
+          for (int c = 0; c < d; ++c) sum[c] += pr * value[c];
+          tile_sum += pr;
+        }
+        denominator = denominator * correction + tile_sum;
+        maximum = next_max;
+      }
+      float* crow = core + ((size_t)row * q_heads + h) * d;
+      for (int c = 0; c < d; ++c) crow[c] = sum[c] / denominator;
+      if (out_y)
+        for (int c = 0; c < d; ++c) {
+          const float gate = qg[(((size_t)row * q_heads + h) * 2 + 1) * d + c];
+          const float sigmoid = rnd(1.0f / (1.0f + expf(-gate)), round);
+          out_y[((size_t)row * q_heads + h) * d + c] = rnd(rnd(crow[c], round) * sigmoid, round);
+        }
+      for (int t = 0; t <= row; ++t) {
+        const float* key = k + ((size_t)t * kv_heads + kv) * d;
+        float dot = 0.0f;
+        for (int c = 0; c < d; ++c) dot += key[c] * query[c];
+        p[((size_t)h * T + row) * T + t] = expf(dot * scale - maximum) / denominator;
+      }
+    }
+  /* GateBackwardKernel */
+  for (size_t i = 0; i < (size_t)T * q_heads; ++i)
+    for (int c = 0; c < d; ++c) {
+      const float gate = qg[(i * 2 + 1) * d + c];
+      const float sigmoid = 1.0f / (1.0f + expf(-gate));
+      const float grad = dy[i * d + c];
+      dc[i * d + c] = grad * rnd(sigmoid, round);
+      dqg[(i * 2 + 1) * d + c] = grad * rnd(core[i * d + c], round) * sigmoid * (1.0f - sigmoid);
+    }
+  /* QueryBackwardKernel */
+  for (int row = 0; row < T; ++row)
+    for (int h = 0; h < q_heads; ++h) {
+      const int kv = h / group;
+      const float* grad = dc + ((size_t)row * q_heads + h) * d;
+      const float* value = core + ((size_t)row * q_heads + h) * d;
+      float delta = 0.0f, sum[256];
+      for (int c = 0; c < d; ++c) { delta += grad[c] * value[c]; sum[c] = 0.0f; }
+      for (int t = 0; t <= row; ++t) {
+        const float* values = v + ((size_t)t * kv_heads + kv) * d;
+        const float* keys = k + ((size_t)t * kv_heads + kv) * d;
+        float dot = 0.0f;
+        for (int c = 0; c < d; ++c) dot += grad[c] * values[c];
+        const float score_grad = p[((size_t)h * T + row) * T + t] * (dot - delta);
+        ds[((size_t)h * T + row) * T + t] = score_grad;
+        for (int c = 0; c < d; ++c) sum[c] += score_grad * keys[c] * scale;
+      }
+      for (int c = 0; c < d; ++c) dq_rope[((size_t)row * q_heads + h) * d + c] = sum[c];
+    }
+  /* KeyValueBackwardKernel: fixed order over the group's heads, then over later rows */
+  for (int row = 0; row < T; ++row)
+    for (int kv = 0; kv < kv_heads; ++kv) {
+      float kg[256], vg[256];
+      for (int c = 0; c < d; ++c) kg[c] = vg[c] = 0.0f;
+      for (int h = kv * group; h < (kv + 1) * group; ++h)
+        for (int t = row; t < T; ++t) {
+          const float prob = p[((size_t)h * T + t) * T + row];
+          const float score_grad = ds[((size_t)h * T + t) * T + row];
+          const float* query = q + ((size_t)t * q_heads + h) * d;
+          const float* grad = dc + ((size_t)t * q_heads + h) * d;
+          for (int c = 0; c < d; ++c) {
+            kg[c] += score_grad * query[c] * scale;
+            vg[c] += prob * grad[c];
+          }
+        }
+      for (int c = 0; c < d; ++c) {
+        dk_rope[((size_t)row * kv_heads + kv) * d + c] = kg[c];
+        dv[((size_t)row * kv_heads + kv) * d + c] = vg[c];
+      }
+    }
+  /* NormBackwardKernel + ReduceNormKernel, queries then keys */
+  for (size_t i = 0; i < (size_t)T * q_heads; ++i)
+    norm_backward_row(qg + i * 2 * d, q_norm, dq_rope + i * d, d, rotary, (int)(i / q_heads),
+                      epsilon, log_theta, round, dqg + i * 2 * d, dqw ? parts + i * d : NULL);
+  if (dqw)
+    for (int c = 0; c < d; ++c) {
+      float sum = 0.0f;
+      for (size_t i = 0; i < (size_t)T * q_heads; ++i) sum += parts[i * d + c];
+      dqw[c] += sum;
+    }
+  for (size_t i = 0; i < (size_t)T * kv_heads; ++i)
+    norm_backward_row(k_in + i * d, k_norm, dk_rope + i * d, d, rotary, (int)(i / kv_heads),
+                      epsilon, log_theta, round, dk + i * d, dkw ? parts + i * d : NULL);
+  if (dkw)
+    for (int c = 0; c < d; ++c) {
+      float sum = 0.0f;
+      for (size_t i = 0; i < (size_t)T * kv_heads; ++i) sum += parts[i * d + c];
+      dkw[c] += sum;
+    }
+  free(q); free(k); free(core); free(dc); free(dq_rope); free(dk_rope); free(p); free(ds);
+  free(parts);
+  return 0;
+}
+
 /* ========================================================================================== *
  * Gated delta-net
  * ========================================================================================== */
