@@ -120,6 +120,51 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
                           size_t gate_token_stride, size_t gate_head_stride, int round_to_bf16);
 
 /* --------------------------------------------------------------------------------------------
+ * Backward of the Qwen sequence attention, QwenAttentionLayer::SequenceBackward
+ * (src/llm/layers/qwen_attention.cc:450-499), in the reference's three stages.  None of them
+ * materialises the [Hq,T,T] probabilities or score gradients the reference saves: the core pass
+ * recomputes P from the saved maxima / normalizers, so the T <= 128 limit does not apply.
+ *
+ * 1. pluto_gqa_gate_bwd: GateBackwardKernel (:123-138) plus the row term of the softmax
+ *    backward (QueryBackwardKernel :153-155):
+ *      dc = dy * R(sigmoid(gate)),  d_gate = dy * R(core) * s * (1 - s),  deltas = sum_c dc * core
+ *    gate bf16 and d_gate fp32 are addressed by (token, head) element strides (the gate half of
+ *    [T,Hq,2,D] is base + D with strides (2*Hq*D, 2*D)); core, dy, dc fp32 dense
+ *    [batch, seq, q_heads, head_dim]; deltas fp32 [batch*q_heads*seq] indexed like maxima.
+ * 2. pluto_gqa_prefill_bwd: QueryBackwardKernel + KeyValueBackwardKernel (:140-190):
+ *      dS = P * (dc . v - delta),  dq = scale * dS k,  dk = scale * sum dS^T q,  dv = sum P^T dc
+ *    with dk / dv summed over the query heads of the group and the later rows in a fixed order
+ *    (single writer, no atomics: repeated runs are bitwise equal).  q (strided like the forward),
+ *    k, v are the prepared tensors of the forward, bf16 or fp32 (dtype); dq fp32
+ *    [batch, seq, q_heads, head_dim], dk / dv fp32 [batch, seq, kv_heads, head_dim]: gradients
+ *    of the normalised, rotated vectors.  Exact fp32 arithmetic.
+ * 3. pluto_qk_prepare_bwd: NormBackwardKernel + ReduceNormKernel (:192-239): inverse partial
+ *    RoPE with the forward's (rounded) cos/sin, RMSNorm backward through the layer input x
+ *    (bf16, strided), dx fp32 strided (the query half of dQG [T,Hq,2,D], or dK [T,Hkv,D]).
+ *    d_weight (optional fp32 [head_dim]) is ACCUMULATED into, as the reference accumulates into
+ *    BlockParameter::gradient(); it needs a workspace of pluto_qk_prepare_bwd_workspace_bytes
+ *    (per-row parts reduced in a fixed order).  positions as in pluto_qk_prepare (null: token t of
+ *    every sequence sits at position t). */
+int pluto_gqa_gate_bwd(pluto_stream_t stream, const void* gate, size_t gate_token_stride,
+                       size_t gate_head_stride, const float* core, const float* dy, float* dc,
+                       float* d_gate, size_t d_gate_token_stride, size_t d_gate_head_stride,
+                       float* deltas, int batch, int seq, int q_heads, int head_dim,
+                       int round_to_bf16);
+int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, const void* v,
+                          int dtype, size_t q_token_stride, size_t q_head_stride, const float* dc,
+                          const float* maxima, const float* normalizers, const float* deltas,
+                          float* dq, float* dk, float* dv, int batch, int seq, int q_heads,
+                          int kv_heads, int head_dim);
+size_t pluto_qk_prepare_bwd_workspace_bytes(int batch, int tokens, int heads, int head_dim);
+int pluto_qk_prepare_bwd(pluto_stream_t stream, const void* x, size_t x_token_stride,
+                         size_t x_head_stride, const float* weight, const float* grad,
+                         const int32_t* positions, float* dx, size_t dx_token_stride,
+                         size_t dx_head_stride, float* d_weight, void* workspace,
+                         size_t workspace_bytes, int batch, int tokens, int heads, int head_dim,
+                         int rotary_dim, float rms_norm_epsilon, float rope_theta,
+                         int round_to_bf16);
+
+/* --------------------------------------------------------------------------------------------
  * KV cache addressing shared by prepare and decode.  The reference keeps one KeyValueCache per
  * sequence: two fp32 buffers [capacity, kv_heads, head_dim] plus a position counter
  * (src/llm/key_value_cache.h:25-57).  Every value it stores is already rounded to bf16 when

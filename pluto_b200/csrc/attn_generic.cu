@@ -278,15 +278,27 @@ attn_probs_generic(const T* __restrict__ qkv, const float* __restrict__ maxima,
   }
 }
 
+// Addressing for the backward passes: element strides of the separate tensors.  `group` query
+// heads share one key/value head; the packed [rows, 3E] layout is the special case with all token
+// strides 3E, head strides D and group 1.
+struct BwdViews {
+  size_t q_token, q_head, kv_token, kv_head;      // q, and k/v (indexed by key/value head)
+  size_t o_token, o_head;                         // saved output (only when deltas are computed here)
+  size_t g_token, g_head;                         // upstream gradient (fp32)
+  size_t dq_token, dq_head, dkv_token, dkv_head;  // gradients (fp32)
+  int group;
+};
+
 // ------------------------------------------------------------------------------------------
-// backward, query-owned pass: deltas and dQ.  grid (query tiles, heads, batch)
+// backward, query-owned pass: deltas and dQ.  grid (query tiles, query heads, batch)
+// With `out` null the deltas were written by the caller (gate backward) and are only read.
 // ------------------------------------------------------------------------------------------
 template <typename T, int DP, int BM>
 __global__ void __launch_bounds__(kThreads)
-attn_bwd_dq_generic(const T* __restrict__ qkv, const T* __restrict__ out,
-                    const float* __restrict__ d_out, const float* __restrict__ maxima,
-                    const float* __restrict__ normalizers, float* __restrict__ d_qkv,
-                    float* __restrict__ deltas, Dims dims) {
+attn_bwd_dq_generic(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                    const T* __restrict__ out, const float* __restrict__ d_out,
+                    const float* __restrict__ maxima, const float* __restrict__ normalizers,
+                    float* __restrict__ dq, float* __restrict__ deltas, Dims dims, BwdViews views) {
   constexpr int BN = BM, MI = BM / 16, NJ = BN / 16, DC = DP / 16;
   extern __shared__ float smem[];
   float(*Qs)[DP + 1] = reinterpret_cast<float(*)[DP + 1]>(smem);
@@ -295,37 +307,43 @@ attn_bwd_dq_generic(const T* __restrict__ qkv, const T* __restrict__ out,
   float(*Vs)[DP + 1] = Ks + BN;
   float(*Ps)[BN + 1] = reinterpret_cast<float(*)[BN + 1]>(Vs + BN);
 
-  const int S = dims.seq, H = dims.heads, D = dims.head_dim, E = H * D;
+  const int S = dims.seq, H = dims.heads, D = dims.head_dim;
   const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
-  const size_t stride = 3 * static_cast<size_t>(E);
-  const T* base = qkv + static_cast<size_t>(b) * S * stride + static_cast<size_t>(h) * D;
-  const float* g_base = d_out + static_cast<size_t>(b) * S * E + static_cast<size_t>(h) * D;
-  const T* o_base = out + static_cast<size_t>(b) * S * E + static_cast<size_t>(h) * D;
+  const T* q_base = q + static_cast<size_t>(b) * S * views.q_token + h * views.q_head;
+  const T* k_base = k + static_cast<size_t>(b) * S * views.kv_token + (h / views.group) * views.kv_head;
+  const T* v_base = v + static_cast<size_t>(b) * S * views.kv_token + (h / views.group) * views.kv_head;
+  const float* g_base = d_out + static_cast<size_t>(b) * S * views.g_token + h * views.g_head;
 
-  load_tile<T, BM, DP>(Qs, base, stride, qt * BM, S, D);
-  load_tile<float, BM, DP>(Gs, g_base, E, qt * BM, S, D);
-  load_tile<T, BM, DP>(Ks, o_base, E, qt * BM, S, D);  // borrow Ks for the saved output
+  load_tile<T, BM, DP>(Qs, q_base, views.q_token, qt * BM, S, D);
+  load_tile<float, BM, DP>(Gs, g_base, views.g_token, qt * BM, S, D);
+  if (out != nullptr)  // borrow Ks for the saved output
+    load_tile<T, BM, DP>(Ks, out + static_cast<size_t>(b) * S * views.o_token + h * views.o_head,
+                         views.o_token, qt * BM, S, D);
   __syncthreads();
   float m[MI], inv[MI], delta[MI], acc[MI][DC];
 #pragma unroll
   for (int i = 0; i < MI; ++i) {
     const int r = ty + 16 * i;
-    float part = 0.0f;
-    for (int d = tx; d < D; d += 16) part = fmaf(Gs[r][d], Ks[r][d], part);
-    delta[i] = group16_sum(part);
     const int query = qt * BM + r;
     const size_t stat = (static_cast<size_t>(b) * H + h) * S + min(query, S - 1);
+    if (out != nullptr) {
+      float part = 0.0f;
+      for (int d = tx; d < D; d += 16) part = fmaf(Gs[r][d], Ks[r][d], part);
+      delta[i] = group16_sum(part);
+      if (tx == 0 && query < S) deltas[stat] = delta[i];
+    } else {
+      delta[i] = deltas[stat];
+    }
     m[i] = maxima[stat];
     inv[i] = 1.0f / normalizers[stat];
-    if (tx == 0 && query < S) deltas[stat] = delta[i];
 #pragma unroll
     for (int c = 0; c < DC; ++c) acc[i][c] = 0.0f;
   }
   for (int kt = 0; kt <= qt; ++kt) {
     __syncthreads();
-    load_tile<T, BN, DP>(Ks, base + E, stride, kt * BN, S, D);
-    load_tile<T, BN, DP>(Vs, base + 2 * E, stride, kt * BN, S, D);
+    load_tile<T, BN, DP>(Ks, k_base, views.kv_token, kt * BN, S, D);
+    load_tile<T, BN, DP>(Vs, v_base, views.kv_token, kt * BN, S, D);
     __syncthreads();
     float s[MI][NJ], dp[MI][NJ];
     mm_nt<MI, NJ, DP>(s, Qs, Ks, D, ty, tx);
@@ -348,23 +366,26 @@ attn_bwd_dq_generic(const T* __restrict__ qkv, const T* __restrict__ out,
   for (int i = 0; i < MI; ++i) {
     const int query = qt * BM + ty + 16 * i;
     if (query >= S) continue;
-    float* dq = d_qkv + (static_cast<size_t>(b) * S + query) * stride + static_cast<size_t>(h) * D;
+    float* row = dq + (static_cast<size_t>(b) * S + query) * views.dq_token + h * views.dq_head;
 #pragma unroll
     for (int c = 0; c < DC; ++c) {
       const int d = tx + 16 * c;
-      if (d < D) dq[d] = acc[i][c];
+      if (d < D) row[d] = acc[i][c];
     }
   }
 }
 
 // ------------------------------------------------------------------------------------------
-// backward, key/value-owned pass: dK and dV.  grid (key tiles, heads, batch)
+// backward, key/value-owned pass: dK and dV.  grid (key tiles, key/value heads, batch).  The
+// query heads of the group and the query tiles are visited in a fixed order (single writer).
 // ------------------------------------------------------------------------------------------
 template <typename T, int DP, int BM>
 __global__ void __launch_bounds__(kThreads)
-attn_bwd_dkv_generic(const T* __restrict__ qkv, const float* __restrict__ d_out,
-                     const float* __restrict__ maxima, const float* __restrict__ normalizers,
-                     const float* __restrict__ deltas, float* __restrict__ d_qkv, Dims dims) {
+attn_bwd_dkv_generic(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                     const float* __restrict__ d_out, const float* __restrict__ maxima,
+                     const float* __restrict__ normalizers, const float* __restrict__ deltas,
+                     float* __restrict__ dk_out, float* __restrict__ dv_out, Dims dims,
+                     BwdViews views) {
   constexpr int BN = BM, MI = BM / 16, NJ = BN / 16, DC = DP / 16;
   extern __shared__ float smem[];
   float(*Qs)[DP + 1] = reinterpret_cast<float(*)[DP + 1]>(smem);
@@ -374,59 +395,62 @@ attn_bwd_dkv_generic(const T* __restrict__ qkv, const float* __restrict__ d_out,
   float(*Ps)[BN + 1] = reinterpret_cast<float(*)[BN + 1]>(Vs + BN);
   float(*Ss)[BN + 1] = Ps + BM;  // dS
 
-  const int S = dims.seq, H = dims.heads, D = dims.head_dim, E = H * D;
-  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int S = dims.seq, H = dims.heads, D = dims.head_dim;
+  const int kt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
-  const size_t stride = 3 * static_cast<size_t>(E);
-  const T* base = qkv + static_cast<size_t>(b) * S * stride + static_cast<size_t>(h) * D;
-  const float* g_base = d_out + static_cast<size_t>(b) * S * E + static_cast<size_t>(h) * D;
+  const T* k_base = k + static_cast<size_t>(b) * S * views.kv_token + kvh * views.kv_head;
+  const T* v_base = v + static_cast<size_t>(b) * S * views.kv_token + kvh * views.kv_head;
 
-  load_tile<T, BN, DP>(Ks, base + E, stride, kt * BN, S, D);
-  load_tile<T, BN, DP>(Vs, base + 2 * E, stride, kt * BN, S, D);
+  load_tile<T, BN, DP>(Ks, k_base, views.kv_token, kt * BN, S, D);
+  load_tile<T, BN, DP>(Vs, v_base, views.kv_token, kt * BN, S, D);
   float dk[MI][DC], dv[MI][DC];
 #pragma unroll
   for (int i = 0; i < MI; ++i)
 #pragma unroll
     for (int c = 0; c < DC; ++c) dk[i][c] = dv[i][c] = 0.0f;
   const int tiles = (S + BM - 1) / BM;
-  for (int qt = kt; qt < tiles; ++qt) {
-    __syncthreads();
-    load_tile<T, BM, DP>(Qs, base, stride, qt * BM, S, D);
-    load_tile<float, BM, DP>(Gs, g_base, E, qt * BM, S, D);
-    __syncthreads();
-    float s[MI][NJ], dp[MI][NJ];
-    mm_nt<MI, NJ, DP>(s, Qs, Ks, D, ty, tx);
-    mm_nt<MI, NJ, DP>(dp, Gs, Vs, D, ty, tx);
+  for (int h = kvh * views.group; h < (kvh + 1) * views.group; ++h) {
+    const T* q_base = q + static_cast<size_t>(b) * S * views.q_token + h * views.q_head;
+    const float* g_base = d_out + static_cast<size_t>(b) * S * views.g_token + h * views.g_head;
+    for (int qt = kt; qt < tiles; ++qt) {
+      __syncthreads();
+      load_tile<T, BM, DP>(Qs, q_base, views.q_token, qt * BM, S, D);
+      load_tile<float, BM, DP>(Gs, g_base, views.g_token, qt * BM, S, D);
+      __syncthreads();
+      float s[MI][NJ], dp[MI][NJ];
+      mm_nt<MI, NJ, DP>(s, Qs, Ks, D, ty, tx);
+      mm_nt<MI, NJ, DP>(dp, Gs, Vs, D, ty, tx);
 #pragma unroll
-    for (int i = 0; i < MI; ++i) {
-      const int query = qt * BM + ty + 16 * i;
-      const size_t stat = (static_cast<size_t>(b) * H + h) * S + min(query, S - 1);
-      const float m = maxima[stat], inv = 1.0f / normalizers[stat], delta = deltas[stat];
+      for (int i = 0; i < MI; ++i) {
+        const int query = qt * BM + ty + 16 * i;
+        const size_t stat = (static_cast<size_t>(b) * H + h) * S + min(query, S - 1);
+        const float m = maxima[stat], inv = 1.0f / normalizers[stat], delta = deltas[stat];
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        const int key = kt * BN + tx + 16 * j;
-        const bool valid = key <= query && key < S && query < S;
-        const float p = valid ? expf(s[i][j] * dims.scale - m) * inv : 0.0f;
-        Ps[ty + 16 * i][tx + 16 * j] = p;
-        Ss[ty + 16 * i][tx + 16 * j] = p * (dp[i][j] - delta) * dims.scale;
+        for (int j = 0; j < NJ; ++j) {
+          const int key = kt * BN + tx + 16 * j;
+          const bool valid = key <= query && key < S && query < S;
+          const float p = valid ? expf(s[i][j] * dims.scale - m) * inv : 0.0f;
+          Ps[ty + 16 * i][tx + 16 * j] = p;
+          Ss[ty + 16 * i][tx + 16 * j] = p * (dp[i][j] - delta) * dims.scale;
+        }
       }
+      __syncthreads();
+      const int qcount = min(BM, S - qt * BM);
+      mm_tn<MI, DC, BN, DP>(dv, Ps, Gs, qcount, ty, tx);
+      mm_tn<MI, DC, BN, DP>(dk, Ss, Qs, qcount, ty, tx);
     }
-    __syncthreads();
-    const int qcount = min(BM, S - qt * BM);
-    mm_tn<MI, DC, BN, DP>(dv, Ps, Gs, qcount, ty, tx);
-    mm_tn<MI, DC, BN, DP>(dk, Ss, Qs, qcount, ty, tx);
   }
 #pragma unroll
   for (int i = 0; i < MI; ++i) {
     const int key = kt * BN + ty + 16 * i;
     if (key >= S) continue;
-    float* row = d_qkv + (static_cast<size_t>(b) * S + key) * stride + static_cast<size_t>(h) * D;
+    const size_t off = (static_cast<size_t>(b) * S + key) * views.dkv_token + kvh * views.dkv_head;
 #pragma unroll
     for (int c = 0; c < DC; ++c) {
       const int d = tx + 16 * c;
       if (d < D) {
-        row[E + d] = dk[i][c];
-        row[2 * E + d] = dv[i][c];
+        dk_out[off + d] = dk[i][c];
+        dv_out[off + d] = dv[i][c];
       }
     }
   }
@@ -473,24 +497,26 @@ cudaError_t launch_probs(cudaStream_t stream, const void* qkv, const float* maxi
   return cudaGetLastError();
 }
 template <typename T, int DP, int BM>
-cudaError_t launch_bwd(cudaStream_t stream, const void* qkv, const void* out, const float* d_out,
-                       const float* maxima, const float* normalizers, float* d_qkv, float* deltas,
-                       int batch, Dims dims) {
+cudaError_t launch_bwd(cudaStream_t stream, const void* q, const void* k, const void* v,
+                       const void* out, const float* d_out, const float* maxima,
+                       const float* normalizers, float* dq_out, float* dk_out, float* dv_out,
+                       float* deltas, int batch, Dims dims, BwdViews views) {
   auto dq = attn_bwd_dq_generic<T, DP, BM>;
   auto dkv = attn_bwd_dkv_generic<T, DP, BM>;
   cudaError_t e = opt_in(dq, dq_smem<DP, BM>());
   if (e != cudaSuccess) return e;
   e = opt_in(dkv, dkv_smem<DP, BM>());
   if (e != cudaSuccess) return e;
-  dim3 grid((dims.seq + BM - 1) / BM, dims.heads, batch);
-  dq<<<grid, kThreads, dq_smem<DP, BM>(), stream>>>(static_cast<const T*>(qkv),
-                                                    static_cast<const T*>(out), d_out, maxima,
-                                                    normalizers, d_qkv, deltas, dims);
+  const int tiles = (dims.seq + BM - 1) / BM;
+  dq<<<dim3(tiles, dims.heads, batch), kThreads, dq_smem<DP, BM>(), stream>>>(
+      static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v),
+      static_cast<const T*>(out), d_out, maxima, normalizers, dq_out, deltas, dims, views);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   // Same-stream ordering makes every delta visible to the key/value-owned pass.
-  dkv<<<grid, kThreads, dkv_smem<DP, BM>(), stream>>>(static_cast<const T*>(qkv), d_out, maxima,
-                                                      normalizers, deltas, d_qkv, dims);
+  dkv<<<dim3(tiles, dims.heads / views.group, batch), kThreads, dkv_smem<DP, BM>(), stream>>>(
+      static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), d_out, maxima,
+      normalizers, deltas, dk_out, dv_out, dims, views);
   return cudaGetLastError();
 }
 
@@ -541,16 +567,45 @@ cudaError_t attn_generic_bwd(cudaStream_t stream, const void* qkv, const void* o
                              const float* d_out, const float* maxima, const float* normalizers,
                              float* d_qkv, float* deltas, int batch, int seq, int heads,
                              int head_dim, bool bf16) {
-  Dims dims{seq, heads, head_dim, 1.0f / sqrtf(static_cast<float>(head_dim))};
-#define CALL_B(T, DP, BM) \
-  launch_bwd<T, DP, BM>(stream, qkv, out, d_out, maxima, normalizers, d_qkv, deltas, batch, dims)
-  if (bf16) {
-    if (head_dim <= 64) return CALL_B(__nv_bfloat16, 64, 64);
-    if (head_dim <= 128) return CALL_B(__nv_bfloat16, 128, 64);
+  const size_t E = static_cast<size_t>(heads) * head_dim, D = head_dim;
+  const size_t elem = bf16 ? 2 : 4;
+  const char* base = static_cast<const char*>(qkv);
+  GqaBwdArgs a{};
+  a.q = base;
+  a.k = base + E * elem;
+  a.v = base + 2 * E * elem;
+  a.out = out;
+  a.d_out = d_out;
+  a.maxima = maxima;
+  a.normalizers = normalizers;
+  a.deltas = deltas;
+  a.dq = d_qkv;
+  a.dk = d_qkv + E;
+  a.dv = d_qkv + 2 * E;
+  a.batch = batch; a.seq = seq; a.q_heads = heads; a.kv_heads = heads; a.head_dim = head_dim;
+  a.q_token = a.kv_token = a.dq_token = a.dkv_token = 3 * E;
+  a.q_head = a.kv_head = a.dq_head = a.dkv_head = a.o_head = a.g_head = D;
+  a.o_token = a.g_token = E;
+  a.bf16 = bf16;
+  return gqa_generic_bwd(stream, a);
+}
+
+// Backward of the attention core over separate tensors with grouped query heads (the Qwen
+// sequence layer): see GqaBwdArgs in engine.h.
+cudaError_t gqa_generic_bwd(cudaStream_t stream, const GqaBwdArgs& a) {
+  Dims dims{a.seq, a.q_heads, a.head_dim, 1.0f / sqrtf(static_cast<float>(a.head_dim))};
+  BwdViews views{a.q_token, a.q_head, a.kv_token, a.kv_head, a.o_token, a.o_head, a.g_token,
+                 a.g_head, a.dq_token, a.dq_head, a.dkv_token, a.dkv_head, a.q_heads / a.kv_heads};
+#define CALL_B(T, DP, BM)                                                                        \
+  launch_bwd<T, DP, BM>(stream, a.q, a.k, a.v, a.out, a.d_out, a.maxima, a.normalizers, a.dq, a.dk, \
+                        a.dv, a.deltas, a.batch, dims, views)
+  if (a.bf16) {
+    if (a.head_dim <= 64) return CALL_B(__nv_bfloat16, 64, 64);
+    if (a.head_dim <= 128) return CALL_B(__nv_bfloat16, 128, 64);
     return CALL_B(__nv_bfloat16, 256, 32);
   }
-  if (head_dim <= 64) return CALL_B(float, 64, 64);
-  if (head_dim <= 128) return CALL_B(float, 128, 64);
+  if (a.head_dim <= 64) return CALL_B(float, 64, 64);
+  if (a.head_dim <= 128) return CALL_B(float, 128, 64);
   return CALL_B(float, 256, 32);
 #undef CALL_B
 }

@@ -189,6 +189,96 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
       "GQA prefill launch");
 }
 
+int pluto_gqa_gate_bwd(pluto_stream_t stream, const void* gate, size_t gate_token_stride,
+                       size_t gate_head_stride, const float* core, const float* dy, float* dc,
+                       float* d_gate, size_t d_gate_token_stride, size_t d_gate_head_stride,
+                       float* deltas, int batch, int seq, int q_heads, int head_dim,
+                       int round_to_bf16) {
+  if (batch <= 0 || seq <= 0 || q_heads <= 0 || head_dim <= 0 || head_dim > 256 ||
+      static_cast<long long>(batch) * seq * q_heads > 0x7fffffffLL)
+    return fail(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
+  if (!gate || !core || !dy || !dc || !d_gate || !deltas)
+    return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
+  pluto::GateBwdArgs a{};
+  a.gate = static_cast<const __nv_bfloat16*>(gate);
+  a.gate_token = gate_token_stride; a.gate_head = gate_head_stride;
+  a.core = core; a.dy = dy; a.dc = dc; a.d_gate = d_gate;
+  a.dgate_token = d_gate_token_stride; a.dgate_head = d_gate_head_stride;
+  a.deltas = deltas;
+  a.batch = batch; a.seq = seq; a.q_heads = q_heads; a.head_dim = head_dim;
+  a.round = round_to_bf16;
+  return from_cuda(pluto::gqa_gate_bwd(stream, a), "sequence full attention backward (gate)");
+}
+
+int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, const void* v,
+                          int dtype, size_t q_token_stride, size_t q_head_stride, const float* dc,
+                          const float* maxima, const float* normalizers, const float* deltas,
+                          float* dq, float* dk, float* dv, int batch, int seq, int q_heads,
+                          int kv_heads, int head_dim) {
+  if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
+      q_heads % kv_heads != 0 || head_dim > 256 || batch > 65535 || q_heads > 65535)
+    return fail(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
+  if (dtype != PLUTO_FP32 && dtype != PLUTO_BF16)
+    return fail(PLUTO_E_INVALID, "attention tensors have an unknown dtype");
+  if (!q || !k || !v || !dc || !dq || !dk || !dv)
+    return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
+  if (!maxima) return fail(PLUTO_E_INVALID, "attention backward requires saved maxima");
+  if (!normalizers) return fail(PLUTO_E_INVALID, "attention backward requires saved normalizers");
+  if (!deltas) return fail(PLUTO_E_INVALID, "attention backward requires the gate pass deltas");
+  if (q_head_stride < static_cast<size_t>(head_dim) ||
+      q_token_stride < (static_cast<size_t>(q_heads) - 1) * q_head_stride + head_dim)
+    return fail(PLUTO_E_INVALID, "attention query strides overlap");
+  const size_t D = head_dim, qd = static_cast<size_t>(q_heads) * D, kd = static_cast<size_t>(kv_heads) * D;
+  pluto::GqaBwdArgs a{};
+  a.q = q; a.k = k; a.v = v; a.out = nullptr;
+  a.d_out = dc; a.maxima = maxima; a.normalizers = normalizers;
+  a.deltas = const_cast<float*>(deltas);   // only read when out is null
+  a.dq = dq; a.dk = dk; a.dv = dv;
+  a.batch = batch; a.seq = seq; a.q_heads = q_heads; a.kv_heads = kv_heads; a.head_dim = head_dim;
+  a.q_token = q_token_stride; a.q_head = q_head_stride;
+  a.kv_token = kd; a.kv_head = D;
+  a.o_token = qd; a.o_head = D; a.g_token = qd; a.g_head = D;
+  a.dq_token = qd; a.dq_head = D; a.dkv_token = kd; a.dkv_head = D;
+  a.bf16 = dtype == PLUTO_BF16;
+  return from_cuda(pluto::gqa_generic_bwd(stream, a), "sequence full attention backward");
+}
+
+size_t pluto_qk_prepare_bwd_workspace_bytes(int batch, int tokens, int heads, int head_dim) {
+  if (batch <= 0 || tokens <= 0 || heads <= 0 || head_dim <= 0) return 0;
+  return pluto::qk_prepare_bwd_workspace_bytes(static_cast<long long>(batch) * tokens * heads, head_dim);
+}
+
+int pluto_qk_prepare_bwd(pluto_stream_t stream, const void* x, size_t x_token_stride,
+                         size_t x_head_stride, const float* weight, const float* grad,
+                         const int32_t* positions, float* dx, size_t dx_token_stride,
+                         size_t dx_head_stride, float* d_weight, void* workspace,
+                         size_t workspace_bytes, int batch, int tokens, int heads, int head_dim,
+                         int rotary_dim, float rms_norm_epsilon, float rope_theta,
+                         int round_to_bf16) {
+  if (batch <= 0 || tokens <= 0 || heads <= 0 || head_dim <= 0 || head_dim > 256 ||
+      rotary_dim <= 0 || rotary_dim > head_dim || rotary_dim % 2 != 0 ||
+      !(rms_norm_epsilon > 0.0f) || !std::isfinite(rms_norm_epsilon) || !(rope_theta > 0.0f) ||
+      !std::isfinite(rope_theta) ||
+      static_cast<long long>(batch) * tokens * heads > 0x7fffffffLL)
+    return fail(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
+  if (!x || !weight || !grad || !dx)
+    return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
+  if (d_weight != nullptr &&
+      (workspace == nullptr ||
+       workspace_bytes < pluto_qk_prepare_bwd_workspace_bytes(batch, tokens, heads, head_dim)))
+    return fail(PLUTO_E_INVALID, "norm-weight gradient requires its workspace");
+  pluto::NormBwdArgs a{};
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.x_token = x_token_stride; a.x_head = x_head_stride;
+  a.weight = weight; a.grad = grad; a.positions = positions;
+  a.dx = dx; a.dx_token = dx_token_stride; a.dx_head = dx_head_stride;
+  a.batch = batch; a.tokens = tokens; a.heads = heads; a.head_dim = head_dim; a.rotary = rotary_dim;
+  a.epsilon = rms_norm_epsilon; a.log_theta = logf(rope_theta);
+  a.round = round_to_bf16;
+  return from_cuda(pluto::qk_prepare_bwd(stream, a, d_weight, workspace),
+                   "sequence full attention backward (norm)");
+}
+
 }  // extern "C"
 
 namespace {

@@ -4,6 +4,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -28,6 +29,50 @@ cudaError_t attn_generic_bwd(cudaStream_t stream, const void* qkv, const void* o
                              const float* d_out, const float* maxima, const float* normalizers,
                              float* d_qkv, float* deltas, int batch, int seq, int heads,
                              int head_dim, bool bf16);
+
+// Backward of the causal attention core over separate tensors (element strides), `q_heads /
+// kv_heads` query heads per key/value head.  q, k, v: bf16 or fp32 (`bf16`); d_out, dq, dk, dv,
+// maxima, normalizers, deltas fp32; statistics indexed (b*q_heads + h)*seq + s.  With `out` set
+// the deltas (row sums of d_out * out) are computed and stored; with `out` null they are read.
+struct GqaBwdArgs {
+  const void *q, *k, *v, *out;
+  const float *d_out, *maxima, *normalizers;
+  float *deltas, *dq, *dk, *dv;
+  int batch, seq, q_heads, kv_heads, head_dim;
+  size_t q_token, q_head, kv_token, kv_head, o_token, o_head, g_token, g_head;
+  size_t dq_token, dq_head, dkv_token, dkv_head;
+  bool bf16;
+};
+cudaError_t gqa_generic_bwd(cudaStream_t stream, const GqaBwdArgs& args);
+
+// ---- qwen_bwd.cu: gate, RoPE^-1 + RMSNorm backward, norm-weight reduction -----------------------
+struct GateBwdArgs {
+  const __nv_bfloat16* gate;   // element strides gate_token / gate_head
+  size_t gate_token, gate_head;
+  const float* core;           // dense [B, S, Hq, D]
+  const float* dy;             // dense
+  float* dc;                   // dense
+  float* d_gate;               // element strides dgate_token / dgate_head
+  size_t dgate_token, dgate_head;
+  float* deltas;               // [(b*Hq + h)*S + s]
+  int batch, seq, q_heads, head_dim, round;
+};
+cudaError_t gqa_gate_bwd(cudaStream_t stream, const GateBwdArgs& args);
+struct NormBwdArgs {
+  const __nv_bfloat16* x;      // layer input, element strides x_token / x_head
+  size_t x_token, x_head;
+  const float* weight;         // zero-centred [D]
+  const float* grad;           // dense [B, T, heads, D]: gradient of the rotated, normalised vector
+  const int* positions;        // optional [B]: RoPE position of token 0 (null = 0)
+  float* dx;                   // element strides dx_token / dx_head
+  size_t dx_token, dx_head;
+  float* parts;                // set by qk_prepare_bwd
+  int batch, tokens, heads, head_dim, rotary;
+  float epsilon, log_theta;
+  int round;
+};
+size_t qk_prepare_bwd_workspace_bytes(long long rows, int head_dim);
+cudaError_t qk_prepare_bwd(cudaStream_t stream, NormBwdArgs args, float* d_weight, void* workspace);
 
 // ---- attn_bwd_sm100.cu: tcgen05 backward, bf16, head_dim 64 or 128 -----------------------------
 size_t attn_bwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim);

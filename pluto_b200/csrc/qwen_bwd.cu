@@ -1,0 +1,137 @@
+// Elementwise pieces of the Qwen sequence-attention backward
+// (src/llm/layers/qwen_attention.cc:120-239): the sigmoid output gate, the inverse partial RoPE
+// followed by the per-head RMSNorm backward, and the deterministic reduction of the shared
+// norm-weight gradient.  The attention core between them runs in attn_generic.cu
+// (gqa_generic_bwd).  One CTA of 256 threads per (token, head); head width <= 256.
+#include "common.cuh"
+#include "engine.h"
+
+namespace pluto {
+namespace {
+
+__device__ __forceinline__ float rnd(float v, int round) { return round ? bf16_round(v) : v; }
+
+// Sum over the 256 threads of a CTA in a fixed order (warp shuffles, then warp 0..7 in sequence).
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();   // red may still be read from a previous call
+  if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = v;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) total += red[w];
+  return total;
+}
+
+// GateBackwardKernel (:123-138): dc = dy * R(sigmoid(gate)); d_gate = dy * R(core) * s * (1 - s),
+// s in fp32.  Also the row term of the softmax backward, delta = dc . core with the unrounded
+// core (QueryBackwardKernel :153-155), so the core pass only reads it.
+__global__ void __launch_bounds__(256) gate_bwd_kernel(GateBwdArgs a) {
+  __shared__ float red[8];
+  const int token = blockIdx.x / a.q_heads, h = blockIdx.x % a.q_heads;
+  const int b = token / a.seq, s = token % a.seq;
+  const int c = threadIdx.x, D = a.head_dim;
+  const size_t dense = (static_cast<size_t>(token) * a.q_heads + h) * D;
+  float part = 0.0f;
+  if (c < D) {
+    const float gate = __bfloat162float(
+        a.gate[static_cast<size_t>(token) * a.gate_token + static_cast<size_t>(h) * a.gate_head + c]);
+    const float sigmoid = 1.0f / (1.0f + expf(-gate));
+    const float grad = a.dy[dense + c], core = a.core[dense + c];
+    const float dc = grad * rnd(sigmoid, a.round);
+    a.dc[dense + c] = dc;
+    a.d_gate[static_cast<size_t>(token) * a.dgate_token + static_cast<size_t>(h) * a.dgate_head + c] =
+        grad * rnd(core, a.round) * sigmoid * (1.0f - sigmoid);
+    part = dc * core;
+  }
+  const float delta = block_sum(part, red);
+  if (c == 0) a.deltas[(static_cast<size_t>(b) * a.q_heads + h) * a.seq + s] = delta;
+}
+
+// NormBackwardKernel (:196-226): rotate the gradient back with the rounded cos/sin of the forward,
+// then the RMSNorm backward; `parts` (optional) receives normalized_grad * x * inv per row.
+__global__ void __launch_bounds__(256) norm_bwd_kernel(NormBwdArgs a) {
+  __shared__ float red[8];
+  const int token = blockIdx.x / a.heads, h = blockIdx.x % a.heads;
+  const int b = token / a.tokens, t = token % a.tokens;
+  const int c = threadIdx.x, D = a.head_dim;
+  const int position = (a.positions ? a.positions[b] : 0) + t;
+  const size_t dense = (static_cast<size_t>(token) * a.heads + h) * D;
+  const size_t in0 = static_cast<size_t>(token) * a.x_token + static_cast<size_t>(h) * a.x_head;
+  const float x = c < D ? __bfloat162float(a.x[in0 + c]) : 0.0f;
+  const float inv = rsqrtf(block_sum(x * x, red) / static_cast<float>(D) + a.epsilon);
+  float ng = 0.0f, weighted = 0.0f;
+  if (c < D) {
+    ng = a.grad[dense + c];
+    if (c < a.rotary) {
+      const int half = a.rotary / 2;
+      const int partner = c < half ? c + half : c - half;
+      const int f = c < half ? c : c - half;
+      const float angle = static_cast<float>(position) *
+                          expf(static_cast<float>(f) * (-2.0f * a.log_theta / static_cast<float>(a.rotary)));
+      const float co = rnd(cosf(angle), a.round), si = rnd(sinf(angle), a.round);
+      const float gp = a.grad[dense + partner];
+      ng = ng * co + (c < half ? gp * si : -gp * si);
+    }
+    weighted = ng * (1.0f + a.weight[c]);
+  }
+  const float dot = block_sum(weighted * x, red);
+  if (c < D) {
+    a.dx[static_cast<size_t>(token) * a.dx_token + static_cast<size_t>(h) * a.dx_head + c] =
+        inv * weighted - x * (inv * inv * inv / static_cast<float>(D)) * dot;
+    if (a.parts) a.parts[dense + c] = ng * x * inv;
+  }
+}
+
+// ReduceNormKernel (:228-239) in two fixed-order levels: CTA i sums rows [i*kChunk, (i+1)*kChunk)
+// per column, then one CTA sums the chunk rows in order and accumulates into the gradient.
+constexpr int kChunk = 1024;
+__global__ void __launch_bounds__(256) norm_reduce_chunks(const float* parts, long long rows, int D,
+                                                          float* chunk_sums) {
+  const int c = threadIdx.x;
+  if (c >= D) return;
+  const long long r0 = static_cast<long long>(blockIdx.x) * kChunk;
+  const long long r1 = r0 + kChunk < rows ? r0 + kChunk : rows;
+  float sum = 0.0f;
+  for (long long r = r0; r < r1; ++r) sum += parts[r * D + c];
+  chunk_sums[static_cast<size_t>(blockIdx.x) * D + c] = sum;
+}
+__global__ void __launch_bounds__(256) norm_reduce_final(const float* chunk_sums, int chunks, int D,
+                                                         float* dw) {
+  const int c = threadIdx.x;
+  if (c >= D) return;
+  float sum = 0.0f;
+  for (int i = 0; i < chunks; ++i) sum += chunk_sums[static_cast<size_t>(i) * D + c];
+  dw[c] += sum;
+}
+
+}  // namespace
+
+cudaError_t gqa_gate_bwd(cudaStream_t stream, const GateBwdArgs& a) {
+  const long long blocks = static_cast<long long>(a.batch) * a.seq * a.q_heads;
+  gate_bwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+size_t qk_prepare_bwd_workspace_bytes(long long rows, int head_dim) {
+  const long long chunks = (rows + kChunk - 1) / kChunk;
+  return static_cast<size_t>(rows + chunks) * head_dim * sizeof(float);
+}
+
+cudaError_t qk_prepare_bwd(cudaStream_t stream, NormBwdArgs a, float* d_weight, void* workspace) {
+  const long long rows = static_cast<long long>(a.batch) * a.tokens * a.heads;
+  a.parts = d_weight ? static_cast<float*>(workspace) : nullptr;
+  norm_bwd_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || d_weight == nullptr) return e;
+  const int chunks = static_cast<int>((rows + kChunk - 1) / kChunk);
+  float* chunk_sums = a.parts + static_cast<size_t>(rows) * a.head_dim;
+  norm_reduce_chunks<<<chunks, 256, 0, stream>>>(a.parts, rows, a.head_dim, chunk_sums);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  norm_reduce_final<<<1, 256, 0, stream>>>(chunk_sums, chunks, a.head_dim, d_weight);
+  return cudaGetLastError();
+}
+
+}  // namespace pluto

@@ -81,6 +81,35 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+class BlockParameter:
+    """A trainable or frozen fp32 parameter shared between a layer and its optimizer
+    (src/llm/block_parameter.h): `value()`, `active()`, `Activate()` (allocates a zeroed gradient),
+    `gradient()`.  Backward passes ACCUMULATE into the gradient of an active parameter."""
+
+    def __init__(self, value: torch.Tensor):
+        self.value_ = value
+        self.gradient_ = None
+
+    @staticmethod
+    def Create(value: torch.Tensor) -> "BlockParameter":
+        if value is None or value.dtype != torch.float32 or not value.is_cuda:
+            raise _invalid("BlockParameter requires an FP32 device buffer")
+        return BlockParameter(value)
+
+    def value(self) -> torch.Tensor:
+        return self.value_
+
+    def active(self) -> bool:
+        return self.gradient_ is not None
+
+    def Activate(self) -> None:
+        if self.gradient_ is None:
+            self.gradient_ = torch.zeros_like(self.value_)
+
+    def gradient(self) -> Optional[torch.Tensor]:
+        return self.gradient_
+
+
 class Layer:
     """Public fwd/bwd wrappers of src/llm/layer.cc:35-84."""
 
@@ -616,15 +645,20 @@ class QwenAttentionLayer(Layer):
 
     def __init__(self, parameters, q_norm, k_norm, sequence_length, cache):
         self.parameters_ = parameters
-        self.weights_ = [q_norm, k_norm]
+        self.norms_ = [q_norm, k_norm]                       # BlockParameter
+        self.weights_ = [q_norm.value(), k_norm.value()]
         self.sequence_length_ = sequence_length
         self.cache_ = cache
 
     @staticmethod
-    def Create(parameters: FullAttentionParameters, q_norm: torch.Tensor, k_norm: torch.Tensor,
+    def Create(parameters: FullAttentionParameters, q_norm, k_norm,
                sequence_length: int, cache: Optional[KeyValueCache] = None) -> "QwenAttentionLayer":
+        """q_norm / k_norm: a BlockParameter (shared, possibly active) or a raw fp32 tensor (the
+        reference's Buffer overload, qwen_attention.h:42-47: a frozen parameter)."""
         import math
         p = parameters
+        q_norm = q_norm if isinstance(q_norm, BlockParameter) or q_norm is None else BlockParameter(q_norm)
+        k_norm = k_norm if isinstance(k_norm, BlockParameter) or k_norm is None else BlockParameter(k_norm)
         if cache is not None:
             if sequence_length != 1:
                 raise _invalid("cached Qwen attention requires sequence_length == 1")
@@ -642,7 +676,8 @@ class QwenAttentionLayer(Layer):
                     or not math.isfinite(p.rms_norm_epsilon) or not (p.rope_theta > 0)
                     or not math.isfinite(p.rope_theta)):
                 raise _invalid("sequence Qwen attention requires valid GQA dimensions and D<=256")
-        for norm in (q_norm, k_norm):
+        for parameter in (q_norm, k_norm):
+            norm = None if parameter is None else parameter.value()
             if norm is None or norm.dtype != torch.float32 or norm.numel() != p.head_dim or not norm.is_cuda:
                 raise _invalid("Qwen attention norms must be FP32 head-width parameters on its Executor")
         _capi.lib()
@@ -656,6 +691,9 @@ class QwenAttentionLayer(Layer):
 
     def weights(self):
         return self.weights_
+
+    def gradients(self):
+        return [n.gradient() for n in self.norms_ if n.active()]
 
     def input_types(self):
         p, t = self.parameters_, self.sequence_length_
@@ -674,7 +712,7 @@ class QwenAttentionLayer(Layer):
     def bwd_impl(self, output_gradients, state, hooks):
         if self.cache_ is not None:
             raise _unimplemented("QwenAttentionLayer with a KV cache supports inference only")
-        raise _unimplemented("QwenAttentionLayer sequence backward is not built in this engine yet")
+        return self._sequence_backward(output_gradients, state)
 
     def _cached_forward(self, inputs, hooks) -> FwdResult:
         # src/llm/layers/qwen_attention.cc:370-412, minus the bf16<->fp32 cast launches
@@ -716,7 +754,8 @@ class QwenAttentionLayer(Layer):
                                  None, _ptr(q), 1, C_byref(layout), 1, t, hq, hkv, d, p.rotary_dim,
                                  p.rms_norm_epsilon, p.rope_theta, 1))
         qg = inputs[0].view(1, t, hq, 2, d)
-        result = gqa_prefill(q, k, v, gate=qg[:, :, :, 1], round_to_bfloat16=True, want_core=True)
+        result = gqa_prefill(q, k, v, gate=qg[:, :, :, 1], round_to_bfloat16=True, want_core=True,
+                             want_stats=True)
         output = result["out"].view(t, hq * d)
         probabilities = torch.empty((0,), dtype=torch.float32, device=device)
         if hooks is not None and hooks.attention_probabilities_hook is not None:
@@ -728,9 +767,54 @@ class QwenAttentionLayer(Layer):
                                            _ptr(probabilities), t, t * t, t, hq, hkv, d))
             hooks.attention_probabilities_hook(
                 self.name(), ActivationType(DataType.FP32, (1, hq, t, t)), probabilities)
+        # the reference's seven saved buffers (its probabilities are empty here unless a hook asked
+        # for them) plus what replaces them for backward: the softmax statistics and the value rows
         state = BackwardState(intermediates=[inputs[0], inputs[1], inputs[2], q, k, probabilities,
-                                             result["core"]])
+                                             result["core"], result["maxima"],
+                                             result["normalizers"], v])
         return FwdResult([output], state)
+
+    def _sequence_backward(self, output_gradients, state):
+        # src/llm/layers/qwen_attention.cc:450-499: gate -> attention core -> RoPE^-1 + RMSNorm
+        p, t = self.parameters_, self.sequence_length_
+        hq, hkv, d = p.query_heads, p.key_value_heads, p.head_dim
+        if len(state.intermediates) != 10:
+            raise _invalid("sequence attention backward Executor/state mismatch")
+        if len(output_gradients) != 1:
+            raise _invalid("sequence attention received an unexpected number of buffers")
+        dy = output_gradients[0]
+        if dy is None or not dy.is_cuda or dy.dtype != torch.float32 or dy.numel() != t * hq * d:
+            raise _invalid("sequence attention buffer has an invalid size or Executor")
+        qg_in, k_in, _, q, k, _, core, maxima, normalizers, v = state.intermediates
+        L = _capi.lib()
+        device = dy.device
+        f32 = dict(dtype=torch.float32, device=device)
+        dqg = torch.empty((t, hq, 2, d), **f32)
+        dk = torch.empty((t, hkv, d), **f32)
+        dv = torch.empty((t, hkv, d), **f32)
+        dq_rope = torch.empty((t, hq, d), **f32)
+        dk_rope = torch.empty((t, hkv, d), **f32)
+        dc = torch.empty((t, hq, d), **f32)
+        deltas = torch.empty((hq * t,), **f32)
+        check(L.pluto_gqa_gate_bwd(_stream(), qg_in.data_ptr() + 2 * d, 2 * hq * d, 2 * d, _ptr(core),
+                                   _ptr(dy), _ptr(dc), dqg.data_ptr() + 4 * d, 2 * hq * d, 2 * d,
+                                   _ptr(deltas), 1, t, hq, d, int(p.round_to_bfloat16)))
+        check(L.pluto_gqa_prefill_bwd(_stream(), _ptr(q), _ptr(k), _ptr(v), 1, hq * d, d, _ptr(dc),
+                                      _ptr(maxima), _ptr(normalizers), _ptr(deltas), _ptr(dq_rope),
+                                      _ptr(dk_rope), _ptr(dv), 1, t, hq, hkv, d))
+        for x, x_token, x_head, norm, grad, dx, heads in (
+                (qg_in, 2 * hq * d, 2 * d, self.norms_[0], dq_rope, dqg, hq),
+                (k_in, hkv * d, d, self.norms_[1], dk_rope, dk, hkv)):
+            workspace, size = None, 0
+            if norm.active():
+                size = L.pluto_qk_prepare_bwd_workspace_bytes(1, t, heads, d)
+                workspace = torch.empty((size,), dtype=torch.uint8, device=device)
+            check(L.pluto_qk_prepare_bwd(_stream(), _ptr(x), x_token, x_head, _ptr(norm.value()),
+                                         _ptr(grad), None, _ptr(dx), x_token, x_head,
+                                         _ptr(norm.gradient()), _ptr(workspace), size, 1, t, heads, d,
+                                         p.rotary_dim, p.rms_norm_epsilon, p.rope_theta,
+                                         int(p.round_to_bfloat16)))
+        return [dqg, dk, dv]
 
 
 class DeltaNetLayer(Layer):
