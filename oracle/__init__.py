@@ -287,3 +287,25 @@ def gdn_output(core, z, norm_weight, eps, rnd, final_round=True):
     lib().oracle_gdn_output(_p(core), _p(z), _p(norm_weight), heads, dim, C.c_float(eps), int(rnd),
                             int(final_round), _p(out))
     return out
+
+
+def gdn_sequence_bwd(qkv, z, a, b, conv_w, a_log, dt_bias, norm, dy, kh, vh, kd, vd, eps, rnd=True,
+                     d_conv=None, d_a_log=None, d_dt_bias=None, d_norm=None):
+    """SequenceDeltaNetLayer forward + backward (sequence_delta_net.cc:31-339, 482-561) for one
+    sequence; fp32 arrays qkv [T,channels], z [T,vh*vd], a,b [T,vh], conv_w [channels,kernel],
+    dy [T,vh*vd].  The d_* arrays (fp32) are accumulated into when given.  Returns dqkv, dz, da,
+    db and the forward output y (before its bf16 store)."""
+    f = lambda x: np.ascontiguousarray(x, np.float32)
+    qkv, z, a, b, conv_w, dy = f(qkv), f(z), f(a), f(b), f(conv_w), f(dy)
+    t, channels = qkv.shape
+    kernel = conv_w.shape[1]
+    dqkv, dz = np.zeros_like(qkv), np.zeros_like(z)
+    da, db = np.zeros_like(a), np.zeros_like(b)
+    y = np.zeros_like(z)
+    rc = lib().oracle_gdn_sequence_bwd(
+        _p(qkv), _p(z), _p(a), _p(b), _p(conv_w), _p(f(a_log)), _p(f(dt_bias)), _p(f(norm)), _p(dy),
+        t, kh, vh, kd, vd, kernel, C.c_float(eps), int(rnd), _p(dqkv), _p(dz), _p(da), _p(db),
+        _p(d_conv), _p(d_a_log), _p(d_dt_bias), _p(d_norm), _p(y))
+    if rc != 0:
+        raise MemoryError("oracle_gdn_sequence_bwd scratch allocation failed")
+    return {"dqkv": dqkv, "dz": dz, "da": da, "db": db, "y": y}

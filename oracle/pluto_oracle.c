@@ -717,3 +717,258 @@ void oracle_gdn_output(const float* core, const float* z, const float* norm_weig
     }
   }
 }
+
+/* SequenceDeltaNetLayer forward + backward for one sequence, sequence_delta_net.cc:31-121
+ * (ConvForward, RecurrenceForward, OutputForward) and :126-339 with the host order of :482-561
+ * (OutputBackward, SumNormGradient, RecurrenceBackward, GatherQkGradient, GatherScalarGradient,
+ * ConvSiluBackward, ConvInputBackward, ConvWeightBackward).  All arrays fp32 (bf16 inputs hold
+ * bf16-exact values): qkv [T,channels] with channels = 2*kh*kd + vh*vd laid out all-Q, all-K,
+ * all-V; z [T,vh*vd]; a, b [T,vh]; conv_w [channels,kernel] oldest tap first; a_log, dt_bias
+ * [vh]; norm [vd]; dy [T,vh*vd].  Outputs dqkv, dz, da, db; the four parameter gradients are
+ * ACCUMULATED into (NULL = frozen).  y_out (optional) receives the forward output (the final
+ * product is left unrounded, as OutputForward's bf16 store is the only rounding there).
+ * Stores every intermediate state like the reference, so it is for short sequences. */
+int oracle_gdn_sequence_bwd(const float* qkv, const float* z, const float* a, const float* b,
+                            const float* conv_w, const float* a_log, const float* dt_bias,
+                            const float* norm, const float* dy, int T, int kh, int vh, int kd,
+                            int vd, int kernel, float epsilon, int round, float* dqkv, float* dz,
+                            float* da, float* db, float* d_conv, float* d_a_log, float* d_dt_bias,
+                            float* d_norm, float* y_out) {
+  const int channels = 2 * kh * kd + vh * vd, width = vh * vd, tiles = (vd + 31) / 32;
+  const size_t stride = (size_t)vh * kd * vd;
+  float* pre = (float*)malloc((size_t)T * channels * sizeof(float));
+  float* post = (float*)malloc((size_t)T * channels * sizeof(float));
+  float* core = (float*)malloc((size_t)T * width * sizeof(float));
+  float* states = (float*)calloc((size_t)(T + 1) * stride, sizeof(float));
+  float* dcore = (float*)malloc((size_t)T * width * sizeof(float));
+  float* dpost = (float*)calloc((size_t)T * channels, sizeof(float));
+  float* dpre = (float*)malloc((size_t)T * channels * sizeof(float));
+  float* qk = (float*)calloc((size_t)T * vh * tiles * 2 * kd, sizeof(float));
+  float* scalars = (float*)calloc((size_t)T * vh * tiles * 3, sizeof(float));
+  float* parts = (float*)malloc((size_t)T * width * sizeof(float));
+  if (!pre || !post || !core || !states || !dcore || !dpost || !dpre || !qk || !scalars || !parts) {
+    free(pre); free(post); free(core); free(states); free(dcore); free(dpost); free(dpre);
+    free(qk); free(scalars); free(parts);
+    return -1;
+  }
+  const float norm_scale = sqrtf((float)kd);
+  /* ConvForward */
+  for (int t = 0; t < T; ++t)
+    for (int c = 0; c < channels; ++c) {
+      float sum = 0.0f;
+      for (int tap = 0; tap < kernel; ++tap) {
+        const int source = t + tap - kernel + 1;
+        if (source >= 0) sum += qkv[(size_t)source * channels + c] * conv_w[(size_t)c * kernel + tap];
+      }
+      sum = rnd(sum, round);
+      pre[(size_t)t * channels + c] = sum;
+      post[(size_t)t * channels + c] = rnd(sum / (1.0f + expf(-sum)), round);
+    }
+  /* RecurrenceForward: per (head, 32-column tile), every S_t saved */
+  for (int head = 0; head < vh; ++head)
+    for (int tile = 0; tile < tiles; ++tile) {
+      const int key_head = head / (vh / kh);
+      const int c0 = tile * 32, c1 = c0 + 32 < vd ? c0 + 32 : vd;
+      for (int t = 0; t < T; ++t) {
+        const float* row = post + (size_t)t * channels;
+        float q[128], k[128], sq = 0.0f, sk = 0.0f;
+        for (int i = 0; i < kd; ++i) {
+          q[i] = row[key_head * kd + i];
+          k[i] = row[(kh + key_head) * kd + i];
+          sq += q[i] * q[i];
+          sk += k[i] * k[i];
+        }
+        const float iq = 1.0f / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+        for (int i = 0; i < kd; ++i) { q[i] = q[i] * iq / norm_scale; k[i] = k[i] * ik; }
+        const float decay = oracle_gdn_decay(a[(size_t)t * vh + head], dt_bias[head], a_log[head]);
+        const float beta = oracle_gdn_beta(b[(size_t)t * vh + head], round);
+        const float* prev = states + (size_t)t * stride + (size_t)head * kd * vd;
+        float* next = states + (size_t)(t + 1) * stride + (size_t)head * kd * vd;
+        for (int c = c0; c < c1; ++c) {
+          float prediction = 0.0f;
+          for (int i = 0; i < kd; ++i) {
+            next[(size_t)i * vd + c] = prev[(size_t)i * vd + c] * decay;
+            prediction += next[(size_t)i * vd + c] * k[i];
+          }
+          const float delta = (row[2 * kh * kd + head * vd + c] - prediction) * beta;
+          float out = 0.0f;
+          for (int i = 0; i < kd; ++i) {
+            next[(size_t)i * vd + c] += k[i] * delta;
+            out += next[(size_t)i * vd + c] * q[i];
+          }
+          core[((size_t)t * vh + head) * vd + c] = rnd(out, round);
+        }
+      }
+    }
+  /* OutputForward (optional) and OutputBackward */
+  for (int r = 0; r < T * vh; ++r) {
+    const float* x = core + (size_t)r * vd;
+    float square = 0.0f;
+    for (int c = 0; c < vd; ++c) square += x[c] * x[c];
+    const float inverse = 1.0f / sqrtf(square / (float)vd + epsilon);
+    float dot = 0.0f;
+    for (int c = 0; c < vd; ++c) {
+      const float gate = z[(size_t)r * vd + c], sigmoid = 1.0f / (1.0f + expf(-gate));
+      dot += dy[(size_t)r * vd + c] * gate * sigmoid * norm[c] * x[c];
+    }
+    for (int c = 0; c < vd; ++c) {
+      const size_t i = (size_t)r * vd + c;
+      const float normalized = rnd(x[c] * inverse, round);
+      const float affine = rnd(normalized * norm[c], round);
+      const float gate = z[i], sigmoid = 1.0f / (1.0f + expf(-gate));
+      if (y_out) y_out[i] = affine * gate / (1.0f + expf(-gate));
+      const float dn = dy[i] * gate * sigmoid * norm[c];
+      dcore[i] = inverse * dn - x[c] * inverse * inverse * inverse / (float)vd * dot;
+      dz[i] = dy[i] * affine * sigmoid * (1.0f + gate * (1.0f - sigmoid));
+      parts[i] = dy[i] * gate * sigmoid * normalized;
+    }
+  }
+  if (d_norm)   /* SumNormGradient */
+    for (int c = 0; c < vd; ++c) {
+      float sum = 0.0f;
+      for (int r = 0; r < T * vh; ++r) sum += parts[(size_t)r * vd + c];
+      d_norm[c] += sum;
+    }
+  /* RecurrenceBackward */
+  float* dm = (float*)malloc((size_t)kd * 32 * sizeof(float));
+  if (!dm) return -1;
+  for (int head = 0; head < vh; ++head)
+    for (int tile = 0; tile < tiles; ++tile) {
+      const int key_head = head / (vh / kh);
+      const int c0 = tile * 32, c1 = c0 + 32 < vd ? c0 + 32 : vd, nc = c1 - c0;
+      for (int i = 0; i < kd * 32; ++i) dm[i] = 0.0f;
+      for (int t = T - 1; t >= 0; --t) {
+        const float* row = post + (size_t)t * channels;
+        float raw_q[128], raw_k[128], q[128], k[128], sq = 0.0f, sk = 0.0f;
+        for (int i = 0; i < kd; ++i) {
+          raw_q[i] = row[key_head * kd + i];
+          raw_k[i] = row[(kh + key_head) * kd + i];
+          sq += raw_q[i] * raw_q[i];
+          sk += raw_k[i] * raw_k[i];
+        }
+        const float iq = 1.0f / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+        for (int i = 0; i < kd; ++i) { q[i] = raw_q[i] * iq / norm_scale; k[i] = raw_k[i] * ik; }
+        const float alpha = a[(size_t)t * vh + head] + dt_bias[head];
+        const float softplus = fmaxf(alpha, 0.0f) + logf(1.0f + expf(-fabsf(alpha)));
+        const float rate = expf(a_log[head]);
+        const float decay = expf(-rate * softplus);
+        const float sigmoid = 1.0f / (1.0f + expf(-b[(size_t)t * vh + head]));
+        const float beta = rnd(sigmoid, round);
+        const float* prev = states + (size_t)t * stride + (size_t)head * kd * vd;
+        const float* matrix = states + (size_t)(t + 1) * stride + (size_t)head * kd * vd;
+        float dq[128], dk[128], difference[32], delta[32], ddelta[32], dv[32];
+        for (int j = 0; j < nc; ++j) {
+          float prediction = 0.0f;
+          for (int i = 0; i < kd; ++i) prediction += prev[(size_t)i * vd + c0 + j] * decay * k[i];
+          difference[j] = row[2 * kh * kd + head * vd + c0 + j] - prediction;
+          delta[j] = difference[j] * beta;
+        }
+        for (int i = 0; i < kd; ++i) {
+          float s = 0.0f;
+          for (int j = 0; j < nc; ++j)
+            s += matrix[(size_t)i * vd + c0 + j] * dcore[((size_t)t * vh + head) * vd + c0 + j];
+          dq[i] = s;
+          for (int j = 0; j < nc; ++j)
+            dm[i * 32 + j] += q[i] * dcore[((size_t)t * vh + head) * vd + c0 + j];
+        }
+        float dbeta_sum = 0.0f;
+        for (int j = 0; j < nc; ++j) {
+          float s = 0.0f;
+          for (int i = 0; i < kd; ++i) s += dm[i * 32 + j] * k[i];
+          ddelta[j] = s;
+          dv[j] = s * beta;
+          dbeta_sum += s * difference[j];
+        }
+        float dg = 0.0f;
+        for (int i = 0; i < kd; ++i) {
+          float s = 0.0f;
+          for (int j = 0; j < nc; ++j) {
+            const float decayed = prev[(size_t)i * vd + c0 + j] * decay;
+            s += dm[i * 32 + j] * delta[j] - decayed * dv[j];
+          }
+          dk[i] = s;
+        }
+        /* ddecayed = dm - k dv; dg = sum(ddecayed * previous); dm <- ddecayed * decay */
+        float dg_cols[32];
+        for (int j = 0; j < nc; ++j) dg_cols[j] = 0.0f;
+        for (int i = 0; i < kd; ++i)
+          for (int j = 0; j < nc; ++j) {
+            const float ddecayed = dm[i * 32 + j] - k[i] * dv[j];
+            dg_cols[j] += ddecayed * prev[(size_t)i * vd + c0 + j];
+            dm[i * 32 + j] = ddecayed * decay;
+          }
+        for (int j = 0; j < nc; ++j) dg += dg_cols[j];
+        const size_t partial = ((size_t)t * vh + head) * tiles + tile;
+        scalars[partial * 3 + 0] = -dg * decay * rate / (1.0f + expf(-alpha));
+        scalars[partial * 3 + 1] = dbeta_sum * sigmoid * (1.0f - sigmoid);
+        scalars[partial * 3 + 2] = -dg * decay * rate * softplus;
+        float dot_q = 0.0f, dot_k = 0.0f;
+        for (int i = 0; i < kd; ++i) { dot_q += dq[i] * raw_q[i]; dot_k += dk[i] * raw_k[i]; }
+        for (int i = 0; i < kd; ++i) {
+          qk[partial * 2 * kd + i] = (dq[i] * iq - raw_q[i] * iq * iq * iq * dot_q) / norm_scale;
+          qk[partial * 2 * kd + kd + i] = dk[i] * ik - raw_k[i] * ik * ik * ik * dot_k;
+        }
+        for (int j = 0; j < nc; ++j)
+          dpost[(size_t)t * channels + 2 * kh * kd + head * vd + c0 + j] = dv[j];
+      }
+    }
+  free(dm);
+  /* GatherQkGradient */
+  for (int t = 0; t < T; ++t)
+    for (int key_head = 0; key_head < kh; ++key_head) {
+      const int group = vh / kh;
+      for (int i = 0; i < kd; ++i) {
+        float sq = 0.0f, sk = 0.0f;
+        for (int h = key_head * group; h < (key_head + 1) * group; ++h)
+          for (int tile = 0; tile < tiles; ++tile) {
+            const size_t partial = (((size_t)t * vh + h) * tiles + tile) * 2 * kd;
+            sq += qk[partial + i];
+            sk += qk[partial + kd + i];
+          }
+        dpost[(size_t)t * channels + key_head * kd + i] = sq;
+        dpost[(size_t)t * channels + (kh + key_head) * kd + i] = sk;
+      }
+    }
+  /* GatherScalarGradient */
+  for (int head = 0; head < vh; ++head) {
+    float sum_log = 0.0f, sum_a = 0.0f;
+    for (int t = 0; t < T; ++t) {
+      float ga = 0.0f, gb = 0.0f, gl = 0.0f;
+      for (int tile = 0; tile < tiles; ++tile) {
+        const size_t index = (((size_t)t * vh + head) * tiles + tile) * 3;
+        ga += scalars[index]; gb += scalars[index + 1]; gl += scalars[index + 2];
+      }
+      da[(size_t)t * vh + head] = ga;
+      db[(size_t)t * vh + head] = gb;
+      sum_log += gl;
+      sum_a += ga;
+    }
+    if (d_a_log) d_a_log[head] += sum_log;
+    if (d_dt_bias) d_dt_bias[head] += sum_a;
+  }
+  /* ConvSiluBackward, ConvInputBackward, ConvWeightBackward */
+  for (size_t i = 0; i < (size_t)T * channels; ++i) {
+    const float x = pre[i], sigmoid = 1.0f / (1.0f + expf(-x));
+    dpre[i] = dpost[i] * sigmoid * (1.0f + x * (1.0f - sigmoid));
+  }
+  for (int t = 0; t < T; ++t)
+    for (int c = 0; c < channels; ++c) {
+      float sum = 0.0f;
+      for (int tap = 0; tap < kernel; ++tap) {
+        const int future = t + kernel - 1 - tap;
+        if (future < T) sum += dpre[(size_t)future * channels + c] * conv_w[(size_t)c * kernel + tap];
+      }
+      dqkv[(size_t)t * channels + c] = sum;
+    }
+  if (d_conv)
+    for (int c = 0; c < channels; ++c)
+      for (int tap = 0; tap < kernel; ++tap) {
+        float sum = 0.0f;
+        for (int t = kernel - 1 - tap; t < T; ++t)
+          sum += dpre[(size_t)t * channels + c] * qkv[(size_t)(t + tap - kernel + 1) * channels + c];
+        d_conv[(size_t)c * kernel + tap] += sum;
+      }
+  free(pre); free(post); free(core); free(states); free(dcore); free(dpost); free(dpre);
+  free(qk); free(scalars); free(parts);
+  return 0;
+}
