@@ -31,6 +31,7 @@ def test_all_gradients_match_numerical_bptt(shape, rnd, tol):
     eps = 0.03
     values, upstream = make_example(length, kh, vh, kd, vd)
     actual, got = run_oracle(values, upstream, length, kh, vh, kd, vd, eps, rnd)
+    upstream = [float(u) for u in upstream]   # python floats: the differences need double precision
     model = DoubleModel(length, kh, vh, kd, vd, 3, eps, rnd)
     if shape[-1] == 35:   # the large example: check a strided sample of coordinates per tensor
         expected = None
@@ -47,7 +48,7 @@ def test_all_gradients_match_numerical_bptt(shape, rnd, tol):
                 e = (plus - minus) / 2e-5
                 assert abs(actual[tensor][i] - e) <= tol[0] + abs(e) * tol[1], (NAMES[tensor], i)
     else:
-        expected = model.gradients(values, list(upstream))
+        expected = model.gradients(values, upstream)
         for name, a, e in zip(NAMES, actual, expected):
             assert np.all(np.abs(a - e) <= tol[0] + np.abs(e) * tol[1]), (name, np.abs(a - e).max())
     # the loss sits at the last token only: the first token must still receive a gradient

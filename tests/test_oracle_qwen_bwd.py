@@ -16,7 +16,7 @@ def test_backward_matches_finite_differences_of_double_model(rnd):
     values = [wave(t * 12, .1), wave(t * 3, 1.2), wave(t * 3, 2.3), wave(3, .2), wave(3, .4)]
     upstream = wave(t * 6, .7)
     model = DoubleModel(t, hq, hkv, d, rotary, eps, theta, rnd)
-    expected = model.gradients(values, list(upstream))
+    expected = model.gradients(values, [float(u) for u in upstream])
     dqw, dkw = np.zeros(d, np.float32), np.zeros(d, np.float32)
     got = oracle.gqa_sequence_bwd(values[0].reshape(t, hq, 2, d), values[1].reshape(t, hkv, d),
                                   values[2].reshape(t, hkv, d), values[3], values[4],

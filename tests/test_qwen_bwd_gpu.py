@@ -55,7 +55,7 @@ def test_backward_matches_independent_finite_difference():
     _, grads = run(layer, values[0].reshape(t, hq, 2, d), values[1].reshape(t, hkv, d),
                    values[2].reshape(t, hkv, d), upstream.reshape(t, hq, d))
     model = DoubleModel(t, hq, hkv, d, rotary, p.rms_norm_epsilon, p.rope_theta, True)
-    expected = model.gradients(values, list(upstream))
+    expected = model.gradients(values, [float(u) for u in upstream])
     actual = [grads[0].ravel(), grads[1].ravel(), grads[2].ravel(),
               qw.gradient().cpu().numpy(), kw.gradient().cpu().numpy()]
     for name, a, e in zip(["dqg", "dk", "dv", "dq_norm", "dk_norm"], actual, expected):
