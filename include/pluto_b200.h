@@ -333,6 +333,49 @@ int pluto_gdn_out_norm_gate(pluto_stream_t stream, const void* core, int core_dt
                             int out_dtype);
 
 /* --------------------------------------------------------------------------------------------
+ * Backward of the sequence gated delta-net, SequenceDeltaNetLayer::bwd_impl
+ * (src/llm/layers/sequence_delta_net.cc:482-561), in the reference's three stages.  The
+ * reference stores every intermediate state S_t and is limited to 128 tokens; the recurrence
+ * pass here keeps one state per 64 tokens and recomputes inside a chunk, so any length runs.
+ * Parameter gradients (d_norm_weight, d_a_log, d_dt_bias, d_weight; all optional) are
+ * ACCUMULATED into, as the reference accumulates into BlockParameter::gradient().
+ *
+ * 1. pluto_gdn_out_norm_gate_bwd: OutputBackward + SumNormGradient (:126-171).  core (the rounded
+ *    recurrence output saved by the forward, bf16 or fp32) and z are [rows, dim]; dy, dcore, dz
+ *    fp32 [rows, dim]; rows = batch * tokens * value_heads.  The workspace is needed only with
+ *    d_norm_weight.
+ * 2. pluto_gdn_recurrence_bwd: RecurrenceBackward + GatherQkGradient + GatherScalarGradient
+ *    (:176-309).  q, k, v are the convolved, SiLU'd activations (raw: the L2 normalisation of q
+ *    and k and the 1/sqrt(key_dim) query scale are part of this stage and are differentiated
+ *    here), addressed as in pluto_gdn_prefill; a, b the raw gate inputs [batch, tokens,
+ *    value_heads]; dcore from stage 1.  dq, dk (token stride dqk_token_stride) and dv (token
+ *    stride dv_token_stride) are fp32 and normally point into one [batch, tokens, channels]
+ *    gradient of the convolved activations; da, db fp32 [batch, tokens, value_heads].
+ *    key_dim <= 128, value_dim <= 256.
+ * 3. pluto_gdn_conv_silu_bwd: ConvSiluBackward + ConvInputBackward + ConvWeightBackward
+ *    (:311-362) for sequences that start from an empty history.  input is the layer's QKV input
+ *    [batch, tokens, channels]; d_post the gradient of the convolved activations; dx fp32. */
+int pluto_gdn_out_norm_gate_bwd(pluto_stream_t stream, const void* core, int core_dtype,
+                                const void* z, int z_dtype, const float* norm_weight,
+                                const float* dy, float* dcore, float* dz, float* d_norm_weight,
+                                void* workspace, size_t workspace_bytes, long long rows, int dim,
+                                float rms_norm_epsilon, int round_to_bf16);
+size_t pluto_gdn_out_norm_gate_bwd_workspace_bytes(long long rows, int dim);
+size_t pluto_gdn_recurrence_bwd_workspace_bytes(int batch, int tokens, int key_heads, int value_heads,
+                                                int key_dim, int value_dim);
+int pluto_gdn_recurrence_bwd(pluto_stream_t stream, const void* q, const void* k, const void* v,
+                             int in_dtype, size_t qk_token_stride, size_t v_token_stride,
+                             const void* a, const void* b, int ab_dtype, const float* a_log,
+                             const float* dt_bias, const float* dcore, float* dq, float* dk,
+                             size_t dqk_token_stride, float* dv, size_t dv_token_stride, float* da,
+                             float* db, float* d_a_log, float* d_dt_bias, void* workspace,
+                             size_t workspace_bytes, int batch, int tokens, int key_heads,
+                             int value_heads, int key_dim, int value_dim, int round_to_bf16);
+int pluto_gdn_conv_silu_bwd(pluto_stream_t stream, const void* input, int in_dtype,
+                            const float* weight, const float* d_post, float* dx, float* d_weight,
+                            int batch, int tokens, int channels, int width, int round_to_bf16);
+
+/* --------------------------------------------------------------------------------------------
  * Head-sharded multi-GPU support.  The reference is single-GPU (its only cudaSetDevice pins a
  * thread pool to one device, src/cuda/thread_pool.h:19-22, src/cuda/thread_pool.cc:109), so this
  * has no kernel to mirror: it is the local half of "all-gather the head-sharded output" for a

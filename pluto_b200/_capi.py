@@ -39,6 +39,12 @@ _SIGNATURES = {
     "pluto_qk_prepare_bwd_workspace_bytes": (_sz, [_i] * 4),
     "pluto_qk_prepare_bwd": (_i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _sz]
                              + [_i] * 5 + [_fp, _fp, _i]),
+    "pluto_gdn_out_norm_gate_bwd": (_i, [_vp, _vp, _i, _vp, _i] + [_vp] * 6 + [_sz, C.c_longlong, _i, _fp, _i]),
+    "pluto_gdn_out_norm_gate_bwd_workspace_bytes": (_sz, [C.c_longlong, _i]),
+    "pluto_gdn_recurrence_bwd_workspace_bytes": (_sz, [_i] * 6),
+    "pluto_gdn_recurrence_bwd": (_i, [_vp] * 4 + [_i, _sz, _sz, _vp, _vp, _i] + [_vp] * 5 + [_sz, _vp, _sz]
+                                 + [_vp] * 5 + [_sz] + [_i] * 7),
+    "pluto_gdn_conv_silu_bwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp] + [_i] * 5),
     "pluto_qk_prepare": (_i, [_vp] * 4 + [_i, _sz, _sz] + [_vp] * 4 + [_i, _vp] + [_i] * 6
                          + [_fp, _fp, _i]),
     "pluto_gqa_decode_workspace_bytes": (_sz, [_i] * 5),

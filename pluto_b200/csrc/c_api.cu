@@ -525,6 +525,87 @@ int pluto_gdn_out_norm_gate(pluto_stream_t stream, const void* core, int core_dt
                    "Qwen gated delta output norm");
 }
 
+int pluto_gdn_out_norm_gate_bwd(pluto_stream_t stream, const void* core, int core_dtype,
+                                const void* z, int z_dtype, const float* norm_weight,
+                                const float* dy, float* dcore, float* dz, float* d_norm_weight,
+                                void* workspace, size_t workspace_bytes, long long rows, int dim,
+                                float rms_norm_epsilon, int round_to_bf16) {
+  if (rows <= 0 || rows > 0x7fffffffLL || dim <= 0 || dim > 256 || !(rms_norm_epsilon > 0.0f) ||
+      !std::isfinite(rms_norm_epsilon) || !dtype_ok(core_dtype) || !dtype_ok(z_dtype))
+    return fail(PLUTO_E_INVALID, "unsupported SequenceDeltaNetLayer shape");
+  if (!core || !z || !norm_weight || !dy || !dcore || !dz)
+    return fail(PLUTO_E_INVALID, "invalid DeltaNet backward state or gradient");
+  if (d_norm_weight != nullptr &&
+      (workspace == nullptr || workspace_bytes < pluto_gdn_out_norm_gate_bwd_workspace_bytes(rows, dim)))
+    return fail(PLUTO_E_INVALID, "norm-weight gradient requires its workspace");
+  float* parts = d_norm_weight ? static_cast<float*>(workspace) : nullptr;
+  int rc = from_cuda(pluto::gdn_out_bwd(stream, core, core_dtype == PLUTO_BF16, z, z_dtype == PLUTO_BF16,
+                                        norm_weight, dy, rows, dim, rms_norm_epsilon, round_to_bf16,
+                                        dcore, dz, parts),
+                     "sequence DeltaNet backward (output)");
+  if (rc != PLUTO_OK || !d_norm_weight) return rc;
+  return from_cuda(pluto::reduce_rows_accumulate(stream, parts, rows, dim,
+                                                 parts + static_cast<size_t>(rows) * dim, d_norm_weight),
+                   "sequence DeltaNet backward (norm gradient)");
+}
+
+size_t pluto_gdn_out_norm_gate_bwd_workspace_bytes(long long rows, int dim) {
+  if (rows <= 0 || dim <= 0) return 0;
+  return (static_cast<size_t>(rows) * dim + pluto::reduce_rows_scratch_floats(rows, dim)) * sizeof(float);
+}
+
+size_t pluto_gdn_recurrence_bwd_workspace_bytes(int batch, int tokens, int key_heads, int value_heads,
+                                                int key_dim, int value_dim) {
+  if (batch <= 0 || tokens <= 0 || key_heads <= 0 || value_heads <= 0 || key_dim <= 0 || value_dim <= 0)
+    return 0;
+  return pluto::gdn_recurrence_bwd_workspace_bytes(batch, tokens, value_heads, key_dim, value_dim);
+}
+
+int pluto_gdn_recurrence_bwd(pluto_stream_t stream, const void* q, const void* k, const void* v,
+                             int in_dtype, size_t qk_token_stride, size_t v_token_stride,
+                             const void* a, const void* b, int ab_dtype, const float* a_log,
+                             const float* dt_bias, const float* dcore, float* dq, float* dk,
+                             size_t dqk_token_stride, float* dv, size_t dv_token_stride, float* da,
+                             float* db, float* d_a_log, float* d_dt_bias, void* workspace,
+                             size_t workspace_bytes, int batch, int tokens, int key_heads,
+                             int value_heads, int key_dim, int value_dim, int round_to_bf16) {
+  if (batch <= 0 || tokens <= 0 || key_heads <= 0 || value_heads <= 0 || key_dim <= 0 ||
+      key_dim > 128 || value_dim <= 0 || value_dim > 256 || value_heads % key_heads != 0 ||
+      batch > 65535 || value_heads > 65535 || !dtype_ok(in_dtype) || !dtype_ok(ab_dtype))
+    return fail(PLUTO_E_INVALID, "unsupported SequenceDeltaNetLayer shape");
+  if (!q || !k || !v || !a || !b || !a_log || !dt_bias || !dcore || !dq || !dk || !dv || !da || !db)
+    return fail(PLUTO_E_INVALID, "invalid DeltaNet backward state or gradient");
+  if (!workspace || workspace_bytes < pluto_gdn_recurrence_bwd_workspace_bytes(
+                                          batch, tokens, key_heads, value_heads, key_dim, value_dim))
+    return fail(PLUTO_E_INVALID, "DeltaNet backward workspace is too small");
+  pluto::GdnBwdArgs args{};
+  args.q = q; args.k = k; args.v = v;
+  args.in_is_bf16 = in_dtype == PLUTO_BF16;
+  args.qk_token = qk_token_stride; args.v_token = v_token_stride;
+  args.a_in = a; args.b_in = b; args.ab_is_bf16 = ab_dtype == PLUTO_BF16;
+  args.a_log = a_log; args.dt_bias = dt_bias; args.dcore = dcore;
+  args.dv_out = dv; args.dv_token = dv_token_stride;
+  args.batch = batch; args.tokens = tokens; args.key_heads = key_heads; args.value_heads = value_heads;
+  args.key_dim = key_dim; args.value_dim = value_dim; args.round = round_to_bf16;
+  return from_cuda(pluto::gdn_recurrence_bwd(stream, args, dq, dk, dqk_token_stride, da, db, d_a_log,
+                                             d_dt_bias, workspace),
+                   "sequence DeltaNet backward (recurrence)");
+}
+
+int pluto_gdn_conv_silu_bwd(pluto_stream_t stream, const void* input, int in_dtype,
+                            const float* weight, const float* d_post, float* dx, float* d_weight,
+                            int batch, int tokens, int channels, int width, int round_to_bf16) {
+  if (batch <= 0 || batch > 65535 || tokens <= 0 || channels <= 0 || width < 1 || width > 32 ||
+      !dtype_ok(in_dtype) ||
+      static_cast<long long>((channels + 127) / 128) * tokens > 0x7fffffffLL)
+    return fail(PLUTO_E_INVALID, "unsupported SequenceDeltaNetLayer shape");
+  if (!input || !weight || !d_post || !dx)
+    return fail(PLUTO_E_INVALID, "invalid DeltaNet backward state or gradient");
+  return from_cuda(pluto::gdn_conv_bwd(stream, input, in_dtype == PLUTO_BF16, weight, d_post, batch,
+                                       tokens, channels, width, round_to_bf16, dx, d_weight),
+                   "sequence DeltaNet backward (convolution)");
+}
+
 }  // extern "C"
 
 extern "C" int pluto_interleave_heads(pluto_stream_t stream, const void* gathered, void* out,

@@ -189,6 +189,40 @@ cudaError_t gdn_recurrent(cudaStream_t stream, const GdnArgs& args);
 bool gdn_chunked_supported(const GdnArgs& args);
 size_t gdn_chunked_workspace_bytes(int batch, int tokens, int value_heads, int value_dim);
 cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& args, void* workspace, uint32_t* status);
+// gdn_bwd.cu: backward of the sequence layer
+struct GdnBwdArgs {
+  const void* q;            // convolved + SiLU'd activations, as GdnArgs (raw, not normalised)
+  const void* k;
+  const void* v;
+  int in_is_bf16;
+  size_t qk_token, v_token;
+  const void* a_in;         // raw a, b inputs [batch, tokens, value_heads]
+  const void* b_in;
+  int ab_is_bf16;
+  const float* a_log;       // [value_heads]
+  const float* dt_bias;
+  const float* dcore;       // [batch, tokens, value_heads, value_dim] fp32
+  float* dv_out;            // gradient of v, element stride dv_token between tokens
+  size_t dv_token;
+  float *checkpoints, *scratch, *qk_partials, *scalar_partials;   // set by gdn_recurrence_bwd
+  int batch, tokens, key_heads, value_heads, key_dim, value_dim, round;
+};
+cudaError_t gdn_out_bwd(cudaStream_t stream, const void* core, int core_is_bf16, const void* z,
+                        int z_is_bf16, const float* norm, const float* dy, long long rows, int dim,
+                        float epsilon, int round, float* dcore, float* dz, float* parts);
+size_t gdn_recurrence_bwd_workspace_bytes(int batch, int tokens, int value_heads, int key_dim,
+                                          int value_dim);
+cudaError_t gdn_recurrence_bwd(cudaStream_t stream, GdnBwdArgs args, float* dq_out, float* dk_out,
+                               size_t dqk_token, float* da, float* db, float* d_a_log,
+                               float* d_dt_bias, void* workspace);
+cudaError_t gdn_conv_bwd(cudaStream_t stream, const void* input, int in_is_bf16, const float* weight,
+                         const float* dpost, int batch, int tokens, int channels, int width, int round,
+                         float* dx, float* d_weight);
+// qwen_bwd.cu: dst[c] += sum over rows of parts[row, c] in a fixed order; chunk_scratch holds
+// ceil(rows / 1024) * dim floats
+cudaError_t reduce_rows_accumulate(cudaStream_t stream, const float* parts, long long rows, int dim,
+                                   float* chunk_scratch, float* dst);
+size_t reduce_rows_scratch_floats(long long rows, int dim);
 cudaError_t gdn_gates(cudaStream_t stream, const void* a_in, const void* b_in, const float* a_log,
                       const float* dt_bias, int in_is_bf16, long long tokens, int heads, int round,
                       float* g, float* beta);

@@ -125,12 +125,21 @@ cudaError_t qk_prepare_bwd(cudaStream_t stream, NormBwdArgs a, float* d_weight, 
   norm_bwd_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || d_weight == nullptr) return e;
+  return reduce_rows_accumulate(stream, a.parts, rows, a.head_dim,
+                                a.parts + static_cast<size_t>(rows) * a.head_dim, d_weight);
+}
+
+size_t reduce_rows_scratch_floats(long long rows, int dim) {
+  return static_cast<size_t>((rows + kChunk - 1) / kChunk) * dim;
+}
+
+cudaError_t reduce_rows_accumulate(cudaStream_t stream, const float* parts, long long rows, int dim,
+                                   float* chunk_scratch, float* dst) {
   const int chunks = static_cast<int>((rows + kChunk - 1) / kChunk);
-  float* chunk_sums = a.parts + static_cast<size_t>(rows) * a.head_dim;
-  norm_reduce_chunks<<<chunks, 256, 0, stream>>>(a.parts, rows, a.head_dim, chunk_sums);
-  e = cudaGetLastError();
+  norm_reduce_chunks<<<chunks, 256, 0, stream>>>(parts, rows, dim, chunk_scratch);
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  norm_reduce_final<<<1, 256, 0, stream>>>(chunk_sums, chunks, a.head_dim, d_weight);
+  norm_reduce_final<<<1, 256, 0, stream>>>(chunk_scratch, chunks, dim, dst);
   return cudaGetLastError();
 }
 

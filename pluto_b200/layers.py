@@ -878,11 +878,14 @@ class SequenceDeltaNetLayer(Layer):
     (src/llm/layers/sequence_delta_net.h:20-67, .cc:396-480): causal depthwise convolution + SiLU,
     the recurrence, RMSNorm * weight * SiLU(z).  Inputs bf16 QKV [1,T,channels], Z [1,T,Hv*dv],
     A and B [1,T,Hv]; output bf16 [1,T,Hv*dv].  The reference caps T at 128 because it stores every
-    intermediate state; here the recurrence is chunked and any T runs.  Backward is not built."""
+    intermediate state; here the forward recurrence is chunked, the backward keeps one state per
+    64 tokens and recomputes inside a chunk, and any T runs.  Each of the four parameters is a
+    BlockParameter (or a raw fp32 tensor = frozen); backward accumulates into active ones."""
 
-    def __init__(self, parameters, weights, sequence_length):
+    def __init__(self, parameters, owned, sequence_length):
         self.parameters_ = parameters
-        self.weights_ = weights
+        self.parameters_owned_ = owned                    # convolution, A_log, dt_bias, norm
+        self.weights_ = [p.value() for p in owned]
         self.sequence_length_ = sequence_length
 
     @staticmethod
@@ -897,13 +900,16 @@ class SequenceDeltaNetLayer(Layer):
             raise _invalid("unsupported SequenceDeltaNetLayer shape")
         channels = 2 * p.key_heads * p.key_head_dim + p.value_heads * p.value_head_dim
         counts = [channels * p.conv_kernel_dim, p.value_heads, p.value_heads, p.value_head_dim]
-        for weight, count in zip((convolution, a_log, dt_bias, norm), counts):
+        owned = []
+        for parameter, count in zip((convolution, a_log, dt_bias, norm), counts):
+            weight = parameter.value() if isinstance(parameter, BlockParameter) else parameter
             if weight is None or weight.dtype != torch.float32:
                 raise _invalid("DeltaNet parameters must be FP32")
             if not weight.is_cuda or weight.numel() != count:
                 raise _invalid(f"DeltaNet parameter has {weight.numel() * 4} bytes; expected {count * 4}")
+            owned.append(parameter if isinstance(parameter, BlockParameter) else BlockParameter(weight))
         _capi.lib()
-        return SequenceDeltaNetLayer(p, [convolution, a_log, dt_bias, norm], sequence_length)
+        return SequenceDeltaNetLayer(p, owned, sequence_length)
 
     def name(self) -> str:
         return "SequenceDeltaNetLayer"
@@ -957,5 +963,51 @@ class SequenceDeltaNetLayer(Layer):
         saved = BackwardState(intermediates=[inputs[0], inputs[1], inputs[2], inputs[3], post, core, state])
         return FwdResult([output], saved)
 
+    def gradients(self):
+        return [p.gradient() for p in self.parameters_owned_ if p.active()]
+
     def bwd_impl(self, output_gradients, state, hooks):
-        raise _unimplemented("SequenceDeltaNetLayer backward is not built in this engine yet")
+        # src/llm/layers/sequence_delta_net.cc:482-561
+        p, t = self.parameters_, self.sequence_length_
+        width = p.value_heads * p.value_head_dim
+        kq = p.key_heads * p.key_head_dim
+        channels = 2 * kq + width
+        if len(output_gradients) != 1 or len(state.intermediates) != 7:
+            raise _invalid("invalid DeltaNet backward state or gradient")
+        dy = output_gradients[0]
+        if dy is None or not dy.is_cuda or dy.dtype != torch.float32 or dy.numel() != t * width:
+            raise _invalid("SequenceDeltaNetLayer requires batch-one buffers of the declared shape")
+        qkv_in, z, a, b, post, core, _ = state.intermediates
+        L, rnd = _capi.lib(), int(p.round_to_bfloat16)
+        device = dy.device
+        f32 = dict(dtype=torch.float32, device=device)
+        conv_p, a_log_p, dt_bias_p, norm_p = self.parameters_owned_
+        dqkv = torch.empty((t, channels), **f32)
+        dz = torch.empty((t, width), **f32)
+        da = torch.empty((t, p.value_heads), **f32)
+        db = torch.empty((t, p.value_heads), **f32)
+        dcore = torch.empty((t, width), **f32)
+        dpost = torch.empty((t, channels), **f32)
+        rows = t * p.value_heads
+        ws, size = None, 0
+        if norm_p.active():
+            size = L.pluto_gdn_out_norm_gate_bwd_workspace_bytes(rows, p.value_head_dim)
+            ws = torch.empty((size,), dtype=torch.uint8, device=device)
+        check(L.pluto_gdn_out_norm_gate_bwd(_stream(), _ptr(core), 1, _ptr(z), 1, _ptr(norm_p.value()),
+                                            _ptr(dy), _ptr(dcore), _ptr(dz), _ptr(norm_p.gradient()),
+                                            _ptr(ws), size, rows, p.value_head_dim,
+                                            p.rms_norm_epsilon, rnd))
+        size = L.pluto_gdn_recurrence_bwd_workspace_bytes(1, t, p.key_heads, p.value_heads,
+                                                          p.key_head_dim, p.value_head_dim)
+        ws = torch.empty((size,), dtype=torch.uint8, device=device)
+        flat, dflat = post.view(-1), dpost.view(-1)
+        check(L.pluto_gdn_recurrence_bwd(
+            _stream(), _ptr(flat), _ptr(flat[kq:]), _ptr(flat[2 * kq:]), 1, channels, channels,
+            _ptr(a), _ptr(b), 1, _ptr(a_log_p.value()), _ptr(dt_bias_p.value()), _ptr(dcore),
+            _ptr(dflat), _ptr(dflat[kq:]), channels, _ptr(dflat[2 * kq:]), channels, _ptr(da), _ptr(db),
+            _ptr(a_log_p.gradient()), _ptr(dt_bias_p.gradient()), _ptr(ws), size, 1, t, p.key_heads,
+            p.value_heads, p.key_head_dim, p.value_head_dim, rnd))
+        check(L.pluto_gdn_conv_silu_bwd(_stream(), _ptr(qkv_in), 1, _ptr(conv_p.value()), _ptr(dpost),
+                                        _ptr(dqkv), _ptr(conv_p.gradient()), 1, t, channels,
+                                        p.conv_kernel_dim, rnd))
+        return [dqkv, dz, da, db]
