@@ -378,6 +378,7 @@ def _other_rest(peaks, only, time_ms):
 def _gdn_workload(time_ms):
     import torch
 
+    from pluto_b200 import _capi
     from pluto_b200.layers import gdn_prefill, gdn_step
 
     result = {}
@@ -399,10 +400,32 @@ def _gdn_workload(time_ms):
     q1, k1, v1 = qn[:, 0].contiguous(), kn[:, 0].contiguous(), vn[:, 0].contiguous()
     g1, b1, o1 = g[:, 0].contiguous(), beta[:, 0].contiguous(), torch.empty_like(vn[:, 0])
     step_ms = time_ms(lambda: gdn_step(q1, k1, v1, g1, b1, st, out=o1), steps=256)
+    # BPTT through the recurrence (checkpointed every 64 tokens), q/k normalisation included
+    L = _capi.lib()
+    a_raw = torch.randn(bb, tt, hh, device="cuda").bfloat16()
+    b_raw = torch.randn(bb, tt, hh, device="cuda").bfloat16()
+    a_log = torch.full((hh,), -0.7, device="cuda")
+    dt_bias = torch.zeros(hh, device="cuda")
+    dcore = torch.randn(bb, tt, hh, dd, device="cuda")
+    dq, dk2, dv2 = (torch.empty(bb, tt, hh, dd, device="cuda") for _ in range(3))
+    da, db = torch.empty(bb, tt, hh, device="cuda"), torch.empty(bb, tt, hh, device="cuda")
+    ws_bytes = L.pluto_gdn_recurrence_bwd_workspace_bytes(bb, tt, hh, hh, dd, dd)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def bptt():
+        _capi.check(L.pluto_gdn_recurrence_bwd(
+            stream, qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), 1, hh * dd, hh * dd,
+            a_raw.data_ptr(), b_raw.data_ptr(), 1, a_log.data_ptr(), dt_bias.data_ptr(),
+            dcore.data_ptr(), dq.data_ptr(), dk2.data_ptr(), hh * dd, dv2.data_ptr(), hh * dd,
+            da.data_ptr(), db.data_ptr(), None, None, ws.data_ptr(), ws_bytes, bb, tt, hh, hh, dd, dd, 1))
+
+    bptt_ms = time_ms(bptt, steps=2, warmup=1)
     result["gated_delta_net"] = {
         "workload": "batch 2, 16 heads, d_k = d_v = 128, seq 16384 prefill then single-token steps",
         "prefill_ms": pre_ms, "prefill_tflops_chunked_count": 94.49e9 / (pre_ms * 1e-3) / 1e12,
-        "step_us": step_ms * 1e3, "step_state_gbs": 4.19e6 / (step_ms * 1e-3) / 1e9}
+        "step_us": step_ms * 1e3, "step_state_gbs": 4.19e6 / (step_ms * 1e-3) / 1e9,
+        "recurrence_bwd_ms": bptt_ms, "recurrence_bwd_workspace_gb": ws_bytes / 1e9}
     return result
 
 
