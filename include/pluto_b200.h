@@ -137,7 +137,10 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
  *    (single writer, no atomics: repeated runs are bitwise equal).  q (strided like the forward),
  *    k, v are the prepared tensors of the forward, bf16 or fp32 (dtype); dq fp32
  *    [batch, seq, q_heads, head_dim], dk / dv fp32 [batch, seq, kv_heads, head_dim]: gradients
- *    of the normalised, rotated vectors.  Exact fp32 arithmetic.
+ *    of the normalised, rotated vectors.  With a workspace of
+ *    pluto_gqa_prefill_bwd_workspace_bytes (non-zero for bf16 tensors of head width 64/128) and
+ *    a dense query (q_head_stride == head_dim) the two passes run on tcgen05 with bf16 operands;
+ *    with workspace null, or for any other shape, in exact fp32 arithmetic.
  * 3. pluto_qk_prepare_bwd: NormBackwardKernel + ReduceNormKernel (:192-239): inverse partial
  *    RoPE with the forward's (rounded) cos/sin, RMSNorm backward through the layer input x
  *    (bf16, strided), dx fp32 strided (the query half of dQG [T,Hq,2,D], or dK [T,Hkv,D]).
@@ -153,8 +156,9 @@ int pluto_gqa_gate_bwd(pluto_stream_t stream, const void* gate, size_t gate_toke
 int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, const void* v,
                           int dtype, size_t q_token_stride, size_t q_head_stride, const float* dc,
                           const float* maxima, const float* normalizers, const float* deltas,
-                          float* dq, float* dk, float* dv, int batch, int seq, int q_heads,
-                          int kv_heads, int head_dim);
+                          float* dq, float* dk, float* dv, void* workspace, size_t workspace_bytes,
+                          int batch, int seq, int q_heads, int kv_heads, int head_dim);
+size_t pluto_gqa_prefill_bwd_workspace_bytes(int batch, int seq, int q_heads, int head_dim, int dtype);
 size_t pluto_qk_prepare_bwd_workspace_bytes(int batch, int tokens, int heads, int head_dim);
 int pluto_qk_prepare_bwd(pluto_stream_t stream, const void* x, size_t x_token_stride,
                          size_t x_head_stride, const float* weight, const float* grad,

@@ -33,11 +33,14 @@ constexpr int kBwdThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
-  int seq, heads, head_dim;
+  int seq, heads, head_dim;   // heads = query heads
+  int group;                  // query heads per key/value head
+  int q_col0, k_col0, v_col0; // column of head 0 inside a token row of the q / k / v tensor maps
   float scale, scale_log2;
   const float4* stats;   // [(b*H+h) * seq_pad + s] = (max*log2e, 1/l, delta, 0); zero past seq
   int seq_pad;
-  float* d_qkv;          // fp32 [rows, 3E]
+  float *dq, *dk, *dv;   // fp32; token strides dq_token / dkv_token elements, head stride D
+  size_t dq_token, dkv_token;
   uint32_t* status;
 };
 
@@ -45,7 +48,7 @@ struct BwdParams {
 // prep: grid (rows), 128 threads; one row (all heads) per CTA
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
-attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d_out,
+attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d_out,  // out may be null
               const float* __restrict__ maxima, const float* __restrict__ normalizers,
               __nv_bfloat16* __restrict__ d_out_bf16, float4* __restrict__ stats,
               float* __restrict__ deltas, int seq, int seq_pad, int heads, int head_dim) {
@@ -63,21 +66,26 @@ attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d
     const size_t base = row * E + static_cast<size_t>(h) * head_dim;
     if (head_dim == 128) {          // four channels per lane: 16-byte gradient loads
       const float4 g = *reinterpret_cast<const float4*>(d_out + base + lane * 4);
-      const uint2 o = *reinterpret_cast<const uint2*>(out + base + lane * 4);
-      part = g.x * bf16_lo(o.x) + g.y * bf16_hi(o.x) + g.z * bf16_lo(o.y) + g.w * bf16_hi(o.y);
+      if (out != nullptr) {
+        const uint2 o = *reinterpret_cast<const uint2*>(out + base + lane * 4);
+        part = g.x * bf16_lo(o.x) + g.y * bf16_hi(o.x) + g.z * bf16_lo(o.y) + g.w * bf16_hi(o.y);
+      }
       *reinterpret_cast<uint2*>(d_out_bf16 + base + lane * 4) =
           make_uint2(pack_bf16(g.x, g.y), pack_bf16(g.z, g.w));
     } else {                        // head_dim 64: two channels per lane
       const float2 g = *reinterpret_cast<const float2*>(d_out + base + lane * 2);
-      const uint32_t o = *reinterpret_cast<const uint32_t*>(out + base + lane * 2);
-      part = g.x * bf16_lo(o) + g.y * bf16_hi(o);
+      if (out != nullptr) {
+        const uint32_t o = *reinterpret_cast<const uint32_t*>(out + base + lane * 2);
+        part = g.x * bf16_lo(o) + g.y * bf16_hi(o);
+      }
       *reinterpret_cast<uint32_t*>(d_out_bf16 + base + lane * 2) = pack_bf16(g.x, g.y);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     if (lane == 0) {
       const size_t stat = (static_cast<size_t>(b) * heads + h) * seq + s;
-      deltas[stat] = part;
+      if (out != nullptr) deltas[stat] = part;   // otherwise the caller's deltas are the input
+      else part = deltas[stat];
       stats[record] = make_float4(maxima[stat] * kLog2e, 1.0f / normalizers[stat], part, 0.0f);
     }
   }
@@ -94,8 +102,9 @@ struct DqBarriers {
 // ---------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, D == 64 ? 2 : 1)
-attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
-                  const __grid_constant__ CUtensorMap map_qkv64,
+attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
+                  const __grid_constant__ CUtensorMap map_k64,
+                  const __grid_constant__ CUtensorMap map_v64,
                   const __grid_constant__ CUtensorMap map_do128, BwdParams p) {
   constexpr int kSlabs = D / 64;
   constexpr int kRowTileBytes = kSlabs * kRowTile * 128;   // [128 x D] bf16
@@ -117,7 +126,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   // (sequence, head) varies fastest and the tile index slowest: longest tiles start first
   const int q_tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
-  const int E = p.heads * D;
+  const int kv_head = head / p.group;
   const int col_tiles = (p.seq + kColTile - 1) / kColTile;
   const int n_steps = min(2 * q_tile + 2, col_tiles);   // key tiles that hold a visible key
 
@@ -144,13 +153,14 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&map_qkv128);
-      tma_prefetch_desc(&map_qkv64);
+      tma_prefetch_desc(&map_q128);
+      tma_prefetch_desc(&map_k64);
+      tma_prefetch_desc(&map_v64);
       tma_prefetch_desc(&map_do128);
       mbar_expect_tx(&bar->qdo_full, 2 * kRowTileBytes);
       for (int s = 0; s < kSlabs; ++s) {
-        tma_load_3d(q_smem + s * kRowTile * 128, &map_qkv128, head * D + s * 64, q_tile * kRowTile,
-                    batch, &bar->qdo_full);
+        tma_load_3d(q_smem + s * kRowTile * 128, &map_q128, p.q_col0 + head * D + s * 64,
+                    q_tile * kRowTile, batch, &bar->qdo_full);
         tma_load_3d(do_smem + s * kRowTile * 128, &map_do128, head * D + s * 64, q_tile * kRowTile,
                     batch, &bar->qdo_full);
       }
@@ -162,10 +172,10 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
         mbar_expect_tx(&bar->k_full[st], kColTileBytes);
         mbar_expect_tx(&bar->v_full[st], kColTileBytes);
         for (int s = 0; s < kSlabs; ++s) {
-          tma_load_3d(k_smem + st * kColTileBytes + s * kColTile * 128, &map_qkv64,
-                      E + head * D + s * 64, j * kColTile, batch, &bar->k_full[st]);
-          tma_load_3d(v_smem + st * kColTileBytes + s * kColTile * 128, &map_qkv64,
-                      2 * E + head * D + s * 64, j * kColTile, batch, &bar->v_full[st]);
+          tma_load_3d(k_smem + st * kColTileBytes + s * kColTile * 128, &map_k64,
+                      p.k_col0 + kv_head * D + s * 64, j * kColTile, batch, &bar->k_full[st]);
+          tma_load_3d(v_smem + st * kColTileBytes + s * kColTile * 128, &map_v64,
+                      p.v_col0 + kv_head * D + s * 64, j * kColTile, batch, &bar->v_full[st]);
         }
       }
       mbar_wait(&bar->qdo_full, 0, p.status, 51);
@@ -263,7 +273,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_qkv128,
     if (ok) ok = mbar_wait(&bar->dq_done, 0, p.status, 59);
     if (ok) {
       tc_fence_after();
-      float* dst = p.d_qkv + (static_cast<size_t>(batch) * p.seq + query) * 3 * E + head * D;
+      float* dst = p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -296,8 +306,9 @@ struct DkvBarriers {
 // ---------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, D == 64 ? 2 : 1)
-attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
-                   const __grid_constant__ CUtensorMap map_qkv64,
+attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
+                   const __grid_constant__ CUtensorMap map_v128,
+                   const __grid_constant__ CUtensorMap map_q64,
                    const __grid_constant__ CUtensorMap map_do64, BwdParams p) {
   constexpr int kSlabs = D / 64;
   constexpr int kRowTileBytes = kSlabs * kRowTile * 128;
@@ -319,11 +330,12 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
 
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   // key tile 0 is seen by every query tile: the lowest tile index is the longest, and it starts first
-  const int k_tile = blockIdx.y, head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
-  const int E = p.heads * D;
+  const int kv_heads = p.heads / p.group;
+  const int k_tile = blockIdx.y, kv_head = blockIdx.x % kv_heads, batch = blockIdx.x / kv_heads;
   const int col_tiles = (p.seq + kColTile - 1) / kColTile;
   const int first = 2 * k_tile;                    // first query tile that can see these keys
-  const int n_steps = max(0, col_tiles - first);
+  const int per_head = max(0, col_tiles - first);  // steps per query head of the group
+  const int n_steps = per_head * p.group;          // heads of the group one after the other
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->kv_full, 1);
@@ -344,34 +356,40 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
-  const float4* stats_row = p.stats + (static_cast<size_t>(batch) * p.heads + head) * p.seq_pad;
+  const float4* stats_group =
+      p.stats + (static_cast<size_t>(batch) * p.heads + kv_head * p.group) * p.seq_pad;
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&map_qkv128);
-      tma_prefetch_desc(&map_qkv64);
+      tma_prefetch_desc(&map_k128);
+      tma_prefetch_desc(&map_v128);
+      tma_prefetch_desc(&map_q64);
       tma_prefetch_desc(&map_do64);
       mbar_expect_tx(&bar->kv_full, 2 * kRowTileBytes);
       for (int s = 0; s < kSlabs; ++s) {
-        tma_load_3d(k_smem + s * kRowTile * 128, &map_qkv128, E + head * D + s * 64,
+        tma_load_3d(k_smem + s * kRowTile * 128, &map_k128, p.k_col0 + kv_head * D + s * 64,
                     k_tile * kRowTile, batch, &bar->kv_full);
-        tma_load_3d(v_smem + s * kRowTile * 128, &map_qkv128, 2 * E + head * D + s * 64,
+        tma_load_3d(v_smem + s * kRowTile * 128, &map_v128, p.v_col0 + kv_head * D + s * 64,
                     k_tile * kRowTile, batch, &bar->kv_full);
       }
       bool ok = true;
       for (int i = 0; i < n_steps && ok; ++i) {
-        const int st = i % kBwdStages, use = i / kBwdStages, tile = first + i;
+        const int st = i % kBwdStages, use = i / kBwdStages;
+        const int in_group = i / per_head, tile = first + i % per_head;
+        const int head = kv_head * p.group + in_group;
         if (use > 0) ok = mbar_wait(&bar->q_empty[st], (use - 1) & 1, p.status, 60);
         if (!ok) break;
         uint8_t* dst = stage_smem + st * kStageBytes;
         mbar_expect_tx(&bar->q_full[st], kStageBytes);
         for (int s = 0; s < kSlabs; ++s) {
-          tma_load_3d(dst + s * kColTile * 128, &map_qkv64, head * D + s * 64, tile * kColTile,
-                      batch, &bar->q_full[st]);
+          tma_load_3d(dst + s * kColTile * 128, &map_q64, p.q_col0 + head * D + s * 64,
+                      tile * kColTile, batch, &bar->q_full[st]);
           tma_load_3d(dst + kColTileBytes + s * kColTile * 128, &map_do64, head * D + s * 64,
                       tile * kColTile, batch, &bar->q_full[st]);
         }
-        bulk_load(dst + 2 * kColTileBytes, stats_row + tile * kColTile, kStatsBytes, &bar->q_full[st]);
+        bulk_load(dst + 2 * kColTileBytes,
+                  stats_group + static_cast<size_t>(in_group) * p.seq_pad + tile * kColTile,
+                  kStatsBytes, &bar->q_full[st]);
       }
       mbar_wait(&bar->kv_full, 0, p.status, 61);
       for (int i = max(0, n_steps - kBwdStages); i < n_steps; ++i)
@@ -433,7 +451,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
     for (int i = 0; i < n_steps && ok; ++i) {
-      const int st = i % kBwdStages, tile = first + i;
+      const int st = i % kBwdStages, tile = first + i % per_head;
       ok = mbar_wait(&bar->s_full, i & 1, p.status, 66) &&
            mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 68);  // stats landed (acquire)
       if (!ok) break;
@@ -472,9 +490,9 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
     if (ok && n_steps > 0) ok = mbar_wait(&bar->done, 0, p.status, 67);
     if (ok) {
       tc_fence_after();
-      float* dst = p.d_qkv + (static_cast<size_t>(batch) * p.seq + key) * 3 * E + head * D;
+      const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {   // 0: dV at 2E, 1: dK at E
+      for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
@@ -486,7 +504,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
             for (int i = 0; i < 32; ++i) o[i] = 0u;
           }
           if (key < p.seq) {
-            float* out = dst + (which == 0 ? 2 * E : E) + c * 32;
+            float* out = (which == 0 ? p.dv : p.dk) + dst + c * 32;
 #pragma unroll
             for (int i = 0; i < 32; i += 4)
               *reinterpret_cast<uint4*>(out + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
@@ -503,10 +521,12 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_qkv128,
   }
 }
 
+struct BwdMaps {
+  CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64;
+};
+
 template <int D>
-cudaError_t launch_bwd_tc(cudaStream_t stream, const CUtensorMap& qkv128, const CUtensorMap& qkv64,
-                          const CUtensorMap& do128, const CUtensorMap& do64, const BwdParams& p,
-                          int batch) {
+cudaError_t launch_bwd_tc(cudaStream_t stream, const BwdMaps& m, const BwdParams& p, int batch) {
   constexpr int kSlabs = D / 64;
   const size_t dq_smem = 1024 + 2 * kSlabs * kRowTile * 128 + 2 * kBwdStages * kSlabs * kColTile * 128 +
                          sizeof(DqBarriers);
@@ -518,11 +538,13 @@ cudaError_t launch_bwd_tc(cudaStream_t stream, const CUtensorMap& qkv128, const 
   e = cudaFuncSetAttribute(attn_bwd_dkv_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(dkv_smem));
   if (e != cudaSuccess) return e;
-  const dim3 grid(p.heads * batch, (p.seq + kRowTile - 1) / kRowTile);
-  attn_bwd_dq_sm100<D><<<grid, kBwdThreads, dq_smem, stream>>>(qkv128, qkv64, do128, p);
+  const int tiles = (p.seq + kRowTile - 1) / kRowTile;
+  attn_bwd_dq_sm100<D><<<dim3(p.heads * batch, tiles), kBwdThreads, dq_smem, stream>>>(
+      m.q128, m.k64, m.v64, m.do128, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  attn_bwd_dkv_sm100<D><<<grid, kBwdThreads, dkv_smem, stream>>>(qkv128, qkv64, do64, p);
+  attn_bwd_dkv_sm100<D><<<dim3((p.heads / p.group) * batch, tiles), kBwdThreads, dkv_smem, stream>>>(
+      m.k128, m.v128, m.q64, m.do64, p);
   return cudaGetLastError();
 }
 
@@ -534,39 +556,69 @@ size_t attn_bwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim) 
   return do_bytes + static_cast<size_t>(batch) * heads * seq_pad * sizeof(float4);
 }
 
+// See engine.h for the contract.
+cudaError_t gqa_bwd_tc(cudaStream_t stream, const GqaBwdTcArgs& a) {
+  const int D = a.head_dim, E = a.q_heads * D;
+  const int seq_pad = (a.seq + kColTile - 1) / kColTile * kColTile + kColTile;
+  const size_t do_bytes = (static_cast<size_t>(a.batch) * a.seq * E * 2 + 255) / 256 * 256;
+  auto* do_bf16 = static_cast<__nv_bfloat16*>(a.workspace);
+  auto* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.workspace) + do_bytes);
+  attn_bwd_prep<<<dim3(seq_pad, a.batch), 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(a.out), a.d_out, a.maxima, a.normalizers, do_bf16, stats,
+      a.deltas, a.seq, seq_pad, a.q_heads, D);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  BwdMaps m;
+  if (!make_token_map(&m.q128, a.q, a.q_cols, a.seq, a.batch, a.q_token, kRowTile) ||
+      !make_token_map(&m.q64, a.q, a.q_cols, a.seq, a.batch, a.q_token, kColTile) ||
+      !make_token_map(&m.k128, a.k, a.kv_cols, a.seq, a.batch, a.kv_token, kRowTile) ||
+      !make_token_map(&m.k64, a.k, a.kv_cols, a.seq, a.batch, a.kv_token, kColTile) ||
+      !make_token_map(&m.v128, a.v, a.kv_cols, a.seq, a.batch, a.kv_token, kRowTile) ||
+      !make_token_map(&m.v64, a.v, a.kv_cols, a.seq, a.batch, a.kv_token, kColTile) ||
+      !make_token_map(&m.do128, do_bf16, E, a.seq, a.batch, E, kRowTile) ||
+      !make_token_map(&m.do64, do_bf16, E, a.seq, a.batch, E, kColTile))
+    return cudaErrorInvalidValue;
+  BwdParams p;
+  p.seq = a.seq;
+  p.heads = a.q_heads;
+  p.head_dim = D;
+  p.group = a.q_heads / a.kv_heads;
+  p.q_col0 = a.q_col0;
+  p.k_col0 = a.k_col0;
+  p.v_col0 = a.v_col0;
+  p.scale = 1.0f / sqrtf(static_cast<float>(D));
+  p.scale_log2 = p.scale * kLog2e;
+  p.stats = stats;
+  p.seq_pad = seq_pad;
+  p.dq = a.dq;
+  p.dk = a.dk;
+  p.dv = a.dv;
+  p.dq_token = a.dq_token;
+  p.dkv_token = a.dkv_token;
+  p.status = a.status;
+  if (D == 64) return launch_bwd_tc<64>(stream, m, p, a.batch);
+  if (D == 128) return launch_bwd_tc<128>(stream, m, p, a.batch);
+  return cudaErrorInvalidValue;
+}
+
+// Packed [rows, 3E] layout of AttentionLayer: q, k, v are column ranges of one tensor.
 cudaError_t attn_bwd_tc(cudaStream_t stream, const void* qkv, const void* out, const float* d_out,
                         const float* maxima, const float* normalizers, float* d_qkv, float* deltas,
                         void* workspace, int batch, int seq, int heads, int head_dim,
                         uint32_t* status) {
   const int E = heads * head_dim;
-  const int seq_pad = (seq + kColTile - 1) / kColTile * kColTile + kColTile;
-  const size_t do_bytes = (static_cast<size_t>(batch) * seq * E * 2 + 255) / 256 * 256;
-  auto* do_bf16 = static_cast<__nv_bfloat16*>(workspace);
-  auto* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(workspace) + do_bytes);
-  attn_bwd_prep<<<dim3(seq_pad, batch), 128, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(out), d_out, maxima, normalizers, do_bf16, stats, deltas, seq,
-      seq_pad, heads, head_dim);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  CUtensorMap qkv128, qkv64, do128, do64;
-  if (!make_token_map(&qkv128, qkv, 3 * E, seq, batch, 3 * static_cast<size_t>(E), kRowTile) ||
-      !make_token_map(&qkv64, qkv, 3 * E, seq, batch, 3 * static_cast<size_t>(E), kColTile) ||
-      !make_token_map(&do128, do_bf16, E, seq, batch, E, kRowTile) ||
-      !make_token_map(&do64, do_bf16, E, seq, batch, E, kColTile))
-    return cudaErrorInvalidValue;
-  BwdParams p;
-  p.seq = seq;
-  p.heads = heads;
-  p.head_dim = head_dim;
-  p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
-  p.scale_log2 = p.scale * kLog2e;
-  p.stats = stats;
-  p.seq_pad = seq_pad;
-  p.d_qkv = d_qkv;
-  p.status = status;
-  if (head_dim == 64) return launch_bwd_tc<64>(stream, qkv128, qkv64, do128, do64, p, batch);
-  if (head_dim == 128) return launch_bwd_tc<128>(stream, qkv128, qkv64, do128, do64, p, batch);
-  return cudaErrorInvalidValue;
+  GqaBwdTcArgs a{};
+  a.q = a.k = a.v = qkv;
+  a.q_cols = a.kv_cols = 3 * E;
+  a.q_token = a.kv_token = 3 * static_cast<size_t>(E);
+  a.q_col0 = 0; a.k_col0 = E; a.v_col0 = 2 * E;
+  a.out = out; a.d_out = d_out; a.maxima = maxima; a.normalizers = normalizers; a.deltas = deltas;
+  a.dq = d_qkv; a.dk = d_qkv + E; a.dv = d_qkv + 2 * E;
+  a.dq_token = a.dkv_token = 3 * static_cast<size_t>(E);
+  a.workspace = workspace;
+  a.batch = batch; a.seq = seq; a.q_heads = heads; a.kv_heads = heads; a.head_dim = head_dim;
+  a.status = status;
+  return gqa_bwd_tc(stream, a);
 }
 
 }  // namespace pluto

@@ -213,8 +213,8 @@ int pluto_gqa_gate_bwd(pluto_stream_t stream, const void* gate, size_t gate_toke
 int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, const void* v,
                           int dtype, size_t q_token_stride, size_t q_head_stride, const float* dc,
                           const float* maxima, const float* normalizers, const float* deltas,
-                          float* dq, float* dk, float* dv, int batch, int seq, int q_heads,
-                          int kv_heads, int head_dim) {
+                          float* dq, float* dk, float* dv, void* workspace, size_t workspace_bytes,
+                          int batch, int seq, int q_heads, int kv_heads, int head_dim) {
   if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
       q_heads % kv_heads != 0 || head_dim > 256 || batch > 65535 || q_heads > 65535)
     return fail(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
@@ -229,6 +229,26 @@ int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, c
       q_token_stride < (static_cast<size_t>(q_heads) - 1) * q_head_stride + head_dim)
     return fail(PLUTO_E_INVALID, "attention query strides overlap");
   const size_t D = head_dim, qd = static_cast<size_t>(q_heads) * D, kd = static_cast<size_t>(kv_heads) * D;
+  // bf16 tensors of head width 64/128 with a dense query run on tcgen05 when a workspace is given
+  if (workspace != nullptr && tensor_core_shape(head_dim, dtype) && q_head_stride == D &&
+      q_token_stride % 8 == 0 && q_token_stride <= 0x7fffffffu && aligned16(q) && aligned16(k) &&
+      aligned16(v) && aligned16(workspace)) {
+    if (workspace_bytes < pluto::attn_bwd_tc_workspace_bytes(batch, seq, q_heads, head_dim))
+      return fail(PLUTO_E_INVALID, "attention backward workspace is too small");
+    pluto::GqaBwdTcArgs t{};
+    t.q = q; t.k = k; t.v = v; t.out = nullptr;
+    t.q_cols = static_cast<int>(qd); t.kv_cols = static_cast<int>(kd);
+    t.q_col0 = t.k_col0 = t.v_col0 = 0;
+    t.q_token = q_token_stride; t.kv_token = kd;
+    t.d_out = dc; t.maxima = maxima; t.normalizers = normalizers;
+    t.deltas = const_cast<float*>(deltas);   // only read when out is null
+    t.dq = dq; t.dk = dk; t.dv = dv; t.dq_token = qd; t.dkv_token = kd;
+    t.workspace = workspace;
+    t.batch = batch; t.seq = seq; t.q_heads = q_heads; t.kv_heads = kv_heads; t.head_dim = head_dim;
+    t.status = pluto::kernel_status_word();
+    if (!t.status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
+    return from_cuda(pluto::gqa_bwd_tc(stream, t), "sequence full attention backward (tcgen05)");
+  }
   pluto::GqaBwdArgs a{};
   a.q = q; a.k = k; a.v = v; a.out = nullptr;
   a.d_out = dc; a.maxima = maxima; a.normalizers = normalizers;
@@ -241,6 +261,11 @@ int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, c
   a.dq_token = qd; a.dq_head = D; a.dkv_token = kd; a.dkv_head = D;
   a.bf16 = dtype == PLUTO_BF16;
   return from_cuda(pluto::gqa_generic_bwd(stream, a), "sequence full attention backward");
+}
+
+size_t pluto_gqa_prefill_bwd_workspace_bytes(int batch, int seq, int q_heads, int head_dim, int dtype) {
+  if (batch <= 0 || seq <= 0 || q_heads <= 0 || !tensor_core_shape(head_dim, dtype)) return 0;
+  return pluto::attn_bwd_tc_workspace_bytes(batch, seq, q_heads, head_dim);
 }
 
 size_t pluto_qk_prepare_bwd_workspace_bytes(int batch, int tokens, int heads, int head_dim) {

@@ -80,6 +80,24 @@ cudaError_t attn_bwd_tc(cudaStream_t stream, const void* qkv, const void* out, c
                         const float* maxima, const float* normalizers, float* d_qkv, float* deltas,
                         void* workspace, int batch, int seq, int heads, int head_dim,
                         uint32_t* status);
+// The same two passes over separate bf16 tensors with grouped query heads.  q has q_cols valid
+// columns per token (token stride q_token elements), head h at column q_col0 + h*head_dim; k, v
+// likewise with kv_cols / kv_token / k_col0, v_col0 and key/value head h/group.  d_out fp32 dense
+// [batch, seq, q_heads*head_dim].  With `out` (bf16, dense) set, deltas are computed and stored;
+// with `out` null they are read.  dq / dk / dv fp32, token strides dq_token / dkv_token, head
+// stride head_dim.  workspace: attn_bwd_tc_workspace_bytes(batch, seq, q_heads, head_dim).
+struct GqaBwdTcArgs {
+  const void *q, *k, *v, *out;
+  int q_cols, kv_cols, q_col0, k_col0, v_col0;
+  size_t q_token, kv_token;
+  const float *d_out, *maxima, *normalizers;
+  float *deltas, *dq, *dk, *dv;
+  size_t dq_token, dkv_token;
+  void* workspace;
+  int batch, seq, q_heads, kv_heads, head_dim;
+  uint32_t* status;
+};
+cudaError_t gqa_bwd_tc(cudaStream_t stream, const GqaBwdTcArgs& args);
 
 // ---- attn_fwd_sm100.cu: tcgen05 forward, bf16, head_dim 64 or 128 ------------------------------
 struct AttnFwdArgs {

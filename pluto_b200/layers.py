@@ -646,6 +646,9 @@ class QwenAttentionLayer(Layer):
     def __init__(self, parameters, q_norm, k_norm, sequence_length, cache):
         self.parameters_ = parameters
         self.norms_ = [q_norm, k_norm]                       # BlockParameter
+        # head widths 64/128 run the backward attention core on the tensor cores; set False to
+        # force the exact fp32 kernels (every shape has them)
+        self.tensor_core_backward = True
         self.weights_ = [q_norm.value(), k_norm.value()]
         self.sequence_length_ = sequence_length
         self.cache_ = cache
@@ -799,9 +802,11 @@ class QwenAttentionLayer(Layer):
         check(L.pluto_gqa_gate_bwd(_stream(), qg_in.data_ptr() + 2 * d, 2 * hq * d, 2 * d, _ptr(core),
                                    _ptr(dy), _ptr(dc), dqg.data_ptr() + 4 * d, 2 * hq * d, 2 * d,
                                    _ptr(deltas), 1, t, hq, d, int(p.round_to_bfloat16)))
+        size = L.pluto_gqa_prefill_bwd_workspace_bytes(1, t, hq, d, 1) if self.tensor_core_backward else 0
+        workspace = torch.empty((size,), dtype=torch.uint8, device=device) if size else None
         check(L.pluto_gqa_prefill_bwd(_stream(), _ptr(q), _ptr(k), _ptr(v), 1, hq * d, d, _ptr(dc),
                                       _ptr(maxima), _ptr(normalizers), _ptr(deltas), _ptr(dq_rope),
-                                      _ptr(dk_rope), _ptr(dv), 1, t, hq, hkv, d))
+                                      _ptr(dk_rope), _ptr(dv), _ptr(workspace), size, 1, t, hq, hkv, d))
         for x, x_token, x_head, norm, grad, dx, heads in (
                 (qg_in, 2 * hq * d, 2 * d, self.norms_[0], dq_rope, dqg, hq),
                 (k_in, hkv * d, d, self.norms_[1], dk_rope, dk, hkv)):

@@ -105,6 +105,32 @@ def test_backward_matches_oracle(shape, tol):
     assert len(layer.gradients()) == 2
 
 
+def test_tensor_core_backward_agrees_with_exact_backward_on_long_sequence():
+    """Ragged length above several 128-row tiles, five query heads per KV head: the tcgen05
+    passes against the exact fp32 passes on the same saved forward state."""
+    t, hq, hkv, d, rotary = 700, 10, 2, 128, 64
+    p = FullAttentionParameters(query_heads=hq, key_value_heads=hkv, head_dim=d, rotary_dim=rotary,
+                                capacity=t, rope_theta=1e6)
+    rng = np.random.default_rng(41)
+    qg = oracle.from_bf16_bits(bf(rng.standard_normal((t, hq, 2, d)) * 0.8))
+    k = oracle.from_bf16_bits(bf(rng.standard_normal((t, hkv, d)) * 0.8))
+    v = oracle.from_bf16_bits(bf(rng.standard_normal((t, hkv, d)) * 0.8))
+    dy = rng.standard_normal((t, hq, d)).astype(np.float32)
+    q_norm, k_norm = sine_values(d, 0.2, 0.3), sine_values(d, 0.8, 0.4)
+    results = []
+    for tensor_core in (True, False):
+        layer, qw, kw = make_layer(p, t, q_norm, k_norm)
+        layer.tensor_core_backward = tensor_core
+        _, grads = run(layer, qg, k, v, dy)
+        results.append(grads + [qw.gradient().cpu().numpy(), kw.gradient().cpu().numpy()])
+    for name, a, b in zip(["dqg", "dk", "dv", "dq_norm", "dk_norm"], *results):
+        scale = max(1.0, float(np.abs(b).max()))
+        assert np.abs(a - b).max() <= 1.5e-2 * scale, (name, float(np.abs(a - b).max()), scale)
+        assert np.abs(a - b).mean() <= 1e-3 * scale, name
+    from pluto_b200 import _capi
+    assert _capi.kernel_status() == 0
+
+
 def test_frozen_norms_still_propagate_and_either_norm_may_be_active():
     """qwen_attention_test.cc:304-345, 453-490."""
     t, hq, hkv, d, rotary = 20, 4, 2, 32, 16
