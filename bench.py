@@ -354,6 +354,8 @@ def _other_rest(peaks, only, time_ms):
     result = {}
     if only == "gdn":
         return _gdn_workload(time_ms)
+    if only == "gqa_bwd":
+        return _gqa_bwd_workload(time_ms)
     # GPT-2 small training forward + backward, bf16
     b, h, s, d = 8, 12, 1024, 64
     e = h * d
@@ -371,8 +373,49 @@ def _other_rest(peaks, only, time_ms):
         "bwd_tflops": 10.0 * d * pairs * b * h / (bwd_ms * 1e-3) / 1e12}
     if only == "mha_train":
         return result
+    result.update(_gqa_bwd_workload(time_ms))
     result.update(_gdn_workload(time_ms))
     return result
+
+
+def _gqa_bwd_workload(time_ms):
+    """Backward of the attention core at the headline prefill shape (gate pass + the two tcgen05
+    passes of pluto_gqa_prefill_bwd); 10*D*S(S+1)/2 FLOP per query head."""
+    import torch
+
+    from pluto_b200 import _capi
+    from pluto_b200.layers import gqa_prefill
+
+    L = _capi.lib()
+    t, hq, hkv, d = SEQ, Q_HEADS, KV_HEADS, HEAD_DIM
+    q = (torch.randn(1, t, hq, d, device="cuda") * 0.5).bfloat16()
+    k = (torch.randn(1, t, hkv, d, device="cuda") * 0.5).bfloat16()
+    v = (torch.randn(1, t, hkv, d, device="cuda") * 0.5).bfloat16()
+    gate = torch.randn(1, t, hq, d, device="cuda").bfloat16()
+    fwd = gqa_prefill(q, k, v, gate=gate, want_core=True, want_stats=True)
+    dy = torch.randn(t, hq, d, device="cuda")
+    dc, dgate, dq = (torch.empty(t, hq, d, device="cuda") for _ in range(3))
+    dk, dv = torch.empty(t, hkv, d, device="cuda"), torch.empty(t, hkv, d, device="cuda")
+    deltas = torch.empty(hq * t, device="cuda")
+    size = L.pluto_gqa_prefill_bwd_workspace_bytes(1, t, hq, d, 1)
+    ws = torch.empty(size, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def bwd():
+        _capi.check(L.pluto_gqa_gate_bwd(stream, gate.data_ptr(), hq * d, d, fwd["core"].data_ptr(),
+                                         dy.data_ptr(), dc.data_ptr(), dgate.data_ptr(), hq * d, d,
+                                         deltas.data_ptr(), 1, t, hq, d, 1))
+        _capi.check(L.pluto_gqa_prefill_bwd(stream, q.data_ptr(), k.data_ptr(), v.data_ptr(), 1, hq * d, d,
+                                            dc.data_ptr(), fwd["maxima"].data_ptr(),
+                                            fwd["normalizers"].data_ptr(), deltas.data_ptr(),
+                                            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), size,
+                                            1, t, hq, hkv, d))
+
+    ms = time_ms(bwd, steps=5, warmup=2)
+    flop = 10.0 * d * (t * (t + 1) // 2) * hq
+    return {"gqa_prefill_bwd": {
+        "workload": "backward of the headline prefill shape: gate pass + attention core (tcgen05)",
+        "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12}}
 
 
 def _gdn_workload(time_ms):
@@ -437,7 +480,7 @@ def main():
     parser.add_argument("--impl", choices=["engine", "reference"], default="engine")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the secondary workloads and the CPU baseline (profiling runs)")
-    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn"], default=None,
+    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gqa_bwd"], default=None,
                         help="run only one secondary workload at a capture-friendly size and exit")
     args = parser.parse_args()
     if args.profile_case:

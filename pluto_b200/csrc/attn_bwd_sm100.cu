@@ -93,7 +93,7 @@ attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d
 
 struct DqBarriers {
   uint64_t qdo_full, k_full[kBwdStages], v_full[kBwdStages], kv_empty[kBwdStages];
-  uint64_t s_full, ds_full, dq_done;
+  uint64_t s_full[2], ds_full[2], dq_done;
   uint32_t tmem_base;
 };
 
@@ -109,8 +109,12 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
   constexpr int kSlabs = D / 64;
   constexpr int kRowTileBytes = kSlabs * kRowTile * 128;   // [128 x D] bf16
   constexpr int kColTileBytes = kSlabs * kColTile * 128;   // [64 x D] bf16
-  constexpr uint32_t kTmemCols = 256;
-  constexpr uint32_t kColS = 0, kColDP = 64, kColDQ = 128;
+  // Head width 128 (one CTA per SM): two (S, dP) buffers of 64 + 64 columns, then dQ; the MMA warp
+  // computes step j+1's S and dP while the row threads turn step j's into dS.  Head width 64: one
+  // buffer and 256 columns, so that two CTAs share an SM and overlap each other instead.
+  constexpr bool kPipe = D == 128;
+  constexpr uint32_t kTmemCols = kPipe ? 512 : 256;
+  constexpr uint32_t kColS = 0, kColDP = 64, kBuf = kPipe ? 128 : 0, kColDQ = kPipe ? 256 : 128;
   constexpr uint32_t kIdescS = umma_idesc_bf16(kRowTile, kColTile, false);
   constexpr uint32_t kIdescDQ = umma_idesc_bf16(kRowTile, D, true);
 
@@ -137,8 +141,10 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
       mbar_init(&bar->v_full[s], 1);
       mbar_init(&bar->kv_empty[s], 1);
     }
-    mbar_init(&bar->s_full, 1);
-    mbar_init(&bar->ds_full, 4);   // one arrival per warp
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar->s_full[s], 1);
+      mbar_init(&bar->ds_full[s], 4);   // one arrival per warp
+    }
     mbar_init(&bar->dq_done, 1);
     mbar_fence_init();
   }
@@ -190,44 +196,53 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
       bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->qdo_full, 0, p.status, 54));
       const uint64_t q_desc = umma_desc_sw128(smem_u32(q_smem), 16, 1024);
       const uint64_t do_desc = umma_desc_sw128(smem_u32(do_smem), 16, 1024);
-      for (int j = 0; j < n_steps && ok; ++j) {
+      auto issue_scores = [&](int j) -> bool {   // S(j) = Q K_j^T, dP(j) = dO V_j^T into buffer j & 1
         const int st = j % kBwdStages;
-        ok = __all_sync(0xffffffffu, mbar_wait(&bar->k_full[st], (j / kBwdStages) & 1, p.status, 55) &&
-                                         mbar_wait(&bar->v_full[st], (j / kBwdStages) & 1, p.status, 56));
-        if (!ok) break;
+        if (!__all_sync(0xffffffffu,
+                        mbar_wait(&bar->k_full[st], (j / kBwdStages) & 1, p.status, 55) &&
+                            mbar_wait(&bar->v_full[st], (j / kBwdStages) & 1, p.status, 56)))
+          return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(k_smem + st * kColTileBytes);
-        const uint32_t v_addr = smem_u32(v_smem + st * kColTileBytes);
         if (elect_one()) {
-          const uint64_t k_desc = umma_desc_sw128(k_addr, 16, 1024);
-          const uint64_t v_desc = umma_desc_sw128(v_addr, 16, 1024);
+          const uint64_t k_desc = umma_desc_sw128(smem_u32(k_smem + st * kColTileBytes), 16, 1024);
+          const uint64_t v_desc = umma_desc_sw128(smem_u32(v_smem + st * kColTileBytes), 16, 1024);
+          const uint32_t buf = tmem + (j & 1) * kBuf;
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
             const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
-            umma_ss(tmem + kColS, q_desc + a_off, k_desc + b_off, kIdescS, ks > 0);
+            umma_ss(buf + kColS, q_desc + a_off, k_desc + b_off, kIdescS, ks > 0);
           }
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
             const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
-            umma_ss(tmem + kColDP, do_desc + a_off, v_desc + b_off, kIdescS, ks > 0);
+            umma_ss(buf + kColDP, do_desc + a_off, v_desc + b_off, kIdescS, ks > 0);
           }
-          tc_commit(&bar->s_full);
+          tc_commit(&bar->s_full[j & 1]);
         }
         __syncwarp();
-        ok = __all_sync(0xffffffffu, mbar_wait(&bar->ds_full, j & 1, p.status, 57));
+        return true;
+      };
+      if (ok && n_steps > 0) ok = issue_scores(0);
+      for (int j = 0; j < n_steps && ok; ++j) {
+        const int st = j % kBwdStages;
+        // buffer (j+1) & 1 was last read by the dQ instructions of step j-1, issued before these
+        if (kPipe && j + 1 < n_steps) ok = issue_scores(j + 1);
+        if (!ok) break;
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->ds_full[j & 1], (j >> 1) & 1, p.status, 57));
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
-          const uint64_t k_mn = umma_desc_sw128(k_addr, kColTile * 128, 1024);
+          const uint64_t k_mn = umma_desc_sw128(smem_u32(k_smem + st * kColTileBytes), kColTile * 128, 1024);
 #pragma unroll
           for (int ks = 0; ks < kColTile / 16; ++ks)   // dQ += dS K: 16 keys per step, K MN-major
-            umma_ts(tmem + kColDQ, tmem + kColS + ks * 8, k_mn + ks * (2048 >> 4), kIdescDQ,
-                    j > 0 || ks > 0);
+            umma_ts(tmem + kColDQ, tmem + (j & 1) * kBuf + kColS + ks * 8, k_mn + ks * (2048 >> 4),
+                    kIdescDQ, j > 0 || ks > 0);
           tc_commit(&bar->kv_empty[st]);
         }
         __syncwarp();
+        if (!kPipe && j + 1 < n_steps) ok = issue_scores(j + 1);
       }
       if (ok && elect_one()) tc_commit(&bar->dq_done);
       __syncwarp();
@@ -241,15 +256,16 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
     const float neg_m = -st4.x, inv_l = st4.y, delta = st4.z;
     bool ok = true;
     for (int j = 0; j < n_steps && ok; ++j) {
-      ok = mbar_wait(&bar->s_full, j & 1, p.status, 58);
+      const uint32_t buf = tmem + (j & 1) * kBuf;
+      ok = mbar_wait(&bar->s_full[j & 1], (j >> 1) & 1, p.status, 58);
       if (!ok) break;
       tc_fence_after();
       const bool masked = (j + 1) * kColTile - 1 > q_tile * kRowTile;  // tile may cross the diagonal
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t s[32], dp[32], packed[16];
-        tmem_ld32(tmem + lane_base + kColS + half * 32, s);
-        tmem_ld32(tmem + lane_base + kColDP + half * 32, dp);
+        tmem_ld32(buf + lane_base + kColS + half * 32, s);
+        tmem_ld32(buf + lane_base + kColDP + half * 32, dp);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -263,12 +279,12 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
           }
           packed[i / 2] = pack_bf16(ds[0], ds[1]);
         }
-        tmem_st16(tmem + lane_base + kColS + half * 16, packed);
+        tmem_st16(buf + lane_base + kColS + half * 16, packed);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->ds_full);
+      if (lane == 0) mbar_arrive(&bar->ds_full[j & 1]);
     }
     if (ok) ok = mbar_wait(&bar->dq_done, 0, p.status, 59);
     if (ok) {
@@ -297,7 +313,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
 
 struct DkvBarriers {
   uint64_t kv_full, q_full[kBwdStages], q_empty[kBwdStages];
-  uint64_t s_full, ds_full, done;
+  uint64_t s_full[2], ds_full[2], done;
   uint32_t tmem_base;
 };
 
@@ -315,8 +331,12 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
   constexpr int kColTileBytes = kSlabs * kColTile * 128;
   constexpr int kStatsBytes = kColTile * 16;
   constexpr int kStageBytes = 2 * kColTileBytes + kStatsBytes;   // Q_i, dO_i, stats
-  constexpr uint32_t kTmemCols = D == 64 ? 256 : 512;
-  constexpr uint32_t kColS = 0, kColDP = 64, kColDV = 128, kColDK = 128 + D;
+  // as in the dQ kernel: two (S^T, dP^T) buffers for head width 128 (256 + 2 D = 512 columns),
+  // one buffer and 256 columns for head width 64
+  constexpr bool kPipe = D == 128;
+  constexpr uint32_t kTmemCols = kPipe ? 512 : 256;
+  constexpr uint32_t kColS = 0, kColDP = 64, kBuf = kPipe ? 128 : 0;
+  constexpr uint32_t kColDV = kPipe ? 256 : 128, kColDK = kColDV + D;
   constexpr uint32_t kIdescS = umma_idesc_bf16(kRowTile, kColTile, false);
   constexpr uint32_t kIdescAcc = umma_idesc_bf16(kRowTile, D, true);
 
@@ -343,8 +363,10 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
       mbar_init(&bar->q_full[s], 1);
       mbar_init(&bar->q_empty[s], 1);
     }
-    mbar_init(&bar->s_full, 1);
-    mbar_init(&bar->ds_full, 4);   // one arrival per warp
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar->s_full[s], 1);
+      mbar_init(&bar->ds_full[s], 4);   // one arrival per warp
+    }
     mbar_init(&bar->done, 1);
     mbar_fence_init();
   }
@@ -400,47 +422,57 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
       bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->kv_full, 0, p.status, 63));
       const uint64_t k_desc = umma_desc_sw128(smem_u32(k_smem), 16, 1024);
       const uint64_t v_desc = umma_desc_sw128(smem_u32(v_smem), 16, 1024);
-      for (int i = 0; i < n_steps && ok; ++i) {
+      auto issue_scores = [&](int i) -> bool {   // S^T = K Q_i^T, dP^T = V dO_i^T into buffer i & 1
         const int st = i % kBwdStages;
-        ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 64));
-        if (!ok) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 64)))
+          return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(stage_smem + st * kStageBytes);
-        const uint32_t do_addr = q_addr + kColTileBytes;
         if (elect_one()) {
+          const uint32_t q_addr = smem_u32(stage_smem + st * kStageBytes);
           const uint64_t q_desc = umma_desc_sw128(q_addr, 16, 1024);
-          const uint64_t do_desc = umma_desc_sw128(do_addr, 16, 1024);
+          const uint64_t do_desc = umma_desc_sw128(q_addr + kColTileBytes, 16, 1024);
+          const uint32_t buf = tmem + (i & 1) * kBuf;
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {   // S^T = K Q^T
+          for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
             const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
-            umma_ss(tmem + kColS, k_desc + a_off, q_desc + b_off, kIdescS, ks > 0);
+            umma_ss(buf + kColS, k_desc + a_off, q_desc + b_off, kIdescS, ks > 0);
           }
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {   // dP^T = V dO^T
+          for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
             const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
-            umma_ss(tmem + kColDP, v_desc + a_off, do_desc + b_off, kIdescS, ks > 0);
+            umma_ss(buf + kColDP, v_desc + a_off, do_desc + b_off, kIdescS, ks > 0);
           }
-          tc_commit(&bar->s_full);
+          tc_commit(&bar->s_full[i & 1]);
         }
         __syncwarp();
-        ok = __all_sync(0xffffffffu, mbar_wait(&bar->ds_full, i & 1, p.status, 65));
+        return true;
+      };
+      if (ok && n_steps > 0) ok = issue_scores(0);
+      for (int i = 0; i < n_steps && ok; ++i) {
+        const int st = i % kBwdStages;
+        if (kPipe && i + 1 < n_steps) ok = issue_scores(i + 1);
+        if (!ok) break;
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->ds_full[i & 1], (i >> 1) & 1, p.status, 65));
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
-          const uint64_t do_mn = umma_desc_sw128(do_addr, kColTile * 128, 1024);
+          const uint32_t q_addr = smem_u32(stage_smem + st * kStageBytes);
+          const uint64_t do_mn = umma_desc_sw128(q_addr + kColTileBytes, kColTile * 128, 1024);
           const uint64_t q_mn = umma_desc_sw128(q_addr, kColTile * 128, 1024);
+          const uint32_t buf = tmem + (i & 1) * kBuf;
 #pragma unroll
           for (int ks = 0; ks < kColTile / 16; ++ks) {   // 16 queries per step, operands MN-major
-            umma_ts(tmem + kColDV, tmem + kColS + ks * 8, do_mn + ks * (2048 >> 4), kIdescAcc,
+            umma_ts(tmem + kColDV, buf + kColS + ks * 8, do_mn + ks * (2048 >> 4), kIdescAcc,
                     i > 0 || ks > 0);
-            umma_ts(tmem + kColDK, tmem + kColDP + ks * 8, q_mn + ks * (2048 >> 4), kIdescAcc,
+            umma_ts(tmem + kColDK, buf + kColDP + ks * 8, q_mn + ks * (2048 >> 4), kIdescAcc,
                     i > 0 || ks > 0);
           }
           tc_commit(&bar->q_empty[st]);
         }
         __syncwarp();
+        if (!kPipe && i + 1 < n_steps) ok = issue_scores(i + 1);
       }
       if (ok && elect_one()) tc_commit(&bar->done);
       __syncwarp();
@@ -452,7 +484,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
     bool ok = true;
     for (int i = 0; i < n_steps && ok; ++i) {
       const int st = i % kBwdStages, tile = first + i % per_head;
-      ok = mbar_wait(&bar->s_full, i & 1, p.status, 66) &&
+      const uint32_t buf = tmem + (i & 1) * kBuf;
+      ok = mbar_wait(&bar->s_full[i & 1], (i >> 1) & 1, p.status, 66) &&
            mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 68);  // stats landed (acquire)
       if (!ok) break;
       tc_fence_after();
@@ -461,8 +494,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t s[32], dp[32], pp[16], dsp[16];
-        tmem_ld32(tmem + lane_base + kColS + half * 32, s);
-        tmem_ld32(tmem + lane_base + kColDP + half * 32, dp);
+        tmem_ld32(buf + lane_base + kColS + half * 32, s);
+        tmem_ld32(buf + lane_base + kColDP + half * 32, dp);
         tmem_wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
@@ -479,13 +512,13 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
           dsp[c / 2] = pack_bf16(ds[0], ds[1]);
         }
         // P^T over the consumed part of S^T, dS^T over the consumed part of dP^T
-        tmem_st16(tmem + lane_base + kColS + half * 16, pp);
-        tmem_st16(tmem + lane_base + kColDP + half * 16, dsp);
+        tmem_st16(buf + lane_base + kColS + half * 16, pp);
+        tmem_st16(buf + lane_base + kColDP + half * 16, dsp);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->ds_full);
+      if (lane == 0) mbar_arrive(&bar->ds_full[i & 1]);
     }
     if (ok && n_steps > 0) ok = mbar_wait(&bar->done, 0, p.status, 67);
     if (ok) {
