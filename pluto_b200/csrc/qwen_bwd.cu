@@ -27,26 +27,52 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // GateBackwardKernel (:123-138): dc = dy * R(sigmoid(gate)); d_gate = dy * R(core) * s * (1 - s),
 // s in fp32.  Also the row term of the softmax backward, delta = dc . core with the unrounded
 // core (QueryBackwardKernel :153-155), so the core pass only reads it.
-__global__ void __launch_bounds__(256) gate_bwd_kernel(GateBwdArgs a) {
-  __shared__ float red[8];
-  const int token = blockIdx.x / a.q_heads, h = blockIdx.x % a.q_heads;
-  const int b = token / a.seq, s = token % a.seq;
-  const int c = threadIdx.x, D = a.head_dim;
-  const size_t dense = (static_cast<size_t>(token) * a.q_heads + h) * D;
+// One warp per (token, head), eight per CTA; a lane covers kPer consecutive channels per step of
+// 32 * kPer (kPer = 4 with 16-byte accesses when the width and strides allow it).
+template <int kPer>
+__global__ void __launch_bounds__(256) gate_bwd_kernel(GateBwdArgs a, long long rows) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + threadIdx.x / 32;
+  if (row >= rows) return;
+  const int lane = threadIdx.x % 32, D = a.head_dim;
+  const long long token = row / a.q_heads;
+  const int h = static_cast<int>(row % a.q_heads);
+  const int b = static_cast<int>(token / a.seq), s = static_cast<int>(token % a.seq);
+  const size_t dense = static_cast<size_t>(row) * D;
+  const __nv_bfloat16* gate = a.gate + static_cast<size_t>(token) * a.gate_token + static_cast<size_t>(h) * a.gate_head;
+  float* d_gate = a.d_gate + static_cast<size_t>(token) * a.dgate_token + static_cast<size_t>(h) * a.dgate_head;
   float part = 0.0f;
-  if (c < D) {
-    const float gate = __bfloat162float(
-        a.gate[static_cast<size_t>(token) * a.gate_token + static_cast<size_t>(h) * a.gate_head + c]);
-    const float sigmoid = 1.0f / (1.0f + expf(-gate));
-    const float grad = a.dy[dense + c], core = a.core[dense + c];
-    const float dc = grad * rnd(sigmoid, a.round);
-    a.dc[dense + c] = dc;
-    a.d_gate[static_cast<size_t>(token) * a.dgate_token + static_cast<size_t>(h) * a.dgate_head + c] =
-        grad * rnd(core, a.round) * sigmoid * (1.0f - sigmoid);
-    part = dc * core;
+  for (int c0 = lane * kPer; c0 < D; c0 += 32 * kPer) {
+    float g[kPer], grad[kPer], core[kPer], dc[kPer], dg[kPer];
+    if (kPer == 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(gate + c0);
+      g[0] = bf16_lo(raw.x); g[1] = bf16_hi(raw.x); g[2] = bf16_lo(raw.y); g[3] = bf16_hi(raw.y);
+      const float4 y = *reinterpret_cast<const float4*>(a.dy + dense + c0);
+      const float4 c = *reinterpret_cast<const float4*>(a.core + dense + c0);
+      grad[0] = y.x; grad[1] = y.y; grad[2] = y.z; grad[3] = y.w;
+      core[0] = c.x; core[1] = c.y; core[2] = c.z; core[3] = c.w;
+    } else {
+      g[0] = __bfloat162float(gate[c0]);
+      grad[0] = a.dy[dense + c0];
+      core[0] = a.core[dense + c0];
+    }
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const float sigmoid = 1.0f / (1.0f + expf(-g[i]));
+      dc[i] = grad[i] * rnd(sigmoid, a.round);
+      dg[i] = grad[i] * rnd(core[i], a.round) * sigmoid * (1.0f - sigmoid);
+      part = fmaf(dc[i], core[i], part);
+    }
+    if (kPer == 4) {
+      *reinterpret_cast<float4*>(a.dc + dense + c0) = make_float4(dc[0], dc[1], dc[2], dc[3]);
+      *reinterpret_cast<float4*>(d_gate + c0) = make_float4(dg[0], dg[1], dg[2], dg[3]);
+    } else {
+      a.dc[dense + c0] = dc[0];
+      d_gate[c0] = dg[0];
+    }
   }
-  const float delta = block_sum(part, red);
-  if (c == 0) a.deltas[(static_cast<size_t>(b) * a.q_heads + h) * a.seq + s] = delta;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) a.deltas[(static_cast<size_t>(b) * a.q_heads + h) * a.seq + s] = part;
 }
 
 // NormBackwardKernel (:196-226): rotate the gradient back with the rounded cos/sin of the forward,
@@ -109,8 +135,15 @@ __global__ void __launch_bounds__(256) norm_reduce_final(const float* chunk_sums
 }  // namespace
 
 cudaError_t gqa_gate_bwd(cudaStream_t stream, const GateBwdArgs& a) {
-  const long long blocks = static_cast<long long>(a.batch) * a.seq * a.q_heads;
-  gate_bwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(a);
+  const long long rows = static_cast<long long>(a.batch) * a.seq * a.q_heads;
+  const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+  const auto aligned = [](const void* p, size_t n) { return reinterpret_cast<uintptr_t>(p) % n == 0; };
+  const bool vector = a.head_dim % 4 == 0 && a.gate_token % 4 == 0 && a.gate_head % 4 == 0 &&
+                      a.dgate_token % 4 == 0 && a.dgate_head % 4 == 0 && aligned(a.gate, 8) &&
+                      aligned(a.dy, 16) && aligned(a.core, 16) && aligned(a.dc, 16) &&
+                      aligned(a.d_gate, 16);
+  if (vector) gate_bwd_kernel<4><<<blocks, 256, 0, stream>>>(a, rows);
+  else gate_bwd_kernel<1><<<blocks, 256, 0, stream>>>(a, rows);
   return cudaGetLastError();
 }
 
