@@ -120,6 +120,26 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
                           size_t gate_token_stride, size_t gate_head_stride, int round_to_bf16);
 
 /* --------------------------------------------------------------------------------------------
+ * pluto_gqa_prefill_fwd (the attention core of src/llm/layers/qwen_attention.cc:414-448) for
+ * activations that live in pinned HOST memory; the one entry point that takes host pointers
+ * (the reference stages such buffers with one cudaMemcpyAsync per tensor, as its tests do,
+ * src/llm/layers/qwen_attention_test.cc:118-131): q_host / out_host bf16 [batch, seq, q_heads, head_dim], k_host /
+ * v_host bf16 [batch, seq, kv_heads, head_dim], all dense.  The key/value heads are processed in
+ * groups of kv_heads_per_group (with their query heads); each group's host->device copy, kernel
+ * and device->host copy run on separate streams, two groups in flight, so the PCIe transfers of
+ * both directions overlap each other and the kernels.  No gate, statistics or core output.
+ * workspace: device memory of pluto_gqa_prefill_host_workspace_bytes, 256-byte aligned.  Ordered
+ * behind `stream`; `stream` waits for the last output copy, so synchronising it (or ordering
+ * later work on it) is enough.  Uses two internal copy streams and a few events per device,
+ * created on first use; calls for one device must not run concurrently from several threads. */
+size_t pluto_gqa_prefill_host_workspace_bytes(int batch, int seq, int q_heads, int kv_heads,
+                                              int head_dim, int kv_heads_per_group);
+int pluto_gqa_prefill_fwd_host(pluto_stream_t stream, const void* q_host, const void* k_host,
+                               const void* v_host, void* out_host, void* workspace,
+                               size_t workspace_bytes, int batch, int seq, int q_heads, int kv_heads,
+                               int head_dim, int kv_heads_per_group);
+
+/* --------------------------------------------------------------------------------------------
  * Backward of the Qwen sequence attention, QwenAttentionLayer::SequenceBackward
  * (src/llm/layers/qwen_attention.cc:450-499), in the reference's three stages.  None of them
  * materialises the [Hq,T,T] probabilities or score gradients the reference saves: the core pass

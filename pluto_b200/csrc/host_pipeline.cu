@@ -1,0 +1,134 @@
+// Prefill from host memory: the K/V heads are independent, so the sequence is cut into groups of
+// key/value heads and each group's host->device copy, attention kernel and device->host copy run
+// on three streams, two groups in flight.  PCIe then carries inputs and outputs at the same time
+// and the kernel hides behind the copies; the call a host makes when activations live in pinned
+// host memory (offloaded prefill, or a CPU-resident producer/consumer either side of the layer).
+//
+// The copies are strided (a group's columns of every token row): cudaMemcpy2DAsync, one per
+// tensor and group.  Streams and events are created once per device and reused; the call itself
+// allocates nothing and does not synchronise: everything is ordered behind `stream`, and `stream`
+// is made to wait for the last output copy.
+#include <mutex>
+
+#include "../../include/pluto_b200.h"
+#include "engine.h"
+
+namespace {
+
+constexpr int kSlots = 2;
+constexpr int kMaxDevices = 64;
+
+struct Lanes {
+  cudaStream_t h2d = nullptr, d2h = nullptr;
+  cudaEvent_t start = nullptr, loaded[kSlots] = {}, computed[kSlots] = {}, stored[kSlots] = {};
+  bool ok = false;
+};
+Lanes g_lanes[kMaxDevices];
+std::once_flag g_once[kMaxDevices];
+
+Lanes* lanes_for_current_device() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+  std::call_once(g_once[device], [device] {
+    Lanes& l = g_lanes[device];
+    bool ok = cudaStreamCreateWithFlags(&l.h2d, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&l.d2h, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&l.start, cudaEventDisableTiming) == cudaSuccess;
+    for (int s = 0; s < kSlots && ok; ++s)
+      ok = cudaEventCreateWithFlags(&l.loaded[s], cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&l.computed[s], cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&l.stored[s], cudaEventDisableTiming) == cudaSuccess;
+    l.ok = ok;
+  });
+  return g_lanes[device].ok ? &g_lanes[device] : nullptr;
+}
+
+size_t round256(size_t n) { return (n + 255) / 256 * 256; }
+
+}  // namespace
+
+extern "C" {
+
+size_t pluto_gqa_prefill_host_workspace_bytes(int batch, int seq, int q_heads, int kv_heads,
+                                              int head_dim, int kv_heads_per_group) {
+  if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
+      q_heads % kv_heads != 0 || kv_heads_per_group <= 0)
+    return 0;
+  const size_t tokens = static_cast<size_t>(batch) * seq;
+  const size_t g = q_heads / kv_heads, hc = kv_heads_per_group;
+  const size_t q_bytes = round256(tokens * hc * g * head_dim * 2);
+  const size_t kv_bytes = round256(tokens * hc * head_dim * 2);
+  return kSlots * (2 * q_bytes + 2 * kv_bytes);   // q, out, k, v per slot
+}
+
+int pluto_gqa_prefill_fwd_host(pluto_stream_t stream, const void* q_host, const void* k_host,
+                               const void* v_host, void* out_host, void* workspace,
+                               size_t workspace_bytes, int batch, int seq, int q_heads, int kv_heads,
+                               int head_dim, int kv_heads_per_group) {
+  const size_t need = pluto_gqa_prefill_host_workspace_bytes(batch, seq, q_heads, kv_heads, head_dim,
+                                                             kv_heads_per_group);
+  if (need == 0) return PLUTO_E_INVALID;
+  if (!q_host || !k_host || !v_host || !out_host || !workspace || workspace_bytes < need ||
+      reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return PLUTO_E_INVALID;
+  Lanes* l = lanes_for_current_device();
+  if (l == nullptr) return PLUTO_E_INTERNAL;
+  const size_t tokens = static_cast<size_t>(batch) * seq;
+  const size_t g = q_heads / kv_heads, D = head_dim;
+  const size_t hc_max = kv_heads_per_group;
+  const size_t q_bytes = round256(tokens * hc_max * g * D * 2);
+  const size_t kv_bytes = round256(tokens * hc_max * D * 2);
+  const size_t slot_bytes = 2 * q_bytes + 2 * kv_bytes;
+  const size_t q_pitch = static_cast<size_t>(q_heads) * D * 2, kv_pitch = static_cast<size_t>(kv_heads) * D * 2;
+  cudaStream_t compute = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaEventRecord(l->start, compute);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(l->h2d, l->start, 0);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(l->d2h, l->start, 0);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int groups = (kv_heads + kv_heads_per_group - 1) / kv_heads_per_group;
+  for (int c = 0; c < groups; ++c) {
+    const int slot = c % kSlots;
+    const size_t h0 = static_cast<size_t>(c) * hc_max;
+    const size_t hc = (h0 + hc_max <= static_cast<size_t>(kv_heads)) ? hc_max : kv_heads - h0;
+    uint8_t* base = static_cast<uint8_t*>(workspace) + slot * slot_bytes;
+    uint8_t *q_dev = base, *out_dev = base + q_bytes, *k_dev = base + 2 * q_bytes,
+            *v_dev = base + 2 * q_bytes + kv_bytes;
+    const size_t q_width = hc * g * D * 2, kv_width = hc * D * 2;
+    // inputs of this group; the slot's buffers are free once the kernel of group c-2 is done
+    if (c >= kSlots) e = cudaStreamWaitEvent(l->h2d, l->computed[slot], 0);
+    if (e == cudaSuccess)
+      e = cudaMemcpy2DAsync(q_dev, q_width, static_cast<const uint8_t*>(q_host) + h0 * g * D * 2, q_pitch,
+                            q_width, tokens, cudaMemcpyHostToDevice, l->h2d);
+    if (e == cudaSuccess)
+      e = cudaMemcpy2DAsync(k_dev, kv_width, static_cast<const uint8_t*>(k_host) + h0 * D * 2, kv_pitch,
+                            kv_width, tokens, cudaMemcpyHostToDevice, l->h2d);
+    if (e == cudaSuccess)
+      e = cudaMemcpy2DAsync(v_dev, kv_width, static_cast<const uint8_t*>(v_host) + h0 * D * 2, kv_pitch,
+                            kv_width, tokens, cudaMemcpyHostToDevice, l->h2d);
+    if (e == cudaSuccess) e = cudaEventRecord(l->loaded[slot], l->h2d);
+    // kernel: after its inputs landed and after the output buffer's previous content left
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(compute, l->loaded[slot], 0);
+    if (e == cudaSuccess && c >= kSlots) e = cudaStreamWaitEvent(compute, l->stored[slot], 0);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    const int rc = pluto_gqa_prefill_fwd(stream, q_dev, nullptr, k_dev, v_dev, out_dev, nullptr, nullptr,
+                                         nullptr, batch, seq, static_cast<int>(hc * g),
+                                         static_cast<int>(hc), head_dim, hc * g * D, D, 0, 0, 1);
+    if (rc != PLUTO_OK) return rc;
+    e = cudaEventRecord(l->computed[slot], compute);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(l->d2h, l->computed[slot], 0);
+    if (e == cudaSuccess)
+      e = cudaMemcpy2DAsync(static_cast<uint8_t*>(out_host) + h0 * g * D * 2, q_pitch, out_dev, q_width,
+                            q_width, tokens, cudaMemcpyDeviceToHost, l->d2h);
+    if (e == cudaSuccess) e = cudaEventRecord(l->stored[slot], l->d2h);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  // later work on the caller's stream sees the whole output
+  for (int s = 0; s < kSlots && s < groups; ++s) {
+    e = cudaStreamWaitEvent(compute, l->stored[s], 0);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  // (the last copy on each slot's event covers earlier ones: events are re-recorded per group)
+  return PLUTO_OK;
+}
+
+}  // extern "C"

@@ -287,6 +287,32 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     return result
 
 
+def gqa_prefill_host(q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
+                     out_host: torch.Tensor, kv_heads_per_group: int = 1,
+                     workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """gqa_prefill for activations in pinned host memory (bf16, dense [B,T,Hq,D] / [B,T,Hkv,D]):
+    the copies in both directions and the kernels of successive key/value-head groups overlap
+    (pluto_gqa_prefill_fwd_host).  Writes out_host; the caller synchronises the current stream
+    before reading it.  Pass `workspace` (uint8 device tensor) to reuse one across calls."""
+    B, T, Hq, D = q_host.shape
+    Hkv = k_host.shape[2]
+    for t in (q_host, k_host, v_host, out_host):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.is_cuda or not t.is_pinned():
+            raise _invalid("host prefill requires dense bf16 tensors in pinned host memory")
+    L = _capi.lib()
+    need = L.pluto_gqa_prefill_host_workspace_bytes(B, T, Hq, Hkv, D, kv_heads_per_group)
+    if need == 0:
+        raise _invalid("invalid full-attention dimensions or parameters")
+    if workspace is None or workspace.numel() < need + 256:
+        workspace = torch.empty((need + 256,), dtype=torch.uint8, device="cuda")
+    ws_ptr = (workspace.data_ptr() + 255) // 256 * 256
+    check(L.pluto_gqa_prefill_fwd_host(_stream(), q_host.data_ptr(), k_host.data_ptr(),
+                                       v_host.data_ptr(), out_host.data_ptr(), ws_ptr,
+                                       workspace.numel() - (ws_ptr - workspace.data_ptr()), B, T, Hq,
+                                       Hkv, D, kv_heads_per_group))
+    return workspace
+
+
 # =================================================================================================
 # Qwen cached attention: KeyValueCache, FullAttentionParameters, CachedAttentionStep
 # =================================================================================================

@@ -227,3 +227,21 @@ def test_prefill_full_size_properties():
     ones = gqa_prefill(q, k, torch.ones_like(v))["out"]
     assert (ones.float() - 1.0).abs().max().item() <= 2 ** -8
     assert _capi.kernel_status() == 0
+
+
+def test_host_memory_prefill_matches_device_prefill():
+    """pluto_gqa_prefill_fwd_host: per-KV-head pipelined copies and kernels give exactly what the
+    device-resident call gives, for whole and ragged head groups."""
+    import torch
+    from pluto_b200.layers import gqa_prefill, gqa_prefill_host
+    gen = torch.Generator().manual_seed(5)
+    for (t, hq, hkv, d, per_group) in [(300, 10, 5, 128, 2), (517, 8, 8, 64, 3), (129, 6, 2, 128, 1)]:
+        q = (torch.randn(1, t, hq, d, generator=gen) * 0.5).bfloat16().pin_memory()
+        k = (torch.randn(1, t, hkv, d, generator=gen) * 0.5).bfloat16().pin_memory()
+        v = (torch.randn(1, t, hkv, d, generator=gen) * 0.5).bfloat16().pin_memory()
+        out = torch.zeros(1, t, hq, d, dtype=torch.bfloat16).pin_memory()
+        workspace = gqa_prefill_host(q, k, v, out, kv_heads_per_group=per_group)
+        gqa_prefill_host(q, k, v, out, kv_heads_per_group=per_group, workspace=workspace)  # slot reuse
+        torch.cuda.synchronize()
+        want = gqa_prefill(q.cuda(), k.cuda(), v.cuda())["out"].cpu()
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16)), (t, hq, hkv, d)
