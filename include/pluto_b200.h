@@ -400,6 +400,21 @@ int pluto_gdn_conv_silu_bwd(pluto_stream_t stream, const void* input, int in_dty
                             int batch, int tokens, int channels, int width, int round_to_bf16);
 
 /* --------------------------------------------------------------------------------------------
+ * Imported (frozen checkpoint) projection for a few tokens, FullyConnectedLayer::ImportedForward
+ * (src/llm/layers/fully_connected.cc:295-341; kernels :40-95): output[t][r] = bf16(sum_c
+ * W[r][c] * x[t][c]) in fp32 arithmetic.  weights [output_dim, input_dim] output-major in the
+ * storage of MatrixStorage (src/llm/layers/matrix_common.h:11, same numbering): bf16, fp32, or
+ * FP8 E4M3 bytes with fp32 block scales [ceil(output_dim/128), ceil(input_dim/128)]; for FP8 the
+ * activation is first quantised to E4M3 in groups of 128 with a dynamic scale max|x|/448, as the
+ * reference does.  input bf16 [tokens, input_dim], output bf16 [tokens, output_dim] (the reference
+ * layer is single-token; several tokens share one pass over the weights here).  scales must be
+ * null unless the storage is FP8. */
+enum { PLUTO_MATRIX_BF16 = 0, PLUTO_MATRIX_FP32 = 1, PLUTO_MATRIX_FP8_E4M3 = 2 };
+int pluto_linear_imported_fwd(pluto_stream_t stream, const void* weights, int storage,
+                              const float* scales, const void* input, void* output, int tokens,
+                              int input_dim, int output_dim);
+
+/* --------------------------------------------------------------------------------------------
  * Head-sharded multi-GPU support.  The reference is single-GPU (its only cudaSetDevice pins a
  * thread pool to one device, src/cuda/thread_pool.h:19-22, src/cuda/thread_pool.cc:109), so this
  * has no kernel to mirror: it is the local half of "all-gather the head-sharded output" for a

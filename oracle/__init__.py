@@ -309,3 +309,43 @@ def gdn_sequence_bwd(qkv, z, a, b, conv_w, a_log, dt_bias, norm, dy, kh, vh, kd,
     if rc != 0:
         raise MemoryError("oracle_gdn_sequence_bwd scratch allocation failed")
     return {"dqkv": dqkv, "dz": dz, "da": da, "db": db, "y": y}
+
+
+# ---------------------------------------------------------------------------- imported projections
+def float_to_e4m3(x: np.ndarray) -> np.ndarray:
+    """fp32 -> FP8 E4M3 bytes (round to nearest even, saturating), element by element."""
+    L = lib()
+    L.oracle_float_to_e4m3.restype = C.c_uint8
+    L.oracle_float_to_e4m3.argtypes = [C.c_float]
+    flat = np.asarray(x, np.float32).ravel()
+    return np.array([L.oracle_float_to_e4m3(float(v)) for v in flat], np.uint8).reshape(np.shape(x))
+
+
+def e4m3_to_float(b: np.ndarray) -> np.ndarray:
+    L = lib()
+    L.oracle_e4m3_to_float.restype = C.c_float
+    L.oracle_e4m3_to_float.argtypes = [C.c_uint8]
+    flat = np.asarray(b, np.uint8).ravel()
+    return np.array([L.oracle_e4m3_to_float(int(v)) for v in flat], np.float32).reshape(np.shape(b))
+
+
+def quantize_imported_input(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.zeros_like(x)
+    lib().oracle_quantize_imported_input(_p(x), x.size, _p(out))
+    return out
+
+
+def linear_imported(weights: np.ndarray, storage: str, x: np.ndarray, scales=None) -> np.ndarray:
+    """FullyConnectedLayer::ImportedForward (fully_connected.cc:295-341) for one token: weights
+    [rows, cols] as fp32 ("fp32"), bf16 bits uint16 ("bf16") or e4m3 bytes uint8 ("fp8", with fp32
+    block scales [ceil(rows/128), ceil(cols/128)]); x fp32 values of the bf16 activation.
+    Returns the bf16 output as fp32."""
+    code = {"fp32": 0, "bf16": 1, "fp8": 2}[storage]
+    rows, cols = weights.shape
+    w = np.ascontiguousarray(weights)
+    out = np.zeros(rows, np.uint16)
+    sc = None if scales is None else np.ascontiguousarray(scales, np.float32)
+    lib().oracle_linear_imported(_p(w), code, _p(sc), _p(np.ascontiguousarray(x, np.float32)), cols,
+                                 rows, _p(out))
+    return from_bf16_bits(out)

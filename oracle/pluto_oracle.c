@@ -972,3 +972,77 @@ int oracle_gdn_sequence_bwd(const float* qkv, const float* z, const float* a, co
   free(qk); free(scalars); free(parts);
   return 0;
 }
+
+/* ========================================================================================== *
+ * Imported (frozen, output-major) projections: FullyConnectedLayer::ImportedForward,
+ * src/llm/layers/fully_connected.cc:40-95, 295-341
+ * ========================================================================================== */
+
+/* FP8 E4M3 (4 exponent bits, bias 7, 3 mantissa bits, no infinities, 0x7f/0xff = NaN, largest
+ * finite 448), the format of __nv_fp8_e4m3: round to nearest even, saturating to +-448. */
+float oracle_e4m3_to_float(uint8_t b) {
+  const int sign = b >> 7, e = (b >> 3) & 15, m = b & 7;
+  float v;
+  if (e == 15 && m == 7) return NAN;
+  if (e == 0) v = ldexpf((float)m, -9);
+  else v = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+  return sign ? -v : v;
+}
+uint8_t oracle_float_to_e4m3(float x) {
+  if (x != x) return 0x7f;
+  const uint8_t sign = signbit(x) ? 0x80 : 0;
+  const float a = fabsf(x);
+  if (a >= 448.0f) return sign | 0x7e;
+  if (a < ldexpf(1.0f, -6)) {                    /* subnormal range: multiples of 2^-9 */
+    const int q = (int)nearbyintf(ldexpf(a, 9));  /* ties to even; q = 8 is the smallest normal */
+    return sign | (uint8_t)q;
+  }
+  int e;
+  const float mant = frexpf(a, &e) * 2.0f;       /* in [1, 2) */
+  e -= 1;
+  int q = (int)nearbyintf((mant - 1.0f) * 8.0f);
+  if (q == 8) { q = 0; e += 1; }
+  return sign | (uint8_t)(((e + 7) << 3) | q);
+}
+
+/* QuantizeImportedInputKernel (:73-95): per group of 128 inputs scale = max|x| / 448,
+ * x <- e4m3(x / max(scale, 1e-12)) * scale. */
+void oracle_quantize_imported_input(const float* input, int n, float* output) {
+  for (int start = 0; start < n; start += 128) {
+    const int end = start + 128 < n ? start + 128 : n;
+    float maximum = 0.0f;
+    for (int i = start; i < end; ++i) maximum = fmaxf(maximum, fabsf(input[i]));
+    const float scale = maximum / 448.0f;
+    for (int i = start; i < end; ++i)
+      output[i] = oracle_e4m3_to_float(oracle_float_to_e4m3(input[i] / fmaxf(scale, 1e-12f))) * scale;
+  }
+}
+
+/* ImportedMatVecKernel (:40-71): y[r] = bf16(sum_c w[r][c] * x[c]) with all arithmetic in fp32;
+ * weights [rows, cols] output-major in fp32 (storage 0), bf16 bits (1) or e4m3 bytes (2, each
+ * multiplied by scales[(r/128) * ceil(cols/128) + c/128]); for e4m3 weights the input is first
+ * quantized in groups of 128.  The reference accumulates 128 column lanes per output row and
+ * reduces them at the end; the same here.  input: fp32 values of the bf16 activation. */
+void oracle_linear_imported(const void* weights, int storage, const float* scales,
+                            const float* input, int cols, int rows, uint16_t* output) {
+  float* x = (float*)malloc((size_t)cols * sizeof(float));
+  if (storage == 2) oracle_quantize_imported_input(input, cols, x);
+  else memcpy(x, input, (size_t)cols * sizeof(float));
+  const int scale_cols = (cols + 127) / 128;
+  for (int r = 0; r < rows; ++r) {
+    float lanes[128];
+    for (int l = 0; l < 128; ++l) lanes[l] = 0.0f;
+    for (int c = 0; c < cols; ++c) {
+      const size_t i = (size_t)r * cols + c;
+      float w;
+      if (storage == 0) w = ((const float*)weights)[i];
+      else if (storage == 1) w = bf2f(((const uint16_t*)weights)[i]);
+      else w = oracle_e4m3_to_float(((const uint8_t*)weights)[i]) * scales[(size_t)(r / 128) * scale_cols + c / 128];
+      lanes[c % 128] += w * x[c];
+    }
+    float sum = 0.0f;
+    for (int l = 0; l < 128; ++l) sum += lanes[l];
+    output[r] = f2bf(sum);
+  }
+  free(x);
+}

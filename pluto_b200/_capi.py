@@ -36,6 +36,7 @@ _SIGNATURES = {
     "pluto_gqa_prefill_fwd": (_i, [_vp] * 9 + [_i] * 5 + [_sz, _sz, _sz, _sz, _i]),
     "pluto_gqa_prefill_host_workspace_bytes": (_sz, [_i] * 6),
     "pluto_gqa_prefill_fwd_host": (_i, [_vp] * 6 + [_sz] + [_i] * 6),
+    "pluto_linear_imported_fwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i]),
     "pluto_gqa_gate_bwd": (_i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _sz, _sz, _vp] + [_i] * 5),
     "pluto_gqa_prefill_bwd": (_i, [_vp] * 4 + [_i, _sz, _sz] + [_vp] * 8 + [_sz] + [_i] * 5),
     "pluto_gqa_prefill_bwd_workspace_bytes": (_sz, [_i] * 5),

@@ -631,6 +631,25 @@ int pluto_gdn_conv_silu_bwd(pluto_stream_t stream, const void* input, int in_dty
                    "sequence DeltaNet backward (convolution)");
 }
 
+int pluto_linear_imported_fwd(pluto_stream_t stream, const void* weights, int storage,
+                              const float* scales, const void* input, void* output, int tokens,
+                              int input_dim, int output_dim) {
+  constexpr int kMaximumDimension = 1048576;   // fully_connected.h:52
+  if (input_dim <= 0 || input_dim > kMaximumDimension || output_dim <= 0 ||
+      output_dim > kMaximumDimension)
+    return fail(PLUTO_E_INVALID, "imported linear dimensions must be in [1, 1048576]");
+  if (storage != PLUTO_MATRIX_BF16 && storage != PLUTO_MATRIX_FP32 && storage != PLUTO_MATRIX_FP8_E4M3)
+    return fail(PLUTO_E_INVALID, "unknown matrix storage");
+  if ((storage == PLUTO_MATRIX_FP8_E4M3) != (scales != nullptr))
+    return fail(PLUTO_E_INVALID, "only FP8 linear weights require block scales");
+  if (tokens <= 0 || !weights || !input || !output)
+    return fail(PLUTO_E_INVALID, "imported linear requires non-null device pointers and tokens > 0");
+  const int internal = storage == PLUTO_MATRIX_FP32 ? 0 : (storage == PLUTO_MATRIX_BF16 ? 1 : 2);
+  return from_cuda(pluto::linear_imported(stream, weights, internal, scales, input, output, tokens,
+                                          input_dim, output_dim),
+                   "ImportedMatVecKernel launch");
+}
+
 }  // extern "C"
 
 extern "C" int pluto_interleave_heads(pluto_stream_t stream, const void* gathered, void* out,

@@ -1042,3 +1042,98 @@ class SequenceDeltaNetLayer(Layer):
                                         _ptr(dqkv), _ptr(conv_p.gradient()), 1, t, channels,
                                         p.conv_kernel_dim, rnd))
         return [dqkv, dz, da, db]
+
+
+# =================================================================================================
+# Imported projections (FullyConnectedLayer, frozen checkpoint form)
+# =================================================================================================
+class MatrixStorage(enum.Enum):
+    """src/llm/layers/matrix_common.h:11."""
+    kBFloat16 = 0
+    kFloat32 = 1
+    kFp8E4M3 = 2
+
+
+def _matrix_element_bytes(storage: MatrixStorage) -> int:
+    return {MatrixStorage.kBFloat16: 2, MatrixStorage.kFloat32: 4, MatrixStorage.kFp8E4M3: 1}[storage]
+
+
+class FullyConnectedLayer(Layer):
+    """The imported form of FullyConnectedLayer (src/llm/layers/fully_connected.h:36-49,
+    .cc:267-341): a frozen, biasless [output_dim, input_dim] matrix shared with the checkpoint
+    (bf16, fp32, or FP8 E4M3 bytes with fp32 128x128 block scales), bf16 activations in and out,
+    no gradients; initialisation and backward are rejected.  The reference runs one token per
+    call; `tokens` > 1 rows are accepted here and share one pass over the weights.  The trainable
+    dense form of the reference class is not built."""
+
+    kMaximumDimension = 1048576
+
+    def __init__(self, weights, storage, input_dim, output_dim, scales):
+        self.weights_ = [weights] + ([scales] if scales is not None else [])
+        self.imported_storage_ = storage
+        self.input_dim_, self.output_dim_ = input_dim, output_dim
+
+    @staticmethod
+    def Create(weights: torch.Tensor, storage: MatrixStorage, input_dim: int, output_dim: int,
+               scales: Optional[torch.Tensor] = None) -> "FullyConnectedLayer":
+        limit = FullyConnectedLayer.kMaximumDimension
+        if input_dim <= 0 or input_dim > limit or output_dim <= 0 or output_dim > limit:
+            raise _invalid("imported linear dimensions must be in [1, 1048576]")
+        if not isinstance(storage, MatrixStorage):
+            raise _invalid("unknown matrix storage")
+        expected = input_dim * output_dim * _matrix_element_bytes(storage)
+        if weights is None or not weights.is_cuda:
+            raise _invalid("imported linear weights belong to a different Executor")
+        _validate_buffer(weights, expected, "imported linear weights")
+        if (storage == MatrixStorage.kFp8E4M3) != (scales is not None):
+            raise _invalid("only FP8 linear weights require block scales")
+        if scales is not None:
+            if not scales.is_cuda:
+                raise _invalid("imported linear block scales belong to a different Executor")
+            _validate_buffer(scales, ((input_dim + 127) // 128) * ((output_dim + 127) // 128) * 4,
+                             "imported linear block scales")
+        _capi.lib()
+        return FullyConnectedLayer(weights, storage, input_dim, output_dim, scales)
+
+    def name(self) -> str:
+        return "FullyConnectedLayer"
+
+    def output_type(self) -> DataType:
+        return DataType.BF16
+
+    def input_dim(self) -> int:
+        return self.input_dim_
+
+    def output_dim(self) -> int:
+        return self.output_dim_
+
+    def weights(self):
+        return self.weights_
+
+    def input_types(self):
+        return [ActivationType(DataType.BF16, (-2, 1, self.input_dim_))]
+
+    def output_types(self):
+        return [ActivationType(DataType.BF16, (-2, 1, self.output_dim_))]
+
+    def InitializeIdentity(self, scale: float = 1.0):
+        raise PlutoStatusError("FailedPrecondition", "imported linear weights are frozen", -1)
+
+    def InitializeNormal(self, standard_deviation: float, seed: int):
+        raise PlutoStatusError("FailedPrecondition", "imported linear weights are frozen", -1)
+
+    def fwd_impl(self, inputs, hooks) -> FwdResult:
+        if len(inputs) != 1 or inputs[0] is None or not inputs[0].is_cuda or \
+                inputs[0].dtype != torch.bfloat16 or inputs[0].numel() == 0 or \
+                inputs[0].numel() % self.input_dim_ != 0:
+            raise _invalid("FullyConnectedLayer expects one BF16 activation of its input width")
+        tokens = inputs[0].numel() // self.input_dim_
+        output = torch.empty((tokens, self.output_dim_), dtype=torch.bfloat16, device=inputs[0].device)
+        scales = self.weights_[1] if len(self.weights_) == 2 else None
+        check(_capi.lib().pluto_linear_imported_fwd(
+            _stream(), _ptr(self.weights_[0]), self.imported_storage_.value, _ptr(scales),
+            _ptr(inputs[0]), _ptr(output), tokens, self.input_dim_, self.output_dim_))
+        return FwdResult([output], BackwardState())
+
+    def bwd_impl(self, output_gradients, state, hooks):
+        raise _unimplemented("imported FullyConnectedLayer has no backward")
