@@ -361,6 +361,8 @@ def _other_rest(peaks, only, time_ms):
         return _gdn_workload(time_ms)
     if only == "gqa_bwd":
         return _gqa_bwd_workload(time_ms)
+    if only == "linear":
+        return _linear_workload(time_ms, peaks)
     # GPT-2 small training forward + backward, bf16
     b, h, s, d = 8, 12, 1024, 64
     e = h * d
@@ -379,8 +381,53 @@ def _other_rest(peaks, only, time_ms):
     if only == "mha_train":
         return result
     result.update(_gqa_bwd_workload(time_ms))
+    result.update(_linear_workload(time_ms, peaks))
     result.update(_gdn_workload(time_ms))
     return result
+
+
+def _linear_workload(time_ms, peaks):
+    """Imported projection of the Qwen decoder (hidden 5120 -> 2*40*128 query/gate columns), one
+    token, bf16 and FP8 weights: a weight stream against the HBM roofline.  Calls rotate over
+    enough distinct weight matrices (> 3x the 126 MB L2) that every call streams from HBM, as the
+    layers of a decoder do."""
+    import torch
+
+    from pluto_b200.layers import FullyConnectedLayer, MatrixStorage
+
+    cols, rows = 5120, 10240
+    x = torch.randn(1, cols, device="cuda").bfloat16()
+    out = {}
+    for name, storage, elem in (("bf16", MatrixStorage.kBFloat16, 2), ("fp8_e4m3", MatrixStorage.kFp8E4M3, 1)):
+        copies = (420 << 20) // (rows * cols * elem) + 1
+        layers = []
+        for _ in range(copies):
+            if elem == 2:
+                w, scales = (torch.randn(rows, cols, device="cuda") * 0.02).bfloat16(), None
+            else:
+                w = torch.randint(0, 120, (rows, cols), dtype=torch.uint8, device="cuda")
+                scales = torch.full((rows // 128 * (cols // 128),), 0.01, device="cuda")
+            layers.append(FullyConnectedLayer.Create(w, storage, cols, rows, scales))
+        # the C entry point directly with a preallocated output: the kernel runs ~20 us, less
+        # than the Python layer object spends per call
+        from pluto_b200 import _capi
+        L, stream = _capi.lib(), torch.cuda.current_stream().cuda_stream
+        y = torch.empty(1, rows, dtype=torch.bfloat16, device="cuda")
+        args = [(l.weights()[0].data_ptr(), l.weights()[1].data_ptr() if elem == 1 else None) for l in layers]
+        state = {"i": 0}
+
+        def call():
+            w_ptr, s_ptr = args[state["i"] % copies]
+            L.pluto_linear_imported_fwd(stream, w_ptr, storage.value, s_ptr, x.data_ptr(), y.data_ptr(),
+                                        1, cols, rows)
+            state["i"] += 1
+
+        ms = time_ms(call, steps=4 * copies, warmup=copies)
+        nbytes = rows * cols * elem + (0 if elem == 2 else rows // 128 * (cols // 128) * 4) + cols * 2 + rows * 2
+        out[name] = {"ms": ms, "weight_gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    return {"imported_linear": {"workload": "one token, [10240 x 5120] frozen weights, calls rotate over "
+                                            "> 420 MB of distinct matrices", **out}}
 
 
 def _gqa_bwd_workload(time_ms):
@@ -485,7 +532,7 @@ def main():
     parser.add_argument("--impl", choices=["engine", "reference"], default="engine")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the secondary workloads and the CPU baseline (profiling runs)")
-    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gqa_bwd"], default=None,
+    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gqa_bwd", "linear"], default=None,
                         help="run only one secondary workload at a capture-friendly size and exit")
     args = parser.parse_args()
     if args.profile_case:

@@ -21,8 +21,19 @@ namespace pluto {
 namespace {
 
 constexpr int kWarps = 8, kThreads = kWarps * 32;
-constexpr int kRows = 2;          // output rows per warp
+constexpr int kRows = 4;          // output rows per task
 constexpr int kChunk = 8192;      // staged activation floats per CTA (all tokens together)
+
+// The staged activation is read as 16-byte chunks at a lane stride of 1, 2 or 4 chunks (fp32,
+// bf16, FP8 weights); XOR-ing the chunk index with two bits of its octet index spreads every
+// quarter-warp over all eight 16-byte bank groups.
+__device__ __forceinline__ int swizzled(int c) {
+  const int j = c >> 2;
+  return ((j ^ ((j >> 3) & 3)) << 2) | (c & 3);
+}
+__device__ __forceinline__ float4 staged4(const float* xs, int c) {   // c % 4 == 0
+  return *reinterpret_cast<const float4*>(xs + swizzled(c));
+}
 
 __device__ __forceinline__ float e4m3_to_float(uint8_t b) {
   const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
@@ -37,16 +48,21 @@ __device__ __forceinline__ float quantize_e4m3(float v, float scale) {
 template <int STORAGE> struct Weights;
 template <> struct Weights<0> {
   static constexpr int kPer = 4;
-  __device__ static void load(const void* w, size_t i, float (&v)[4]) {
-    const float4 r = *reinterpret_cast<const float4*>(static_cast<const float*>(w) + i);
-    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  __device__ static uint4 raw(const void* w, size_t i) {
+    return *reinterpret_cast<const uint4*>(static_cast<const float*>(w) + i);
+  }
+  __device__ static void convert(const uint4& r, float (&v)[4]) {
+    v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y);
+    v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
   }
   __device__ static float one(const void* w, size_t i) { return static_cast<const float*>(w)[i]; }
 };
 template <> struct Weights<1> {
   static constexpr int kPer = 8;
-  __device__ static void load(const void* w, size_t i, float (&v)[8]) {
-    const uint4 r = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(w) + i);
+  __device__ static uint4 raw(const void* w, size_t i) {
+    return *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(w) + i);
+  }
+  __device__ static void convert(const uint4& r, float (&v)[8]) {
     v[0] = bf16_lo(r.x); v[1] = bf16_hi(r.x); v[2] = bf16_lo(r.y); v[3] = bf16_hi(r.y);
     v[4] = bf16_lo(r.z); v[5] = bf16_hi(r.z); v[6] = bf16_lo(r.w); v[7] = bf16_hi(r.w);
   }
@@ -56,8 +72,10 @@ template <> struct Weights<1> {
 };
 template <> struct Weights<2> {
   static constexpr int kPer = 16;
-  __device__ static void load(const void* w, size_t i, float (&v)[16]) {
-    const uint4 r = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(w) + i);
+  __device__ static uint4 raw(const void* w, size_t i) {
+    return *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(w) + i);
+  }
+  __device__ static void convert(const uint4& r, float (&v)[16]) {
     const uint32_t words[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -76,8 +94,13 @@ template <> struct Weights<2> {
   }
 };
 
-// grid: ceil(rows / (kWarps * kRows)) CTAs.  VECTOR: every weight row starts 16-byte aligned and
-// cols is a multiple of the elements per load.
+// One task = kRows consecutive output rows, done by one CTA: its 256 threads interleave over the
+// columns (thread i takes the 16-byte chunks i, i + 256, ...), then the eight warps' partial sums
+// are combined through shared memory in warp order.  When the whole activation fits the staging
+// buffer (cols <= kCols) the grid is three CTAs per SM, the activation is staged once per CTA and
+// task i goes to CTA i % gridDim.x, so every SM gets the same number of 4-row tasks to within one.
+// Longer rows take one task per CTA and several staging passes.
+// VECTOR: every weight row starts 16-byte aligned and cols is a multiple of the elements per load.
 template <int STORAGE, int TOK, bool VECTOR>
 __global__ void __launch_bounds__(kThreads)
 linear_gemv_kernel(const void* __restrict__ weights, const float* __restrict__ scales,
@@ -85,22 +108,19 @@ linear_gemv_kernel(const void* __restrict__ weights, const float* __restrict__ s
                    int rows) {
   constexpr int kPer = Weights<STORAGE>::kPer;
   constexpr int kCols = kChunk / TOK / 128 * 128;     // staged columns per pass (multiple of 128)
+  constexpr size_t kElem = STORAGE == 0 ? 4 : (STORAGE == 1 ? 2 : 1);
   __shared__ float xs[TOK][kCols];
+  __shared__ float partial[kWarps][kRows][TOK];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int row0 = (blockIdx.x * kWarps + warp) * kRows;
   const int scale_cols = (cols + 127) / 128;
-  float acc[kRows][TOK];
-#pragma unroll
-  for (int r = 0; r < kRows; ++r)
-#pragma unroll
-    for (int t = 0; t < TOK; ++t) acc[r][t] = 0.0f;
+  const int n_tasks = (rows + kRows - 1) / kRows;
+  const uint8_t* wbytes = static_cast<const uint8_t*>(weights);
 
-  for (int c0 = 0; c0 < cols; c0 += kCols) {
-    const int count = min(kCols, cols - c0);
-    __syncthreads();   // the previous pass is done with xs
-    // stage the activation: bf16 -> fp32, FP8 path: quantise each group of 128 (one warp a group)
-    for (int group = warp; group < TOK * ((count + 127) / 128); group += kWarps) {
-      const int t = group / ((count + 127) / 128), g = group % ((count + 127) / 128);
+  // bf16 -> fp32 into xs; FP8 path: quantise each group of 128 (one warp a group)
+  auto stage = [&](int c0, int count) {
+    const int groups = (count + 127) / 128;
+    for (int group = warp; group < TOK * groups; group += kWarps) {
+      const int t = group / groups, g = group % groups;
       float v[4], maximum = 0.0f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -118,72 +138,133 @@ linear_gemv_kernel(const void* __restrict__ weights, const float* __restrict__ s
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int c = g * 128 + lane + 32 * i;
-        if (c < kCols) xs[t][c] = v[i];
+        if (c < kCols) xs[t][swizzled(c)] = v[i];
       }
     }
-    __syncthreads();
+  };
+  // acc[r][t] += sum over the staged columns [c0, c0 + count) of W[row0 + r][c] * x[t][c]
+  auto accumulate = [&](float (&acc)[kRows][TOK], int row0, int c0, int count) {
+    if (VECTOR) {
+      // all rows of the task advance together: kRows * kUnroll 16-byte loads in flight per lane,
+      // and each staged activation chunk is read once for the kRows rows
+      constexpr int kUnroll = 2;
+      size_t base[kRows];
+      const float* srow[kRows];
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      const int row = row0 + r;
-      if (row >= rows) continue;
-      const size_t base = static_cast<size_t>(row) * cols + c0;
-      const float* srow = STORAGE == 2 ? scales + static_cast<size_t>(row / 128) * scale_cols : nullptr;
-      if (VECTOR) {
-        constexpr int kUnroll = 4;
-        int c = lane * kPer;
-        for (; c + (kUnroll - 1) * 32 * kPer < count; c += kUnroll * 32 * kPer) {
-          float w[kUnroll][kPer];
+      for (int r = 0; r < kRows; ++r) {
+        const int row = min(row0 + r, rows - 1);          // rows past the end repeat the last one
+        base[r] = (static_cast<size_t>(row) * cols + c0) * kElem;
+        srow[r] = STORAGE == 2 ? scales + static_cast<size_t>(row / 128) * scale_cols : nullptr;
+      }
+      for (int c = threadIdx.x * kPer; c < count; c += kUnroll * kThreads * kPer) {
+        uint4 raw[kRows][kUnroll];
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) Weights<STORAGE>::load(weights, base + c + u * 32 * kPer, w[u]);
+        for (int u = 0; u < kUnroll; ++u) {
+          const int cu = min(c + u * kThreads * kPer, count - kPer);   // a tail step re-reads a valid chunk
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int cu = c + u * 32 * kPer;
-            const float s = STORAGE == 2 ? srow[(c0 + cu) / 128] : 1.0f;
+          for (int r = 0; r < kRows; ++r)
+            raw[r][u] = *reinterpret_cast<const uint4*>(wbytes + base[r] + static_cast<size_t>(cu) * kElem);
+        }
 #pragma unroll
-            for (int i = 0; i < kPer; ++i) {
-              const float wv = STORAGE == 2 ? w[u][i] * s : w[u][i];
+        for (int u = 0; u < kUnroll; ++u) {
+          const int cu = c + u * kThreads * kPer;
+          if (cu >= count) break;
+          float4 xv[TOK][kPer / 4];
 #pragma unroll
-              for (int t = 0; t < TOK; ++t) acc[r][t] = fmaf(wv, xs[t][cu + i], acc[r][t]);
+          for (int t = 0; t < TOK; ++t)
+#pragma unroll
+            for (int i = 0; i < kPer / 4; ++i) xv[t][i] = staged4(xs[t], cu + 4 * i);
+#pragma unroll
+          for (int r = 0; r < kRows; ++r) {
+            float w[kPer];
+            Weights<STORAGE>::convert(raw[r][u], w);
+            const float s = STORAGE == 2 ? srow[r][(c0 + cu) / 128] : 1.0f;
+#pragma unroll
+            for (int t = 0; t < TOK; ++t) {
+              float part = 0.0f;
+#pragma unroll
+              for (int i = 0; i < kPer / 4; ++i) {
+                part = fmaf(w[4 * i], xv[t][i].x, part);
+                part = fmaf(w[4 * i + 1], xv[t][i].y, part);
+                part = fmaf(w[4 * i + 2], xv[t][i].z, part);
+                part = fmaf(w[4 * i + 3], xv[t][i].w, part);
+              }
+              acc[r][t] = STORAGE == 2 ? fmaf(part, s, acc[r][t]) : acc[r][t] + part;
             }
           }
         }
-        for (; c < count; c += 32 * kPer) {
-          float w[kPer];
-          Weights<STORAGE>::load(weights, base + c, w);
-          const float s = STORAGE == 2 ? srow[(c0 + c) / 128] : 1.0f;
+      }
+    } else {
 #pragma unroll
-          for (int i = 0; i < kPer; ++i) {
-            const float wv = STORAGE == 2 ? w[i] * s : w[i];
-#pragma unroll
-            for (int t = 0; t < TOK; ++t) acc[r][t] = fmaf(wv, xs[t][c + i], acc[r][t]);
-          }
-        }
-      } else {
-        for (int c = lane; c < count; c += 32) {
+      for (int r = 0; r < kRows; ++r) {
+        const int row = row0 + r;
+        if (row >= rows) continue;
+        const size_t base = static_cast<size_t>(row) * cols + c0;
+        const float* srow = STORAGE == 2 ? scales + static_cast<size_t>(row / 128) * scale_cols : nullptr;
+        for (int c = threadIdx.x; c < count; c += kThreads) {
           float wv = Weights<STORAGE>::one(weights, base + c);
           if (STORAGE == 2) wv *= srow[(c0 + c) / 128];
 #pragma unroll
-          for (int t = 0; t < TOK; ++t) acc[r][t] = fmaf(wv, xs[t][c], acc[r][t]);
+          for (int t = 0; t < TOK; ++t) acc[r][t] = fmaf(wv, xs[t][swizzled(c)], acc[r][t]);
         }
       }
     }
-  }
+  };
+  auto finish = [&](float (&acc)[kRows][TOK], int row0) {
 #pragma unroll
-  for (int r = 0; r < kRows; ++r)
+    for (int r = 0; r < kRows; ++r)
 #pragma unroll
-    for (int t = 0; t < TOK; ++t) {
-      float v = acc[r][t];
+      for (int t = 0; t < TOK; ++t) {
+        float v = acc[r][t];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0 && row0 + r < rows)
-        y[static_cast<size_t>(t) * rows + row0 + r] = __float2bfloat16_rn(v);
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) partial[warp][r][t] = v;
+      }
+    __syncthreads();
+    if (threadIdx.x < kRows * TOK) {
+      const int r = threadIdx.x / TOK, t = threadIdx.x % TOK;
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) v += partial[w][r][t];
+      if (row0 + r < rows) y[static_cast<size_t>(t) * rows + row0 + r] = __float2bfloat16_rn(v);
     }
+    __syncthreads();   // partial is rewritten by the next task
+  };
+
+  if (cols <= kCols) {
+    stage(0, cols);
+    __syncthreads();
+    for (int task = blockIdx.x; task < n_tasks; task += gridDim.x) {
+      float acc[kRows][TOK] = {};
+      accumulate(acc, task * kRows, 0, cols);
+      finish(acc, task * kRows);
+    }
+  } else {
+    const int task = blockIdx.x;
+    float acc[kRows][TOK] = {};
+    for (int c0 = 0; c0 < cols; c0 += kCols) {
+      const int count = min(kCols, cols - c0);
+      __syncthreads();   // the previous pass is done with xs
+      stage(c0, count);
+      __syncthreads();
+      accumulate(acc, task * kRows, c0, count);
+    }
+    finish(acc, task * kRows);
+  }
 }
 
 template <int STORAGE, int TOK>
 cudaError_t launch(cudaStream_t stream, const void* weights, const float* scales, const void* x,
                    void* y, int cols, int rows) {
-  const unsigned grid = (rows + kWarps * kRows - 1) / (kWarps * kRows);
+  constexpr int kCols = kChunk / TOK / 128 * 128;
+  const int n_tasks = (rows + kRows - 1) / kRows;
+  unsigned grid = n_tasks;
+  if (cols <= kCols) {
+    int sms = 148, device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess)
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    grid = min(grid, static_cast<unsigned>(3 * sms));
+  }
   const size_t elem = STORAGE == 0 ? 4 : (STORAGE == 1 ? 2 : 1);
   const bool vector = reinterpret_cast<uintptr_t>(weights) % 16 == 0 &&
                       (static_cast<size_t>(cols) * elem) % 16 == 0;
