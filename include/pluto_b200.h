@@ -415,6 +415,28 @@ int pluto_linear_imported_fwd(pluto_stream_t stream, const void* weights, int st
                               int input_dim, int output_dim);
 
 /* --------------------------------------------------------------------------------------------
+ * Trainable dense projection, FullyConnectedLayer::fwd_impl / bwd_impl
+ * (src/llm/layers/fully_connected.cc:415-520; kernels :97-232), as tcgen05 GEMMs:
+ *   forward   output = cast(input) * cast(matrix) + bias     [rows, output_dim], dtype of input
+ *   backward  input_gradient  = cast(dY) * cast(matrix)^T    fp32 [rows, input_dim]
+ *             matrix_gradient = cast(input)^T * cast(dY)     fp32 [input_dim, output_dim]
+ *             bias_gradient   = column sums of dY            fp32 [output_dim]
+ * matrix is the fp32 master copy [input_dim, output_dim] (input-major), bias fp32; input is bf16
+ * (dtype PLUTO_BF16) or fp32 (PLUTO_FP32: the reference's FP16 compute policy); cast = bf16 or
+ * fp16 respectively, accumulation fp32, as in the reference's tile MMAs.  The gradients are
+ * overwritten, not accumulated, like the reference's.  workspace: device memory of
+ * pluto_dense_workspace_bytes (the 2-byte operand copies), 256-byte aligned.  Any positive
+ * extents (tiles are padded inside the workspace). */
+size_t pluto_dense_workspace_bytes(int rows, int input_dim, int output_dim);
+int pluto_dense_fwd(pluto_stream_t stream, const void* input, int dtype, const float* matrix,
+                    const float* bias, void* output, int rows, int input_dim, int output_dim,
+                    void* workspace, size_t workspace_bytes);
+int pluto_dense_bwd(pluto_stream_t stream, const void* input, int dtype, const float* matrix,
+                    const float* output_gradient, float* input_gradient, float* matrix_gradient,
+                    float* bias_gradient, int rows, int input_dim, int output_dim, void* workspace,
+                    size_t workspace_bytes);
+
+/* --------------------------------------------------------------------------------------------
  * Head-sharded multi-GPU support.  The reference is single-GPU (its only cudaSetDevice pins a
  * thread pool to one device, src/cuda/thread_pool.h:19-22, src/cuda/thread_pool.cc:109), so this
  * has no kernel to mirror: it is the local half of "all-gather the head-sharded output" for a

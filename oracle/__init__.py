@@ -349,3 +349,26 @@ def linear_imported(weights: np.ndarray, storage: str, x: np.ndarray, scales=Non
     lib().oracle_linear_imported(_p(w), code, _p(sc), _p(np.ascontiguousarray(x, np.float32)), cols,
                                  rows, _p(out))
     return from_bf16_bits(out)
+
+
+# ---------------------------------------------------------------------------- dense projections
+def _mma_cast(a: np.ndarray, bf16: bool) -> np.ndarray:
+    """Operand type of the reference's tile MMAs (fully_connected.cc:31-33): bf16 for bf16
+    activations, fp16 for the fp32-activation policy."""
+    a = np.asarray(a, np.float32)
+    return round_bf16(a) if bf16 else a.astype(np.float16).astype(np.float32)
+
+
+def dense_fwd(x, w, bias, bf16: bool) -> np.ndarray:
+    """DenseForwardKernel (fully_connected.cc:97-132): cast(x) @ cast(w) + bias, accumulated in
+    higher precision than the reference's fp32 tiles; output rounded to bf16 for bf16 layers."""
+    y = _mma_cast(x, bf16).astype(np.float64) @ _mma_cast(w, bf16).astype(np.float64) + np.asarray(bias, np.float64)
+    y = y.astype(np.float32)
+    return round_bf16(y) if bf16 else y
+
+
+def dense_bwd(x, w, dy, bf16: bool):
+    """DenseInputGradientKernel, DenseWeightGradientKernel, DenseBiasGradientKernel (:134-232)."""
+    xc, wc, gc = (_mma_cast(a, bf16).astype(np.float64) for a in (x, w, dy))
+    return {"dx": (gc @ wc.T).astype(np.float32), "dw": (xc.T @ gc).astype(np.float32),
+            "db": np.asarray(dy, np.float64).sum(0).astype(np.float32)}

@@ -650,6 +650,54 @@ int pluto_linear_imported_fwd(pluto_stream_t stream, const void* weights, int st
                    "ImportedMatVecKernel launch");
 }
 
+size_t pluto_dense_workspace_bytes(int rows, int input_dim, int output_dim) {
+  if (rows <= 0 || input_dim <= 0 || output_dim <= 0) return 0;
+  return pluto::dense_workspace_bytes(rows, input_dim, output_dim);
+}
+
+namespace {
+int check_dense(int rows, int input_dim, int output_dim, int dtype, const void* workspace,
+                size_t workspace_bytes) {
+  if (rows <= 0 || input_dim <= 0 || output_dim <= 0 || rows > (1 << 24) || input_dim > (1 << 24) ||
+      output_dim > (1 << 24))
+    return fail(PLUTO_E_INVALID, "dense layer extents must be positive");
+  if (dtype != PLUTO_FP32 && dtype != PLUTO_BF16)
+    return fail(PLUTO_E_UNIMPLEMENTED, "dense layers compute in FP16 (fp32 activations) or BF16");
+  if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 ||
+      workspace_bytes < pluto_dense_workspace_bytes(rows, input_dim, output_dim))
+    return fail(PLUTO_E_INVALID, "dense layer workspace is missing, misaligned or too small");
+  return PLUTO_OK;
+}
+}  // namespace
+
+int pluto_dense_fwd(pluto_stream_t stream, const void* input, int dtype, const float* matrix,
+                    const float* bias, void* output, int rows, int input_dim, int output_dim,
+                    void* workspace, size_t workspace_bytes) {
+  if (int rc = check_dense(rows, input_dim, output_dim, dtype, workspace, workspace_bytes)) return rc;
+  if (!input || !matrix || !bias || !output)
+    return fail(PLUTO_E_INVALID, "dense layer requires non-null device pointers");
+  uint32_t* status = pluto::kernel_status_word();
+  if (!status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
+  return from_cuda(pluto::dense_fwd(stream, input, dtype == PLUTO_BF16, matrix, bias, output, rows,
+                                    input_dim, output_dim, workspace, status),
+                   "DenseForwardKernel launch");
+}
+
+int pluto_dense_bwd(pluto_stream_t stream, const void* input, int dtype, const float* matrix,
+                    const float* output_gradient, float* input_gradient, float* matrix_gradient,
+                    float* bias_gradient, int rows, int input_dim, int output_dim, void* workspace,
+                    size_t workspace_bytes) {
+  if (int rc = check_dense(rows, input_dim, output_dim, dtype, workspace, workspace_bytes)) return rc;
+  if (!input || !matrix || !output_gradient || !input_gradient || !matrix_gradient || !bias_gradient)
+    return fail(PLUTO_E_INVALID, "dense layer requires non-null device pointers");
+  uint32_t* status = pluto::kernel_status_word();
+  if (!status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
+  return from_cuda(pluto::dense_bwd(stream, input, dtype == PLUTO_BF16, matrix, output_gradient,
+                                    input_gradient, matrix_gradient, bias_gradient, rows, input_dim,
+                                    output_dim, workspace, status),
+                   "dense backward launch");
+}
+
 }  // extern "C"
 
 extern "C" int pluto_interleave_heads(pluto_stream_t stream, const void* gathered, void* out,

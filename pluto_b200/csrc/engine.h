@@ -211,6 +211,15 @@ cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& args, void* workspac
 cudaError_t linear_imported(cudaStream_t stream, const void* weights, int storage, const float* scales,
                             const void* x, void* y, int tokens, int cols, int rows);
 
+// ---- gemm_sm100.cu: trainable dense projection (tcgen05 GEMMs over 2-byte casts of the operands) --
+size_t dense_workspace_bytes(int rows, int in, int out);
+cudaError_t dense_fwd(cudaStream_t stream, const void* x, bool x_is_bf16, const float* w,
+                      const float* bias, void* y, int rows, int in, int out, void* workspace,
+                      uint32_t* status);
+cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const float* w,
+                      const float* dy, float* dx, float* dw, float* db, int rows, int in, int out,
+                      void* workspace, uint32_t* status);
+
 // gdn_bwd.cu: backward of the sequence layer
 struct GdnBwdArgs {
   const void* q;            // convolved + SiLU'd activations, as GdnArgs (raw, not normalised)

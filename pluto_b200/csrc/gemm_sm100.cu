@@ -1,0 +1,324 @@
+// Dense projection GEMMs on the Blackwell tensor cores for the trainable form of
+// FullyConnectedLayer (src/llm/layers/fully_connected.cc:97-232, 415-520):
+//     forward          Y  = cast(X) cast(W) + b          [rows, out]   (activation dtype)
+//     input gradient   dX = cast(dY) cast(W)^T           [rows, in]    fp32
+//     weight gradient  dW = cast(X)^T cast(dY)           [in, out]     fp32 (overwritten)
+//     bias gradient    db = column sums of dY            [out]         fp32 (overwritten)
+// with fp32 master weights W [in, out], and `cast` = bf16 for bf16 activations, fp16 for the
+// fp32-activation ("FP16") policy, fp32 accumulation -- the operand types of the reference's
+// 64x64 tile MMAs.
+//
+// Here the operands are first cast once into zero-padded 2-byte copies (every extent rounded up to
+// 128), so that all three products are the same kernel: C[M,N] = sum_k A(m,k) B(k,n) over
+// 128 x 128 x 64 tiles, TMA-staged through a 6-stage shared-memory ring with 128-byte swizzle,
+// tcgen05.mma with the accumulator in TMEM, and the two operand layouts the products need:
+//   K-major   (k contiguous:  X for the forward, dY and W for dX)
+//   MN-major  (m or n contiguous: W for the forward, X and dY for dW), read as two 64-wide slabs.
+// One CTA per output tile: warp 0 issues the TMA loads, warp 1 walks the MMA schedule with one
+// elected issuing lane, warps 4-7 move the accumulator from TMEM to global memory (one row per
+// thread) adding the bias.  All waits are bounded.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "engine.h"
+
+namespace pluto {
+namespace {
+
+constexpr int kTile = 128, kBK = 64, kGemmStages = 6, kGemmThreads = 256;
+constexpr int kOperandBytes = kTile * kBK * 2;   // 16 KB per operand per stage
+
+struct GemmParams {
+  int M, N;            // valid extent of C
+  int k_tiles;         // padded K / 64
+  uint32_t idesc;
+  const float* bias;   // optional [N]
+  void* c;             // row-major, ldc elements between rows
+  size_t ldc;
+  int c_kind;          // 0 fp32, 1 bf16
+  uint32_t* status;
+};
+
+struct GemmBarriers {
+  uint64_t full[kGemmStages], empty[kGemmStages], done;
+  uint32_t tmem_base;
+};
+
+// kind::f16 instruction descriptor: D fp32; A/B format 0 = f16, 1 = bf16; major bits 15 (A) and
+// 16 (B): 0 = K-major, 1 = MN-major; N >> 3 at [17,23), M >> 4 at [24,29).
+constexpr uint32_t gemm_idesc(int format, bool a_mn, bool b_mn) {
+  return (1u << 4) | (static_cast<uint32_t>(format) << 7) | (static_cast<uint32_t>(format) << 10) |
+         (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
+         (static_cast<uint32_t>(kTile >> 3) << 17) | (static_cast<uint32_t>(kTile >> 4) << 24);
+}
+
+// grid (N tiles, M tiles)
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+           GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* a_smem = smem;
+  uint8_t* b_smem = smem + kGemmStages * kOperandBytes;
+  GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(b_smem + kGemmStages * kOperandBytes);
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGemmStages; ++s) {
+      mbar_init(&bar->full[s], 1);
+      mbar_init(&bar->empty[s], 1);
+    }
+    mbar_init(&bar->done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, kTile);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      bool ok = true;
+      for (int kt = 0; kt < p.k_tiles && ok; ++kt) {
+        const int st = kt % kGemmStages, use = kt / kGemmStages;
+        if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, p.status, 70);
+        if (!ok) break;
+        mbar_expect_tx(&bar->full[st], 2 * kOperandBytes);
+        uint8_t* a_dst = a_smem + st * kOperandBytes;
+        uint8_t* b_dst = b_smem + st * kOperandBytes;
+        if (A_MN) {   // memory [k][m]: two slabs of 64 m-columns x 64 k-rows
+          tma_load_3d(a_dst, &map_a, m0, kt * kBK, 0, &bar->full[st]);
+          tma_load_3d(a_dst + kOperandBytes / 2, &map_a, m0 + 64, kt * kBK, 0, &bar->full[st]);
+        } else {      // memory [m][k]: 64 k-columns x 128 m-rows
+          tma_load_3d(a_dst, &map_a, kt * kBK, m0, 0, &bar->full[st]);
+        }
+        if (B_MN) {
+          tma_load_3d(b_dst, &map_b, n0, kt * kBK, 0, &bar->full[st]);
+          tma_load_3d(b_dst + kOperandBytes / 2, &map_b, n0 + 64, kt * kBK, 0, &bar->full[st]);
+        } else {
+          tma_load_3d(b_dst, &map_b, kt * kBK, n0, 0, &bar->full[st]);
+        }
+      }
+      for (int kt = max(0, p.k_tiles - kGemmStages); kt < p.k_tiles; ++kt)   // copies have landed
+        mbar_wait(&bar->full[kt % kGemmStages], (kt / kGemmStages) & 1, p.status, 71);
+    }
+  } else if (warp == 1) {
+    bool ok = true;
+    for (int kt = 0; kt < p.k_tiles && ok; ++kt) {
+      const int st = kt % kGemmStages;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->full[st], (kt / kGemmStages) & 1, p.status, 72));
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t a_addr = smem_u32(a_smem + st * kOperandBytes);
+        const uint32_t b_addr = smem_u32(b_smem + st * kOperandBytes);
+        // K-major: rows of 128 bytes, a K step of 16 elements is 32 bytes along the row.
+        // MN-major: [64 k-rows x 128 bytes] slabs, a K step is 16 rows (2048 bytes), the second
+        // 64-wide slab sits kOperandBytes / 2 further (leading-dimension byte offset).
+        const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr, kOperandBytes / 2, 1024)
+                                     : umma_desc_sw128(a_addr, 16, 1024);
+        const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr, kOperandBytes / 2, 1024)
+                                     : umma_desc_sw128(b_addr, 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < kBK / 16; ++ks)
+          umma_ss(tmem, a_desc + ks * ((A_MN ? 2048 : 32) >> 4), b_desc + ks * ((B_MN ? 2048 : 32) >> 4),
+                  p.idesc, kt > 0 || ks > 0);
+        tc_commit(&bar->empty[st]);
+        if (kt + 1 == p.k_tiles) tc_commit(&bar->done);
+      }
+      __syncwarp();
+    }
+  } else if (warp >= 4) {
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    if (mbar_wait(&bar->done, 0, p.status, 73)) {
+      tc_fence_after();
+      const int m = m0 + row;
+      const bool vec = (p.ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
+#pragma unroll
+      for (int c = 0; c < kTile / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld32(tmem + lane_base + c * 32, acc);
+        tmem_wait_ld();
+        if (m >= p.M) continue;
+        const int n_base = n0 + c * 32;
+        if (n_base >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = __uint_as_float(acc[i]);
+          if (p.bias != nullptr && n_base + i < p.N) v[i] += p.bias[n_base + i];
+        }
+        if (p.c_kind == 0) {
+          float* dst = static_cast<float*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
+          if (vec && n_base + 32 <= p.N) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          } else {
+            for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = v[i];
+          }
+        } else {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
+          if (p.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(p.c) % 16 == 0 && n_base + 32 <= p.N) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8)
+              *reinterpret_cast<uint4*>(dst + i) =
+                  make_uint4(pack_bf16(v[i], v[i + 1]), pack_bf16(v[i + 2], v[i + 3]),
+                             pack_bf16(v[i + 4], v[i + 5]), pack_bf16(v[i + 6], v[i + 7]));
+          } else {
+            for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTile);
+  }
+}
+
+// src [rows, cols] (fp32 or bf16) -> dst [rows_p, cols_p] 2-byte (bf16 or fp16), zero padded
+template <typename In, bool kHalf>
+__global__ void cast_pad_kernel(const In* __restrict__ src, uint16_t* __restrict__ dst, int rows,
+                                int cols, int rows_p, int cols_p) {
+  const size_t total = static_cast<size_t>(rows_p) * cols_p;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / cols_p), c = static_cast<int>(i % cols_p);
+    float v = 0.0f;
+    if (r < rows && c < cols) {
+      if constexpr (sizeof(In) == 4) v = src[static_cast<size_t>(r) * cols + c];
+      else v = __bfloat162float(src[static_cast<size_t>(r) * cols + c]);
+    }
+    uint16_t bits;
+    if (kHalf) bits = __half_as_ushort(__float2half_rn(v));
+    else bits = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    dst[i] = bits;
+  }
+}
+
+// db[n] = sum over rows of dy[r][n]: a CTA owns 32 columns; warp w sums rows w, w + 8, ... of its
+// columns, then the eight partial sums are added in warp order (fixed order, no atomics).
+__global__ void __launch_bounds__(256) bias_grad_kernel(const float* __restrict__ dy, int rows, int cols,
+                                                        float* __restrict__ db) {
+  __shared__ float part[8][32];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int n = blockIdx.x * 32 + lane;
+  float sum = 0.0f;
+  if (n < cols)
+    for (int r = warp; r < rows; r += 8) sum += dy[static_cast<size_t>(r) * cols + n];
+  part[warp][lane] = sum;
+  __syncthreads();
+  if (warp == 0 && n < cols) {
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += part[w][lane];
+    db[n] = total;
+  }
+}
+
+int pad128(int v) { return (v + 127) / 128 * 128; }
+
+template <bool A_MN, bool B_MN>
+cudaError_t launch_gemm(cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b,
+                        const GemmParams& p) {
+  const size_t smem = 1024 + 2 * kGemmStages * kOperandBytes + sizeof(GemmBarriers);
+  cudaError_t e = cudaFuncSetAttribute(gemm_sm100<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  const dim3 grid((p.N + kTile - 1) / kTile, (p.M + kTile - 1) / kTile);
+  gemm_sm100<A_MN, B_MN><<<grid, kGemmThreads, smem, stream>>>(a, b, p);
+  return cudaGetLastError();
+}
+
+template <typename In>
+cudaError_t cast_pad(cudaStream_t stream, const void* src, void* dst, int rows, int cols, bool half) {
+  const int rows_p = pad128(rows), cols_p = pad128(cols);
+  const size_t total = static_cast<size_t>(rows_p) * cols_p;
+  const unsigned blocks = static_cast<unsigned>(std::min<size_t>((total + 255) / 256, 148 * 16));
+  if (half)
+    cast_pad_kernel<In, true><<<blocks, 256, 0, stream>>>(static_cast<const In*>(src),
+                                                           static_cast<uint16_t*>(dst), rows, cols, rows_p, cols_p);
+  else
+    cast_pad_kernel<In, false><<<blocks, 256, 0, stream>>>(static_cast<const In*>(src),
+                                                            static_cast<uint16_t*>(dst), rows, cols, rows_p, cols_p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t dense_workspace_bytes(int rows, int in, int out) {
+  const size_t r = pad128(rows), i = pad128(in), o = pad128(out);
+  return 2 * (r * i + i * o + r * o);   // casts of X, W, dY
+}
+
+// x: [rows, in] bf16 (x_is_bf16) or fp32; w fp32 [in, out]; bias fp32 [out]; y same dtype as x.
+cudaError_t dense_fwd(cudaStream_t stream, const void* x, bool x_is_bf16, const float* w,
+                      const float* bias, void* y, int rows, int in, int out, void* workspace,
+                      uint32_t* status) {
+  const int r = pad128(rows), i = pad128(in), o = pad128(out);
+  auto* xc = static_cast<uint8_t*>(workspace);
+  auto* wc = xc + 2 * static_cast<size_t>(r) * i;
+  const bool half = !x_is_bf16;
+  cudaError_t e = x_is_bf16 ? cast_pad<__nv_bfloat16>(stream, x, xc, rows, in, half)
+                            : cast_pad<float>(stream, x, xc, rows, in, half);
+  if (e != cudaSuccess) return e;
+  e = cast_pad<float>(stream, w, wc, in, out, half);
+  if (e != cudaSuccess) return e;
+  CUtensorMap ma, mb;
+  if (!make_token_map(&ma, xc, i, r, 1, i, kTile) ||       // A K-major: [rows][in]
+      !make_token_map(&mb, wc, o, i, 1, o, kBK))           // B MN-major: [in][out]
+    return cudaErrorInvalidValue;
+  GemmParams p{rows, out, i / kBK, gemm_idesc(half ? 0 : 1, false, true), bias, y,
+               static_cast<size_t>(out), x_is_bf16 ? 1 : 0, status};
+  return launch_gemm<false, true>(stream, ma, mb, p);
+}
+
+// dy fp32 [rows, out]; dx fp32 [rows, in]; dw fp32 [in, out]; db fp32 [out] (all overwritten)
+cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const float* w,
+                      const float* dy, float* dx, float* dw, float* db, int rows, int in, int out,
+                      void* workspace, uint32_t* status) {
+  const int r = pad128(rows), i = pad128(in), o = pad128(out);
+  auto* xc = static_cast<uint8_t*>(workspace);
+  auto* wc = xc + 2 * static_cast<size_t>(r) * i;
+  auto* gc = wc + 2 * static_cast<size_t>(i) * o;
+  const bool half = !x_is_bf16;
+  cudaError_t e = x_is_bf16 ? cast_pad<__nv_bfloat16>(stream, x, xc, rows, in, half)
+                            : cast_pad<float>(stream, x, xc, rows, in, half);
+  if (e == cudaSuccess) e = cast_pad<float>(stream, w, wc, in, out, half);
+  if (e == cudaSuccess) e = cast_pad<float>(stream, dy, gc, rows, out, half);
+  if (e != cudaSuccess) return e;
+  const int format = half ? 0 : 1;
+  CUtensorMap ma, mb;
+  // dX[rows, in] = dY[rows][out] (K-major) * W^T: B(k, n) = W[n][k], memory [in][out] = K-major
+  if (!make_token_map(&ma, gc, o, r, 1, o, kTile) || !make_token_map(&mb, wc, o, i, 1, o, kTile))
+    return cudaErrorInvalidValue;
+  GemmParams pdx{rows, in, o / kBK, gemm_idesc(format, false, false), nullptr, dx,
+                 static_cast<size_t>(in), 0, status};
+  e = launch_gemm<false, false>(stream, ma, mb, pdx);
+  if (e != cudaSuccess) return e;
+  // dW[in, out] = X^T dY: A(m, k) = X[k][m], memory [rows][in] = MN-major; B = dY [rows][out] MN-major
+  if (!make_token_map(&ma, xc, i, r, 1, i, kBK) || !make_token_map(&mb, gc, o, r, 1, o, kBK))
+    return cudaErrorInvalidValue;
+  GemmParams pdw{in, out, r / kBK, gemm_idesc(format, true, true), nullptr, dw,
+                 static_cast<size_t>(out), 0, status};
+  e = launch_gemm<true, true>(stream, ma, mb, pdw);
+  if (e != cudaSuccess) return e;
+  bias_grad_kernel<<<(out + 31) / 32, 256, 0, stream>>>(dy, rows, out, db);
+  return cudaGetLastError();
+}
+
+}  // namespace pluto

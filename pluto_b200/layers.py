@@ -1063,8 +1063,9 @@ class FullyConnectedLayer(Layer):
     .cc:267-341): a frozen, biasless [output_dim, input_dim] matrix shared with the checkpoint
     (bf16, fp32, or FP8 E4M3 bytes with fp32 128x128 block scales), bf16 activations in and out,
     no gradients; initialisation and backward are rejected.  The reference runs one token per
-    call; `tokens` > 1 rows are accepted here and share one pass over the weights.  The trainable
-    dense form of the reference class is not built."""
+    call; `tokens` > 1 rows are accepted here and share one pass over the weights.
+
+    The trainable form is DenseLayer below (same reference class, :343-520)."""
 
     kMaximumDimension = 1048576
 
@@ -1137,3 +1138,107 @@ class FullyConnectedLayer(Layer):
 
     def bwd_impl(self, output_gradients, state, hooks):
         raise _unimplemented("imported FullyConnectedLayer has no backward")
+
+
+class DenseLayer(Layer):
+    """The trainable form of FullyConnectedLayer (src/llm/layers/fully_connected.h:27-35,
+    .cc:343-520): fp32 master matrix [input_dim, output_dim] and bias, fp32 gradients (overwritten
+    by every backward), activations bf16 (DataType.BF16) or fp32 (DataType.FP16 compute policy),
+    MMA operands cast to bf16 / fp16 with fp32 accumulation.  Runs as tcgen05 GEMMs."""
+
+    def __init__(self, input_dim, output_dim, data_type, sequence_length, device):
+        self.input_dim_, self.output_dim_ = input_dim, output_dim
+        self.output_type_, self.sequence_length_ = data_type, sequence_length
+        f32 = dict(dtype=torch.float32, device=device)
+        self.weights_ = [torch.zeros((input_dim, output_dim), **f32), torch.zeros((output_dim,), **f32)]
+        self.gradients_ = [torch.zeros((input_dim, output_dim), **f32), torch.zeros((output_dim,), **f32)]
+
+    @staticmethod
+    def Create(input_dim: int, output_dim: Optional[int] = None, data_type: DataType = DataType.BF16,
+               sequence_length: int = 1, device="cuda") -> "DenseLayer":
+        output_dim = input_dim if output_dim is None else output_dim
+        if sequence_length <= 0:
+            raise _invalid("sequence_length must be positive")
+        if data_type not in (DataType.FP16, DataType.BF16):
+            raise _unimplemented("dense layers compute in FP16 or BF16")
+        if input_dim <= 0:
+            raise _invalid("input_dim must be positive")
+        if output_dim <= 0:
+            raise _invalid("output_dim must be positive")
+        _capi.lib()
+        return DenseLayer(input_dim, output_dim, data_type, sequence_length, device)
+
+    def name(self) -> str:
+        return "FullyConnectedLayer"
+
+    def output_type(self) -> DataType:
+        return self.output_type_
+
+    def input_dim(self) -> int:
+        return self.input_dim_
+
+    def output_dim(self) -> int:
+        return self.output_dim_
+
+    def weights(self):
+        return self.weights_
+
+    def gradients(self):
+        return self.gradients_
+
+    def input_types(self):
+        return [ActivationType(self.output_type_, (-2, self.sequence_length_, self.input_dim_))]
+
+    def output_types(self):
+        return [ActivationType(self.output_type_, (-2, self.sequence_length_, self.output_dim_))]
+
+    def InitializeIdentity(self, scale: float = 1.0) -> None:
+        matrix = torch.zeros((self.input_dim_, self.output_dim_), dtype=torch.float32)
+        n = min(self.input_dim_, self.output_dim_)
+        matrix[torch.arange(n), torch.arange(n)] = scale
+        self.weights_[0].copy_(matrix)
+        self.weights_[1].zero_()
+
+    def InitializeNormal(self, standard_deviation: float, seed: int) -> None:
+        if not standard_deviation > 0.0:
+            raise _invalid("dense initialization standard deviation must be positive")
+        gen = torch.Generator().manual_seed(seed)
+        self.weights_[0].copy_(torch.randn((self.input_dim_, self.output_dim_), generator=gen)
+                               * standard_deviation)
+
+    def _workspace(self, rows, device):
+        need = _capi.lib().pluto_dense_workspace_bytes(rows, self.input_dim_, self.output_dim_)
+        ws = torch.empty((need + 256,), dtype=torch.uint8, device=device)
+        ptr = (ws.data_ptr() + 255) // 256 * 256
+        return ws, ptr, need
+
+    def fwd_impl(self, inputs, hooks) -> FwdResult:
+        if len(inputs) != 1:
+            raise _invalid("FullyConnectedLayer fwd expects one input")
+        rows = _activation_rows(inputs[0], self.input_dim_, self.output_type_, "dense input")
+        dtype = activation_torch_dtype(self.output_type_)
+        output = torch.empty((rows, self.output_dim_), dtype=dtype, device=inputs[0].device)
+        ws, ptr, need = self._workspace(rows, inputs[0].device)
+        check(_capi.lib().pluto_dense_fwd(
+            _stream(), _ptr(inputs[0]), 1 if self.output_type_ == DataType.BF16 else 0,
+            _ptr(self.weights_[0]), _ptr(self.weights_[1]), _ptr(output), rows, self.input_dim_,
+            self.output_dim_, ptr, need))
+        return FwdResult([output], BackwardState(intermediates=[inputs[0]]))
+
+    def bwd_impl(self, output_gradients, state, hooks):
+        if len(output_gradients) != 1 or len(state.intermediates) != 1:
+            raise _invalid("FullyConnectedLayer bwd received an incompatible gradient or state")
+        dy = output_gradients[0]
+        if dy.dtype != torch.float32:
+            raise _invalid("dense output gradient must be FP32")
+        rows = _activation_rows(dy, self.output_dim_, DataType.FP32, "dense output gradient")
+        x = state.intermediates[0]
+        element = 2 if self.output_type_ == DataType.BF16 else 4
+        _validate_buffer(x, rows * self.input_dim_ * element, "dense saved input")
+        dx = torch.empty((rows, self.input_dim_), dtype=torch.float32, device=dy.device)
+        ws, ptr, need = self._workspace(rows, dy.device)
+        check(_capi.lib().pluto_dense_bwd(
+            _stream(), _ptr(x), 1 if self.output_type_ == DataType.BF16 else 0, _ptr(self.weights_[0]),
+            _ptr(dy), _ptr(dx), _ptr(self.gradients_[0]), _ptr(self.gradients_[1]), rows,
+            self.input_dim_, self.output_dim_, ptr, need))
+        return [dx]
