@@ -363,6 +363,8 @@ def _other_rest(peaks, only, time_ms):
         return _gqa_bwd_workload(time_ms)
     if only == "linear":
         return _linear_workload(time_ms, peaks)
+    if only == "dense":
+        return _dense_workload(time_ms, peaks)
     # GPT-2 small training forward + backward, bf16
     b, h, s, d = 8, 12, 1024, 64
     e = h * d
@@ -382,6 +384,7 @@ def _other_rest(peaks, only, time_ms):
         return result
     result.update(_gqa_bwd_workload(time_ms))
     result.update(_linear_workload(time_ms, peaks))
+    result.update(_dense_workload(time_ms, peaks))
     result.update(_gdn_workload(time_ms))
     return result
 
@@ -428,6 +431,29 @@ def _linear_workload(time_ms, peaks):
                      "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     return {"imported_linear": {"workload": "one token, [10240 x 5120] frozen weights, calls rotate over "
                                             "> 420 MB of distinct matrices", **out}}
+
+
+def _dense_workload(time_ms, peaks):
+    """Trainable dense projection (tcgen05 GEMMs incl. the operand casts): the GPT-2 QKV projection
+    of 8192 tokens, and a square 8192 problem against the measured cuBLAS bf16 peak."""
+    import torch
+
+    from pluto_b200.layers import DataType, DenseLayer
+
+    out = {}
+    for name, (rows, i, o) in (("gpt2_qkv_8192x768x2304", (8192, 768, 2304)), ("square_8192", (8192, 8192, 8192))):
+        layer = DenseLayer.Create(i, o, DataType.BF16)
+        layer.InitializeNormal(0.02, 1)
+        x = torch.randn(rows, i, device="cuda").bfloat16()
+        dy = torch.randn(rows, o, device="cuda")
+        fwd_ms = time_ms(lambda: layer.fwd([x]), steps=10)
+        state = layer.fwd([x]).state
+        bwd_ms = time_ms(lambda: layer.bwd([dy], state), steps=5)
+        flop = 2.0 * rows * i * o
+        out[name] = {"fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "fwd_tflops": flop / (fwd_ms * 1e-3) / 1e12,
+                     "bwd_tflops": 2 * flop / (bwd_ms * 1e-3) / 1e12,
+                     "fwd_frac_of_measured_bf16": flop / (fwd_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+    return {"dense_projection": {"workload": "bf16 activations, fp32 master weights, casts included", **out}}
 
 
 def _gqa_bwd_workload(time_ms):
@@ -532,7 +558,7 @@ def main():
     parser.add_argument("--impl", choices=["engine", "reference"], default="engine")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the secondary workloads and the CPU baseline (profiling runs)")
-    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gqa_bwd", "linear"], default=None,
+    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gqa_bwd", "linear", "dense"], default=None,
                         help="run only one secondary workload at a capture-friendly size and exit")
     args = parser.parse_args()
     if args.profile_case:

@@ -10,10 +10,11 @@
 //
 // Here the operands are first cast once into zero-padded 2-byte copies (every extent rounded up to
 // 128), so that all three products are the same kernel: C[M,N] = sum_k A(m,k) B(k,n) over
-// 128 x 128 x 64 tiles, TMA-staged through a 6-stage shared-memory ring with 128-byte swizzle,
+// 128 x 256 x 64 tiles (a 128 x 128 tile needs more shared-memory fill bandwidth per MMA cycle
+// than an SM gets from L2), TMA-staged through a 4-stage shared-memory ring with 128-byte swizzle,
 // tcgen05.mma with the accumulator in TMEM, and the two operand layouts the products need:
 //   K-major   (k contiguous:  X for the forward, dY and W for dX)
-//   MN-major  (m or n contiguous: W for the forward, X and dY for dW), read as two 64-wide slabs.
+//   MN-major  (m or n contiguous: W for the forward, X and dY for dW), read as 64-wide slabs.
 // One CTA per output tile: warp 0 issues the TMA loads, warp 1 walks the MMA schedule with one
 // elected issuing lane, warps 4-7 move the accumulator from TMEM to global memory (one row per
 // thread) adding the bias.  All waits are bounded.
@@ -25,8 +26,10 @@
 namespace pluto {
 namespace {
 
-constexpr int kTile = 128, kBK = 64, kGemmStages = 6, kGemmThreads = 256;
-constexpr int kOperandBytes = kTile * kBK * 2;   // 16 KB per operand per stage
+constexpr int kTile = 128, kTileN = 256, kBK = 64, kGemmStages = 4, kGemmThreads = 256;
+constexpr int kSlab = 64 * kBK * 2;              // one [64 x 64] 2-byte slab: 8 KB
+constexpr int kABytes = kTile * kBK * 2;         // 16 KB per stage
+constexpr int kBBytes = kTileN * kBK * 2;        // 32 KB per stage
 
 struct GemmParams {
   int M, N;            // valid extent of C
@@ -49,7 +52,7 @@ struct GemmBarriers {
 constexpr uint32_t gemm_idesc(int format, bool a_mn, bool b_mn) {
   return (1u << 4) | (static_cast<uint32_t>(format) << 7) | (static_cast<uint32_t>(format) << 10) |
          (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
-         (static_cast<uint32_t>(kTile >> 3) << 17) | (static_cast<uint32_t>(kTile >> 4) << 24);
+         (static_cast<uint32_t>(kTileN >> 3) << 17) | (static_cast<uint32_t>(kTile >> 4) << 24);
 }
 
 // grid (N tiles, M tiles)
@@ -61,10 +64,10 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* a_smem = smem;
-  uint8_t* b_smem = smem + kGemmStages * kOperandBytes;
-  GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(b_smem + kGemmStages * kOperandBytes);
+  uint8_t* b_smem = smem + kGemmStages * kABytes;
+  GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(b_smem + kGemmStages * kBBytes);
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
-  const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
+  const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTileN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGemmStages; ++s) {
@@ -75,7 +78,7 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&bar->tmem_base, kTile);
+    tmem_alloc(&bar->tmem_base, kTileN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -92,19 +95,19 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         const int st = kt % kGemmStages, use = kt / kGemmStages;
         if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, p.status, 70);
         if (!ok) break;
-        mbar_expect_tx(&bar->full[st], 2 * kOperandBytes);
-        uint8_t* a_dst = a_smem + st * kOperandBytes;
-        uint8_t* b_dst = b_smem + st * kOperandBytes;
-        if (A_MN) {   // memory [k][m]: two slabs of 64 m-columns x 64 k-rows
-          tma_load_3d(a_dst, &map_a, m0, kt * kBK, 0, &bar->full[st]);
-          tma_load_3d(a_dst + kOperandBytes / 2, &map_a, m0 + 64, kt * kBK, 0, &bar->full[st]);
+        mbar_expect_tx(&bar->full[st], kABytes + kBBytes);
+        uint8_t* a_dst = a_smem + st * kABytes;
+        uint8_t* b_dst = b_smem + st * kBBytes;
+        if (A_MN) {   // memory [k][m]: slabs of 64 m-columns x 64 k-rows
+          for (int h = 0; h < kTile / 64; ++h)
+            tma_load_3d(a_dst + h * kSlab, &map_a, m0 + 64 * h, kt * kBK, 0, &bar->full[st]);
         } else {      // memory [m][k]: 64 k-columns x 128 m-rows
           tma_load_3d(a_dst, &map_a, kt * kBK, m0, 0, &bar->full[st]);
         }
         if (B_MN) {
-          tma_load_3d(b_dst, &map_b, n0, kt * kBK, 0, &bar->full[st]);
-          tma_load_3d(b_dst + kOperandBytes / 2, &map_b, n0 + 64, kt * kBK, 0, &bar->full[st]);
-        } else {
+          for (int h = 0; h < kTileN / 64; ++h)
+            tma_load_3d(b_dst + h * kSlab, &map_b, n0 + 64 * h, kt * kBK, 0, &bar->full[st]);
+        } else {      // memory [n][k]: 64 k-columns x 256 n-rows
           tma_load_3d(b_dst, &map_b, kt * kBK, n0, 0, &bar->full[st]);
         }
       }
@@ -119,14 +122,14 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       if (!ok) break;
       tc_fence_after();
       if (elect_one()) {
-        const uint32_t a_addr = smem_u32(a_smem + st * kOperandBytes);
-        const uint32_t b_addr = smem_u32(b_smem + st * kOperandBytes);
+        const uint32_t a_addr = smem_u32(a_smem + st * kABytes);
+        const uint32_t b_addr = smem_u32(b_smem + st * kBBytes);
         // K-major: rows of 128 bytes, a K step of 16 elements is 32 bytes along the row.
         // MN-major: [64 k-rows x 128 bytes] slabs, a K step is 16 rows (2048 bytes), the second
-        // 64-wide slab sits kOperandBytes / 2 further (leading-dimension byte offset).
-        const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr, kOperandBytes / 2, 1024)
+        // 64-wide slab sits kSlab bytes further (leading-dimension byte offset).
+        const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr, kSlab, 1024)
                                      : umma_desc_sw128(a_addr, 16, 1024);
-        const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr, kOperandBytes / 2, 1024)
+        const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr, kSlab, 1024)
                                      : umma_desc_sw128(b_addr, 16, 1024);
 #pragma unroll
         for (int ks = 0; ks < kBK / 16; ++ks)
@@ -145,7 +148,7 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       const int m = m0 + row;
       const bool vec = (p.ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
 #pragma unroll
-      for (int c = 0; c < kTile / 32; ++c) {
+      for (int c = 0; c < kTileN / 32; ++c) {
         uint32_t acc[32];
         tmem_ld32(tmem + lane_base + c * 32, acc);
         tmem_wait_ld();
@@ -186,7 +189,7 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, kTile);
+    tmem_dealloc(tmem, kTileN);
   }
 }
 
@@ -235,11 +238,11 @@ int pad128(int v) { return (v + 127) / 128 * 128; }
 template <bool A_MN, bool B_MN>
 cudaError_t launch_gemm(cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b,
                         const GemmParams& p) {
-  const size_t smem = 1024 + 2 * kGemmStages * kOperandBytes + sizeof(GemmBarriers);
+  const size_t smem = 1024 + kGemmStages * (kABytes + kBBytes) + sizeof(GemmBarriers);
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  const dim3 grid((p.N + kTile - 1) / kTile, (p.M + kTile - 1) / kTile);
+  const dim3 grid((p.N + kTileN - 1) / kTileN, (p.M + kTile - 1) / kTile);
   gemm_sm100<A_MN, B_MN><<<grid, kGemmThreads, smem, stream>>>(a, b, p);
   return cudaGetLastError();
 }
@@ -304,7 +307,7 @@ cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
   const int format = half ? 0 : 1;
   CUtensorMap ma, mb;
   // dX[rows, in] = dY[rows][out] (K-major) * W^T: B(k, n) = W[n][k], memory [in][out] = K-major
-  if (!make_token_map(&ma, gc, o, r, 1, o, kTile) || !make_token_map(&mb, wc, o, i, 1, o, kTile))
+  if (!make_token_map(&ma, gc, o, r, 1, o, kTile) || !make_token_map(&mb, wc, o, i, 1, o, kTileN))
     return cudaErrorInvalidValue;
   GemmParams pdx{rows, in, o / kBK, gemm_idesc(format, false, false), nullptr, dx,
                  static_cast<size_t>(in), 0, status};
