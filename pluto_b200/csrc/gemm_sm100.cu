@@ -15,9 +15,9 @@
 // tcgen05.mma with the accumulator in TMEM, and the two operand layouts the products need:
 //   K-major   (k contiguous:  X for the forward, dY and W for dX)
 //   MN-major  (m or n contiguous: W for the forward, X and dY for dW), read as 64-wide slabs.
-// One CTA per output tile: warp 0 issues the TMA loads, warp 1 walks the MMA schedule with one
-// elected issuing lane, warps 4-7 move the accumulator from TMEM to global memory (one row per
-// thread) adding the bias.  All waits are bounded.
+// One persistent CTA per SM walks its output tiles: warp 0 issues the TMA loads, warp 1 the MMA
+// schedule with one elected issuing lane into one of two TMEM accumulators, warps 4-7 move the
+// other accumulator to global memory (one row per thread) adding the bias.  All waits are bounded.
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -43,7 +43,7 @@ struct GemmParams {
 };
 
 struct GemmBarriers {
-  uint64_t full[kGemmStages], empty[kGemmStages], done;
+  uint64_t full[kGemmStages], empty[kGemmStages], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
 };
 
@@ -55,7 +55,19 @@ constexpr uint32_t gemm_idesc(int format, bool a_mn, bool b_mn) {
          (static_cast<uint32_t>(kTileN >> 3) << 17) | (static_cast<uint32_t>(kTile >> 4) << 24);
 }
 
-// grid (N tiles, M tiles)
+// Persistent: gridDim.x CTAs (one per SM) take the output tiles i = blockIdx.x, blockIdx.x +
+// gridDim.x, ...  Tiles are numbered along M first inside bands of kBand tile columns, so the CTAs
+// that run at the same time share B tiles (and neighbouring A tiles) in L2.  Two 256-column
+// accumulators in TMEM alternate: the epilogue warps drain one while the MMA warp fills the other.
+constexpr int kBand = 4;
+__device__ __forceinline__ void tile_origin(int tile, int m_tiles, int n_tiles, int& m0, int& n0) {
+  const int band = tile / (kBand * m_tiles);
+  const int width = min(kBand, n_tiles - band * kBand);
+  const int within = tile - band * kBand * m_tiles;
+  m0 = (within / width) * kTile;
+  n0 = (band * kBand + within % width) * kTileN;
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -67,18 +79,22 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   uint8_t* b_smem = smem + kGemmStages * kABytes;
   GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(b_smem + kGemmStages * kBBytes);
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
-  const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTileN;
+  const int m_tiles = (p.M + kTile - 1) / kTile, n_tiles = (p.N + kTileN - 1) / kTileN;
+  const int tiles = m_tiles * n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGemmStages; ++s) {
       mbar_init(&bar->full[s], 1);
       mbar_init(&bar->empty[s], 1);
     }
-    mbar_init(&bar->done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar->acc_full[s], 1);
+      mbar_init(&bar->acc_empty[s], 4);   // one arrival per epilogue warp
+    }
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&bar->tmem_base, kTileN);
+    tmem_alloc(&bar->tmem_base, 2 * kTileN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -91,70 +107,87 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       tma_prefetch_desc(&map_a);
       tma_prefetch_desc(&map_b);
       bool ok = true;
-      for (int kt = 0; kt < p.k_tiles && ok; ++kt) {
-        const int st = kt % kGemmStages, use = kt / kGemmStages;
-        if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, p.status, 70);
-        if (!ok) break;
-        mbar_expect_tx(&bar->full[st], kABytes + kBBytes);
-        uint8_t* a_dst = a_smem + st * kABytes;
-        uint8_t* b_dst = b_smem + st * kBBytes;
-        if (A_MN) {   // memory [k][m]: slabs of 64 m-columns x 64 k-rows
-          for (int h = 0; h < kTile / 64; ++h)
-            tma_load_3d(a_dst + h * kSlab, &map_a, m0 + 64 * h, kt * kBK, 0, &bar->full[st]);
-        } else {      // memory [m][k]: 64 k-columns x 128 m-rows
-          tma_load_3d(a_dst, &map_a, kt * kBK, m0, 0, &bar->full[st]);
-        }
-        if (B_MN) {
-          for (int h = 0; h < kTileN / 64; ++h)
-            tma_load_3d(b_dst + h * kSlab, &map_b, n0 + 64 * h, kt * kBK, 0, &bar->full[st]);
-        } else {      // memory [n][k]: 64 k-columns x 256 n-rows
-          tma_load_3d(b_dst, &map_b, kt * kBK, n0, 0, &bar->full[st]);
+      int it = 0;   // k-tile counter over all tiles of this CTA: the ring never restarts
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        int m0, n0;
+        tile_origin(tile, m_tiles, n_tiles, m0, n0);
+        for (int kt = 0; kt < p.k_tiles && ok; ++kt, ++it) {
+          const int st = it % kGemmStages, use = it / kGemmStages;
+          if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, p.status, 70);
+          if (!ok) break;
+          mbar_expect_tx(&bar->full[st], kABytes + kBBytes);
+          uint8_t* a_dst = a_smem + st * kABytes;
+          uint8_t* b_dst = b_smem + st * kBBytes;
+          if (A_MN) {   // memory [k][m]: slabs of 64 m-columns x 64 k-rows
+            for (int h = 0; h < kTile / 64; ++h)
+              tma_load_3d(a_dst + h * kSlab, &map_a, m0 + 64 * h, kt * kBK, 0, &bar->full[st]);
+          } else {      // memory [m][k]: 64 k-columns x 128 m-rows
+            tma_load_3d(a_dst, &map_a, kt * kBK, m0, 0, &bar->full[st]);
+          }
+          if (B_MN) {
+            for (int h = 0; h < kTileN / 64; ++h)
+              tma_load_3d(b_dst + h * kSlab, &map_b, n0 + 64 * h, kt * kBK, 0, &bar->full[st]);
+          } else {      // memory [n][k]: 64 k-columns x 256 n-rows
+            tma_load_3d(b_dst, &map_b, kt * kBK, n0, 0, &bar->full[st]);
+          }
         }
       }
-      for (int kt = max(0, p.k_tiles - kGemmStages); kt < p.k_tiles; ++kt)   // copies have landed
-        mbar_wait(&bar->full[kt % kGemmStages], (kt / kGemmStages) & 1, p.status, 71);
+      for (int back = max(0, it - kGemmStages); back < it; ++back)   // the last copies have landed
+        mbar_wait(&bar->full[back % kGemmStages], (back / kGemmStages) & 1, p.status, 71);
     }
   } else if (warp == 1) {
     bool ok = true;
-    for (int kt = 0; kt < p.k_tiles && ok; ++kt) {
-      const int st = kt % kGemmStages;
-      ok = __all_sync(0xffffffffu, mbar_wait(&bar->full[st], (kt / kGemmStages) & 1, p.status, 72));
+    int it = 0, local = 0;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1, use = local >> 1;
+      if (use > 0)   // the epilogue has drained this accumulator's previous tile
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->acc_empty[buf], (use - 1) & 1, p.status, 74));
       if (!ok) break;
       tc_fence_after();
-      if (elect_one()) {
-        const uint32_t a_addr = smem_u32(a_smem + st * kABytes);
-        const uint32_t b_addr = smem_u32(b_smem + st * kBBytes);
-        // K-major: rows of 128 bytes, a K step of 16 elements is 32 bytes along the row.
-        // MN-major: [64 k-rows x 128 bytes] slabs, a K step is 16 rows (2048 bytes), the second
-        // 64-wide slab sits kSlab bytes further (leading-dimension byte offset).
-        const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr, kSlab, 1024)
-                                     : umma_desc_sw128(a_addr, 16, 1024);
-        const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr, kSlab, 1024)
-                                     : umma_desc_sw128(b_addr, 16, 1024);
+      for (int kt = 0; kt < p.k_tiles && ok; ++kt, ++it) {
+        const int st = it % kGemmStages;
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->full[st], (it / kGemmStages) & 1, p.status, 72));
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+          const uint32_t a_addr = smem_u32(a_smem + st * kABytes);
+          const uint32_t b_addr = smem_u32(b_smem + st * kBBytes);
+          // K-major: rows of 128 bytes, a K step of 16 elements is 32 bytes along the row.
+          // MN-major: [64 k-rows x 128 bytes] slabs, a K step is 16 rows (2048 bytes), the next
+          // 64-wide slab sits kSlab bytes further (leading-dimension byte offset).
+          const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr, kSlab, 1024)
+                                       : umma_desc_sw128(a_addr, 16, 1024);
+          const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr, kSlab, 1024)
+                                       : umma_desc_sw128(b_addr, 16, 1024);
 #pragma unroll
-        for (int ks = 0; ks < kBK / 16; ++ks)
-          umma_ss(tmem, a_desc + ks * ((A_MN ? 2048 : 32) >> 4), b_desc + ks * ((B_MN ? 2048 : 32) >> 4),
-                  p.idesc, kt > 0 || ks > 0);
-        tc_commit(&bar->empty[st]);
-        if (kt + 1 == p.k_tiles) tc_commit(&bar->done);
+          for (int ks = 0; ks < kBK / 16; ++ks)
+            umma_ss(tmem + buf * kTileN, a_desc + ks * ((A_MN ? 2048 : 32) >> 4),
+                    b_desc + ks * ((B_MN ? 2048 : 32) >> 4), p.idesc, kt > 0 || ks > 0);
+          tc_commit(&bar->empty[st]);
+          if (kt + 1 == p.k_tiles) tc_commit(&bar->acc_full[buf]);
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else if (warp >= 4) {
     const int quarter = warp & 3, row = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    if (mbar_wait(&bar->done, 0, p.status, 73)) {
+    const bool vec = (p.ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
+    int local = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      int m0, n0;
+      tile_origin(tile, m_tiles, n_tiles, m0, n0);
+      if (!mbar_wait(&bar->acc_full[buf], (local >> 1) & 1, p.status, 73)) break;
       tc_fence_after();
       const int m = m0 + row;
-      const bool vec = (p.ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
-#pragma unroll
+#pragma unroll 2
       for (int c = 0; c < kTileN / 32; ++c) {
         uint32_t acc[32];
-        tmem_ld32(tmem + lane_base + c * 32, acc);
+        tmem_ld32(tmem + lane_base + buf * kTileN + c * 32, acc);
         tmem_wait_ld();
-        if (m >= p.M) continue;
         const int n_base = n0 + c * 32;
-        if (n_base >= p.N) continue;
+        if (m >= p.M || n_base >= p.N) continue;
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -183,13 +216,17 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           }
         }
       }
+      // the accumulator has been read into registers by every lane of this warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->acc_empty[buf]);
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, kTileN);
+    tmem_dealloc(tmem, 2 * kTileN);
   }
 }
 
@@ -242,8 +279,11 @@ cudaError_t launch_gemm(cudaStream_t stream, const CUtensorMap& a, const CUtenso
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  const dim3 grid((p.N + kTileN - 1) / kTileN, (p.M + kTile - 1) / kTile);
-  gemm_sm100<A_MN, B_MN><<<grid, kGemmThreads, smem, stream>>>(a, b, p);
+  const int tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kTile - 1) / kTile);
+  int sms = 148, device = 0;
+  if (cudaGetDevice(&device) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  gemm_sm100<A_MN, B_MN><<<std::min(tiles, sms), kGemmThreads, smem, stream>>>(a, b, p);
   return cudaGetLastError();
 }
 
