@@ -230,44 +230,84 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   }
 }
 
-// src [rows, cols] (fp32 or bf16) -> dst [rows_p, cols_p] 2-byte (bf16 or fp16), zero padded
+// src [rows, cols] (fp32 or bf16) -> dst [rows_p, cols_p] 2-byte (bf16 or fp16), zero padded.
+// grid (cols_p / 8 / 256 rounded up, rows_p): a thread converts 8 consecutive columns.
 template <typename In, bool kHalf>
-__global__ void cast_pad_kernel(const In* __restrict__ src, uint16_t* __restrict__ dst, int rows,
-                                int cols, int rows_p, int cols_p) {
-  const size_t total = static_cast<size_t>(rows_p) * cols_p;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / cols_p), c = static_cast<int>(i % cols_p);
-    float v = 0.0f;
-    if (r < rows && c < cols) {
-      if constexpr (sizeof(In) == 4) v = src[static_cast<size_t>(r) * cols + c];
-      else v = __bfloat162float(src[static_cast<size_t>(r) * cols + c]);
+__global__ void __launch_bounds__(256)
+cast_pad_kernel(const In* __restrict__ src, uint16_t* __restrict__ dst, int rows, int cols, int cols_p) {
+  const int r = blockIdx.y;
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (c >= cols_p) return;
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+  if (r < rows && c < cols) {
+    const In* p = src + static_cast<size_t>(r) * cols + c;
+    if (c + 8 <= cols && reinterpret_cast<uintptr_t>(p) % 16 == 0) {
+      if constexpr (sizeof(In) == 4) {
+        const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      } else {
+        const uint4 a = *reinterpret_cast<const uint4*>(p);
+        v[0] = bf16_lo(a.x); v[1] = bf16_hi(a.x); v[2] = bf16_lo(a.y); v[3] = bf16_hi(a.y);
+        v[4] = bf16_lo(a.z); v[5] = bf16_hi(a.z); v[6] = bf16_lo(a.w); v[7] = bf16_hi(a.w);
+      }
+    } else {
+      for (int i = 0; i < 8 && c + i < cols; ++i) {
+        if constexpr (sizeof(In) == 4) v[i] = p[i];
+        else v[i] = __bfloat162float(p[i]);
+      }
     }
-    uint16_t bits;
-    if (kHalf) bits = __half_as_ushort(__float2half_rn(v));
-    else bits = __bfloat16_as_ushort(__float2bfloat16_rn(v));
-    dst[i] = bits;
   }
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (kHalf) {
+      const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+    }
+  }
+  *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * cols_p + c) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// db[n] = sum over rows of dy[r][n]: a CTA owns 32 columns; warp w sums rows w, w + 8, ... of its
-// columns, then the eight partial sums are added in warp order (fixed order, no atomics).
-__global__ void __launch_bounds__(256) bias_grad_kernel(const float* __restrict__ dy, int rows, int cols,
-                                                        float* __restrict__ db) {
-  __shared__ float part[8][32];
+// Column sums of dy [rows, cols] in two fixed-order levels: CTA (x, y) sums rows y, y + gridDim.y,
+// ... of its 128 columns (a lane owns 4, the 8 warps split the rows and are added in warp order)
+// into partial[y][cols]; the second kernel adds the partial rows in order.
+constexpr int kBiasChunks = 16;
+__global__ void __launch_bounds__(256) bias_partial_kernel(const float* __restrict__ dy, int rows, int cols,
+                                                           float* __restrict__ partial) {
+  __shared__ float part[8][128];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int n = blockIdx.x * 32 + lane;
-  float sum = 0.0f;
-  if (n < cols)
-    for (int r = warp; r < rows; r += 8) sum += dy[static_cast<size_t>(r) * cols + n];
-  part[warp][lane] = sum;
+  const int n = blockIdx.x * 128 + lane * 4;
+  float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  const bool vec = cols % 4 == 0 && reinterpret_cast<uintptr_t>(dy) % 16 == 0 && n + 4 <= cols;
+  for (int r = blockIdx.y * 8 + warp; r < rows; r += gridDim.y * 8) {
+    const float* p = dy + static_cast<size_t>(r) * cols + n;
+    if (vec) {
+      const float4 v = *reinterpret_cast<const float4*>(p);
+      sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+    } else {
+      for (int i = 0; i < 4 && n + i < cols; ++i) sum[i] += p[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) part[warp][lane * 4 + i] = sum[i];
   __syncthreads();
-  if (warp == 0 && n < cols) {
+  if (threadIdx.x < 128 && blockIdx.x * 128 + threadIdx.x < cols) {
     float total = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) total += part[w][lane];
-    db[n] = total;
+    for (int w = 0; w < 8; ++w) total += part[w][threadIdx.x];
+    partial[static_cast<size_t>(blockIdx.y) * cols + blockIdx.x * 128 + threadIdx.x] = total;
   }
+}
+__global__ void bias_final_kernel(const float* __restrict__ partial, int chunks, int cols, float* __restrict__ db) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= cols) return;
+  float total = 0.0f;
+  for (int c = 0; c < chunks; ++c) total += partial[static_cast<size_t>(c) * cols + n];
+  db[n] = total;
 }
 
 int pad128(int v) { return (v + 127) / 128 * 128; }
@@ -290,22 +330,42 @@ cudaError_t launch_gemm(cudaStream_t stream, const CUtensorMap& a, const CUtenso
 template <typename In>
 cudaError_t cast_pad(cudaStream_t stream, const void* src, void* dst, int rows, int cols, bool half) {
   const int rows_p = pad128(rows), cols_p = pad128(cols);
-  const size_t total = static_cast<size_t>(rows_p) * cols_p;
-  const unsigned blocks = static_cast<unsigned>(std::min<size_t>((total + 255) / 256, 148 * 16));
+  const dim3 grid((cols_p / 8 + 255) / 256, rows_p);
   if (half)
-    cast_pad_kernel<In, true><<<blocks, 256, 0, stream>>>(static_cast<const In*>(src),
-                                                           static_cast<uint16_t*>(dst), rows, cols, rows_p, cols_p);
+    cast_pad_kernel<In, true><<<grid, 256, 0, stream>>>(static_cast<const In*>(src),
+                                                         static_cast<uint16_t*>(dst), rows, cols, cols_p);
   else
-    cast_pad_kernel<In, false><<<blocks, 256, 0, stream>>>(static_cast<const In*>(src),
-                                                            static_cast<uint16_t*>(dst), rows, cols, rows_p, cols_p);
+    cast_pad_kernel<In, false><<<grid, 256, 0, stream>>>(static_cast<const In*>(src),
+                                                          static_cast<uint16_t*>(dst), rows, cols, cols_p);
   return cudaGetLastError();
+}
+
+// The bf16 activation can be read by TMA in place (rows and columns past its extent read as zero)
+// when its rows are 16-byte aligned; otherwise, and for fp32 activations, a padded 2-byte copy is made.
+struct Operand {
+  const void* base;
+  int cols, rows;        // extents the tensor map describes
+  size_t pitch;          // elements between rows
+};
+cudaError_t activation_operand(cudaStream_t stream, const void* x, bool x_is_bf16, int rows, int cols,
+                               void* copy, Operand* out) {
+  if (x_is_bf16 && cols % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0) {
+    *out = Operand{x, cols, rows, static_cast<size_t>(cols)};
+    return cudaSuccess;
+  }
+  *out = Operand{copy, pad128(cols), pad128(rows), static_cast<size_t>(pad128(cols))};
+  return x_is_bf16 ? cast_pad<__nv_bfloat16>(stream, x, copy, rows, cols, false)
+                   : cast_pad<float>(stream, x, copy, rows, cols, true);
+}
+bool operand_map(CUtensorMap* map, const Operand& t, int box_rows) {
+  return make_token_map(map, t.base, t.cols, t.rows, 1, t.pitch, box_rows);
 }
 
 }  // namespace
 
 size_t dense_workspace_bytes(int rows, int in, int out) {
   const size_t r = pad128(rows), i = pad128(in), o = pad128(out);
-  return 2 * (r * i + i * o + r * o);   // casts of X, W, dY
+  return 2 * (r * i + i * o + r * o) + sizeof(float) * kBiasChunks * o;   // casts of X, W, dY; bias partials
 }
 
 // x: [rows, in] bf16 (x_is_bf16) or fp32; w fp32 [in, out]; bias fp32 [out]; y same dtype as x.
@@ -316,13 +376,13 @@ cudaError_t dense_fwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
   auto* xc = static_cast<uint8_t*>(workspace);
   auto* wc = xc + 2 * static_cast<size_t>(r) * i;
   const bool half = !x_is_bf16;
-  cudaError_t e = x_is_bf16 ? cast_pad<__nv_bfloat16>(stream, x, xc, rows, in, half)
-                            : cast_pad<float>(stream, x, xc, rows, in, half);
+  Operand xo;
+  cudaError_t e = activation_operand(stream, x, x_is_bf16, rows, in, xc, &xo);
   if (e != cudaSuccess) return e;
   e = cast_pad<float>(stream, w, wc, in, out, half);
   if (e != cudaSuccess) return e;
   CUtensorMap ma, mb;
-  if (!make_token_map(&ma, xc, i, r, 1, i, kTile) ||       // A K-major: [rows][in]
+  if (!operand_map(&ma, xo, kTile) ||                      // A K-major: [rows][in]
       !make_token_map(&mb, wc, o, i, 1, o, kBK))           // B MN-major: [in][out]
     return cudaErrorInvalidValue;
   GemmParams p{rows, out, i / kBK, gemm_idesc(half ? 0 : 1, false, true), bias, y,
@@ -339,8 +399,8 @@ cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
   auto* wc = xc + 2 * static_cast<size_t>(r) * i;
   auto* gc = wc + 2 * static_cast<size_t>(i) * o;
   const bool half = !x_is_bf16;
-  cudaError_t e = x_is_bf16 ? cast_pad<__nv_bfloat16>(stream, x, xc, rows, in, half)
-                            : cast_pad<float>(stream, x, xc, rows, in, half);
+  Operand xo;
+  cudaError_t e = activation_operand(stream, x, x_is_bf16, rows, in, xc, &xo);
   if (e == cudaSuccess) e = cast_pad<float>(stream, w, wc, in, out, half);
   if (e == cudaSuccess) e = cast_pad<float>(stream, dy, gc, rows, out, half);
   if (e != cudaSuccess) return e;
@@ -354,13 +414,17 @@ cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
   e = launch_gemm<false, false>(stream, ma, mb, pdx);
   if (e != cudaSuccess) return e;
   // dW[in, out] = X^T dY: A(m, k) = X[k][m], memory [rows][in] = MN-major; B = dY [rows][out] MN-major
-  if (!make_token_map(&ma, xc, i, r, 1, i, kBK) || !make_token_map(&mb, gc, o, r, 1, o, kBK))
+  if (!operand_map(&ma, xo, kBK) || !make_token_map(&mb, gc, o, r, 1, o, kBK))
     return cudaErrorInvalidValue;
   GemmParams pdw{in, out, r / kBK, gemm_idesc(format, true, true), nullptr, dw,
                  static_cast<size_t>(out), 0, status};
   e = launch_gemm<true, true>(stream, ma, mb, pdw);
   if (e != cudaSuccess) return e;
-  bias_grad_kernel<<<(out + 31) / 32, 256, 0, stream>>>(dy, rows, out, db);
+  float* partial = reinterpret_cast<float*>(gc + 2 * static_cast<size_t>(r) * o);
+  bias_partial_kernel<<<dim3((out + 127) / 128, kBiasChunks), 256, 0, stream>>>(dy, rows, out, partial);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  bias_final_kernel<<<(out + 255) / 256, 256, 0, stream>>>(partial, kBiasChunks, out, db);
   return cudaGetLastError();
 }
 
