@@ -437,6 +437,28 @@ int pluto_dense_bwd(pluto_stream_t stream, const void* input, int dtype, const f
                     size_t workspace_bytes);
 
 /* --------------------------------------------------------------------------------------------
+ * BlockLinearLayer and DequantizeMatrix (src/llm/layers/block_training.h:11-83,
+ * block_training.cc:19-98, 281-399): resident bf16 weight [output_dim, input_dim] (output-major,
+ * no bias), bf16 input [tokens, input_dim].
+ *   forward   output[t][r] = sum_c x[t][c] W[r][c], fp32 accumulation, bf16 or fp32 output
+ *   backward  input_gradient fp32 [tokens, input_dim] = dY W;  weight_gradient fp32
+ *             [output_dim, input_dim] += dY^T x (ACCUMULATED; null for a frozen weight)
+ * All three are tcgen05 GEMMs on the bf16 values; the fp32 dY enters as hi + lo bf16 halves so its
+ * products keep 16 mantissa bits.  workspace: pluto_block_linear_workspace_bytes, 256-byte aligned.
+ * pluto_dequantize_matrix converts an fp32 or FP8-E4M3 (fp32 block scales [ceil(rows/128),
+ * ceil(cols/128)]) matrix to the resident bf16 form; bf16 matrices are shared, not converted. */
+size_t pluto_block_linear_workspace_bytes(int tokens, int input_dim, int output_dim);
+int pluto_block_linear_fwd(pluto_stream_t stream, const void* weight, const void* input, void* output,
+                           int output_dtype, int tokens, int input_dim, int output_dim,
+                           void* workspace, size_t workspace_bytes);
+int pluto_block_linear_bwd(pluto_stream_t stream, const void* weight, const void* input,
+                           const float* output_gradient, float* input_gradient,
+                           float* weight_gradient, int tokens, int input_dim, int output_dim,
+                           void* workspace, size_t workspace_bytes);
+int pluto_dequantize_matrix(pluto_stream_t stream, const void* input, int storage, const float* scales,
+                            void* output, int rows, int cols);
+
+/* --------------------------------------------------------------------------------------------
  * Head-sharded multi-GPU support.  The reference is single-GPU (its only cudaSetDevice pins a
  * thread pool to one device, src/cuda/thread_pool.h:19-22, src/cuda/thread_pool.cc:109), so this
  * has no kernel to mirror: it is the local half of "all-gather the head-sharded output" for a

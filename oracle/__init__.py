@@ -372,3 +372,18 @@ def dense_bwd(x, w, dy, bf16: bool):
     xc, wc, gc = (_mma_cast(a, bf16).astype(np.float64) for a in (x, w, dy))
     return {"dx": (gc @ wc.T).astype(np.float32), "dw": (xc.T @ gc).astype(np.float32),
             "db": np.asarray(dy, np.float64).sum(0).astype(np.float32)}
+
+
+def block_linear_fwd(w_bf16, x_bf16, output_float32: bool) -> np.ndarray:
+    """LinearForward (block_training.cc:38-56): y[t][r] = sum_c x[t][c] w[r][c] over the bf16
+    values in fp32 arithmetic (here in double: every product is exact, only the sum order differs)."""
+    y = (np.asarray(x_bf16, np.float64) @ np.asarray(w_bf16, np.float64).T).astype(np.float32)
+    return y if output_float32 else round_bf16(y)
+
+
+def block_linear_bwd(w_bf16, x_bf16, dy):
+    """LinearInputGradient / LinearWeightGradient (block_training.cc:58-98): fp32 dy against the
+    bf16 weight and input values; dw is the increment the layer adds to its accumulator."""
+    dy = np.asarray(dy, np.float64)
+    return {"dx": (dy @ np.asarray(w_bf16, np.float64)).astype(np.float32),
+            "dw": (dy.T @ np.asarray(x_bf16, np.float64)).astype(np.float32)}

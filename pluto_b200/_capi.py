@@ -40,6 +40,10 @@ _SIGNATURES = {
     "pluto_dense_workspace_bytes": (_sz, [_i] * 3),
     "pluto_dense_fwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _sz]),
     "pluto_dense_bwd": (_i, [_vp, _vp, _i] + [_vp] * 5 + [_i, _i, _i, _vp, _sz]),
+    "pluto_block_linear_workspace_bytes": (_sz, [_i] * 3),
+    "pluto_block_linear_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz]),
+    "pluto_block_linear_bwd": (_i, [_vp] * 6 + [_i, _i, _i, _vp, _sz]),
+    "pluto_dequantize_matrix": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i]),
     "pluto_gqa_gate_bwd": (_i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _sz, _sz, _vp] + [_i] * 5),
     "pluto_gqa_prefill_bwd": (_i, [_vp] * 4 + [_i, _sz, _sz] + [_vp] * 8 + [_sz] + [_i] * 5),
     "pluto_gqa_prefill_bwd_workspace_bytes": (_sz, [_i] * 5),

@@ -698,6 +698,68 @@ int pluto_dense_bwd(pluto_stream_t stream, const void* input, int dtype, const f
                    "dense backward launch");
 }
 
+size_t pluto_block_linear_workspace_bytes(int tokens, int input_dim, int output_dim) {
+  if (tokens <= 0 || input_dim <= 0 || output_dim <= 0) return 0;
+  return pluto::block_linear_workspace_bytes(tokens, input_dim, output_dim);
+}
+
+namespace {
+int check_block_linear(int tokens, int input_dim, int output_dim, const void* workspace,
+                       size_t workspace_bytes) {
+  if (tokens <= 0 || input_dim <= 0 || output_dim <= 0 || input_dim > 1048576 || output_dim > 1048576 ||
+      static_cast<long long>(tokens) * input_dim > 0x7fffffffLL ||
+      static_cast<long long>(tokens) * output_dim > 0x7fffffffLL)
+    return fail(PLUTO_E_INVALID, "invalid block parameter dimensions, storage or executor");
+  if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 ||
+      workspace_bytes < pluto_block_linear_workspace_bytes(tokens, input_dim, output_dim))
+    return fail(PLUTO_E_INVALID, "block linear workspace is missing, misaligned or too small");
+  return PLUTO_OK;
+}
+}  // namespace
+
+int pluto_block_linear_fwd(pluto_stream_t stream, const void* weight, const void* input, void* output,
+                           int output_dtype, int tokens, int input_dim, int output_dim,
+                           void* workspace, size_t workspace_bytes) {
+  if (int rc = check_block_linear(tokens, input_dim, output_dim, workspace, workspace_bytes)) return rc;
+  if (!weight || !input || !output || !dtype_ok(output_dtype))
+    return fail(PLUTO_E_INVALID, "linear requires one input");
+  uint32_t* status = pluto::kernel_status_word();
+  if (!status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
+  return from_cuda(pluto::block_linear_fwd(stream, weight, input, output, output_dtype == PLUTO_FP32,
+                                           tokens, input_dim, output_dim, workspace, status),
+                   "block linear forward");
+}
+
+int pluto_block_linear_bwd(pluto_stream_t stream, const void* weight, const void* input,
+                           const float* output_gradient, float* input_gradient,
+                           float* weight_gradient, int tokens, int input_dim, int output_dim,
+                           void* workspace, size_t workspace_bytes) {
+  if (int rc = check_block_linear(tokens, input_dim, output_dim, workspace, workspace_bytes)) return rc;
+  if (!weight || !input || !output_gradient || !input_gradient)
+    return fail(PLUTO_E_INVALID, "invalid linear backward state/gradient");
+  uint32_t* status = pluto::kernel_status_word();
+  if (!status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
+  return from_cuda(pluto::block_linear_bwd(stream, weight, input, output_gradient, input_gradient,
+                                           weight_gradient, tokens, input_dim, output_dim, workspace,
+                                           status),
+                   "block linear input gradient");
+}
+
+int pluto_dequantize_matrix(pluto_stream_t stream, const void* input, int storage, const float* scales,
+                            void* output, int rows, int cols) {
+  if (rows <= 0 || cols <= 0 || rows > 1048576 || cols > 1048576)
+    return fail(PLUTO_E_INVALID, "invalid imported matrix shape");
+  if (storage != PLUTO_MATRIX_FP32 && storage != PLUTO_MATRIX_FP8_E4M3)
+    return fail(PLUTO_E_INVALID, "only FP32 and FP8 matrices are converted (BF16 is shared)");
+  if (storage == PLUTO_MATRIX_FP8_E4M3 && !scales) return fail(PLUTO_E_INVALID, "FP8 matrix requires scales");
+  if (storage != PLUTO_MATRIX_FP8_E4M3 && scales)
+    return fail(PLUTO_E_INVALID, "non-FP8 matrix must not have scales");
+  if (!input || !output) return fail(PLUTO_E_INVALID, "imported matrix requires non-null device pointers");
+  return from_cuda(pluto::dequantize_matrix(stream, input, storage == PLUTO_MATRIX_FP32 ? 1 : 2, scales,
+                                            rows, cols, output),
+                   "DequantizeKernel launch");
+}
+
 }  // extern "C"
 
 extern "C" int pluto_interleave_heads(pluto_stream_t stream, const void* gathered, void* out,

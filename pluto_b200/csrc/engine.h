@@ -220,6 +220,18 @@ cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
                       const float* dy, float* dx, float* dw, float* db, int rows, int in, int out,
                       void* workspace, uint32_t* status);
 
+// BlockLinearLayer: resident bf16 weight [out, in], bf16 x [tokens, in]; see gemm_sm100.cu
+size_t block_linear_workspace_bytes(int tokens, int in, int out);
+cudaError_t block_linear_fwd(cudaStream_t stream, const void* weight, const void* x, void* y,
+                             bool y_is_fp32, int tokens, int in, int out, void* workspace,
+                             uint32_t* status);
+cudaError_t block_linear_bwd(cudaStream_t stream, const void* weight, const void* x, const float* dy,
+                             float* dx, float* d_weight, int tokens, int in, int out, void* workspace,
+                             uint32_t* status);
+// storage 1 = fp32, 2 = FP8 E4M3 with block scales -> bf16 [rows, cols]
+cudaError_t dequantize_matrix(cudaStream_t stream, const void* input, int storage, const float* scales,
+                              long long rows, int cols, void* output);
+
 // gdn_bwd.cu: backward of the sequence layer
 struct GdnBwdArgs {
   const void* q;            // convolved + SiLU'd activations, as GdnArgs (raw, not normalised)

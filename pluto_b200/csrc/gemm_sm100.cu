@@ -19,6 +19,7 @@
 // schedule with one elected issuing lane into one of two TMEM accumulators, warps 4-7 move the
 // other accumulator to global memory (one row per thread) adding the bias.  All waits are bounded.
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "common.cuh"
 #include "engine.h"
@@ -33,7 +34,10 @@ constexpr int kBBytes = kTileN * kBK * 2;        // 32 KB per stage
 
 struct GemmParams {
   int M, N;            // valid extent of C
-  int k_tiles;         // padded K / 64
+  int k_tiles;         // K steps of 64 (over both halves of a split operand)
+  int a_wrap, b_wrap;  // K steps per half: step kt reads A at (kt % a_wrap, half kt / a_wrap) and B at
+                       // kt % b_wrap, so [hi | lo] * [B; B] needs neither B twice nor a wide A
+  int c_accumulate;    // add to C instead of overwriting (single writer per element)
   uint32_t idesc;
   const float* bias;   // optional [N]
   void* c;             // row-major, ldc elements between rows
@@ -118,17 +122,18 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           mbar_expect_tx(&bar->full[st], kABytes + kBBytes);
           uint8_t* a_dst = a_smem + st * kABytes;
           uint8_t* b_dst = b_smem + st * kBBytes;
+          const int ka = (kt % p.a_wrap) * kBK, half = kt / p.a_wrap, kb = (kt % p.b_wrap) * kBK;
           if (A_MN) {   // memory [k][m]: slabs of 64 m-columns x 64 k-rows
             for (int h = 0; h < kTile / 64; ++h)
-              tma_load_3d(a_dst + h * kSlab, &map_a, m0 + 64 * h, kt * kBK, 0, &bar->full[st]);
+              tma_load_3d(a_dst + h * kSlab, &map_a, m0 + 64 * h, ka, half, &bar->full[st]);
           } else {      // memory [m][k]: 64 k-columns x 128 m-rows
-            tma_load_3d(a_dst, &map_a, kt * kBK, m0, 0, &bar->full[st]);
+            tma_load_3d(a_dst, &map_a, ka, m0, half, &bar->full[st]);
           }
           if (B_MN) {
             for (int h = 0; h < kTileN / 64; ++h)
-              tma_load_3d(b_dst + h * kSlab, &map_b, n0 + 64 * h, kt * kBK, 0, &bar->full[st]);
+              tma_load_3d(b_dst + h * kSlab, &map_b, n0 + 64 * h, kb, 0, &bar->full[st]);
           } else {      // memory [n][k]: 64 k-columns x 256 n-rows
-            tma_load_3d(b_dst, &map_b, kt * kBK, n0, 0, &bar->full[st]);
+            tma_load_3d(b_dst, &map_b, kb, n0, 0, &bar->full[st]);
           }
         }
       }
@@ -196,6 +201,9 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         }
         if (p.c_kind == 0) {
           float* dst = static_cast<float*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
+          if (p.c_accumulate) {
+            for (int i = 0; i < 32 && n_base + i < p.N; ++i) v[i] += dst[i];
+          }
           if (vec && n_base + 32 <= p.N) {
 #pragma unroll
             for (int i = 0; i < 32; i += 4)
@@ -385,7 +393,7 @@ cudaError_t dense_fwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
   if (!operand_map(&ma, xo, kTile) ||                      // A K-major: [rows][in]
       !make_token_map(&mb, wc, o, i, 1, o, kBK))           // B MN-major: [in][out]
     return cudaErrorInvalidValue;
-  GemmParams p{rows, out, i / kBK, gemm_idesc(half ? 0 : 1, false, true), bias, y,
+  GemmParams p{rows, out, i / kBK, i / kBK, i / kBK, 0, gemm_idesc(half ? 0 : 1, false, true), bias, y,
                static_cast<size_t>(out), x_is_bf16 ? 1 : 0, status};
   return launch_gemm<false, true>(stream, ma, mb, p);
 }
@@ -409,14 +417,14 @@ cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
   // dX[rows, in] = dY[rows][out] (K-major) * W^T: B(k, n) = W[n][k], memory [in][out] = K-major
   if (!make_token_map(&ma, gc, o, r, 1, o, kTile) || !make_token_map(&mb, wc, o, i, 1, o, kTileN))
     return cudaErrorInvalidValue;
-  GemmParams pdx{rows, in, o / kBK, gemm_idesc(format, false, false), nullptr, dx,
+  GemmParams pdx{rows, in, o / kBK, o / kBK, o / kBK, 0, gemm_idesc(format, false, false), nullptr, dx,
                  static_cast<size_t>(in), 0, status};
   e = launch_gemm<false, false>(stream, ma, mb, pdx);
   if (e != cudaSuccess) return e;
   // dW[in, out] = X^T dY: A(m, k) = X[k][m], memory [rows][in] = MN-major; B = dY [rows][out] MN-major
   if (!operand_map(&ma, xo, kBK) || !make_token_map(&mb, gc, o, r, 1, o, kBK))
     return cudaErrorInvalidValue;
-  GemmParams pdw{in, out, r / kBK, gemm_idesc(format, true, true), nullptr, dw,
+  GemmParams pdw{in, out, r / kBK, r / kBK, r / kBK, 0, gemm_idesc(format, true, true), nullptr, dw,
                  static_cast<size_t>(out), 0, status};
   e = launch_gemm<true, true>(stream, ma, mb, pdw);
   if (e != cudaSuccess) return e;
@@ -425,6 +433,147 @@ cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   bias_final_kernel<<<(out + 255) / 256, 256, 0, stream>>>(partial, kBiasChunks, out, db);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// BlockLinearLayer (src/llm/layers/block_training.cc:38-98, 321-399): resident bf16 weight
+// [out, in] (output-major, no bias), bf16 activations, fp32 arithmetic on the exact bf16 values.
+//   forward          Y[t][r]  = sum_c X[t][c] W[r][c]                       bf16 or fp32 output
+//   input gradient   dX[t][c] = sum_r dY[t][r] W[r][c]                      fp32
+//   weight gradient  dW[r][c] += sum_t dY[t][r] X[t][c]                     fp32, accumulated
+// bf16 x bf16 products are exact in fp32, so the forward is the tensor-core GEMM as it is.  The
+// gradients multiply an fp32 dY: it is split into hi = bf16(dY) and lo = bf16(dY - hi) (relative
+// error 2^-17 instead of bf16's 2^-9) and both halves are accumulated into the same TMEM tile:
+// [hi | lo] x [W; W], with the second pass re-reading the same W / X tiles (b_wrap).
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+// dst[0] = bf16(src), dst[1] = bf16(src - dst[0]); both [rows_p][cols_p], zero padded
+__global__ void __launch_bounds__(256)
+split_pad_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, int rows, int cols,
+                 int rows_p, int cols_p) {
+  const int r = blockIdx.y;
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (c >= cols_p) return;
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+  if (r < rows && c < cols) {
+    const float* p = src + static_cast<size_t>(r) * cols + c;
+    if (c + 8 <= cols && reinterpret_cast<uintptr_t>(p) % 16 == 0) {
+      const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+      for (int i = 0; i < 8 && c + i < cols; ++i) v[i] = p[i];
+    }
+  }
+  uint32_t hi[4], lo[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float h0 = bf16_round(v[2 * i]), h1 = bf16_round(v[2 * i + 1]);
+    hi[i] = pack_bf16(h0, h1);
+    lo[i] = pack_bf16(v[2 * i] - h0, v[2 * i + 1] - h1);
+  }
+  const size_t at = static_cast<size_t>(r) * cols_p + c;
+  *reinterpret_cast<uint4*>(dst + at) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rows_p) * cols_p + at) =
+      make_uint4(lo[0], lo[1], lo[2], lo[3]);
+}
+
+// DequantizeKernel (block_training.cc:19-36): fp32 or FP8 E4M3 (x block scale) -> bf16
+__global__ void dequantize_kernel(const void* __restrict__ input, int storage, const float* __restrict__ scales,
+                                  long long rows, int cols, __nv_bfloat16* __restrict__ output) {
+  const long long total = rows * cols;
+  const int scale_cols = (cols + 127) / 128;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float v;
+    if (storage == 1) {
+      v = static_cast<const float*>(input)[i];
+    } else {
+      const long long r = i / cols;
+      const int c = static_cast<int>(i % cols);
+      const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<const uint8_t*>(input)[i], __NV_E4M3);
+      v = __half2float(*reinterpret_cast<const __half*>(&h)) * scales[(r / 128) * scale_cols + c / 128];
+    }
+    output[i] = __float2bfloat16_rn(v);
+  }
+}
+
+// A bf16 matrix [rows][cols] as a TMA operand: in place when its rows are 16-byte aligned, else
+// through a padded copy.
+cudaError_t bf16_operand(cudaStream_t stream, const void* x, int rows, int cols, void* copy, Operand* out) {
+  return activation_operand(stream, x, true, rows, cols, copy, out);
+}
+
+}  // namespace
+
+size_t block_linear_workspace_bytes(int tokens, int in, int out) {
+  const size_t t = pad128(tokens), i = pad128(in), o = pad128(out);
+  return 2 * (t * i + o * i + 2 * t * o);   // copies of X and W (only if unaligned), hi/lo split of dY
+}
+
+cudaError_t block_linear_fwd(cudaStream_t stream, const void* weight, const void* x, void* y,
+                             bool y_is_fp32, int tokens, int in, int out, void* workspace,
+                             uint32_t* status) {
+  const size_t t = pad128(tokens), i = pad128(in), o = pad128(out);
+  auto* xc = static_cast<uint8_t*>(workspace);
+  auto* wc = xc + 2 * t * i;
+  Operand xo, wo;
+  cudaError_t e = bf16_operand(stream, x, tokens, in, xc, &xo);
+  if (e == cudaSuccess) e = bf16_operand(stream, weight, out, in, wc, &wo);
+  if (e != cudaSuccess) return e;
+  CUtensorMap ma, mb;
+  if (!operand_map(&ma, xo, kTile) || !operand_map(&mb, wo, kTileN)) return cudaErrorInvalidValue;
+  const int k_tiles = static_cast<int>(i / kBK);
+  GemmParams p{tokens, out, k_tiles, k_tiles, k_tiles, 0, gemm_idesc(1, false, false), nullptr, y,
+               static_cast<size_t>(out), y_is_fp32 ? 0 : 1, status};
+  return launch_gemm<false, false>(stream, ma, mb, p);
+}
+
+cudaError_t block_linear_bwd(cudaStream_t stream, const void* weight, const void* x, const float* dy,
+                             float* dx, float* d_weight, int tokens, int in, int out, void* workspace,
+                             uint32_t* status) {
+  const size_t t = pad128(tokens), i = pad128(in), o = pad128(out);
+  auto* xc = static_cast<uint8_t*>(workspace);
+  auto* wc = xc + 2 * t * i;
+  auto* gc = wc + 2 * o * i;
+  Operand xo, wo;
+  cudaError_t e = bf16_operand(stream, weight, out, in, wc, &wo);
+  if (e == cudaSuccess && d_weight != nullptr) e = bf16_operand(stream, x, tokens, in, xc, &xo);
+  if (e != cudaSuccess) return e;
+  split_pad_kernel<<<dim3((static_cast<unsigned>(o) / 8 + 255) / 256, static_cast<unsigned>(t)), 256, 0,
+                     stream>>>(dy, reinterpret_cast<uint16_t*>(gc), tokens, out, static_cast<int>(t),
+                               static_cast<int>(o));
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  // hi and lo of dY as the two "batches" of one 3-D tensor [2][tokens_p][out_p]
+  CUtensorMap ma, mb;
+  // dX[tokens, in]: A = dY halves, K-major over out; B(k = r, n = c) = W[r][c]: MN-major, wraps
+  if (!make_token_map(&ma, gc, static_cast<int>(o), static_cast<int>(t), 2, o, kTile) ||
+      !operand_map(&mb, wo, kBK))
+    return cudaErrorInvalidValue;
+  const int ko = static_cast<int>(o / kBK), kt = static_cast<int>(t / kBK);
+  GemmParams pdx{tokens, in, 2 * ko, ko, ko, 0, gemm_idesc(1, false, true), nullptr, dx,
+                 static_cast<size_t>(in), 0, status};
+  e = launch_gemm<false, true>(stream, ma, mb, pdx);
+  if (e != cudaSuccess || d_weight == nullptr) return e;
+  // dW[out, in] += dY^T X: A(m = r, k = t) = dY[t][r]: MN-major halves over tokens; B = X MN-major
+  if (!make_token_map(&ma, gc, static_cast<int>(o), static_cast<int>(t), 2, o, kBK) ||
+      !operand_map(&mb, xo, kBK))
+    return cudaErrorInvalidValue;
+  GemmParams pdw{out, in, 2 * kt, kt, kt, 1, gemm_idesc(1, true, true), nullptr, d_weight,
+                 static_cast<size_t>(in), 0, status};
+  return launch_gemm<true, true>(stream, ma, mb, pdw);
+}
+
+cudaError_t dequantize_matrix(cudaStream_t stream, const void* input, int storage, const float* scales,
+                              long long rows, int cols, void* output) {
+  const long long total = rows * cols;
+  const unsigned blocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 148 * 32));
+  dequantize_kernel<<<blocks, 256, 0, stream>>>(input, storage, scales, rows, cols,
+                                                static_cast<__nv_bfloat16*>(output));
   return cudaGetLastError();
 }
 

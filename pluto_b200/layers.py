@@ -92,8 +92,8 @@ class BlockParameter:
 
     @staticmethod
     def Create(value: torch.Tensor) -> "BlockParameter":
-        if value is None or value.dtype != torch.float32 or not value.is_cuda:
-            raise _invalid("BlockParameter requires an FP32 device buffer")
+        if value is None or value.dtype not in (torch.float32, torch.bfloat16) or not value.is_cuda:
+            raise _invalid("BlockParameter requires an FP32 or BF16 device buffer")
         return BlockParameter(value)
 
     def value(self) -> torch.Tensor:
@@ -103,8 +103,11 @@ class BlockParameter:
         return self.gradient_ is not None
 
     def Activate(self) -> None:
-        if self.gradient_ is None:
-            self.gradient_ = torch.zeros_like(self.value_)
+        if self.gradient_ is None:   # the gradient (optimizer storage) is fp32 whatever the value is
+            self.gradient_ = torch.zeros(self.value_.shape, dtype=torch.float32, device=self.value_.device)
+
+    def Deactivate(self) -> None:
+        self.gradient_ = None
 
     def gradient(self) -> Optional[torch.Tensor]:
         return self.gradient_
@@ -1241,4 +1244,111 @@ class DenseLayer(Layer):
             _stream(), _ptr(x), 1 if self.output_type_ == DataType.BF16 else 0, _ptr(self.weights_[0]),
             _ptr(dy), _ptr(dx), _ptr(self.gradients_[0]), _ptr(self.gradients_[1]), rows,
             self.input_dim_, self.output_dim_, ptr, need))
+        return [dx]
+
+
+def DequantizeMatrix(input: torch.Tensor, storage: MatrixStorage, scales: Optional[torch.Tensor],
+                     rows: int, cols: int) -> torch.Tensor:
+    """src/llm/layers/block_training.cc:281-319: an imported matrix as resident bf16 storage.
+    bf16 inputs are shared, fp32 and FP8 (with block scales) are converted."""
+    if rows <= 0 or cols <= 0 or rows > 1048576 or cols > 1048576:
+        raise _invalid("invalid imported matrix shape")
+    if not isinstance(storage, MatrixStorage):
+        raise _invalid("unknown matrix storage")
+    if input is None or not input.is_cuda or \
+            input.numel() * input.element_size() != rows * cols * _matrix_element_bytes(storage):
+        raise _invalid("block training requires the owning executor, exact dimensions and batch size one")
+    if storage == MatrixStorage.kFp8E4M3:
+        if scales is None:
+            raise _invalid("FP8 matrix requires scales")
+        if not scales.is_cuda or scales.numel() * scales.element_size() != \
+                ((rows + 127) // 128) * ((cols + 127) // 128) * 4:
+            raise _invalid("block training requires the owning executor, exact dimensions and batch size one")
+    elif scales is not None:
+        raise _invalid("non-FP8 matrix must not have scales")
+    if storage == MatrixStorage.kBFloat16:
+        return input
+    output = torch.empty((rows, cols), dtype=torch.bfloat16, device=input.device)
+    check(_capi.lib().pluto_dequantize_matrix(_stream(), _ptr(input), storage.value, _ptr(scales),
+                                              _ptr(output), rows, cols))
+    return output
+
+
+class BlockLinearLayer(Layer):
+    """Bias-free [output, input] bf16 matrix with bf16 forward and fp32 backward
+    (src/llm/layers/block_training.h:49-83, .cc:321-399).  A frozen weight still propagates input
+    gradients but never accumulates a weight gradient; an active BlockParameter's gradient is
+    accumulated into.  One sample of sequence_length tokens."""
+
+    def __init__(self, weight, input_dim, output_dim, sequence_length, output_float32):
+        self.parameter_ = weight
+        self.weights_ = [weight.value()]
+        self.input_dim_, self.output_dim_ = input_dim, output_dim
+        self.sequence_length_, self.output_float32_ = sequence_length, output_float32
+
+    @staticmethod
+    def Create(weight: BlockParameter, input_dim: int, output_dim: int, sequence_length: int,
+               output_float32: bool = False) -> "BlockLinearLayer":
+        if (weight is None or input_dim <= 0 or output_dim <= 0 or sequence_length <= 0
+                or input_dim > 1048576 or output_dim > 1048576
+                or sequence_length * input_dim > 2 ** 31 - 1 or sequence_length * output_dim > 2 ** 31 - 1
+                or weight.value().dtype != torch.bfloat16 or not weight.value().is_cuda
+                or weight.value().numel() != input_dim * output_dim):
+            raise _invalid("invalid block parameter dimensions, storage or executor")
+        _capi.lib()
+        return BlockLinearLayer(weight, input_dim, output_dim, sequence_length, output_float32)
+
+    def name(self) -> str:
+        return "BlockLinearLayer"
+
+    def output_type(self) -> DataType:
+        return DataType.FP32 if self.output_float32_ else DataType.BF16
+
+    def weights(self):
+        return self.weights_
+
+    def gradients(self):
+        return [self.parameter_.gradient()] if self.parameter_.active() else []
+
+    def input_types(self):
+        return [ActivationType(DataType.BF16, (-2, self.sequence_length_, self.input_dim_))]
+
+    def output_types(self):
+        return [ActivationType(self.output_type(), (-2, self.sequence_length_, self.output_dim_))]
+
+    def _check(self, buffer, elements, element_size):
+        if buffer is None or not buffer.is_cuda or buffer.numel() * buffer.element_size() != elements * element_size:
+            raise _invalid("block training requires the owning executor, exact dimensions and batch size one")
+
+    def _workspace(self, device):
+        need = _capi.lib().pluto_block_linear_workspace_bytes(self.sequence_length_, self.input_dim_,
+                                                              self.output_dim_)
+        ws = torch.empty((need + 256,), dtype=torch.uint8, device=device)
+        return ws, (ws.data_ptr() + 255) // 256 * 256, need
+
+    def fwd_impl(self, inputs, hooks) -> FwdResult:
+        if len(inputs) != 1:
+            raise _invalid("linear requires one input")
+        t = self.sequence_length_
+        self._check(inputs[0], t * self.input_dim_, 2)
+        output = torch.empty((t, self.output_dim_), device=inputs[0].device,
+                             dtype=torch.float32 if self.output_float32_ else torch.bfloat16)
+        ws, ptr, need = self._workspace(inputs[0].device)
+        check(_capi.lib().pluto_block_linear_fwd(
+            _stream(), _ptr(self.weights_[0]), _ptr(inputs[0]), _ptr(output),
+            0 if self.output_float32_ else 1, t, self.input_dim_, self.output_dim_, ptr, need))
+        return FwdResult([output], BackwardState(intermediates=[inputs[0]]))
+
+    def bwd_impl(self, output_gradients, state, hooks):
+        if len(output_gradients) != 1 or len(state.intermediates) != 1:
+            raise _invalid("invalid linear backward state/gradient")
+        t = self.sequence_length_
+        dy = output_gradients[0]
+        self._check(dy, t * self.output_dim_, 4)
+        self._check(state.intermediates[0], t * self.input_dim_, 2)
+        dx = torch.empty((t, self.input_dim_), dtype=torch.float32, device=dy.device)
+        ws, ptr, need = self._workspace(dy.device)
+        check(_capi.lib().pluto_block_linear_bwd(
+            _stream(), _ptr(self.weights_[0]), _ptr(state.intermediates[0]), _ptr(dy), _ptr(dx),
+            _ptr(self.parameter_.gradient()), t, self.input_dim_, self.output_dim_, ptr, need))
         return [dx]
