@@ -380,6 +380,20 @@ def _other_rest(peaks, only, time_ms):
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "fwd_tflops": 4.0 * d * pairs * b * h / (fwd_ms * 1e-3) / 1e12,
         "bwd_tflops": 10.0 * d * pairs * b * h / (bwd_ms * 1e-3) / 1e12}
+    # BASELINE config 1 (the reference's CPU-runnable case): fp32 activations, exact fp32 kernels
+    b1, h1, s1, d1 = 16, 6, 256, 64
+    qkv1 = torch.randn(b1 * s1, 3 * h1 * d1, device="cuda")
+    dout1 = torch.randn(b1 * s1, h1 * d1, device="cuda")
+    layer1 = AttentionLayer.Create(s1, h1, h1 * d1, DataType.FP16)
+    f1 = time_ms(lambda: layer1.fwd([qkv1]), steps=20)
+    state1 = layer1.fwd([qkv1]).state
+    g1 = time_ms(lambda: layer1.bwd([dout1], state1), steps=10)
+    pairs1 = s1 * (s1 + 1) // 2
+    result["mha_fp32_config1"] = {
+        "workload": "batch 16, 6 heads, seq 256, head_dim 64, fp32 activations (exact fp32 FFMA kernels)",
+        "fwd_ms": f1, "bwd_ms": g1,
+        "fwd_tflops": 4.0 * d1 * pairs1 * b1 * h1 / (f1 * 1e-3) / 1e12,
+        "bwd_tflops": 10.0 * d1 * pairs1 * b1 * h1 / (g1 * 1e-3) / 1e12}
     if only == "mha_train":
         return result
     result.update(_gqa_bwd_workload(time_ms))

@@ -25,6 +25,15 @@ int from_cuda(cudaError_t e, const char* what) {
   return static_cast<int>(e);
 }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+}  // namespace
+
+// the same two helpers for entry points defined in other files
+namespace pluto {
+int report(int code, const char* message) { return fail(code, message); }
+int report_cuda(cudaError_t e, const char* what) { return from_cuda(e, what); }
+}  // namespace pluto
+
+namespace {
 
 // AttentionLayer::Create's checks (src/llm/layers/attention.cc:400-416) plus the extents the
 // kernels index with.

@@ -207,6 +207,10 @@ cudaError_t gdn_recurrent(cudaStream_t stream, const GdnArgs& args);
 bool gdn_chunked_supported(const GdnArgs& args);
 size_t gdn_chunked_workspace_bytes(int batch, int tokens, int value_heads, int value_dim);
 cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& args, void* workspace, uint32_t* status);
+// ---- c_api.cu: per-thread error text for entry points defined outside it -----------------------------
+int report(int code, const char* message);
+int report_cuda(cudaError_t e, const char* what);
+
 // ---- linear_gemv.cu: imported output-major projection; storage 0 fp32, 1 bf16, 2 FP8 E4M3 ---------
 cudaError_t linear_imported(cudaStream_t stream, const void* weights, int storage, const float* scales,
                             const void* x, void* y, int tokens, int cols, int rows);

@@ -67,12 +67,13 @@ int pluto_gqa_prefill_fwd_host(pluto_stream_t stream, const void* q_host, const 
                                int head_dim, int kv_heads_per_group) {
   const size_t need = pluto_gqa_prefill_host_workspace_bytes(batch, seq, q_heads, kv_heads, head_dim,
                                                              kv_heads_per_group);
-  if (need == 0) return PLUTO_E_INVALID;
-  if (!q_host || !k_host || !v_host || !out_host || !workspace || workspace_bytes < need ||
-      reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
-    return PLUTO_E_INVALID;
+  if (need == 0) return pluto::report(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
+  if (!q_host || !k_host || !v_host || !out_host)
+    return pluto::report(PLUTO_E_INVALID, "attention requires non-null host pointers");
+  if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return pluto::report(PLUTO_E_INVALID, "host prefill workspace is missing, misaligned or too small");
   Lanes* l = lanes_for_current_device();
-  if (l == nullptr) return PLUTO_E_INTERNAL;
+  if (l == nullptr) return pluto::report(PLUTO_E_INTERNAL, "copy streams could not be created");
   const size_t tokens = static_cast<size_t>(batch) * seq;
   const size_t g = q_heads / kv_heads, D = head_dim;
   const size_t hc_max = kv_heads_per_group;
@@ -84,7 +85,7 @@ int pluto_gqa_prefill_fwd_host(pluto_stream_t stream, const void* q_host, const 
   cudaError_t e = cudaEventRecord(l->start, compute);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(l->h2d, l->start, 0);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(l->d2h, l->start, 0);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  if (e != cudaSuccess) return pluto::report_cuda(e, "host prefill stream ordering");
   const int groups = (kv_heads + kv_heads_per_group - 1) / kv_heads_per_group;
   for (int c = 0; c < groups; ++c) {
     const int slot = c % kSlots;
@@ -109,7 +110,7 @@ int pluto_gqa_prefill_fwd_host(pluto_stream_t stream, const void* q_host, const 
     // kernel: after its inputs landed and after the output buffer's previous content left
     if (e == cudaSuccess) e = cudaStreamWaitEvent(compute, l->loaded[slot], 0);
     if (e == cudaSuccess && c >= kSlots) e = cudaStreamWaitEvent(compute, l->stored[slot], 0);
-    if (e != cudaSuccess) return static_cast<int>(e);
+    if (e != cudaSuccess) return pluto::report_cuda(e, "host prefill input copy");
     const int rc = pluto_gqa_prefill_fwd(stream, q_dev, nullptr, k_dev, v_dev, out_dev, nullptr, nullptr,
                                          nullptr, batch, seq, static_cast<int>(hc * g),
                                          static_cast<int>(hc), head_dim, hc * g * D, D, 0, 0, 1);
@@ -120,12 +121,12 @@ int pluto_gqa_prefill_fwd_host(pluto_stream_t stream, const void* q_host, const 
       e = cudaMemcpy2DAsync(static_cast<uint8_t*>(out_host) + h0 * g * D * 2, q_pitch, out_dev, q_width,
                             q_width, tokens, cudaMemcpyDeviceToHost, l->d2h);
     if (e == cudaSuccess) e = cudaEventRecord(l->stored[slot], l->d2h);
-    if (e != cudaSuccess) return static_cast<int>(e);
+    if (e != cudaSuccess) return pluto::report_cuda(e, "host prefill output copy");
   }
   // later work on the caller's stream sees the whole output
   for (int s = 0; s < kSlots && s < groups; ++s) {
     e = cudaStreamWaitEvent(compute, l->stored[s], 0);
-    if (e != cudaSuccess) return static_cast<int>(e);
+    if (e != cudaSuccess) return pluto::report_cuda(e, "host prefill stream ordering");
   }
   // (the last copy on each slot's event covers earlier ones: events are re-recorded per group)
   return PLUTO_OK;
