@@ -112,12 +112,18 @@ int pluto_attn_probs(pluto_stream_t stream, const void* qkv, const float* maxima
  *   core         optional fp32 [batch, seq, q_heads, head_dim]: the ungated, unrounded result the
  *                reference saves for backward
  *   maxima, normalizers   optional fp32 [batch*q_heads*seq] as in pluto_attn_fwd (both or neither)
+ *   workspace    optional (may be null): with pluto_gqa_prefill_fwd_workspace_bytes of 16-byte
+ *                aligned device memory, shapes with too few (sequence, head) pairs to fill the
+ *                GPU (long prompts head-sharded over several GPUs) are cut along the keys into 2 or
+ *                4 parts per query-tile pair and combined by a second kernel
  * q_heads % kv_heads == 0, head_dim <= 256; head_dim 64/128 runs on tcgen05. */
 int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate, const void* k,
                           const void* v, void* out, float* core, float* maxima,
                           float* normalizers, int batch, int seq, int q_heads, int kv_heads,
                           int head_dim, size_t q_token_stride, size_t q_head_stride,
-                          size_t gate_token_stride, size_t gate_head_stride, int round_to_bf16);
+                          size_t gate_token_stride, size_t gate_head_stride, int round_to_bf16,
+                          void* workspace, size_t workspace_bytes);
+size_t pluto_gqa_prefill_fwd_workspace_bytes(int batch, int seq, int q_heads, int head_dim);
 
 /* --------------------------------------------------------------------------------------------
  * pluto_gqa_prefill_fwd (the attention core of src/llm/layers/qwen_attention.cc:414-448) for

@@ -33,7 +33,8 @@ _SIGNATURES = {
     "pluto_attn_bwd": (_i, [_vp] * 8 + [_i] * 5 + [_vp, _sz]),
     "pluto_attn_bwd_workspace_bytes": (_sz, [_i] * 5),
     "pluto_attn_probs": (_i, [_vp] * 5 + [_i] * 5),
-    "pluto_gqa_prefill_fwd": (_i, [_vp] * 9 + [_i] * 5 + [_sz, _sz, _sz, _sz, _i]),
+    "pluto_gqa_prefill_fwd": (_i, [_vp] * 9 + [_i] * 5 + [_sz, _sz, _sz, _sz, _i, _vp, _sz]),
+    "pluto_gqa_prefill_fwd_workspace_bytes": (_sz, [_i] * 4),
     "pluto_gqa_prefill_host_workspace_bytes": (_sz, [_i] * 6),
     "pluto_gqa_prefill_fwd_host": (_i, [_vp] * 6 + [_sz] + [_i] * 6),
     "pluto_linear_imported_fwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i]),

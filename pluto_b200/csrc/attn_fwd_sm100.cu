@@ -47,6 +47,12 @@ struct FwdParams {
   const __nv_bfloat16* gate;   // optional, indexed like q: token stride gate_token, head stride gate_head
   size_t gate_token, gate_head;
   int round_gate;              // apply bf16 rounding inside the gate product (reference behaviour)
+  // key/value split (pair kernel only): `splits` CTAs share one tile pair, each walks a contiguous
+  // part of the key blocks and writes an unnormalised partial; attn_fwd_merge combines them
+  int splits;
+  float* part_o;               // [split][batch*seq tokens][heads][D] accumulator relative to part_m.x
+  float4* part_m;              // [split][batch][heads][seq] = (max used * scale_log2, true max *
+                               //  scale_log2, sum relative to max used, 0)
   uint32_t* status;
 };
 
@@ -377,11 +383,18 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
   // CTAs are handed to SMs in blockIdx.x-major order: (sequence, head) varies fastest and the pair
   // index slowest, so every head's longest pairs start first and the shortest ones fill the tail
   // (longest-processing-time-first over the whole grid, not per head).
-  const int pair = gridDim.y - 1 - blockIdx.y;
+  // With key/value splits, blockIdx.y = slot * splits + part and the parts of the longest pairs
+  // still start first.
+  const int pair = gridDim.y / p.splits - 1 - blockIdx.y / p.splits;
+  const int part = blockIdx.y % p.splits;
   const int head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
   const int q_tiles = (p.seq + kBM - 1) / kBM;
   const int tile_of[2] = {2 * pair, 2 * pair + 1};
-  const int n_of[2] = {tile_of[0] + 1, tile_of[1] < q_tiles ? tile_of[1] + 1 : 0};
+  const int blocks_of[2] = {tile_of[0] + 1, tile_of[1] < q_tiles ? tile_of[1] + 1 : 0};
+  // this CTA's key blocks [jb, je); tile x takes the ones below its own count n_of[x]
+  const int chunk = (max(blocks_of[0], blocks_of[1]) + p.splits - 1) / p.splits;
+  const int jb = part * chunk;
+  const int n_of[2] = {max(jb, min(blocks_of[0], jb + chunk)), max(jb, min(blocks_of[1], jb + chunk))};
   const int n_max = max(n_of[0], n_of[1]);
 
   if (threadIdx.x == 0) {
@@ -427,8 +440,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
                       p.q_col0 + head * p.q_head_cols + s * 64, tile_of[x] * kBM, batch,
                       &bar->q_full);
       bool ok = true;
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j % kStages, use = j / kStages;
+      for (int j = jb; j < n_max && ok; ++j) {
+        const int st = (j - jb) % kStages, use = (j - jb) / kStages;
         if (use > 0) ok = mbar_wait(&bar->k_empty[st], (use - 1) & 1, p.status, 1);
         if (!ok) break;
         mbar_expect_tx(&bar->k_full[st], kTileBytes);
@@ -445,9 +458,9 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
                       &bar->v_full[st]);
       }
       mbar_wait(&bar->q_full, 0, p.status, 3);
-      for (int j = max(0, n_max - kStages); j < n_max; ++j) {
-        mbar_wait(&bar->k_full[j % kStages], (j / kStages) & 1, p.status, 4);
-        mbar_wait(&bar->v_full[j % kStages], (j / kStages) & 1, p.status, 5);
+      for (int j = max(jb, n_max - kStages); j < n_max; ++j) {
+        mbar_wait(&bar->k_full[(j - jb) % kStages], ((j - jb) / kStages) & 1, p.status, 4);
+        mbar_wait(&bar->v_full[(j - jb) % kStages], ((j - jb) / kStages) & 1, p.status, 5);
       }
     }
   } else if (warp == 1) {
@@ -459,8 +472,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
       tc_fence_after();
       const uint32_t q_base = smem_u32(q_smem), k_base = smem_u32(k_smem), v_base = smem_u32(v_smem);
       auto issue_qk = [&](int x, int j) -> bool {
-        const int st = j % kStages;
-        if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[st], (j / kStages) & 1, p.status, 13)))
+        const int st = (j - jb) % kStages;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[st], ((j - jb) / kStages) & 1, p.status, 13)))
           return false;
         tc_fence_after();
         if (elect_one()) {
@@ -478,11 +491,11 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
         return true;
       };
       auto issue_pv = [&](int x, int j) -> bool {
-        const int st = j % kStages;
+        const int st = (j - jb) % kStages;
         // P arrives in two parts (96 + 32 keys): the first kEarly PV instructions run while the
         // softmax warps still work on the rest of the row.
-        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_early[x], j & 1, p.status, 14))) return false;
-        if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full[st], (j / kStages) & 1, p.status, 12)))
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_early[x], (j - jb) & 1, p.status, 14))) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full[st], ((j - jb) / kStages) & 1, p.status, 12)))
           return false;
         tc_fence_after();
         const uint64_t v_desc = umma_desc_sw128(v_base + st * kTileBytes, kSlabBytes, 1024);
@@ -490,10 +503,10 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
           for (int ks = 0; ks < kEarly; ++ks)
             umma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, v_desc + ks * (2048 >> 4),
-                    kIdescPV, j > 0 || ks > 0);
+                    kIdescPV, j > jb || ks > 0);
         }
         __syncwarp();
-        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[x], j & 1, p.status, 11))) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[x], (j - jb) & 1, p.status, 11))) return false;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -507,10 +520,10 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
       };
 #pragma unroll
       for (int x = 0; x < 2; ++x)
-        if (ok && n_of[x] > 0) ok = issue_qk(x, 0);
+        if (ok && n_of[x] > jb) ok = issue_qk(x, jb);
       if (ok && elect_one()) tc_commit(&bar->k_empty[0]);
       __syncwarp();
-      for (int j = 0; j < n_max && ok; ++j) {
+      for (int j = jb; j < n_max && ok; ++j) {
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (!ok || j >= n_of[x]) continue;
@@ -519,8 +532,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
         }
         if (!ok) break;
         if (elect_one()) {
-          tc_commit(&bar->v_empty[j % kStages]);
-          if (j + 1 < n_max) tc_commit(&bar->k_empty[(j + 1) % kStages]);
+          tc_commit(&bar->v_empty[(j - jb) % kStages]);
+          if (j + 1 < n_max) tc_commit(&bar->k_empty[(j + 1 - jb) % kStages]);
         }
         __syncwarp();
       }
@@ -539,8 +552,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
     const uint32_t o_addr = tmem + lane_base + 256 + x * 128;
     float m_used = -INFINITY, m_true = -INFINITY, l = 0.0f;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      ok = mbar_wait(&bar->s_full[x], j & 1, p.status, 20);
+    for (int j = jb; j < n_tiles && ok; ++j) {
+      ok = mbar_wait(&bar->s_full[x], (j - jb) & 1, p.status, 20);
       if (!ok) break;
       tc_fence_after();
       const bool diagonal = j == q_tile;
@@ -571,8 +584,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
         const float factor = grow ? fast_exp2((m_used - m_true) * p.scale_log2) : 1.0f;
         if (grow) m_used = m_true;
         l *= factor;
-        if (j > 0) {
-          ok = mbar_wait(&bar->pv_done[x], (j - 1) & 1, p.status, 21);
+        if (j > jb) {
+          ok = mbar_wait(&bar->pv_done[x], (j - 1 - jb) & 1, p.status, 21);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
@@ -632,8 +645,36 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->p_full[x]);
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(&bar->pv_done[x], (n_tiles - 1) & 1, p.status, 22);
-    if (ok && n_tiles > 0) {
+    const bool any = n_tiles > jb;             // this part holds key blocks of this tile
+    if (ok && any) ok = mbar_wait(&bar->pv_done[x], (n_tiles - 1 - jb) & 1, p.status, 22);
+    if (ok && p.splits > 1 && blocks_of[x] > 0) {
+      // unnormalised partial of this part: accumulator and sums are relative to m_used
+      if (any) tc_fence_after();
+      const bool live = query < p.seq;
+      const size_t token = static_cast<size_t>(batch) * p.seq + query;
+      const size_t tokens = static_cast<size_t>(gridDim.x / p.heads) * p.seq;
+      float* dst = p.part_o + ((static_cast<size_t>(part) * tokens + token) * p.heads + head) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (any) {
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+        }
+      }
+      if (live)
+        p.part_m[((static_cast<size_t>(part) * (gridDim.x / p.heads) + batch) * p.heads + head) * p.seq + query] =
+            make_float4(any ? m_used * p.scale_log2 : -INFINITY, any ? m_true * p.scale_log2 : -INFINITY,
+                        any ? l : 0.0f, 0.0f);
+    } else if (ok && any) {
       tc_fence_after();
       const float inv = 1.0f / l;
       const bool live = query < p.seq;
@@ -694,6 +735,63 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
   }
 }
 
+// Combines the key/value parts of the pair kernel: one warp per (token, head), a lane owns D / 32
+// consecutive channels.  With M = max over parts of the maximum each part's numbers are relative
+// to:  O = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M); then the same epilogue as the kernel
+// (fp32 core, gate with the reference's rounding sequence, bf16 output, statistics).
+template <int D>
+__global__ void __launch_bounds__(256) attn_fwd_merge(FwdParams p, int batch) {
+  constexpr int kPer = D / 32;
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + threadIdx.x / 32;
+  const long long rows = static_cast<long long>(batch) * p.seq * p.heads;
+  if (row >= rows) return;
+  const int lane = threadIdx.x % 32;
+  const size_t token = static_cast<size_t>(row / p.heads);
+  const int head = static_cast<int>(row % p.heads);
+  const int b = static_cast<int>(token / p.seq), s = static_cast<int>(token % p.seq);
+  const size_t tokens = static_cast<size_t>(batch) * p.seq;
+  float m_used = -INFINITY, m_true = -INFINITY;
+  float4 rec[4];
+  for (int part = 0; part < p.splits; ++part) {
+    rec[part] = p.part_m[((static_cast<size_t>(part) * batch + b) * p.heads + head) * p.seq + s];
+    m_used = fmaxf(m_used, rec[part].x);
+    m_true = fmaxf(m_true, rec[part].y);
+  }
+  float acc[kPer], l = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) acc[i] = 0.0f;
+  for (int part = 0; part < p.splits; ++part) {
+    const float w = fast_exp2(rec[part].x - m_used);      // 0 for a part without key blocks
+    l = fmaf(rec[part].z, w, l);
+    const float* src = p.part_o + ((static_cast<size_t>(part) * tokens + token) * p.heads + head) * D + lane * kPer;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) acc[i] = fmaf(src[i], w, acc[i]);
+  }
+  const float inv = 1.0f / l;
+  __nv_bfloat16* out = p.out + token * p.out_token + head * p.out_head + lane * kPer;
+  float* core = p.core ? p.core + token * p.out_token + head * p.out_head + lane * kPer : nullptr;
+  const __nv_bfloat16* gate = p.gate ? p.gate + token * p.gate_token + head * p.gate_head + lane * kPer : nullptr;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    float a = acc[i] * inv;
+    if (core) core[i] = a;
+    if (gate) {
+      float g = 1.0f / (1.0f + expf(-__bfloat162float(gate[i])));
+      if (p.round_gate) {
+        g = bf16_round(g);
+        a = bf16_round(a);
+      }
+      a *= g;
+    }
+    out[i] = __float2bfloat16_rn(a);
+  }
+  if (lane == 0 && p.maxima) {
+    const size_t stat = (static_cast<size_t>(b) * p.heads + head) * p.seq + s;
+    p.maxima[stat] = m_true * 0.6931471805599453f;       // back from log2 units
+    p.normalizers[stat] = l * fast_exp2(m_used - m_true);
+  }
+}
+
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -729,6 +827,12 @@ bool make_token_map(CUtensorMap* map, const void* base, int cols, int seq, int b
                 box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
          CUDA_SUCCESS;
+}
+
+// Partials of the key/value-split mode: a float4 record and D floats per (part, token, head), 4 parts.
+size_t attn_fwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim) {
+  const size_t units = static_cast<size_t>(batch) * seq * heads;
+  return 4 * units * (sizeof(float4) + static_cast<size_t>(head_dim) * sizeof(float));
 }
 
 // See engine.h for the contract.  Returns cudaErrorInvalidValue when a tensor map cannot be
@@ -776,14 +880,35 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   }
   const long long pair_units = static_cast<long long>((q_tiles + 1) / 2) * a.heads * a.batch;
-  if (q_tiles >= 2 && pair_units >= 2LL * sms) {
+  // With a workspace, too few units are made finer by cutting every pair's key range into 2 or 4
+  // parts (partials combined by attn_fwd_merge) instead of falling back to single tiles.
+  int splits = 1;
+  if (a.workspace != nullptr && q_tiles >= 8 && pair_units < 2LL * sms)
+    splits = pair_units * 2 >= 2LL * sms ? 2 : 4;
+  p.splits = splits;
+  p.part_o = nullptr;
+  p.part_m = nullptr;
+  if (splits > 1) {
+    const size_t tokens = static_cast<size_t>(a.batch) * a.seq;
+    p.part_m = static_cast<float4*>(a.workspace);
+    p.part_o = reinterpret_cast<float*>(p.part_m + 4 * tokens * a.heads);
+  }
+  if (q_tiles >= 2 && (pair_units >= 2LL * sms || splits > 1)) {
     // two query tiles per CTA in ping-pong
-    const dim3 grid(a.heads * a.batch, (q_tiles + 1) / 2);
+    const dim3 grid(a.heads * a.batch, ((q_tiles + 1) / 2) * splits);
     const size_t smem = 1024 + tile * (2 + 2 * kStages) + sizeof(PairBarriers);
     auto kernel = a.head_dim == 128 ? attn_fwd_sm100_pair<128> : attn_fwd_sm100_pair<64>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     kernel<<<grid, kThreadsPair, smem, stream>>>(map_q, map_k, map_v, p);
+    if (splits > 1) {
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      const long long rows = static_cast<long long>(a.batch) * a.seq * a.heads;
+      const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+      if (a.head_dim == 128) attn_fwd_merge<128><<<blocks, 256, 0, stream>>>(p, a.batch);
+      else attn_fwd_merge<64><<<blocks, 256, 0, stream>>>(p, a.batch);
+    }
   } else {
     const dim3 grid(a.heads * a.batch, q_tiles);
     const size_t smem = 1024 + tile * (1 + 2 * kStages) + sizeof(Barriers);

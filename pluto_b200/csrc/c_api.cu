@@ -156,7 +156,8 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
                           const void* v, void* out, float* core, float* maxima,
                           float* normalizers, int batch, int seq, int q_heads, int kv_heads,
                           int head_dim, size_t q_token_stride, size_t q_head_stride,
-                          size_t gate_token_stride, size_t gate_head_stride, int round_to_bf16) {
+                          size_t gate_token_stride, size_t gate_head_stride, int round_to_bf16,
+                          void* workspace, size_t workspace_bytes) {
   if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
       q_heads % kv_heads != 0 || head_dim > 256 || batch > 65535 || q_heads > 65535)
     return fail(PLUTO_E_INVALID, "invalid full-attention dimensions or parameters");
@@ -186,6 +187,10 @@ int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate
     a.maxima = maxima; a.normalizers = normalizers; a.core = core;
     a.gate = gate; a.gate_token = gate_token_stride; a.gate_head = gate_head_stride;
     a.round_gate = round_to_bf16;
+    // the optional workspace enables the key/value split for shapes with few (sequence, head) units
+    if (workspace != nullptr && aligned16(workspace) &&
+        workspace_bytes >= pluto::attn_fwd_tc_workspace_bytes(batch, seq, q_heads, head_dim))
+      a.workspace = workspace;
     a.status = pluto::kernel_status_word();
     if (!a.status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
     return from_cuda(pluto::attn_fwd_tc(stream, a), "GQA prefill (tcgen05) launch");
@@ -270,6 +275,11 @@ int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, c
   a.dq_token = qd; a.dq_head = D; a.dkv_token = kd; a.dkv_head = D;
   a.bf16 = dtype == PLUTO_BF16;
   return from_cuda(pluto::gqa_generic_bwd(stream, a), "sequence full attention backward");
+}
+
+size_t pluto_gqa_prefill_fwd_workspace_bytes(int batch, int seq, int q_heads, int head_dim) {
+  if (batch <= 0 || seq <= 0 || q_heads <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
+  return pluto::attn_fwd_tc_workspace_bytes(batch, seq, q_heads, head_dim);
 }
 
 size_t pluto_gqa_prefill_bwd_workspace_bytes(int batch, int seq, int q_heads, int head_dim, int dtype) {

@@ -118,9 +118,11 @@ struct AttnFwdArgs {
   const void* gate;            // optional bf16, gate_token / gate_head element strides
   size_t gate_token, gate_head;
   int round_gate;
+  void* workspace;             // optional, attn_fwd_tc_workspace_bytes: enables the key/value split
   uint32_t* status;
 };
 cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& args);
+size_t attn_fwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim);
 bool make_token_map(CUtensorMap* map, const void* base, int cols, int seq, int batch,
                     size_t token_stride, int box_rows);
 

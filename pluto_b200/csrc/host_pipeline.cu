@@ -113,7 +113,7 @@ int pluto_gqa_prefill_fwd_host(pluto_stream_t stream, const void* q_host, const 
     if (e != cudaSuccess) return pluto::report_cuda(e, "host prefill input copy");
     const int rc = pluto_gqa_prefill_fwd(stream, q_dev, nullptr, k_dev, v_dev, out_dev, nullptr, nullptr,
                                          nullptr, batch, seq, static_cast<int>(hc * g),
-                                         static_cast<int>(hc), head_dim, hc * g * D, D, 0, 0, 1);
+                                         static_cast<int>(hc), head_dim, hc * g * D, D, 0, 0, 1, nullptr, 0);
     if (rc != PLUTO_OK) return rc;
     e = cudaEventRecord(l->computed[slot], compute);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(l->d2h, l->computed[slot], 0);

@@ -258,7 +258,8 @@ class AttentionLayer(Layer):
 
 def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                 gate: Optional[torch.Tensor] = None, round_to_bfloat16: bool = True,
-                want_core: bool = False, want_stats: bool = False):
+                want_core: bool = False, want_stats: bool = False,
+                workspace: Optional[torch.Tensor] = None):
     """Attention core of QwenAttentionLayer::SequenceForward (qwen_attention.cc:414-448) for
     already prepared q [B,T,Hq,D] (any token/head strides with a contiguous last dim), k, v
     [B,T,Hkv,D] bf16.  Returns dict(out[, core, maxima, normalizers])."""
@@ -278,10 +279,19 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         if gate.stride(3) != 1 or gate.stride(0) != T * gate.stride(1):
             raise _invalid("attention gate must have a contiguous head dimension and batch")
         gts, ghs = gate.stride(1), gate.stride(2)
-    check(_capi.lib().pluto_gqa_prefill_fwd(
+    # few (sequence, head) units for a long prompt (e.g. one head shard of several GPUs): give the
+    # kernel scratch for its key/value split; pass `workspace` to reuse one across calls
+    L = _capi.lib()
+    ws_ptr, ws_bytes = None, 0
+    if D in (64, 128) and T >= 1024 and B * Hq * ((T + 255) // 256) < 2 * 148:
+        ws_bytes = L.pluto_gqa_prefill_fwd_workspace_bytes(B, T, Hq, D)
+        if workspace is None or workspace.numel() < ws_bytes + 16:
+            workspace = torch.empty((ws_bytes + 16,), dtype=torch.uint8, device=q.device)
+        ws_ptr = (workspace.data_ptr() + 15) // 16 * 16
+    check(L.pluto_gqa_prefill_fwd(
         _stream(), _ptr(q), _ptr(gate), _ptr(k), _ptr(v), _ptr(out), _ptr(core), _ptr(maxima),
         _ptr(normalizers), B, T, Hq, Hkv, D, q.stride(1), q.stride(2), gts, ghs,
-        int(round_to_bfloat16)))
+        int(round_to_bfloat16), ws_ptr, ws_bytes))
     result = {"out": out}
     if want_core:
         result["core"] = core

@@ -245,3 +245,44 @@ def test_host_memory_prefill_matches_device_prefill():
         torch.cuda.synchronize()
         want = gqa_prefill(q.cuda(), k.cuda(), v.cuda())["out"].cpu()
         assert torch.equal(out.view(torch.int16), want.view(torch.int16)), (t, hq, hkv, d)
+
+
+@pytest.mark.parametrize("shape", [(2048, 4, 2, 128), (3000, 10, 2, 128), (2304, 6, 6, 64), (1100, 16, 4, 128)])
+def test_key_value_split_prefill_matches_oracle_and_unsplit_kernel(shape):
+    """Few (sequence, head) units for a long prompt: with a workspace every query-tile pair is cut
+    along the keys into 2 or 4 parts and merged.  Checked against the CPU oracle on sampled rows
+    (first rows, rows around tile and part boundaries, last rows) and against the same call without
+    a workspace; gate, fp32 core and statistics included."""
+    import torch
+    from pluto_b200 import _capi
+    from pluto_b200.layers import gqa_prefill
+    t, hq, hkv, d = shape
+    rng = np.random.default_rng(t)
+    q = oracle.to_bf16_bits(rng.standard_normal((t, hq, d), dtype=np.float32) * 0.6)
+    k = oracle.to_bf16_bits(rng.standard_normal((t, hkv, d), dtype=np.float32) * 0.6)
+    v = oracle.to_bf16_bits(rng.standard_normal((t, hkv, d), dtype=np.float32) * 0.6)
+    gate = oracle.to_bf16_bits(rng.standard_normal((t, hq, d), dtype=np.float32))
+    dq, dk, dv, dg = (to_device_bf16(x)[None] for x in (q, k, v, gate))
+    split = gqa_prefill(dq, dk, dv, gate=dg, want_core=True, want_stats=True)       # allocates the workspace
+    L = _capi.lib()
+    out = torch.empty_like(split["out"])
+    core = torch.empty_like(split["core"])
+    maxima, normalizers = torch.empty_like(split["maxima"]), torch.empty_like(split["normalizers"])
+    _capi.check(L.pluto_gqa_prefill_fwd(torch.cuda.current_stream().cuda_stream, dq.data_ptr(), dg.data_ptr(),
+                                        dk.data_ptr(), dv.data_ptr(), out.data_ptr(), core.data_ptr(),
+                                        maxima.data_ptr(), normalizers.data_ptr(), 1, t, hq, hkv, d,
+                                        hq * d, d, hq * d, d, 1, None, 0))
+    torch.cuda.synchronize()
+    assert _capi.kernel_status() == 0
+    a, b = split["out"].float().cpu().numpy(), out.float().cpu().numpy()
+    assert np.abs(a - b).max() <= 2e-2
+    assert np.abs(split["core"].cpu().numpy() - core.cpu().numpy()).max() <= 8e-3
+    assert np.abs(split["maxima"].cpu().numpy() - maxima.cpu().numpy()).max() <= 1e-5
+    ratio = split["normalizers"].cpu().numpy() / normalizers.cpu().numpy()
+    assert np.abs(ratio - 1).max() <= 2e-3
+    for rows in ((0, 40), (t // 2 - 20, t // 2 + 20), (t - 40, t)):
+        want = oracle.gqa_prefill(q, k, v, gate=gate, threads=4, rows=rows, want_core=True)
+        got = a[0, rows[0]:rows[1]]
+        ref = oracle.from_bf16_bits(want["out"])[rows[0]:rows[1]]
+        assert np.abs(got - ref).max() <= 2e-2, rows
+        assert np.abs(split["core"].cpu().numpy()[0, rows[0]:rows[1]] - want["core"][rows[0]:rows[1]]).max() <= 8e-3
