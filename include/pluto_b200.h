@@ -113,9 +113,9 @@ int pluto_attn_probs(pluto_stream_t stream, const void* qkv, const float* maxima
  *                reference saves for backward
  *   maxima, normalizers   optional fp32 [batch*q_heads*seq] as in pluto_attn_fwd (both or neither)
  *   workspace    optional (may be null): with pluto_gqa_prefill_fwd_workspace_bytes of 16-byte
- *                aligned device memory, shapes with too few (sequence, head) pairs to fill the
- *                GPU (long prompts head-sharded over several GPUs) are cut along the keys into 2 or
- *                4 parts per query-tile pair and combined by a second kernel
+ *                aligned device memory, shapes whose query tiles cannot fill the GPU (one or two
+ *                heads of a long prompt) are cut along the keys into 2 or 4 parts per query-tile
+ *                pair and combined by a second kernel
  * q_heads % kv_heads == 0, head_dim <= 256; head_dim 64/128 runs on tcgen05. */
 int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate, const void* k,
                           const void* v, void* out, float* core, float* maxima,

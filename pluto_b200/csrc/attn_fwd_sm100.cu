@@ -880,10 +880,13 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   }
   const long long pair_units = static_cast<long long>((q_tiles + 1) / 2) * a.heads * a.batch;
-  // With a workspace, too few units are made finer by cutting every pair's key range into 2 or 4
-  // parts (partials combined by attn_fwd_merge) instead of falling back to single tiles.
+  // With a workspace, a shape that cannot even fill the SMs with single tiles (one or two heads of
+  // a long prompt) is made finer by cutting every pair's key range into parts, combined by
+  // attn_fwd_merge.  Measured at S = 8192, D = 128: 1 head 74 -> 50 us, 2 heads 76 -> 62 us, but
+  // 3 heads 77 -> 95 us and 5 heads 103 -> 114 us (the per-CTA prologue/epilogue outweighs the
+  // better balance), hence the threshold.
   int splits = 1;
-  if (a.workspace != nullptr && q_tiles >= 8 && pair_units < 2LL * sms)
+  if (a.workspace != nullptr && q_tiles >= 8 && static_cast<long long>(q_tiles) * a.heads * a.batch <= sms)
     splits = pair_units * 2 >= 2LL * sms ? 2 : 4;
   p.splits = splits;
   p.part_o = nullptr;

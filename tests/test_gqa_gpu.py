@@ -247,7 +247,7 @@ def test_host_memory_prefill_matches_device_prefill():
         assert torch.equal(out.view(torch.int16), want.view(torch.int16)), (t, hq, hkv, d)
 
 
-@pytest.mark.parametrize("shape", [(2048, 4, 2, 128), (3000, 10, 2, 128), (2304, 6, 6, 64), (1100, 16, 4, 128)])
+@pytest.mark.parametrize("shape", [(2048, 4, 2, 128), (3000, 5, 1, 128), (2304, 6, 6, 64), (9000, 2, 1, 128)])
 def test_key_value_split_prefill_matches_oracle_and_unsplit_kernel(shape):
     """Few (sequence, head) units for a long prompt: with a workspace every query-tile pair is cut
     along the keys into 2 or 4 parts and merged.  Checked against the CPU oracle on sampled rows
