@@ -451,7 +451,9 @@ def _linear_workload(time_ms, peaks):
         out[name] = {"ms": ms, "weight_gbs": nbytes / (ms * 1e-3) / 1e9,
                      "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     return {"imported_linear": {"workload": "one token, [10240 x 5120] frozen weights, calls rotate over "
-                                            "> 420 MB of distinct matrices", **out}}
+                                            "> 420 MB of distinct matrices; back-to-back calls in one "
+                                            "stream (programmatic dependent launch lets a call's weight "
+                                            "copies start under the previous call's tail)", **out}}
 
 
 def _dense_workload(time_ms, peaks):

@@ -97,6 +97,15 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
       : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with programmatic stream serialisation may
+// start once every CTA of its predecessor has executed pdl_launch_dependents (or exited), and
+// must call pdl_wait before it reads anything the predecessor writes or writes anything the
+// predecessor reads.  Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Tiled loads (no multicast anywhere in this engine).  c0 is the innermost coordinate and must
 // make c0 * element_size a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1,
