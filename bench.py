@@ -544,6 +544,19 @@ def _gdn_workload(time_ms):
     q1, k1, v1 = qn[:, 0].contiguous(), kn[:, 0].contiguous(), vn[:, 0].contiguous()
     g1, b1, o1 = g[:, 0].contiguous(), beta[:, 0].contiguous(), torch.empty_like(vn[:, 0])
     step_ms = time_ms(lambda: gdn_step(q1, k1, v1, g1, b1, st, out=o1), steps=256)
+    # the same 256 steps as one CUDA graph: the entry point neither allocates nor synchronises,
+    # so a serving loop can capture it, and the replay shows the device cost without the ~10 us
+    # a Python call spends per launch
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        gdn_step(q1, k1, v1, g1, b1, st, out=o1)
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(256):
+                gdn_step(q1, k1, v1, g1, b1, st, out=o1)
+    torch.cuda.current_stream().wait_stream(side)
+    graph_ms = time_ms(graph.replay, steps=5, warmup=3) / 256
     # BPTT through the recurrence (checkpointed every 64 tokens), q/k normalisation included
     L = _capi.lib()
     a_raw = torch.randn(bb, tt, hh, device="cuda").bfloat16()
@@ -569,6 +582,7 @@ def _gdn_workload(time_ms):
         "workload": "batch 2, 16 heads, d_k = d_v = 128, seq 16384 prefill then single-token steps",
         "prefill_ms": pre_ms, "prefill_tflops_chunked_count": 94.49e9 / (pre_ms * 1e-3) / 1e12,
         "step_us": step_ms * 1e3, "step_state_gbs": 4.19e6 / (step_ms * 1e-3) / 1e9,
+        "step_in_cuda_graph_us": graph_ms * 1e3, "step_in_cuda_graph_state_gbs": 4.19e6 / (graph_ms * 1e-3) / 1e9,
         "recurrence_bwd_ms": bptt_ms, "recurrence_bwd_workspace_gb": ws_bytes / 1e9}
     return result
 
