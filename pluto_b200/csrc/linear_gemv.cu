@@ -11,9 +11,11 @@
 // stream bound by HBM, so here the activation is cast (and, for FP8, quantised) inside the same
 // kernel and staged in shared memory, a small decode batch shares one pass over the weights, and
 // there are three forms of the stream itself:
-//  * linear_gemv_stream: bf16/FP8, one to three tokens -- persistent CTAs fed by a ring of
-//    bulk-copied weight slabs (TMA unit), launched so that consecutive calls overlap;
-//  * linear_gemv_mma: bf16/FP8 batches of up to 8 tokens on the tensor cores (mma.sync);
+//  * linear_gemv_stream, linear_gemv_stream_e4m3: persistent CTAs fed by a ring of bulk-copied
+//    weight slabs (TMA unit), launched so that consecutive calls overlap; FMA arithmetic for one
+//    bf16 token, E4M3 tensor-core MMAs for FP8 weights;
+//  * linear_gemv_mma: bf16/FP8 batches of up to 8 tokens on the tensor cores (mma.sync), loading
+//    from global memory;
 //  * linear_gemv_kernel: fp32 weights, unaligned or small shapes -- 16-byte loads from global
 //    memory, FMA arithmetic.
 #include <cuda_fp8.h>
@@ -104,26 +106,37 @@ template <int STORAGE, int TOK>
 __device__ __forceinline__ void stage_activation(const __nv_bfloat16* __restrict__ x, float* xs, int ld,
                                                  int cols, int c0, int count, int warp, int lane) {
   const int groups = (count + 127) / 128;
-  for (int group = warp; group < TOK * groups; group += kWarps) {
-    const int t = group / groups, g = group % groups;
-    float v[4], maximum = 0.0f;
+  constexpr int kBatch = 4;   // groups whose loads are in flight together (the latency is paid once)
+  for (int first = warp; first < TOK * groups; first += kWarps * kBatch) {
+    float v[kBatch][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = g * 128 + lane + 32 * i;
-      v[i] = c < count ? __bfloat162float(x[static_cast<size_t>(t) * cols + c0 + c]) : 0.0f;
-      maximum = fmaxf(maximum, fabsf(v[i]));
-    }
-    if (STORAGE == 2) {
+    for (int u = 0; u < kBatch; ++u) {
+      const int group = min(first + u * kWarps, TOK * groups - 1);
+      const int t = group / groups, g = group % groups;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
-      const float scale = maximum / 448.0f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = quantize_e4m3(v[i], scale);
+      for (int i = 0; i < 4; ++i) {
+        const int c = g * 128 + lane + 32 * i;
+        v[u][i] = c < count ? __bfloat162float(x[static_cast<size_t>(t) * cols + c0 + c]) : 0.0f;
+      }
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = g * 128 + lane + 32 * i;
-      if (c < ld) xs[t * ld + swizzled(c)] = v[i];
+    for (int u = 0; u < kBatch; ++u) {
+      // no early exit: the batch's reductions are independent chains that interleave
+      const int group = min(first + u * kWarps, TOK * groups - 1);   // past the end: repeats the last group
+      const int t = group / groups, g = group % groups;
+      if (STORAGE == 2) {
+        float maximum = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
+        const float scale = maximum / 448.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[u][i] = quantize_e4m3(v[u][i], scale);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = g * 128 + lane + 32 * i;
+        if (c < ld) xs[t * ld + swizzled(c)] = v[u][i];
+      }
     }
   }
 }
@@ -576,6 +589,226 @@ linear_gemv_mma(const void* __restrict__ weights, const float* __restrict__ scal
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// FP8 weights, one to four tokens, cols % 256 == 0: the streaming ring feeding the tensor cores.
+// The FMA form above spends its time converting E4M3 to fp32 (its slope is 4.1 TB/s); an
+// m16n8k32 E4M3 MMA takes the codes as they are.  A slab is 4 (2, 1) weight rows in one contiguous
+// piece of memory, so the MMA is laid out around that: every row is cut into two halves of
+// cols / 2, the 8 columns of the B operand are the 8 (row, half) pieces, and the rows of the A
+// operand are the (token, half) pieces of the quantised activation.  D[(t, h)][(r, h')] is the
+// dot product of token t's half h with row r's half h'; only h == h' means anything, and
+// y[t][r] = D[(t,0)][(r,0)] + D[(t,1)][(r,1)].  Half of the tensor work is thrown away, which
+// costs nothing here.  Every piece sits in shared memory at a stride of its length + 64 bytes,
+// which makes the fragments' 16-byte loads conflict-free, and a lane loads 16 consecutive bytes
+// at 16 * (lane % 4) of a 64-byte block on both sides, so the K order inside a block is the same
+// permutation for A and B.  Scales: each 128-column group's four MMAs go into a fresh
+// accumulator that is added with (weight block scale x activation group scale).
+// ------------------------------------------------------------------------------------------------
+constexpr int kPiecePad = 64;
+
+struct StreamMmaLayout {
+  int stages, slab_rows, half;               // half = cols / 2
+  size_t piece_stride, slab_bytes, xs_offset, xscale_offset, partial_offset, bar_offset, total;
+};
+inline StreamMmaLayout stream_mma_layout(int cols, int tokens) {
+  StreamMmaLayout l;
+  l.half = cols / 2;
+  l.piece_stride = static_cast<size_t>(l.half) + kPiecePad;
+  const size_t xs_bytes = 2 * static_cast<size_t>(tokens) * l.piece_stride;
+  const size_t xscale_bytes = static_cast<size_t>(tokens) * (cols / 128) * 4;
+  const size_t partial_bytes = 2 * kWarps * 4 * kRows * 4;   // [buffer][warp][token][row]
+  const size_t tail = 2 * kStreamMaxStages * 8 + 4 * kGroups;
+  const size_t fixed = xs_bytes + xscale_bytes + partial_bytes + tail;
+  l.stages = 0;
+  for (l.slab_rows = kRows; l.slab_rows >= 1; l.slab_rows /= 2) {
+    l.slab_bytes = (2 * l.slab_rows * l.piece_stride + 1023) / 1024 * 1024;
+    if (fixed < static_cast<size_t>(kStreamBudget))
+      l.stages = static_cast<int>(std::min<size_t>(kStreamMaxStages, (kStreamBudget - fixed) / l.slab_bytes)) /
+                 kGroups * kGroups;
+    if (l.stages > 0) break;
+  }
+  if (l.stages == 0) l.slab_rows = kRows;
+  l.xs_offset = l.stages * l.slab_bytes;
+  l.xscale_offset = l.xs_offset + xs_bytes;
+  l.partial_offset = l.xscale_offset + xscale_bytes;
+  l.bar_offset = (l.partial_offset + partial_bytes + 7) / 8 * 8;
+  l.total = l.bar_offset + tail;
+  return l;
+}
+
+__global__ void __launch_bounds__(kThreads + 32, 2)
+linear_gemv_stream_e4m3(const uint8_t* __restrict__ weights, const float* __restrict__ scales,
+                        const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int cols,
+                        int rows, int tokens, StreamMmaLayout layout, uint32_t* status) {
+  extern __shared__ __align__(1024) uint8_t stream_smem[];
+  uint8_t* ring = stream_smem;
+  uint8_t* xs = stream_smem + layout.xs_offset;                                   // [token][half][piece]
+  float* xscale = reinterpret_cast<float*>(stream_smem + layout.xscale_offset);   // [token][cols / 128]
+  float* partial = reinterpret_cast<float*>(stream_smem + layout.partial_offset);
+  uint64_t* full = reinterpret_cast<uint64_t*>(stream_smem + layout.bar_offset);
+  uint64_t* empty = full + kStreamMaxStages;
+  int* failed = reinterpret_cast<int*>(empty + kStreamMaxStages);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int stages = layout.stages, slab_rows = layout.slab_rows, half = layout.half;
+  const size_t stride = layout.piece_stride;
+  const int n_tasks = (rows + slab_rows - 1) / slab_rows;
+  const int groups128 = cols / 128;
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kGroupWarps);
+    }
+    for (int g = 0; g < kGroups; ++g) failed[g] = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // slab n of this CTA = task blockIdx.x + n * gridDim.x; piece 2 r + h = half h of its row r
+  auto issue = [&](int n) {
+    const int task = blockIdx.x + n * gridDim.x;
+    const int st = n % stages;
+    const int rows_here = min(slab_rows, rows - task * slab_rows);
+    mbar_expect_tx(&full[st], static_cast<uint32_t>(rows_here) * cols);
+    const uint8_t* src = weights + static_cast<size_t>(task) * slab_rows * cols;
+    uint8_t* dst = ring + st * layout.slab_bytes;
+    for (int piece = 0; piece < 2 * rows_here; ++piece)
+      bulk_load(dst + piece * stride, src + static_cast<size_t>(piece) * half, half, &full[st]);
+  };
+  const int my_tasks = blockIdx.x < n_tasks ? (n_tasks - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+
+  if (warp == kWarps) {
+    if (lane == 0) {
+      for (int n = 0; n < min(stages, my_tasks); ++n) issue(n);
+      for (int n = stages; n < my_tasks; ++n) {
+        if (!mbar_wait(&empty[n % stages], (n / stages - 1) & 1, status, 42)) break;
+        issue(n);
+      }
+    }
+    return;
+  }
+
+  // activation -> E4M3 codes per (token, half) piece + one scale per group of 128 (one warp a group)
+  pdl_wait();   // the previous kernel's output may be this activation
+  {
+    constexpr int kBatch = 5;   // groups whose 8-byte loads are in flight together
+    const int total = tokens * groups128;
+    for (int first = warp; first < total; first += kWarps * kBatch) {
+      uint2 raw[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int group = min(first + u * kWarps, total - 1);
+        const int t = group / groups128, g = group % groups128;
+        raw[u] = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t) * cols + g * 128 + lane * 4);
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        // no early exit: the batch's reductions are independent chains that interleave
+        const int group = min(first + u * kWarps, total - 1);   // past the end: repeats the last group
+        const int t = group / groups128, g = group % groups128;
+        const float v[4] = {bf16_lo(raw[u].x), bf16_hi(raw[u].x), bf16_lo(raw[u].y), bf16_hi(raw[u].y)};
+        float maximum = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
+        const float scale = maximum / 448.0f, divisor = fmaxf(scale, 1e-12f);
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          word |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] / divisor, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+        const int c = g * 128 + lane * 4, h = c / half;
+        *reinterpret_cast<uint32_t*>(xs + (2 * t + h) * stride + (c - h * half)) = word;
+        if (lane == 0) xscale[t * groups128 + g] = scale;
+      }
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+
+  const int group = warp / kGroupWarps, gwarp = warp % kGroupWarps;
+  const int gthread = threadIdx.x % kGroupThreads;
+  const int g = lane / 4, q = lane % 4;
+  // A row g = (token g / 2, half g % 2); B column g = piece g = (row g / 2, half g % 2);
+  // accumulator element i < 2 of this lane: A row g, B column 2 q + i = (row q, half i)
+  const int my_half = g & 1, my_token = g >> 1;
+  const bool a_valid = my_token < tokens;
+  const uint8_t* a_ptr = xs + g * stride + q * 16;
+  const int half_groups = half / 128;
+  const float* my_xscale = xscale + min(my_token, tokens - 1) * groups128 + my_half * half_groups;
+  for (int n = group, turn = 0; n < my_tasks; n += kGroups, ++turn) {
+    const int task = blockIdx.x + n * gridDim.x, row0 = task * slab_rows, st = n % stages;
+    const int rows_here = min(slab_rows, rows - row0);
+    // the rows of a slab lie in one 128-row scale block (1, 2 and 4 divide 128)
+    const float* wscale = scales + static_cast<size_t>(row0 / 128) * groups128 + my_half * half_groups;
+    float total = 0.0f;
+    const bool ok = mbar_wait(&full[st], (n / stages) & 1, status, 43);
+    if (!ok) *reinterpret_cast<volatile int*>(failed + group) = 1;
+    if (ok) {
+      // columns past the slab's pieces (slabs of fewer than 4 rows) re-read its last piece; their
+      // results are never stored
+      const uint8_t* b_ptr = ring + st * layout.slab_bytes + min(g, 2 * slab_rows - 1) * stride + q * 16;
+      for (int kg = gwarp; kg < half_groups; kg += kGroupWarps) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int block = 0; block < 2; ++block) {
+          const uint4 b = *reinterpret_cast<const uint4*>(b_ptr + kg * 128 + block * 64);
+          uint4 a = make_uint4(0u, 0u, 0u, 0u);
+          if (a_valid) a = *reinterpret_cast<const uint4*>(a_ptr + kg * 128 + block * 64);
+          mma_e4m3(acc, a.x, 0u, a.y, 0u, b.x, b.y);
+          mma_e4m3(acc, a.z, 0u, a.w, 0u, b.z, b.w);
+        }
+        // the element whose B half matches this lane's A half
+        total = fmaf(my_half ? acc[1] : acc[0], wscale[kg] * my_xscale[kg], total);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);
+    }
+    total += __shfl_xor_sync(0xffffffffu, total, 4);   // the two halves: lanes g and g ^ 1
+    // [buffer][group][warp of the group][token][row]
+    float* mine = partial + (((turn & 1) * kGroups + group) * kGroupWarps) * 4 * kRows;
+    if (my_half == 0) mine[(gwarp * 4 + my_token) * kRows + q] = total;
+    asm volatile("bar.sync %0, %1;" ::"r"(2 + group), "n"(kGroupThreads) : "memory");
+    if (*reinterpret_cast<volatile int*>(failed + group)) break;   // same for the whole group
+    if (gthread < 4 * kRows) {
+      const int t = gthread / kRows, r = gthread % kRows;
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kGroupWarps; ++w) v += mine[(w * 4 + t) * kRows + r];
+      if (t < tokens && r < rows_here) y[static_cast<size_t>(t) * rows + row0 + r] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+// Rows so long that only slabs of fewer than 4 rows fit the ring leave B columns unused and were
+// measured slower than the FMA form ([5120 x 8192]: 19.8 against 18.3 us), so they do not qualify.
+inline bool stream_mma_ok(const void* weights, const void* x, int cols, int rows, int tokens, int sms) {
+  if (tokens > 4 || cols % 256 != 0 || reinterpret_cast<uintptr_t>(weights) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(x) % 8 != 0 || rows < 2 * kRows * kStreamCtasPerSm * sms)
+    return false;
+  const StreamMmaLayout layout = stream_mma_layout(cols, tokens);
+  return layout.stages > 0 && layout.slab_rows == kRows;
+}
+
+inline cudaError_t launch_stream_mma(cudaStream_t stream, const void* weights, const float* scales,
+                                     const void* x, void* y, int cols, int rows, int tokens, int sms) {
+  const StreamMmaLayout layout = stream_mma_layout(cols, tokens);
+  const cudaError_t e = cudaFuncSetAttribute(linear_gemv_stream_e4m3, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(layout.total));
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(kStreamCtasPerSm * sms);
+  config.blockDim = dim3(kThreads + 32);
+  config.dynamicSmemBytes = layout.total;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, linear_gemv_stream_e4m3, static_cast<const uint8_t*>(weights), scales,
+                            static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), cols, rows,
+                            tokens, layout, kernel_status_word());
+}
+
 template <int STORAGE>
 bool mma_path_ok(const void* weights, const void* x, int cols, int tokens) {
   const size_t smem = static_cast<size_t>(tokens) * cols * (STORAGE == 1 ? 2 : 1) +
@@ -657,17 +890,29 @@ cudaError_t dispatch(cudaStream_t stream, const void* weights, const float* scal
   auto* yout = static_cast<__nv_bfloat16*>(y);
   if constexpr (STORAGE != 0) {
     // Measured on a [10240 x 5120] matrix, us per call with the weights coming from HBM:
-    //   tokens              1      2      3      4      8
-    //   bf16 streaming     21.2   29.0    -     35.3    -
-    //   bf16 tensor-core   24.7   24.7    -     35.4   38.2
-    //   FP8 streaming      17.2   23.2   38.3   56.1    -
-    //   FP8 tensor-core    26.9   33.0    -     45.1    -
+    //   tokens                          1      2      3      4      8
+    //   bf16 ring, FMA                 21.2   29.0    -     35.3    -
+    //   bf16 tensor cores from global  24.7   24.7    -     35.4   38.2
+    //   FP8 ring, tensor cores         14.8   17.0    -     21.5   41.2 (two passes)
+    //   FP8 ring, FMA                  17.2   23.2   38.3   56.1    -
+    //   FP8 tensor cores from global   26.9   33.0    -     45.1   69.0
     // (the FMA form without the ring: 25.7 and 23.3 for one token, 80-143 for FP8 batches whose
-    // activation no longer fits its staging buffer).  So one bf16 token and up to three FP8 tokens
-    // stream; everything else that qualifies takes the tensor-core form, 8 tokens per pass.
+    // activation no longer fits its staging buffer).  So FP8 takes the ring with tensor cores in
+    // passes of 4 tokens when the shape qualifies, else the FMA ring for up to three tokens; one
+    // bf16 token takes the FMA ring; everything else that qualifies takes the tensor-core form
+    // that loads from global memory, 8 tokens per pass.
     int sms = 148, device = 0;
     if (cudaGetDevice(&device) == cudaSuccess)
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (STORAGE == 2 && stream_mma_ok(weights, x, cols, rows, std::min(tokens, 4), sms)) {
+      for (int t0 = 0; t0 < tokens; t0 += 4) {
+        const cudaError_t e = launch_stream_mma(stream, weights, scales, xin + static_cast<size_t>(t0) * cols,
+                                                yout + static_cast<size_t>(t0) * rows, cols, rows,
+                                                std::min(4, tokens - t0), sms);
+        if (e != cudaSuccess) return e;
+      }
+      return cudaSuccess;
+    }
     const bool streamed = tokens <= (STORAGE == 1 ? 1 : 3) &&
                           stream_path_ok<STORAGE>(weights, cols, rows, tokens >= 2 ? 2 : 1, sms);
     if (!streamed && mma_path_ok<STORAGE>(weights, x, cols, std::min(tokens, kMmaTokens))) {

@@ -131,22 +131,24 @@ def test_several_tokens_share_one_pass_and_match_single_token_calls():
             assert np.all(np.abs(part - batched[:n]) <= 5e-5 + 0.008 * np.abs(part)), n
 
 
-@pytest.mark.parametrize("cols,rows", [(1024, 1290), (2176, 1400), (5120, 1536), (8192, 1203)])
+@pytest.mark.parametrize("cols,rows", [(1024, 2402), (2176, 2370), (5120, 2560), (8192, 2371)])
 def test_streamed_weight_ring_matches_oracle_for_one_to_four_tokens(cols, rows):
-    """Enough 4-row tasks for the persistent streaming kernel (a ring of bulk-copied weight
-    slabs per SM), a last slab of two rows, a width that is not a multiple of the 256-thread
-    stride, and every token count of one pass; bf16 and FP8 against the CPU oracle."""
+    """Enough 4-row tasks for the persistent streaming kernels (a ring of bulk-copied weight
+    slabs, two CTAs per SM), a last slab of fewer rows, a width that is not a multiple of 256
+    (FP8 then takes the FMA form of the ring instead of the tensor-core form), slabs of two rows
+    (8192 columns), and one to six tokens; bf16 and FP8 against the CPU oracle."""
     rng = np.random.default_rng(cols + rows)
     w = (rng.standard_normal((rows, cols)) * 0.5).astype(np.float32)
-    x = oracle.round_bf16(rng.standard_normal((4, cols)).astype(np.float32))
+    x = oracle.round_bf16(rng.standard_normal((6, cols)).astype(np.float32))
+    x[1, 128:256] = 0.0          # an all-zero quantisation group
     scale_cols, scale_rows = (cols + 127) // 128, (rows + 127) // 128
     scales = (0.25 + rng.random((scale_rows, scale_cols))).astype(np.float32)
     for storage in (MatrixStorage.kBFloat16, MatrixStorage.kFp8E4M3):
         weights, stored, name = upload(w, storage)
         fp8 = storage == MatrixStorage.kFp8E4M3
         layer = FullyConnectedLayer.Create(weights, storage, cols, rows, dev(scales) if fp8 else None)
-        want = np.stack([oracle.linear_imported(stored, name, x[t], scales if fp8 else None) for t in range(4)])
-        for n in (1, 2, 3, 4):
+        want = np.stack([oracle.linear_imported(stored, name, x[t], scales if fp8 else None) for t in range(6)])
+        for n in (1, 2, 3, 4, 6):
             got = layer.fwd([to_device_bf16(bf(x[:n])).view(n, cols)]).outputs[0].float().cpu().numpy()
             assert np.all(np.abs(got - want[:n]) <= 5e-5 + 0.008 * np.abs(want[:n])), (name, n)
 
