@@ -45,50 +45,66 @@ struct BwdParams {
 };
 
 // ---------------------------------------------------------------------------------------------
-// prep: grid (rows), 128 threads; one row (all heads) per CTA
+// prep: a stream over the (token, head) rows of dO and O, which are contiguous in that order.
+// D / 8 lanes share a row (8 channels a lane: two 16-byte gradient loads, one 16-byte output
+// load, one 16-byte bf16 store), so a warp covers 4 (D = 64) or 2 (D = 128) rows per step and
+// the row sum needs 3 or 4 shuffles; two steps are in flight per warp.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
+template <int D>
+__global__ void __launch_bounds__(256)
 attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d_out,  // out may be null
               const float* __restrict__ maxima, const float* __restrict__ normalizers,
               __nv_bfloat16* __restrict__ d_out_bf16, float4* __restrict__ stats,
-              float* __restrict__ deltas, int seq, int seq_pad, int heads, int head_dim) {
-  const int b = blockIdx.y, s = blockIdx.x;   // s runs over the padded length
-  const int E = heads * head_dim;
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  for (int h = warp; h < heads; h += 4) {
-    const size_t record = (static_cast<size_t>(b) * heads + h) * seq_pad + s;
-    if (s >= seq) {
-      if (lane == 0) stats[record] = make_float4(0.f, 0.f, 0.f, 0.f);
-      continue;
-    }
-    const size_t row = static_cast<size_t>(b) * seq + s;
-    float part = 0.0f;
-    const size_t base = row * E + static_cast<size_t>(h) * head_dim;
-    if (head_dim == 128) {          // four channels per lane: 16-byte gradient loads
-      const float4 g = *reinterpret_cast<const float4*>(d_out + base + lane * 4);
-      if (out != nullptr) {
-        const uint2 o = *reinterpret_cast<const uint2*>(out + base + lane * 4);
-        part = g.x * bf16_lo(o.x) + g.y * bf16_hi(o.x) + g.z * bf16_lo(o.y) + g.w * bf16_hi(o.y);
-      }
-      *reinterpret_cast<uint2*>(d_out_bf16 + base + lane * 4) =
-          make_uint2(pack_bf16(g.x, g.y), pack_bf16(g.z, g.w));
-    } else {                        // head_dim 64: two channels per lane
-      const float2 g = *reinterpret_cast<const float2*>(d_out + base + lane * 2);
-      if (out != nullptr) {
-        const uint32_t o = *reinterpret_cast<const uint32_t*>(out + base + lane * 2);
-        part = g.x * bf16_lo(o) + g.y * bf16_hi(o);
-      }
-      *reinterpret_cast<uint32_t*>(d_out_bf16 + base + lane * 2) = pack_bf16(g.x, g.y);
+              float* __restrict__ deltas, int batch, int seq, int seq_pad, int heads) {
+  constexpr int kLanes = D / 8;              // lanes per row
+  constexpr int kRowsPerWarp = 32 / kLanes;
+  constexpr int kUnroll = 2;
+  const int lane = threadIdx.x % 32, sub = lane % kLanes;
+  const long long n_rows = static_cast<long long>(batch) * seq * heads;
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
+  const long long n_warps = static_cast<long long>(gridDim.x) * blockDim.x / 32;
+  for (long long first = warp_global * kRowsPerWarp; first < n_rows; first += n_warps * kRowsPerWarp * kUnroll) {
+    float4 g0[kUnroll], g1[kUnroll];
+    uint4 o[kUnroll];
+    long long row[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      row[u] = first + u * n_warps * kRowsPerWarp + lane / kLanes;
+      const long long r = row[u] < n_rows ? row[u] : n_rows - 1;   // past the end: a valid row, not stored
+      const size_t base = static_cast<size_t>(r) * D + sub * 8;
+      g0[u] = *reinterpret_cast<const float4*>(d_out + base);
+      g1[u] = *reinterpret_cast<const float4*>(d_out + base + 4);
+      o[u] = out != nullptr ? *reinterpret_cast<const uint4*>(out + base) : make_uint4(0u, 0u, 0u, 0u);
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    if (lane == 0) {
-      const size_t stat = (static_cast<size_t>(b) * heads + h) * seq + s;
-      if (out != nullptr) deltas[stat] = part;   // otherwise the caller's deltas are the input
-      else part = deltas[stat];
-      stats[record] = make_float4(maxima[stat] * kLog2e, 1.0f / normalizers[stat], part, 0.0f);
+    for (int u = 0; u < kUnroll; ++u) {
+      float part = g0[u].x * bf16_lo(o[u].x) + g0[u].y * bf16_hi(o[u].x) + g0[u].z * bf16_lo(o[u].y) +
+                   g0[u].w * bf16_hi(o[u].y) + g1[u].x * bf16_lo(o[u].z) + g1[u].y * bf16_hi(o[u].z) +
+                   g1[u].z * bf16_lo(o[u].w) + g1[u].w * bf16_hi(o[u].w);
+#pragma unroll
+      for (int off = kLanes / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+      if (row[u] >= n_rows) continue;
+      *reinterpret_cast<uint4*>(d_out_bf16 + static_cast<size_t>(row[u]) * D + sub * 8) =
+          make_uint4(pack_bf16(g0[u].x, g0[u].y), pack_bf16(g0[u].z, g0[u].w), pack_bf16(g1[u].x, g1[u].y),
+                     pack_bf16(g1[u].z, g1[u].w));
+      if (sub == 0) {
+        const int h = static_cast<int>(row[u] % heads);
+        const long long token = row[u] / heads;
+        const int b = static_cast<int>(token / seq), t = static_cast<int>(token % seq);
+        const size_t stat = (static_cast<size_t>(b) * heads + h) * seq + t;
+        if (out != nullptr) deltas[stat] = part;   // otherwise the caller's deltas are the input
+        else part = deltas[stat];
+        stats[(static_cast<size_t>(b) * heads + h) * seq_pad + t] =
+            make_float4(maxima[stat] * kLog2e, 1.0f / normalizers[stat], part, 0.0f);
+      }
     }
   }
+  // records of the padding past the sequence end read as zero
+  const int pad = seq_pad - seq;
+  const long long n_pad = static_cast<long long>(batch) * heads * pad;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_pad;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    stats[(i / pad) * seq_pad + seq + i % pad] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
 struct DqBarriers {
@@ -596,9 +612,14 @@ cudaError_t gqa_bwd_tc(cudaStream_t stream, const GqaBwdTcArgs& a) {
   const size_t do_bytes = (static_cast<size_t>(a.batch) * a.seq * E * 2 + 255) / 256 * 256;
   auto* do_bf16 = static_cast<__nv_bfloat16*>(a.workspace);
   auto* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.workspace) + do_bytes);
-  attn_bwd_prep<<<dim3(seq_pad, a.batch), 128, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(a.out), a.d_out, a.maxima, a.normalizers, do_bf16, stats,
-      a.deltas, a.seq, seq_pad, a.q_heads, D);
+  {
+    const long long n_rows = static_cast<long long>(a.batch) * a.seq * a.q_heads;
+    const long long rows_per_cta = 8 * (32 / (D / 8)) * 2;   // 8 warps, two steps each
+    const unsigned blocks = static_cast<unsigned>(std::min<long long>((n_rows + rows_per_cta - 1) / rows_per_cta, 148 * 8));
+    auto prep = D == 128 ? attn_bwd_prep<128> : attn_bwd_prep<64>;
+    prep<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.out), a.d_out, a.maxima, a.normalizers,
+                                     do_bf16, stats, a.deltas, a.batch, a.seq, seq_pad, a.q_heads);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   BwdMaps m;

@@ -115,8 +115,8 @@ int pluto_attn_bwd(pluto_stream_t stream, const void* qkv, const void* out, cons
     if (need == 0)
       return fail(PLUTO_E_INVALID, "attention backward has no tensor-core path for this shape; pass a null workspace");
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 ||
-        !aligned16(qkv) || !aligned16(d_qkv))
-      return fail(PLUTO_E_INVALID, "attention backward workspace is too small or misaligned");
+        !aligned16(qkv) || !aligned16(d_qkv) || !aligned16(out) || !aligned16(d_out))
+      return fail(PLUTO_E_INVALID, "attention backward workspace is too small or a tensor is misaligned");
     uint32_t* status = pluto::kernel_status_word();
     if (!status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
     return from_cuda(pluto::attn_bwd_tc(stream, qkv, out, d_out, maxima, normalizers, d_qkv, deltas,
@@ -246,7 +246,7 @@ int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, c
   // bf16 tensors of head width 64/128 with a dense query run on tcgen05 when a workspace is given
   if (workspace != nullptr && tensor_core_shape(head_dim, dtype) && q_head_stride == D &&
       q_token_stride % 8 == 0 && q_token_stride <= 0x7fffffffu && aligned16(q) && aligned16(k) &&
-      aligned16(v) && aligned16(workspace)) {
+      aligned16(v) && aligned16(dc) && aligned16(workspace)) {
     if (workspace_bytes < pluto::attn_bwd_tc_workspace_bytes(batch, seq, q_heads, head_dim))
       return fail(PLUTO_E_INVALID, "attention backward workspace is too small");
     pluto::GqaBwdTcArgs t{};
