@@ -6,7 +6,7 @@ import torch
 
 import oracle
 from gpu_util import to_device_bf16
-from pluto_b200 import PlutoStatusError
+from pluto_b200 import PlutoStatusError, _capi
 from pluto_b200.layers import DataType, FullyConnectedLayer, MatrixStorage
 
 pytestmark = pytest.mark.gpu
@@ -151,6 +151,44 @@ def test_streamed_weight_ring_matches_oracle_for_one_to_four_tokens(cols, rows):
         for n in (1, 2, 3, 4, 6):
             got = layer.fwd([to_device_bf16(bf(x[:n])).view(n, cols)]).outputs[0].float().cpu().numpy()
             assert np.all(np.abs(got - want[:n]) <= 5e-5 + 0.008 * np.abs(want[:n])), (name, n)
+
+
+def test_back_to_back_projections_see_each_others_outputs():
+    """The streaming kernels start copying weights while the previous kernel of the stream still
+    runs; a chain in which every call's activation is the previous call's output (no host
+    synchronisation in between, buffers re-used round after round) must still equal the oracle."""
+    width = 2560
+    rng = np.random.default_rng(11)
+    x = oracle.round_bf16(rng.standard_normal((1, width)).astype(np.float32))
+    scales = (0.5 + rng.random((width // 128, width // 128))).astype(np.float32)
+    for storage in (MatrixStorage.kBFloat16, MatrixStorage.kFp8E4M3):
+        fp8 = storage == MatrixStorage.kFp8E4M3
+        layers, stored = [], []
+        for i in range(3):
+            w = (rng.standard_normal((width, width)) * (0.6 / np.sqrt(width) if not fp8 else 0.4)).astype(np.float32)
+            weights, kept, name = upload(w, storage)
+            layers.append(FullyConnectedLayer.Create(weights, storage, width, width, dev(scales) if fp8 else None))
+            stored.append(kept)
+        want = x[0]
+        for kept in stored:
+            want = oracle.linear_imported(kept, name, want, scales if fp8 else None)
+        L, stream = _capi.lib(), torch.cuda.current_stream().cuda_stream
+        buffers = [to_device_bf16(bf(x)).view(1, width)] + [torch.zeros(1, width, dtype=torch.bfloat16, device="cuda")
+                                                           for _ in range(3)]
+        results = []
+        for _ in range(20):
+            buffers[1].zero_(); buffers[2].zero_(); buffers[3].zero_()
+            for i, layer in enumerate(layers):
+                held = layer.weights()
+                _capi.check(L.pluto_linear_imported_fwd(stream, held[0].data_ptr(), storage.value,
+                                                        held[1].data_ptr() if fp8 else None, buffers[i].data_ptr(),
+                                                        buffers[i + 1].data_ptr(), 1, width, width))
+            results.append(buffers[3].clone())
+        torch.cuda.synchronize()
+        for got in results:
+            got = got.float().cpu().numpy().ravel()
+            assert np.all(np.abs(got - want) <= 2e-3 + 0.03 * np.abs(want)), name
+            assert np.array_equal(got, results[0].float().cpu().numpy().ravel())   # and bit-identical every round
 
 
 def test_rejects_bad_storage_dimensions_and_scales():
