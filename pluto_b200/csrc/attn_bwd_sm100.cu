@@ -59,6 +59,7 @@ attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d
   constexpr int kLanes = D / 8;              // lanes per row
   constexpr int kRowsPerWarp = 32 / kLanes;
   constexpr int kUnroll = 2;
+  pdl_launch_dependents();   // the dQ kernel may set itself up (barriers, TMEM) while this one runs
   const int lane = threadIdx.x % 32, sub = lane % kLanes;
   const long long n_rows = static_cast<long long>(batch) * seq * heads;
   const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
@@ -172,6 +173,12 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
+  // Launched with programmatic stream serialisation: everything above overlapped the prep kernel;
+  // its records and the bf16 gradient are read, and dQ is written, only after it has completed.
+  // The dK/dV kernel reads nothing this kernel writes, so it may start as soon as every CTA of
+  // this grid has got here (prep is then complete) and fill the SMs this grid's last CTAs leave.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -588,13 +595,21 @@ cudaError_t launch_bwd_tc(cudaStream_t stream, const BwdMaps& m, const BwdParams
                            static_cast<int>(dkv_smem));
   if (e != cudaSuccess) return e;
   const int tiles = (p.seq + kRowTile - 1) / kRowTile;
-  attn_bwd_dq_sm100<D><<<dim3(p.heads * batch, tiles), kBwdThreads, dq_smem, stream>>>(
-      m.q128, m.k64, m.v64, m.do128, p);
-  e = cudaGetLastError();
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config = {};
+  config.blockDim = dim3(kBwdThreads);
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  config.gridDim = dim3(p.heads * batch, tiles);
+  config.dynamicSmemBytes = dq_smem;
+  e = cudaLaunchKernelEx(&config, attn_bwd_dq_sm100<D>, m.q128, m.k64, m.v64, m.do128, p);
   if (e != cudaSuccess) return e;
-  attn_bwd_dkv_sm100<D><<<dim3((p.heads / p.group) * batch, tiles), kBwdThreads, dkv_smem, stream>>>(
-      m.k128, m.v128, m.q64, m.do64, p);
-  return cudaGetLastError();
+  config.gridDim = dim3((p.heads / p.group) * batch, tiles);
+  config.dynamicSmemBytes = dkv_smem;
+  return cudaLaunchKernelEx(&config, attn_bwd_dkv_sm100<D>, m.k128, m.v128, m.q64, m.do64, p);
 }
 
 }  // namespace
