@@ -1,4 +1,4 @@
-"""Head sharding across the GPUs of one box.
+"""Head sharding across the GPUs of one box, and the matching split of the projections either side.
 
 Attention is independent per (sequence, head) and per KV-head group, so the engine scales by
 giving each rank a contiguous range of KV heads together with the query heads that read them;
@@ -73,3 +73,69 @@ def allgather_heads(local: torch.Tensor, group: Optional[dist.ProcessGroup] = No
         # host tensors (gloo, used by the CPU tests of this plumbing): a plain strided copy
         out.view(rows, world, cols).copy_(gathered.view(world, rows, cols).permute(1, 0, 2))
     return out
+
+
+# -------------------------------------------------------------------------------------------------
+# Projections either side of a head-sharded attention layer (src/llm/qwen/model.cc:192-227 calls
+# them in this order: q/gate, k, v projections -> attention -> output projection).
+#   * The q/gate, k and v projections are split by OUTPUT (column-parallel): an output-major
+#     matrix [rows, hidden] gives each rank the contiguous rows of its own heads, so a rank's
+#     shard is a view and its projection needs no communication.
+#   * The output projection is split by INPUT (row-parallel): a rank multiplies its heads'
+#     columns of W_o and the partial results are summed over the ranks (one all-reduce).
+# -------------------------------------------------------------------------------------------------
+def projection_rows(shard: HeadShard, head_dim: int, values_per_head: int = 1, kv: bool = False):
+    """Row range [begin, end) of an output-major projection matrix that produces this rank's heads.
+    values_per_head = 2 for Qwen's fused query + gate projection ([Hq, 2, D] outputs)."""
+    if head_dim <= 0 or values_per_head <= 0:
+        raise PlutoStatusError("InvalidArgument", "invalid projection dimensions", -1)
+    per_head = head_dim * values_per_head
+    if kv:
+        return shard.kv_begin * per_head, shard.kv_end * per_head
+    return shard.q_begin * per_head, shard.q_end * per_head
+
+
+def shard_output_major(weights: torch.Tensor, scales: Optional[torch.Tensor], begin: int, end: int):
+    """Rows [begin, end) of an output-major matrix [rows, cols] as a view, with the matching rows
+    of its 128x128 block scales (fully_connected.cc:267-293) when it has them; the range must
+    then start and end on a multiple of 128 rows (or at the matrix end)."""
+    rows, cols = weights.shape
+    if not 0 <= begin < end <= rows:
+        raise PlutoStatusError("InvalidArgument", "projection shard outside the matrix", -1)
+    if scales is None:
+        return weights[begin:end], None
+    if begin % 128 != 0 or (end % 128 != 0 and end != rows):
+        raise PlutoStatusError("InvalidArgument",
+                               "FP8 projection shards must cover whole 128-row scale blocks", -1)
+    scale_cols = (cols + 127) // 128
+    table = scales.view((rows + 127) // 128, scale_cols)
+    return weights[begin:end], table[begin // 128:(end + 127) // 128].reshape(-1)
+
+
+def shard_input_columns(weights: torch.Tensor, scales: Optional[torch.Tensor], begin: int, end: int):
+    """Columns [begin, end) of an output-major matrix (the row-parallel split of the output
+    projection), copied once at load time into a contiguous matrix, with the matching columns of
+    its block scales; FP8 ranges must cover whole 128-column scale blocks."""
+    rows, cols = weights.shape
+    if not 0 <= begin < end <= cols:
+        raise PlutoStatusError("InvalidArgument", "projection shard outside the matrix", -1)
+    part = weights[:, begin:end].contiguous()
+    if scales is None:
+        return part, None
+    if begin % 128 != 0 or (end % 128 != 0 and end != cols):
+        raise PlutoStatusError("InvalidArgument",
+                               "FP8 projection shards must cover whole 128-column scale blocks", -1)
+    table = scales.view((rows + 127) // 128, (cols + 127) // 128)
+    return part, table[:, begin // 128:(end + 127) // 128].contiguous().reshape(-1)
+
+
+def reduce_row_parallel(partial: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Sum of the ranks' partial output-projection results, returned in the input's dtype.  The
+    partials are summed at fp32 (bf16 partials get one final rounding whatever the number of
+    ranks).  This is NCCL's all-reduce over NVLink / NVSwitch as it stands: the projection kernel
+    and the reduction are separate steps, not one fused kernel over peer memory."""
+    if dist.get_world_size(group) == 1:
+        return partial
+    total = partial.float()
+    dist.all_reduce(total, group=group)
+    return total.to(partial.dtype)
