@@ -378,22 +378,68 @@ __global__ void __launch_bounds__(128) gqa_decode_generic(DecodeArgs a) {
 }
 
 // Merge of the per-chunk partials in chunk order, then the reference's output stage
-// (cached_attention_ops.cc:120-125): out = R(R(acc/l) * R(sigmoid(gate))).  grid (q_heads, batch).
-__global__ void gqa_decode_merge(DecodeArgs a) {
+// (cached_attention_ops.cc:120-125): out = R(R(acc/l) * R(sigmoid(gate))).  grid (q_heads, batch),
+// 128 threads.  The chunks' maxima are reduced in parallel and every chunk's weight
+// 2^(m_s - m) is computed once, by one thread, into shared memory; the sums then run over the
+// chunks in order (so the result does not depend on the thread count) with the loads of eight
+// chunks in flight.
+constexpr int kMergeThreads = 128;
+constexpr int kMergeSplits = 1024;   // chunk weights held in shared memory per pass
+
+__global__ void __launch_bounds__(kMergeThreads) gqa_decode_merge(DecodeArgs a) {
   const int head = blockIdx.x, b = blockIdx.y, D = a.head_dim;
   const int length = a.seq_lens[b];
   const int splits = (length + a.split_tokens - 1) / a.split_tokens;
   const size_t slot0 = (static_cast<size_t>(b) * a.q_heads + head) * a.splits;
-  float m_tot = -INFINITY;
-  for (int s = 0; s < splits; ++s) m_tot = fmaxf(m_tot, a.partial_ml[(slot0 + s) * 2]);
+  __shared__ float weight[kMergeSplits];   // 2^(m_s - m_tot)
+  __shared__ float scaled_l[kMergeSplits]; // l_s * weight_s
+  __shared__ float warp_max[kMergeThreads / 32];
+  const float2* ml = reinterpret_cast<const float2*>(a.partial_ml) + slot0;   // (m_s, l_s)
+
+  float m_part = -INFINITY;
+  for (int s = threadIdx.x; s < splits; s += kMergeThreads) m_part = fmaxf(m_part, ml[s].x);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m_part = fmaxf(m_part, __shfl_xor_sync(0xffffffffu, m_part, o));
+  if (threadIdx.x % 32 == 0) warp_max[threadIdx.x / 32] = m_part;
+  __syncthreads();
+  float m_tot = warp_max[0];
+#pragma unroll
+  for (int w = 1; w < kMergeThreads / 32; ++w) m_tot = fmaxf(m_tot, warp_max[w]);
+
   float l_tot = 0.0f;
-  for (int s = 0; s < splits; ++s)
-    l_tot += a.partial_ml[(slot0 + s) * 2 + 1] * exp2f(a.partial_ml[(slot0 + s) * 2] - m_tot);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.0f;
-    for (int s = 0; s < splits; ++s)
-      acc += a.partial_acc[(slot0 + s) * D + d] * exp2f(a.partial_ml[(slot0 + s) * 2] - m_tot);
-    float value = acc / l_tot;
+  float acc[2] = {0.0f, 0.0f};               // channels threadIdx.x and threadIdx.x + 128
+  for (int s0 = 0; s0 < splits; s0 += kMergeSplits) {
+    const int count = min(kMergeSplits, splits - s0);
+    __syncthreads();                          // the previous pass is done with the arrays
+    for (int s = threadIdx.x; s < count; s += kMergeThreads) {
+      const float2 v = ml[s0 + s];
+      const float w = exp2f(v.x - m_tot);
+      weight[s] = w;
+      scaled_l[s] = v.y * w;
+    }
+    __syncthreads();
+    for (int s = 0; s < count; ++s) l_tot += scaled_l[s];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int d = threadIdx.x + c * kMergeThreads;
+      if (d >= D) continue;
+      const float* column = a.partial_acc + (slot0 + s0) * D + d;
+      int s = 0;
+      for (; s + 8 <= count; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = column[static_cast<size_t>(s + u) * D];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[c] += v[u] * weight[s + u];
+      }
+      for (; s < count; ++s) acc[c] += column[static_cast<size_t>(s) * D] * weight[s];
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int d = threadIdx.x + c * kMergeThreads;
+    if (d >= D) continue;
+    float value = acc[c] / l_tot;
     if (a.round) value = bf16_round(value);
     if (a.gate) {
       const size_t g = static_cast<size_t>(b) * a.gate_token + static_cast<size_t>(head) * a.gate_head + d;
@@ -532,7 +578,7 @@ cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
-  gqa_decode_merge<<<dim3(a.q_heads, a.batch), 128, 0, stream>>>(a);
+  gqa_decode_merge<<<dim3(a.q_heads, a.batch), kMergeThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }
 
