@@ -57,8 +57,10 @@ __global__ void __launch_bounds__(kRecThreads) gdn_recurrent_kernel(GdnArgs a) {
   }
 
   auto stage = [&](int buf, int t0) {
-    // q, k vectors of kBlockT tokens (normalised here), this slice of v, the two gates
-    for (int idx = threadIdx.x; idx < kBlockT * 128; idx += kRecThreads) {
+    // q, k vectors of up to kBlockT tokens (normalised here), this slice of v, the two gates; a
+    // single-token step stages one token, not sixteen
+    const int n_tok = min(kBlockT, a.tokens - t0);
+    for (int idx = threadIdx.x; idx < n_tok * 128; idx += kRecThreads) {
       const int tt = idx / 128, i = idx % 128, t = t0 + tt;
       float qv = 0.0f, kv = 0.0f;
       if (t < a.tokens && i < dk) {
@@ -69,7 +71,7 @@ __global__ void __launch_bounds__(kRecThreads) gdn_recurrent_kernel(GdnArgs a) {
       sq[buf][tt][i] = qv;
       sk[buf][tt][i] = kv;
     }
-    for (int idx = threadIdx.x; idx < kBlockT * kSlice; idx += kRecThreads) {
+    for (int idx = threadIdx.x; idx < n_tok * kSlice; idx += kRecThreads) {
       const int tt = idx / kSlice, j = idx % kSlice, t = t0 + tt, c = slice * kSlice + j;
       float x = 0.0f;
       if (t < a.tokens && c < dv)
@@ -77,17 +79,19 @@ __global__ void __launch_bounds__(kRecThreads) gdn_recurrent_kernel(GdnArgs a) {
                      a.in_is_bf16);
       sv[buf][tt][j] = x;
     }
-    if (threadIdx.x < kBlockT) {
+    if (threadIdx.x < n_tok) {
       const int t = t0 + threadIdx.x;
       const size_t off = (static_cast<size_t>(b) * a.tokens + min(t, a.tokens - 1)) * a.value_heads + h;
       sg[buf][threadIdx.x] = a.g[off];
       sb[buf][threadIdx.x] = a.beta[off];
     }
   };
-  auto normalise = [&](int buf) {
-    // each warp owns 4 tokens x {q, k}: lane covers 4 channels
-    for (int v = warp; v < 2 * kBlockT; v += 4) {
-      float* vec = v < kBlockT ? sq[buf][v] : sk[buf][v - kBlockT];
+  auto normalise = [&](int buf, int t0) {
+    // vectors 0 .. n_tok-1 are the queries, n_tok .. 2 n_tok - 1 the keys; lane covers 4 channels
+    const int n_tok = min(kBlockT, a.tokens - t0);
+    for (int v = warp; v < 2 * n_tok; v += 4) {
+      const bool is_query = v < n_tok;
+      float* vec = is_query ? sq[buf][v] : sk[buf][v - n_tok];
       float x[4], ss = 0.0f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) { x[i] = vec[lane + 32 * i]; ss += x[i] * x[i]; }
@@ -96,9 +100,9 @@ __global__ void __launch_bounds__(kRecThreads) gdn_recurrent_kernel(GdnArgs a) {
       float f;
       if (a.normalize_qk) {
         f = rsqrtf(ss + 1e-6f);
-        if (v < kBlockT) f = f / sqrtf(static_cast<float>(dk));
+        if (is_query) f = f / sqrtf(static_cast<float>(dk));
       } else {
-        f = v < kBlockT ? a.q_scale : 1.0f;
+        f = is_query ? a.q_scale : 1.0f;
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) vec[lane + 32 * i] = x[i] * f;
@@ -107,7 +111,7 @@ __global__ void __launch_bounds__(kRecThreads) gdn_recurrent_kernel(GdnArgs a) {
 
   stage(0, 0);
   __syncthreads();
-  normalise(0);
+  normalise(0, 0);
   __syncthreads();
   const int blocks = (a.tokens + kBlockT - 1) / kBlockT;
   for (int blk = 0; blk < blocks; ++blk) {
@@ -143,7 +147,7 @@ __global__ void __launch_bounds__(kRecThreads) gdn_recurrent_kernel(GdnArgs a) {
     }
     __syncthreads();
     if (blk + 1 < blocks) {
-      normalise(buf ^ 1);
+      normalise(buf ^ 1, (blk + 1) * kBlockT);
       __syncthreads();
     }
   }
