@@ -133,7 +133,11 @@ size_t pluto_gqa_prefill_fwd_workspace_bytes(int batch, int seq, int q_heads, in
  * v_host bf16 [batch, seq, kv_heads, head_dim], all dense.  The key/value heads are processed in
  * groups of kv_heads_per_group (with their query heads); each group's host->device copy, kernel
  * and device->host copy run on separate streams, two groups in flight, so the PCIe transfers of
- * both directions overlap each other and the kernels.  No gate, statistics or core output.
+ * both directions overlap each other and the kernels.  kv_heads_per_group = 0 (head width 64 or
+ * 128) cuts the prompt by query tokens instead: chunks of 1024 tokens are copied as contiguous
+ * pieces (queries, keys and values alike), a chunk's queries run against all keys copied so far
+ * (causal attention needs no later ones), and its output rows leave as one contiguous piece; the
+ * workspace then holds the whole Q, K, V and output.  No gate, statistics or core output.
  * workspace: device memory of pluto_gqa_prefill_host_workspace_bytes, 256-byte aligned.  Ordered
  * behind `stream`; `stream` waits for the last output copy, so synchronising it (or ordering
  * later work on it) is enough.  Uses two internal copy streams and a few events per device,

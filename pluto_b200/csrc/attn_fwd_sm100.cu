@@ -54,6 +54,7 @@ struct FwdParams {
   float4* part_m;              // [split][batch][heads][seq] = (max used * scale_log2, true max *
                                //  scale_log2, sum relative to max used, 0)
   uint32_t* status;
+  int tile_end;                // one past the last query tile this launch computes
 };
 
 struct Barriers {
@@ -86,7 +87,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   // (sequence, head) varies fastest, the tile index slowest: the longest tiles of every head start
   // first and the shortest fill the tail.
-  const int q_tile = gridDim.y - 1 - blockIdx.y;
+  // The grid's y extent may cover only the query tiles [tile_end - gridDim.y, tile_end).
+  const int q_tile = p.tile_end - 1 - blockIdx.y;
   const int head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
   const int n_tiles = q_tile + 1;                 // causal: key tiles 0..q_tile
 
@@ -385,7 +387,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
   // (longest-processing-time-first over the whole grid, not per head).
   // With key/value splits, blockIdx.y = slot * splits + part and the parts of the longest pairs
   // still start first.
-  const int pair = gridDim.y / p.splits - 1 - blockIdx.y / p.splits;
+  const int pair = (p.tile_end + 1) / 2 - 1 - blockIdx.y / p.splits;   // pairs below the grid's range are not run
   const int part = blockIdx.y % p.splits;
   const int head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
   const int q_tiles = (p.seq + kBM - 1) / kBM;
@@ -865,7 +867,14 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
   p.gate_head = a.gate_head;
   p.round_gate = a.round_gate;
   p.status = a.status;
-  const int q_tiles = (a.seq + kBM - 1) / kBM;
+  const int all_tiles = (a.seq + kBM - 1) / kBM;
+  // a caller may ask for the query tiles [tile_begin, tile_begin + tile_count) only (rows of a
+  // longer causal problem whose earlier rows were, or later rows will be, computed by other calls)
+  const int tile_begin = a.tile_count > 0 ? a.tile_begin : 0;
+  const int q_tiles = a.tile_count > 0 ? a.tile_count : all_tiles;
+  if (tile_begin < 0 || tile_begin + q_tiles > all_tiles) return cudaErrorInvalidValue;
+  p.tile_end = tile_begin + q_tiles;
+  const bool whole = q_tiles == all_tiles;
   const size_t tile = static_cast<size_t>(a.head_dim / 64) * kSlabBytes;
   cudaError_t e;
   if (a.head_dim != 128 && a.head_dim != 64) return cudaErrorInvalidValue;
@@ -879,6 +888,8 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
     if (cudaGetDevice(&device) == cudaSuccess)
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   }
+  // a partial range runs as pairs only when it starts on a pair and ends on one (or at the end)
+  const bool pairable = tile_begin % 2 == 0 && (q_tiles % 2 == 0 || p.tile_end == all_tiles);
   const long long pair_units = static_cast<long long>((q_tiles + 1) / 2) * a.heads * a.batch;
   // With a workspace, a shape that cannot even fill the SMs with single tiles (one or two heads of
   // a long prompt) is made finer by cutting every pair's key range into parts, combined by
@@ -886,7 +897,7 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
   // 3 heads 77 -> 95 us and 5 heads 103 -> 114 us (the per-CTA prologue/epilogue outweighs the
   // better balance), hence the threshold.
   int splits = 1;
-  if (a.workspace != nullptr && q_tiles >= 8 && static_cast<long long>(q_tiles) * a.heads * a.batch <= sms)
+  if (whole && a.workspace != nullptr && q_tiles >= 8 && static_cast<long long>(q_tiles) * a.heads * a.batch <= sms)
     splits = pair_units * 2 >= 2LL * sms ? 2 : 4;
   p.splits = splits;
   p.part_o = nullptr;
@@ -896,7 +907,7 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
     p.part_m = static_cast<float4*>(a.workspace);
     p.part_o = reinterpret_cast<float*>(p.part_m + 4 * tokens * a.heads);
   }
-  if (q_tiles >= 2 && (pair_units >= 2LL * sms || splits > 1)) {
+  if (q_tiles >= 2 && pairable && (pair_units >= 2LL * sms || splits > 1)) {
     // two query tiles per CTA in ping-pong
     const dim3 grid(a.heads * a.batch, ((q_tiles + 1) / 2) * splits);
     const size_t smem = 1024 + tile * (2 + 2 * kStages) + sizeof(PairBarriers);

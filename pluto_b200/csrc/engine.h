@@ -120,6 +120,7 @@ struct AttnFwdArgs {
   int round_gate;
   void* workspace;             // optional, attn_fwd_tc_workspace_bytes: enables the key/value split
   uint32_t* status;
+  int tile_begin, tile_count;  // query tiles (128 rows) to compute; tile_count 0 = all of them
 };
 cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& args);
 size_t attn_fwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim);

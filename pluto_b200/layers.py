@@ -305,8 +305,10 @@ def gqa_prefill_host(q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.T
                      workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """gqa_prefill for activations in pinned host memory (bf16, dense [B,T,Hq,D] / [B,T,Hkv,D]):
     the copies in both directions and the kernels of successive key/value-head groups overlap
-    (pluto_gqa_prefill_fwd_host).  Writes out_host; the caller synchronises the current stream
-    before reading it.  Pass `workspace` (uint8 device tensor) to reuse one across calls."""
+    (pluto_gqa_prefill_fwd_host).  kv_heads_per_group = 0 cuts the prompt by query tokens instead
+    (contiguous copies, the whole Q / K / V / output on the device).  Writes out_host; the caller
+    synchronises the current stream before reading it.  Pass `workspace` (uint8 device tensor) to
+    reuse one across calls."""
     B, T, Hq, D = q_host.shape
     Hkv = k_host.shape[2]
     for t in (q_host, k_host, v_host, out_host):

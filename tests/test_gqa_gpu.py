@@ -247,6 +247,33 @@ def test_host_memory_prefill_matches_device_prefill():
         assert torch.equal(out.view(torch.int16), want.view(torch.int16)), (t, hq, hkv, d)
 
 
+def test_host_memory_prefill_by_token_chunks_matches_device_prefill():
+    """kv_heads_per_group = 0: the prompt is cut by query tokens (contiguous copies; every chunk's
+    queries run against the keys copied so far).  Several chunks with a ragged last one, two
+    sequences, both head widths; the chunks may take the other tcgen05 kernel than the whole
+    prompt does, hence a bf16-level tolerance instead of bit equality, and bit equality between
+    two runs."""
+    import torch
+    from pluto_b200 import _capi
+    from pluto_b200.layers import gqa_prefill, gqa_prefill_host
+    gen = torch.Generator().manual_seed(9)
+    for (b, t, hq, hkv, d) in [(2, 2500, 10, 2, 128), (1, 1024, 4, 4, 64), (1, 3333, 6, 3, 64), (1, 77, 2, 1, 128)]:
+        q = (torch.randn(b, t, hq, d, generator=gen) * 0.5).bfloat16().pin_memory()
+        k = (torch.randn(b, t, hkv, d, generator=gen) * 0.5).bfloat16().pin_memory()
+        v = (torch.randn(b, t, hkv, d, generator=gen) * 0.5).bfloat16().pin_memory()
+        out = torch.zeros(b, t, hq, d, dtype=torch.bfloat16).pin_memory()
+        workspace = gqa_prefill_host(q, k, v, out, kv_heads_per_group=0)
+        torch.cuda.synchronize()
+        first = out.clone()
+        out.zero_()
+        gqa_prefill_host(q, k, v, out, kv_heads_per_group=0, workspace=workspace)
+        torch.cuda.synchronize()
+        want = gqa_prefill(q.cuda(), k.cuda(), v.cuda())["out"].cpu()
+        assert torch.equal(out.view(torch.int16), first.view(torch.int16)), (b, t, hq, hkv, d)
+        assert (out.float() - want.float()).abs().max().item() <= 2.0 ** -6, (b, t, hq, hkv, d)
+    assert _capi.kernel_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(2048, 4, 2, 128), (3000, 5, 1, 128), (2304, 6, 6, 64), (9000, 2, 1, 128)])
 def test_key_value_split_prefill_matches_oracle_and_unsplit_kernel(shape):
     """Few (sequence, head) units for a long prompt: with a workspace every query-tile pair is cut
