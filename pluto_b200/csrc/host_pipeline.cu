@@ -78,8 +78,11 @@ int prefill_by_token_chunks(Lanes* l, cudaStream_t compute, const void* q_host, 
   cudaError_t e = cudaSuccess;
   int n = 0;   // chunks issued so far
   for (int b = 0; b < batch; ++b) {
-    for (int t0 = 0; t0 < seq; t0 += kChunkTokens, ++n) {
-      const int count = std::min(kChunkTokens, seq - t0);
+    for (int t0 = 0, count = 0; t0 < seq; t0 += count, ++n) {
+      // The last chunk's kernel and output copy have nothing to hide behind, so the chunks get
+      // smaller towards the end of a sequence (all sizes are multiples of 256: whole tile pairs).
+      const int left = seq - t0;
+      count = std::min(left, left > 2 * kChunkTokens ? kChunkTokens : (left > kChunkTokens ? kChunkTokens / 2 : kChunkTokens / 4));
       const size_t first = static_cast<size_t>(b) * seq + t0;
       const int slot = n % kMaxChunkEvents;
       // the events of chunk n - kMaxChunkEvents are reused: its kernel must have taken them
