@@ -134,7 +134,7 @@ size_t pluto_gqa_prefill_fwd_workspace_bytes(int batch, int seq, int q_heads, in
  * groups of kv_heads_per_group (with their query heads); each group's host->device copy, kernel
  * and device->host copy run on separate streams, two groups in flight, so the PCIe transfers of
  * both directions overlap each other and the kernels.  kv_heads_per_group = 0 (head width 64 or
- * 128) cuts the prompt by query tokens instead: chunks of up to 1024 tokens are copied as contiguous
+ * 128) cuts the prompt by query tokens instead: chunks of 1024 tokens or more (at least 4 MB of input) are copied as contiguous
  * pieces (queries, keys and values alike), a chunk's queries run against all keys copied so far
  * (causal attention needs no later ones), and its output rows leave as one contiguous piece; the
  * workspace then holds the whole Q, K, V and output.  No gate, statistics or core output.

@@ -26,7 +26,8 @@ namespace {
 
 constexpr int kSlots = 2;
 constexpr int kMaxDevices = 64;
-constexpr int kChunkTokens = 1024;  // token-chunk mode: 8 query tiles per launch (a multiple of 256: whole pairs)
+constexpr int kChunkTokens = 1024;  // token-chunk mode: smallest full-size chunk (8 query tiles; whole pairs)
+constexpr size_t kChunkBytes = 4u << 20;   // ... grown until a chunk's input is at least this much
 constexpr int kMaxChunkEvents = 64; // chunks in flight before the events are reused
 
 struct Lanes {
@@ -75,6 +76,11 @@ int prefill_by_token_chunks(Lanes* l, cudaStream_t compute, const void* q_host, 
   uint8_t* v_dev = k_dev + round256(tokens * kv_row);
   uint32_t* status = pluto::kernel_status_word();
   if (!status) return pluto::report(PLUTO_E_INTERNAL, "kernel status word unavailable");
+  // With few heads per rank a 1024-token chunk is a fraction of a megabyte and the per-copy cost
+  // would dominate: the full-size chunk grows (in steps of 1024 tokens) to at least kChunkBytes.
+  const size_t token_bytes = q_row + 2 * kv_row;
+  const int full = static_cast<int>(std::max<size_t>(1, (kChunkBytes / token_bytes + kChunkTokens - 1) / kChunkTokens)) *
+                   kChunkTokens;
   cudaError_t e = cudaSuccess;
   int n = 0;   // chunks issued so far
   for (int b = 0; b < batch; ++b) {
@@ -82,7 +88,7 @@ int prefill_by_token_chunks(Lanes* l, cudaStream_t compute, const void* q_host, 
       // The last chunk's kernel and output copy have nothing to hide behind, so the chunks get
       // smaller towards the end of a sequence (all sizes are multiples of 256: whole tile pairs).
       const int left = seq - t0;
-      count = std::min(left, left > 2 * kChunkTokens ? kChunkTokens : (left > kChunkTokens ? kChunkTokens / 2 : kChunkTokens / 4));
+      count = std::min(left, left > 2 * full ? full : (left > full ? full / 2 : full / 4));
       const size_t first = static_cast<size_t>(b) * seq + t0;
       const int slot = n % kMaxChunkEvents;
       // the events of chunk n - kMaxChunkEvents are reused: its kernel must have taken them
