@@ -11,6 +11,9 @@
  *   - work is queued on `stream` (the caller's Executor::stream()); nothing synchronises, nothing
  *     touches the default stream, nothing allocates or frees -- scratch comes in through
  *     explicit workspace arguments whose size the *_workspace_bytes functions report;
+ *   - the device that owns `stream` must be the calling thread's current device: per-device state
+ *     (the kernel status word, the built-in decode scratch, the host-prefill copy streams) is
+ *     looked up by the current device;
  *   - all validation happens before any GPU work is queued;
  *   - return value: 0 = queued; > 0 = a cudaError_t from the launch; < 0 = one of PLUTO_E_*.
  *     PLUTO_E_INVALID maps to absl::InvalidArgumentError, PLUTO_E_UNIMPLEMENTED to
@@ -53,6 +56,16 @@ const char* pluto_build_info(void);
 /* Diagnostic: reads (and optionally clears) the device status word that kernels set when one of
  * their bounded waits ran out.  SYNCHRONISES the device.  *value == 0 means healthy. */
 int pluto_kernel_status(uint32_t* value /* host */, int clear);
+
+/* Diagnostic with no counterpart in the reference: proves on the running GPU that a bounded wait
+ * gives up instead of hanging.  Queues a one-thread kernel that waits on a barrier nobody arrives
+ * at; after limit_ns (at most 100 ms) the wait gives up, the kernel stores 1 to *gave_up (device
+ * uint32) and returns, and the status word reads (PLUTO_SELFTEST_WAIT_SITE << 8) | 1 until it is
+ * cleared.  Clear it (pluto_kernel_status with clear = 1) before queuing other work: while the
+ * word is non-zero every other bounded wait that has to spin gives up early too. */
+#define PLUTO_SELFTEST_WAIT_SITE 63u
+int pluto_selftest_bounded_wait(pluto_stream_t stream, unsigned long long limit_ns,
+                                uint32_t* gave_up);
 
 /* --------------------------------------------------------------------------------------------
  * Causal multi-head attention over a packed activation (GPT-2 recipe).
@@ -270,15 +283,20 @@ int pluto_gqa_decode(pluto_stream_t stream, const void* q, int q_dtype, const vo
  * cudaMalloc (and the stream-ordered allocators) to loaded libraries, decode loops that must not
  * contend for an allocator lock.  It has no counterpart in the reference, whose CachedAttentionStep
  * allocates its scratch with a stream-ordered Buffer on every token.  The split-KV partials live
- * in a 24 MiB area inside the library image (pluto_gqa_decode_builtin_scratch_bytes(); every GPU
- * that loads the library holds it until the process exits).  Arguments, results and kernels are
- * those of pluto_gqa_decode minus the workspace pair.
+ * in a 24 MiB area inside the library image (pluto_gqa_decode_builtin_scratch_bytes()).  Arguments,
+ * results and kernels are those of pluto_gqa_decode minus the workspace pair.
  *   - A call whose pluto_gqa_decode_workspace_bytes(...) exceeds the area returns
  *     PLUTO_E_EXHAUSTED with the two sizes in pluto_last_error(); nothing is launched.
- *   - No cudaMalloc/cudaFree or allocating library routine is called, now or later.
- *   - The first call on each device looks up the area's device address
- *     (cudaGetSymbolAddress, with that device current); make that first call before starting any
- *     stream capture on the device.
+ *   - The entry point itself calls no cudaMalloc/cudaFree or allocating library routine.  The
+ *     area is a static device array: the CUDA runtime gives it memory when it loads this
+ *     library's device code on a GPU, which with lazy module loading (the default) happens at the
+ *     first call on that GPU, not when the process loads the .so; the GPU then holds the 24 MiB
+ *     until the process exits.  So make ONE warm-up call per device at start-up -- before the HBM
+ *     plan is committed and before any stream capture: that call loads the device code, looks up
+ *     the area's device address (cudaGetSymbolAddress, with that device current) and the status
+ *     word's, and sets the kernels' shared-memory attribute.  Later calls touch no allocator.
+ *   - `stream` must belong to the current device (PLUTO_E_INVALID otherwise): the area and the
+ *     status word are per device and are looked up by the current device.
  *   - All calls share the one area.  Nothing in it has to start at zero (each call overwrites
  *     every partial it later reads), but two calls whose kernels overlap on the GPU -- different
  *     streams, or different host threads -- race on it: order them on one stream. */
@@ -478,6 +496,22 @@ int pluto_dequantize_matrix(pluto_stream_t stream, const void* input, int storag
  * out = [rows][ranks * local_bytes].  Only local memory is touched. */
 int pluto_interleave_heads(pluto_stream_t stream, const void* gathered, void* out, int ranks,
                            long long rows, size_t local_bytes);
+
+/* The whole gather in one call, for a caller that owns an NCCL communicator over the head-sharded
+ * ranks (same single-GPU reference as above, src/cuda/thread_pool.h:19-22: nothing to mirror; the
+ * output is the [rows, E] layout of src/llm/layers/attention.h:64-70): ncclAllGather of `local`
+ * ([rows][local_bytes], this rank's heads) into `gathered` ([ranks][rows][local_bytes], scratch
+ * owned by the caller) on `stream`, then pluto_interleave_heads into out
+ * ([rows][ranks * local_bytes]).  nccl_comm is the caller's ncclComm_t, passed as an opaque
+ * pointer so this header needs no nccl.h; `ranks` must be its size.  The library does not link
+ * NCCL: it binds ncclAllGather and ncclGetErrorString at first use to the NCCL already loaded in
+ * the process (the communicator's own library), falling back to loading libnccl.so.2, and returns
+ * PLUTO_E_UNIMPLEMENTED when neither is there.  NCCL moves the data over NVLink / NVSwitch into
+ * this GPU's own memory; no kernel of this library reads peer memory.  Returns > 0 with the
+ * ncclResult_t offset by 10000 when NCCL reports an error. */
+int pluto_allgather_heads(pluto_stream_t stream, void* nccl_comm, const void* local,
+                          void* gathered, void* out, int ranks, long long rows,
+                          size_t local_bytes);
 
 #ifdef __cplusplus
 } /* extern "C" */

@@ -178,6 +178,18 @@ def gqa_decode_batch(q, keys, values, lengths, rnd=True, threads=1):
     return out
 
 
+def gqa_prefill_rows(q, k, v, rows, rnd=True, threads=1):
+    """Rows `rows` (a list of token indices) of the ungated sequence forward: q [T,Hq,D], k,v
+    [T,Hkv,D] -> [len(rows),Hq,D].  Row r of the sequence layer is the cached step at position r
+    over keys [0, r] (the reference pins the two paths to each other,
+    qwen_attention_test.cc:155-228), so each sampled row costs only its own prefix instead of
+    the whole triangle."""
+    rows = np.asarray(rows, dtype=np.int64)
+    k, v = np.ascontiguousarray(k), np.ascontiguousarray(v)
+    return gqa_decode_batch(np.ascontiguousarray(q[rows]), [k] * len(rows), [v] * len(rows),
+                            (rows + 1).astype(np.int32), rnd=rnd, threads=threads)
+
+
 def gqa_probabilities(queries, keys, length):
     hq, d = queries.shape
     hkv = keys.shape[1]

@@ -73,6 +73,8 @@ _SIGNATURES = {
     "pluto_gdn_prefill_workspace_bytes": (_sz, [_i] * 7),
     "pluto_gdn_step": (_i, [_vp] * 4 + [_i] + [_vp] * 4 + [_i] * 7 + [_fp, _i]),
     "pluto_interleave_heads": (_i, [_vp, _vp, _vp, _i, C.c_longlong, _sz]),
+    "pluto_allgather_heads": (_i, [_vp, _vp, _vp, _vp, _vp, _i, C.c_longlong, _sz]),
+    "pluto_selftest_bounded_wait": (_i, [_vp, C.c_ulonglong, _vp]),
     "pluto_gdn_out_norm_gate": (_i, [_vp, _vp, _i, _vp, _i, _vp, C.c_longlong, _i, _fp, _i, _i,
                                      _vp, _i]),
 }

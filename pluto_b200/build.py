@@ -53,7 +53,7 @@ def build(verbose: bool = False) -> str:
                 print(log)
     if (not os.path.exists(LIB)) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
         proc = subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-gencode",
-                               "arch=compute_100a,code=sm_100a", "-lcudart"],
+                               "arch=compute_100a,code=sm_100a", "-lcudart", "-ldl"],
                               capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")

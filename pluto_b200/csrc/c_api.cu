@@ -452,8 +452,10 @@ int pluto_gqa_decode(pluto_stream_t stream, const void* q, int q_dtype, const vo
   a.gate_token = gate_token_stride; a.gate_head = gate_head_stride;
   a.out = out; a.out_is_bf16 = out_dtype == PLUTO_BF16; a.lse = lse;
   a.round = round_to_bf16;
-  a.partial_acc = static_cast<float*>(workspace);
-  a.partial_ml = a.partial_acc + static_cast<size_t>(batch) * q_heads * a.splits * head_dim;
+  // (max, sum) pairs first: the merge reads them as 8-byte pairs, and the workspace start is the
+  // only address here whose alignment does not depend on head_dim (odd widths are legal).
+  a.partial_ml = static_cast<float*>(workspace);
+  a.partial_acc = a.partial_ml + pluto::decode_ml_floats(batch, q_heads, a.splits);
   return from_cuda(pluto::gqa_decode(stream, a), "Qwen full attention");
 }
 
@@ -847,6 +849,9 @@ extern "C" int pluto_gqa_decode_noalloc(pluto_stream_t stream, const void* q, in
              needed, kBuiltInScratchBytes);
     return PLUTO_E_EXHAUSTED;
   }
+  if (!pluto::stream_on_current_device(stream))
+    return fail(PLUTO_E_INVALID, "the stream belongs to another device than the current one; the "
+                                 "built-in scratch area is per device");
   void* scratch = nullptr;
   if (int c = from_cuda(builtin_scratch(&scratch), "built-in decode scratch address")) return c;
   // Same validation and launches as pluto_gqa_decode (dimension errors surface from there);

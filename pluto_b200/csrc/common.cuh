@@ -15,7 +15,16 @@ namespace pluto {
 // Status word written by kernels (device global, one per launch family; see status.cu).
 // 0 = ok; otherwise (site << 8) | kind.
 // ----------------------------------------------------------------------------------------------
-enum : uint32_t { kWaitTimeout = 1u };
+enum : uint32_t {
+  kWaitTimeout = 1u,   // a bounded wait ran out
+  kBadLength = 2u,     // a device-side sequence length lay outside the host-declared bound
+  kBadPage = 3u        // a block-table entry lay outside the page pool
+};
+
+// Records (site << 8) | kind if the word is still healthy; the first report wins.
+__device__ __forceinline__ void report_status(uint32_t* status, uint32_t site, uint32_t kind) {
+  if (status != nullptr) atomicCAS(status, 0u, (site << 8) | kind);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -64,14 +73,14 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 // is still 0) and returns false; the caller must then leave its loop and fall through to the
 // kernel's common exit path.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status,
-                                          uint32_t site) {
+                                          uint32_t site, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_test(bar, parity)) return true;
   const uint64_t start = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_test(bar, parity)) {
     if ((++spins & 0x3ffu) == 0) {
       if (*reinterpret_cast<volatile uint32_t*>(status) != 0) return false;  // someone else gave up
-      if (global_timer_ns() - start > kWaitLimitNs) {
+      if (global_timer_ns() - start > limit_ns) {
         atomicCAS(status, 0u, (site << 8) | kWaitTimeout);
         return false;
       }

@@ -14,6 +14,9 @@ namespace pluto {
 // Device word that kernels set when one of their bounded waits runs out (0 = healthy).
 uint32_t* kernel_status_word();           // device address, per current device
 cudaError_t read_kernel_status(uint32_t* host_value, bool clear);  // synchronising diagnostic
+// Per-device state (status word, built-in scratch, copy lanes) is looked up by the CURRENT device;
+// entry points that depend on it beyond the status word refuse a stream that belongs to another.
+bool stream_on_current_device(cudaStream_t stream);
 
 // ---- attn_generic.cu: exact fp32-math attention for every shape --------------------------------
 cudaError_t attn_generic_fwd(cudaStream_t stream, const void* q, const void* k, const void* v,
@@ -150,8 +153,8 @@ struct DecodeArgs {
   void* out;                // [batch, q_heads, head_dim]
   int out_is_bf16;
   float* lse;               // optional [batch, q_heads]
-  float* partial_acc;       // workspace [batch, q_heads, splits, head_dim]
-  float* partial_ml;        // workspace [batch, q_heads, splits, 2]
+  float* partial_ml;        // workspace [batch, q_heads, splits, 2], 8-byte aligned (first section)
+  float* partial_acc;       // workspace [batch, q_heads, splits, head_dim] (second section)
   int batch, q_heads, kv_heads, head_dim;
   int splits, split_tokens;
   float scale;
@@ -159,6 +162,12 @@ struct DecodeArgs {
   uint32_t* status;
 };
 bool gqa_decode_uses_tensor_cores(const DecodeArgs& args);
+// Floats of the (max, sum) section at the start of the decode workspace; the accumulators
+// [batch, q_heads, splits, head_dim] follow it.  Always an even count, so a workspace aligned to
+// 8 bytes or more keeps the pairs 8-byte aligned whatever head_dim is.
+inline size_t decode_ml_floats(int batch, int q_heads, int splits) {
+  return static_cast<size_t>(batch) * q_heads * splits * 2;
+}
 cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args);
 cudaError_t gqa_decode_probabilities(cudaStream_t stream, const DecodeArgs& args, float* probs,
                                      size_t batch_stride, size_t head_stride);

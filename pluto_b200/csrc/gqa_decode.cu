@@ -31,10 +31,27 @@ constexpr int kDecodeStages = 3;
 constexpr int kConsumerWarps = 4;  // 16 tokens of every tile each
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
 
+// Sequence length as the kernels use it: the device value clamped into what the host sized the
+// grid and the workspace for, [0, splits * split_tokens].  A value outside is a caller error; it
+// is reported through the status word and the launch stays inside its buffers.
+__device__ __forceinline__ int bounded_length(const DecodeArgs& a, int b, uint32_t site) {
+  const int length = a.seq_lens[b];
+  const long long limit = static_cast<long long>(a.splits) * a.split_tokens;
+  if (length < 0 || length > limit) {
+    report_status(a.status, site, kBadLength);
+    return length < 0 ? 0 : static_cast<int>(limit);
+  }
+  return length;
+}
+
 __device__ __forceinline__ const char* kv_row(const DecodeArgs& a, const void* base, int b, int t,
                                               int kv_head, size_t element) {
-  const int page = a.block_table ? a.block_table[static_cast<size_t>(b) * a.max_blocks + t / a.page_size]
-                                 : b;
+  int page = a.block_table ? a.block_table[static_cast<size_t>(b) * a.max_blocks + t / a.page_size]
+                           : b;
+  if (a.block_table && a.num_pages > 0 && (page < 0 || page >= a.num_pages)) {
+    report_status(a.status, 35, kBadPage);   // the tiled-TMA path reads zeros there instead
+    page = 0;
+  }
   const size_t offset = static_cast<size_t>(page) * a.page_stride +
                         static_cast<size_t>(t % a.page_size) * a.token_stride +
                         static_cast<size_t>(kv_head) * a.head_dim;
@@ -80,7 +97,7 @@ gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   DecodeBarriers* bar = reinterpret_cast<DecodeBarriers*>(smem + kDecodeStages * kStageBytes);
 
   const int split = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
-  const int length = a.seq_lens[b];
+  const int length = bounded_length(a, b, 36);
   const int begin = split * a.split_tokens;
   if (begin >= length) return;  // whole CTA leaves before touching any barrier
   const int end = min(length, begin + a.split_tokens);
@@ -307,7 +324,7 @@ gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) gqa_decode_generic(DecodeArgs a) {
   const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
-  const int length = a.seq_lens[b];
+  const int length = bounded_length(a, b, 37);
   const int begin = split * a.split_tokens;
   if (begin >= length) return;
   const int end = min(length, begin + a.split_tokens);
@@ -388,8 +405,18 @@ constexpr int kMergeSplits = 1024;   // chunk weights held in shared memory per 
 
 __global__ void __launch_bounds__(kMergeThreads) gqa_decode_merge(DecodeArgs a) {
   const int head = blockIdx.x, b = blockIdx.y, D = a.head_dim;
-  const int length = a.seq_lens[b];
-  const int splits = (length + a.split_tokens - 1) / a.split_tokens;
+  const int length = bounded_length(a, b, 38);
+  const int splits = (length + a.split_tokens - 1) / a.split_tokens;   // <= a.splits
+  if (length <= 0) {
+    // nothing to attend to (a caller error: lengths are >= 1): zeros, not 0/0
+    for (int d = threadIdx.x; d < D; d += kMergeThreads) {
+      const size_t idx = (static_cast<size_t>(b) * a.q_heads + head) * D + d;
+      if (a.out_is_bf16) static_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(0.0f);
+      else static_cast<float*>(a.out)[idx] = 0.0f;
+    }
+    if (threadIdx.x == 0 && a.lse) a.lse[static_cast<size_t>(b) * a.q_heads + head] = -INFINITY;
+    return;
+  }
   const size_t slot0 = (static_cast<size_t>(b) * a.q_heads + head) * a.splits;
   __shared__ float weight[kMergeSplits];   // 2^(m_s - m_tot)
   __shared__ float scaled_l[kMergeSplits]; // l_s * weight_s

@@ -166,6 +166,9 @@ int pluto_gqa_prefill_fwd_host(pluto_stream_t stream, const void* q_host, const 
     return pluto::report(PLUTO_E_INVALID, "attention requires non-null host pointers");
   if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return pluto::report(PLUTO_E_INVALID, "host prefill workspace is missing, misaligned or too small");
+  if (!pluto::stream_on_current_device(static_cast<cudaStream_t>(stream)))
+    return pluto::report(PLUTO_E_INVALID, "the stream belongs to another device than the current one; "
+                                          "the copy streams are per device");
   Lanes* l = lanes_for_current_device();
   if (l == nullptr) return pluto::report(PLUTO_E_INTERNAL, "copy streams could not be created");
   if (kv_heads_per_group == 0) {

@@ -634,7 +634,8 @@ def gqa_decode_noalloc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
                        seq_lens: torch.Tensor, max_seq_len: int, out: torch.Tensor, *,
                        block_table: Optional[torch.Tensor] = None,
                        gate: Optional[torch.Tensor] = None,
-                       round_to_bfloat16: bool = True) -> torch.Tensor:
+                       round_to_bfloat16: bool = True,
+                       lse: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`gqa_decode` for callers that may not allocate device memory (a fixed, fully committed
     memory plan; a sandbox that forbids cudaMalloc to plugins; a decode loop that must stay off
     the allocator lock).  Nothing is allocated here or in the library: `out` comes from the
@@ -649,7 +650,7 @@ def gqa_decode_noalloc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
         gts, ghs = gate.stride(0), gate.stride(1)
     check(_capi.lib().pluto_gqa_decode_noalloc(
         _stream(), _ptr(q), _dt(q), _ptr(gate), _dt(gate) if gate is not None else 0, gts, ghs,
-        C_byref(layout), _ptr(seq_lens), max_seq_len, _ptr(out), _dt(out), None, B, Hq, Hkv, D,
+        C_byref(layout), _ptr(seq_lens), max_seq_len, _ptr(out), _dt(out), _ptr(lse), B, Hq, Hkv, D,
         int(round_to_bfloat16)))
     return out
 

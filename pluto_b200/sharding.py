@@ -9,6 +9,8 @@ followed by a local interleave kernel.  The reference has no multi-GPU path to m
 """
 from __future__ import annotations
 
+import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -54,17 +56,73 @@ def shard_heads(q_heads: int, kv_heads: int, world: int, rank: int) -> HeadShard
                      (rank + 1) * per * group)
 
 
-def allgather_heads(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+class NcclCommunicator:
+    """An ncclComm_t over the ranks of a torch.distributed group, for the C entry point
+    pluto_allgather_heads (a C++ host owns such a communicator anyway; this is the Python
+    stand-in).  It is created with ctypes on the NCCL library torch itself loads, made globally
+    visible so that the engine binds the same copy; the unique id travels through the group's
+    own broadcast.  The calling thread's current CUDA device is the rank's GPU."""
+
+    class _UniqueId(C.Structure):
+        _fields_ = [("internal", C.c_byte * 128)]
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None):
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._nccl = C.CDLL(self._library_path(), mode=C.RTLD_GLOBAL)
+        self._nccl.ncclGetErrorString.restype = C.c_char_p
+        uid = self._UniqueId()
+        if self.rank == 0:
+            self._check(self._nccl.ncclGetUniqueId(C.byref(uid)))
+        box = [bytes(uid.internal)]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group else 0, group=group)
+        C.memmove(C.byref(uid), box[0], 128)
+        self.handle = C.c_void_p()
+        self._nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, self._UniqueId, C.c_int]
+        self._check(self._nccl.ncclCommInitRank(C.byref(self.handle), self.world, uid, self.rank))
+
+    @staticmethod
+    def _library_path() -> str:
+        bundled = os.path.join(os.path.dirname(os.path.dirname(torch.__file__)), "nvidia", "nccl", "lib",
+                               "libnccl.so.2")
+        return bundled if os.path.exists(bundled) else "libnccl.so.2"
+
+    def _check(self, code: int) -> None:
+        if code != 0:
+            raise PlutoStatusError("Internal", "NCCL: " + self._nccl.ncclGetErrorString(code).decode(), code)
+
+    def close(self) -> None:
+        if self.handle:
+            self._nccl.ncclCommDestroy.argtypes = [C.c_void_p]
+            self._nccl.ncclCommDestroy(self.handle)
+            self.handle = C.c_void_p()
+
+
+def allgather_heads(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                    comm: Optional[NcclCommunicator] = None, out: Optional[torch.Tensor] = None,
+                    scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """local [rows, E/G] (this rank's heads, same shape on every rank) -> [rows, E] on every rank,
-    columns ordered by rank.  One all-gather plus a local interleave."""
-    world = dist.get_world_size(group)
+    columns ordered by rank.  One all-gather plus a local interleave.  With `comm` both happen
+    inside the C entry point pluto_allgather_heads (NCCL on the current stream); without it the
+    gather goes through torch.distributed.  `out` / `scratch` ([world*rows, cols]) let a caller
+    reuse buffers."""
+    world = comm.world if comm is not None else dist.get_world_size(group)
     if world == 1:
         return local
     local = local.contiguous()
     rows, cols = local.shape
-    gathered = torch.empty((world * rows, cols), dtype=local.dtype, device=local.device)
+    gathered = scratch if scratch is not None else torch.empty((world * rows, cols), dtype=local.dtype,
+                                                              device=local.device)
+    if comm is not None:
+        if out is None:
+            out = torch.empty((rows, world * cols), dtype=local.dtype, device=local.device)
+        check(_capi.lib().pluto_allgather_heads(torch.cuda.current_stream().cuda_stream, comm.handle,
+                                                local.data_ptr(), gathered.data_ptr(), out.data_ptr(),
+                                                world, rows, cols * local.element_size()))
+        return out
     dist.all_gather_into_tensor(gathered, local, group=group)  # rank-major [world][rows][cols]
-    out = torch.empty((rows, world * cols), dtype=local.dtype, device=local.device)
+    if out is None:
+        out = torch.empty((rows, world * cols), dtype=local.dtype, device=local.device)
     if local.is_cuda:
         check(_capi.lib().pluto_interleave_heads(torch.cuda.current_stream().cuda_stream,
                                                  gathered.data_ptr(), out.data_ptr(), world, rows,

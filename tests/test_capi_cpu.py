@@ -35,7 +35,7 @@ def test_header_cites_the_reference_for_every_entry_point():
         if name in ("pluto_last_error", "pluto_build_info", "pluto_kernel_status",
                     "pluto_gqa_decode_workspace_bytes", "pluto_gdn_prefill_workspace_bytes",
                     "pluto_attn_bwd_workspace_bytes",
-                    "pluto_gqa_decode_noalloc",
+                    "pluto_gqa_decode_noalloc", "pluto_selftest_bounded_wait",
                     "pluto_gqa_decode_builtin_scratch_bytes"):
             continue
         start = text.index(name + "(")

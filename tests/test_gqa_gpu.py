@@ -102,7 +102,8 @@ def test_zero_queries_give_uniform_probabilities():
 
 
 @pytest.mark.parametrize("shape", [(3, 40, 8, 128, 704), (2, 8, 8, 64, 304), (4, 40, 8, 128, 5008),
-                                   (3, 40, 8, 128, 700), (2, 24, 4, 256, 200), (1, 6, 3, 20, 90)])
+                                   (3, 40, 8, 128, 700), (2, 24, 4, 256, 200), (1, 6, 3, 20, 90),
+                                   (3, 1, 1, 5, 41), (2, 3, 3, 7, 300)])
 def test_batched_decode_ragged_contiguous_and_paged(shape):
     """Ragged lengths (including 1 and the maximum), bf16 cache; a shuffled 16-token page pool
     must give the same bytes as the contiguous layout."""

@@ -45,6 +45,48 @@ def test_noalloc_decode_matches_workspace_decode_twice_in_a_row():
     assert _capi.kernel_status() == 0
 
 
+def test_noalloc_decode_other_paths_and_shorter_lengths_after_longer_ones():
+    """The shared area keeps the previous call's partials.  Same shape twice, the second time with
+    much shorter sequences (so most slots of the area still hold the first call's numbers and must
+    not be read), with a gate and the log-sum-exp output; then the exact fp32 kernel (fp32 cache,
+    head width 6) and a paged bf16 cache.  Each against the caller-workspace entry point, bit
+    for bit."""
+    q, k, v, lens = make_case(4, 4, 40, 8, 128, 6000)
+    gate = torch.randn_like(q)
+    for lengths in (lens, torch.clamp(lens // 7, min=1)):
+        want, want_lse = gqa_decode(q, k, v, lengths, 6000, gate=gate, want_lse=True)
+        got = torch.full_like(q, float("nan"))
+        lse = torch.full((4, 40), float("nan"), device="cuda")
+        gqa_decode_noalloc(q, k, v, lengths, 6000, got, gate=gate, lse=lse)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want) and torch.equal(lse, want_lse)
+    # exact fp32 kernel: fp32 cache, a head width no tensor-core path takes
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    k32 = torch.randn(3, 90, 2, 6, device="cuda", generator=gen)
+    v32 = torch.randn(3, 90, 2, 6, device="cuda", generator=gen)
+    q32 = torch.randn(3, 4, 6, device="cuda", generator=gen)
+    l32 = torch.tensor([90, 1, 37], dtype=torch.int32, device="cuda")
+    want = gqa_decode(q32, k32, v32, l32, 90, round_to_bfloat16=False)
+    got = torch.full_like(q32, float("nan"))
+    gqa_decode_noalloc(q32, k32, v32, l32, 90, got, round_to_bfloat16=False)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    # paged bf16 cache: 16-token pages in shuffled order
+    q, k, v, lens = make_case(6, 2, 10, 2, 128, 640)
+    pages = 2 * 40
+    table = torch.randperm(pages, device="cuda", dtype=torch.int32).view(2, 40)
+    pool_k = torch.zeros(pages, 16, 2, 128, dtype=torch.bfloat16, device="cuda")
+    pool_v = torch.zeros_like(pool_k)
+    pool_k[table.reshape(-1).long()] = k.view(pages, 16, 2, 128)
+    pool_v[table.reshape(-1).long()] = v.view(pages, 16, 2, 128)
+    want = gqa_decode(q, pool_k, pool_v, lens, 640, block_table=table)
+    got = torch.full_like(q, float("nan"))
+    gqa_decode_noalloc(q, pool_k, pool_v, lens, 640, got, block_table=table)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and torch.equal(got, gqa_decode(q, k, v, lens, 640))
+    assert _capi.kernel_status() == 0
+
+
 def test_noalloc_decode_rejects_shapes_beyond_the_built_in_area():
     q, k, v, lens = make_case(3, 2, 40, 8, 128, 64)
     out = torch.zeros_like(q)
