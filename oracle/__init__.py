@@ -2,7 +2,9 @@
 
 `libpluto_oracle.so` is this repository's C restatement of the reference arithmetic
 (pluto_oracle.c); `_ref/libpluto_ref.so` is the reference project's own
-AttentionLayerReference compiled from its sources (ref_shim.cc, Makefile).  Only tests, the
+AttentionLayerReference compiled from its sources (ref_shim.cc, Makefile), and
+`_ref/libpluto_ref_specs.so` holds the scalar specifications the reference keeps in its GPU layer
+tests (ref_specs_shim.cc; the `spec_*` functions below).  Only tests, the
 smoke check and the benchmark's CPU-baseline leg import this package; the engine in
 `pluto_b200` never does.
 """
@@ -17,6 +19,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ORACLE_SO = os.path.join(_HERE, "libpluto_oracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libpluto_ref.so")
+_SPECS_SO = os.path.join(_HERE, "_ref", "libpluto_ref_specs.so")
 
 
 def build(quiet: bool = True) -> None:
@@ -55,6 +58,122 @@ def ref() -> C.CDLL:
 
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+# ------------------------------------------------------------- the reference's own specifications
+_specs = None
+
+
+def have_ref_specs() -> bool:
+    return os.path.exists(_SPECS_SO)
+
+
+def ref_specs() -> C.CDLL:
+    global _specs
+    if _specs is None:
+        _specs = C.CDLL(_SPECS_SO)
+    return _specs
+
+
+def _f32(x):
+    return np.ascontiguousarray(x, dtype=np.float32)
+
+
+def _f64(x):
+    return np.ascontiguousarray(x, dtype=np.float64)
+
+
+def spec_attention_steps(query_heads, key_value_heads, head_dim, rotary_dim, capacity, epsilon, theta,
+                         rnd, q_gate, key, value, q_norm, k_norm):
+    """class AttentionReference (cached_attention_ops_test.cc:43-131) stepped over
+    q_gate [steps, Hq, 2, D], key/value [steps, Hkv, D].  Returns (out [steps, Hq, D], list of
+    per-step probability arrays [Hq, t+1])."""
+    steps = q_gate.shape[0]
+    out = np.empty((steps, query_heads, head_dim), np.float32)
+    probs = np.empty((query_heads * steps * (steps + 1) // 2,), np.float32)
+    ref_specs().ref_spec_attention_steps(
+        query_heads, key_value_heads, head_dim, rotary_dim, capacity, C.c_float(epsilon), C.c_float(theta),
+        int(rnd), steps, _p(_f32(q_gate)), _p(_f32(key)), _p(_f32(value)), _p(_f32(q_norm)),
+        _p(_f32(k_norm)), _p(out), _p(probs))
+    rows, offset = [], 0
+    for t in range(steps):
+        rows.append(probs[offset:offset + query_heads * (t + 1)].reshape(query_heads, t + 1))
+        offset += query_heads * (t + 1)
+    return out, rows
+
+
+def spec_delta_steps(key_heads, value_heads, key_dim, value_dim, kernel, epsilon, rnd, qkv, z, a, b,
+                     weights, a_log, dt_bias, norm):
+    """class DeltaReference (cached_attention_ops_test.cc:133-220) stepped from a fresh state over
+    qkv [steps, channels], z [steps, Hv*dv], a, b [steps, Hv].  Returns out [steps, Hv, dv]."""
+    steps = qkv.shape[0]
+    out = np.empty((steps, value_heads, value_dim), np.float32)
+    ref_specs().ref_spec_delta_steps(
+        key_heads, value_heads, key_dim, value_dim, kernel, C.c_float(epsilon), int(rnd), steps,
+        _p(_f32(qkv)), _p(_f32(z)), _p(_f32(a)), _p(_f32(b)), _p(_f32(weights)), _p(_f32(a_log)),
+        _p(_f32(dt_bias)), _p(_f32(norm)), _p(out))
+    return out
+
+
+def _example_sizes(length, kh, vh, kd, vd, kernel):
+    channels = 2 * kh * kd + vh * vd
+    return [length * channels, length * vh * vd, length * vh, length * vh, channels * kernel, vh, vh, vd]
+
+
+def _pointer_array(arrays):
+    return (C.c_void_p * len(arrays))(*[a.ctypes.data for a in arrays])
+
+
+def spec_sequence_delta_example(length, kh, vh, kd, vd, rnd):
+    """MakeExample of sequence_delta_net_test.cc:31-62 (kernel 3, epsilon 0.03): the eight tensors
+    QKV, Z, A, B, convolution, A_log, dt_bias, norm (float64, flat) and the upstream gradient."""
+    tensors = [np.empty((n,), np.float64) for n in _example_sizes(length, kh, vh, kd, vd, 3)]
+    upstream = np.empty((length * vh * vd,), np.float32)
+    ref_specs().ref_spec_sequence_delta_example(length, kh, vh, kd, vd, int(rnd), _pointer_array(tensors),
+                                                _p(upstream))
+    return tensors, upstream
+
+
+def spec_sequence_delta_forward(length, kh, vh, kd, vd, kernel, epsilon, rnd, tensors):
+    """Reference(...) of sequence_delta_net_test.cc:66-159: out [T, Hv, dv] float64."""
+    tensors = [_f64(t) for t in tensors]
+    out = np.empty((length, vh, vd), np.float64)
+    ref_specs().ref_spec_sequence_delta_forward(length, kh, vh, kd, vd, kernel, C.c_float(epsilon), int(rnd),
+                                                _pointer_array(tensors), _p(out))
+    return out
+
+
+def spec_sequence_delta_gradients(length, kh, vh, kd, vd, kernel, epsilon, rnd, tensors, upstream, step):
+    """Numerical BPTT of sequence_delta_net_test.cc:299-373 with the specification's own Loss:
+    central differences (frozen rounding offsets) in every coordinate of the eight tensors."""
+    tensors = [_f64(t) for t in tensors]
+    grads = [np.empty_like(t) for t in tensors]
+    ref_specs().ref_spec_sequence_delta_gradients(length, kh, vh, kd, vd, kernel, C.c_float(epsilon), int(rnd),
+                                                  _pointer_array(tensors), _p(_f32(upstream)),
+                                                  C.c_double(step), _pointer_array(grads))
+    return grads
+
+
+def spec_qwen_sequence_forward(query_heads, key_value_heads, head_dim, rotary_dim, epsilon, theta, rnd, length,
+                               qg, k, v, qw, kw):
+    """Reference(...) of qwen_attention_test.cc:26-95: out [T, Hq, D] float64."""
+    out = np.empty((length, query_heads, head_dim), np.float64)
+    ref_specs().ref_spec_qwen_sequence_forward(
+        query_heads, key_value_heads, head_dim, rotary_dim, C.c_float(epsilon), C.c_float(theta), int(rnd),
+        length, _p(_f64(qg)), _p(_f64(k)), _p(_f64(v)), _p(_f64(qw)), _p(_f64(kw)), _p(out))
+    return out
+
+
+def spec_qwen_sequence_gradients(query_heads, key_value_heads, head_dim, rotary_dim, epsilon, theta, rnd,
+                                 length, qg, k, v, qw, kw, upstream, step):
+    """Central differences of qwen_attention_test.cc:230-301 with the specification's own
+    Reference: gradients of sum(out * upstream) with respect to qg, k, v, qw, kw."""
+    inputs = [_f64(x) for x in (qg, k, v, qw, kw)]
+    grads = [np.empty_like(x) for x in inputs]
+    ref_specs().ref_spec_qwen_sequence_gradients(
+        query_heads, key_value_heads, head_dim, rotary_dim, C.c_float(epsilon), C.c_float(theta), int(rnd),
+        length, *[_p(x) for x in inputs], _p(_f64(upstream)), C.c_double(step), _pointer_array(grads))
+    return grads
 
 
 # ---------------------------------------------------------------------------- bf16 helpers

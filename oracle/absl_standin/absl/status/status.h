@@ -32,4 +32,9 @@ inline Status UnimplementedError(std::string_view m) { return Status(StatusCode:
 inline Status ResourceExhaustedError(std::string_view m) { return Status(StatusCode::kResourceExhausted, m); }
 inline Status InternalError(std::string_view m) { return Status(StatusCode::kInternal, m); }
 inline Status FailedPreconditionError(std::string_view m) { return Status(StatusCode::kFailedPrecondition, m); }
+inline bool IsInvalidArgument(const Status& s) { return s.code() == StatusCode::kInvalidArgument; }
+inline bool IsUnimplemented(const Status& s) { return s.code() == StatusCode::kUnimplemented; }
+inline bool IsResourceExhausted(const Status& s) { return s.code() == StatusCode::kResourceExhausted; }
+inline bool IsInternal(const Status& s) { return s.code() == StatusCode::kInternal; }
+inline bool IsFailedPrecondition(const Status& s) { return s.code() == StatusCode::kFailedPrecondition; }
 }  // namespace absl

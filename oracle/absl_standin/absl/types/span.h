@@ -32,4 +32,16 @@ class Span {
   T* data_ = nullptr;
   size_t size_ = 0;
 };
+template <class T>
+constexpr Span<T> MakeSpan(T* data, size_t size) { return Span<T>(data, size); }
+template <class C>
+constexpr auto MakeSpan(C& c) -> Span<std::remove_pointer_t<decltype(c.data())>> {
+  return Span<std::remove_pointer_t<decltype(c.data())>>(c.data(), c.size());
+}
+template <class T>
+constexpr Span<const T> MakeConstSpan(const T* data, size_t size) { return Span<const T>(data, size); }
+template <class C>
+constexpr auto MakeConstSpan(const C& c) -> Span<const std::remove_pointer_t<decltype(c.data())>> {
+  return Span<const std::remove_pointer_t<decltype(c.data())>>(c.data(), c.size());
+}
 }  // namespace absl

@@ -13,19 +13,32 @@
  *       reproduce its hand-computable answer (attention_test.cc:282-360).
  *   oracle_qk_prepare, oracle_gqa_decode, oracle_gqa_probabilities   restate PrepareAttentionKernel,
  *       FullAttentionKernel, AttentionProbabilitiesKernel (src/llm/layers/util/
- *       cached_attention_ops.cc:30-79, :83-126, :131-178).  No compilable reference CPU code exists
- *       for them; they are pinned by the reference tests' known answers
- *       (cached_attention_ops_test.cc:364-398 exact gate products, :472-503 uniform 1/length rows,
- *       cached_attention_test.cc:108-156) and cross-checked against an independent double-precision
- *       statement of the same layer written from the equations in the tests' specification
- *       (cached_attention_ops_test.cc:43-131).
+ *       cached_attention_ops.cc:30-79, :83-126, :131-178).  The GPU kernels themselves cannot be
+ *       compiled without cuTile, but the scalar specification the reference tests them against can:
+ *       class AttentionReference (cached_attention_ops_test.cc:43-131) is compiled from the
+ *       reference tree into oracle/_ref/libpluto_ref_specs.so, its outputs on that test's own 35
+ *       steps, shapes and inputs are committed (tests/golden/reference_specs.npz), and these
+ *       functions must match them at the test's tolerance (3e-5 + 1e-4|x| unrounded, 2e-4 + 0.8 %
+ *       rounded); plus the tests' known answers (:364-398 exact gate products, :472-503 uniform
+ *       1/length rows, cached_attention_test.cc:108-156).
  *   oracle_gqa_prefill   restates the attention core of ForwardKernel
  *       (src/llm/layers/qwen_attention.cc:68-119); pinned by equality with oracle_gqa_decode run
- *       token by token (the reference's own cross-path check, qwen_attention_test.cc:155-228).
+ *       token by token (the reference's own cross-path check, qwen_attention_test.cc:155-228), and
+ *       the sequence layer as a whole by the compiled Reference of qwen_attention_test.cc:26-95 on
+ *       that test's shapes.
  *   oracle_gdn_*   restate ConvolutionKernel/ConvForward, DeltaRecurrenceKernel/RecurrenceForward,
  *       DeltaOutputKernel/OutputForward (cached_attention_ops.cc:180-272,
- *       sequence_delta_net.cc:31-121); pinned by the a=+-100 softplus extremes and Reset-replay
- *       properties of cached_attention_ops_test.cc:400-470 and a double-precision cross-check.
+ *       sequence_delta_net.cc:31-121); pinned by the compiled class DeltaReference
+ *       (cached_attention_ops_test.cc:133-220; six steps incl. the a=+-100 softplus extremes) and
+ *       the compiled Reference of sequence_delta_net_test.cc:66-159 on the three shapes of
+ *       :241-297, at those tests' tolerances, through the same committed records.
+ *   oracle_gqa_sequence_bwd, oracle_gdn_sequence_bwd   restate the backward kernels
+ *       (qwen_attention.cc:124-239, sequence_delta_net.cc:126-339); pinned by the central
+ *       differences the reference's gradient tests take of those compiled specifications
+ *       (qwen_attention_test.cc:230-301, 3e-5; sequence_delta_net_test.cc:299-373, 2e-5 + 0.2 %),
+ *       recorded in the same file.
+ *   Where oracle/_ref/libpluto_ref_specs.so is present the comparisons also run live on random
+ *   inputs (tests/test_oracle_specs.py).
  *
  * All tensors are caller-owned; nothing here allocates except scratch rows on the stack/heap.
  */
