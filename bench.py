@@ -10,10 +10,16 @@ device time.
     python bench.py --impl reference [...]                       the reference's CPU layer
 
 The JSON line also carries: `roofline` for the dominant kernel (tensor-core bound), `e2e` (the
-same metric through the public API from pinned host buffers, copies inside the timed region),
+same metric through the public API from pinned host buffers, copies inside the timed region)
+with `e2e_copy_floor_ms` (the same chunked copies with no kernels) beside it, `parity_max_abs`
+(sampled rows of this run's own output against the CPU oracle, outside the timed region),
+`clocks` sampled during the timed region, and at every N the other half of the metric:
+`decode` (batch-64 GQA decode sharded by KV head, KV GB/s against the HBM roofline), `gdn` (gated
+delta-net sharded by head: chunked prefill, single steps, a fused 256-token launch) and
+`allgather_ms` (the optional NCCL gather of the head-sharded outputs, reported separately).  At
+N = 1 it adds `sustained` (seconds of back-to-back headline launches with sampled clocks),
 `cpu_baseline` (the reference's own CPU attention layer timed on a bounded sample on the host
-cores), `clocks` sampled during the timed region, and `other_workloads` with the decode (HBM
-roofline), training forward/backward and delta-net figures measured in the same run (N = 1 only).
+cores) and `other_workloads` (training forward/backward, projections).
 Inputs are seeded synthetic tensors with the configuration's shapes and distributions.
 """
 from __future__ import annotations
@@ -168,24 +174,305 @@ def run_reference_arm(args):
 # --------------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------------
+class Ranks:
+    """The process group as the timed legs need it: barriers and max-over-ranks device times."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > 126 MB L2
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, value: float) -> float:
+        if self.world == 1:
+            return value
+        t = self.torch.tensor([value], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, fn, steps, warmup, flush=True):
+        """Mean device time per step in ms: CUDA events around each step, L2 flushed between
+        steps (outside the events), barrier + synchronize either side, max over ranks."""
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        self.barrier()
+        for i in range(steps):
+            if flush:
+                self.flush.fill_(i & 0xFF)
+            starts[i].record()
+            fn()
+            stops[i].record()
+        self.barrier()
+        total = sum(s.elapsed_time(e) for s, e in zip(starts, stops))
+        return self.max_over_ranks(total) / steps
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def prefill_parity(out, q, k, v, count=24):
+    """max |engine - oracle| over `count` sampled query rows (all heads of this rank) of the
+    step's own output; the oracle runs outside every timed region."""
+    import numpy as np
+
+    import oracle
+    seq = out.shape[1]
+    rows = sorted({0, 127, 128, 255, 256, seq // 2 - 1, seq // 2, seq - 129, seq - 128, seq - 1,
+                   *(int(r) for r in np.random.default_rng(SEED).integers(0, seq, size=count))})
+    import torch
+    bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    want = oracle.gqa_prefill_rows(bits(q[0]), bits(k[0]), bits(v[0]), rows, threads=os.cpu_count() or 1)
+    got = bits(out[0][rows])
+    return float(np.abs(oracle.from_bf16_bits(got) - oracle.from_bf16_bits(want)).max()), len(rows)
+
+
+def copy_floor_ms(ranks, q_host, k_host, v_host, out_host, steps=5):
+    """The end-to-end call's transfers with no kernels: the same token chunks (pluto_b200/csrc/
+    host_pipeline.cu: 1024 tokens, grown to 4 MB of input, tapering at the end), input copies on
+    one stream and output copies on another, so both PCIe directions are busy as in the real
+    call.  What the link delivers is the floor of `e2e`."""
+    torch = ranks.torch
+    seq = q_host.shape[1]
+    token_bytes = (q_host.shape[2] + 2 * k_host.shape[2]) * HEAD_DIM * 2
+    full = max(1, ((4 << 20) // token_bytes + 1023) // 1024) * 1024
+    chunks, t0 = [], 0
+    while t0 < seq:
+        left = seq - t0
+        count = min(left, full if left > 2 * full else (full // 2 if left > full else full // 4))
+        chunks.append((t0, count))
+        t0 += count
+    q_dev, k_dev, v_dev = (torch.empty_like(t, device="cuda") for t in (q_host, k_host, v_host))
+    out_dev = torch.zeros_like(out_host, device="cuda")
+    h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def step():
+        main = torch.cuda.current_stream()
+        h2d.wait_stream(main)
+        d2h.wait_stream(main)
+        for (t0, count) in chunks:
+            with torch.cuda.stream(h2d):
+                for dev, host in ((k_dev, k_host), (v_dev, v_host), (q_dev, q_host)):
+                    dev[:, t0:t0 + count].copy_(host[:, t0:t0 + count], non_blocking=True)
+            d2h.wait_stream(h2d)
+            with torch.cuda.stream(d2h):
+                out_host[:, t0:t0 + count].copy_(out_dev[:, t0:t0 + count], non_blocking=True)
+        main.wait_stream(d2h)
+
+    return ranks.timed(step, steps, 2)
+
+
+def decode_leg(ranks, peaks, steps=20, batch=64, capacity=32768):
+    """BASELINE config 4: one query token per sequence, 40/8 heads, head width 128, bf16 cache,
+    cached lengths U[4096, 32768] from the seed, sharded by KV head (rank r holds KV heads
+    [r*8/N, (r+1)*8/N) of every sequence and their query heads).  One step = one pluto_gqa_decode
+    call (chunk kernel + merge kernel).  KV GB/s = algorithmic bytes of all ranks / max-over-ranks
+    device time; the roofline fraction is one GPU's share against the measured HBM copy peak."""
+    import numpy as np
+    torch = ranks.torch
+
+    import oracle
+    from pluto_b200.layers import gqa_decode
+    from pluto_b200.sharding import shard_heads
+
+    shard = shard_heads(Q_HEADS, KV_HEADS, ranks.world, ranks.rank)
+    lens = np.random.default_rng(SEED).integers(4096, capacity + 1, size=batch).astype(np.int32)
+    gen = torch.Generator(device="cuda").manual_seed(SEED + 101 * ranks.rank)
+    k_pool = torch.empty((batch, capacity, shard.kv_heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+    v_pool = torch.empty_like(k_pool)
+    for pool in (k_pool, v_pool):
+        for b in range(batch):
+            pool[b] = (torch.randn(capacity, shard.kv_heads, HEAD_DIM, device="cuda", generator=gen) * 0.5).bfloat16()
+    q = (torch.randn(batch, shard.q_heads, HEAD_DIM, device="cuda", generator=gen) * 0.5).bfloat16()
+    tl = torch.from_numpy(lens).cuda()
+    out = torch.empty_like(q)
+    ms = ranks.timed(lambda: gqa_decode(q, k_pool, v_pool, tl, capacity, out=out), steps, 3)
+    per_rank_bytes = 512.0 * shard.kv_heads * float(lens.sum()) + 2 * q.numel() * 2
+    total_bytes = 512.0 * KV_HEADS * float(lens.sum()) + 2 * batch * Q_HEADS * HEAD_DIM * 2
+    # parity: every head of this rank for the shortest and the median sequence
+    order = np.argsort(lens)
+    picked = [int(order[0]), int(order[batch // 2])]
+    bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    want = oracle.gqa_decode_batch(bits(q[picked]), [bits(k_pool[b, :lens[b]]) for b in picked],
+                                   [bits(v_pool[b, :lens[b]]) for b in picked], lens[picked],
+                                   threads=os.cpu_count() or 1)
+    parity = float(np.abs(oracle.from_bf16_bits(bits(out[picked])) - oracle.from_bf16_bits(want)).max())
+    parity = ranks.max_over_ranks(parity)
+    per_gpu = per_rank_bytes / (ms * 1e-3) / 1e9
+    result = {
+        "workload": f"batch {batch}, 40/8 heads, head_dim 128, cached lengths U[4096,32768], bf16 cache, "
+                    f"{shard.kv_heads} KV head(s) per GPU",
+        "ms": ms, "kv_gbs": total_bytes / (ms * 1e-3) / 1e9, "kv_gbs_per_gpu": per_gpu,
+        "sum_lengths": int(lens.sum()), "algorithmic_bytes": total_bytes,
+        "algorithmic_bytes_per_gpu": per_rank_bytes, "steps": steps, "gpu_launches": 2 * steps,
+        "parity_max_abs": parity, "parity_sample": "all heads of the shortest and the median sequence",
+        "roofline": {"bound": "hbm", "kernel": "gqa_decode_tc<128> + gqa_decode_merge", "achieved": per_gpu,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": per_gpu / peaks["hbm_gbs"],
+                     "frac_of_nominal_8TBs": per_gpu / 8000.0, "peak_source": peaks["source"] + " (copy)"}}
+    return result, out
+
+
+def gdn_leg(ranks, peaks, batch=2, tokens=16384, heads=16, dim=128):
+    """BASELINE config 5 sharded by head: chunked prefill from a zero state, then single-token
+    steps from the final state (256 of them replayed as one CUDA graph: the device cost without
+    the per-call host cost), and the same 256 tokens as ONE launch of the token-sequential kernel
+    (state on chip for all of them)."""
+    import numpy as np
+    torch = ranks.torch
+
+    import oracle
+    from pluto_b200.layers import gdn_prefill, gdn_step
+
+    local = heads // ranks.world
+    gen = torch.Generator(device="cuda").manual_seed(SEED + 7 * ranks.rank)
+    total = tokens + 256
+    unit = lambda: torch.nn.functional.normalize(torch.randn(batch, total, local, dim, device="cuda", generator=gen), dim=-1).bfloat16()
+    q, k = unit(), unit()
+    v = torch.randn(batch, total, local, dim, device="cuda", generator=gen).bfloat16()
+    g = torch.sigmoid(torch.randn(batch, total, local, device="cuda", generator=gen) * 2 + 2)
+    beta = torch.sigmoid(torch.randn(batch, total, local, device="cuda", generator=gen))
+    qp, kp, vp = (t[:, :tokens].contiguous() for t in (q, k, v))
+    gp, bp = g[:, :tokens].contiguous(), beta[:, :tokens].contiguous()
+    state = torch.zeros(batch, local, dim, dim, device="cuda")
+    out = torch.empty_like(vp)
+
+    def prefill():
+        state.zero_()
+        gdn_prefill(qp, kp, vp, gp, bp, state, out=out)
+
+    prefill_ms = ranks.timed(prefill, 5, 2)
+    final = state.clone()
+    # parity: one (sequence, head) unit of this rank over its first 2048 tokens
+    bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    n = 2048
+    ref_state = np.zeros((1, 1, dim, dim), np.float32)
+    want = oracle.gdn_recurrence(bits(qp[1:2, :n, :1]), bits(kp[1:2, :n, :1]), bits(vp[1:2, :n, :1]),
+                                 gp[1:2, :n, :1].cpu().numpy(), bp[1:2, :n, :1].cpu().numpy(), ref_state,
+                                 True, 1.0, True)
+    parity = float(np.abs(oracle.from_bf16_bits(bits(out[1:2, :n, :1])) - oracle.from_bf16_bits(want)).max())
+    parity = ranks.max_over_ranks(parity)
+
+    # single steps: 256 fresh tokens from the final state, replayed as one CUDA graph
+    steps_in = [tuple(t[:, tokens + i].contiguous() for t in (q, k, v, g, beta)) for i in range(256)]
+    o1 = torch.empty_like(v[:, 0])
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        gdn_step(*steps_in[0], state, out=o1)
+        with torch.cuda.graph(graph, stream=side):
+            for item in steps_in:
+                gdn_step(*item, state, out=o1)
+    torch.cuda.current_stream().wait_stream(side)
+    graph_ms = ranks.timed(graph.replay, 5, 2, flush=False)
+    # the same 256 tokens as one launch (token-sequential kernel, state held on chip throughout)
+    qs, ks, vs = (t[:, tokens:].contiguous() for t in (q, k, v))
+    gs, bs = g[:, tokens:].contiguous(), beta[:, tokens:].contiguous()
+    fused_out = torch.empty_like(vs)
+
+    def fused():
+        state.copy_(final)
+        gdn_prefill(qs, ks, vs, gs, bs, state, out=fused_out, chunked=False)
+
+    fused_ms = ranks.timed(fused, 5, 2, flush=False)
+    state_bytes = 2.0 * batch * local * dim * dim * 4
+    flop = 94.49e9 * (batch * local * tokens) / (2 * 16 * 16384)
+    tflops = flop / (prefill_ms * 1e-3) / 1e12
+    return {
+        "workload": f"batch {batch}, {local} of {heads} heads per GPU, d_k = d_v = {dim}, {tokens}-token chunked "
+                    "prefill from a zero state, then 256 single-token steps",
+        "prefill_ms": prefill_ms, "prefill_tflops_chunked_count": tflops * ranks.world,
+        "prefill_tflops_per_gpu": tflops,
+        "prefill_roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                             "frac": tflops / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                             "note": "dense chunked count (11.53 MFLOP per chunk and head); the kernel is bound "
+                                     "by the chain of dependent chunk steps, not by the tensor pipe"},
+        "step_in_cuda_graph_us": graph_ms * 1e3 / 256,
+        "step_state_gbs_per_gpu": state_bytes / (graph_ms * 1e-3 / 256) / 1e9,
+        "fused_256_step_launch_us": fused_ms * 1e3, "fused_us_per_token": fused_ms * 1e3 / 256,
+        "fused_note": "one launch, state read and written once: not bound by per-step state traffic",
+        "parity_max_abs": parity, "parity_sample": "one (sequence, head) unit per rank, first 2048 prefill tokens",
+    }
+
+
+def allgather_leg(ranks, prefill_out, decode_out):
+    """The optional gather of the head-sharded outputs into the [rows, E] layout (outside `value`):
+    ncclAllGather over NVLink + local interleave through the C entry point pluto_allgather_heads,
+    for the headline's 84 MB output and the decode step's 0.66 MB output."""
+    torch = ranks.torch
+    from pluto_b200.sharding import NcclCommunicator, allgather_heads
+    comm = NcclCommunicator()
+    result = {}
+    for name, local in (("prefill_out", prefill_out.reshape(SEQ, -1)), ("decode_out", decode_out.reshape(decode_out.shape[0], -1))):
+        rows, cols = local.shape
+        scratch = torch.empty((ranks.world * rows, cols), dtype=local.dtype, device="cuda")
+        full = torch.empty((rows, ranks.world * cols), dtype=local.dtype, device="cuda")
+        ms = ranks.timed(lambda: allgather_heads(local, comm=comm, out=full, scratch=scratch), 10, 3)
+        # check: this rank's own columns come back where they belong
+        mine = full[:, ranks.rank * cols:(ranks.rank + 1) * cols]
+        if not torch.equal(mine, local):
+            raise SystemExit("all-gather returned this rank's heads in the wrong place")
+        result[name] = {"ms": ms, "bytes_gathered": rows * cols * ranks.world * local.element_size()}
+    comm.close()
+    return result
+
+
+def sustained_leg(ranks, step, peaks, seconds=2.5):
+    """Back-to-back headline launches for a few seconds (no L2 flush, no pauses) with the clocks
+    sampled: the regime of a long job under the power cap, against the sustained cuBLAS figure."""
+    torch = ranks.torch
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    with ClockSampler(ranks.local_rank) as sampler:
+        begin = time.perf_counter()
+        a.record()
+        while time.perf_counter() - begin < seconds:
+            for _ in range(50):
+                step()
+            launches += 50
+            torch.cuda.synchronize()
+        b.record()
+        torch.cuda.synchronize()
+    clocks = sampler.summary()
+    ms = a.elapsed_time(b) / launches
+    tflops = FLOP_PER_STEP / (ms * 1e-3) / 1e12
+    peak = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
+    return {"seconds": a.elapsed_time(b) / 1e3, "launches": launches, "ms_per_step": ms, "tflops": tflops,
+            "sm_mhz_median": clocks.get("sm_mhz"), "ms_times_mhz": ms * (clocks.get("sm_mhz") or 0.0),
+            "power_w_max": clocks.get("power_w_max"), "reasons": clocks.get("reasons"),
+            "frac_of_sustained_peak": tflops / peak, "sustained_peak": peak}
+
+
 def run_engine(args):
     import numpy as np
     import torch
-    import torch.distributed as dist
 
     from pluto_b200 import _capi
     from pluto_b200.layers import gqa_prefill, gqa_prefill_host
     from pluto_b200.sharding import shard_heads
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if int(os.environ.get("WORLD_SIZE", "1")) == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    ranks = Ranks()
+    world, rank = ranks.world, ranks.rank
     _capi.lib()
     shard = shard_heads(Q_HEADS, KV_HEADS, world, rank)
 
@@ -198,23 +485,16 @@ def run_engine(args):
     k_host = k_host[:, :, shard.kv_begin:shard.kv_end].contiguous().pin_memory()
     v_host = v_host[:, :, shard.kv_begin:shard.kv_end].contiguous().pin_memory()
     q, k, v = q_host.cuda(), k_host.cuda(), v_host.cuda()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > 126 MB L2
     out_host = torch.empty((1, SEQ, shard.q_heads, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    step_state = {"workspace": None}
+    step_state = {"workspace": None, "out": None}
 
     def step():
         # (with few heads per GPU the kernel cuts the key range of every query-tile pair into parts
         # and needs scratch for the partials; it is allocated once and handed back in)
         result = gqa_prefill(q, k, v, workspace=step_state["workspace"])
         step_state["workspace"] = result.get("workspace")
-        return result["out"]
+        step_state["out"] = result["out"]
 
     e2e_state = {"workspace": None}
 
@@ -226,34 +506,36 @@ def run_engine(args):
                                                   kv_heads_per_group=0,
                                                   workspace=e2e_state["workspace"])
 
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-        stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-        barrier()
-        for i in range(steps):
-            flush.fill_(i & 0xFF)          # evict L2 between timed iterations (outside the events)
-            starts[i].record()
-            fn()
-            stops[i].record()
-        barrier()
-        total = sum(s.elapsed_time(e) for s, e in zip(starts, stops))
-        t = torch.tensor([total], dtype=torch.float64, device="cuda")
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) / steps
-
-    with ClockSampler(local_rank) as sampler:
+    with ClockSampler(ranks.local_rank) as sampler:
         time.sleep(0.3)  # let the sampler take its first readings before the timed region
-        ms = timed(step, args.steps, max(args.warmup, 3))
-        e2e_ms = timed(e2e_step, max(3, min(args.steps, 10)), 3)
+        ms = ranks.timed(step, args.steps, max(args.warmup, 3))
+        e2e_ms = ranks.timed(e2e_step, max(3, min(args.steps, 10)), 3)
     clocks = sampler.summary()
     status = _capi.kernel_status()
     if status != 0:
         raise SystemExit(f"kernel status word = {status:#x}")
 
+    # parity of what was just timed (outside the timed region): sampled rows of the device-resident
+    # step's output and of the end-to-end call's host output, against the CPU oracle
+    parity, parity_rows = prefill_parity(step_state["out"], q, k, v)
+    e2e_parity, _ = prefill_parity(out_host.cuda(), q, k, v)
+    parity = ranks.max_over_ranks(max(parity, e2e_parity))
+
     peaks = measured_peaks()
+    floor_ms = copy_floor_ms(ranks, q_host, k_host, v_host, out_host)
+    extras = {}
+    if not args.no_extras:
+        decode, decode_out = decode_leg(ranks, peaks)
+        extras["decode"] = decode
+        torch.cuda.empty_cache()
+        extras["gdn"] = gdn_leg(ranks, peaks)
+        torch.cuda.empty_cache()
+        if world > 1:
+            extras["allgather_ms"] = allgather_leg(ranks, step_state["out"], decode_out)
+        status = _capi.kernel_status()
+        if status != 0:
+            raise SystemExit(f"kernel status word = {status:#x}")
+
     value = FLOP_PER_STEP / (ms * 1e-3) / 1e12
     elements = 2  # bf16
     h2d = (q_host.numel() + k_host.numel() + v_host.numel()) * elements
@@ -271,25 +553,32 @@ def run_engine(args):
         "e2e": {"value": FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "api": "pluto_b200.layers.gqa_prefill_host (pluto_gqa_prefill_fwd_host): pinned host buffers in and out, copies and kernels pipelined per chunk of 1024 prompt tokens"},
+        "e2e_copy_floor_ms": floor_ms,
+        "parity_max_abs": parity,
+        "parity_sample": f"{parity_rows} query rows x all heads of every rank, device-resident and end-to-end outputs",
         # one attention kernel per step, plus the merge kernel when the key/value split is active
         "gpu_launches": args.steps * (2 if step_state["workspace"] is not None else 1),
         "clocks": clocks,
     }
+    line.update(extras)
     if rank == 0:
-        # roofline of the one kernel in the step (attn_fwd_sm100_pair<128>): bf16 tensor-core bound.
+        # roofline of the one kernel in the step: bf16 tensor-core bound, timed as isolated launches
+        # with an L2 flush between them, hence against the burst figure
         per_rank_flop = FLOP_PER_STEP / world
         achieved = per_rank_flop / (ms * 1e-3) / 1e12
+        pairs_per_sm = shard.q_heads * (SEQ // 256) / 148.0
         line["roofline"] = {
-            "bound": "tensor", "kernel": "attn_fwd_sm100_pair<128>", "achieved": achieved,
+            "bound": "tensor",
+            "kernel": "attn_fwd_sm100_pair<128>" if pairs_per_sm >= 2 else "attn_fwd_sm100<128>",
+            "achieved": achieved,
             "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-            "frac_of_sustained": (achieved / peaks["bf16_tflops_sustained"]
-                                  if peaks.get("bf16_tflops_sustained") else None),
             "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
             "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
             "algorithmic_flop_per_launch": per_rank_flop,
         }
         if world == 1 and not args.no_extras:
-            line["other_workloads"] = other_workloads(peaks)
+            line["sustained"] = sustained_leg(ranks, step, peaks)
+            line["other_workloads"] = other_workloads(peaks, skip=("decode", "gdn"))
             cores = os.cpu_count() or 1
             heads = min(Q_HEADS, cores)
             seconds, flop, kind = cpu_reference_sample(4096, heads, cores)
@@ -299,8 +588,7 @@ def run_engine(args):
                 "sample": f"{heads} of {Q_HEADS} query heads x first 4096 of {SEQ} prompt tokens "
                           f"({flop / 1e9:.2f} GFLOP), one single-head CPU-layer instance per thread"}
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    ranks.close()
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_sm100_pair<128> launch on this
@@ -308,7 +596,7 @@ def run_engine(args):
 TRAFFIC_BYTES_PER_LAUNCH = 164.5e6
 
 
-def other_workloads(peaks, only=None, decode_batch=64, steps_scale=1.0):
+def other_workloads(peaks, only=None, decode_batch=64, steps_scale=1.0, skip=()):
     """Secondary figures of the same run (one GPU): decode against the HBM roofline, the GPT-2
     training forward/backward, and the delta-net prefill + step.  `only` restricts the run to one
     of them (used by --profile-case, with a smaller decode batch so an ncu capture stays small)."""
@@ -331,7 +619,9 @@ def other_workloads(peaks, only=None, decode_batch=64, steps_scale=1.0):
 
     result = {}
     if only not in (None, "decode"):
-        return _other_rest(peaks, only, time_ms)
+        return _other_rest(peaks, only, time_ms, skip)
+    if "decode" in skip:
+        return _other_rest(peaks, only, time_ms, skip)
     # decode: batch 64, L ~ U[4096, 32768]; cache 8.6 GB >> L2
     rng = np.random.default_rng(SEED)
     batch, cap = decode_batch, 32768
@@ -355,11 +645,11 @@ def other_workloads(peaks, only=None, decode_batch=64, steps_scale=1.0):
     del k_pool, v_pool
     if only == "decode":
         return result
-    result.update(_other_rest(peaks, only, time_ms))
+    result.update(_other_rest(peaks, only, time_ms, skip))
     return result
 
 
-def _other_rest(peaks, only, time_ms):
+def _other_rest(peaks, only, time_ms, skip=()):
     import torch
 
     from pluto_b200.layers import AttentionLayer, DataType, gdn_prefill, gdn_step
@@ -407,7 +697,7 @@ def _other_rest(peaks, only, time_ms):
     result.update(_gqa_bwd_workload(time_ms))
     result.update(_linear_workload(time_ms, peaks))
     result.update(_dense_workload(time_ms, peaks))
-    result.update(_gdn_workload(time_ms))
+    result.update(_gdn_workload(time_ms, bptt_only="gdn" in skip))
     return result
 
 
@@ -520,7 +810,7 @@ def _gqa_bwd_workload(time_ms):
         "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12}}
 
 
-def _gdn_workload(time_ms):
+def _gdn_workload(time_ms, bptt_only=False):
     import torch
 
     from pluto_b200 import _capi
@@ -541,6 +831,17 @@ def _gdn_workload(time_ms):
         st.zero_()
         gdn_prefill(qn, kn, vn, g, beta, st, out=og)
 
+    pre_ms = step_ms = graph_ms = None
+    if not bptt_only:
+        pre_ms, step_ms, graph_ms = _gdn_forward_times(time_ms, prefill, qn, kn, vn, g, beta, st)
+    result.update(_gdn_bptt(time_ms, qn, kn, vn, bb, tt, hh, dd, pre_ms, step_ms, graph_ms))
+    return result
+
+
+def _gdn_forward_times(time_ms, prefill, qn, kn, vn, g, beta, st):
+    import torch
+
+    from pluto_b200.layers import gdn_step
     pre_ms = time_ms(prefill, steps=3, warmup=1)
     q1, k1, v1 = qn[:, 0].contiguous(), kn[:, 0].contiguous(), vn[:, 0].contiguous()
     g1, b1, o1 = g[:, 0].contiguous(), beta[:, 0].contiguous(), torch.empty_like(vn[:, 0])
@@ -558,7 +859,15 @@ def _gdn_workload(time_ms):
                 gdn_step(q1, k1, v1, g1, b1, st, out=o1)
     torch.cuda.current_stream().wait_stream(side)
     graph_ms = time_ms(graph.replay, steps=5, warmup=3) / 256
-    # BPTT through the recurrence (checkpointed every 64 tokens), q/k normalisation included
+    return pre_ms, step_ms, graph_ms
+
+
+def _gdn_bptt(time_ms, qn, kn, vn, bb, tt, hh, dd, pre_ms, step_ms, graph_ms):
+    """BPTT through the recurrence (checkpointed every 64 tokens), q/k normalisation included."""
+    import torch
+
+    from pluto_b200 import _capi
+    result = {}
     L = _capi.lib()
     a_raw = torch.randn(bb, tt, hh, device="cuda").bfloat16()
     b_raw = torch.randn(bb, tt, hh, device="cuda").bfloat16()
@@ -579,12 +888,15 @@ def _gdn_workload(time_ms):
             da.data_ptr(), db.data_ptr(), None, None, ws.data_ptr(), ws_bytes, bb, tt, hh, hh, dd, dd, 1))
 
     bptt_ms = time_ms(bptt, steps=2, warmup=1)
-    result["gated_delta_net"] = {
-        "workload": "batch 2, 16 heads, d_k = d_v = 128, seq 16384 prefill then single-token steps",
-        "prefill_ms": pre_ms, "prefill_tflops_chunked_count": 94.49e9 / (pre_ms * 1e-3) / 1e12,
-        "step_us": step_ms * 1e3, "step_state_gbs": 4.19e6 / (step_ms * 1e-3) / 1e9,
-        "step_in_cuda_graph_us": graph_ms * 1e3, "step_in_cuda_graph_state_gbs": 4.19e6 / (graph_ms * 1e-3) / 1e9,
-        "recurrence_bwd_ms": bptt_ms, "recurrence_bwd_workspace_gb": ws_bytes / 1e9}
+    entry = {"workload": "batch 2, 16 heads, d_k = d_v = 128, seq 16384",
+             "recurrence_bwd_ms": bptt_ms, "recurrence_bwd_workspace_gb": ws_bytes / 1e9}
+    if pre_ms is not None:
+        entry.update({
+            "prefill_ms": pre_ms, "prefill_tflops_chunked_count": 94.49e9 / (pre_ms * 1e-3) / 1e12,
+            "step_us": step_ms * 1e3, "step_state_gbs": 4.19e6 / (step_ms * 1e-3) / 1e9,
+            "step_in_cuda_graph_us": graph_ms * 1e3,
+            "step_in_cuda_graph_state_gbs": 4.19e6 / (graph_ms * 1e-3) / 1e9})
+    result["gated_delta_net"] = entry
     return result
 
 

@@ -293,6 +293,8 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         _ptr(normalizers), B, T, Hq, Hkv, D, q.stride(1), q.stride(2), gts, ghs,
         int(round_to_bfloat16), ws_ptr, ws_bytes))
     result = {"out": out}
+    if ws_ptr is not None:
+        result["workspace"] = workspace   # hand it back in to skip the allocation next time
     if want_core:
         result["core"] = core
     if want_stats:
