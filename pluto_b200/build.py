@@ -66,12 +66,13 @@ HOST_LIB = os.path.join(HERE, "libpluto_b200_host.so")
 
 def build_host() -> str:
     """C++ host adapter (pluto_b200/host): the reference-shaped layer classes over the C ABI."""
-    src = os.path.join(HERE, "host", "host.cc")
-    deps = [src, LIB] + [os.path.join(HERE, "host", f) for f in ("layers.h", "runtime.h", "status.h")]
+    srcs = [os.path.join(HERE, "host", f) for f in ("host.cc", "qwen_layers.cc")]
+    deps = srcs + [LIB] + [os.path.join(HERE, "host", f) for f in ("layers.h", "qwen_layers.h", "runtime.h",
+                                                                    "status.h")]
     if os.path.exists(HOST_LIB) and os.path.getmtime(HOST_LIB) > max(os.path.getmtime(p) for p in deps):
         return HOST_LIB
     cxx = os.environ.get("CXX", "g++")
-    proc = subprocess.run([cxx, "-std=c++17", "-O2", "-fPIC", "-shared", src, "-I/usr/local/cuda/include",
+    proc = subprocess.run([cxx, "-std=c++17", "-O2", "-fPIC", "-shared", *srcs, "-I/usr/local/cuda/include",
                            "-L" + HERE, "-lpluto_b200", "-L/usr/local/cuda/lib64", "-lcudart",
                            "-Wl,-rpath,$ORIGIN", "-o", HOST_LIB], capture_output=True, text=True)
     if proc.returncode != 0:

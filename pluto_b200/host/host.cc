@@ -285,7 +285,18 @@ Status CachedAttentionStep(cuda::Executor& executor, const FullAttentionParamete
                            KeyValueCache& cache, const float* q_gate, const float* k, const float* v,
                            const float* q_norm, const float* k_norm, float* output,
                            float* probabilities) {
+  return CachedAttentionStepTyped(executor, p, cache, q_gate, k, v, PLUTO_FP32, q_norm, k_norm, output,
+                                  PLUTO_FP32, probabilities);
+}
+
+Status CachedAttentionStepTyped(cuda::Executor& executor, const FullAttentionParameters& p,
+                                KeyValueCache& cache, const void* q_gate, const void* k, const void* v,
+                                int input_dtype, const float* q_norm, const float* k_norm, void* output,
+                                int output_dtype, float* probabilities) {
   PLUTO_RETURN_IF_ERROR(ValidateCachedAttention(executor, p, cache));
+  if ((input_dtype != PLUTO_FP32 && input_dtype != PLUTO_BF16) ||
+      (output_dtype != PLUTO_FP32 && output_dtype != PLUTO_BF16))
+    return InvalidArgumentError("attention activations must be FP32 or BF16");
   if (!q_gate || !k || !v || !q_norm || !k_norm || !output)
     return InvalidArgumentError("attention requires non-null device pointers");
   if (cache.position() >= cache.capacity())
@@ -306,14 +317,17 @@ Status CachedAttentionStep(cuda::Executor& executor, const FullAttentionParamete
   const pluto_kv_cache view = View(cache);
   const size_t token = 2 * static_cast<size_t>(p.query_heads) * p.head_dim, head = 2 * static_cast<size_t>(p.head_dim);
   PLUTO_RETURN_IF_ERROR(FromEngine(
-      pluto_qk_prepare(executor.stream(), q_gate, k, v, PLUTO_FP32, token, head, q_norm, k_norm,
+      pluto_qk_prepare(executor.stream(), q_gate, k, v, input_dtype, token, head, q_norm, k_norm,
                        device_counters, queries.data(), PLUTO_FP32, &view, 1, 1, p.query_heads,
                        p.key_value_heads, p.head_dim, p.rotary_dim, p.rms_norm_epsilon,
                        p.rope_theta, p.round_to_bfloat16),
       "prepare Qwen attention"));
   PLUTO_RETURN_IF_ERROR(FromEngine(
-      pluto_gqa_decode(executor.stream(), queries.data(), PLUTO_FP32, q_gate + p.head_dim, PLUTO_FP32,
-                       token, head, &view, device_counters + 1, position + 1, output, PLUTO_FP32,
+      pluto_gqa_decode(executor.stream(), queries.data(), PLUTO_FP32,
+                       static_cast<const char*>(q_gate) +
+                           static_cast<size_t>(p.head_dim) * (input_dtype == PLUTO_BF16 ? 2 : 4),
+                       input_dtype, token, head, &view, device_counters + 1, position + 1, output,
+                       output_dtype,
                        nullptr, workspace.data(), ws_bytes, 1, p.query_heads, p.key_value_heads,
                        p.head_dim, p.round_to_bfloat16),
       "Qwen full attention"));
@@ -351,6 +365,16 @@ StatusOr<std::unique_ptr<DeltaNetState>> DeltaNetState::Create(cuda::Executor& e
 Status DeltaNetState::Step(const float* qkv, const float* z, const float* a, const float* b,
                            const float* conv_weight, const float* a_log, const float* dt_bias,
                            const float* norm_weight, float* output) {
+  return StepTyped(qkv, z, a, b, PLUTO_FP32, conv_weight, a_log, dt_bias, norm_weight, output, PLUTO_FP32);
+}
+
+Status DeltaNetState::StepTyped(const void* qkv, const void* z, const void* a, const void* b,
+                                int input_dtype, const float* conv_weight, const float* a_log,
+                                const float* dt_bias, const float* norm_weight, void* output,
+                                int output_dtype) {
+  if ((input_dtype != PLUTO_FP32 && input_dtype != PLUTO_BF16) ||
+      (output_dtype != PLUTO_FP32 && output_dtype != PLUTO_BF16))
+    return InvalidArgumentError("DeltaNet activations must be FP32 or BF16");
   if (!qkv || !z || !a || !b || !conv_weight || !a_log || !dt_bias || !norm_weight || !output)
     return InvalidArgumentError("DeltaNet requires non-null device pointers");
   const auto& p = parameters_;
@@ -361,12 +385,12 @@ Status DeltaNetState::Step(const float* qkv, const float* z, const float* a, con
   float* beta = g + p.value_heads;
   cudaStream_t stream = executor_.stream();
   PLUTO_RETURN_IF_ERROR(FromEngine(
-      pluto_gdn_conv_silu(stream, qkv, conv_weight, PLUTO_FP32, 1, 1, channels, p.conv_kernel_dim,
+      pluto_gdn_conv_silu(stream, qkv, conv_weight, input_dtype, 1, 1, channels, p.conv_kernel_dim,
                           p.round_to_bfloat16, static_cast<float*>(convolution_state_.data()),
                           convolved, PLUTO_FP32),
       "Qwen causal convolution"));
   PLUTO_RETURN_IF_ERROR(FromEngine(
-      pluto_gdn_gates(stream, a, b, a_log, dt_bias, PLUTO_FP32, 1, p.value_heads,
+      pluto_gdn_gates(stream, a, b, a_log, dt_bias, input_dtype, 1, p.value_heads,
                       p.round_to_bfloat16, g, beta),
       "Qwen gated delta gates"));
   PLUTO_RETURN_IF_ERROR(FromEngine(
@@ -376,9 +400,9 @@ Status DeltaNetState::Step(const float* qkv, const float* z, const float* a, con
                      p.round_to_bfloat16),
       "Qwen gated delta recurrence"));
   return FromEngine(
-      pluto_gdn_out_norm_gate(stream, core_output_.data(), PLUTO_FP32, z, PLUTO_FP32, norm_weight,
+      pluto_gdn_out_norm_gate(stream, core_output_.data(), PLUTO_FP32, z, input_dtype, norm_weight,
                               p.value_heads, p.value_head_dim, p.rms_norm_epsilon,
-                              p.round_to_bfloat16, 1, output, PLUTO_FP32),
+                              p.round_to_bfloat16, 1, output, output_dtype),
       "Qwen gated delta output norm");
 }
 

@@ -146,6 +146,17 @@ Status CachedAttentionStep(cuda::Executor& executor, const FullAttentionParamete
                            const float* v, const float* q_norm, const float* k_norm, float* output,
                            float* probabilities = nullptr);
 
+// The same step for activations that are not fp32: q_gate, k, v are read as `input_dtype`
+// (PLUTO_FP32 / PLUTO_BF16 of include/pluto_b200.h) and the output is written as `output_dtype`,
+// so a layer whose activations are bf16 needs no cast launches either side (the reference's
+// QwenAttentionLayer::CachedForward converts with ToFloat / ToBFloat16,
+// src/llm/layers/qwen_attention.cc:370-412).  Norm weights and probabilities stay fp32.
+Status CachedAttentionStepTyped(cuda::Executor& executor, const FullAttentionParameters& parameters,
+                                KeyValueCache& cache, const void* q_gate, const void* k,
+                                const void* v, int input_dtype, const float* q_norm,
+                                const float* k_norm, void* output, int output_dtype,
+                                float* probabilities = nullptr);
+
 struct DeltaNetParameters {
   int key_heads = 16;
   int value_heads = 48;
@@ -163,6 +174,11 @@ class DeltaNetState final {
   Status Step(const float* qkv, const float* z, const float* a, const float* b,
               const float* conv_weight, const float* a_log, const float* dt_bias,
               const float* norm_weight, float* output);
+  // Step for activations stored as `input_dtype` with the output written as `output_dtype`
+  // (see CachedAttentionStepTyped); weights stay fp32.
+  Status StepTyped(const void* qkv, const void* z, const void* a, const void* b, int input_dtype,
+                   const float* conv_weight, const float* a_log, const float* dt_bias,
+                   const float* norm_weight, void* output, int output_dtype);
   Status Reset();
 
  private:

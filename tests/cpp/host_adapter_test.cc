@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "../../pluto_b200/host/layers.h"
+#include "../../pluto_b200/host/qwen_layers.h"
 
 extern "C" {
 int oracle_attention_fwd(const void*, int, int, int, int, int, int, void*, float*, float*, float*);
@@ -27,6 +28,12 @@ int oracle_gdn_recurrence(const void*, const void*, const void*, const float*, c
                           int, int, int, int, int, int, float, int, int, float*, void*);
 void oracle_gdn_conv_step(const float*, const float*, int, int, int, float*, float*);
 void oracle_gdn_output(const float*, const float*, const float*, int, int, float, int, int, float*);
+int oracle_gqa_sequence_bwd(const float*, const float*, const float*, const float*, const float*, const float*,
+                            int, int, int, int, int, float, float, int, float*, float*, float*, float*, float*,
+                            float*);
+int oracle_gdn_sequence_bwd(const float*, const float*, const float*, const float*, const float*, const float*,
+                            const float*, const float*, const float*, int, int, int, int, int, int, float, int,
+                            float*, float*, float*, float*, float*, float*, float*, float*, float*);
 }
 
 using namespace pluto;
@@ -277,6 +284,239 @@ static void TestDeltaNetState(cuda::Executor& ex, int dim, bool round) {
   std::printf("ok DeltaNetState dim %d round %d\n", dim, round);
 }
 
+// ---- the three Qwen decoder layer classes -------------------------------------------------------
+static std::vector<float> Bf16Values(int count, float phase) {   // qwen_attention_test.cc:97-102
+  std::vector<float> r(count);
+  for (int i = 0; i < count; ++i)
+    r[i] = oracle_bf16_to_float(oracle_float_to_bf16(static_cast<float>(0.8 * std::sin(phase + 0.29 * i))));
+  return r;
+}
+static cuda::Buffer UploadBf16(cuda::Executor& ex, const std::vector<float>& values) {
+  std::vector<uint16_t> bits(values.size());
+  for (size_t i = 0; i < values.size(); ++i) bits[i] = oracle_float_to_bf16(values[i]);
+  return Upload(ex, bits.data(), bits.size() * 2);
+}
+static std::vector<float> DownloadBf16(cuda::Executor& ex, const cuda::Buffer& buffer) {
+  auto raw = Download<uint16_t>(ex, buffer.data(), buffer.size_bytes() / 2);
+  std::vector<float> r(raw.size());
+  for (size_t i = 0; i < raw.size(); ++i) r[i] = oracle_bf16_to_float(raw[i]);
+  return r;
+}
+static std::shared_ptr<BlockParameter> Parameter(cuda::Executor& ex, const std::vector<float>& values, bool active) {
+  auto parameter = BlockParameter::Create(ex, Upload(ex, values.data(), values.size() * 4), DataType::FP32);
+  CHECK(parameter.ok());
+  if (active) CHECK_OK((*parameter)->Activate());
+  return *parameter;
+}
+
+// qwen_attention_test.cc:155-228: sequence forward against the oracle, the causal hook, and the
+// cached layer fed token by token.
+static void TestQwenAttentionForward(cuda::Executor& ex, int d) {
+  FullAttentionParameters p;
+  p.query_heads = 2;
+  p.key_value_heads = 1;
+  p.head_dim = d;
+  p.rotary_dim = d == 3 ? 2 : 64;
+  p.capacity = 40;
+  const int length = d == 3 ? 33 : 3;
+  auto qg = Bf16Values(length * 2 * p.query_heads * d, .1f), k = Bf16Values(length * d, 1.2f),
+       v = Bf16Values(length * d, 2.3f), qw = Bf16Values(d, .2f), kw = Bf16Values(d, .4f);
+  auto layer = QwenAttentionLayer::Create(ex, p, Parameter(ex, qw, false), Parameter(ex, kw, false), length);
+  CHECK(layer.ok());
+  CHECK((*layer)->input_types()[0] == (ActivationType{DataType::BF16, {-2, length, 4 * d}}));
+  BufferVec inputs = {UploadBf16(ex, qg), UploadBf16(ex, k), UploadBf16(ex, v)};
+  int hook_calls = 0;
+  LayerHooks hooks;
+  hooks.attention_probabilities_hook = [&](cuda::Executor& e, const std::string&, const ActivationType& type,
+                                           const Buffer& buffer) {
+    CHECK(type == (ActivationType{DataType::FP32, {1, 2, length, length}}));
+    auto probs = Download<float>(e, buffer.data(), static_cast<size_t>(2) * length * length);
+    for (int h = 0; h < 2; ++h)
+      for (int row = 0; row < length; ++row) {
+        double sum = 0;
+        for (int t = 0; t < length; ++t) {
+          const float value = probs[(static_cast<size_t>(h) * length + row) * length + t];
+          if (t > row) CHECK(value == 0);
+          sum += value;
+        }
+        CHECK(std::fabs(sum - 1) <= 2e-6);
+      }
+    ++hook_calls;
+    return OkStatus();
+  };
+  auto fwd = (*layer)->fwd(ex, inputs, &hooks);
+  CHECK(fwd.ok());
+  CHECK(hook_calls == 1 && fwd->state.intermediates.size() == QwenAttentionLayer::kSavedBuffers);
+  const auto actual = DownloadBf16(ex, fwd->outputs[0]);
+  std::vector<float> want(actual.size()), zero(actual.size(), 0.f), dqg(qg.size()), dk(k.size()), dv(v.size());
+  CHECK(oracle_gqa_sequence_bwd(qg.data(), k.data(), v.data(), qw.data(), kw.data(), zero.data(), length, 2, 1, d,
+                                p.rotary_dim, p.rms_norm_epsilon, p.rope_theta, 1, dqg.data(), dk.data(), dv.data(),
+                                nullptr, nullptr, want.data()) == 0);
+  for (size_t i = 0; i < want.size(); ++i) CHECK(std::fabs(actual[i] - want[i]) <= 2e-4f + 8e-3f * std::fabs(want[i]));
+  // the cached layer, one token at a time, must reproduce the sequence layer's rows
+  auto cache = KeyValueCache::Create(ex, p.capacity, p.key_value_heads, p.head_dim);
+  CHECK(cache.ok());
+  auto cached = QwenAttentionLayer::Create(ex, p, Upload(ex, qw.data(), qw.size() * 4),
+                                           Upload(ex, kw.data(), kw.size() * 4), 1, cache->get());
+  CHECK(cached.ok());
+  for (int row = 0; row < length; ++row) {
+    BufferVec token = {UploadBf16(ex, {qg.begin() + row * 4 * d, qg.begin() + (row + 1) * 4 * d}),
+                       UploadBf16(ex, {k.begin() + row * d, k.begin() + (row + 1) * d}),
+                       UploadBf16(ex, {v.begin() + row * d, v.begin() + (row + 1) * d})};
+    auto output = (*cached)->fwd(ex, token);
+    CHECK(output.ok());
+    CHECK((*cache)->position() == row + 1);
+    const auto expected = DownloadBf16(ex, output->outputs[0]);
+    // (the reference pins bit equality here; the two kernels of this engine agree within bf16
+    // rounding of the same fp32 result)
+    for (int c = 0; c < 2 * d; ++c)
+      CHECK(std::fabs(actual[static_cast<size_t>(row) * 2 * d + c] - expected[c]) <=
+            2e-4f + 1.6e-2f * std::fabs(expected[c]));
+  }
+  auto no_backward = (*cached)->bwd(ex, {fwd->outputs[0]}, BackwardState{cached->get(), {}, {}});
+  CHECK(!no_backward.ok() && no_backward.status().code() == StatusCode::kUnimplemented);
+  CHECK(!QwenAttentionLayer::Create(ex, p, Parameter(ex, qw, false), Parameter(ex, kw, false), 2, cache->get()).ok());
+  FullAttentionParameters bad = p;
+  bad.rotary_dim = 3;
+  CHECK(!QwenAttentionLayer::Create(ex, bad, Parameter(ex, qw, false), Parameter(ex, kw, false), 3).ok());
+  std::printf("ok QwenAttentionLayer forward d %d\n", d);
+}
+
+// qwen_attention_test.cc:230-301: every gradient against the oracle's backward (itself pinned by
+// the reference's finite differences), and accumulation of the shared norm gradients.
+static void TestQwenAttentionBackward(cuda::Executor& ex) {
+  FullAttentionParameters p;
+  p.query_heads = 2;
+  p.key_value_heads = 1;
+  p.head_dim = 3;
+  p.rotary_dim = 2;
+  const int t = 3;
+  auto qg = Bf16Values(t * 12, .1f), k = Bf16Values(t * 3, 1.2f), v = Bf16Values(t * 3, 2.3f),
+       qw = Bf16Values(3, .2f), kw = Bf16Values(3, .4f), upstream = Bf16Values(t * 6, .7f);
+  auto qp = Parameter(ex, qw, true), kp = Parameter(ex, kw, true);
+  auto layer = QwenAttentionLayer::Create(ex, p, qp, kp, t);
+  CHECK(layer.ok());
+  BufferVec inputs = {UploadBf16(ex, qg), UploadBf16(ex, k), UploadBf16(ex, v)};
+  BufferVec dy = {Upload(ex, upstream.data(), upstream.size() * 4)};
+  auto fwd = (*layer)->fwd(ex, inputs);
+  CHECK(fwd.ok());
+  auto backward = (*layer)->bwd(ex, dy, fwd->state);
+  CHECK(backward.ok() && backward->size() == 3);
+  std::vector<float> dqg(qg.size()), dk(k.size()), dv(v.size()), dqw(3, 0.f), dkw(3, 0.f), y(t * 6);
+  CHECK(oracle_gqa_sequence_bwd(qg.data(), k.data(), v.data(), qw.data(), kw.data(), upstream.data(), t, 2, 1, 3, 2,
+                                p.rms_norm_epsilon, p.rope_theta, 1, dqg.data(), dk.data(), dv.data(), dqw.data(),
+                                dkw.data(), y.data()) == 0);
+  const std::vector<float>* wants[] = {&dqg, &dk, &dv};
+  std::vector<std::vector<float>> first;
+  for (int i = 0; i < 3; ++i) {
+    first.push_back(Download<float>(ex, (*backward)[i].data(), wants[i]->size()));
+    CHECK(MaxAbsDiff(first.back(), *wants[i]) <= 3e-5f);
+  }
+  auto got_qw = Download<float>(ex, qp->gradient().data(), 3), got_kw = Download<float>(ex, kp->gradient().data(), 3);
+  CHECK(MaxAbsDiff(got_qw, dqw) <= 3e-5f && MaxAbsDiff(got_kw, dkw) <= 3e-5f);
+  auto second = (*layer)->fwd(ex, inputs);
+  CHECK(second.ok());
+  auto repeated = (*layer)->bwd(ex, dy, second->state);
+  CHECK(repeated.ok());
+  for (int i = 0; i < 3; ++i) CHECK(Download<float>(ex, (*repeated)[i].data(), first[i].size()) == first[i]);
+  auto summed = Download<float>(ex, qp->gradient().data(), 3);
+  for (int i = 0; i < 3; ++i) CHECK(std::fabs(summed[i] - 2 * got_qw[i]) <= 1e-6f);
+  auto wrong = (*layer)->bwd(ex, {inputs[0]}, second->state);
+  CHECK(!wrong.ok() && wrong.status().code() == StatusCode::kInvalidArgument);
+  std::printf("ok QwenAttentionLayer backward\n");
+}
+
+// The reference's closed-form example (sequence_delta_net_test.cc:31-62).
+struct DeltaExample {
+  DeltaNetParameters p;
+  int length, channels;
+  std::vector<float> values[8], upstream;
+};
+static DeltaExample MakeDeltaExample(int length, int kh, int vh, int kd, int vd) {
+  DeltaExample e;
+  e.p = {kh, vh, kd, vd, 3, 0.03f, true};
+  e.length = length;
+  e.channels = 2 * kh * kd + vh * vd;
+  const int sizes[] = {length * e.channels, length * vh * vd, length * vh, length * vh, e.channels * 3, vh, vh, vd};
+  for (int tensor = 0; tensor < 8; ++tensor)
+    for (int i = 0; i < sizes[tensor]; ++i) {
+      float value = 0.15f + 0.4f * std::sin(0.37f * i + 0.41f * tensor);
+      if (tensor == 5) value -= 0.7f;
+      if (tensor == 7) value += 1.f;
+      e.values[tensor].push_back(tensor < 4 ? oracle_bf16_to_float(oracle_float_to_bf16(value)) : value);
+    }
+  e.upstream.assign(static_cast<size_t>(length) * vh * vd, 0.f);
+  for (int i = (length - 1) * vh * vd; i < length * vh * vd; ++i) e.upstream[i] = 0.4f * std::cos(0.2f * i);
+  return e;
+}
+
+// sequence_delta_net_test.cc:241-297 (forward, cached-token equivalence) and :299-373 (gradients).
+static void TestSequenceDeltaNet(cuda::Executor& ex, int length, int kh, int vh, int kd, int vd, bool gradients) {
+  const DeltaExample e = MakeDeltaExample(length, kh, vh, kd, vd);
+  std::shared_ptr<BlockParameter> parameters[4];
+  for (int i = 0; i < 4; ++i) parameters[i] = Parameter(ex, e.values[4 + i], gradients);
+  auto layer = SequenceDeltaNetLayer::Create(ex, e.p, parameters[0], parameters[1], parameters[2], parameters[3], length);
+  CHECK(layer.ok());
+  BufferVec inputs;
+  for (int i = 0; i < 4; ++i) inputs.push_back(UploadBf16(ex, e.values[i]));
+  auto result = (*layer)->fwd(ex, inputs);
+  CHECK(result.ok());
+  CHECK(result->state.intermediates.size() == SequenceDeltaNetLayer::kSavedBuffers);
+  const auto actual = DownloadBf16(ex, result->outputs[0]);
+  const int width = vh * vd;
+  std::vector<float> y(actual.size()), dqkv(e.values[0].size()), dz(e.values[1].size()), da(e.values[2].size()),
+      db(e.values[3].size()), dparam[4];
+  for (int i = 0; i < 4; ++i) dparam[i].assign(e.values[4 + i].size(), 0.f);
+  CHECK(oracle_gdn_sequence_bwd(e.values[0].data(), e.values[1].data(), e.values[2].data(), e.values[3].data(),
+                                e.values[4].data(), e.values[5].data(), e.values[6].data(), e.values[7].data(),
+                                e.upstream.data(), length, kh, vh, kd, vd, 3, 0.03f, 1, dqkv.data(), dz.data(),
+                                da.data(), db.data(), dparam[0].data(), dparam[1].data(), dparam[2].data(),
+                                dparam[3].data(), y.data()) == 0);
+  for (size_t i = 0; i < actual.size(); ++i) {
+    const float want = oracle_bf16_to_float(oracle_float_to_bf16(y[i]));
+    CHECK(std::fabs(actual[i] - want) <= 1.5e-4f + 0.015f * std::fabs(want) + 2e-3f * std::fabs(want));
+  }
+  // the single-token layer, fed the same tokens, agrees with the sequence layer
+  auto cached = DeltaNetLayer::Create(ex, e.p, parameters[0]->value(), parameters[1]->value(),
+                                      parameters[2]->value(), parameters[3]->value());
+  CHECK(cached.ok());
+  const int counts[] = {e.channels, width, vh, vh};
+  for (int t = 0; t < length; ++t) {
+    BufferVec token;
+    for (int i = 0; i < 4; ++i)
+      token.push_back(UploadBf16(ex, {e.values[i].begin() + t * counts[i], e.values[i].begin() + (t + 1) * counts[i]}));
+    auto step = (*cached)->fwd(ex, token);
+    CHECK(step.ok());
+    const auto one = DownloadBf16(ex, step->outputs[0]);
+    for (int i = 0; i < width; ++i)
+      CHECK(std::fabs(actual[static_cast<size_t>(t) * width + i] - one[i]) <= 1.5e-4f + 0.015f * std::fabs(one[i]));
+  }
+  CHECK_OK((*cached)->Reset());
+  CHECK((*cached)->bwd(ex, {}, BackwardState{cached->get(), {}, {}}).status().code() == StatusCode::kUnimplemented);
+  // a second sequence must not inherit state from the first
+  auto repeat = (*layer)->fwd(ex, inputs);
+  CHECK(repeat.ok() && DownloadBf16(ex, repeat->outputs[0]) == actual);
+  if (gradients) {
+    BufferVec dy = {Upload(ex, e.upstream.data(), e.upstream.size() * 4)};
+    auto backward = (*layer)->bwd(ex, dy, result->state);
+    CHECK(backward.ok() && backward->size() == 4);
+    const std::vector<float>* wants[] = {&dqkv, &dz, &da, &db};
+    auto close = [](const std::vector<float>& got, const std::vector<float>& want) {
+      for (size_t i = 0; i < want.size(); ++i)
+        if (std::fabs(got[i] - want[i]) > 3e-5f + 0.003f * std::fabs(want[i])) return false;
+      return true;
+    };
+    for (int i = 0; i < 4; ++i) CHECK(close(Download<float>(ex, (*backward)[i].data(), wants[i]->size()), *wants[i]));
+    for (int i = 0; i < 4; ++i)
+      CHECK(close(Download<float>(ex, parameters[i]->gradient().data(), dparam[i].size()), dparam[i]));
+  }
+  DeltaNetParameters bad = e.p;
+  bad.value_heads = vh + 1;   // not a multiple of the key heads (or a parameter size mismatch)
+  CHECK(!SequenceDeltaNetLayer::Create(ex, bad, parameters[0], parameters[1], parameters[2], parameters[3], length).ok());
+  std::printf("ok SequenceDeltaNetLayer + DeltaNetLayer (%d,%d,%d,%d,%d)%s\n", length, kh, vh, kd, vd,
+              gradients ? " with gradients" : "");
+}
+
 int main() {
   auto executor = cuda::Executor::Create();
   CHECK(executor.ok());
@@ -296,6 +536,13 @@ int main() {
     for (bool round : {false, true}) TestCachedAttention(ex, dim, round);
   for (int dim : {5, 128})
     for (bool round : {false, true}) TestDeltaNetState(ex, dim, round);
+  for (int d : {3, 256}) TestQwenAttentionForward(ex, d);
+  TestQwenAttentionBackward(ex);
+  TestSequenceDeltaNet(ex, 3, 1, 2, 3, 5, false);
+  TestSequenceDeltaNet(ex, 3, 2, 4, 5, 35, false);
+  TestSequenceDeltaNet(ex, 3, 16, 48, 128, 128, false);
+  TestSequenceDeltaNet(ex, 5, 1, 2, 3, 5, true);
+  TestSequenceDeltaNet(ex, 3, 2, 4, 5, 35, true);
   CHECK_OK(ex.Synchronize());
   std::printf("PASS %d checks\n", g_checks);
   return 0;
