@@ -421,7 +421,7 @@ static void TestQwenAttentionBackward(cuda::Executor& ex) {
   for (int i = 0; i < 3; ++i) CHECK(Download<float>(ex, (*repeated)[i].data(), first[i].size()) == first[i]);
   auto summed = Download<float>(ex, qp->gradient().data(), 3);
   for (int i = 0; i < 3; ++i) CHECK(std::fabs(summed[i] - 2 * got_qw[i]) <= 1e-6f);
-  auto wrong = (*layer)->bwd(ex, {inputs[0]}, second->state);
+  auto wrong = (*layer)->bwd(ex, {inputs[1]}, second->state);   // a buffer of the wrong size
   CHECK(!wrong.ok() && wrong.status().code() == StatusCode::kInvalidArgument);
   std::printf("ok QwenAttentionLayer backward\n");
 }
