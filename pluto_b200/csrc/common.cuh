@@ -279,6 +279,13 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool b_mn_m
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// The same with either operand MN-major: bit 15 = A major, bit 16 = B major (0 = K, 1 = MN).  An A
+// operand read from TMEM is always K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16_majors(int m, int n, bool a_mn_major,
+                                                              bool b_mn_major) {
+  return umma_idesc_bf16(m, n, b_mn_major) | (static_cast<uint32_t>(a_mn_major) << 15);
+}
+
 // ----------------------------------------------------------------------------------------------
 // small math helpers
 // ----------------------------------------------------------------------------------------------

@@ -28,8 +28,13 @@
 //                         ldmatrix is bank-conflict free.
 #include "common.cuh"
 #include "engine.h"
+#include "gdn_records.cuh"
 
 namespace pluto {
+// gdn_scan_sm100.cu
+size_t gdn_scan_smem_bytes();
+cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int chunks,
+                            uint32_t* status);
 namespace {
 
 constexpr int kC = 64;           // tokens per chunk
@@ -537,6 +542,75 @@ __global__ void __launch_bounds__(96) gdn_chunk_recurrence(GdnArgs a, const uint
     }
 }
 
+// -------------------------------------------------------------------------------------------
+// Rewrites a (sequence, head, chunk) record of gdn_chunk_prepare into the swizzled operand tiles
+// the tcgen05 scan kernel reads (gdn_records.cuh), computing the two chunk-local products that
+// take the dependent pair of state products off the sequential path:
+//     Pn = -(Kt^T W)   and   Qt = c.Q - M W.
+// grid (chunks, value heads, batch), 256 threads; plain fp32 arithmetic.
+// -------------------------------------------------------------------------------------------
+struct ConvertSmem {
+  __nv_bfloat16 w[kC][kDK + 2];
+  __nv_bfloat16 kt[kC][kDK + 2];
+  __nv_bfloat16 m[kC][kC + 2];
+};
+
+__global__ void __launch_bounds__(256) gdn_chunk_convert(const uint8_t* __restrict__ old_records,
+                                                         uint8_t* __restrict__ new_records, int chunks,
+                                                         int value_heads, int dv) {
+  extern __shared__ __align__(16) uint8_t convert_raw[];
+  ConvertSmem& s = *reinterpret_cast<ConvertSmem*>(convert_raw);
+  const size_t index = (static_cast<size_t>(blockIdx.z) * value_heads + blockIdx.y) * chunks + blockIdx.x;
+  const uint8_t* src = old_records + index * Record::bytes(dv);
+  uint8_t* dst = new_records + index * GdnRecord::bytes(dv);
+  const __nv_bfloat16* w_in = reinterpret_cast<const __nv_bfloat16*>(src + Record::kW);
+  const __nv_bfloat16* q_in = reinterpret_cast<const __nv_bfloat16*>(src + Record::kQ);
+  const __nv_bfloat16* k_in = reinterpret_cast<const __nv_bfloat16*>(src + Record::kK);
+  const __nv_bfloat16* m_in = reinterpret_cast<const __nv_bfloat16*>(src + Record::kM);
+  const float* u_in = reinterpret_cast<const float*>(src + Record::kU);
+  for (int e = threadIdx.x; e < kC * kDK; e += 256) {
+    const int t = e / kDK, i = e % kDK;
+    s.w[t][i] = w_in[t * kPitch + i];
+    const __nv_bfloat16 k = k_in[t * kPitch + i];
+    s.kt[t][i] = k;
+    *reinterpret_cast<__nv_bfloat16*>(dst + GdnRecord::kKT + gdn_swizzled_offset(kC, t, i)) = k;
+  }
+  for (int e = threadIdx.x; e < kC * kC; e += 256) {
+    const int t = e / kC, sc = e % kC;
+    const __nv_bfloat16 v = m_in[t * kMPitch + sc];
+    s.m[t][sc] = v;
+    *reinterpret_cast<__nv_bfloat16*>(dst + GdnRecord::kMM + gdn_swizzled_offset(kC, t, sc)) = v;
+  }
+  if (threadIdx.x == 0)
+    *reinterpret_cast<float*>(dst + GdnRecord::kGM) = *reinterpret_cast<const float*>(src + Record::gamma(dv));
+  __syncthreads();
+  // Pn[i_out][i_in] = -sum_t Kt[t][i_out] W[t][i_in]
+  for (int e = threadIdx.x; e < kDK * kDK; e += 256) {
+    const int io = e / kDK, ii = e % kDK;
+    float acc = 0.0f;
+    for (int t = 0; t < kC; ++t) acc = fmaf(__bfloat162float(s.kt[t][io]), __bfloat162float(s.w[t][ii]), acc);
+    *reinterpret_cast<__nv_bfloat16*>(dst + GdnRecord::kPN + gdn_swizzled_offset(kDK, io, ii)) =
+        __float2bfloat16_rn(-acc);
+  }
+  // Qt[t][i] = (c.Q)[t][i] - sum_s M[t][s] W[s][i]
+  for (int e = threadIdx.x; e < kC * kDK; e += 256) {
+    const int t = e / kDK, i = e % kDK;
+    float acc = __bfloat162float(q_in[t * kPitch + i]);
+    for (int sc = 0; sc < kC; ++sc) acc = fmaf(-__bfloat162float(s.m[t][sc]), __bfloat162float(s.w[sc][i]), acc);
+    *reinterpret_cast<__nv_bfloat16*>(dst + GdnRecord::kQT + gdn_swizzled_offset(kC, t, i)) = __float2bfloat16_rn(acc);
+  }
+  // U [token][value column] as high parts and remainders, one pair of tiles per 128-column slice
+  for (int e = threadIdx.x; e < kC * dv; e += 256) {
+    const int j = e / kC, t = e % kC;
+    const float u = u_in[static_cast<size_t>(j) * kUPitch + t];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(u);
+    uint8_t* tile = dst + GdnRecord::kCommon + static_cast<size_t>(j / kGdnSliceCols) * GdnRecord::kSlice;
+    const uint32_t off = gdn_swizzled_offset(kC, t, j % kGdnSliceCols);
+    *reinterpret_cast<__nv_bfloat16*>(tile + GdnRecord::kUH + off) = hi;
+    *reinterpret_cast<__nv_bfloat16*>(tile + GdnRecord::kUL + off) = __float2bfloat16_rn(u - __bfloat162float(hi));
+  }
+}
+
 }  // namespace
 
 bool gdn_chunked_supported(const GdnArgs& a) {
@@ -546,9 +620,20 @@ bool gdn_chunked_supported(const GdnArgs& a) {
          (reinterpret_cast<uintptr_t>(a.v) & 15u) == 0;
 }
 
+// Value widths that are whole 128-column slices take the tcgen05 scan kernel.
+static bool scan_on_tensor_memory(int value_dim) { return value_dim % kGdnSliceCols == 0; }
+
+static size_t old_record_bytes(int batch, int tokens, int value_heads, int value_dim) {
+  const size_t chunks = (static_cast<size_t>(tokens) + kC - 1) / kC;
+  return (static_cast<size_t>(batch) * value_heads * chunks * Record::bytes(value_dim) + 1023) / 1024 * 1024;
+}
+
 size_t gdn_chunked_workspace_bytes(int batch, int tokens, int value_heads, int value_dim) {
   const size_t chunks = (static_cast<size_t>(tokens) + kC - 1) / kC;
-  return static_cast<size_t>(batch) * value_heads * chunks * Record::bytes(value_dim);
+  size_t bytes = old_record_bytes(batch, tokens, value_heads, value_dim);
+  if (scan_on_tensor_memory(value_dim))
+    bytes += static_cast<size_t>(batch) * value_heads * chunks * GdnRecord::bytes(value_dim) + 1024;
+  return bytes;
 }
 
 cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, uint32_t* status) {
@@ -560,6 +645,18 @@ cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, 
       a, static_cast<uint8_t*>(workspace), chunks);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
+  if (scan_on_tensor_memory(a.value_dim)) {
+    uint8_t* base = static_cast<uint8_t*>(workspace) + old_record_bytes(a.batch, a.tokens, a.value_heads, a.value_dim);
+    uint8_t* records = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(base) + 1023) & ~static_cast<uintptr_t>(1023));
+    e = cudaFuncSetAttribute(gdn_chunk_convert, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(sizeof(ConvertSmem)));
+    if (e != cudaSuccess) return e;
+    gdn_chunk_convert<<<dim3(chunks, a.value_heads, a.batch), 256, sizeof(ConvertSmem), stream>>>(
+        static_cast<const uint8_t*>(workspace), records, chunks, a.value_heads, a.value_dim);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return gdn_scan_launch(stream, a, records, chunks, status);
+  }
   const size_t smem = kRecStages * kStageBytes + sizeof(RecBarriers);
   e = cudaFuncSetAttribute(gdn_chunk_recurrence, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem));

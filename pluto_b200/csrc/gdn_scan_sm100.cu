@@ -1,0 +1,289 @@
+// Chunked gated delta-net prefill on the 5th-generation tensor cores: the sequential part.
+//
+// Notation of gdn_chunked.cu (chunk of C = 64 tokens, chunk-start state S0 [dk x dv]):
+//     D = U - W S0,      O = (c.Q) S0 + M D,      S_C = gamma S0 + Kt^T D          (Kt = K . c_C/c)
+// Substituting D removes the dependent pair of products from the chain between chunks:
+//     S_C = gamma S0 + Kt^T U - (Kt^T W) S0  =  gamma S0 + Kt^T U + Pn S0,     Pn = -(Kt^T W)
+//     O   = (c.Q - M W) S0 + M U             =  Qt S0 + M U,                   Qt = c.Q - M W
+// Pn [dk x dk], Qt [C x dk], M, Kt and U depend only on the chunk's own tokens, so a prepare
+// kernel computes them for all chunks in parallel; what is left per chunk on the sequential path
+// is ONE product with the state plus a rescale by gamma.
+//
+// gdn_scan_sm100: one CTA per (sequence, head, slice of 128 value columns) walks the chunks.
+//   * The state lives in TMEM for the whole sequence, transposed: lane j = value column, 128 fp32
+//     columns = keys.  Each chunk the eight arithmetic warps read it (tcgen05.ld), write back
+//     gamma * S (tcgen05.st) and a bf16 copy of S (high part + remainder, so the product keeps
+//     16 mantissa bits) that the tensor core reads as its A operand straight from TMEM.
+//   * One elected thread issues, per chunk, tcgen05.mma M128 N128:  acc += U^T Kt  (A = U from
+//     shared memory, token-major as stored) and  acc += S_bf16^T Pn^T  (A from TMEM); then, off the
+//     chain, M128 N64:  O^T = S_bf16^T Qt^T + U^T M^T  into one of two TMEM output buffers that
+//     the arithmetic warps drain (round, store) while the next chunk's state product runs.
+//   * A producer thread streams the chunk records (already in the 128-byte-swizzled operand
+//     layout, so a record is two linear bulk copies) through a two-stage ring.
+// TMEM columns: state 0-127 | S_bf16 buffer 0: 128-255 | buffer 1: 256-383 | O^T 384-447, 448-511.
+// Every wait is bounded (common.cuh); on a time-out the kernel falls through to its exit path,
+// frees its TMEM and reports through the status word.
+#include "common.cuh"
+#include "engine.h"
+#include "gdn_records.cuh"
+
+namespace pluto {
+namespace {
+
+constexpr int kScanThreads = 320;     // warp 0 producer, warp 1 MMA issuer, warps 2-9 arithmetic
+constexpr int kScanStages = 2;
+constexpr uint32_t kStageBytes = GdnRecord::kCommon + GdnRecord::kSlice;   // 107520
+constexpr uint32_t kColState = 0, kColSbf = 128, kColOut = 384;
+// Which bf16 remainders enter the products (each costs its own MMAs on the tensor pipe).
+constexpr bool kStateLoInUpdate = true;    // S remainder in  acc += S Pn^T   (on the chain)
+constexpr bool kULoInUpdate = true;        // U remainder in  acc += U^T Kt   (on the chain)
+constexpr bool kStateLoInOutput = false;   // outputs are rounded to bf16 anyway
+constexpr bool kULoInOutput = false;
+
+struct ScanBarriers {
+  uint64_t full[kScanStages], empty[kScanStages];
+  uint64_t sbf_ready;     // 256 arrivals: the chunk's scaled state and its bf16 copy are in TMEM
+  uint64_t state_done;    // tcgen05.commit: the chunk's state products have landed
+  uint64_t out_done[2];   // tcgen05.commit: O^T of a chunk is complete
+  uint64_t out_free[2];   // 256 arrivals: the arithmetic warps have drained that buffer
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(kScanThreads, 1)
+gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint32_t* status) {
+  extern __shared__ uint8_t scan_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(scan_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  ScanBarriers* bar = reinterpret_cast<ScanBarriers*>(smem + kScanStages * kStageBytes);
+  const int slice = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  const int dv = a.value_dim;
+  const size_t record_bytes = GdnRecord::bytes(dv);
+  const uint8_t* rec0 = records + (static_cast<size_t>(b) * a.value_heads + h) * chunks * record_bytes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kScanStages; ++s) {
+      mbar_init(&bar->full[s], 1);
+      mbar_init(&bar->empty[s], 1);
+    }
+    mbar_init(&bar->sbf_ready, 256);
+    mbar_init(&bar->state_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar->out_done[s], 1);
+      mbar_init(&bar->out_free[s], 256);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ record producer
+    if (lane == 0) {
+      bool ok = true;
+      for (int c = 0; c < chunks && ok; ++c) {
+        const int st = c % kScanStages, use = c / kScanStages;
+        if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, status, 50);
+        if (!ok) break;
+        uint8_t* dst = smem + st * kStageBytes;
+        const uint8_t* rec = rec0 + static_cast<size_t>(c) * record_bytes;
+        mbar_expect_tx(&bar->full[st], kStageBytes);
+        bulk_load(dst, rec, GdnRecord::kCommon, &bar->full[st]);
+        bulk_load(dst + GdnRecord::kCommon, rec + GdnRecord::kCommon + static_cast<size_t>(slice) * GdnRecord::kSlice,
+                  GdnRecord::kSlice, &bar->full[st]);
+      }
+      // nothing may still be writing this CTA's shared memory when it exits
+      for (int c = max(0, chunks - kScanStages); c < chunks; ++c)
+        mbar_wait(&bar->full[c % kScanStages], (c / kScanStages) & 1, status, 51);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t kIdescUpdU = umma_idesc_bf16_majors(128, 128, true, true);    // U^T Kt
+    constexpr uint32_t kIdescUpdS = umma_idesc_bf16_majors(128, 128, false, false);  // S Pn^T
+    constexpr uint32_t kIdescOutS = umma_idesc_bf16_majors(128, 64, false, false);   // S Qt^T
+    constexpr uint32_t kIdescOutU = umma_idesc_bf16_majors(128, 64, true, false);    // U^T M^T
+    bool ok = true;
+    for (int c = 0; c < chunks && ok; ++c) {
+      const int st = c % kScanStages, buf = c & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->full[st], (c / kScanStages) & 1, status, 52));
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->sbf_ready, c & 1, status, 53));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t base = smem_u32(smem + st * kStageBytes);
+      const uint32_t sbf_hi = tmem + kColSbf + buf * 128, sbf_lo = sbf_hi + 64;
+      // token-major tiles (MN-major operands): 64-column slabs 8192 bytes apart, 16 tokens = 2048 bytes
+      const uint64_t uh = umma_desc_sw128(base + GdnRecord::kCommon + GdnRecord::kUH, 8192, 1024);
+      const uint64_t ul = umma_desc_sw128(base + GdnRecord::kCommon + GdnRecord::kUL, 8192, 1024);
+      const uint64_t kt = umma_desc_sw128(base + GdnRecord::kKT, 8192, 1024);
+      // K-major tiles: a K step of 16 elements is 32 bytes along the row, 64-element slabs apart
+      const uint64_t pn = umma_desc_sw128(base + GdnRecord::kPN, 16, 1024);
+      const uint64_t qt = umma_desc_sw128(base + GdnRecord::kQT, 16, 1024);
+      const uint64_t mm = umma_desc_sw128(base + GdnRecord::kMM, 16, 1024);
+      if (elect_one()) {
+        // state: acc (= gamma S) += U^T Kt + S Pn^T
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + kColState, uh + ks * 128, kt + ks * 128, kIdescUpdU, true);
+        if (kULoInUpdate) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ss(tmem + kColState, ul + ks * 128, kt + ks * 128, kIdescUpdU, true);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + kColState, sbf_hi + ks * 8, pn + (((ks / 4) * 16384 + (ks % 4) * 32) >> 4),
+                  kIdescUpdS, true);
+        if (kStateLoInUpdate) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts(tmem + kColState, sbf_lo + ks * 8, pn + (((ks / 4) * 16384 + (ks % 4) * 32) >> 4),
+                    kIdescUpdS, true);
+        }
+        tc_commit(&bar->state_done);
+      }
+      __syncwarp();
+      if (c >= 2) {   // the arithmetic warps have drained this output buffer's previous chunk
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->out_free[buf], ((c >> 1) - 1) & 1, status, 54));
+        if (!ok) break;
+        tc_fence_after();
+      }
+      if (elect_one()) {
+        const uint32_t out = tmem + kColOut + buf * 64;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(out, sbf_hi + ks * 8, qt + (((ks / 4) * 8192 + (ks % 4) * 32) >> 4), kIdescOutS, ks > 0);
+        if (kStateLoInOutput) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts(out, sbf_lo + ks * 8, qt + (((ks / 4) * 8192 + (ks % 4) * 32) >> 4), kIdescOutS, true);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) umma_ss(out, uh + ks * 128, mm + ks * 2, kIdescOutU, true);
+        if (kULoInOutput) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) umma_ss(out, ul + ks * 128, mm + ks * 2, kIdescOutU, true);
+        }
+        tc_commit(&bar->out_done[buf]);
+        tc_commit(&bar->empty[st]);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ arithmetic warps
+    const int quarter = warp & 3;                 // the TMEM lanes this warp may touch
+    const int half = (warp - 2) / 4;              // its half of the columns
+    const int j = slice * 128 + quarter * 32 + lane;   // value column == TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    float* state = a.state + (static_cast<size_t>(b) * a.value_heads + h) * kGdnKeyDim * dv + j;
+    {
+      // chunk-start state of the sequence: keys half*64 .. +63 of this value column
+      uint32_t s0[2][32];
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          s0[g][i] = __float_as_uint(state[static_cast<size_t>(half * 64 + g * 32 + i) * dv]);
+      tmem_st32(tmem + lane_base + kColState + half * 64, s0[0]);
+      tmem_st32(tmem + lane_base + kColState + half * 64 + 32, s0[1]);
+      tmem_wait_st();
+    }
+    auto drain_output = [&](int e) -> bool {
+      const int buf = e & 1;
+      if (!mbar_wait(&bar->out_done[buf], (e >> 1) & 1, status, 55)) return false;
+      tc_fence_after();
+      uint32_t o[32];
+      tmem_ld32(tmem + lane_base + kColOut + buf * 64 + half * 32, o);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&bar->out_free[buf]);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int t = e * kGdnChunk + half * 32 + i;
+        if (t < a.tokens) {
+          const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv + j;
+          const float value = a.round ? bf16_round(__uint_as_float(o[i])) : __uint_as_float(o[i]);
+          if (a.out_is_bf16) static_cast<__nv_bfloat16*>(a.out)[off] = __float2bfloat16_rn(value);
+          else static_cast<float*>(a.out)[off] = value;
+        }
+      }
+      return true;
+    };
+    bool ok = true;
+    for (int c = 0; c < chunks && ok; ++c) {
+      const int st = c % kScanStages, buf = c & 1;
+      if (c > 0) ok = mbar_wait(&bar->state_done, (c - 1) & 1, status, 56);
+      if (ok) ok = mbar_wait(&bar->full[st], (c / kScanStages) & 1, status, 57);   // gamma is in the record
+      if (!ok) break;
+      tc_fence_after();
+      const float gamma = *reinterpret_cast<const float*>(smem + st * kStageBytes + GdnRecord::kGM);
+      uint32_t s[2][32], hi[32], lo[32];
+      tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
+      tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
+      tmem_wait_ld();
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float x = __uint_as_float(s[g][i]), y = __uint_as_float(s[g][i + 1]);
+          const uint32_t top = pack_bf16(x, y);
+          hi[g * 16 + i / 2] = top;
+          lo[g * 16 + i / 2] = pack_bf16(x - bf16_lo(top), y - bf16_hi(top));
+          s[g][i] = __float_as_uint(x * gamma);
+          s[g][i + 1] = __float_as_uint(y * gamma);
+        }
+      // bf16 pairs: 64 keys of this half = 32 packed columns
+      tmem_st32(tmem + lane_base + kColSbf + buf * 128 + half * 32, hi);
+      tmem_st32(tmem + lane_base + kColSbf + buf * 128 + 64 + half * 32, lo);
+      tmem_st32(tmem + lane_base + kColState + half * 64, s[0]);
+      tmem_st32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->sbf_ready);
+      if (c > 0) ok = drain_output(c - 1);
+    }
+    if (ok) ok = mbar_wait(&bar->state_done, (chunks - 1) & 1, status, 58);
+    if (ok) {
+      tc_fence_after();
+      uint32_t s[2][32];
+      tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
+      tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
+      tmem_wait_ld();
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          state[static_cast<size_t>(half * 64 + g * 32 + i) * dv] = __uint_as_float(s[g][i]);
+      drain_output(chunks - 1);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace
+
+size_t gdn_scan_smem_bytes() { return 1024 + kScanStages * kStageBytes + sizeof(ScanBarriers); }
+
+cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int chunks,
+                            uint32_t* status) {
+  const size_t smem = gdn_scan_smem_bytes();
+  cudaError_t e = cudaFuncSetAttribute(gdn_scan_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  gdn_scan_sm100<<<dim3(a.value_dim / 128, a.value_heads, a.batch), kScanThreads, smem, stream>>>(
+      a, static_cast<const uint8_t*>(records), chunks, status);
+  return cudaGetLastError();
+}
+
+}  // namespace pluto
