@@ -35,6 +35,10 @@ namespace pluto {
 size_t gdn_scan_smem_bytes();
 cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int chunks,
                             uint32_t* status);
+// gdn_prepare_sm100.cu
+bool gdn_prepare_sm100_supported(const GdnArgs& a);
+cudaError_t gdn_prepare_sm100_launch(cudaStream_t stream, const GdnArgs& a, void* records, int chunks,
+                                     uint32_t* status);
 namespace {
 
 constexpr int kC = 64;           // tokens per chunk
@@ -628,16 +632,27 @@ static size_t old_record_bytes(int batch, int tokens, int value_heads, int value
   return (static_cast<size_t>(batch) * value_heads * chunks * Record::bytes(value_dim) + 1023) / 1024 * 1024;
 }
 
+// One 128-column slice: both kernels are tcgen05 and only the swizzled records exist.  Several
+// slices: the mma.sync prepare writes its records, a conversion kernel rewrites them, tcgen05 scan.
+// Other widths: the mma.sync pair of kernels.
 size_t gdn_chunked_workspace_bytes(int batch, int tokens, int value_heads, int value_dim) {
   const size_t chunks = (static_cast<size_t>(tokens) + kC - 1) / kC;
+  const size_t swizzled = static_cast<size_t>(batch) * value_heads * chunks * GdnRecord::bytes(value_dim) + 1024;
+  if (value_dim == kGdnSliceCols) return swizzled;
   size_t bytes = old_record_bytes(batch, tokens, value_heads, value_dim);
-  if (scan_on_tensor_memory(value_dim))
-    bytes += static_cast<size_t>(batch) * value_heads * chunks * GdnRecord::bytes(value_dim) + 1024;
+  if (scan_on_tensor_memory(value_dim)) bytes += swizzled;
   return bytes;
 }
 
 cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, uint32_t* status) {
   const int chunks = (a.tokens + kC - 1) / kC;
+  if (gdn_prepare_sm100_supported(a)) {
+    uint8_t* records = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(workspace) + 1023) &
+                                                  ~static_cast<uintptr_t>(1023));
+    cudaError_t launched = gdn_prepare_sm100_launch(stream, a, records, chunks, status);
+    if (launched != cudaSuccess) return launched;
+    return gdn_scan_launch(stream, a, records, chunks, status);
+  }
   cudaError_t e = cudaFuncSetAttribute(gdn_chunk_prepare, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(PrepareSmem)));
   if (e != cudaSuccess) return e;

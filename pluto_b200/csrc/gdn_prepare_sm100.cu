@@ -1,0 +1,466 @@
+// Chunked gated delta-net prefill on the 5th-generation tensor cores: the chunk-parallel part.
+//
+// For every chunk of 64 tokens (notation of gdn_chunked.cu; b_t = running sum of log decay inside
+// the chunk, c_t = e^{b_t}, k^, q^ the normalised key / scaled query):
+//     A[t,s] = beta_t e^{b_t-b_s} (k^_t.k^_s)  (s < t),   T = (I + A)^-1
+//     M[t,s] = e^{b_t-b_s} (q^_t.k^_s)         (s <= t)
+//     W = T (beta c k^),   U = T (beta v),   Kt = k^ . c_C/c
+//     Pn = -(Kt^T W),      Qt = c q^ - M W
+// and the record of gdn_records.cuh (Pn, Kt, Qt, M, gamma = c_C, U) goes to the scan kernel.
+//
+// One CTA takes TWO consecutive chunks of a (sequence, head): 128 tokens = the 128 rows of a
+// tcgen05.mma tile = the 128 lanes of TMEM, so every product below is a full M128 instruction and
+// every thread owns one token row from the raw scores to the records (two threads per row, one per
+// half of the columns):
+//   * raw q, k, v tiles arrive by TMA straight from the activations (128-byte swizzle, zero fill
+//     past the sequence end); no register staging, no normalised copies: the row scalings (norms,
+//     decays, beta) are applied to the small matrices instead of the 128-wide operands;
+//   * K K^T and Q K^T for both chunks in two M128 N128 K128 products (the cross-chunk blocks are
+//     ignored); the key norms are the diagonal of K K^T;
+//   * (I + A)^-1 in fp32 on the CUDA cores from shared memory;
+//   * W = (T . col-scale) K and U = (T . beta) V as block-diagonal products: the A tiles are laid
+//     out [T_a][zero block][T_b] so that "rows 0-63 = T_a, rest zero" and "rows 64-127 = T_b, rest
+//     zero" are two overlapping 128-row views sharing the zero block; U's T enters as bf16 high
+//     part plus remainder;
+//   * Pn (per chunk) and M W from the bf16 W written back to shared memory, then the records are
+//     written from registers in the swizzled operand order (16-byte pieces, 128 contiguous bytes
+//     per row and slab).
+// TMEM columns: K K^T 0-127 | Q K^T 128-255 | W 256-383 | U 384-511, then Pn(a) 0-127 |
+// Pn(b) 128-255 | M W 256-383.
+#include "common.cuh"
+#include "engine.h"
+#include "gdn_records.cuh"
+
+namespace pluto {
+namespace {
+
+constexpr int kPrepThreads = 256;
+constexpr float kMinLogDecay = -60.0f;
+constexpr bool kULoFromT = true;   // U = (T_hi + T_lo)(beta v): the remainder costs 8 more MMAs
+
+// shared-memory regions, byte offsets from the 1024-aligned base
+constexpr uint32_t kRegK = 0;          // raw keys [128 tokens][128]: 2 slabs x 16384   -> Kt in place
+constexpr uint32_t kRegQ = 32768;      // raw queries                                   -> fp32 scratch [128][64]
+constexpr uint32_t kRegV = 65536;      // raw values                                    -> W (bf16)
+constexpr uint32_t kRegT1 = 98304;     // T . (beta c kn)        [T_a 8192][zero 8192][T_b 8192]
+constexpr uint32_t kRegT2H = 122880;   // T . beta, high parts
+constexpr uint32_t kRegT2L = 147456;   // T . beta, remainders
+constexpr uint32_t kRegM = 172032;     // M                      same three-block layout
+constexpr uint32_t kRegSmall = 196608;
+
+struct PrepSmall {
+  float b[128], beta[128], kn[128], scale1[128], qsq[2][128];
+  uint64_t loaded, mma_done;
+  uint32_t tmem_base;
+};
+
+// scratch element (row, s) of the fp32 [128][64] matrix; the low five column bits are XORed with
+// the row so that a warp touching one column of 32 consecutive rows hits 32 banks
+__device__ __forceinline__ int scratch_index(int row, int s) {
+  return row * 64 + ((s & 32) | ((s ^ row) & 31));
+}
+
+__global__ void __launch_bounds__(kPrepThreads, 1)
+gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, GdnArgs a, uint8_t* __restrict__ records,
+                  int chunks, uint32_t* status) {
+  extern __shared__ uint8_t prep_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(prep_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  PrepSmall& sm = *reinterpret_cast<PrepSmall*>(smem + kRegSmall);
+  float* scratch = reinterpret_cast<float*>(smem + kRegQ);
+  const int pair = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kh = h / (a.value_heads / a.key_heads);
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  const int quarter = warp & 3, half = warp >> 2;     // TMEM lane quarter; column half of the row
+  const int r = quarter * 32 + lane;                  // token row of the pair == TMEM lane
+  const int cb = r >> 6, rl = r & 63;                 // chunk of the pair, row inside the chunk
+  const int t0 = pair * 128;
+  const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+  const int dv = a.value_dim;
+  const int chunk = pair * 2 + cb;
+  uint8_t* rec = records + ((static_cast<size_t>(b) * a.value_heads + h) * chunks + chunk) * GdnRecord::bytes(dv);
+  const bool live_chunk = chunk < chunks;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.loaded, 1);
+    mbar_init(&sm.mma_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  // the zero blocks shared by the two 128-row views of every three-block tile
+  for (int i = threadIdx.x; i < 4 * 512; i += kPrepThreads) {
+    const uint32_t region = i / 512 == 0 ? kRegT1 : (i / 512 == 1 ? kRegT2H : (i / 512 == 2 ? kRegT2L : kRegM));
+    *reinterpret_cast<uint4*>(smem + region + 8192 + (i % 512) * 16) = make_uint4(0, 0, 0, 0);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    mbar_expect_tx(&sm.loaded, 3 * 32768);
+    for (int s = 0; s < 2; ++s) {
+      tma_load_3d(smem + kRegK + s * 16384, &map_k, kh * kGdnKeyDim + s * 64, t0, b, &sm.loaded);
+      tma_load_3d(smem + kRegQ + s * 16384, &map_q, kh * kGdnKeyDim + s * 64, t0, b, &sm.loaded);
+      tma_load_3d(smem + kRegV + s * 16384, &map_v, h * dv + s * 64, t0, b, &sm.loaded);
+    }
+  }
+  // ---- gates: running sum of log decay inside each chunk (past the sequence end: g = 1, beta = 0)
+  float run = 0.0f, be = 0.0f;
+  if (half == 0) {
+    const int t = t0 + r;
+    if (t < a.tokens) {
+      const size_t off = (static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h;
+      run = fmaxf(logf(a.g[off]), kMinLogDecay);
+      be = a.beta[off];
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, run, o);
+      if (lane >= o) run += v;
+    }
+    if (lane == 31) sm.kn[quarter] = run;   // (kn is free until the key norms are known)
+  }
+  __syncthreads();
+  if (half == 0) {
+    if (quarter & 1) run += sm.kn[quarter - 1];
+    sm.b[r] = run;
+    sm.beta[r] = be;
+  }
+  __syncthreads();
+
+  // ---- raw scores on the tensor cores; meanwhile every thread takes its half of its query row
+  bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.loaded, 0, status, 60));
+  constexpr uint32_t kIdescKK = umma_idesc_bf16_majors(128, 128, false, false);
+  constexpr uint32_t kIdescTB = umma_idesc_bf16_majors(128, 128, false, true);    // K-major A, token-major B
+  constexpr uint32_t kIdescTT = umma_idesc_bf16_majors(128, 128, true, true);     // both token-major
+  const uint32_t base = smem_u32(smem);
+  if (warp == 0 && ok) {
+    if (elect_one()) {
+      const uint64_t kd = umma_desc_sw128(base + kRegK, 16, 1024), qd = umma_desc_sw128(base + kRegQ, 16, 1024);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t off = ((ks / 4) * 16384 + (ks % 4) * 32) >> 4;
+        umma_ss(tmem + 0, kd + off, kd + off, kIdescKK, ks > 0);
+      }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t off = ((ks / 4) * 16384 + (ks % 4) * 32) >> 4;
+        umma_ss(tmem + 128, qd + off, kd + off, kIdescKK, ks > 0);
+      }
+      tc_commit(&sm.mma_done);
+    }
+    __syncwarp();
+  }
+  uint32_t qrow[32];   // this thread's 64 query elements (bf16 pairs), kept for Qt
+  {
+    const uint8_t* row = smem + kRegQ + half * 16384 + r * 128;
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 v = *reinterpret_cast<const uint4*>(row + ((c ^ (r & 7)) * 16));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        qrow[c * 4 + e] = w[e];
+        ss += bf16_lo(w[e]) * bf16_lo(w[e]) + bf16_hi(w[e]) * bf16_hi(w[e]);
+      }
+    }
+    sm.qsq[half][r] = ss;
+  }
+  __syncthreads();
+  const float qn = a.normalize_qk
+                       ? rsqrtf(sm.qsq[0][r] + sm.qsq[1][r] + 1e-6f) / sqrtf(static_cast<float>(kGdnKeyDim))
+                       : a.q_scale;
+
+  ok = __all_sync(0xffffffffu, ok && mbar_wait(&sm.mma_done, 0, status, 61));
+  tc_fence_after();
+  uint32_t kk[32], qk[32];
+  if (ok) {
+    tmem_ld32(tmem + lane_base + 0 + cb * 64 + half * 32, kk);
+    tmem_ld32(tmem + lane_base + 128 + cb * 64 + half * 32, qk);
+    tmem_wait_ld();
+    if ((rl >> 5) == half)   // the diagonal of K K^T is |k|^2
+      sm.kn[r] = a.normalize_qk ? rsqrtf(__uint_as_float(kk[rl & 31]) + 1e-6f) : 1.0f;
+  }
+  __syncthreads();
+  const float br = sm.b[r], betar = sm.beta[r], knr = sm.kn[r];
+  if (half == 0) sm.scale1[r] = betar * __expf(br) * knr;
+  if (ok) {
+    // ---- A (fp32, to the scratch) and M (bf16, to its operand tile) for this thread's 32 columns
+    uint32_t mrow[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float mv[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int s = half * 32 + i + e, sg = cb * 64 + s;
+        const float ratio = s <= rl ? __expf(br - sm.b[sg]) : 0.0f;
+        const float kns = sm.kn[sg];
+        scratch[scratch_index(r, s)] = s < rl ? betar * ratio * knr * kns * __uint_as_float(kk[i + e]) : 0.0f;
+        mv[e] = ratio * qn * kns * __uint_as_float(qk[i + e]);
+      }
+      mrow[i / 2] = pack_bf16(mv[0], mv[1]);
+    }
+    uint8_t* mtile = smem + kRegM + r * 128 + (cb ? 8192 : 0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      *reinterpret_cast<uint4*>(mtile + (((half * 4 + q) ^ (r & 7)) * 16)) =
+          make_uint4(mrow[4 * q], mrow[4 * q + 1], mrow[4 * q + 2], mrow[4 * q + 3]);
+  }
+  __syncthreads();
+
+  // ---- T = (I + A)^-1 by forward substitution: one thread per (chunk, column)
+  {
+    float col[64];
+    const int c2 = threadIdx.x >> 6, jj = threadIdx.x & 63;
+    if (threadIdx.x < 128) {
+#pragma unroll
+      for (int t = 0; t < 64; ++t) {
+        float acc = t == jj ? 1.0f : 0.0f;
+#pragma unroll
+        for (int sc = 0; sc < t; ++sc) acc = fmaf(-scratch[scratch_index(c2 * 64 + t, sc)], col[sc], acc);
+        col[t] = acc;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
+#pragma unroll
+      for (int t = 0; t < 64; ++t) scratch[scratch_index(c2 * 64 + t, jj)] = col[t];
+    }
+  }
+  __syncthreads();
+
+  // ---- T . column scales -> bf16 operand tiles
+  {
+    uint32_t t1[16], t2h[16], t2l[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float x1[2], x2[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int s = half * 32 + i + e, sg = cb * 64 + s;
+        const float tv = scratch[scratch_index(r, s)];
+        x1[e] = tv * sm.scale1[sg];
+        x2[e] = tv * sm.beta[sg];
+      }
+      t1[i / 2] = pack_bf16(x1[0], x1[1]);
+      t2h[i / 2] = pack_bf16(x2[0], x2[1]);
+      t2l[i / 2] = pack_bf16(x2[0] - bf16_lo(t2h[i / 2]), x2[1] - bf16_hi(t2h[i / 2]));
+    }
+    const uint32_t row_off = r * 128 + (cb ? 8192 : 0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t piece = ((half * 4 + q) ^ (r & 7)) * 16;
+      *reinterpret_cast<uint4*>(smem + kRegT1 + row_off + piece) =
+          make_uint4(t1[4 * q], t1[4 * q + 1], t1[4 * q + 2], t1[4 * q + 3]);
+      *reinterpret_cast<uint4*>(smem + kRegT2H + row_off + piece) =
+          make_uint4(t2h[4 * q], t2h[4 * q + 1], t2h[4 * q + 2], t2h[4 * q + 3]);
+      *reinterpret_cast<uint4*>(smem + kRegT2L + row_off + piece) =
+          make_uint4(t2l[4 * q], t2l[4 * q + 1], t2l[4 * q + 2], t2l[4 * q + 3]);
+    }
+  }
+  fence_proxy_async();
+  __syncthreads();
+
+  // ---- W = (T . scale1) K and U = (T . beta) V, each chunk through its 128-row view
+  if (warp == 0 && ok) {
+    if (elect_one()) {
+#pragma unroll
+      for (int view = 0; view < 2; ++view) {
+        const uint64_t t1d = umma_desc_sw128(base + kRegT1 + view * 8192, 16, 1024);
+        const uint64_t kd = umma_desc_sw128(base + kRegK + view * 8192, 16384, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + 256, t1d + ks * 2, kd + ks * 128, kIdescTB, view > 0 || ks > 0);
+      }
+#pragma unroll
+      for (int part = 0; part < (kULoFromT ? 2 : 1); ++part)
+#pragma unroll
+        for (int view = 0; view < 2; ++view) {
+          const uint64_t t2d = umma_desc_sw128(base + (part ? kRegT2L : kRegT2H) + view * 8192, 16, 1024);
+          const uint64_t vd = umma_desc_sw128(base + kRegV + view * 8192, 16384, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ss(tmem + 384, t2d + ks * 2, vd + ks * 128, kIdescTB, part > 0 || view > 0 || ks > 0);
+        }
+      tc_commit(&sm.mma_done);
+    }
+    __syncwarp();
+  }
+  ok = __all_sync(0xffffffffu, ok && mbar_wait(&sm.mma_done, 1, status, 62));
+  tc_fence_after();
+  const float tail = __expf(sm.b[cb * 64 + 63] - br) * knr;   // Kt = k . (c_C / c) . kn
+  if (ok) {
+    // W row -> bf16 operand tile (over the raw values, which the U products no longer need)
+    uint32_t x[2][32];
+    tmem_ld32(tmem + lane_base + 256 + half * 64, x[0]);
+    tmem_ld32(tmem + lane_base + 256 + half * 64 + 32, x[1]);
+    tmem_wait_ld();
+    uint8_t* wrow = smem + kRegV + half * 16384 + r * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = c * 8 + e * 2;
+        w[e] = pack_bf16(__uint_as_float(x[i / 32][i % 32]), __uint_as_float(x[i / 32][i % 32 + 1]));
+      }
+      *reinterpret_cast<uint4*>(wrow + ((c ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // U row -> record (high parts and remainders), straight from registers
+    tmem_ld32(tmem + lane_base + 384 + half * 64, x[0]);
+    tmem_ld32(tmem + lane_base + 384 + half * 64 + 32, x[1]);
+    tmem_wait_ld();
+    if (live_chunk) {
+      uint8_t* urow = rec + GdnRecord::kCommon + half * 8192 + rl * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = c * 8 + e * 2;
+          const float u0 = __uint_as_float(x[i / 32][i % 32]), u1 = __uint_as_float(x[i / 32][i % 32 + 1]);
+          hi[e] = pack_bf16(u0, u1);
+          lo[e] = pack_bf16(u0 - bf16_lo(hi[e]), u1 - bf16_hi(hi[e]));
+        }
+        const uint32_t piece = (c ^ (rl & 7)) * 16;
+        *reinterpret_cast<uint4*>(urow + GdnRecord::kUH + piece) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(urow + GdnRecord::kUL + piece) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      }
+    }
+    // Kt row: scaled keys, in place (operand of Pn) and to the record
+    uint8_t* krow = smem + kRegK + half * 16384 + r * 128;
+    uint8_t* kt_out = rec + GdnRecord::kKT + half * 8192 + rl * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint32_t piece = (c ^ (r & 7)) * 16;
+      uint4 v = *reinterpret_cast<const uint4*>(krow + piece);
+      v.x = pack_bf16(bf16_lo(v.x) * tail, bf16_hi(v.x) * tail);
+      v.y = pack_bf16(bf16_lo(v.y) * tail, bf16_hi(v.y) * tail);
+      v.z = pack_bf16(bf16_lo(v.z) * tail, bf16_hi(v.z) * tail);
+      v.w = pack_bf16(bf16_lo(v.w) * tail, bf16_hi(v.w) * tail);
+      *reinterpret_cast<uint4*>(krow + piece) = v;
+      if (live_chunk) *reinterpret_cast<uint4*>(kt_out + piece) = v;
+    }
+  }
+  tc_fence_before();
+  fence_proxy_async();
+  __syncthreads();
+  tc_fence_after();
+
+  // ---- Pn(chunk) = Kt^T W over the chunk's 64 tokens; M W through the two views of M
+  if (warp == 0 && ok) {
+    if (elect_one()) {
+#pragma unroll
+      for (int view = 0; view < 2; ++view) {
+        const uint64_t ktd = umma_desc_sw128(base + kRegK + view * 8192, 16384, 1024);
+        const uint64_t wd = umma_desc_sw128(base + kRegV + view * 8192, 16384, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + view * 128, ktd + ks * 128, wd + ks * 128, kIdescTT, ks > 0);
+      }
+#pragma unroll
+      for (int view = 0; view < 2; ++view) {
+        const uint64_t md = umma_desc_sw128(base + kRegM + view * 8192, 16, 1024);
+        const uint64_t wd = umma_desc_sw128(base + kRegV + view * 8192, 16384, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + 256, md + ks * 2, wd + ks * 128, kIdescTB, view > 0 || ks > 0);
+      }
+      tc_commit(&sm.mma_done);
+    }
+    __syncwarp();
+  }
+  ok = __all_sync(0xffffffffu, ok && mbar_wait(&sm.mma_done, 0, status, 63));
+  tc_fence_after();
+  if (ok) {
+    uint32_t x[2][32];
+    // Pn rows: row r = key index of the output, this thread's 64 input keys, for both chunks
+#pragma unroll
+    for (int view = 0; view < 2; ++view) {
+      tmem_ld32(tmem + lane_base + view * 128 + half * 64, x[0]);
+      tmem_ld32(tmem + lane_base + view * 128 + half * 64 + 32, x[1]);
+      tmem_wait_ld();
+      if (pair * 2 + view < chunks) {
+        uint8_t* prow = records +
+                        ((static_cast<size_t>(b) * a.value_heads + h) * chunks + pair * 2 + view) * GdnRecord::bytes(dv) +
+                        GdnRecord::kPN + half * 16384 + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = c * 8 + e * 2;
+            w[e] = pack_bf16(-__uint_as_float(x[i / 32][i % 32]), -__uint_as_float(x[i / 32][i % 32 + 1]));
+          }
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+    // Qt = c q^ - M W
+    tmem_ld32(tmem + lane_base + 256 + half * 64, x[0]);
+    tmem_ld32(tmem + lane_base + 256 + half * 64 + 32, x[1]);
+    tmem_wait_ld();
+    if (live_chunk) {
+      const float cq = __expf(br) * qn;
+      uint8_t* qrow_out = rec + GdnRecord::kQT + half * 8192 + rl * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = c * 8 + e * 2;
+          const uint32_t q2 = qrow[c * 4 + e];
+          w[e] = pack_bf16(cq * bf16_lo(q2) - __uint_as_float(x[i / 32][i % 32]),
+                           cq * bf16_hi(q2) - __uint_as_float(x[i / 32][i % 32 + 1]));
+        }
+        *reinterpret_cast<uint4*>(qrow_out + ((c ^ (rl & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      // M row: already in operand order in shared memory
+      const uint8_t* mtile = smem + kRegM + r * 128 + (cb ? 8192 : 0);
+      uint8_t* m_out = rec + GdnRecord::kMM + rl * 128;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t piece = ((half * 4 + q) ^ (r & 7)) * 16;
+        *reinterpret_cast<uint4*>(m_out + piece) = *reinterpret_cast<const uint4*>(mtile + piece);
+      }
+      if (rl == 63 && half == 0) *reinterpret_cast<float*>(rec + GdnRecord::kGM) = __expf(br);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace
+
+bool gdn_prepare_sm100_supported(const GdnArgs& a) { return a.value_dim == kGdnSliceCols; }
+
+cudaError_t gdn_prepare_sm100_launch(cudaStream_t stream, const GdnArgs& a, void* records, int chunks,
+                                     uint32_t* status) {
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_token_map(&map_q, a.q, a.key_heads * kGdnKeyDim, a.tokens, a.batch, a.qk_token, 128) ||
+      !make_token_map(&map_k, a.k, a.key_heads * kGdnKeyDim, a.tokens, a.batch, a.qk_token, 128) ||
+      !make_token_map(&map_v, a.v, a.value_heads * a.value_dim, a.tokens, a.batch, a.v_token, 128))
+    return cudaErrorInvalidValue;
+  const size_t smem = 1024 + kRegSmall + sizeof(PrepSmall);
+  cudaError_t e = cudaFuncSetAttribute(gdn_prepare_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  gdn_prepare_sm100<<<dim3((chunks + 1) / 2, a.value_heads, a.batch), kPrepThreads, smem, stream>>>(
+      map_q, map_k, map_v, a, static_cast<uint8_t*>(records), chunks, status);
+  return cudaGetLastError();
+}
+
+}  // namespace pluto
