@@ -603,15 +603,13 @@ __global__ void __launch_bounds__(256) gdn_chunk_convert(const uint8_t* __restri
     for (int sc = 0; sc < kC; ++sc) acc = fmaf(-__bfloat162float(s.m[t][sc]), __bfloat162float(s.w[sc][i]), acc);
     *reinterpret_cast<__nv_bfloat16*>(dst + GdnRecord::kQT + gdn_swizzled_offset(kC, t, i)) = __float2bfloat16_rn(acc);
   }
-  // U [token][value column] as high parts and remainders, one pair of tiles per 128-column slice
+  // U [token][value column] in bf16, one tile per 128-column slice
   for (int e = threadIdx.x; e < kC * dv; e += 256) {
     const int j = e / kC, t = e % kC;
     const float u = u_in[static_cast<size_t>(j) * kUPitch + t];
-    const __nv_bfloat16 hi = __float2bfloat16_rn(u);
     uint8_t* tile = dst + GdnRecord::kCommon + static_cast<size_t>(j / kGdnSliceCols) * GdnRecord::kSlice;
-    const uint32_t off = gdn_swizzled_offset(kC, t, j % kGdnSliceCols);
-    *reinterpret_cast<__nv_bfloat16*>(tile + GdnRecord::kUH + off) = hi;
-    *reinterpret_cast<__nv_bfloat16*>(tile + GdnRecord::kUL + off) = __float2bfloat16_rn(u - __bfloat162float(hi));
+    *reinterpret_cast<__nv_bfloat16*>(tile + GdnRecord::kUH + gdn_swizzled_offset(kC, t, j % kGdnSliceCols)) =
+        __float2bfloat16_rn(u);
   }
 }
 

@@ -6,7 +6,7 @@
 //     M[t,s] = e^{b_t-b_s} (q^_t.k^_s)         (s <= t)
 //     W = T (beta c k^),   U = T (beta v),   Kt = k^ . c_C/c
 //     Pn = -(Kt^T W),      Qt = c q^ - M W
-// and the record of gdn_records.cuh (Pn, Kt, Qt, M, gamma = c_C, U) goes to the scan kernel.
+// and the record of gdn_records.cuh (Pn, Kt, Qt, M, gamma = c_C, U; all bf16) goes to the scan kernel.
 //
 // One CTA takes TWO consecutive chunks of a (sequence, head): 128 tokens = the 128 rows of a
 // tcgen05.mma tile = the 128 lanes of TMEM, so every product below is a full M128 instruction and
@@ -315,25 +315,21 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       *reinterpret_cast<uint4*>(wrow + ((c ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    // U row -> record (high parts and remainders), straight from registers
+    // U row -> record (bf16), straight from registers
     tmem_ld32(tmem + lane_base + 384 + half * 64, x[0]);
     tmem_ld32(tmem + lane_base + 384 + half * 64 + 32, x[1]);
     tmem_wait_ld();
     if (live_chunk) {
-      uint8_t* urow = rec + GdnRecord::kCommon + half * 8192 + rl * 128;
+      uint8_t* urow = rec + GdnRecord::kCommon + GdnRecord::kUH + half * 8192 + rl * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        uint32_t hi[4], lo[4];
+        uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = c * 8 + e * 2;
-          const float u0 = __uint_as_float(x[i / 32][i % 32]), u1 = __uint_as_float(x[i / 32][i % 32 + 1]);
-          hi[e] = pack_bf16(u0, u1);
-          lo[e] = pack_bf16(u0 - bf16_lo(hi[e]), u1 - bf16_hi(hi[e]));
+          w[e] = pack_bf16(__uint_as_float(x[i / 32][i % 32]), __uint_as_float(x[i / 32][i % 32 + 1]));
         }
-        const uint32_t piece = (c ^ (rl & 7)) * 16;
-        *reinterpret_cast<uint4*>(urow + GdnRecord::kUH + piece) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4*>(urow + GdnRecord::kUL + piece) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4*>(urow + ((c ^ (rl & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
     // Kt row: scaled keys, in place (operand of Pn) and to the record

@@ -24,9 +24,8 @@ struct GdnRecord {
   static constexpr uint32_t kGM = 73728;    // gamma (one float), padded to 1024
   static constexpr uint32_t kCommon = 74752;
   // per slice of 128 value columns
-  static constexpr uint32_t kUH = 0;        // U high parts  [64 tokens][128 value columns], token-major
-  static constexpr uint32_t kUL = 16384;    // U remainders
-  static constexpr uint32_t kSlice = 32768;
+  static constexpr uint32_t kUH = 0;        // U (bf16)  [64 tokens][128 value columns], token-major
+  static constexpr uint32_t kSlice = 16384;
   static __host__ __device__ size_t bytes(int value_dim) {
     return kCommon + static_cast<size_t>(value_dim / kGdnSliceCols) * kSlice;
   }

@@ -12,15 +12,23 @@
 // gdn_scan_sm100: one CTA per (sequence, head, slice of 128 value columns) walks the chunks.
 //   * The state lives in TMEM for the whole sequence, transposed: lane j = value column, 128 fp32
 //     columns = keys.  Each chunk the eight arithmetic warps read it (tcgen05.ld), write back
-//     gamma * S (tcgen05.st) and a bf16 copy of S (high part + remainder, so the product keeps
-//     16 mantissa bits) that the tensor core reads as its A operand straight from TMEM.
+//     gamma * S (tcgen05.st) and a bf16 copy of S that the tensor core reads as its A operand
+//     straight from TMEM.
 //   * One elected thread issues, per chunk, tcgen05.mma M128 N128:  acc += U^T Kt  (A = U from
-//     shared memory, token-major as stored) and  acc += S_bf16^T Pn^T  (A from TMEM); then, off the
-//     chain, M128 N64:  O^T = S_bf16^T Qt^T + U^T M^T  into one of two TMEM output buffers that
-//     the arithmetic warps drain (round, store) while the next chunk's state product runs.
+//     shared memory, token-major as stored) and  acc += S_bf16^T Pn^T  (A from TMEM): 12
+//     instructions on the chain; then, off the chain, M128 N64:  O^T = S_bf16^T Qt^T + U^T M^T  into
+//     one of two TMEM output buffers.
+//   * The arithmetic warps drain an output buffer while the next chunk's state product runs: O^T is
+//     lane = value column, so it is turned through a shared-memory tile into [token][value
+//     column] rows and leaves as 16-byte stores.
 //   * A producer thread streams the chunk records (already in the 128-byte-swizzled operand
 //     layout, so a record is two linear bulk copies) through a two-stage ring.
-// TMEM columns: state 0-127 | S_bf16 buffer 0: 128-255 | buffer 1: 256-383 | O^T 384-447, 448-511.
+// Measured on the way here: with bf16 remainders of S and U in the state products (24
+// instructions on the chain instead of 12) the state error against the fp32 token-recurrent
+// kernel fell only from 1.8e-3 to 1.1e-3 (it is set by the bf16 rounding of Pn and W), so the
+// remainders are not used; scattering O^T as 2-byte stores took 5000 cycles per chunk and made
+// the stores, not the tensor pipe, the limit.
+// TMEM columns: state 0-127 | S_bf16 buffers 128-191, 192-255 | O^T buffers 256-319, 320-383.
 // Every wait is bounded (common.cuh); on a time-out the kernel falls through to its exit path,
 // frees its TMEM and reports through the status word.
 #include "common.cuh"
@@ -32,29 +40,31 @@ namespace {
 
 constexpr int kScanThreads = 320;     // warp 0 producer, warp 1 MMA issuer, warps 2-9 arithmetic
 constexpr int kScanStages = 2;
-constexpr uint32_t kStageBytes = GdnRecord::kCommon + GdnRecord::kSlice;   // 107520
-constexpr uint32_t kColState = 0, kColSbf = 128, kColOut = 384;
-// Which bf16 remainders enter the products (each costs its own MMAs on the tensor pipe).
-constexpr bool kStateLoInUpdate = true;    // S remainder in  acc += S Pn^T   (on the chain)
-constexpr bool kULoInUpdate = true;        // U remainder in  acc += U^T Kt   (on the chain)
-constexpr bool kStateLoInOutput = false;   // outputs are rounded to bf16 anyway
-constexpr bool kULoInOutput = false;
+constexpr uint32_t kStageBytes = GdnRecord::kCommon + GdnRecord::kSlice;   // 91136
+constexpr uint32_t kOutTileBytes = kGdnChunk * kGdnSliceCols * 2;          // [64 tokens][128 columns] bf16
+constexpr uint32_t kColState = 0, kColSbf = 128, kColOut = 256;
 
 struct ScanBarriers {
   uint64_t full[kScanStages], empty[kScanStages];
-  uint64_t sbf_ready;     // 256 arrivals: the chunk's scaled state and its bf16 copy are in TMEM
+  uint64_t sbf_ready;     // 8 warp arrivals: the chunk's scaled state and its bf16 copy are in TMEM
   uint64_t state_done;    // tcgen05.commit: the chunk's state products have landed
   uint64_t out_done[2];   // tcgen05.commit: O^T of a chunk is complete
-  uint64_t out_free[2];   // 256 arrivals: the arithmetic warps have drained that buffer
+  uint64_t out_free[2];   // 8 warp arrivals: the arithmetic warps hold that buffer in registers
   uint32_t tmem_base;
 };
+
+// Barrier among the 256 arithmetic threads only (the producer and the MMA warp never join it).
+// Every arithmetic thread executes every one of these, whatever its waits returned, so the
+// arrival counts always match.
+__device__ __forceinline__ void arithmetic_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kScanThreads, 1)
 gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint32_t* status) {
   extern __shared__ uint8_t scan_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(scan_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  ScanBarriers* bar = reinterpret_cast<ScanBarriers*>(smem + kScanStages * kStageBytes);
+  uint8_t* out_tile = smem + kScanStages * kStageBytes;
+  ScanBarriers* bar = reinterpret_cast<ScanBarriers*>(out_tile + kOutTileBytes);
   const int slice = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   const int dv = a.value_dim;
@@ -66,11 +76,11 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
       mbar_init(&bar->full[s], 1);
       mbar_init(&bar->empty[s], 1);
     }
-    mbar_init(&bar->sbf_ready, 256);
+    mbar_init(&bar->sbf_ready, 8);
     mbar_init(&bar->state_done, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bar->out_done[s], 1);
-      mbar_init(&bar->out_free[s], 256);
+      mbar_init(&bar->out_free[s], 8);
     }
     mbar_fence_init();
   }
@@ -117,10 +127,9 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
       if (!ok) break;
       tc_fence_after();
       const uint32_t base = smem_u32(smem + st * kStageBytes);
-      const uint32_t sbf_hi = tmem + kColSbf + buf * 128, sbf_lo = sbf_hi + 64;
+      const uint32_t sbf = tmem + kColSbf + buf * 64;
       // token-major tiles (MN-major operands): 64-column slabs 8192 bytes apart, 16 tokens = 2048 bytes
-      const uint64_t uh = umma_desc_sw128(base + GdnRecord::kCommon + GdnRecord::kUH, 8192, 1024);
-      const uint64_t ul = umma_desc_sw128(base + GdnRecord::kCommon + GdnRecord::kUL, 8192, 1024);
+      const uint64_t u = umma_desc_sw128(base + GdnRecord::kCommon + GdnRecord::kUH, 8192, 1024);
       const uint64_t kt = umma_desc_sw128(base + GdnRecord::kKT, 8192, 1024);
       // K-major tiles: a K step of 16 elements is 32 bytes along the row, 64-element slabs apart
       const uint64_t pn = umma_desc_sw128(base + GdnRecord::kPN, 16, 1024);
@@ -130,26 +139,15 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
         // state: acc (= gamma S) += U^T Kt + S Pn^T
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + kColState, uh + ks * 128, kt + ks * 128, kIdescUpdU, true);
-        if (kULoInUpdate) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_ss(tmem + kColState, ul + ks * 128, kt + ks * 128, kIdescUpdU, true);
-        }
+          umma_ss(tmem + kColState, u + ks * 128, kt + ks * 128, kIdescUpdU, true);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tmem + kColState, sbf_hi + ks * 8, pn + (((ks / 4) * 16384 + (ks % 4) * 32) >> 4),
+          umma_ts(tmem + kColState, sbf + ks * 8, pn + (((ks / 4) * 16384 + (ks % 4) * 32) >> 4),
                   kIdescUpdS, true);
-        if (kStateLoInUpdate) {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_ts(tmem + kColState, sbf_lo + ks * 8, pn + (((ks / 4) * 16384 + (ks % 4) * 32) >> 4),
-                    kIdescUpdS, true);
-        }
         tc_commit(&bar->state_done);
       }
       __syncwarp();
-      if (c >= 2) {   // the arithmetic warps have drained this output buffer's previous chunk
+      if (c >= 2) {   // the arithmetic warps have taken this output buffer's previous chunk
         ok = __all_sync(0xffffffffu, mbar_wait(&bar->out_free[buf], ((c >> 1) - 1) & 1, status, 54));
         if (!ok) break;
         tc_fence_after();
@@ -158,18 +156,9 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
         const uint32_t out = tmem + kColOut + buf * 64;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts(out, sbf_hi + ks * 8, qt + (((ks / 4) * 8192 + (ks % 4) * 32) >> 4), kIdescOutS, ks > 0);
-        if (kStateLoInOutput) {
+          umma_ts(out, sbf + ks * 8, qt + (((ks / 4) * 8192 + (ks % 4) * 32) >> 4), kIdescOutS, ks > 0);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_ts(out, sbf_lo + ks * 8, qt + (((ks / 4) * 8192 + (ks % 4) * 32) >> 4), kIdescOutS, true);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) umma_ss(out, uh + ks * 128, mm + ks * 2, kIdescOutU, true);
-        if (kULoInOutput) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) umma_ss(out, ul + ks * 128, mm + ks * 2, kIdescOutU, true);
-        }
+        for (int ks = 0; ks < 4; ++ks) umma_ss(out, u + ks * 128, mm + ks * 2, kIdescOutU, true);
         tc_commit(&bar->out_done[buf]);
         tc_commit(&bar->empty[st]);
       }
@@ -179,9 +168,13 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
     // ------------------------------------------------------------------ arithmetic warps
     const int quarter = warp & 3;                 // the TMEM lanes this warp may touch
     const int half = (warp - 2) / 4;              // its half of the columns
-    const int j = slice * 128 + quarter * 32 + lane;   // value column == TMEM lane
+    const int jl = quarter * 32 + lane;           // value column inside the slice == TMEM lane
+    const int j = slice * kGdnSliceCols + jl;
+    const int u256 = (warp - 2) * 32 + lane;      // index among the arithmetic threads
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     float* state = a.state + (static_cast<size_t>(b) * a.value_heads + h) * kGdnKeyDim * dv + j;
+    // (uniform over the CTA) bf16 output rows that can leave as 16-byte pieces
+    const bool wide_stores = a.out_is_bf16 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0 && dv % 8 == 0;
     {
       // chunk-start state of the sequence: keys half*64 .. +63 of this value column
       uint32_t s0[2][32];
@@ -194,61 +187,90 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
       tmem_st32(tmem + lane_base + kColState + half * 64 + 32, s0[1]);
       tmem_wait_st();
     }
-    auto drain_output = [&](int e) -> bool {
+    bool ok = true;
+    // O^T of chunk e: this thread holds tokens half*32 .. +31 of value column jl.  Called by every
+    // arithmetic thread for every chunk; the work inside is skipped once a wait has failed.
+    auto drain_output = [&](int e) {
       const int buf = e & 1;
-      if (!mbar_wait(&bar->out_done[buf], (e >> 1) & 1, status, 55)) return false;
-      tc_fence_after();
+      ok = __all_sync(0xffffffffu, ok && mbar_wait(&bar->out_done[buf], (e >> 1) & 1, status, 55));
       uint32_t o[32];
-      tmem_ld32(tmem + lane_base + kColOut + buf * 64 + half * 32, o);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&bar->out_free[buf]);
+      if (ok) {
+        tc_fence_after();
+        tmem_ld32(tmem + lane_base + kColOut + buf * 64 + half * 32, o);
+        tmem_wait_ld();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->out_free[buf]);
+      if (wide_stores) {
+        arithmetic_sync();   // the previous chunk's rows have left the tile
+        if (ok) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int t = e * kGdnChunk + half * 32 + i;
-        if (t < a.tokens) {
-          const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv + j;
-          const float value = a.round ? bf16_round(__uint_as_float(o[i])) : __uint_as_float(o[i]);
-          if (a.out_is_bf16) static_cast<__nv_bfloat16*>(a.out)[off] = __float2bfloat16_rn(value);
-          else static_cast<float*>(a.out)[off] = value;
+          for (int i = 0; i < 32; ++i)
+            reinterpret_cast<__nv_bfloat16*>(out_tile)[(half * 32 + i) * kGdnSliceCols + jl] =
+                __float2bfloat16_rn(__uint_as_float(o[i]));
+        }
+        arithmetic_sync();
+        if (ok) {
+          // 16 threads per token row of 256 bytes, four passes of 16 rows
+#pragma unroll
+          for (int pass = 0; pass < 4; ++pass) {
+            const int row = pass * 16 + u256 / 16, piece = u256 % 16;
+            const int t = e * kGdnChunk + row;
+            if (t < a.tokens) {
+              const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv +
+                                 slice * kGdnSliceCols + piece * 8;
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + off) =
+                  *reinterpret_cast<const uint4*>(out_tile + row * (kGdnSliceCols * 2) + piece * 16);
+            }
+          }
+        }
+      } else if (ok) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int t = e * kGdnChunk + half * 32 + i;
+          if (t < a.tokens) {
+            const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv + j;
+            const float value = a.round ? bf16_round(__uint_as_float(o[i])) : __uint_as_float(o[i]);
+            if (a.out_is_bf16) static_cast<__nv_bfloat16*>(a.out)[off] = __float2bfloat16_rn(value);
+            else static_cast<float*>(a.out)[off] = value;
+          }
         }
       }
-      return true;
     };
-    bool ok = true;
-    for (int c = 0; c < chunks && ok; ++c) {
+    for (int c = 0; c < chunks; ++c) {
       const int st = c % kScanStages, buf = c & 1;
-      if (c > 0) ok = mbar_wait(&bar->state_done, (c - 1) & 1, status, 56);
-      if (ok) ok = mbar_wait(&bar->full[st], (c / kScanStages) & 1, status, 57);   // gamma is in the record
-      if (!ok) break;
-      tc_fence_after();
-      const float gamma = *reinterpret_cast<const float*>(smem + st * kStageBytes + GdnRecord::kGM);
-      uint32_t s[2][32], hi[32], lo[32];
-      tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
-      tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
-      tmem_wait_ld();
+      if (c > 0) ok = ok && mbar_wait(&bar->state_done, (c - 1) & 1, status, 56);
+      // (warp-uniform from here on: the tcgen05 loads and stores below are warp-wide instructions)
+      ok = __all_sync(0xffffffffu, ok && mbar_wait(&bar->full[st], (c / kScanStages) & 1, status, 57));   // gamma is in the record
+      if (ok) {
+        tc_fence_after();
+        const float gamma = *reinterpret_cast<const float*>(smem + st * kStageBytes + GdnRecord::kGM);
+        uint32_t s[2][32], packed[32];
+        tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
+        tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
+        tmem_wait_ld();
 #pragma unroll
-      for (int g = 0; g < 2; ++g)
+        for (int g = 0; g < 2; ++g)
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float x = __uint_as_float(s[g][i]), y = __uint_as_float(s[g][i + 1]);
-          const uint32_t top = pack_bf16(x, y);
-          hi[g * 16 + i / 2] = top;
-          lo[g * 16 + i / 2] = pack_bf16(x - bf16_lo(top), y - bf16_hi(top));
-          s[g][i] = __float_as_uint(x * gamma);
-          s[g][i + 1] = __float_as_uint(y * gamma);
-        }
-      // bf16 pairs: 64 keys of this half = 32 packed columns
-      tmem_st32(tmem + lane_base + kColSbf + buf * 128 + half * 32, hi);
-      tmem_st32(tmem + lane_base + kColSbf + buf * 128 + 64 + half * 32, lo);
-      tmem_st32(tmem + lane_base + kColState + half * 64, s[0]);
-      tmem_st32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&bar->sbf_ready);
-      if (c > 0) ok = drain_output(c - 1);
+          for (int i = 0; i < 32; i += 2) {
+            const float x = __uint_as_float(s[g][i]), y = __uint_as_float(s[g][i + 1]);
+            packed[g * 16 + i / 2] = pack_bf16(x, y);
+            s[g][i] = __float_as_uint(x * gamma);
+            s[g][i + 1] = __float_as_uint(y * gamma);
+          }
+        // bf16 pairs: the 64 keys of this half are 32 packed columns
+        tmem_st32(tmem + lane_base + kColSbf + buf * 64 + half * 32, packed);
+        tmem_st32(tmem + lane_base + kColState + half * 64, s[0]);
+        tmem_st32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
+        tmem_wait_st();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->sbf_ready);
+      if (c > 0) drain_output(c - 1);
     }
-    if (ok) ok = mbar_wait(&bar->state_done, (chunks - 1) & 1, status, 58);
+    ok = __all_sync(0xffffffffu, ok && mbar_wait(&bar->state_done, (chunks - 1) & 1, status, 58));
     if (ok) {
       tc_fence_after();
       uint32_t s[2][32];
@@ -260,8 +282,8 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
 #pragma unroll
         for (int i = 0; i < 32; ++i)
           state[static_cast<size_t>(half * 64 + g * 32 + i) * dv] = __uint_as_float(s[g][i]);
-      drain_output(chunks - 1);
     }
+    drain_output(chunks - 1);
   }
   tc_fence_before();
   __syncthreads();
@@ -273,7 +295,9 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
 
 }  // namespace
 
-size_t gdn_scan_smem_bytes() { return 1024 + kScanStages * kStageBytes + sizeof(ScanBarriers); }
+size_t gdn_scan_smem_bytes() {
+  return 1024 + kScanStages * kStageBytes + kOutTileBytes + sizeof(ScanBarriers);
+}
 
 cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int chunks,
                             uint32_t* status) {
@@ -281,7 +305,7 @@ cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* r
   cudaError_t e = cudaFuncSetAttribute(gdn_scan_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  gdn_scan_sm100<<<dim3(a.value_dim / 128, a.value_heads, a.batch), kScanThreads, smem, stream>>>(
+  gdn_scan_sm100<<<dim3(a.value_dim / kGdnSliceCols, a.value_heads, a.batch), kScanThreads, smem, stream>>>(
       a, static_cast<const uint8_t*>(records), chunks, status);
   return cudaGetLastError();
 }

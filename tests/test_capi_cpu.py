@@ -100,6 +100,6 @@ def test_delta_net_argument_validation(engine):
     big = [None, 16, 16, 16, 1, 16, 16, 16, 16, 1, 1, 128]
     assert _code(engine, L.pluto_gdn_prefill, *big, 2, 4, 128, 128, 0, 0, 1, 1.0, 1, 256, 1024)[0] == "InvalidArgument"
     units = 2 * 16 * 256   # (sequence, head, chunk) records
-    assert L.pluto_gdn_prefill_workspace_bytes(2, 16384, 16, 16, 128, 128, 1) == units * 107520 + 1024
+    assert L.pluto_gdn_prefill_workspace_bytes(2, 16384, 16, 16, 128, 128, 1) == units * 91136 + 1024
     assert L.pluto_gdn_prefill_workspace_bytes(2, 16384, 16, 16, 64, 128, 1) == 0
     assert _code(engine, L.pluto_gdn_conv_silu, None, 16, 16, 0, 1, 1, 8, 33, 1, 16, 16, 0)[0] == "InvalidArgument"
