@@ -54,6 +54,18 @@ struct PrepSmall {
   uint32_t tmem_base;
 };
 
+// Linear bulk copy shared -> global (both 16-byte aligned, size a multiple of 16); the issuing
+// thread later commits and waits for the group before the shared memory may be reused or freed.
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 // scratch element (row, s) of the fp32 [128][64] matrix; the low five column bits are XORed with
 // the row so that a warp touching one column of 32 consecutive rows hits 32 banks
 __device__ __forceinline__ int scratch_index(int row, int s) {
@@ -86,6 +98,16 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     mbar_init(&sm.loaded, 1);
     mbar_init(&sm.mma_done, 1);
     mbar_fence_init();
+    // the raw tiles are requested first: everything up to the first product hides their latency
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    mbar_expect_tx(&sm.loaded, 3 * 32768);
+    for (int s = 0; s < 2; ++s) {
+      tma_load_3d(smem + kRegK + s * 16384, &map_k, kh * kGdnKeyDim + s * 64, t0, b, &sm.loaded);
+      tma_load_3d(smem + kRegQ + s * 16384, &map_q, kh * kGdnKeyDim + s * 64, t0, b, &sm.loaded);
+      tma_load_3d(smem + kRegV + s * 16384, &map_v, h * dv + s * 64, t0, b, &sm.loaded);
+    }
   }
   if (warp == 1) {
     tmem_alloc(&sm.tmem_base, 512);
@@ -101,17 +123,6 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
 
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&map_q);
-    tma_prefetch_desc(&map_k);
-    tma_prefetch_desc(&map_v);
-    mbar_expect_tx(&sm.loaded, 3 * 32768);
-    for (int s = 0; s < 2; ++s) {
-      tma_load_3d(smem + kRegK + s * 16384, &map_k, kh * kGdnKeyDim + s * 64, t0, b, &sm.loaded);
-      tma_load_3d(smem + kRegQ + s * 16384, &map_q, kh * kGdnKeyDim + s * 64, t0, b, &sm.loaded);
-      tma_load_3d(smem + kRegV + s * 16384, &map_v, h * dv + s * 64, t0, b, &sm.loaded);
-    }
-  }
   // ---- gates: running sum of log decay inside each chunk (past the sequence end: g = 1, beta = 0)
   float run = 0.0f, be = 0.0f;
   if (half == 0) {
@@ -217,7 +228,10 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   }
   __syncthreads();
 
-  // ---- T = (I + A)^-1 by forward substitution: one thread per (chunk, column)
+  // ---- T = (I + A)^-1 by forward substitution: one thread per (chunk, column); the 64 threads of a
+  //      chunk read the same element of A at every step (a broadcast).  (A blocked variant -- 16 x 16
+  //      diagonal blocks, then block rows with all 256 threads -- was measured at 28000 cycles
+  //      against 6000 for this one: its sweeps are short runtime loops separated by barriers.)
   {
     float col[64];
     const int c2 = threadIdx.x >> 6, jj = threadIdx.x & 63;
@@ -315,12 +329,12 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       *reinterpret_cast<uint4*>(wrow + ((c ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    // U row -> record (bf16), straight from registers
+    // U row -> staging tile in record order (over the scratch, which nobody reads any more)
     tmem_ld32(tmem + lane_base + 384 + half * 64, x[0]);
     tmem_ld32(tmem + lane_base + 384 + half * 64 + 32, x[1]);
     tmem_wait_ld();
-    if (live_chunk) {
-      uint8_t* urow = rec + GdnRecord::kCommon + GdnRecord::kUH + half * 8192 + rl * 128;
+    {
+      uint8_t* urow = smem + kRegQ + cb * 16384 + half * 8192 + rl * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t w[4];
@@ -332,9 +346,8 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         *reinterpret_cast<uint4*>(urow + ((c ^ (rl & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    // Kt row: scaled keys, in place (operand of Pn) and to the record
+    // Kt row: scaled keys, in place (operand of Pn, and the record's tile)
     uint8_t* krow = smem + kRegK + half * 16384 + r * 128;
-    uint8_t* kt_out = rec + GdnRecord::kKT + half * 8192 + rl * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const uint32_t piece = (c ^ (r & 7)) * 16;
@@ -344,13 +357,25 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       v.z = pack_bf16(bf16_lo(v.z) * tail, bf16_hi(v.z) * tail);
       v.w = pack_bf16(bf16_lo(v.w) * tail, bf16_hi(v.w) * tail);
       *reinterpret_cast<uint4*>(krow + piece) = v;
-      if (live_chunk) *reinterpret_cast<uint4*>(kt_out + piece) = v;
     }
   }
   tc_fence_before();
   fence_proxy_async();
   __syncthreads();
   tc_fence_after();
+
+  // the tiles that are final leave now, as linear bulk copies from shared memory
+  uint8_t* pair_rec = records + ((static_cast<size_t>(b) * a.value_heads + h) * chunks + pair * 2) * GdnRecord::bytes(dv);
+  if (threadIdx.x == 32 && ok) {
+    for (int v = 0; v < 2 && pair * 2 + v < chunks; ++v) {
+      uint8_t* out = pair_rec + static_cast<size_t>(v) * GdnRecord::bytes(dv);
+      bulk_store(out + GdnRecord::kCommon + GdnRecord::kUH, smem + kRegQ + v * 16384, 16384);
+      bulk_store(out + GdnRecord::kKT, smem + kRegK + v * 8192, 8192);
+      bulk_store(out + GdnRecord::kKT + 8192, smem + kRegK + 16384 + v * 8192, 8192);
+      bulk_store(out + GdnRecord::kMM, smem + kRegM + v * 16384, 8192);
+    }
+    bulk_store_commit();
+  }
 
   // ---- Pn(chunk) = Kt^T W over the chunk's 64 tokens; M W through the two views of M
   if (warp == 0 && ok) {
@@ -379,35 +404,32 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tc_fence_after();
   if (ok) {
     uint32_t x[2][32];
-    // Pn rows: row r = key index of the output, this thread's 64 input keys, for both chunks
+    // Pn rows: row r = key index of the output, this thread's 64 input keys, for both chunks; staged
+    // in record order over the T tiles (72 KB, dead since the W / U products)
 #pragma unroll
     for (int view = 0; view < 2; ++view) {
       tmem_ld32(tmem + lane_base + view * 128 + half * 64, x[0]);
       tmem_ld32(tmem + lane_base + view * 128 + half * 64 + 32, x[1]);
       tmem_wait_ld();
-      if (pair * 2 + view < chunks) {
-        uint8_t* prow = records +
-                        ((static_cast<size_t>(b) * a.value_heads + h) * chunks + pair * 2 + view) * GdnRecord::bytes(dv) +
-                        GdnRecord::kPN + half * 16384 + r * 128;
+      uint8_t* prow = smem + kRegT1 + view * 32768 + half * 16384 + r * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t w[4];
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = c * 8 + e * 2;
-            w[e] = pack_bf16(-__uint_as_float(x[i / 32][i % 32]), -__uint_as_float(x[i / 32][i % 32 + 1]));
-          }
-          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int e = 0; e < 4; ++e) {
+          const int i = c * 8 + e * 2;
+          w[e] = pack_bf16(-__uint_as_float(x[i / 32][i % 32]), -__uint_as_float(x[i / 32][i % 32 + 1]));
         }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    // Qt = c q^ - M W
+    // Qt = c q^ - M W, staged over W (dead since the last products)
     tmem_ld32(tmem + lane_base + 256 + half * 64, x[0]);
     tmem_ld32(tmem + lane_base + 256 + half * 64 + 32, x[1]);
     tmem_wait_ld();
-    if (live_chunk) {
+    {
       const float cq = __expf(br) * qn;
-      uint8_t* qrow_out = rec + GdnRecord::kQT + half * 8192 + rl * 128;
+      uint8_t* qrow_out = smem + kRegV + cb * 16384 + half * 8192 + rl * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t w[4];
@@ -420,16 +442,21 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         *reinterpret_cast<uint4*>(qrow_out + ((c ^ (rl & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      // M row: already in operand order in shared memory
-      const uint8_t* mtile = smem + kRegM + r * 128 + (cb ? 8192 : 0);
-      uint8_t* m_out = rec + GdnRecord::kMM + rl * 128;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t piece = ((half * 4 + q) ^ (r & 7)) * 16;
-        *reinterpret_cast<uint4*>(m_out + piece) = *reinterpret_cast<const uint4*>(mtile + piece);
-      }
-      if (rl == 63 && half == 0) *reinterpret_cast<float*>(rec + GdnRecord::kGM) = __expf(br);
     }
+    if (live_chunk && rl == 63 && half == 0) *reinterpret_cast<float*>(rec + GdnRecord::kGM) = __expf(br);
+  }
+  fence_proxy_async();
+  __syncthreads();
+  if (threadIdx.x == 32) {
+    if (ok) {
+      for (int v = 0; v < 2 && pair * 2 + v < chunks; ++v) {
+        uint8_t* out = pair_rec + static_cast<size_t>(v) * GdnRecord::bytes(dv);
+        bulk_store(out + GdnRecord::kPN, smem + kRegT1 + v * 32768, 32768);
+        bulk_store(out + GdnRecord::kQT, smem + kRegV + v * 16384, 16384);
+      }
+      bulk_store_commit();
+    }
+    bulk_store_wait_read();   // shared memory may go away only after the copies have read it
   }
   tc_fence_before();
   __syncthreads();
