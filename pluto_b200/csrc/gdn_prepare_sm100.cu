@@ -66,10 +66,13 @@ __device__ __forceinline__ void bulk_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
-// scratch element (row, s) of the fp32 [128][64] matrix; the low five column bits are XORed with
-// the row so that a warp touching one column of 32 consecutive rows hits 32 banks
-__device__ __forceinline__ int scratch_index(int row, int s) {
-  return row * 64 + ((s & 32) | ((s ^ row) & 31));
+// The fp32 scratch holds, per chunk, first A TRANSPOSED ([s][t], plain: the row owners write
+// consecutive t, and the substitution reads four consecutive t of one column s as one broadcast
+// 16-byte load), then T row-major with the 16-byte pieces of row t permuted by (piece ^ (t & 15)):
+// the column owners write conflict-free and the row owners read 16-byte pieces almost so.
+__device__ __forceinline__ int a_transposed_index(int chunk, int s, int t) { return chunk * 4096 + s * 64 + t; }
+__device__ __forceinline__ int t_index(int row, int s) {
+  return row * 64 + ((((s >> 2) ^ (row & 15)) << 2) | (s & 3));
 }
 
 __global__ void __launch_bounds__(kPrepThreads, 1)
@@ -170,8 +173,9 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
     __syncwarp();
   }
-  uint32_t qrow[32];   // this thread's 64 query elements (bf16 pairs), kept for Qt
   {
+    // |q|^2 of this thread's half of its query row (the row itself is read again for Qt at the end:
+    // holding it in registers across the inversion pushed that phase's column into local memory)
     const uint8_t* row = smem + kRegQ + half * 16384 + r * 128;
     float ss = 0.0f;
 #pragma unroll
@@ -179,10 +183,7 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const uint4 v = *reinterpret_cast<const uint4*>(row + ((c ^ (r & 7)) * 16));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        qrow[c * 4 + e] = w[e];
-        ss += bf16_lo(w[e]) * bf16_lo(w[e]) + bf16_hi(w[e]) * bf16_hi(w[e]);
-      }
+      for (int e = 0; e < 4; ++e) ss += bf16_lo(w[e]) * bf16_lo(w[e]) + bf16_hi(w[e]) * bf16_hi(w[e]);
     }
     sm.qsq[half][r] = ss;
   }
@@ -198,8 +199,13 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     tmem_ld32(tmem + lane_base + 0 + cb * 64 + half * 32, kk);
     tmem_ld32(tmem + lane_base + 128 + cb * 64 + half * 32, qk);
     tmem_wait_ld();
-    if ((rl >> 5) == half)   // the diagonal of K K^T is |k|^2
-      sm.kn[r] = a.normalize_qk ? rsqrtf(__uint_as_float(kk[rl & 31]) + 1e-6f) : 1.0f;
+    if ((rl >> 5) == half) {   // the diagonal of K K^T is |k|^2
+      float diagonal = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)   // (a register array must not be indexed with a runtime value)
+        if (i == (rl & 31)) diagonal = __uint_as_float(kk[i]);
+      sm.kn[r] = a.normalize_qk ? rsqrtf(diagonal + 1e-6f) : 1.0f;
+    }
   }
   __syncthreads();
   const float br = sm.b[r], betar = sm.beta[r], knr = sm.kn[r];
@@ -215,7 +221,7 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int s = half * 32 + i + e, sg = cb * 64 + s;
         const float ratio = s <= rl ? __expf(br - sm.b[sg]) : 0.0f;
         const float kns = sm.kn[sg];
-        scratch[scratch_index(r, s)] = s < rl ? betar * ratio * knr * kns * __uint_as_float(kk[i + e]) : 0.0f;
+        scratch[a_transposed_index(cb, s, rl)] = s < rl ? betar * ratio * knr * kns * __uint_as_float(kk[i + e]) : 0.0f;
         mv[e] = ratio * qn * kns * __uint_as_float(qk[i + e]);
       }
       mrow[i / 2] = pack_bf16(mv[0], mv[1]);
@@ -228,26 +234,34 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   }
   __syncthreads();
 
-  // ---- T = (I + A)^-1 by forward substitution: one thread per (chunk, column); the 64 threads of a
-  //      chunk read the same element of A at every step (a broadcast).  (A blocked variant -- 16 x 16
-  //      diagonal blocks, then block rows with all 256 threads -- was measured at 28000 cycles
-  //      against 6000 for this one: its sweeps are short runtime loops separated by barriers.)
+  // ---- T = (I + A)^-1 by forward substitution, one thread per (chunk, column), right-looking: as
+  //      soon as entry s of the column is final it is folded into every later entry (independent
+  //      FMAs, one of them on the chain to the next step).  The 64 threads of a chunk read the same
+  //      elements of A, four at a time: the shared-memory pipe, one broadcast per cycle, is what
+  //      bounds this phase (2016 scalar loads per thread took 14000 cycles).
   {
     float col[64];
     const int c2 = threadIdx.x >> 6, jj = threadIdx.x & 63;
     if (threadIdx.x < 128) {
 #pragma unroll
-      for (int t = 0; t < 64; ++t) {
-        float acc = t == jj ? 1.0f : 0.0f;
+      for (int t = 0; t < 64; ++t) col[t] = t == jj ? 1.0f : 0.0f;
 #pragma unroll
-        for (int sc = 0; sc < t; ++sc) acc = fmaf(-scratch[scratch_index(c2 * 64 + t, sc)], col[sc], acc);
-        col[t] = acc;
+      for (int sc = 0; sc < 63; ++sc) {
+        const float c = col[sc];
+#pragma unroll
+        for (int t4 = (sc + 1) / 4; t4 < 16; ++t4) {
+          const float4 a4 = *reinterpret_cast<const float4*>(&scratch[a_transposed_index(c2, sc, t4 * 4)]);
+          const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (t4 * 4 + e > sc) col[t4 * 4 + e] = fmaf(-av[e], c, col[t4 * 4 + e]);
+        }
       }
     }
     __syncthreads();
     if (threadIdx.x < 128) {
 #pragma unroll
-      for (int t = 0; t < 64; ++t) scratch[scratch_index(c2 * 64 + t, jj)] = col[t];
+      for (int t = 0; t < 64; ++t) scratch[t_index(c2 * 64 + t, jj)] = col[t];
     }
   }
   __syncthreads();
@@ -256,18 +270,23 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   {
     uint32_t t1[16], t2h[16], t2l[16];
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float x1[2], x2[2];
+    for (int v = 0; v < 8; ++v) {
+      const int piece = half * 8 + v;   // columns piece*4 .. +3 of this row
+      const float4 t4 = *reinterpret_cast<const float4*>(&scratch[r * 64 + ((piece ^ (r & 15)) << 2)]);
+      const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+      float x1[4], x2[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int sg = cb * 64 + piece * 4 + e;
+        x1[e] = tv[e] * sm.scale1[sg];
+        x2[e] = tv[e] * sm.beta[sg];
+      }
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int s = half * 32 + i + e, sg = cb * 64 + s;
-        const float tv = scratch[scratch_index(r, s)];
-        x1[e] = tv * sm.scale1[sg];
-        x2[e] = tv * sm.beta[sg];
+        t1[v * 2 + e] = pack_bf16(x1[2 * e], x1[2 * e + 1]);
+        t2h[v * 2 + e] = pack_bf16(x2[2 * e], x2[2 * e + 1]);
+        t2l[v * 2 + e] = pack_bf16(x2[2 * e] - bf16_lo(t2h[v * 2 + e]), x2[2 * e + 1] - bf16_hi(t2h[v * 2 + e]));
       }
-      t1[i / 2] = pack_bf16(x1[0], x1[1]);
-      t2h[i / 2] = pack_bf16(x2[0], x2[1]);
-      t2l[i / 2] = pack_bf16(x2[0] - bf16_lo(t2h[i / 2]), x2[1] - bf16_hi(t2h[i / 2]));
     }
     const uint32_t row_off = r * 128 + (cb ? 8192 : 0);
 #pragma unroll
@@ -430,13 +449,20 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     {
       const float cq = __expf(br) * qn;
       uint8_t* qrow_out = smem + kRegV + cb * 16384 + half * 8192 + rl * 128;
+      // the raw query row again, from global memory (the TMA load has just pulled it through L2)
+      const bool live_token = t0 + r < a.tokens;
+      const uint4* qsrc = reinterpret_cast<const uint4*>(
+          static_cast<const __nv_bfloat16*>(a.q) + (static_cast<size_t>(b) * a.tokens + (live_token ? t0 + r : 0)) * a.qk_token +
+          static_cast<size_t>(kh) * kGdnKeyDim + half * 64);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
+        const uint4 qv = live_token ? __ldg(qsrc + c) : make_uint4(0, 0, 0, 0);
+        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = c * 8 + e * 2;
-          const uint32_t q2 = qrow[c * 4 + e];
+          const uint32_t q2 = qw[e];
           w[e] = pack_bf16(cq * bf16_lo(q2) - __uint_as_float(x[i / 32][i % 32]),
                            cq * bf16_hi(q2) - __uint_as_float(x[i / 32][i % 32 + 1]));
         }
