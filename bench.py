@@ -657,6 +657,8 @@ def _other_rest(peaks, only, time_ms, skip=()):
     result = {}
     if only == "gdn":
         return _gdn_workload(time_ms)
+    if only == "gdn_prefill":
+        return _gdn_prefill_only(time_ms)
     if only == "gqa_bwd":
         return _gqa_bwd_workload(time_ms)
     if only == "linear":
@@ -810,6 +812,29 @@ def _gqa_bwd_workload(time_ms):
         "ms": ms, "tflops": flop / (ms * 1e-3) / 1e12}}
 
 
+def _gdn_prefill_only(time_ms):
+    """The chunked delta-net prefill alone at the benchmark shape (the two tcgen05 kernels): the
+    case the ncu captures of gdn_prepare_sm100 / gdn_scan_sm100 are taken on."""
+    import torch
+
+    from pluto_b200.layers import gdn_prefill
+    bb, tt, hh, dd = 2, 16384, 16, 128
+    qn = torch.nn.functional.normalize(torch.randn(bb, tt, hh, dd, device="cuda"), dim=-1).bfloat16()
+    kn = torch.nn.functional.normalize(torch.randn(bb, tt, hh, dd, device="cuda"), dim=-1).bfloat16()
+    vn = torch.randn(bb, tt, hh, dd, device="cuda").bfloat16()
+    g = torch.sigmoid(torch.randn(bb, tt, hh, device="cuda") * 2 + 2)
+    beta = torch.sigmoid(torch.randn(bb, tt, hh, device="cuda"))
+    st = torch.zeros(bb, hh, dd, dd, device="cuda")
+    og = torch.empty_like(vn)
+
+    def prefill():
+        gdn_prefill(qn, kn, vn, g, beta, st, out=og)
+
+    ms = time_ms(prefill, steps=5, warmup=2)
+    return {"gated_delta_net_prefill": {"workload": "batch 2, 16 heads, d_k = d_v = 128, seq 16384", "ms": ms,
+                                        "tflops_chunked_count": 94.49e9 / (ms * 1e-3) / 1e12}}
+
+
 def _gdn_workload(time_ms, bptt_only=False):
     import torch
 
@@ -908,7 +933,7 @@ def main():
     parser.add_argument("--impl", choices=["engine", "reference"], default="engine")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the secondary workloads and the CPU baseline (profiling runs)")
-    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gqa_bwd", "linear", "dense"], default=None,
+    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gdn_prefill", "gqa_bwd", "linear", "dense"], default=None,
                         help="run only one secondary workload at a capture-friendly size and exit")
     args = parser.parse_args()
     if args.profile_case:
