@@ -30,16 +30,96 @@
 #include "engine.h"
 #include "gdn_records.cuh"
 
+#include <mutex>
+
 namespace pluto {
 // gdn_scan_sm100.cu
 size_t gdn_scan_smem_bytes();
-cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int chunks,
-                            uint32_t* status);
+cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int first_chunk,
+                            int chunks, int all_chunks, uint32_t* status);
 // gdn_prepare_sm100.cu
 bool gdn_prepare_sm100_supported(const GdnArgs& a);
-cudaError_t gdn_prepare_sm100_launch(cudaStream_t stream, const GdnArgs& a, void* records, int chunks,
-                                     uint32_t* status);
+bool gdn_prepare_sm100_maps(const GdnArgs& a, CUtensorMap maps[3]);
+cudaError_t gdn_prepare_sm100_launch(cudaStream_t stream, const CUtensorMap maps[3], const GdnArgs& a,
+                                     void* records, int first_pair, int pairs, int chunks, uint32_t* status);
 namespace {
+
+// The scan walks a sequence's chunks one after another on (sequences x heads x slices) SMs -- 32 of
+// 148 at batch 2 with 16 heads -- while the prepare kernel fills all of them.  Cut into pieces, the
+// two overlap: the scan of piece i runs on a second, higher-priority stream beside the prepare of
+// piece i + 1, each piece's scan ordered after its prepare by an event, and the caller's stream
+// joins the second one at the end.
+constexpr int kGdnMaxPieces = 16;
+constexpr int kGdnMaxDevices = 64;
+struct GdnLanes {
+  cudaStream_t scan = nullptr;
+  cudaEvent_t prepared[kGdnMaxPieces] = {}, scanned = nullptr;
+  bool ok = false;
+  std::mutex enqueue;   // one call at a time records and waits on the events
+};
+GdnLanes g_gdn_lanes[kGdnMaxDevices];
+std::once_flag g_gdn_once[kGdnMaxDevices];
+
+GdnLanes* gdn_lanes_for_current_device() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kGdnMaxDevices) return nullptr;
+  std::call_once(g_gdn_once[device], [device] {
+    GdnLanes& l = g_gdn_lanes[device];
+    int least = 0, greatest = 0;
+    bool ok = cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess &&
+              cudaStreamCreateWithPriority(&l.scan, cudaStreamNonBlocking, greatest) == cudaSuccess &&
+              cudaEventCreateWithFlags(&l.scanned, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < kGdnMaxPieces && ok; ++i)
+      ok = cudaEventCreateWithFlags(&l.prepared[i], cudaEventDisableTiming) == cudaSuccess;
+    l.ok = ok;
+  });
+  return g_gdn_lanes[device].ok ? &g_gdn_lanes[device] : nullptr;
+}
+
+// Chunk pairs per piece.  Measured at batch 2, 16 heads, 16384 tokens (128 pairs, 32 scan CTAs):
+// 0.81 ms as one piece, 0.69 ms with 32 or 43 pairs per piece, 0.72 / 0.75 / 0.82 ms with 24 / 16 /
+// 12 -- every piece costs the scan a state round trip through global memory and a cold record
+// ring, and the prepare grid a partial last wave.  So: pieces of about a thousand prepare CTAs
+// (seven waves), and one piece when the scan itself fills most of the GPU or the sequence is short.
+int gdn_piece_pairs(const GdnArgs& a, int pairs) {
+  const int units = a.batch * a.value_heads;
+  const int scan_ctas = units * (a.value_dim / kGdnSliceCols);
+  if (scan_ctas > 96) return pairs;
+  int per_piece = max(8, (1024 + units - 1) / units);
+  if (pairs < 2 * per_piece) return pairs;
+  while ((pairs + per_piece - 1) / per_piece > kGdnMaxPieces) per_piece *= 2;
+  return per_piece;
+}
+
+cudaError_t gdn_prepare_and_scan(cudaStream_t stream, const GdnArgs& a, uint8_t* records, int chunks,
+                                 uint32_t* status) {
+  CUtensorMap maps[3];
+  if (!gdn_prepare_sm100_maps(a, maps)) return cudaErrorInvalidValue;
+  const int pairs = (chunks + 1) / 2;
+  const int per_piece = gdn_piece_pairs(a, pairs);
+  if (per_piece >= pairs) {
+    cudaError_t e = gdn_prepare_sm100_launch(stream, maps, a, records, 0, pairs, chunks, status);
+    if (e != cudaSuccess) return e;
+    return gdn_scan_launch(stream, a, records, 0, chunks, chunks, status);
+  }
+  GdnLanes* l = gdn_lanes_for_current_device();
+  if (l == nullptr) return cudaErrorInitializationError;
+  std::lock_guard<std::mutex> lock(l->enqueue);
+  cudaError_t e = cudaSuccess;
+  int piece = 0;
+  for (int first = 0; first < pairs && e == cudaSuccess; first += per_piece, ++piece) {
+    const int n = min(per_piece, pairs - first);
+    e = gdn_prepare_sm100_launch(stream, maps, a, records, first, n, chunks, status);
+    if (e == cudaSuccess) e = cudaEventRecord(l->prepared[piece], stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(l->scan, l->prepared[piece], 0);
+    if (e == cudaSuccess)
+      e = gdn_scan_launch(l->scan, a, records, first * 2, min(n * 2, chunks - first * 2), chunks, status);
+  }
+  // (joined even after a failed launch, so that nothing of this call is left running unordered)
+  cudaError_t joined = cudaEventRecord(l->scanned, l->scan);
+  if (joined == cudaSuccess) joined = cudaStreamWaitEvent(stream, l->scanned, 0);
+  return e != cudaSuccess ? e : joined;
+}
 
 constexpr int kC = 64;           // tokens per chunk
 constexpr int kDK = 128;         // key width handled by this path
@@ -647,9 +727,7 @@ cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, 
   if (gdn_prepare_sm100_supported(a)) {
     uint8_t* records = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(workspace) + 1023) &
                                                   ~static_cast<uintptr_t>(1023));
-    cudaError_t launched = gdn_prepare_sm100_launch(stream, a, records, chunks, status);
-    if (launched != cudaSuccess) return launched;
-    return gdn_scan_launch(stream, a, records, chunks, status);
+    return gdn_prepare_and_scan(stream, a, records, chunks, status);
   }
   cudaError_t e = cudaFuncSetAttribute(gdn_chunk_prepare, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(PrepareSmem)));
@@ -668,7 +746,7 @@ cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, 
         static_cast<const uint8_t*>(workspace), records, chunks, a.value_heads, a.value_dim);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return gdn_scan_launch(stream, a, records, chunks, status);
+    return gdn_scan_launch(stream, a, records, 0, chunks, chunks, status);
   }
   const size_t smem = kRecStages * kStageBytes + sizeof(RecBarriers);
   e = cudaFuncSetAttribute(gdn_chunk_recurrence, cudaFuncAttributeMaxDynamicSharedMemorySize,

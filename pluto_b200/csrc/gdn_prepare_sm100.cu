@@ -27,6 +27,8 @@
 //     per row and slab).
 // TMEM columns: K K^T 0-127 | Q K^T 128-255 | W 256-383 | U 384-511, then Pn(a) 0-127 |
 // Pn(b) 128-255 | M W 256-383.
+#include <stddef.h>
+
 #include "common.cuh"
 #include "engine.h"
 #include "gdn_records.cuh"
@@ -66,11 +68,16 @@ __device__ __forceinline__ void bulk_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
-// The fp32 scratch holds, per chunk, first A TRANSPOSED ([s][t], plain: the row owners write
-// consecutive t, and the substitution reads four consecutive t of one column s as one broadcast
-// 16-byte load), then T row-major with the 16-byte pieces of row t permuted by (piece ^ (t & 15)):
+// The fp32 scratch holds, per chunk, first A TRANSPOSED ([s][t] with the even rows t before the odd
+// ones: the substitution's two threads per column own the even and the odd rows and read four of
+// their rows of one column s as one broadcast 16-byte load), then T row-major with the 16-byte pieces of row t permuted by (piece ^ (t & 15)):
 // the column owners write conflict-free and the row owners read 16-byte pieces almost so.
-__device__ __forceinline__ int a_transposed_index(int chunk, int s, int t) { return chunk * 4096 + s * 64 + t; }
+__device__ __forceinline__ int a_transposed_index(int chunk, int s, int t) {
+  // even rows, then odd rows, of column s; the odd half is rotated by 16 banks, so that the two
+  // 16-byte pieces one substitution step reads (one per parity) and the 32 elements a warp writes
+  // fall into different banks
+  return chunk * 4096 + s * 64 + (t & 1) * 32 + ((t >> 1) ^ ((t & 1) << 4));
+}
 __device__ __forceinline__ int t_index(int row, int s) {
   return row * 64 + ((((s >> 2) ^ (row & 15)) << 2) | (s & 3));
 }
@@ -78,13 +85,22 @@ __device__ __forceinline__ int t_index(int row, int s) {
 __global__ void __launch_bounds__(kPrepThreads, 1)
 gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, GdnArgs a, uint8_t* __restrict__ records,
-                  int chunks, uint32_t* status) {
+                  int first_pair, int chunks, uint32_t* status) {
   extern __shared__ uint8_t prep_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(prep_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  PrepSmall& sm = *reinterpret_cast<PrepSmall*>(smem + kRegSmall);
-  float* scratch = reinterpret_cast<float*>(smem + kRegQ);
-  const int pair = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  PrepSmall& sm = *reinterpret_cast<PrepSmall*>(smem + kRegSmall);   // (barriers; the arrays go through lds/sts)
+  // Every access to shared memory below uses a 32-bit shared address and ld.shared / st.shared:
+  // `smem` is a generic pointer to the compiler (the alignment arithmetic hides its address
+  // space), and generic accesses made the phases that live on shared memory several times slower.
+  const uint32_t base = smem_u32(smem);
+  const uint32_t scratch = base + kRegQ;                       // fp32 [2 chunks][64][64]
+  const uint32_t sm_b = base + kRegSmall + offsetof(PrepSmall, b);
+  const uint32_t sm_beta = base + kRegSmall + offsetof(PrepSmall, beta);
+  const uint32_t sm_kn = base + kRegSmall + offsetof(PrepSmall, kn);
+  const uint32_t sm_scale1 = base + kRegSmall + offsetof(PrepSmall, scale1);
+  const uint32_t sm_qsq = base + kRegSmall + offsetof(PrepSmall, qsq);
+  const int pair = first_pair + blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kh = h / (a.value_heads / a.key_heads);
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   const int quarter = warp & 3, half = warp >> 2;     // TMEM lane quarter; column half of the row
@@ -119,7 +135,7 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   // the zero blocks shared by the two 128-row views of every three-block tile
   for (int i = threadIdx.x; i < 4 * 512; i += kPrepThreads) {
     const uint32_t region = i / 512 == 0 ? kRegT1 : (i / 512 == 1 ? kRegT2H : (i / 512 == 2 ? kRegT2L : kRegM));
-    *reinterpret_cast<uint4*>(smem + region + 8192 + (i % 512) * 16) = make_uint4(0, 0, 0, 0);
+    sts_b32x4(base + region + 8192 + (i % 512) * 16, 0, 0, 0, 0);
   }
   tc_fence_before();
   __syncthreads();
@@ -140,13 +156,13 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const float v = __shfl_up_sync(0xffffffffu, run, o);
       if (lane >= o) run += v;
     }
-    if (lane == 31) sm.kn[quarter] = run;   // (kn is free until the key norms are known)
+    if (lane == 31) sts_f32(sm_kn + quarter * 4, run);   // (kn is free until the key norms are known)
   }
   __syncthreads();
   if (half == 0) {
-    if (quarter & 1) run += sm.kn[quarter - 1];
-    sm.b[r] = run;
-    sm.beta[r] = be;
+    if (quarter & 1) run += lds_f32(sm_kn + (quarter - 1) * 4);
+    sts_f32(sm_b + r * 4, run);
+    sts_f32(sm_beta + r * 4, be);
   }
   __syncthreads();
 
@@ -155,7 +171,6 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   constexpr uint32_t kIdescKK = umma_idesc_bf16_majors(128, 128, false, false);
   constexpr uint32_t kIdescTB = umma_idesc_bf16_majors(128, 128, false, true);    // K-major A, token-major B
   constexpr uint32_t kIdescTT = umma_idesc_bf16_majors(128, 128, true, true);     // both token-major
-  const uint32_t base = smem_u32(smem);
   if (warp == 0 && ok) {
     if (elect_one()) {
       const uint64_t kd = umma_desc_sw128(base + kRegK, 16, 1024), qd = umma_desc_sw128(base + kRegQ, 16, 1024);
@@ -176,20 +191,20 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   {
     // |q|^2 of this thread's half of its query row (the row itself is read again for Qt at the end:
     // holding it in registers across the inversion pushed that phase's column into local memory)
-    const uint8_t* row = smem + kRegQ + half * 16384 + r * 128;
+    const uint32_t row = base + kRegQ + half * 16384 + r * 128;
     float ss = 0.0f;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      const uint4 v = *reinterpret_cast<const uint4*>(row + ((c ^ (r & 7)) * 16));
+      const uint4 v = lds_b32x4(row + ((c ^ (r & 7)) * 16));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) ss += bf16_lo(w[e]) * bf16_lo(w[e]) + bf16_hi(w[e]) * bf16_hi(w[e]);
     }
-    sm.qsq[half][r] = ss;
+    sts_f32(sm_qsq + (half * 128 + r) * 4, ss);
   }
   __syncthreads();
   const float qn = a.normalize_qk
-                       ? rsqrtf(sm.qsq[0][r] + sm.qsq[1][r] + 1e-6f) / sqrtf(static_cast<float>(kGdnKeyDim))
+                       ? rsqrtf(lds_f32(sm_qsq + r * 4) + lds_f32(sm_qsq + (128 + r) * 4) + 1e-6f) / sqrtf(static_cast<float>(kGdnKeyDim))
                        : a.q_scale;
 
   ok = __all_sync(0xffffffffu, ok && mbar_wait(&sm.mma_done, 0, status, 61));
@@ -204,12 +219,12 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
       for (int i = 0; i < 32; ++i)   // (a register array must not be indexed with a runtime value)
         if (i == (rl & 31)) diagonal = __uint_as_float(kk[i]);
-      sm.kn[r] = a.normalize_qk ? rsqrtf(diagonal + 1e-6f) : 1.0f;
+      sts_f32(sm_kn + r * 4, a.normalize_qk ? rsqrtf(diagonal + 1e-6f) : 1.0f);
     }
   }
   __syncthreads();
-  const float br = sm.b[r], betar = sm.beta[r], knr = sm.kn[r];
-  if (half == 0) sm.scale1[r] = betar * __expf(br) * knr;
+  const float br = lds_f32(sm_b + r * 4), betar = lds_f32(sm_beta + r * 4), knr = lds_f32(sm_kn + r * 4);
+  if (half == 0) sts_f32(sm_scale1 + r * 4, betar * __expf(br) * knr);
   if (ok) {
     // ---- A (fp32, to the scratch) and M (bf16, to its operand tile) for this thread's 32 columns
     uint32_t mrow[16];
@@ -219,49 +234,71 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int s = half * 32 + i + e, sg = cb * 64 + s;
-        const float ratio = s <= rl ? __expf(br - sm.b[sg]) : 0.0f;
-        const float kns = sm.kn[sg];
-        scratch[a_transposed_index(cb, s, rl)] = s < rl ? betar * ratio * knr * kns * __uint_as_float(kk[i + e]) : 0.0f;
+        const float ratio = s <= rl ? __expf(br - lds_f32(sm_b + sg * 4)) : 0.0f;
+        const float kns = lds_f32(sm_kn + sg * 4);
+        sts_f32(scratch + a_transposed_index(cb, s, rl) * 4,
+                s < rl ? betar * ratio * knr * kns * __uint_as_float(kk[i + e]) : 0.0f);
         mv[e] = ratio * qn * kns * __uint_as_float(qk[i + e]);
       }
       mrow[i / 2] = pack_bf16(mv[0], mv[1]);
     }
-    uint8_t* mtile = smem + kRegM + r * 128 + (cb ? 8192 : 0);
+    const uint32_t mtile = base + kRegM + r * 128 + (cb ? 8192 : 0);
 #pragma unroll
     for (int q = 0; q < 4; ++q)
-      *reinterpret_cast<uint4*>(mtile + (((half * 4 + q) ^ (r & 7)) * 16)) =
-          make_uint4(mrow[4 * q], mrow[4 * q + 1], mrow[4 * q + 2], mrow[4 * q + 3]);
+      sts_b32x4(mtile + (((half * 4 + q) ^ (r & 7)) * 16), mrow[4 * q], mrow[4 * q + 1], mrow[4 * q + 2],
+                mrow[4 * q + 3]);
   }
   __syncthreads();
 
-  // ---- T = (I + A)^-1 by forward substitution, one thread per (chunk, column), right-looking: as
-  //      soon as entry s of the column is final it is folded into every later entry (independent
-  //      FMAs, one of them on the chain to the next step).  The 64 threads of a chunk read the same
-  //      elements of A, four at a time: the shared-memory pipe, one broadcast per cycle, is what
-  //      bounds this phase (2016 scalar loads per thread took 14000 cycles).
+  // ---- T = (I + A)^-1 by forward substitution, right-looking: as soon as entry s of a column is
+  //      final it is folded into every later entry (independent FMAs, one of them on the chain to
+  //      the next step).  Two threads per (chunk, column), neighbouring lanes: one owns the even
+  //      rows, the other the odd ones; the pivot of step s comes from the lane that owns row s by a
+  //      shuffle.  All threads of a chunk read the same elements of A, four rows at a time.
   {
-    float col[64];
-    const int c2 = threadIdx.x >> 6, jj = threadIdx.x & 63;
-    if (threadIdx.x < 128) {
+    // rows 2 i + parity of column jj, as 16 pairs (i even, i odd) for two-lane fp32 FMAs
+    uint64_t col[16];
+    const int c2 = threadIdx.x >> 7, jj = (threadIdx.x >> 1) & 63, parity = threadIdx.x & 1;
 #pragma unroll
-      for (int t = 0; t < 64; ++t) col[t] = t == jj ? 1.0f : 0.0f;
+    for (int p2 = 0; p2 < 16; ++p2)
+      col[p2] = f2_pack(4 * p2 + parity == jj ? 1.0f : 0.0f, 4 * p2 + 2 + parity == jj ? 1.0f : 0.0f);
+    // The elements of A for step s + 1 are requested before step s waits for its pivot, so the
+    // chain from one step to the next is shuffle -> FMA -> select and never a shared-memory load.
+    // pieces 0-3 and 4-7 of this thread's half of a column (the odd half has them exchanged)
+    const uint32_t a_lo = scratch + (c2 * 4096 + parity * 48) * 4, a_hi = scratch + (c2 * 4096 + parity * 16) * 4;
+    float4 ahead[8];
 #pragma unroll
-      for (int sc = 0; sc < 63; ++sc) {
-        const float c = col[sc];
+    for (int i4 = 0; i4 < 8; ++i4) ahead[i4] = lds_f32x4((i4 < 4 ? a_lo : a_hi) + i4 * 16);
 #pragma unroll
-        for (int t4 = (sc + 1) / 4; t4 < 16; ++t4) {
-          const float4 a4 = *reinterpret_cast<const float4*>(&scratch[a_transposed_index(c2, sc, t4 * 4)]);
-          const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+    for (int sc = 0; sc < 63; ++sc) {
+      float4 now[8];
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (t4 * 4 + e > sc) col[t4 * 4 + e] = fmaf(-av[e], c, col[t4 * 4 + e]);
-        }
+      for (int i4 = sc / 8; i4 < 8; ++i4) now[i4] = ahead[i4];
+      if (sc + 1 < 63) {
+#pragma unroll
+        for (int i4 = (sc + 1) / 8; i4 < 8; ++i4)
+          ahead[i4] = lds_f32x4((i4 < 4 ? a_lo : a_hi) + (sc + 1) * 256 + i4 * 16);
+      }
+      float lo, hi;
+      f2_unpack(col[sc >> 2], lo, hi);
+      const float mine = (sc >> 1) & 1 ? hi : lo;   // entry i = sc >> 1 of this thread
+      const float c = __shfl_sync(0xffffffffu, mine, (lane & ~1) | (sc & 1));
+      const uint64_t minus_c = f2_pack(-c, -c);
+      // own rows t = 2 i + parity > sc; A is zero at and above the pivot (strictly lower
+      // triangular), so whole groups of four rows are folded in from the pivot's group on
+#pragma unroll
+      for (int i4 = sc / 8; i4 < 8; ++i4) {
+        col[2 * i4] = f2_fma(f2_pack(now[i4].x, now[i4].y), minus_c, col[2 * i4]);
+        col[2 * i4 + 1] = f2_fma(f2_pack(now[i4].z, now[i4].w), minus_c, col[2 * i4 + 1]);
       }
     }
     __syncthreads();
-    if (threadIdx.x < 128) {
 #pragma unroll
-      for (int t = 0; t < 64; ++t) scratch[t_index(c2 * 64 + t, jj)] = col[t];
+    for (int p2 = 0; p2 < 16; ++p2) {
+      float lo, hi;
+      f2_unpack(col[p2], lo, hi);
+      sts_f32(scratch + t_index(c2 * 64 + 4 * p2 + parity, jj) * 4, lo);
+      sts_f32(scratch + t_index(c2 * 64 + 4 * p2 + 2 + parity, jj) * 4, hi);
     }
   }
   __syncthreads();
@@ -272,14 +309,14 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
     for (int v = 0; v < 8; ++v) {
       const int piece = half * 8 + v;   // columns piece*4 .. +3 of this row
-      const float4 t4 = *reinterpret_cast<const float4*>(&scratch[r * 64 + ((piece ^ (r & 15)) << 2)]);
+      const float4 t4 = lds_f32x4(scratch + (r * 64 + ((piece ^ (r & 15)) << 2)) * 4);
       const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
       float x1[4], x2[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int sg = cb * 64 + piece * 4 + e;
-        x1[e] = tv[e] * sm.scale1[sg];
-        x2[e] = tv[e] * sm.beta[sg];
+        x1[e] = tv[e] * lds_f32(sm_scale1 + sg * 4);
+        x2[e] = tv[e] * lds_f32(sm_beta + sg * 4);
       }
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
@@ -292,12 +329,9 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const uint32_t piece = ((half * 4 + q) ^ (r & 7)) * 16;
-      *reinterpret_cast<uint4*>(smem + kRegT1 + row_off + piece) =
-          make_uint4(t1[4 * q], t1[4 * q + 1], t1[4 * q + 2], t1[4 * q + 3]);
-      *reinterpret_cast<uint4*>(smem + kRegT2H + row_off + piece) =
-          make_uint4(t2h[4 * q], t2h[4 * q + 1], t2h[4 * q + 2], t2h[4 * q + 3]);
-      *reinterpret_cast<uint4*>(smem + kRegT2L + row_off + piece) =
-          make_uint4(t2l[4 * q], t2l[4 * q + 1], t2l[4 * q + 2], t2l[4 * q + 3]);
+      sts_b32x4(base + kRegT1 + row_off + piece, t1[4 * q], t1[4 * q + 1], t1[4 * q + 2], t1[4 * q + 3]);
+      sts_b32x4(base + kRegT2H + row_off + piece, t2h[4 * q], t2h[4 * q + 1], t2h[4 * q + 2], t2h[4 * q + 3]);
+      sts_b32x4(base + kRegT2L + row_off + piece, t2l[4 * q], t2l[4 * q + 1], t2l[4 * q + 2], t2l[4 * q + 3]);
     }
   }
   fence_proxy_async();
@@ -330,14 +364,14 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   }
   ok = __all_sync(0xffffffffu, ok && mbar_wait(&sm.mma_done, 1, status, 62));
   tc_fence_after();
-  const float tail = __expf(sm.b[cb * 64 + 63] - br) * knr;   // Kt = k . (c_C / c) . kn
+  const float tail = __expf(lds_f32(sm_b + (cb * 64 + 63) * 4) - br) * knr;   // Kt = k . (c_C / c) . kn
   if (ok) {
     // W row -> bf16 operand tile (over the raw values, which the U products no longer need)
     uint32_t x[2][32];
     tmem_ld32(tmem + lane_base + 256 + half * 64, x[0]);
     tmem_ld32(tmem + lane_base + 256 + half * 64 + 32, x[1]);
     tmem_wait_ld();
-    uint8_t* wrow = smem + kRegV + half * 16384 + r * 128;
+    const uint32_t wrow = base + kRegV + half * 16384 + r * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       uint32_t w[4];
@@ -346,14 +380,14 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int i = c * 8 + e * 2;
         w[e] = pack_bf16(__uint_as_float(x[i / 32][i % 32]), __uint_as_float(x[i / 32][i % 32 + 1]));
       }
-      *reinterpret_cast<uint4*>(wrow + ((c ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+      sts_b32x4(wrow + ((c ^ (r & 7)) * 16), w[0], w[1], w[2], w[3]);
     }
     // U row -> staging tile in record order (over the scratch, which nobody reads any more)
     tmem_ld32(tmem + lane_base + 384 + half * 64, x[0]);
     tmem_ld32(tmem + lane_base + 384 + half * 64 + 32, x[1]);
     tmem_wait_ld();
     {
-      uint8_t* urow = smem + kRegQ + cb * 16384 + half * 8192 + rl * 128;
+      const uint32_t urow = base + kRegQ + cb * 16384 + half * 8192 + rl * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t w[4];
@@ -362,39 +396,26 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const int i = c * 8 + e * 2;
           w[e] = pack_bf16(__uint_as_float(x[i / 32][i % 32]), __uint_as_float(x[i / 32][i % 32 + 1]));
         }
-        *reinterpret_cast<uint4*>(urow + ((c ^ (rl & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        sts_b32x4(urow + ((c ^ (rl & 7)) * 16), w[0], w[1], w[2], w[3]);
       }
     }
     // Kt row: scaled keys, in place (operand of Pn, and the record's tile)
-    uint8_t* krow = smem + kRegK + half * 16384 + r * 128;
+    const uint32_t krow = base + kRegK + half * 16384 + r * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const uint32_t piece = (c ^ (r & 7)) * 16;
-      uint4 v = *reinterpret_cast<const uint4*>(krow + piece);
+      uint4 v = lds_b32x4(krow + piece);
       v.x = pack_bf16(bf16_lo(v.x) * tail, bf16_hi(v.x) * tail);
       v.y = pack_bf16(bf16_lo(v.y) * tail, bf16_hi(v.y) * tail);
       v.z = pack_bf16(bf16_lo(v.z) * tail, bf16_hi(v.z) * tail);
       v.w = pack_bf16(bf16_lo(v.w) * tail, bf16_hi(v.w) * tail);
-      *reinterpret_cast<uint4*>(krow + piece) = v;
+      sts_b32x4(krow + piece, v.x, v.y, v.z, v.w);
     }
   }
   tc_fence_before();
   fence_proxy_async();
   __syncthreads();
   tc_fence_after();
-
-  // the tiles that are final leave now, as linear bulk copies from shared memory
-  uint8_t* pair_rec = records + ((static_cast<size_t>(b) * a.value_heads + h) * chunks + pair * 2) * GdnRecord::bytes(dv);
-  if (threadIdx.x == 32 && ok) {
-    for (int v = 0; v < 2 && pair * 2 + v < chunks; ++v) {
-      uint8_t* out = pair_rec + static_cast<size_t>(v) * GdnRecord::bytes(dv);
-      bulk_store(out + GdnRecord::kCommon + GdnRecord::kUH, smem + kRegQ + v * 16384, 16384);
-      bulk_store(out + GdnRecord::kKT, smem + kRegK + v * 8192, 8192);
-      bulk_store(out + GdnRecord::kKT + 8192, smem + kRegK + 16384 + v * 8192, 8192);
-      bulk_store(out + GdnRecord::kMM, smem + kRegM + v * 16384, 8192);
-    }
-    bulk_store_commit();
-  }
 
   // ---- Pn(chunk) = Kt^T W over the chunk's 64 tokens; M W through the two views of M
   if (warp == 0 && ok) {
@@ -419,8 +440,33 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
     __syncwarp();
   }
+  // the raw query row again for Qt, from global memory (the TMA load pulled it through L2 a few
+  // microseconds ago), requested before the wait for the last products so that it hides there
+  uint4 qraw[8];
+  {
+    const bool live_token = t0 + r < a.tokens;
+    const uint4* qsrc = reinterpret_cast<const uint4*>(
+        static_cast<const __nv_bfloat16*>(a.q) + (static_cast<size_t>(b) * a.tokens + (live_token ? t0 + r : 0)) * a.qk_token +
+        static_cast<size_t>(kh) * kGdnKeyDim + half * 64);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) qraw[c] = live_token ? __ldg(qsrc + c) : make_uint4(0, 0, 0, 0);
+  }
   ok = __all_sync(0xffffffffu, ok && mbar_wait(&sm.mma_done, 0, status, 63));
   tc_fence_after();
+  // The tiles that are final leave now, as linear bulk copies from shared memory -- after the
+  // last products, not before them: bulk copies in flight made those products twice as slow.
+  uint8_t* pair_rec = records + ((static_cast<size_t>(b) * a.value_heads + h) * chunks + pair * 2) * GdnRecord::bytes(dv);
+  if (threadIdx.x == 32 && ok) {
+    for (int v = 0; v < 2 && pair * 2 + v < chunks; ++v) {
+      uint8_t* out = pair_rec + static_cast<size_t>(v) * GdnRecord::bytes(dv);
+      bulk_store(out + GdnRecord::kCommon + GdnRecord::kUH, smem + kRegQ + v * 16384, 16384);
+      bulk_store(out + GdnRecord::kKT, smem + kRegK + v * 8192, 8192);
+      bulk_store(out + GdnRecord::kKT + 8192, smem + kRegK + 16384 + v * 8192, 8192);
+      bulk_store(out + GdnRecord::kMM, smem + kRegM + v * 16384, 8192);
+    }
+    bulk_store_commit();
+  }
+
   if (ok) {
     uint32_t x[2][32];
     // Pn rows: row r = key index of the output, this thread's 64 input keys, for both chunks; staged
@@ -430,7 +476,7 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tmem_ld32(tmem + lane_base + view * 128 + half * 64, x[0]);
       tmem_ld32(tmem + lane_base + view * 128 + half * 64 + 32, x[1]);
       tmem_wait_ld();
-      uint8_t* prow = smem + kRegT1 + view * 32768 + half * 16384 + r * 128;
+      const uint32_t prow = base + kRegT1 + view * 32768 + half * 16384 + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t w[4];
@@ -439,7 +485,7 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const int i = c * 8 + e * 2;
           w[e] = pack_bf16(-__uint_as_float(x[i / 32][i % 32]), -__uint_as_float(x[i / 32][i % 32 + 1]));
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        sts_b32x4(prow + ((c ^ (r & 7)) * 16), w[0], w[1], w[2], w[3]);
       }
     }
     // Qt = c q^ - M W, staged over W (dead since the last products)
@@ -448,16 +494,10 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     tmem_wait_ld();
     {
       const float cq = __expf(br) * qn;
-      uint8_t* qrow_out = smem + kRegV + cb * 16384 + half * 8192 + rl * 128;
-      // the raw query row again, from global memory (the TMA load has just pulled it through L2)
-      const bool live_token = t0 + r < a.tokens;
-      const uint4* qsrc = reinterpret_cast<const uint4*>(
-          static_cast<const __nv_bfloat16*>(a.q) + (static_cast<size_t>(b) * a.tokens + (live_token ? t0 + r : 0)) * a.qk_token +
-          static_cast<size_t>(kh) * kGdnKeyDim + half * 64);
+      const uint32_t qrow_out = base + kRegV + cb * 16384 + half * 8192 + rl * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        const uint4 qv = live_token ? __ldg(qsrc + c) : make_uint4(0, 0, 0, 0);
-        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+        const uint32_t qw[4] = {qraw[c].x, qraw[c].y, qraw[c].z, qraw[c].w};
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -466,7 +506,7 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           w[e] = pack_bf16(cq * bf16_lo(q2) - __uint_as_float(x[i / 32][i % 32]),
                            cq * bf16_hi(q2) - __uint_as_float(x[i / 32][i % 32 + 1]));
         }
-        *reinterpret_cast<uint4*>(qrow_out + ((c ^ (rl & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        sts_b32x4(qrow_out + ((c ^ (rl & 7)) * 16), w[0], w[1], w[2], w[3]);
       }
     }
     if (live_chunk && rl == 63 && half == 0) *reinterpret_cast<float*>(rec + GdnRecord::kGM) = __expf(br);
@@ -496,19 +536,24 @@ gdn_prepare_sm100(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
 bool gdn_prepare_sm100_supported(const GdnArgs& a) { return a.value_dim == kGdnSliceCols; }
 
-cudaError_t gdn_prepare_sm100_launch(cudaStream_t stream, const GdnArgs& a, void* records, int chunks,
-                                     uint32_t* status) {
-  CUtensorMap map_q, map_k, map_v;
-  if (!make_token_map(&map_q, a.q, a.key_heads * kGdnKeyDim, a.tokens, a.batch, a.qk_token, 128) ||
-      !make_token_map(&map_k, a.k, a.key_heads * kGdnKeyDim, a.tokens, a.batch, a.qk_token, 128) ||
-      !make_token_map(&map_v, a.v, a.value_heads * a.value_dim, a.tokens, a.batch, a.v_token, 128))
-    return cudaErrorInvalidValue;
+bool gdn_prepare_sm100_maps(const GdnArgs& a, CUtensorMap maps[3]) {
+  return make_token_map(&maps[0], a.q, a.key_heads * kGdnKeyDim, a.tokens, a.batch, a.qk_token, 128) &&
+         make_token_map(&maps[1], a.k, a.key_heads * kGdnKeyDim, a.tokens, a.batch, a.qk_token, 128) &&
+         make_token_map(&maps[2], a.v, a.value_heads * a.value_dim, a.tokens, a.batch, a.v_token, 128);
+}
+
+// Chunk pairs first_pair .. first_pair + pairs - 1 of every (sequence, head); `chunks` is the whole
+// sequence's chunk count (the stride of the record array).
+cudaError_t gdn_prepare_sm100_launch(cudaStream_t stream, const CUtensorMap maps[3], const GdnArgs& a,
+                                     void* records, int first_pair, int pairs, int chunks, uint32_t* status) {
   const size_t smem = 1024 + kRegSmall + sizeof(PrepSmall);
-  cudaError_t e = cudaFuncSetAttribute(gdn_prepare_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
-  gdn_prepare_sm100<<<dim3((chunks + 1) / 2, a.value_heads, a.batch), kPrepThreads, smem, stream>>>(
-      map_q, map_k, map_v, a, static_cast<uint8_t*>(records), chunks, status);
+  if (first_pair == 0) {   // (every call starts with the piece at pair 0)
+    cudaError_t e = cudaFuncSetAttribute(gdn_prepare_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+  }
+  gdn_prepare_sm100<<<dim3(pairs, a.value_heads, a.batch), kPrepThreads, smem, stream>>>(
+      maps[0], maps[1], maps[2], a, static_cast<uint8_t*>(records), first_pair, chunks, status);
   return cudaGetLastError();
 }
 

@@ -59,7 +59,10 @@ struct ScanBarriers {
 __device__ __forceinline__ void arithmetic_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kScanThreads, 1)
-gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint32_t* status) {
+gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, int chunks, int all_chunks,
+               uint32_t* status) {
+  // walks chunks first_chunk .. first_chunk + chunks - 1 of the sequence's all_chunks; the state is
+  // read from and left in a.state, so consecutive launches continue one another
   extern __shared__ uint8_t scan_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(scan_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -69,7 +72,7 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   const int dv = a.value_dim;
   const size_t record_bytes = GdnRecord::bytes(dv);
-  const uint8_t* rec0 = records + (static_cast<size_t>(b) * a.value_heads + h) * chunks * record_bytes;
+  const uint8_t* rec0 = records + ((static_cast<size_t>(b) * a.value_heads + h) * all_chunks + first_chunk) * record_bytes;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kScanStages; ++s) {
@@ -216,7 +219,7 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
 #pragma unroll
           for (int pass = 0; pass < 4; ++pass) {
             const int row = pass * 16 + u256 / 16, piece = u256 % 16;
-            const int t = e * kGdnChunk + row;
+            const int t = (first_chunk + e) * kGdnChunk + row;
             if (t < a.tokens) {
               const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv +
                                  slice * kGdnSliceCols + piece * 8;
@@ -228,7 +231,7 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int chunks, uint3
       } else if (ok) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int t = e * kGdnChunk + half * 32 + i;
+          const int t = (first_chunk + e) * kGdnChunk + half * 32 + i;
           if (t < a.tokens) {
             const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv + j;
             const float value = a.round ? bf16_round(__uint_as_float(o[i])) : __uint_as_float(o[i]);
@@ -299,14 +302,16 @@ size_t gdn_scan_smem_bytes() {
   return 1024 + kScanStages * kStageBytes + kOutTileBytes + sizeof(ScanBarriers);
 }
 
-cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int chunks,
-                            uint32_t* status) {
+cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int first_chunk,
+                            int chunks, int all_chunks, uint32_t* status) {
   const size_t smem = gdn_scan_smem_bytes();
-  cudaError_t e = cudaFuncSetAttribute(gdn_scan_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
+  if (first_chunk == 0) {   // (every call starts with the piece at chunk 0)
+    cudaError_t e = cudaFuncSetAttribute(gdn_scan_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+  }
   gdn_scan_sm100<<<dim3(a.value_dim / kGdnSliceCols, a.value_heads, a.batch), kScanThreads, smem, stream>>>(
-      a, static_cast<const uint8_t*>(records), chunks, status);
+      a, static_cast<const uint8_t*>(records), first_chunk, chunks, all_chunks, status);
   return cudaGetLastError();
 }
 

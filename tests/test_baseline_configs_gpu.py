@@ -138,3 +138,38 @@ def test_delta_net_16384_prefill_then_256_steps():
         assert np.all(error <= 1.5e-4 + 0.015 * np.abs(want) + 2.0 ** -7 * np.abs(want).max())
         state_error = np.abs(state[bi, hi].cpu().numpy() - ref_state[0, 0]).max()
         assert state_error <= 2e-2, ("state after the steps", bi, hi, state_error)
+
+
+def test_delta_net_pieces_with_a_ragged_tail():
+    """A sequence long enough that the prefill runs as overlapping pieces (prepare of one piece
+    beside the scan of the one before, on two streams) whose last piece is short and ends in an
+    odd chunk count and a partial chunk: 9001 tokens = 140 chunks + 41 tokens, from a non-zero
+    state, called twice back to back on the same workspace.  One (sequence, head) unit against the
+    token-recurrent oracle, and the second call's output identical to the first's."""
+    b, t, h, d = 2, 9001, 16, 128
+    gen = torch.Generator(device="cuda").manual_seed(31)
+
+    def unit(shape):
+        return torch.nn.functional.normalize(torch.randn(*shape, device="cuda", generator=gen), dim=-1)
+
+    q, k = unit((b, t, h, d)).bfloat16(), unit((b, t, h, d)).bfloat16()
+    v = torch.randn(b, t, h, d, device="cuda", generator=gen).bfloat16()
+    g = torch.sigmoid(torch.randn(b, t, h, device="cuda", generator=gen) * 2 + 2)
+    beta = torch.sigmoid(torch.randn(b, t, h, device="cuda", generator=gen))
+    start = torch.randn(b, h, d, d, device="cuda", generator=gen) * 0.1
+    state, again = start.clone(), start.clone()
+    out = gdn_prefill(q, k, v, g, beta, state, chunked=True)
+    out_again = gdn_prefill(q, k, v, g, beta, again, chunked=True)
+    torch.cuda.synchronize()
+    assert _capi.kernel_status() == 0
+    assert torch.equal(out, out_again) and torch.equal(state, again)
+    bi, hi = 1, 5
+    one = lambda x: bf16_bits(x[bi:bi + 1, :, hi:hi + 1])
+    ref_state = start[bi:bi + 1, hi:hi + 1].cpu().numpy().copy()
+    want = oracle.gdn_recurrence(one(q), one(k), one(v), g[bi:bi + 1, :, hi:hi + 1].cpu().numpy(),
+                                 beta[bi:bi + 1, :, hi:hi + 1].cpu().numpy(), ref_state, True, 1.0, True)
+    want = bits_to_float(want)[0, :, 0]
+    got = bits_to_float(bf16_bits(out[bi, :, hi]))
+    error = np.abs(got - want)
+    assert error.max() <= 2e-2, (int(error.max(1).argmax()), error.max())
+    assert np.abs(state[bi, hi].cpu().numpy() - ref_state[0, 0]).max() <= 2e-2
