@@ -431,12 +431,26 @@ size_t gdn_recurrence_bwd_workspace_bytes(int batch, int tokens, int value_heads
   const size_t chunks = (tokens + kChunk - 1) / kChunk;
   const size_t slice = static_cast<size_t>(kRows) * kWarps * kCols;
   const size_t per_token = static_cast<size_t>(batch) * tokens * value_heads * tiles;
-  return sizeof(float) * (ctas * (chunks + kChunk + 1) * slice + per_token * (2 * key_dim + 3));
+  const size_t sequential = sizeof(float) * (ctas * (chunks + kChunk + 1) * slice + per_token * (2 * key_dim + 3));
+  const size_t chunked = key_dim == 128 && value_dim == 128 ? gdn_bwd_chunked_workspace_bytes(batch, tokens, value_heads) : 0;
+  return sequential > chunked ? sequential : chunked;
 }
 
 cudaError_t gdn_recurrence_bwd(cudaStream_t stream, GdnBwdArgs a, float* dq_out, float* dk_out,
                                size_t dqk_token, float* da, float* db, float* d_a_log,
                                float* d_dt_bias, void* workspace) {
+  if (gdn_bwd_chunked_supported(a)) {
+    cudaError_t e = gdn_bwd_chunked(stream, a, workspace, kernel_status_word());
+    if (e != cudaSuccess) return e;
+    gdn_gather_qk_kernel<<<dim3(a.batch * a.tokens, a.key_heads), 128, 0, stream>>>(
+        a.qk_partials, a.key_heads, a.value_heads, a.key_dim, 1, dq_out, dk_out, dqk_token);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    gdn_gather_scalar_kernel<<<a.value_heads, 256, 0, stream>>>(
+        a.scalar_partials, static_cast<long long>(a.batch) * a.tokens, a.value_heads, 1, da, db, d_a_log,
+        d_dt_bias);
+    return cudaGetLastError();
+  }
   const int tiles = (a.value_dim + kCols - 1) / kCols;
   const size_t ctas = static_cast<size_t>(a.batch) * a.value_heads * tiles;
   const size_t chunks = (a.tokens + kChunk - 1) / kChunk;

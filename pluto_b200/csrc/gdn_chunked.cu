@@ -36,7 +36,7 @@ namespace pluto {
 // gdn_scan_sm100.cu
 size_t gdn_scan_smem_bytes();
 cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int first_chunk,
-                            int chunks, int all_chunks, uint32_t* status);
+                            int chunks, int all_chunks, float* state_dump, uint32_t* status);
 // gdn_prepare_sm100.cu
 bool gdn_prepare_sm100_supported(const GdnArgs& a);
 bool gdn_prepare_sm100_maps(const GdnArgs& a, CUtensorMap maps[3]);
@@ -92,7 +92,7 @@ int gdn_piece_pairs(const GdnArgs& a, int pairs) {
 }
 
 cudaError_t gdn_prepare_and_scan(cudaStream_t stream, const GdnArgs& a, uint8_t* records, int chunks,
-                                 uint32_t* status) {
+                                 float* state_dump, uint32_t* status) {
   CUtensorMap maps[3];
   if (!gdn_prepare_sm100_maps(a, maps)) return cudaErrorInvalidValue;
   const int pairs = (chunks + 1) / 2;
@@ -100,7 +100,7 @@ cudaError_t gdn_prepare_and_scan(cudaStream_t stream, const GdnArgs& a, uint8_t*
   if (per_piece >= pairs) {
     cudaError_t e = gdn_prepare_sm100_launch(stream, maps, a, records, 0, pairs, chunks, status);
     if (e != cudaSuccess) return e;
-    return gdn_scan_launch(stream, a, records, 0, chunks, chunks, status);
+    return gdn_scan_launch(stream, a, records, 0, chunks, chunks, state_dump, status);
   }
   GdnLanes* l = gdn_lanes_for_current_device();
   if (l == nullptr) return cudaErrorInitializationError;
@@ -113,7 +113,7 @@ cudaError_t gdn_prepare_and_scan(cudaStream_t stream, const GdnArgs& a, uint8_t*
     if (e == cudaSuccess) e = cudaEventRecord(l->prepared[piece], stream);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(l->scan, l->prepared[piece], 0);
     if (e == cudaSuccess)
-      e = gdn_scan_launch(l->scan, a, records, first * 2, min(n * 2, chunks - first * 2), chunks, status);
+      e = gdn_scan_launch(l->scan, a, records, first * 2, min(n * 2, chunks - first * 2), chunks, state_dump, status);
   }
   // (joined even after a failed launch, so that nothing of this call is left running unordered)
   cudaError_t joined = cudaEventRecord(l->scanned, l->scan);
@@ -727,7 +727,7 @@ cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, 
   if (gdn_prepare_sm100_supported(a)) {
     uint8_t* records = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(workspace) + 1023) &
                                                   ~static_cast<uintptr_t>(1023));
-    return gdn_prepare_and_scan(stream, a, records, chunks, status);
+    return gdn_prepare_and_scan(stream, a, records, chunks, nullptr, status);
   }
   cudaError_t e = cudaFuncSetAttribute(gdn_chunk_prepare, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(PrepareSmem)));
@@ -746,7 +746,7 @@ cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, 
         static_cast<const uint8_t*>(workspace), records, chunks, a.value_heads, a.value_dim);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return gdn_scan_launch(stream, a, records, 0, chunks, chunks, status);
+    return gdn_scan_launch(stream, a, records, 0, chunks, chunks, nullptr, status);
   }
   const size_t smem = kRecStages * kStageBytes + sizeof(RecBarriers);
   e = cudaFuncSetAttribute(gdn_chunk_recurrence, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -755,6 +755,15 @@ cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, 
   gdn_chunk_recurrence<<<dim3(a.value_dim / kSliceCols, a.value_heads, a.batch), 96, smem, stream>>>(
       a, static_cast<const uint8_t*>(workspace), chunks, status);
   return cudaGetLastError();
+}
+
+// The tcgen05 prefill (value width 128) with the state at every chunk's start written out as
+// well: the forward half of the chunked backward pass.  `records` is 1024-byte aligned and holds
+// gdn_chunked_workspace_bytes(...) bytes.
+cudaError_t gdn_chunked_with_states(cudaStream_t stream, const GdnArgs& a, void* records, float* state_dump,
+                                    uint32_t* status) {
+  if (!gdn_prepare_sm100_supported(a)) return cudaErrorInvalidValue;
+  return gdn_prepare_and_scan(stream, a, static_cast<uint8_t*>(records), (a.tokens + kC - 1) / kC, state_dump, status);
 }
 
 }  // namespace pluto

@@ -60,9 +60,10 @@ __device__ __forceinline__ void arithmetic_sync() { asm volatile("bar.sync 1, 25
 
 __global__ void __launch_bounds__(kScanThreads, 1)
 gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, int chunks, int all_chunks,
-               uint32_t* status) {
+               float* __restrict__ state_dump, uint32_t* status) {
   // walks chunks first_chunk .. first_chunk + chunks - 1 of the sequence's all_chunks; the state is
-  // read from and left in a.state, so consecutive launches continue one another
+  // read from and left in a.state, so consecutive launches continue one another.  state_dump (optional, for the backward pass): the
+  // state at the START of every chunk, transposed, [sequence, head, chunk, value column, key]
   extern __shared__ uint8_t scan_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(scan_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -253,6 +254,17 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, 
         tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
         tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
         tmem_wait_ld();
+        if (state_dump != nullptr) {
+          float4* dst = reinterpret_cast<float4*>(
+              state_dump + ((((static_cast<size_t>(b) * a.value_heads + h) * all_chunks + first_chunk + c) * dv + j) *
+                            kGdnKeyDim + half * 64));
+#pragma unroll
+          for (int g = 0; g < 2; ++g)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              dst[g * 8 + i / 4] = make_float4(__uint_as_float(s[g][i]), __uint_as_float(s[g][i + 1]),
+                                               __uint_as_float(s[g][i + 2]), __uint_as_float(s[g][i + 3]));
+        }
 #pragma unroll
         for (int g = 0; g < 2; ++g)
 #pragma unroll
@@ -296,6 +308,170 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, 
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Reverse scan of the backward pass.  With the chunk's records, the gradient of the state at the
+// chunk's start follows from the one at its end by the transposed map of the forward step,
+//     dS_0 = gamma dS_C + Pn^T dS_C + Qt^T dO,
+// again ONE dependent product per chunk.  The state gradient lives in TMEM transposed like the
+// state (lane = value column, columns = keys), so per chunk: acc (= gamma dS^T) += dO^T Qt
+// (token-major operands, as U^T Kt forward) + dS^T_bf16 Pn (Pn now read as an MN-major operand:
+// its 64-column slabs are 16384 bytes apart, 16 keys = 2048 bytes).  What the per-chunk part of
+// the backward pass needs is the gradient at every chunk's END: dumped, transposed,
+// [sequence, head, chunk, value column, key], before the chunk's step.  One CTA per (sequence, head,
+// 128 value columns); warp roles as in the forward scan, no output products.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRevStages = 3;
+constexpr uint32_t kRevPn = 0, kRevQt = 32768, kRevDo = 49152, kRevGm = 65536, kRevStageBytes = 66560;
+
+struct RevBarriers {
+  uint64_t full[kRevStages], empty[kRevStages];
+  uint64_t sbf_ready;     // 8 warp arrivals
+  uint64_t state_done;    // tcgen05.commit
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(kScanThreads, 1)
+gdn_scan_bwd_sm100(const __grid_constant__ CUtensorMap map_do, int value_heads,
+                   const uint8_t* __restrict__ records, int chunks, float* __restrict__ dstate_dump,
+                   uint32_t* status) {
+  extern __shared__ uint8_t scan_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(scan_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  RevBarriers* bar = reinterpret_cast<RevBarriers*>(smem + kRevStages * kRevStageBytes);
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  constexpr int dv = kGdnSliceCols;
+  const size_t record_bytes = GdnRecord::bytes(dv);
+  const size_t unit = static_cast<size_t>(b) * value_heads + h;
+  const uint8_t* rec0 = records + unit * chunks * record_bytes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRevStages; ++s) {
+      mbar_init(&bar->full[s], 1);
+      mbar_init(&bar->empty[s], 1);
+    }
+    mbar_init(&bar->sbf_ready, 8);
+    mbar_init(&bar->state_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int n = 0; n < chunks && ok; ++n) {
+        const int chunk = chunks - 1 - n, st = n % kRevStages, use = n / kRevStages;
+        if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, status, 44);
+        if (!ok) break;
+        uint8_t* dst = smem + st * kRevStageBytes;
+        const uint8_t* rec = rec0 + static_cast<size_t>(chunk) * record_bytes;
+        mbar_expect_tx(&bar->full[st], 32768 + 16384 + 16 + 16384);
+        bulk_load(dst + kRevPn, rec + GdnRecord::kPN, 32768, &bar->full[st]);
+        bulk_load(dst + kRevQt, rec + GdnRecord::kQT, 16384, &bar->full[st]);
+        bulk_load(dst + kRevGm, rec + GdnRecord::kGM, 16, &bar->full[st]);
+        for (int s = 0; s < 2; ++s)
+          tma_load_3d(dst + kRevDo + s * 8192, &map_do, h * dv + s * 64, chunk * kGdnChunk, b, &bar->full[st]);
+      }
+      for (int n = max(0, chunks - kRevStages); n < chunks; ++n)
+        mbar_wait(&bar->full[n % kRevStages], (n / kRevStages) & 1, status, 45);
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t kIdescTokens = umma_idesc_bf16_majors(128, 128, true, true);    // dO^T Qt
+    constexpr uint32_t kIdescPn = umma_idesc_bf16_majors(128, 128, false, true);       // dS^T Pn
+    bool ok = true;
+    for (int n = 0; n < chunks && ok; ++n) {
+      const int st = n % kRevStages, buf = n & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->full[st], (n / kRevStages) & 1, status, 46));
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->sbf_ready, n & 1, status, 47));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t base = smem_u32(smem + st * kRevStageBytes);
+      const uint32_t sbf = tmem + kColSbf + buf * 64;
+      const uint64_t d_out = umma_desc_sw128(base + kRevDo, 8192, 1024);
+      const uint64_t qt = umma_desc_sw128(base + kRevQt, 8192, 1024);
+      const uint64_t pn = umma_desc_sw128(base + kRevPn, 16384, 1024);
+      if (elect_one()) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + kColState, d_out + ks * 128, qt + ks * 128, kIdescTokens, true);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + kColState, sbf + ks * 8, pn + ks * 128, kIdescPn, true);
+        tc_commit(&bar->state_done);
+        tc_commit(&bar->empty[st]);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3, half = (warp - 2) / 4;
+    const int j = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    {
+      uint32_t zero[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) zero[i] = 0u;
+      tmem_st32(tmem + lane_base + kColState + half * 64, zero);
+      tmem_st32(tmem + lane_base + kColState + half * 64 + 32, zero);
+      tmem_wait_st();
+    }
+    bool ok = true;
+    for (int n = 0; n < chunks; ++n) {
+      const int chunk = chunks - 1 - n, st = n % kRevStages, buf = n & 1;
+      if (n > 0) ok = ok && mbar_wait(&bar->state_done, (n - 1) & 1, status, 48);
+      ok = __all_sync(0xffffffffu, ok && mbar_wait(&bar->full[st], (n / kRevStages) & 1, status, 49));
+      if (ok) {
+        tc_fence_after();
+        const float gamma = *reinterpret_cast<const float*>(smem + st * kRevStageBytes + kRevGm);
+        uint32_t s[2][32], packed[32];
+        tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
+        tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
+        tmem_wait_ld();
+        float4* dst = reinterpret_cast<float4*>(dstate_dump + (((unit * chunks + chunk) * dv + j) * kGdnKeyDim + half * 64));
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            dst[g * 8 + i / 4] = make_float4(__uint_as_float(s[g][i]), __uint_as_float(s[g][i + 1]),
+                                             __uint_as_float(s[g][i + 2]), __uint_as_float(s[g][i + 3]));
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float x = __uint_as_float(s[g][i]), y = __uint_as_float(s[g][i + 1]);
+            packed[g * 16 + i / 2] = pack_bf16(x, y);
+            s[g][i] = __float_as_uint(x * gamma);
+            s[g][i + 1] = __float_as_uint(y * gamma);
+          }
+        tmem_st32(tmem + lane_base + kColSbf + buf * 64 + half * 32, packed);
+        tmem_st32(tmem + lane_base + kColState + half * 64, s[0]);
+        tmem_st32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
+        tmem_wait_st();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->sbf_ready);
+    }
+    // the last products must have landed before the tensor memory is given back
+    ok = __all_sync(0xffffffffu, ok && mbar_wait(&bar->state_done, (chunks - 1) & 1, status, 43));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
 }  // namespace
 
 size_t gdn_scan_smem_bytes() {
@@ -303,7 +479,7 @@ size_t gdn_scan_smem_bytes() {
 }
 
 cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* records, int first_chunk,
-                            int chunks, int all_chunks, uint32_t* status) {
+                            int chunks, int all_chunks, float* state_dump, uint32_t* status) {
   const size_t smem = gdn_scan_smem_bytes();
   if (first_chunk == 0) {   // (every call starts with the piece at chunk 0)
     cudaError_t e = cudaFuncSetAttribute(gdn_scan_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -311,7 +487,23 @@ cudaError_t gdn_scan_launch(cudaStream_t stream, const GdnArgs& a, const void* r
     if (e != cudaSuccess) return e;
   }
   gdn_scan_sm100<<<dim3(a.value_dim / kGdnSliceCols, a.value_heads, a.batch), kScanThreads, smem, stream>>>(
-      a, static_cast<const uint8_t*>(records), first_chunk, chunks, all_chunks, status);
+      a, static_cast<const uint8_t*>(records), first_chunk, chunks, all_chunks, state_dump, status);
+  return cudaGetLastError();
+}
+
+// dcore_bf16: the output gradient as bf16 [batch, tokens, value_heads * 128]; dstate_dump as above.
+cudaError_t gdn_scan_bwd_launch(cudaStream_t stream, const void* dcore_bf16, const void* records, int batch,
+                                int tokens, int value_heads, int chunks, float* dstate_dump, uint32_t* status) {
+  CUtensorMap map_do;
+  if (!make_token_map(&map_do, dcore_bf16, value_heads * kGdnSliceCols, tokens, batch,
+                      static_cast<size_t>(value_heads) * kGdnSliceCols, 64))
+    return cudaErrorInvalidValue;
+  const size_t smem = 1024 + kRevStages * kRevStageBytes + sizeof(RevBarriers);
+  cudaError_t e = cudaFuncSetAttribute(gdn_scan_bwd_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  gdn_scan_bwd_sm100<<<dim3(1, value_heads, batch), kScanThreads, smem, stream>>>(
+      map_do, value_heads, static_cast<const uint8_t*>(records), chunks, dstate_dump, status);
   return cudaGetLastError();
 }
 

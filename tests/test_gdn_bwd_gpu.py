@@ -72,10 +72,13 @@ def test_all_gradients_match_numerical_bptt(shape, tol):
     assert np.abs(actual[0][:channels]).sum() > 1e-5      # the first token still gets a gradient
 
 
-@pytest.mark.parametrize("shape", [(40, 2, 4, 32, 48, 4), (150, 2, 4, 128, 128, 4), (97, 1, 2, 64, 40, 3)])
+@pytest.mark.parametrize("shape", [(40, 2, 4, 32, 48, 4), (150, 2, 4, 128, 128, 4), (97, 1, 2, 64, 40, 3),
+                                   (333, 1, 2, 128, 128, 4), (512, 2, 2, 128, 128, 4)])
 def test_backward_matches_oracle_across_chunk_boundaries(shape):
     """Sequences longer than one 64-token chunk (state recompute from checkpoints), grouped value
-    heads, partial value tiles; against the CPU restatement that stores every state."""
+    heads, partial value tiles; against the CPU restatement that stores every state.  The last two
+    shapes (256 tokens or more at width 128) take the chunk-parallel backward: two tensor-core
+    scans and one CTA per chunk, with a ragged last chunk in the first of them."""
     t, kh, vh, kd, vd, kernel = shape
     channels = 2 * kh * kd + vh * vd
     rng = np.random.default_rng(17)
@@ -137,3 +140,50 @@ def test_frozen_parameters_and_contracts():
     assert e.value.code == "InvalidArgument"
     with pytest.raises(PlutoStatusError):
         frozen.bwd([torch.zeros((t, vh * vd), dtype=torch.float32, device="cuda")], fwd.state)
+
+
+@pytest.mark.parametrize("shape", [(1, 320, 1, 2), (2, 333, 2, 4), (1, 1100, 1, 1)])
+def test_chunk_parallel_recurrence_backward_matches_the_token_sequential_kernel(shape):
+    """pluto_gdn_recurrence_bwd takes the chunk-parallel path for bf16 activations at width 128 from
+    256 tokens on, the token-sequential kernel otherwise.  The same values given once as bf16 and
+    once as fp32 therefore run both; every gradient within 5e-3 of its largest magnitude (the
+    chunked scans round their operands to bf16), and the chunked path bitwise repeatable."""
+    import ctypes
+
+    from pluto_b200 import _capi
+    L = _capi.lib()
+    P = lambda x: ctypes.c_void_p(x.data_ptr())
+    bsz, t, kh, vh = shape
+    d = 128
+    ch, kq = 2 * kh * d + vh * d, kh * d
+
+    def run(as_bf16):
+        g = torch.Generator(device="cuda").manual_seed(5)
+        post = (torch.randn(bsz, t, ch, device="cuda", generator=g) * 0.5).bfloat16()
+        a = (torch.randn(bsz, t, vh, device="cuda", generator=g) * 0.5).bfloat16()
+        b = (torch.randn(bsz, t, vh, device="cuda", generator=g) * 0.5).bfloat16()
+        a_log = torch.randn(vh, device="cuda", generator=g) * 0.3 - 0.7
+        dt_bias = torch.randn(vh, device="cuda", generator=g) * 0.3
+        dcore = torch.randn(bsz, t, vh, d, device="cuda", generator=g)
+        if not as_bf16:
+            post, a, b = post.float(), a.float(), b.float()
+        dtype = 1 if as_bf16 else 0
+        dpost = torch.zeros(bsz, t, ch, device="cuda")
+        da, db = torch.zeros(bsz, t, vh, device="cuda"), torch.zeros(bsz, t, vh, device="cuda")
+        d_a_log, d_dt = torch.zeros(vh, device="cuda"), torch.zeros(vh, device="cuda")
+        size = L.pluto_gdn_recurrence_bwd_workspace_bytes(bsz, t, kh, vh, d, d)
+        ws = torch.empty(size, dtype=torch.uint8, device="cuda")
+        flat, dflat = post.view(-1), dpost.view(-1)
+        _capi.check(L.pluto_gdn_recurrence_bwd(
+            None, P(flat), P(flat[kq:]), P(flat[2 * kq:]), dtype, ch, ch, P(a), P(b), dtype, P(a_log), P(dt_bias),
+            P(dcore), P(dflat), P(dflat[kq:]), ch, P(dflat[2 * kq:]), ch, P(da), P(db), P(d_a_log), P(d_dt),
+            P(ws), size, bsz, t, kh, vh, d, d, 1))
+        torch.cuda.synchronize()
+        assert _capi.kernel_status() == 0
+        return [dpost, da, db, d_a_log, d_dt]
+
+    chunked, again, sequential = run(True), run(True), run(False)
+    for name, x, y, z in zip(["dpost", "da", "db", "d_a_log", "d_dt_bias"], chunked, again, sequential):
+        assert torch.equal(x, y), name
+        assert torch.isfinite(x).all(), name
+        assert (x - z).abs().max().item() <= 5e-3 * z.abs().max().item(), name
