@@ -55,6 +55,14 @@ __device__ __forceinline__ float load_any(const void* p, size_t i, int is_bf16) 
   return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i])
                  : static_cast<const float*>(p)[i];
 }
+// four consecutive activations (the offset is a multiple of four elements; bf16 rows are 8-byte aligned)
+__device__ __forceinline__ float4 load_any4(const void* p, size_t i, int is_bf16) {
+  if (is_bf16) {
+    const uint2 w = __ldg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + i));
+    return make_float4(bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y));
+  }
+  return __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i));
+}
 __device__ __forceinline__ float4 lds4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ float comp(const float4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
@@ -65,10 +73,12 @@ __device__ __forceinline__ float row_sum16(float v) {
   return v;
 }
 
-// Thread (rg, cg) = (tid / 16, tid % 16) owns rows rg*4 .. +3 of every product.  Columns: eight
-// neighbours cg*8 .. +7 ("dense") where the B operand is read along its rows, every 16th column
-// cg + 16 j ("strided") where it is read along k -- with row pitches of 132 / 68 floats the 16
-// lanes of a row group then fall into different banks.
+// Thread (rg, cg) = (tid / 16, tid % 16) owns rows rg*4 .. +3 of every product.  Columns: two
+// groups of four, cg*4 .. +3 and 64 + cg*4 .. +3 ("dense"), where the B operand is read along its
+// rows -- the 16 lanes of a row group then read 256 contiguous bytes per 16-byte load, every bank
+// once; every 16th column cg + 16 j ("strided") where it is read along k -- with row pitches of
+// 132 / 68 floats those lanes fall into different banks too.
+__device__ __forceinline__ int dense_col(int cg, int j) { return cg * 4 + (j & 3) + ((j >> 2) << 6); }
 
 // acc[i][j] += sum_k A[r0+i][k] B[cg+16j][k]     (A B^T, [64 x 64] result, strided columns)
 template <int K>
@@ -109,7 +119,7 @@ __device__ __forceinline__ void nn_smem(const float* A, int pa, const float* sca
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      const float4 b0 = lds4(B + (k + kk) * pb + cg * 8), b1 = lds4(B + (k + kk) * pb + cg * 8 + 4);
+      const float4 b0 = lds4(B + (k + kk) * pb + cg * 4), b1 = lds4(B + (k + kk) * pb + 64 + cg * 4);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float av = comp(a[i], kk);
@@ -129,7 +139,7 @@ __device__ __forceinline__ void tn_smem(const float* A, int pa, const float* B, 
 #pragma unroll 4
   for (int k = 0; k < K; ++k) {
     const float4 a = lds4(A + k * pa + r0);
-    const float4 b0 = lds4(B + k * pb + cg * 8), b1 = lds4(B + k * pb + cg * 8 + 4);
+    const float4 b0 = lds4(B + k * pb + cg * 4), b1 = lds4(B + k * pb + 64 + cg * 4);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float av = comp(a, i);
@@ -141,49 +151,55 @@ __device__ __forceinline__ void tn_smem(const float* A, int pa, const float* B, 
   }
 }
 
-// acc[i][j] += sum_k A[r0+i][k] Bg[k][cg*8+j]      (B a [128 x 128] matrix in global memory, dense columns)
-__device__ __forceinline__ void nn_glob(const float* A, int pa, const float* __restrict__ Bg, int r0, int cg,
-                                        float (&acc)[4][8]) {
-#pragma unroll 2
-  for (int k = 0; k < kLD; k += 4) {
-    float4 a[4];
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// acc[i][j] += sum_k A[r0+i][k] Bg[k][dense column j]  with Bg a [128 x 128] matrix in global memory.
+// Its rows pass through a ring in shared memory, eight rows (4 KB, one 16-byte asynchronous copy per
+// thread) per stage and kRingStages - 1 stages in flight, so the products never wait for memory; all
+// 256 threads call this together.  `ring` holds kRingStages * 1024 floats and is free again on return.
+constexpr int kRingStages = 6;
+__device__ __forceinline__ void nn_ring(const float* A, int pa, const float* __restrict__ Bg, float* ring,
+                                        int r0, int cg, int tid, float (&acc)[4][8]) {
+  constexpr int kStageRows = 8, kStages = kLD / kStageRows;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = lds4(A + (r0 + i) * pa + k);
+  for (int s = 0; s < kRingStages - 1; ++s) {
+    cp_async16(ring + s * 1024 + tid * 4, Bg + s * 1024 + tid * 4);
+    cp_async_commit();
+  }
+#pragma unroll 1
+  for (int s = 0; s < kStages; ++s) {
+    cp_async_wait<kRingStages - 2>();
+    __syncthreads();   // stage s has landed for every thread; the slot refilled below was read in step s - 1
+    const int ahead = s + kRingStages - 1;
+    if (ahead < kStages) cp_async16(ring + (ahead % kRingStages) * 1024 + tid * 4, Bg + ahead * 1024 + tid * 4);
+    cp_async_commit();
+    const float* Bs = ring + (s % kRingStages) * 1024;
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      const float4 b0 = ldg4(Bg + (k + kk) * kLD + cg * 8), b1 = ldg4(Bg + (k + kk) * kLD + cg * 8 + 4);
+    for (int k = 0; k < kStageRows; k += 4) {
+      float4 a[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float av = comp(a[i], kk);
-        acc[i][0] = fmaf(av, b0.x, acc[i][0]); acc[i][1] = fmaf(av, b0.y, acc[i][1]);
-        acc[i][2] = fmaf(av, b0.z, acc[i][2]); acc[i][3] = fmaf(av, b0.w, acc[i][3]);
-        acc[i][4] = fmaf(av, b1.x, acc[i][4]); acc[i][5] = fmaf(av, b1.y, acc[i][5]);
-        acc[i][6] = fmaf(av, b1.z, acc[i][6]); acc[i][7] = fmaf(av, b1.w, acc[i][7]);
+      for (int i = 0; i < 4; ++i) a[i] = lds4(A + (r0 + i) * pa + s * kStageRows + k);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const float4 b0 = lds4(Bs + (k + kk) * kLD + cg * 4), b1 = lds4(Bs + (k + kk) * kLD + 64 + cg * 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float av = comp(a[i], kk);
+          acc[i][0] = fmaf(av, b0.x, acc[i][0]); acc[i][1] = fmaf(av, b0.y, acc[i][1]);
+          acc[i][2] = fmaf(av, b0.z, acc[i][2]); acc[i][3] = fmaf(av, b0.w, acc[i][3]);
+          acc[i][4] = fmaf(av, b1.x, acc[i][4]); acc[i][5] = fmaf(av, b1.y, acc[i][5]);
+          acc[i][6] = fmaf(av, b1.z, acc[i][6]); acc[i][7] = fmaf(av, b1.w, acc[i][7]);
+        }
       }
     }
   }
-}
-
-// acc[i][j] += sum_k A[r0+i][k] Bg[cg+16j][k]      (A Bg^T, strided columns)
-__device__ __forceinline__ void nt_glob(const float* A, int pa, const float* __restrict__ Bg, int r0, int cg,
-                                        float (&acc)[4][8]) {
-#pragma unroll 1
-  for (int k = 0; k < kLD; k += 4) {
-    float4 a[4], b[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = lds4(A + (r0 + i) * pa + k);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) b[j] = ldg4(Bg + (cg + 16 * j) * kLD + k);
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
-        acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
-        acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
-        acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
-      }
-  }
+  cp_async_wait<0>();
+  __syncthreads();
 }
 
 template <int N>
@@ -197,15 +213,17 @@ __device__ __forceinline__ void zero(float (&acc)[4][N]) {
 __device__ __forceinline__ void store_dense(float* dst, int r0, int cg, const float (&acc)[4][8]) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    *reinterpret_cast<float4*>(dst + (r0 + i) * kLP + cg * 8) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-    *reinterpret_cast<float4*>(dst + (r0 + i) * kLP + cg * 8 + 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    *reinterpret_cast<float4*>(dst + (r0 + i) * kLP + cg * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    *reinterpret_cast<float4*>(dst + (r0 + i) * kLP + 64 + cg * 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
   }
 }
 
 struct LocalArgs {
   GdnBwdArgs a;
-  const float* states;    // [sequence, head, chunk, value column, key]: state at each chunk's start
-  const float* dstates;   // same shape: state gradient at each chunk's end
+  const float* states;      // [sequence, head, chunk, key, value column]: state at each chunk's start
+  const float* states_t;    // the same matrices transposed, [.., value column, key]
+  const float* dstates;     // [sequence, head, chunk, key, value column]: state gradient at each chunk's end
+  const float* dstates_t;
   int chunks;
 };
 
@@ -219,11 +237,20 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   const int rg = tid >> 4, cg = tid & 15, r0 = rg * 4;
   const int t0 = chunk * kLC, count = min(kLC, a.tokens - t0);
   const size_t unit = static_cast<size_t>(b) * a.value_heads + h;
-  const float* S0 = la.states + (unit * la.chunks + chunk) * kLD * kLD;     // [value column][key]
-  const float* dS = la.dstates + (unit * la.chunks + chunk) * kLD * kLD;
+  const size_t matrix = (unit * la.chunks + chunk) * kLD * kLD;
+  const float* S0 = la.states + matrix;        // [key][value column]
+  const float* S0t = la.states_t + matrix;     // [value column][key]
+  const float* dS = la.dstates + matrix;
+  const float* dSt = la.dstates_t + matrix;
   float* Kh = sm.big[0];
   const float q_scale = rsqrtf(static_cast<float>(kLD));
 
+  // The four state matrices are first needed tens of microseconds from now and would come from
+  // DRAM then: ask for them in L2 now.
+  if (tid < 4) {
+    const float* m = tid == 0 ? S0 : (tid == 1 ? dS : (tid == 2 ? S0t : dSt));
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(m), "r"(kLD * kLD * 4) : "memory");
+  }
   // ---- gates
   if (tid < kLC) {
     float lg = 0.0f, be = 0.0f, alpha = 0.0f, softplus = 0.0f, sigmoid = 0.0f;
@@ -258,9 +285,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (t < count) {
       const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + c4 * 4;
-      const void* src = which ? a.q : a.k;
-      v = make_float4(load_any(src, off, a.in_is_bf16), load_any(src, off + 1, a.in_is_bf16),
-                      load_any(src, off + 2, a.in_is_bf16), load_any(src, off + 3, a.in_is_bf16));
+      v = load_any4(which ? a.q : a.k, off, a.in_is_bf16);
     }
     *reinterpret_cast<float4*>(sm.big[which] + t * kLP + c4 * 4) = v;
   }
@@ -337,8 +362,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (t < count) {
       const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.v_token + static_cast<size_t>(h) * kLD + c4 * 4;
-      v = make_float4(load_any(a.v, off, a.in_is_bf16), load_any(a.v, off + 1, a.in_is_bf16),
-                      load_any(a.v, off + 2, a.in_is_bf16), load_any(a.v, off + 3, a.in_is_bf16));
+      v = load_any4(a.v, off, a.in_is_bf16);
     }
     *reinterpret_cast<float4*>(sm.big[2] + t * kLP + c4 * 4) = v;
   }
@@ -350,16 +374,16 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     store_dense(sm.big[3], r0, cg, acc);
   }
   __syncthreads();
-  // ---- U = U' - W S_0 -> big[4] (strided columns)
+  // ---- U = U' - W S_0 -> big[4]
   {
     float acc[4][8];
     zero(acc);
-    nt_glob(sm.big[1], kLP, S0, r0, cg, acc);
+    nn_ring(sm.big[1], kLP, S0, sm.big[2], r0, cg, tid, acc);   // (v in big[2] is dead: U' is complete)
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int e = (r0 + i) * kLP + cg + 16 * j;
+        const int e = (r0 + i) * kLP + dense_col(cg, j);
         sm.big[4][e] = sm.big[3][e] - acc[i][j];
       }
   }
@@ -414,9 +438,9 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   }
   __syncthreads();
 
-  float dk_acc[4][8], dq_acc[4][8];
-  zero(dk_acc);
-  zero(dq_acc);
+  // The two contributions that are known early -- (gamma/c) . dKt to dk^ and c . dQc to dq^ -- wait
+  // in this chunk's rows of the output partials (each thread its own elements) until the last
+  // products, so that no accumulator tile stays live across the phases in between.
   float kt_total = 0.0f;   // sum of dKt . Kt over the chunk (thread partial)
   const float gamma = sm.cdec[kLC - 1];
 
@@ -424,16 +448,18 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   {
     float acc[4][8];
     zero(acc);
-    nn_glob(sm.big[4], kLP, dS, r0, cg, acc);
+    nn_ring(sm.big[4], kLP, dSt, sm.big[3], r0, cg, tid, acc);   // (W and U' are dead from here on: big[1], big[3])
     float rows[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float f = gamma / sm.cdec[r0 + i];
       float rs = 0.0f;
+      float* stash = a.qk_partials + ((static_cast<size_t>(b) * a.tokens + min(t0 + r0 + i, a.tokens - 1)) * a.value_heads + h) * 2 * kLD + kLD;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        dk_acc[i][j] = fmaf(f, acc[i][j], dk_acc[i][j]);
-        rs = fmaf(acc[i][j] * f, Kh[(r0 + i) * kLP + cg * 8 + j], rs);
+        const float scaled = acc[i][j] * f;
+        if (r0 + i < count) stash[dense_col(cg, j)] = scaled;
+        rs = fmaf(scaled, Kh[(r0 + i) * kLP + dense_col(cg, j)], rs);
       }
       rows[i] = rs;
       kt_total += rs;
@@ -443,40 +469,42 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   __syncthreads();   // every read of U is done
   // ---- dU = M^T dO + Kt dS -> big[4]
   {
-    float acc[4][8];
+    float acc[4][8], from_state[4][8];
     zero(acc);
+    zero(from_state);
     tn_smem<kLC>(Mm, kLQ, sm.big[2], kLP, r0, cg, acc);
-    store_dense(sm.big[4], r0, cg, acc);
-  }
-  __syncthreads();
-  {
-    float acc[4][8];
-    zero(acc);
-    nt_glob(Kh, kLP, dS, r0, cg, acc);
+    nn_ring(Kh, kLP, dS, sm.big[3], r0, cg, tid, from_state);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float f = gamma / sm.cdec[r0 + i];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) sm.big[4][(r0 + i) * kLP + cg + 16 * j] += f * acc[i][j];
+      for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(f, from_state[i][j], acc[i][j]);
     }
+    store_dense(sm.big[4], r0, cg, acc);
   }
   // ---- dQc = dO S_0^T: dq^ += c . dQc, db += rows(dQc . c q^)
   {
     float acc[4][8];
     zero(acc);
-    nn_glob(sm.big[2], kLP, S0, r0, cg, acc);
+    nn_ring(sm.big[2], kLP, S0t, sm.big[3], r0, cg, tid, acc);
     float rows[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int t = r0 + i;
       const float c = sm.cdec[t];
       float rs = 0.0f;
-      const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + cg * 8;
+      if (t < count) {
+        const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + cg * 4;
+        const float4 q0 = load_any4(a.q, off, a.in_is_bf16), q1 = load_any4(a.q, off + 64, a.in_is_bf16);
+        const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const float f = sm.iq[t] * q_scale;
+        float* stash = a.qk_partials + ((static_cast<size_t>(b) * a.tokens + t0 + t) * a.value_heads + h) * 2 * kLD;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        dq_acc[i][j] = fmaf(c, acc[i][j], dq_acc[i][j]);
-        const float qh = t < count ? load_any(a.q, off + j, a.in_is_bf16) * sm.iq[t] * q_scale : 0.0f;
-        rs = fmaf(acc[i][j] * c, qh, rs);
+        for (int j = 0; j < 8; ++j) {
+          const float scaled = acc[i][j] * c;
+          stash[dense_col(cg, j)] = scaled;
+          rs = fmaf(scaled, qv[j] * f, rs);
+        }
       }
       rows[i] = rs;
     }
@@ -487,7 +515,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   {
     float acc[4][8];
     zero(acc);
-    nn_glob(sm.big[4], kLP, S0, r0, cg, acc);
+    nn_ring(sm.big[4], kLP, S0t, sm.big[3], r0, cg, tid, acc);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -505,12 +533,14 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       const int t = r0 + i;
       float rs = 0.0f;
       if (t < count) {
-        const size_t voff = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.v_token + static_cast<size_t>(h) * kLD + cg * 8;
-        float* dv = a.dv_out + (static_cast<size_t>(b) * a.tokens + t0 + t) * a.dv_token + static_cast<size_t>(h) * kLD + cg * 8;
+        const size_t voff = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.v_token + static_cast<size_t>(h) * kLD + cg * 4;
+        float* dv = a.dv_out + (static_cast<size_t>(b) * a.tokens + t0 + t) * a.dv_token + static_cast<size_t>(h) * kLD;
+        const float4 v0 = load_any4(a.v, voff, a.in_is_bf16), v1 = load_any4(a.v, voff + 64, a.in_is_bf16);
+        const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          rs = fmaf(acc[i][j], load_any(a.v, voff + j, a.in_is_bf16), rs);
-          dv[j] = sm.beta[t] * acc[i][j];
+          rs = fmaf(acc[i][j], vv[j], rs);
+          dv[dense_col(cg, j)] = sm.beta[t] * acc[i][j];
         }
       }
       rows[i] = rs;
@@ -531,10 +561,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       const float c = sm.cdec[t], be = sm.beta[t];
       float rs = 0.0f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        dk_acc[i][j] = fmaf(be * c, acc[i][j], dk_acc[i][j]);
-        rs = fmaf(acc[i][j] * c, Kh[t * kLP + cg * 8 + j], rs);
-      }
+      for (int j = 0; j < 8; ++j) rs = fmaf(acc[i][j] * c, Kh[t * kLP + dense_col(cg, j)], rs);   // (beta c . X2 joins dk^ at the end)
       rows_beta[i] = rs;
       rows_b[i] = rs * be;
     }
@@ -544,16 +571,41 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     store_dense(sm.big[2], r0, cg, acc);
   }
   __syncthreads();
-  // ---- dA = -mask(X1 U'^T + X2 W^T); with G again: A-bar into db, dbeta; dG + dG^T -> sq[1]
+  // ---- dA = -mask(X1 U'^T + X2 W^T) = -mask(R T^T),  R = X1 (beta . v)^T + X2 (beta c . k^)^T: U' and W
+  //      need not be kept.  v is staged again (big[3]); R -> sq[1] (M is dead)
+  for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
+    const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (t < count) {
+      const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.v_token + static_cast<size_t>(h) * kLD + c4 * 4;
+      v = load_any4(a.v, off, a.in_is_bf16);
+    }
+    *reinterpret_cast<float4*>(sm.big[3] + t * kLP + c4 * 4) = v;
+  }
+  __syncthreads();
+  {
+    float from_v[4][4], from_k[4][4];
+    zero(from_v);
+    zero(from_k);
+    nt_smem<kLD>(sm.big[4], kLP, sm.big[3], kLP, r0, cg, from_v);
+    nt_smem<kLD>(sm.big[2], kLP, Kh, kLP, r0, cg, from_k);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int s2 = cg + 16 * j;
+        sm.sq[1][(r0 + i) * kLQ + s2] = sm.beta[s2] * fmaf(sm.cdec[s2], from_k[i][j], from_v[i][j]);
+      }
+  }
+  __syncthreads();
   {
     float acc[4][4], g[4][4];
     zero(acc);
     zero(g);
-    nt_smem<kLD>(sm.big[4], kLP, sm.big[3], kLP, r0, cg, acc);
-    nt_smem<kLD>(sm.big[2], kLP, sm.big[1], kLP, r0, cg, acc);
+    nt_smem<kLC>(sm.sq[1], kLQ, Tm, kLQ, r0, cg, acc);
     nt_smem<kLD>(Kh, kLP, Kh, kLP, r0, cg, g);
+    __syncthreads();   // every read of R is done: dG + dG^T goes over it
     float rows_beta[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rows_b[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cols[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    // (M was last read by the dU product, two barriers ago)
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -585,22 +637,36 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     for (int g = 0; g < 16; ++g) total += sm.part[g][tid];
     sm.db[tid] -= total;
   }
-  // ---- dk^ += (dG + dG^T) k^ + dH^T q^;  dq^ += dH k^   (q^ is staged again, into big[3])
+  // ---- dk^ += (dG + dG^T) k^ + dH^T q^;  dq^ += dH k^   (q^ is staged again, into big[1])
   for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
     const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
     float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (t < count) {
       const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + c4 * 4;
       const float f = sm.iq[t] * q_scale;
-      v = make_float4(load_any(a.q, off, a.in_is_bf16) * f, load_any(a.q, off + 1, a.in_is_bf16) * f,
-                      load_any(a.q, off + 2, a.in_is_bf16) * f, load_any(a.q, off + 3, a.in_is_bf16) * f);
+      v = load_any4(a.q, off, a.in_is_bf16);
+      v = make_float4(v.x * f, v.y * f, v.z * f, v.w * f);
     }
-    *reinterpret_cast<float4*>(sm.big[3] + t * kLP + c4 * 4) = v;
+    *reinterpret_cast<float4*>(sm.big[1] + t * kLP + c4 * 4) = v;
   }
   __syncthreads();
+  float dk_acc[4][8], dq_acc[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = r0 + i;
+    const float* stash = a.qk_partials + ((static_cast<size_t>(b) * a.tokens + min(t0 + t, a.tokens - 1)) * a.value_heads + h) * 2 * kLD;
+    const float bc = sm.beta[t] * sm.cdec[t];
+    const float4 x0 = lds4(sm.big[2] + t * kLP + cg * 4), x1 = lds4(sm.big[2] + t * kLP + 64 + cg * 4);   // X2
+    const float x2[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dq_acc[i][j] = t < count ? stash[dense_col(cg, j)] : 0.0f;
+      dk_acc[i][j] = (t < count ? stash[kLD + dense_col(cg, j)] : 0.0f) + bc * x2[j];
+    }
+  }
   nn_smem<kLC>(sm.sq[1], kLQ, nullptr, Kh, kLP, r0, cg, dk_acc);
   nn_smem<kLC>(sm.sq[0], kLQ, nullptr, Kh, kLP, r0, cg, dq_acc);
-  tn_smem<kLC>(sm.sq[0], kLQ, sm.big[3], kLP, r0, cg, dk_acc);
+  tn_smem<kLC>(sm.sq[0], kLQ, sm.big[1], kLP, r0, cg, dk_acc);
 
   // ---- through the normalisations: per-token partials in the layout of the gather kernels (one tile)
 #pragma unroll
@@ -609,19 +675,19 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     float pk = 0.0f, pq = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      pk = fmaf(dk_acc[i][j], Kh[t * kLP + cg * 8 + j], pk);
-      pq = fmaf(dq_acc[i][j], sm.big[3][t * kLP + cg * 8 + j], pq);
+      pk = fmaf(dk_acc[i][j], Kh[t * kLP + dense_col(cg, j)], pk);
+      pq = fmaf(dq_acc[i][j], sm.big[1][t * kLP + dense_col(cg, j)], pq);
     }
     pk = row_sum16(pk);
     pq = row_sum16(pq) / (q_scale * q_scale);   // q^ = scale . unit vector
     if (t < count) {
       const size_t partial = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.value_heads + h;
-      float* out = a.qk_partials + partial * 2 * kLD + cg * 8;
+      float* out = a.qk_partials + partial * 2 * kLD;
       const float ikt = sm.ik[t], iqt = sm.iq[t] * q_scale;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        out[j] = iqt * (dq_acc[i][j] - sm.big[3][t * kLP + cg * 8 + j] * pq);
-        out[kLD + j] = ikt * (dk_acc[i][j] - Kh[t * kLP + cg * 8 + j] * pk);
+        out[dense_col(cg, j)] = iqt * (dq_acc[i][j] - sm.big[1][t * kLP + dense_col(cg, j)] * pq);
+        out[kLD + dense_col(cg, j)] = ikt * (dk_acc[i][j] - Kh[t * kLP + dense_col(cg, j)] * pk);
       }
     }
   }
@@ -668,6 +734,24 @@ __global__ void cast_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16
   }
 }
 
+// out[m] = in[m]^T for a batch of [128 x 128] fp32 matrices; one CTA of 256 threads per matrix
+__global__ void __launch_bounds__(256) transpose_128_kernel(const float* __restrict__ in, float* __restrict__ out) {
+  __shared__ float tile[32][129];
+  const size_t base = static_cast<size_t>(blockIdx.x) * kLD * kLD;
+  for (int strip = 0; strip < 4; ++strip) {   // rows strip*32 .. +31 of the input
+    for (int e = threadIdx.x; e < 32 * kLD; e += 256) {
+      const int r = e / kLD, c = e % kLD;
+      tile[r][c] = in[base + static_cast<size_t>(strip * 32 + r) * kLD + c];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 32 * kLD; e += 256) {
+      const int c = e / 32, r = e % 32;
+      out[base + static_cast<size_t>(c) * kLD + strip * 32 + r] = tile[r][c];
+    }
+    __syncthreads();
+  }
+}
+
 size_t align_up(size_t n) { return (n + 1023) / 1024 * 1024; }
 
 }  // namespace
@@ -679,9 +763,9 @@ bool gdn_bwd_chunked_supported(const GdnBwdArgs& a) {
 }
 
 // Layout of the workspace: records | g, beta | dcore as bf16 | forward output (bf16, unused) |
-// states | state gradients | q/k partials | scalar partials
+// states, their transposes | state gradients, their transposes | q/k partials | scalar partials
 struct ChunkedBwdLayout {
-  size_t records, gates, dcore16, out16, states, dstates, qk_partials, scalar_partials, total;
+  size_t records, gates, dcore16, out16, states, states_t, dstates, dstates_t, qk_partials, scalar_partials, total;
 };
 static ChunkedBwdLayout chunked_bwd_layout(int batch, int tokens, int value_heads) {
   const size_t chunks = (tokens + kLC - 1) / kLC, units = static_cast<size_t>(batch) * value_heads;
@@ -693,7 +777,9 @@ static ChunkedBwdLayout chunked_bwd_layout(int batch, int tokens, int value_head
   l.dcore16 = at; at += align_up(rows * kLD * 2);
   l.out16 = at; at += align_up(rows * kLD * 2);
   l.states = at; at += align_up(units * chunks * kLD * kLD * sizeof(float));
+  l.states_t = at; at += align_up(units * chunks * kLD * kLD * sizeof(float));
   l.dstates = at; at += align_up(units * chunks * kLD * kLD * sizeof(float));
+  l.dstates_t = at; at += align_up(units * chunks * kLD * kLD * sizeof(float));
   l.qk_partials = at; at += align_up(rows * 2 * kLD * sizeof(float));
   l.scalar_partials = at; at += align_up(rows * 3 * sizeof(float));
   l.total = at + 1024;   // room to align the base
@@ -715,6 +801,8 @@ cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& a, void* workspace,
   __nv_bfloat16* dcore16 = reinterpret_cast<__nv_bfloat16*>(base + l.dcore16);
   float* states = reinterpret_cast<float*>(base + l.states);
   float* dstates = reinterpret_cast<float*>(base + l.dstates);
+  float* states_t = reinterpret_cast<float*>(base + l.states_t);
+  float* dstates_t = reinterpret_cast<float*>(base + l.dstates_t);
   a.qk_partials = reinterpret_cast<float*>(base + l.qk_partials);
   a.scalar_partials = reinterpret_cast<float*>(base + l.scalar_partials);
 
@@ -736,8 +824,8 @@ cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& a, void* workspace,
   f.batch = a.batch; f.tokens = a.tokens; f.key_heads = a.key_heads; f.value_heads = a.value_heads;
   f.key_dim = kLD; f.value_dim = kLD;
   f.normalize_qk = 1; f.q_scale = 1.0f; f.round = a.round;
-  // the scan reads its initial state from and leaves its final state in f.state: the last chunk's
-  // slot of the state-gradient area is free until the reverse scan runs
+  // the scan reads its initial state from and leaves its final state in f.state: the start of the
+  // state-gradient area is free until the reverse scan runs
   f.state = dstates;
   e = cudaMemsetAsync(dstates, 0, static_cast<size_t>(a.batch) * a.value_heads * kLD * kLD * sizeof(float), stream);
   if (e != cudaSuccess) return e;
@@ -745,7 +833,12 @@ cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& a, void* workspace,
   if (e != cudaSuccess) return e;
   e = gdn_scan_bwd_launch(stream, dcore16, base + l.records, a.batch, a.tokens, a.value_heads, chunks, dstates, status);
   if (e != cudaSuccess) return e;
-  LocalArgs la{a, states, dstates, chunks};
+  const unsigned matrices = static_cast<unsigned>(a.batch) * a.value_heads * chunks;
+  transpose_128_kernel<<<matrices, 256, 0, stream>>>(states, states_t);
+  transpose_128_kernel<<<matrices, 256, 0, stream>>>(dstates, dstates_t);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  LocalArgs la{a, states, states_t, dstates, dstates_t, chunks};
   e = cudaFuncSetAttribute(gdn_bwd_chunk_local, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(sizeof(LocalSmem)));
   if (e != cudaSuccess) return e;

@@ -63,7 +63,7 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, 
                float* __restrict__ state_dump, uint32_t* status) {
   // walks chunks first_chunk .. first_chunk + chunks - 1 of the sequence's all_chunks; the state is
   // read from and left in a.state, so consecutive launches continue one another.  state_dump (optional, for the backward pass): the
-  // state at the START of every chunk, transposed, [sequence, head, chunk, value column, key]
+  // state at the START of every chunk, [sequence, head, chunk, key, value column]
   extern __shared__ uint8_t scan_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(scan_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -255,15 +255,13 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, 
         tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
         tmem_wait_ld();
         if (state_dump != nullptr) {
-          float4* dst = reinterpret_cast<float4*>(
-              state_dump + ((((static_cast<size_t>(b) * a.value_heads + h) * all_chunks + first_chunk + c) * dv + j) *
-                            kGdnKeyDim + half * 64));
+          // (one key per store: the 32 lanes of a warp write 32 neighbouring value columns)
+          float* dst = state_dump + (((static_cast<size_t>(b) * a.value_heads + h) * all_chunks + first_chunk + c) *
+                                         kGdnKeyDim + half * 64) * dv + j;
 #pragma unroll
           for (int g = 0; g < 2; ++g)
 #pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              dst[g * 8 + i / 4] = make_float4(__uint_as_float(s[g][i]), __uint_as_float(s[g][i + 1]),
-                                               __uint_as_float(s[g][i + 2]), __uint_as_float(s[g][i + 3]));
+            for (int i = 0; i < 32; ++i) dst[static_cast<size_t>(g * 32 + i) * dv] = __uint_as_float(s[g][i]);
         }
 #pragma unroll
         for (int g = 0; g < 2; ++g)
@@ -317,8 +315,8 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, 
 // state (lane = value column, columns = keys), so per chunk: acc (= gamma dS^T) += dO^T Qt
 // (token-major operands, as U^T Kt forward) + dS^T_bf16 Pn (Pn now read as an MN-major operand:
 // its 64-column slabs are 16384 bytes apart, 16 keys = 2048 bytes).  What the per-chunk part of
-// the backward pass needs is the gradient at every chunk's END: dumped, transposed,
-// [sequence, head, chunk, value column, key], before the chunk's step.  One CTA per (sequence, head,
+// the backward pass needs is the gradient at every chunk's END: dumped,
+// [sequence, head, chunk, key, value column], before the chunk's step.  One CTA per (sequence, head,
 // 128 value columns); warp roles as in the forward scan, no output products.
 // ---------------------------------------------------------------------------------------------
 constexpr int kRevStages = 3;
@@ -436,13 +434,11 @@ gdn_scan_bwd_sm100(const __grid_constant__ CUtensorMap map_do, int value_heads,
         tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
         tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
         tmem_wait_ld();
-        float4* dst = reinterpret_cast<float4*>(dstate_dump + (((unit * chunks + chunk) * dv + j) * kGdnKeyDim + half * 64));
+        float* dst = dstate_dump + ((unit * chunks + chunk) * kGdnKeyDim + half * 64) * dv + j;
 #pragma unroll
         for (int g = 0; g < 2; ++g)
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            dst[g * 8 + i / 4] = make_float4(__uint_as_float(s[g][i]), __uint_as_float(s[g][i + 1]),
-                                             __uint_as_float(s[g][i + 2]), __uint_as_float(s[g][i + 3]));
+          for (int i = 0; i < 32; ++i) dst[static_cast<size_t>(g * 32 + i) * dv] = __uint_as_float(s[g][i]);
 #pragma unroll
         for (int g = 0; g < 2; ++g)
 #pragma unroll
