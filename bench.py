@@ -888,7 +888,9 @@ def _gdn_forward_times(time_ms, prefill, qn, kn, vn, g, beta, st):
 
 
 def _gdn_bptt(time_ms, qn, kn, vn, bb, tt, hh, dd, pre_ms, step_ms, graph_ms):
-    """BPTT through the recurrence (checkpointed every 64 tokens), q/k normalisation included."""
+    """BPTT through the recurrence at the benchmark shape (the chunk-parallel path: forward prefill
+    with the state kept per chunk, reverse tcgen05 scan, one CTA per chunk), q/k normalisation
+    included."""
     import torch
 
     from pluto_b200 import _capi
@@ -912,9 +914,12 @@ def _gdn_bptt(time_ms, qn, kn, vn, bb, tt, hh, dd, pre_ms, step_ms, graph_ms):
             dcore.data_ptr(), dq.data_ptr(), dk2.data_ptr(), hh * dd, dv2.data_ptr(), hh * dd,
             da.data_ptr(), db.data_ptr(), None, None, ws.data_ptr(), ws_bytes, bb, tt, hh, hh, dd, dd, 1))
 
-    bptt_ms = time_ms(bptt, steps=2, warmup=1)
+    bptt_ms = time_ms(bptt, steps=3, warmup=2)
     entry = {"workload": "batch 2, 16 heads, d_k = d_v = 128, seq 16384",
-             "recurrence_bwd_ms": bptt_ms, "recurrence_bwd_workspace_gb": ws_bytes / 1e9}
+             "recurrence_bwd_ms": bptt_ms, "recurrence_bwd_workspace_gb": ws_bytes / 1e9,
+             "recurrence_bwd_note": "chunk-parallel: two tcgen05 scans + one fp32 CTA per 64-token chunk "
+                                    "(about 215 GFLOP of fp32 products)",
+             "recurrence_bwd_fp32_tflops": 215.0e9 / (bptt_ms * 1e-3) / 1e12}
     if pre_ms is not None:
         entry.update({
             "prefill_ms": pre_ms, "prefill_tflops_chunked_count": 94.49e9 / (pre_ms * 1e-3) / 1e12,

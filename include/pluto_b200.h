@@ -403,7 +403,10 @@ int pluto_gdn_out_norm_gate(pluto_stream_t stream, const void* core, int core_dt
  *    value_heads]; dcore from stage 1.  dq, dk (token stride dqk_token_stride) and dv (token
  *    stride dv_token_stride) are fp32 and normally point into one [batch, tokens, channels]
  *    gradient of the convolved activations; da, db fp32 [batch, tokens, value_heads].
- *    key_dim <= 128, value_dim <= 256.
+ *    key_dim <= 128, value_dim <= 256.  bf16 activations with key_dim = value_dim = 128 and 256
+ *    tokens or more run chunk-parallel (the chunked forward again with the state kept at every
+ *    64-token boundary, a reverse scan for the state gradients, then all chunks at once); everything
+ *    else walks the sequence token by token.  The workspace query covers both.
  * 3. pluto_gdn_conv_silu_bwd: ConvSiluBackward + ConvInputBackward + ConvWeightBackward
  *    (:311-362) for sequences that start from an empty history.  input is the layer's QKV input
  *    [batch, tokens, channels]; d_post the gradient of the convolved activations; dx fp32. */
