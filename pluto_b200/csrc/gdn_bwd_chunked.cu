@@ -39,7 +39,7 @@ constexpr int kLC = 64;            // tokens per chunk
 constexpr int kLD = 128;           // key width == value width
 constexpr int kLP = 132;           // row pitch of the [64 x 128] matrices (floats)
 constexpr int kLQ = 68;            // row pitch of the [64 x 64] matrices
-constexpr int kLThreads = 256;
+constexpr int kLThreads = 512;
 
 struct LocalSmem {
   float big[5][kLC * kLP];
@@ -47,7 +47,8 @@ struct LocalSmem {
   float part[16][kLC];             // column sums: one partial per row group
   float b[kLC], beta[kLC], cdec[kLC], ik[kLC], iq[kLC];
   float alpha[kLC], softplus[kLC], sigmoid[kLC];
-  float dbeta[kLC], db[kLC];
+  float dbeta[2][kLC], db[2][kLC];   // row sums, one slot per column half (summed at the end)
+  float dots[2][2][kLC];             // per column half: <dq^, q^> and <dk^, k^> of every row
   float red[kLThreads / 32];
 };
 
@@ -66,52 +67,91 @@ __device__ __forceinline__ float4 load_any4(const void* p, size_t i, int is_bf16
 __device__ __forceinline__ float4 lds4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ float comp(const float4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
-// sum over the 16 lanes that share a row group (lanes with equal tid / 16)
+// sum over the 16 lanes that share a row group (the two halves of a warp)
 __device__ __forceinline__ float row_sum16(float v) {
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 
-// Thread (rg, cg) = (tid / 16, tid % 16) owns rows rg*4 .. +3 of every product.  Columns: two
-// groups of four, cg*4 .. +3 and 64 + cg*4 .. +3 ("dense"), where the B operand is read along its
-// rows -- the 16 lanes of a row group then read 256 contiguous bytes per 16-byte load, every bank
-// once; every 16th column cg + 16 j ("strided") where it is read along k -- with row pitches of
-// 132 / 68 floats those lanes fall into different banks too.
-__device__ __forceinline__ int dense_col(int cg, int j) { return cg * 4 + (j & 3) + ((j >> 2) << 6); }
+// 512 threads = 16 warps.  Warp w covers the column half ch = w & 1 of the row groups 2 (w >> 1) and
+// 2 (w >> 1) + 1 (one per half warp): thread (rg, ch, cg) owns rows rg*4 .. +3 and
+//   "dense"   columns ch*64 + cg*4 .. +3   where the B operand is read along its rows (the 16 lanes
+//             of a row group read 256 contiguous bytes per 16-byte load, the two row groups of a
+//             warp the same ones),
+//   "strided" columns cg + 16 j + 32 ch (j < 2) of a [64 x 64] result whose B operand is read along
+//             k: with row pitches of 132 / 68 floats those lanes fall into different banks too.
+// All products run on two-lane fp32 FMAs.
+struct Lane {
+  int rg, ch, cg, r0, c0;   // c0: first dense column
+};
 
-// acc[i][j] += sum_k A[r0+i][k] B[cg+16j][k]     (A B^T, [64 x 64] result, strided columns)
+// acc[i][j] += sum_k A[r0+i][k] B[cg+16j+32ch][k]     (A B^T, [64 x 64] result, strided columns)
 template <int K>
-__device__ __forceinline__ void nt_smem(const float* A, int pa, const float* B, int pb, int r0, int cg,
-                                        float (&acc)[4][4]) {
+__device__ __forceinline__ void nt_smem(const float* A, int pa, const float* B, int pb, const Lane& l,
+                                        float (&acc)[4][2]) {
+  uint64_t part[4][2];   // (even k, odd k) partial sums of every accumulator
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) part[i][j] = f2_pack(0.0f, 0.0f);
 #pragma unroll 2
   for (int k = 0; k < K; k += 4) {
-    float4 a[4], b[4];
+    float4 a[4], b[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = lds4(A + (r0 + i) * pa + k);
+    for (int i = 0; i < 4; ++i) a[i] = lds4(A + (l.r0 + i) * pa + k);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) b[j] = lds4(B + (cg + 16 * j) * pb + k);
+    for (int j = 0; j < 2; ++j) b[j] = lds4(B + (l.cg + 16 * j + 32 * l.ch) * pb + k);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 4; ++i) {
+      const uint64_t a01 = f2_pack(a[i].x, a[i].y), a23 = f2_pack(a[i].z, a[i].w);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
-        acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
-        acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
-        acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+      for (int j = 0; j < 2; ++j) {
+        part[i][j] = f2_fma(a01, f2_pack(b[j].x, b[j].y), part[i][j]);
+        part[i][j] = f2_fma(a23, f2_pack(b[j].z, b[j].w), part[i][j]);
       }
+    }
   }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float lo, hi;
+      f2_unpack(part[i][j], lo, hi);
+      acc[i][j] += lo + hi;
+    }
 }
 
-// acc[i][j] += sum_k A[r0+i][k] scale[k] B[k][cg*8+j]   (A B, [64 x 128] result, dense columns)
+__device__ __forceinline__ void to_pairs(const float (&acc)[4][4], uint64_t (&pair)[4][2]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) pair[i][j] = f2_pack(acc[i][2 * j], acc[i][2 * j + 1]);
+}
+__device__ __forceinline__ void from_pairs(const uint64_t (&pair)[4][2], float (&acc)[4][4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) f2_unpack(pair[i][j], acc[i][2 * j], acc[i][2 * j + 1]);
+}
+// pair[i][.] += a . (b.x, b.y), (b.z, b.w)
+__device__ __forceinline__ void dense_step(float av, const float4& bv, uint64_t (&pair)[2]) {
+  const uint64_t av2 = f2_pack(av, av);
+  pair[0] = f2_fma(av2, f2_pack(bv.x, bv.y), pair[0]);
+  pair[1] = f2_fma(av2, f2_pack(bv.z, bv.w), pair[1]);
+}
+
+// acc[i][j] += sum_k A[r0+i][k] scale[k] B[k][c0+j]   (A B, [64 x 128] result, dense columns)
 template <int K>
 __device__ __forceinline__ void nn_smem(const float* A, int pa, const float* scale, const float* B, int pb,
-                                        int r0, int cg, float (&acc)[4][8]) {
+                                        const Lane& l, float (&acc)[4][4]) {
+  uint64_t pair[4][2];
+  to_pairs(acc, pair);
 #pragma unroll 2
   for (int k = 0; k < K; k += 4) {
     float4 a[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = lds4(A + (r0 + i) * pa + k);
+    for (int i = 0; i < 4; ++i) a[i] = lds4(A + (l.r0 + i) * pa + k);
     if (scale != nullptr) {
       const float4 s = lds4(scale + k);
 #pragma unroll
@@ -119,36 +159,28 @@ __device__ __forceinline__ void nn_smem(const float* A, int pa, const float* sca
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      const float4 b0 = lds4(B + (k + kk) * pb + cg * 4), b1 = lds4(B + (k + kk) * pb + 64 + cg * 4);
+      const float4 bv = lds4(B + (k + kk) * pb + l.c0);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float av = comp(a[i], kk);
-        acc[i][0] = fmaf(av, b0.x, acc[i][0]); acc[i][1] = fmaf(av, b0.y, acc[i][1]);
-        acc[i][2] = fmaf(av, b0.z, acc[i][2]); acc[i][3] = fmaf(av, b0.w, acc[i][3]);
-        acc[i][4] = fmaf(av, b1.x, acc[i][4]); acc[i][5] = fmaf(av, b1.y, acc[i][5]);
-        acc[i][6] = fmaf(av, b1.z, acc[i][6]); acc[i][7] = fmaf(av, b1.w, acc[i][7]);
-      }
+      for (int i = 0; i < 4; ++i) dense_step(comp(a[i], kk), bv, pair[i]);
     }
   }
+  from_pairs(pair, acc);
 }
 
-// acc[i][j] += sum_k A[k][r0+i] B[k][cg*8+j]       (A^T B, dense columns)
+// acc[i][j] += sum_k A[k][r0+i] B[k][c0+j]       (A^T B, dense columns)
 template <int K>
-__device__ __forceinline__ void tn_smem(const float* A, int pa, const float* B, int pb, int r0, int cg,
-                                        float (&acc)[4][8]) {
-#pragma unroll 4
+__device__ __forceinline__ void tn_smem(const float* A, int pa, const float* B, int pb, const Lane& l,
+                                        float (&acc)[4][4]) {
+  uint64_t pair[4][2];
+  to_pairs(acc, pair);
+#pragma unroll 8
   for (int k = 0; k < K; ++k) {
-    const float4 a = lds4(A + k * pa + r0);
-    const float4 b0 = lds4(B + k * pb + cg * 4), b1 = lds4(B + k * pb + 64 + cg * 4);
+    const float4 a = lds4(A + k * pa + l.r0);
+    const float4 bv = lds4(B + k * pb + l.c0);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float av = comp(a, i);
-      acc[i][0] = fmaf(av, b0.x, acc[i][0]); acc[i][1] = fmaf(av, b0.y, acc[i][1]);
-      acc[i][2] = fmaf(av, b0.z, acc[i][2]); acc[i][3] = fmaf(av, b0.w, acc[i][3]);
-      acc[i][4] = fmaf(av, b1.x, acc[i][4]); acc[i][5] = fmaf(av, b1.y, acc[i][5]);
-      acc[i][6] = fmaf(av, b1.z, acc[i][6]); acc[i][7] = fmaf(av, b1.w, acc[i][7]);
-    }
+    for (int i = 0; i < 4; ++i) dense_step(comp(a, i), bv, pair[i]);
   }
+  from_pairs(pair, acc);
 }
 
 __device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {
@@ -158,17 +190,19 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// acc[i][j] += sum_k A[r0+i][k] Bg[k][dense column j]  with Bg a [128 x 128] matrix in global memory.
-// Its rows pass through a ring in shared memory, eight rows (4 KB, one 16-byte asynchronous copy per
+// acc[i][j] += sum_k A[r0+i][k] Bg[k][c0+j]  with Bg a [128 x 128] matrix in global memory.  Its
+// rows pass through a ring in shared memory, sixteen rows (8 KB, one 16-byte asynchronous copy per
 // thread) per stage and kRingStages - 1 stages in flight, so the products never wait for memory; all
-// 256 threads call this together.  `ring` holds kRingStages * 1024 floats and is free again on return.
-constexpr int kRingStages = 6;
+// 512 threads call this together.  `ring` holds kRingStages * 2048 floats and is free again on return.
+constexpr int kRingStages = 4;
 __device__ __forceinline__ void nn_ring(const float* A, int pa, const float* __restrict__ Bg, float* ring,
-                                        int r0, int cg, int tid, float (&acc)[4][8]) {
-  constexpr int kStageRows = 8, kStages = kLD / kStageRows;
+                                        const Lane& l, int tid, float (&acc)[4][4]) {
+  constexpr int kStageRows = 16, kStages = kLD / kStageRows, kStageFloats = kStageRows * kLD;
+  uint64_t pair[4][2];
+  to_pairs(acc, pair);
 #pragma unroll
   for (int s = 0; s < kRingStages - 1; ++s) {
-    cp_async16(ring + s * 1024 + tid * 4, Bg + s * 1024 + tid * 4);
+    cp_async16(ring + s * kStageFloats + tid * 4, Bg + s * kStageFloats + tid * 4);
     cp_async_commit();
   }
 #pragma unroll 1
@@ -176,30 +210,26 @@ __device__ __forceinline__ void nn_ring(const float* A, int pa, const float* __r
     cp_async_wait<kRingStages - 2>();
     __syncthreads();   // stage s has landed for every thread; the slot refilled below was read in step s - 1
     const int ahead = s + kRingStages - 1;
-    if (ahead < kStages) cp_async16(ring + (ahead % kRingStages) * 1024 + tid * 4, Bg + ahead * 1024 + tid * 4);
+    if (ahead < kStages)
+      cp_async16(ring + (ahead % kRingStages) * kStageFloats + tid * 4, Bg + ahead * kStageFloats + tid * 4);
     cp_async_commit();
-    const float* Bs = ring + (s % kRingStages) * 1024;
-#pragma unroll
+    const float* Bs = ring + (s % kRingStages) * kStageFloats;
+#pragma unroll 2
     for (int k = 0; k < kStageRows; k += 4) {
       float4 a[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = lds4(A + (r0 + i) * pa + s * kStageRows + k);
+      for (int i = 0; i < 4; ++i) a[i] = lds4(A + (l.r0 + i) * pa + s * kStageRows + k);
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
-        const float4 b0 = lds4(Bs + (k + kk) * kLD + cg * 4), b1 = lds4(Bs + (k + kk) * kLD + 64 + cg * 4);
+        const float4 bv = lds4(Bs + (k + kk) * kLD + l.c0);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float av = comp(a[i], kk);
-          acc[i][0] = fmaf(av, b0.x, acc[i][0]); acc[i][1] = fmaf(av, b0.y, acc[i][1]);
-          acc[i][2] = fmaf(av, b0.z, acc[i][2]); acc[i][3] = fmaf(av, b0.w, acc[i][3]);
-          acc[i][4] = fmaf(av, b1.x, acc[i][4]); acc[i][5] = fmaf(av, b1.y, acc[i][5]);
-          acc[i][6] = fmaf(av, b1.z, acc[i][6]); acc[i][7] = fmaf(av, b1.w, acc[i][7]);
-        }
+        for (int i = 0; i < 4; ++i) dense_step(comp(a[i], kk), bv, pair[i]);
       }
     }
   }
   cp_async_wait<0>();
   __syncthreads();
+  from_pairs(pair, acc);
 }
 
 template <int N>
@@ -210,13 +240,12 @@ __device__ __forceinline__ void zero(float (&acc)[4][N]) {
     for (int j = 0; j < N; ++j) acc[i][j] = 0.0f;
 }
 // dense tile -> [64 x 128] matrix in shared memory
-__device__ __forceinline__ void store_dense(float* dst, int r0, int cg, const float (&acc)[4][8]) {
+__device__ __forceinline__ void store_dense(float* dst, const Lane& l, const float (&acc)[4][4]) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    *reinterpret_cast<float4*>(dst + (r0 + i) * kLP + cg * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-    *reinterpret_cast<float4*>(dst + (r0 + i) * kLP + 64 + cg * 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
-  }
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<float4*>(dst + (l.r0 + i) * kLP + l.c0) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
 }
+__device__ __forceinline__ void to_array(const float4& v, float (&x)[4]) { x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w; }
 
 struct LocalArgs {
   GdnBwdArgs a;
@@ -234,7 +263,13 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kh = h / (a.value_heads / a.key_heads);
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int rg = tid >> 4, cg = tid & 15, r0 = rg * 4;
+  Lane l;
+  l.ch = warp & 1;
+  l.rg = (warp >> 1) * 2 + (lane >> 4);
+  l.cg = lane & 15;
+  l.r0 = l.rg * 4;
+  l.c0 = l.ch * 64 + l.cg * 4;
+  const int r0 = l.r0, c0 = l.c0;
   const int t0 = chunk * kLC, count = min(kLC, a.tokens - t0);
   const size_t unit = static_cast<size_t>(b) * a.value_heads + h;
   const size_t matrix = (unit * la.chunks + chunk) * kLD * kLD;
@@ -244,6 +279,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   const float* dSt = la.dstates_t + matrix;
   float* Kh = sm.big[0];
   const float q_scale = rsqrtf(static_cast<float>(kLD));
+  const size_t token0 = static_cast<size_t>(b) * a.tokens + t0;   // first token of the chunk
 
   // The four state matrices are first needed tens of microseconds from now and would come from
   // DRAM then: ask for them in L2 now.
@@ -255,7 +291,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   if (tid < kLC) {
     float lg = 0.0f, be = 0.0f, alpha = 0.0f, softplus = 0.0f, sigmoid = 0.0f;
     if (tid < count) {
-      const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + tid) * a.value_heads + h;
+      const size_t off = (token0 + tid) * a.value_heads + h;
       alpha = load_any(a.a_in, off, a.ab_is_bf16) + a.dt_bias[h];
       softplus = fmaxf(alpha, 0.0f) + logf(1.0f + expf(-fabsf(alpha)));
       sigmoid = 1.0f / (1.0f + expf(-load_any(a.b_in, off, a.ab_is_bf16)));
@@ -267,29 +303,23 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     sm.sigmoid[tid] = sigmoid;
     sm.beta[tid] = be;
     sm.b[tid] = lg;          // log decay, summed below
-    sm.dbeta[tid] = 0.0f;
-    sm.db[tid] = 0.0f;
+    sm.dbeta[0][tid] = sm.dbeta[1][tid] = 0.0f;
+    sm.db[0][tid] = sm.db[1][tid] = 0.0f;
+  }
+  // ---- keys and queries: k -> big[0], q -> big[1] (normalised below)
+  for (int idx = tid; idx < 2 * kLC * (kLD / 4); idx += kLThreads) {
+    const int which = idx / (kLC * (kLD / 4)), rest = idx % (kLC * (kLD / 4));
+    const int t = rest / (kLD / 4), c4 = rest % (kLD / 4);
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (t < count)
+      v = load_any4(which ? a.q : a.k, (token0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + c4 * 4, a.in_is_bf16);
+    *reinterpret_cast<float4*>(sm.big[which] + t * kLP + c4 * 4) = v;
   }
   __syncthreads();
   if (tid == 0) {
     float run = 0.0f;
     for (int t = 0; t < kLC; ++t) { run += sm.b[t]; sm.b[t] = run; }
   }
-  __syncthreads();
-  if (tid < kLC) sm.cdec[tid] = expf(sm.b[tid]);
-
-  // ---- keys and queries, normalised: k^ -> big[0], q^ -> big[1]
-  for (int idx = tid; idx < 2 * kLC * (kLD / 4); idx += kLThreads) {
-    const int which = idx / (kLC * (kLD / 4)), rest = idx % (kLC * (kLD / 4));
-    const int t = rest / (kLD / 4), c4 = rest % (kLD / 4);
-    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (t < count) {
-      const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + c4 * 4;
-      v = load_any4(which ? a.q : a.k, off, a.in_is_bf16);
-    }
-    *reinterpret_cast<float4*>(sm.big[which] + t * kLP + c4 * 4) = v;
-  }
-  __syncthreads();
   for (int vec = warp; vec < 2 * kLC; vec += kLThreads / 32) {
     const int which = vec / kLC, t = vec % kLC;
     float* row = sm.big[which] + t * kLP;
@@ -303,19 +333,20 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     if (lane == 0) (which ? sm.iq : sm.ik)[t] = inv;
   }
   __syncthreads();
+  if (tid < kLC) sm.cdec[tid] = expf(sm.b[tid]);
 
   // ---- A (transposed, for the substitution) -> sq[0];  M -> sq[1]
   {
-    float g[4][4], hh[4][4];
+    float g[4][2], hh[4][2];
     zero(g);
     zero(hh);
-    nt_smem<kLD>(Kh, kLP, Kh, kLP, r0, cg, g);
-    nt_smem<kLD>(sm.big[1], kLP, Kh, kLP, r0, cg, hh);
+    nt_smem<kLD>(Kh, kLP, Kh, kLP, l, g);
+    nt_smem<kLD>(sm.big[1], kLP, Kh, kLP, l, hh);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int t = r0 + i, s = cg + 16 * j;
+      for (int j = 0; j < 2; ++j) {
+        const int t = r0 + i, s = l.cg + 16 * j + 32 * l.ch;
         const float ratio = s <= t ? expf(sm.b[t] - sm.b[s]) : 0.0f;
         sm.sq[0][s * kLQ + t] = s < t ? sm.beta[t] * ratio * g[i][j] : 0.0f;
         sm.sq[1][t * kLQ + s] = ratio * hh[i][j];
@@ -323,102 +354,99 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   }
   __syncthreads();
 
-  // ---- T = (I + A)^-1 -> sq[2], one thread per column, right-looking forward substitution
+  // ---- T = (I + A)^-1 -> sq[2], one thread per column, right-looking forward substitution;
+  //      meanwhile the other warps stage v -> big[2]
   if (tid < kLC) {
-    float x[kLC];
+    uint64_t x[kLC / 2];
 #pragma unroll
-    for (int t = 0; t < kLC; ++t) x[t] = t == tid ? 1.0f : 0.0f;
+    for (int t = 0; t < kLC / 2; ++t) x[t] = f2_pack(2 * t == tid ? 1.0f : 0.0f, 2 * t + 1 == tid ? 1.0f : 0.0f);
 #pragma unroll
     for (int s = 0; s < kLC - 1; ++s) {
-      const float xs = x[s];
+      float lo, hi;
+      f2_unpack(x[s >> 1], lo, hi);
+      const float xs = s & 1 ? hi : lo;
+      const uint64_t minus = f2_pack(-xs, -xs);
 #pragma unroll
       for (int t4 = (s + 1) / 4; t4 < kLC / 4; ++t4) {
         const float4 av = lds4(sm.sq[0] + s * kLQ + t4 * 4);   // A[t][s], zero for t <= s
-        x[t4 * 4 + 0] = fmaf(-av.x, xs, x[t4 * 4 + 0]);
-        x[t4 * 4 + 1] = fmaf(-av.y, xs, x[t4 * 4 + 1]);
-        x[t4 * 4 + 2] = fmaf(-av.z, xs, x[t4 * 4 + 2]);
-        x[t4 * 4 + 3] = fmaf(-av.w, xs, x[t4 * 4 + 3]);
+        x[2 * t4] = f2_fma(f2_pack(av.x, av.y), minus, x[2 * t4]);
+        x[2 * t4 + 1] = f2_fma(f2_pack(av.z, av.w), minus, x[2 * t4 + 1]);
       }
     }
 #pragma unroll
-    for (int t = 0; t < kLC; ++t) sm.sq[2][t * kLQ + tid] = x[t];
+    for (int t = 0; t < kLC / 2; ++t) {
+      float lo, hi;
+      f2_unpack(x[t], lo, hi);
+      sm.sq[2][(2 * t) * kLQ + tid] = lo;
+      sm.sq[2][(2 * t + 1) * kLQ + tid] = hi;
+    }
+  } else {
+    for (int idx = tid - kLC; idx < kLC * (kLD / 4); idx += kLThreads - kLC) {
+      const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (t < count)
+        v = load_any4(a.v, (token0 + t) * a.v_token + static_cast<size_t>(h) * kLD + c4 * 4, a.in_is_bf16);
+      *reinterpret_cast<float4*>(sm.big[2] + t * kLP + c4 * 4) = v;
+    }
   }
+  if (tid < kLC) sm.part[0][tid] = sm.beta[tid] * sm.cdec[tid];
   __syncthreads();
   const float* Tm = sm.sq[2];
   const float* Mm = sm.sq[1];
 
-  // ---- W = T (beta c . k^) -> big[1] (the queries are read again later)
-  if (tid < kLC) sm.part[0][tid] = sm.beta[tid] * sm.cdec[tid];
-  __syncthreads();
+  // ---- W = T (beta c . k^) -> big[1] (the queries are read again later);  U' = T (beta . v) -> big[3]
   {
-    float acc[4][8];
+    float acc[4][4];
     zero(acc);
-    nn_smem<kLC>(Tm, kLQ, sm.part[0], Kh, kLP, r0, cg, acc);
-    store_dense(sm.big[1], r0, cg, acc);
-  }
-  // ---- v -> big[2];  U' = T (beta . v) -> big[3]
-  for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
-    const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
-    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (t < count) {
-      const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.v_token + static_cast<size_t>(h) * kLD + c4 * 4;
-      v = load_any4(a.v, off, a.in_is_bf16);
-    }
-    *reinterpret_cast<float4*>(sm.big[2] + t * kLP + c4 * 4) = v;
-  }
-  __syncthreads();
-  {
-    float acc[4][8];
+    nn_smem<kLC>(Tm, kLQ, sm.part[0], Kh, kLP, l, acc);
+    store_dense(sm.big[1], l, acc);
     zero(acc);
-    nn_smem<kLC>(Tm, kLQ, sm.beta, sm.big[2], kLP, r0, cg, acc);
-    store_dense(sm.big[3], r0, cg, acc);
+    nn_smem<kLC>(Tm, kLQ, sm.beta, sm.big[2], kLP, l, acc);
+    store_dense(sm.big[3], l, acc);
   }
   __syncthreads();
   // ---- U = U' - W S_0 -> big[4]
   {
-    float acc[4][8];
+    float acc[4][4];
     zero(acc);
-    nn_ring(sm.big[1], kLP, S0, sm.big[2], r0, cg, tid, acc);   // (v in big[2] is dead: U' is complete)
+    nn_ring(sm.big[1], kLP, S0, sm.big[2], l, tid, acc);   // (v in big[2] is dead: U' is complete)
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int e = (r0 + i) * kLP + dense_col(cg, j);
-        sm.big[4][e] = sm.big[3][e] - acc[i][j];
-      }
+    for (int i = 0; i < 4; ++i) {
+      const float4 up = lds4(sm.big[3] + (r0 + i) * kLP + c0);
+      *reinterpret_cast<float4*>(sm.big[4] + (r0 + i) * kLP + c0) =
+          make_float4(up.x - acc[i][0], up.y - acc[i][1], up.z - acc[i][2], up.w - acc[i][3]);
+    }
   }
-  __syncthreads();
-  // ---- dO -> big[2]
+  // ---- dO -> big[2] (the ring is free: nn_ring ends with a barrier)
   for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
     const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
     float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (t < count)
-      v = ldg4(a.dcore + ((static_cast<size_t>(b) * a.tokens + t0 + t) * a.value_heads + h) * kLD + c4 * 4);
+    if (t < count) v = ldg4(a.dcore + ((token0 + t) * a.value_heads + h) * kLD + c4 * 4);
     *reinterpret_cast<float4*>(sm.big[2] + t * kLP + c4 * 4) = v;
   }
   __syncthreads();
 
-  // row sums into sm.db / sm.dbeta are added by the lane with cg == 0 of the row's group; column
-  // sums go through sm.part
-  auto add_rows = [&](float* dst, const float (&v)[4], float sign) {
+  // row sums into sm.db / sm.dbeta: added by the lane with cg == 0 of the row's group, into the
+  // slot of its column half; column sums go through sm.part
+  auto add_rows = [&](float (*dst)[kLC], const float (&v)[4], float sign) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float total = row_sum16(v[i]);
-      if (cg == 0) dst[r0 + i] += sign * total;
+      if (l.cg == 0) dst[l.ch][r0 + i] += sign * total;
     }
   };
 
   // ---- dM = mask(dO U^T): M-bar = dM . M into db, dH = dM . ratio -> sq[0]
   {
-    float acc[4][4];
+    float acc[4][2];
     zero(acc);
-    nt_smem<kLD>(sm.big[2], kLP, sm.big[4], kLP, r0, cg, acc);
-    float rows[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cols[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    nt_smem<kLD>(sm.big[2], kLP, sm.big[4], kLP, l, acc);
+    float rows[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cols[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int t = r0 + i, s = cg + 16 * j;
+      for (int j = 0; j < 2; ++j) {
+        const int t = r0 + i, s = l.cg + 16 * j + 32 * l.ch;
         const float dm = s <= t ? acc[i][j] : 0.0f;
         const float bar = dm * Mm[t * kLQ + s];
         rows[i] += bar;
@@ -427,16 +455,17 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       }
     add_rows(sm.db, rows, 1.0f);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) sm.part[rg][cg + 16 * j] = cols[j];
+    for (int j = 0; j < 2; ++j) sm.part[l.rg][l.cg + 16 * j + 32 * l.ch] = cols[j];
   }
   __syncthreads();
   if (tid < kLC) {
     float total = 0.0f;
 #pragma unroll
     for (int g = 0; g < 16; ++g) total += sm.part[g][tid];
-    sm.db[tid] -= total;
+    sm.part[0][tid] = total;   // (own column of row 0 only: no other thread reads it)
   }
   __syncthreads();
+  if (tid < kLC) sm.db[0][tid] -= sm.part[0][tid];   // cg == 0 lanes add to db only after later barriers
 
   // The two contributions that are known early -- (gamma/c) . dKt to dk^ and c . dQc to dq^ -- wait
   // in this chunk's rows of the output partials (each thread its own elements) until the last
@@ -446,171 +475,183 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
 
   // ---- dKt = U dS^T (dense columns = keys)
   {
-    float acc[4][8];
+    float acc[4][4];
     zero(acc);
-    nn_ring(sm.big[4], kLP, dSt, sm.big[3], r0, cg, tid, acc);   // (W and U' are dead from here on: big[1], big[3])
+    nn_ring(sm.big[4], kLP, dSt, sm.big[3], l, tid, acc);   // (W and U' are dead from here on: big[1], big[3])
     float rows[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float f = gamma / sm.cdec[r0 + i];
-      float rs = 0.0f;
-      float* stash = a.qk_partials + ((static_cast<size_t>(b) * a.tokens + min(t0 + r0 + i, a.tokens - 1)) * a.value_heads + h) * 2 * kLD + kLD;
+      float kv[4];
+      to_array(lds4(Kh + (r0 + i) * kLP + c0), kv);
+      float rs = 0.0f, scaled[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float scaled = acc[i][j] * f;
-        if (r0 + i < count) stash[dense_col(cg, j)] = scaled;
-        rs = fmaf(scaled, Kh[(r0 + i) * kLP + dense_col(cg, j)], rs);
+      for (int j = 0; j < 4; ++j) {
+        scaled[j] = acc[i][j] * f;
+        rs = fmaf(scaled[j], kv[j], rs);
       }
+      if (r0 + i < count)
+        *reinterpret_cast<float4*>(a.qk_partials + ((token0 + r0 + i) * a.value_heads + h) * 2 * kLD + kLD + c0) =
+            make_float4(scaled[0], scaled[1], scaled[2], scaled[3]);
       rows[i] = rs;
       kt_total += rs;
     }
     add_rows(sm.db, rows, -1.0f);
   }
-  __syncthreads();   // every read of U is done
-  // ---- dU = M^T dO + Kt dS -> big[4]
+  // ---- dU = M^T dO + Kt dS -> big[4]   (every read of U is done: nn_ring ends with a barrier)
   {
-    float acc[4][8], from_state[4][8];
+    float acc[4][4], from_state[4][4];
     zero(acc);
     zero(from_state);
-    tn_smem<kLC>(Mm, kLQ, sm.big[2], kLP, r0, cg, acc);
-    nn_ring(Kh, kLP, dS, sm.big[3], r0, cg, tid, from_state);
+    tn_smem<kLC>(Mm, kLQ, sm.big[2], kLP, l, acc);
+    nn_ring(Kh, kLP, dS, sm.big[3], l, tid, from_state);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float f = gamma / sm.cdec[r0 + i];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(f, from_state[i][j], acc[i][j]);
+      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(f, from_state[i][j], acc[i][j]);
     }
-    store_dense(sm.big[4], r0, cg, acc);
+    store_dense(sm.big[4], l, acc);
   }
   // ---- dQc = dO S_0^T: dq^ += c . dQc, db += rows(dQc . c q^)
   {
-    float acc[4][8];
+    float4 qraw[4];   // requested before the product, used after it
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      qraw[i] = r0 + i < count ? load_any4(a.q, (token0 + r0 + i) * a.qk_token + static_cast<size_t>(kh) * kLD + c0, a.in_is_bf16)
+                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float acc[4][4];
     zero(acc);
-    nn_ring(sm.big[2], kLP, S0t, sm.big[3], r0, cg, tid, acc);
+    nn_ring(sm.big[2], kLP, S0t, sm.big[3], l, tid, acc);
     float rows[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int t = r0 + i;
-      const float c = sm.cdec[t];
-      float rs = 0.0f;
-      if (t < count) {
-        const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + cg * 4;
-        const float4 q0 = load_any4(a.q, off, a.in_is_bf16), q1 = load_any4(a.q, off + 64, a.in_is_bf16);
-        const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        const float f = sm.iq[t] * q_scale;
-        float* stash = a.qk_partials + ((static_cast<size_t>(b) * a.tokens + t0 + t) * a.value_heads + h) * 2 * kLD;
+      const float c = sm.cdec[t], f = sm.iq[t] * q_scale;
+      float qv[4], scaled[4], rs = 0.0f;
+      to_array(qraw[i], qv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float scaled = acc[i][j] * c;
-          stash[dense_col(cg, j)] = scaled;
-          rs = fmaf(scaled, qv[j] * f, rs);
-        }
+      for (int j = 0; j < 4; ++j) {
+        scaled[j] = acc[i][j] * c;
+        rs = fmaf(scaled[j], qv[j] * f, rs);
       }
+      if (t < count)
+        *reinterpret_cast<float4*>(a.qk_partials + ((token0 + t) * a.value_heads + h) * 2 * kLD + c0) =
+            make_float4(scaled[0], scaled[1], scaled[2], scaled[3]);
       rows[i] = rs;
     }
     add_rows(sm.db, rows, 1.0f);
   }
-  __syncthreads();   // dU complete; dO no longer needed
-  // ---- dW = -dU S_0^T -> big[2]
+  // ---- dW = -dU S_0^T -> big[2]   (dU is complete and dO no longer needed: barriers inside nn_ring)
   {
-    float acc[4][8];
+    float acc[4][4];
     zero(acc);
-    nn_ring(sm.big[4], kLP, S0t, sm.big[3], r0, cg, tid, acc);
+    nn_ring(sm.big[4], kLP, S0t, sm.big[3], l, tid, acc);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[i][j] = -acc[i][j];
-    store_dense(sm.big[2], r0, cg, acc);
+      for (int j = 0; j < 4; ++j) acc[i][j] = -acc[i][j];
+    store_dense(sm.big[2], l, acc);
   }
   // ---- X1 = T^T dU: dv = beta . X1, dbeta += rows(X1 . v); X1 replaces dU
   {
-    float acc[4][8];
+    float4 vraw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      vraw[i] = r0 + i < count ? load_any4(a.v, (token0 + r0 + i) * a.v_token + static_cast<size_t>(h) * kLD + c0, a.in_is_bf16)
+                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float acc[4][4];
     zero(acc);
-    tn_smem<kLC>(Tm, kLQ, sm.big[4], kLP, r0, cg, acc);
+    tn_smem<kLC>(Tm, kLQ, sm.big[4], kLP, l, acc);
     float rows[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int t = r0 + i;
-      float rs = 0.0f;
-      if (t < count) {
-        const size_t voff = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.v_token + static_cast<size_t>(h) * kLD + cg * 4;
-        float* dv = a.dv_out + (static_cast<size_t>(b) * a.tokens + t0 + t) * a.dv_token + static_cast<size_t>(h) * kLD;
-        const float4 v0 = load_any4(a.v, voff, a.in_is_bf16), v1 = load_any4(a.v, voff + 64, a.in_is_bf16);
-        const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+      float vv[4], rs = 0.0f;
+      to_array(vraw[i], vv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          rs = fmaf(acc[i][j], vv[j], rs);
-          dv[dense_col(cg, j)] = sm.beta[t] * acc[i][j];
-        }
+      for (int j = 0; j < 4; ++j) rs = fmaf(acc[i][j], vv[j], rs);
+      if (t < count) {
+        const float be = sm.beta[t];
+        *reinterpret_cast<float4*>(a.dv_out + (token0 + t) * a.dv_token + static_cast<size_t>(h) * kLD + c0) =
+            make_float4(be * acc[i][0], be * acc[i][1], be * acc[i][2], be * acc[i][3]);
       }
       rows[i] = rs;
     }
     add_rows(sm.dbeta, rows, 1.0f);
     __syncthreads();   // every read of dU is done (and dW is complete)
-    store_dense(sm.big[4], r0, cg, acc);
+    store_dense(sm.big[4], l, acc);
   }
-  // ---- X2 = T^T dW: dk^ += beta c . X2, dbeta += rows(X2 . c k^), db += rows(X2 . beta c k^); X2 replaces dW
+  // ---- X2 = T^T dW: dk^ += beta c . X2 (at the end), dbeta += rows(X2 . c k^), db += rows(X2 . beta c k^); X2 replaces dW
   {
-    float acc[4][8];
+    float acc[4][4];
     zero(acc);
-    tn_smem<kLC>(Tm, kLQ, sm.big[2], kLP, r0, cg, acc);
+    tn_smem<kLC>(Tm, kLQ, sm.big[2], kLP, l, acc);
     float rows_beta[4], rows_b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int t = r0 + i;
-      const float c = sm.cdec[t], be = sm.beta[t];
-      float rs = 0.0f;
+      float kv[4], rs = 0.0f;
+      to_array(lds4(Kh + t * kLP + c0), kv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) rs = fmaf(acc[i][j] * c, Kh[t * kLP + dense_col(cg, j)], rs);   // (beta c . X2 joins dk^ at the end)
-      rows_beta[i] = rs;
-      rows_b[i] = rs * be;
+      for (int j = 0; j < 4; ++j) rs = fmaf(acc[i][j], kv[j], rs);
+      rows_beta[i] = rs * sm.cdec[t];
+      rows_b[i] = rows_beta[i] * sm.beta[t];
     }
     add_rows(sm.dbeta, rows_beta, 1.0f);
     add_rows(sm.db, rows_b, 1.0f);
     __syncthreads();   // every read of dW is done
-    store_dense(sm.big[2], r0, cg, acc);
+    store_dense(sm.big[2], l, acc);
   }
-  __syncthreads();
   // ---- dA = -mask(X1 U'^T + X2 W^T) = -mask(R T^T),  R = X1 (beta . v)^T + X2 (beta c . k^)^T: U' and W
   //      need not be kept.  v is staged again (big[3]); R -> sq[1] (M is dead)
   for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
     const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
     float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (t < count) {
-      const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.v_token + static_cast<size_t>(h) * kLD + c4 * 4;
-      v = load_any4(a.v, off, a.in_is_bf16);
-    }
+    if (t < count)
+      v = load_any4(a.v, (token0 + t) * a.v_token + static_cast<size_t>(h) * kLD + c4 * 4, a.in_is_bf16);
     *reinterpret_cast<float4*>(sm.big[3] + t * kLP + c4 * 4) = v;
   }
   __syncthreads();
   {
-    float from_v[4][4], from_k[4][4];
+    float from_v[4][2], from_k[4][2];
     zero(from_v);
     zero(from_k);
-    nt_smem<kLD>(sm.big[4], kLP, sm.big[3], kLP, r0, cg, from_v);
-    nt_smem<kLD>(sm.big[2], kLP, Kh, kLP, r0, cg, from_k);
+    nt_smem<kLD>(sm.big[4], kLP, sm.big[3], kLP, l, from_v);
+    nt_smem<kLD>(sm.big[2], kLP, Kh, kLP, l, from_k);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int s2 = cg + 16 * j;
+      for (int j = 0; j < 2; ++j) {
+        const int s2 = l.cg + 16 * j + 32 * l.ch;
         sm.sq[1][(r0 + i) * kLQ + s2] = sm.beta[s2] * fmaf(sm.cdec[s2], from_k[i][j], from_v[i][j]);
       }
   }
   __syncthreads();
+  // q^ is staged again (big[1]) while the last [64 x 64] products run
+  for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
+    const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (t < count) {
+      const float f = sm.iq[t] * q_scale;
+      v = load_any4(a.q, (token0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + c4 * 4, a.in_is_bf16);
+      v = make_float4(v.x * f, v.y * f, v.z * f, v.w * f);
+    }
+    *reinterpret_cast<float4*>(sm.big[1] + t * kLP + c4 * 4) = v;
+  }
   {
-    float acc[4][4], g[4][4];
+    float acc[4][2], g[4][2];
     zero(acc);
     zero(g);
-    nt_smem<kLC>(sm.sq[1], kLQ, Tm, kLQ, r0, cg, acc);
-    nt_smem<kLD>(Kh, kLP, Kh, kLP, r0, cg, g);
+    nt_smem<kLC>(sm.sq[1], kLQ, Tm, kLQ, l, acc);
+    nt_smem<kLD>(Kh, kLP, Kh, kLP, l, g);
     __syncthreads();   // every read of R is done: dG + dG^T goes over it
-    float rows_beta[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rows_b[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cols[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float rows_beta[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rows_b[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cols[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int t = r0 + i, s = cg + 16 * j;
+      for (int j = 0; j < 2; ++j) {
+        const int t = r0 + i, s = l.cg + 16 * j + 32 * l.ch;
         if (s < t) {
           const float e = expf(sm.b[t] - sm.b[s]);
           const float per_beta = -acc[i][j] * e * g[i][j];   // dA . dA/dbeta_t
@@ -628,70 +669,59 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     add_rows(sm.dbeta, rows_beta, 1.0f);
     add_rows(sm.db, rows_b, 1.0f);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) sm.part[rg][cg + 16 * j] = cols[j];
+    for (int j = 0; j < 2; ++j) sm.part[l.rg][l.cg + 16 * j + 32 * l.ch] = cols[j];
   }
   __syncthreads();
   if (tid < kLC) {
     float total = 0.0f;
 #pragma unroll
     for (int g = 0; g < 16; ++g) total += sm.part[g][tid];
-    sm.db[tid] -= total;
+    sm.part[0][tid] = total;
   }
-  // ---- dk^ += (dG + dG^T) k^ + dH^T q^;  dq^ += dH k^   (q^ is staged again, into big[1])
-  for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
-    const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
-    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (t < count) {
-      const size_t off = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + c4 * 4;
-      const float f = sm.iq[t] * q_scale;
-      v = load_any4(a.q, off, a.in_is_bf16);
-      v = make_float4(v.x * f, v.y * f, v.z * f, v.w * f);
-    }
-    *reinterpret_cast<float4*>(sm.big[1] + t * kLP + c4 * 4) = v;
-  }
-  __syncthreads();
-  float dk_acc[4][8], dq_acc[4][8];
+  // ---- dk^ = stashed + beta c . X2 + (dG + dG^T) k^ + dH^T q^;  dq^ = stashed + dH k^
+  float dk_acc[4][4], dq_acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int t = r0 + i;
-    const float* stash = a.qk_partials + ((static_cast<size_t>(b) * a.tokens + min(t0 + t, a.tokens - 1)) * a.value_heads + h) * 2 * kLD;
+    const float* stash = a.qk_partials + ((token0 + min(t, count - 1)) * a.value_heads + h) * 2 * kLD + c0;
     const float bc = sm.beta[t] * sm.cdec[t];
-    const float4 x0 = lds4(sm.big[2] + t * kLP + cg * 4), x1 = lds4(sm.big[2] + t * kLP + 64 + cg * 4);   // X2
-    const float x2[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    float x2[4], sq_[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sk_[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    to_array(lds4(sm.big[2] + t * kLP + c0), x2);
+    if (t < count) {
+      to_array(*reinterpret_cast<const float4*>(stash), sq_);
+      to_array(*reinterpret_cast<const float4*>(stash + kLD), sk_);
+    }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      dq_acc[i][j] = t < count ? stash[dense_col(cg, j)] : 0.0f;
-      dk_acc[i][j] = (t < count ? stash[kLD + dense_col(cg, j)] : 0.0f) + bc * x2[j];
+    for (int j = 0; j < 4; ++j) {
+      dq_acc[i][j] = sq_[j];
+      dk_acc[i][j] = sk_[j] + bc * x2[j];
     }
   }
-  nn_smem<kLC>(sm.sq[1], kLQ, nullptr, Kh, kLP, r0, cg, dk_acc);
-  nn_smem<kLC>(sm.sq[0], kLQ, nullptr, Kh, kLP, r0, cg, dq_acc);
-  tn_smem<kLC>(sm.sq[0], kLQ, sm.big[1], kLP, r0, cg, dk_acc);
+  nn_smem<kLC>(sm.sq[1], kLQ, nullptr, Kh, kLP, l, dk_acc);
+  nn_smem<kLC>(sm.sq[0], kLQ, nullptr, Kh, kLP, l, dq_acc);
+  tn_smem<kLC>(sm.sq[0], kLQ, sm.big[1], kLP, l, dk_acc);
 
-  // ---- through the normalisations: per-token partials in the layout of the gather kernels (one tile)
+  // ---- through the normalisations: per-token partials in the layout of the gather kernels (one
+  //      tile).  The row dot products span both column halves: exchanged through sm.dots.
+  float kv[4][4], qv[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int t = r0 + i;
+    to_array(lds4(Kh + t * kLP + c0), kv[i]);
+    to_array(lds4(sm.big[1] + t * kLP + c0), qv[i]);
     float pk = 0.0f, pq = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      pk = fmaf(dk_acc[i][j], Kh[t * kLP + dense_col(cg, j)], pk);
-      pq = fmaf(dq_acc[i][j], sm.big[1][t * kLP + dense_col(cg, j)], pq);
+    for (int j = 0; j < 4; ++j) {
+      pk = fmaf(dk_acc[i][j], kv[i][j], pk);
+      pq = fmaf(dq_acc[i][j], qv[i][j], pq);
     }
     pk = row_sum16(pk);
-    pq = row_sum16(pq) / (q_scale * q_scale);   // q^ = scale . unit vector
-    if (t < count) {
-      const size_t partial = (static_cast<size_t>(b) * a.tokens + t0 + t) * a.value_heads + h;
-      float* out = a.qk_partials + partial * 2 * kLD;
-      const float ikt = sm.ik[t], iqt = sm.iq[t] * q_scale;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        out[dense_col(cg, j)] = iqt * (dq_acc[i][j] - sm.big[1][t * kLP + dense_col(cg, j)] * pq);
-        out[kLD + dense_col(cg, j)] = ikt * (dk_acc[i][j] - Kh[t * kLP + dense_col(cg, j)] * pk);
-      }
+    pq = row_sum16(pq);
+    if (l.cg == 0) {
+      sm.dots[l.ch][0][t] = pq;
+      sm.dots[l.ch][1][t] = pk;
     }
   }
-
   // ---- the chunk-end terms of db: sum(dKt . Kt) + gamma <dS_C, S_0>
   {
     float dot = 0.0f;
@@ -705,21 +735,39 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     if (lane == 0) sm.red[warp] = total;
   }
   __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = r0 + i;
+    if (t < count) {
+      const float pq = (sm.dots[0][0][t] + sm.dots[1][0][t]) / (q_scale * q_scale);   // q^ = scale . unit vector
+      const float pk = sm.dots[0][1][t] + sm.dots[1][1][t];
+      const float ikt = sm.ik[t], iqt = sm.iq[t] * q_scale;
+      float* out = a.qk_partials + ((token0 + t) * a.value_heads + h) * 2 * kLD + c0;
+      *reinterpret_cast<float4*>(out) =
+          make_float4(iqt * (dq_acc[i][0] - qv[i][0] * pq), iqt * (dq_acc[i][1] - qv[i][1] * pq),
+                      iqt * (dq_acc[i][2] - qv[i][2] * pq), iqt * (dq_acc[i][3] - qv[i][3] * pq));
+      *reinterpret_cast<float4*>(out + kLD) =
+          make_float4(ikt * (dk_acc[i][0] - kv[i][0] * pk), ikt * (dk_acc[i][1] - kv[i][1] * pk),
+                      ikt * (dk_acc[i][2] - kv[i][2] * pk), ikt * (dk_acc[i][3] - kv[i][3] * pk));
+    }
+  }
   if (tid == 0) {
     float total = 0.0f;
     for (int w = 0; w < kLThreads / 32; ++w) total += sm.red[w];
-    sm.db[kLC - 1] += total;
-    // d log g_s = sum of db_t over t >= s
+    // d log g_s = sum of db_t over t >= s (db: both column halves, minus the column sums of A-bar)
     float run = 0.0f;
-    for (int t = kLC - 1; t >= 0; --t) { run += sm.db[t]; sm.db[t] = run; }
+    for (int t = kLC - 1; t >= 0; --t) {
+      run += sm.db[0][t] + sm.db[1][t] - sm.part[0][t] + (t == kLC - 1 ? total : 0.0f);
+      sm.db[0][t] = run;
+    }
   }
   __syncthreads();
   if (tid < count) {
-    const size_t partial = (static_cast<size_t>(b) * a.tokens + t0 + tid) * a.value_heads + h;
+    const size_t partial = (token0 + tid) * a.value_heads + h;
     const float rate = expf(a.a_log[h]);
-    const float dlog = sm.db[tid];
+    const float dlog = sm.db[0][tid];
     a.scalar_partials[partial * 3 + 0] = -dlog * rate / (1.0f + expf(-sm.alpha[tid]));
-    a.scalar_partials[partial * 3 + 1] = sm.dbeta[tid] * sm.sigmoid[tid] * (1.0f - sm.sigmoid[tid]);
+    a.scalar_partials[partial * 3 + 1] = (sm.dbeta[0][tid] + sm.dbeta[1][tid]) * sm.sigmoid[tid] * (1.0f - sm.sigmoid[tid]);
     a.scalar_partials[partial * 3 + 2] = -dlog * rate * sm.softplus[tid];
   }
 }
