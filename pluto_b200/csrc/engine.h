@@ -275,11 +275,12 @@ cudaError_t gdn_recurrence_bwd(cudaStream_t stream, GdnBwdArgs args, float* dq_o
                                size_t dqk_token, float* da, float* db, float* d_a_log,
                                float* d_dt_bias, void* workspace);
 // gdn_bwd_chunked.cu: chunk-parallel form (two tensor-core scans + one CTA per chunk) for bf16
-// activations with key width = value width = 128; fills qk_partials / scalar_partials (one tile
-// per head) and dv_out
+// activations with key width = value width = 128; fills scalar_partials (one tile per head), dv_out
+// and the q / k gradients (directly when *qk_direct comes back true, else as qk_partials)
 bool gdn_bwd_chunked_supported(const GdnBwdArgs& args);
 size_t gdn_bwd_chunked_workspace_bytes(int batch, int tokens, int value_heads);
-cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& args, void* workspace, uint32_t* status);
+cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& args, float* dq_out, float* dk_out, size_t dqk_token,
+                            void* workspace, uint32_t* status, bool* qk_direct);
 cudaError_t gdn_conv_bwd(cudaStream_t stream, const void* input, int in_is_bf16, const float* weight,
                          const float* dpost, int batch, int tokens, int channels, int width, int round,
                          float* dx, float* d_weight);

@@ -440,12 +440,15 @@ cudaError_t gdn_recurrence_bwd(cudaStream_t stream, GdnBwdArgs a, float* dq_out,
                                size_t dqk_token, float* da, float* db, float* d_a_log,
                                float* d_dt_bias, void* workspace) {
   if (gdn_bwd_chunked_supported(a)) {
-    cudaError_t e = gdn_bwd_chunked(stream, a, workspace, kernel_status_word());
+    bool qk_direct = false;
+    cudaError_t e = gdn_bwd_chunked(stream, a, dq_out, dk_out, dqk_token, workspace, kernel_status_word(), &qk_direct);
     if (e != cudaSuccess) return e;
-    gdn_gather_qk_kernel<<<dim3(a.batch * a.tokens, a.key_heads), 128, 0, stream>>>(
-        a.qk_partials, a.key_heads, a.value_heads, a.key_dim, 1, dq_out, dk_out, dqk_token);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
+    if (!qk_direct) {
+      gdn_gather_qk_kernel<<<dim3(a.batch * a.tokens, a.key_heads), 128, 0, stream>>>(
+          a.qk_partials, a.key_heads, a.value_heads, a.key_dim, 1, dq_out, dk_out, dqk_token);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+    }
     gdn_gather_scalar_kernel<<<a.value_heads, 256, 0, stream>>>(
         a.scalar_partials, static_cast<long long>(a.batch) * a.tokens, a.value_heads, 1, da, db, d_a_log,
         d_dt_bias);

@@ -254,6 +254,12 @@ struct LocalArgs {
   const float* dstates;     // [sequence, head, chunk, key, value column]: state gradient at each chunk's end
   const float* dstates_t;
   int chunks;
+  // Where the q / k gradients of a token's head go: rows of 2 x 128 floats (q then k) in the
+  // partials when several value heads share a key head (the gather kernel sums them), or the
+  // final dq / dk rows themselves when every value head has its own key head.
+  float* dq_rows;
+  float* dk_rows;
+  size_t row_stride, head_stride;
 };
 
 __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la) {
@@ -491,7 +497,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
         rs = fmaf(scaled[j], kv[j], rs);
       }
       if (r0 + i < count)
-        *reinterpret_cast<float4*>(a.qk_partials + ((token0 + r0 + i) * a.value_heads + h) * 2 * kLD + kLD + c0) =
+        *reinterpret_cast<float4*>(la.dk_rows + (token0 + r0 + i) * la.row_stride + h * la.head_stride + c0) =
             make_float4(scaled[0], scaled[1], scaled[2], scaled[3]);
       rows[i] = rs;
       kt_total += rs;
@@ -536,7 +542,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
         rs = fmaf(scaled[j], qv[j] * f, rs);
       }
       if (t < count)
-        *reinterpret_cast<float4*>(a.qk_partials + ((token0 + t) * a.value_heads + h) * 2 * kLD + c0) =
+        *reinterpret_cast<float4*>(la.dq_rows + (token0 + t) * la.row_stride + h * la.head_stride + c0) =
             make_float4(scaled[0], scaled[1], scaled[2], scaled[3]);
       rows[i] = rs;
     }
@@ -683,13 +689,13 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int t = r0 + i;
-    const float* stash = a.qk_partials + ((token0 + min(t, count - 1)) * a.value_heads + h) * 2 * kLD + c0;
+    const size_t row = (token0 + min(t, count - 1)) * la.row_stride + h * la.head_stride + c0;
     const float bc = sm.beta[t] * sm.cdec[t];
     float x2[4], sq_[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sk_[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     to_array(lds4(sm.big[2] + t * kLP + c0), x2);
     if (t < count) {
-      to_array(*reinterpret_cast<const float4*>(stash), sq_);
-      to_array(*reinterpret_cast<const float4*>(stash + kLD), sk_);
+      to_array(*reinterpret_cast<const float4*>(la.dq_rows + row), sq_);
+      to_array(*reinterpret_cast<const float4*>(la.dk_rows + row), sk_);
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -742,11 +748,11 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       const float pq = (sm.dots[0][0][t] + sm.dots[1][0][t]) / (q_scale * q_scale);   // q^ = scale . unit vector
       const float pk = sm.dots[0][1][t] + sm.dots[1][1][t];
       const float ikt = sm.ik[t], iqt = sm.iq[t] * q_scale;
-      float* out = a.qk_partials + ((token0 + t) * a.value_heads + h) * 2 * kLD + c0;
-      *reinterpret_cast<float4*>(out) =
+      const size_t row = (token0 + t) * la.row_stride + h * la.head_stride + c0;
+      *reinterpret_cast<float4*>(la.dq_rows + row) =
           make_float4(iqt * (dq_acc[i][0] - qv[i][0] * pq), iqt * (dq_acc[i][1] - qv[i][1] * pq),
                       iqt * (dq_acc[i][2] - qv[i][2] * pq), iqt * (dq_acc[i][3] - qv[i][3] * pq));
-      *reinterpret_cast<float4*>(out + kLD) =
+      *reinterpret_cast<float4*>(la.dk_rows + row) =
           make_float4(ikt * (dk_acc[i][0] - kv[i][0] * pk), ikt * (dk_acc[i][1] - kv[i][1] * pk),
                       ikt * (dk_acc[i][2] - kv[i][2] * pk), ikt * (dk_acc[i][3] - kv[i][3] * pk));
     }
@@ -837,9 +843,11 @@ size_t gdn_bwd_chunked_workspace_bytes(int batch, int tokens, int value_heads) {
   return chunked_bwd_layout(batch, tokens, value_heads).total;
 }
 
-// Fills a.qk_partials / a.scalar_partials (one tile per head) and a.dv_out; the caller runs the
-// gather kernels over them.
-cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& a, void* workspace, uint32_t* status) {
+// Fills a.scalar_partials (one tile per head) and a.dv_out, and either a.qk_partials (several value
+// heads per key head: *qk_direct = false, the caller runs the q/k gather over them) or dq_out /
+// dk_out themselves.
+cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& a, float* dq_out, float* dk_out, size_t dqk_token,
+                            void* workspace, uint32_t* status, bool* qk_direct) {
   const ChunkedBwdLayout l = chunked_bwd_layout(a.batch, a.tokens, a.value_heads);
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~static_cast<uintptr_t>(1023));
   const int chunks = (a.tokens + kLC - 1) / kLC;
@@ -886,7 +894,15 @@ cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& a, void* workspace,
   transpose_128_kernel<<<matrices, 256, 0, stream>>>(dstates, dstates_t);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  LocalArgs la{a, states, states_t, dstates, dstates_t, chunks};
+  LocalArgs la{a, states, states_t, dstates, dstates_t, chunks, nullptr, nullptr, 0, 0};
+  *qk_direct = a.value_heads == a.key_heads && dqk_token % 4 == 0 && (reinterpret_cast<uintptr_t>(dq_out) & 15u) == 0 &&
+               (reinterpret_cast<uintptr_t>(dk_out) & 15u) == 0;
+  if (*qk_direct) {
+    la.dq_rows = dq_out; la.dk_rows = dk_out; la.row_stride = dqk_token; la.head_stride = kLD;
+  } else {
+    la.dq_rows = a.qk_partials; la.dk_rows = a.qk_partials + kLD;
+    la.row_stride = static_cast<size_t>(a.value_heads) * 2 * kLD; la.head_stride = 2 * kLD;
+  }
   e = cudaFuncSetAttribute(gdn_bwd_chunk_local, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(sizeof(LocalSmem)));
   if (e != cudaSuccess) return e;
