@@ -657,6 +657,8 @@ def _other_rest(peaks, only, time_ms, skip=()):
     result = {}
     if only == "gdn":
         return _gdn_workload(time_ms)
+    if only == "gdn_bptt":
+        return _gdn_bptt_only(time_ms)
     if only == "gdn_prefill":
         return _gdn_prefill_only(time_ms)
     if only == "gqa_bwd":
@@ -863,6 +865,21 @@ def _gdn_workload(time_ms, bptt_only=False):
     return result
 
 
+def _gdn_bptt_only(time_ms):
+    """The chunk-parallel delta-net BPTT alone on a quarter-size shape (batch 1, 8 heads, 4096 tokens:
+    512 chunk CTAs, under 1 GB on the device): the case the ncu captures of gdn_scan_bwd_sm100 and
+    gdn_bwd_chunk_local are taken on."""
+    import torch
+    bb, tt, hh, dd = 1, 4096, 8, 128
+    qn = torch.nn.functional.normalize(torch.randn(bb, tt, hh, dd, device="cuda"), dim=-1).bfloat16()
+    kn = torch.nn.functional.normalize(torch.randn(bb, tt, hh, dd, device="cuda"), dim=-1).bfloat16()
+    vn = torch.randn(bb, tt, hh, dd, device="cuda").bfloat16()
+    out = _gdn_bptt(time_ms, qn, kn, vn, bb, tt, hh, dd, None, None, None)
+    out["gated_delta_net"]["workload"] = "batch 1, 8 heads, d_k = d_v = 128, seq 4096"
+    del out["gated_delta_net"]["recurrence_bwd_fp32_tflops"]
+    return out
+
+
 def _gdn_forward_times(time_ms, prefill, qn, kn, vn, g, beta, st):
     import torch
 
@@ -938,7 +955,7 @@ def main():
     parser.add_argument("--impl", choices=["engine", "reference"], default="engine")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the secondary workloads and the CPU baseline (profiling runs)")
-    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gdn_prefill", "gqa_bwd", "linear", "dense"], default=None,
+    parser.add_argument("--profile-case", choices=["decode", "mha_train", "gdn", "gdn_prefill", "gdn_bptt", "gqa_bwd", "linear", "dense"], default=None,
                         help="run only one secondary workload at a capture-friendly size and exit")
     args = parser.parse_args()
     if args.profile_case:
