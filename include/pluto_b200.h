@@ -126,9 +126,10 @@ int pluto_attn_probs(pluto_stream_t stream, const void* qkv, const float* maxima
  *                reference saves for backward
  *   maxima, normalizers   optional fp32 [batch*q_heads*seq] as in pluto_attn_fwd (both or neither)
  *   workspace    optional (may be null): with pluto_gqa_prefill_fwd_workspace_bytes of 16-byte
- *                aligned device memory, shapes whose query tiles cannot fill the GPU (one or two
- *                heads of a long prompt) are cut along the keys into 2 or 4 parts per query-tile
- *                pair and combined by a second kernel
+ *                aligned device memory, shapes whose whole query tiles cannot load the SMs evenly
+ *                (a few heads of a long causal prompt, e.g. one GPU's share of a head-sharded
+ *                layer) have their longest query-tile pairs cut along the keys into 2 to 4 CTAs,
+ *                combined by a second kernel; the query returns 0 for shapes that are not cut
  * q_heads % kv_heads == 0, head_dim <= 256; head_dim 64/128 runs on tcgen05. */
 int pluto_gqa_prefill_fwd(pluto_stream_t stream, const void* q, const void* gate, const void* k,
                           const void* v, void* out, float* core, float* maxima,

@@ -18,6 +18,9 @@
 //               maximum grew by more than 2^8), tcgen05.st of P, final normalise and store.
 // QK^T of tile j+1 is issued before PV of tile j, so the tensor pipe works on the next score tile
 // while the softmax warps are busy with the current one.
+#include <cstring>
+#include <mutex>
+
 #include "common.cuh"
 #include "engine.h"
 
@@ -47,9 +50,10 @@ struct FwdParams {
   const __nv_bfloat16* gate;   // optional, indexed like q: token stride gate_token, head stride gate_head
   size_t gate_token, gate_head;
   int round_gate;              // apply bf16 rounding inside the gate product (reference behaviour)
-  // key/value split (pair kernel only): `splits` CTAs share one tile pair, each walks a contiguous
-  // part of the key blocks and writes an unnormalised partial; attn_fwd_merge combines them
-  int splits;
+  // key/value split (pair kernel only): the CTAs of one tile pair each walk a contiguous part of the
+  // key blocks and write an unnormalised partial; attn_fwd_merge combines them.  How many parts a
+  // pair has comes with the schedule (PairSchedule); split_pairs says whether any pair is split.
+  int split_pairs;
   float* part_o;               // [split][batch*seq tokens][heads][D] accumulator relative to part_m.x
   float4* part_m;              // [split][batch][heads][seq] = (max used * scale_log2, true max *
                                //  scale_log2, sum relative to max used, 0)
@@ -362,11 +366,25 @@ struct PairBarriers {
   uint32_t tmem_base;
 };
 
+// The pair kernel's work list, longest item first (CTAs are handed to SMs in blockIdx order, so this
+// is longest-processing-time-first scheduling): item i of every (sequence, head) is part
+// (meta & 15) of (meta >> 4) of tile pair `pair`.  A causal prompt's pairs differ in length by two
+// orders of magnitude; when a GPU holds few heads the longest pair alone exceeds an SM's fair share
+// of the whole problem, and only the pairs above that share are cut (2 to 4 parts), not all of them.
+constexpr int kMaxPairItems = 512;
+constexpr int kMaxPairs = 128;
+struct PairSchedule {
+  uint16_t pair[kMaxPairItems];
+  uint8_t meta[kMaxPairItems];
+  uint8_t parts_of[kMaxPairs];   // per pair, for the merge
+};
+
 template <int D>
 __global__ void __launch_bounds__(kThreadsPair, 1)
 attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
                     const __grid_constant__ CUtensorMap map_k,
-                    const __grid_constant__ CUtensorMap map_v, FwdParams p) {
+                    const __grid_constant__ CUtensorMap map_v, FwdParams p,
+                    const __grid_constant__ PairSchedule schedule) {
   constexpr int kSlabs = D / 64;
   constexpr int kTileBytes = kSlabs * kSlabBytes;
   constexpr uint32_t kTmemCols = 512;
@@ -385,16 +403,15 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
   // CTAs are handed to SMs in blockIdx.x-major order: (sequence, head) varies fastest and the pair
   // index slowest, so every head's longest pairs start first and the shortest ones fill the tail
   // (longest-processing-time-first over the whole grid, not per head).
-  // With key/value splits, blockIdx.y = slot * splits + part and the parts of the longest pairs
-  // still start first.
-  const int pair = (p.tile_end + 1) / 2 - 1 - blockIdx.y / p.splits;   // pairs below the grid's range are not run
-  const int part = blockIdx.y % p.splits;
+  // blockIdx.y indexes the schedule (pairs below the launch's range are not in it).
+  const int pair = schedule.pair[blockIdx.y];
+  const int part = schedule.meta[blockIdx.y] & 15, parts = schedule.meta[blockIdx.y] >> 4;
   const int head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
   const int q_tiles = (p.seq + kBM - 1) / kBM;
   const int tile_of[2] = {2 * pair, 2 * pair + 1};
   const int blocks_of[2] = {tile_of[0] + 1, tile_of[1] < q_tiles ? tile_of[1] + 1 : 0};
   // this CTA's key blocks [jb, je); tile x takes the ones below its own count n_of[x]
-  const int chunk = (max(blocks_of[0], blocks_of[1]) + p.splits - 1) / p.splits;
+  const int chunk = (max(blocks_of[0], blocks_of[1]) + parts - 1) / parts;
   const int jb = part * chunk;
   const int n_of[2] = {max(jb, min(blocks_of[0], jb + chunk)), max(jb, min(blocks_of[1], jb + chunk))};
   const int n_max = max(n_of[0], n_of[1]);
@@ -649,7 +666,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
     }
     const bool any = n_tiles > jb;             // this part holds key blocks of this tile
     if (ok && any) ok = mbar_wait(&bar->pv_done[x], (n_tiles - 1 - jb) & 1, p.status, 22);
-    if (ok && p.splits > 1 && blocks_of[x] > 0) {
+    if (parts > 1 && blocks_of[x] > 0) {   // (uniform over the warpgroup: the other branch holds a barrier)
+      if (ok) {
       // unnormalised partial of this part: accumulator and sums are relative to m_used
       if (any) tc_fence_after();
       const bool live = query < p.seq;
@@ -676,30 +694,37 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
         p.part_m[((static_cast<size_t>(part) * (gridDim.x / p.heads) + batch) * p.heads + head) * p.seq + query] =
             make_float4(any ? m_used * p.scale_log2 : -INFINITY, any ? m_true * p.scale_log2 : -INFINITY,
                         any ? l : 0.0f, 0.0f);
-    } else if (ok && any) {
-      tc_fence_after();
-      const float inv = 1.0f / l;
+      }
+    } else if (any) {
+      // The normalised rows leave through shared memory: each thread writes its row, as bf16, into
+      // this tile's query buffer (free: the tile's last Q K^T has completed) in the swizzled slab
+      // layout, then the warpgroup's 128 threads copy the tile out in 16-byte pieces, 16 threads
+      // per 256-byte row.  (Written straight from the row's thread, every store instruction of a
+      // warp touched 32 rows: 11 to 17 thousand cycles per tile against two thousand this way.)
+      uint8_t* stage = q_smem + x * kTileBytes;
       const bool live = query < p.seq;
       const size_t token = static_cast<size_t>(batch) * p.seq + query;
-      __nv_bfloat16* out = p.out + token * p.out_token + head * p.out_head;
-      float* core = p.core ? p.core + token * p.out_token + head * p.out_head : nullptr;
-      const __nv_bfloat16* gate =
-          p.gate ? p.gate + token * p.gate_token + head * p.gate_head : nullptr;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(o_addr + c * 32, o);
-        tmem_wait_ld();
-        if (live) {
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        float* core = p.core ? p.core + token * p.out_token + head * p.out_head : nullptr;
+        const __nv_bfloat16* gate =
+            p.gate ? p.gate + token * p.gate_token + head * p.gate_head : nullptr;
+        // (not unrolled: this code runs once per CTA, so every instruction of it is fetched cold)
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_wait_ld();
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             float a = __uint_as_float(o[i]) * inv, b = __uint_as_float(o[i + 1]) * inv;
-            if (core) {
+            if (core && live) {
               core[c * 32 + i] = a;
               core[c * 32 + i + 1] = b;
             }
-            if (gate) {
+            if (gate && live) {
               const float g0 = __bfloat162float(gate[c * 32 + i]);
               const float g1 = __bfloat162float(gate[c * 32 + i + 1]);
               float s0 = 1.0f / (1.0f + expf(-g0)), s1 = 1.0f / (1.0f + expf(-g1));
@@ -714,12 +739,31 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
             }
             w[i / 2] = pack_bf16(a, b);
           }
-          uint4* dst = reinterpret_cast<uint4*>(out + c * 32);
+          uint8_t* slab_row = stage + (c / 2) * kSlabBytes + row * 128;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(slab_row + ((((c & 1) * 4 + i) ^ (row & 7)) * 16)) =
+                make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
         }
       }
-      if (live && p.maxima) {
+      // all 128 threads of this tile's warpgroup, whatever their waits returned (`any` is uniform)
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");
+      if (ok) {
+        constexpr int kPieces = D / 8;   // 16-byte pieces per row
+        const int t128 = threadIdx.x - (4 + 4 * x) * 32;
+#pragma unroll 4
+        for (int e = t128; e < kBM * kPieces; e += 128) {
+          const int r = e / kPieces, piece = e % kPieces;
+          const int q_row = q_tile * kBM + r;
+          if (q_row < p.seq) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + (piece / 8) * kSlabBytes + r * 128 +
+                                                            (((piece & 7) ^ (r & 7)) * 16));
+            *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(batch) * p.seq + q_row) * p.out_token +
+                                      head * p.out_head + piece * 8) = v;
+          }
+        }
+      }
+      if (ok && live && p.maxima) {
         const size_t stat = (static_cast<size_t>(batch) * p.heads + head) * p.seq + query;
         p.maxima[stat] = m_true * p.scale;
         p.normalizers[stat] = l * fast_exp2((m_used - m_true) * p.scale_log2);
@@ -742,32 +786,57 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
 // to:  O = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M); then the same epilogue as the kernel
 // (fp32 core, gate with the reference's rounding sequence, bf16 output, statistics).
 template <int D>
-__global__ void __launch_bounds__(256) attn_fwd_merge(FwdParams p, int batch) {
+__global__ void __launch_bounds__(256) attn_fwd_merge(FwdParams p, int batch, int first_token,
+                                                      const __grid_constant__ PairSchedule schedule) {
+  // rows (token, head) of the tokens from first_token on (the first token of the first pair that
+  // was cut: the plan cuts the long pairs, i.e. the late ones)
   constexpr int kPer = D / 32;
+  const int span = p.seq - first_token;
   const long long row = static_cast<long long>(blockIdx.x) * 8 + threadIdx.x / 32;
-  const long long rows = static_cast<long long>(batch) * p.seq * p.heads;
+  const long long rows = static_cast<long long>(batch) * span * p.heads;
   if (row >= rows) return;
   const int lane = threadIdx.x % 32;
-  const size_t token = static_cast<size_t>(row / p.heads);
   const int head = static_cast<int>(row % p.heads);
-  const int b = static_cast<int>(token / p.seq), s = static_cast<int>(token % p.seq);
+  const long long local = row / p.heads;
+  const int b = static_cast<int>(local / span), s = first_token + static_cast<int>(local % span);
+  const size_t token = static_cast<size_t>(b) * p.seq + s;
   const size_t tokens = static_cast<size_t>(batch) * p.seq;
-  float m_used = -INFINITY, m_true = -INFINITY;
+  const int parts = schedule.parts_of[s / (2 * kBM)];
+  if (parts <= 1) return;   // the pair's only CTA wrote the final rows itself
+  // every load of the row is requested before any is used: one memory round trip
   float4 rec[4];
-  for (int part = 0; part < p.splits; ++part) {
-    rec[part] = p.part_m[((static_cast<size_t>(part) * batch + b) * p.heads + head) * p.seq + s];
+  float4 val[4];
+  static_assert(kPer == 4 || kPer == 2, "a lane owns two or four channels");
+#pragma unroll
+  for (int part = 0; part < 4; ++part) {
+    if (part < parts) {
+      rec[part] = p.part_m[((static_cast<size_t>(part) * batch + b) * p.heads + head) * p.seq + s];
+      const float* src = p.part_o + ((static_cast<size_t>(part) * tokens + token) * p.heads + head) * D + lane * kPer;
+      if (kPer == 4) val[part] = *reinterpret_cast<const float4*>(src);
+      else {
+        const float2 v2 = *reinterpret_cast<const float2*>(src);
+        val[part] = make_float4(v2.x, v2.y, 0.0f, 0.0f);
+      }
+    } else {
+      rec[part] = make_float4(-INFINITY, -INFINITY, 0.0f, 0.0f);
+      val[part] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+  }
+  float m_used = -INFINITY, m_true = -INFINITY;
+#pragma unroll
+  for (int part = 0; part < 4; ++part) {
     m_used = fmaxf(m_used, rec[part].x);
     m_true = fmaxf(m_true, rec[part].y);
   }
-  float acc[kPer], l = 0.0f;
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, l = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kPer; ++i) acc[i] = 0.0f;
-  for (int part = 0; part < p.splits; ++part) {
-    const float w = fast_exp2(rec[part].x - m_used);      // 0 for a part without key blocks
+  for (int part = 0; part < 4; ++part) {
+    const float w = part < parts ? fast_exp2(rec[part].x - m_used) : 0.0f;      // 0 for a part without key blocks
     l = fmaf(rec[part].z, w, l);
-    const float* src = p.part_o + ((static_cast<size_t>(part) * tokens + token) * p.heads + head) * D + lane * kPer;
-#pragma unroll
-    for (int i = 0; i < kPer; ++i) acc[i] = fmaf(src[i], w, acc[i]);
+    acc[0] = fmaf(val[part].x, w, acc[0]);
+    acc[1] = fmaf(val[part].y, w, acc[1]);
+    acc[2] = fmaf(val[part].z, w, acc[2]);
+    acc[3] = fmaf(val[part].w, w, acc[3]);
   }
   const float inv = 1.0f / l;
   __nv_bfloat16* out = p.out + token * p.out_token + head * p.out_head + lane * kPer;
@@ -831,6 +900,170 @@ bool make_token_map(CUtensorMap* map, const void* base, int cols, int seq, int b
          CUDA_SUCCESS;
 }
 
+// How a launch over query tiles [tile_begin, tile_begin + q_tiles) of (batch x heads) causal
+// sequences is cut into CTAs.
+//   pairs: two query tiles per CTA in ping-pong (each tile runs faster, but the units are coarser);
+//   split: some or all pairs are cut along their keys into parts_of[pair] CTAs (needs the workspace);
+//   pairs_without_split: what to do when split is wanted but no workspace was given.
+// Work is counted in key blocks: pair p (tiles 2p, 2p + 1) has (2p + 1) + (2p + 2) of them.
+//   * Few units (no more tiles than SMs): every pair in 2 or 4 parts.  Measured at S = 8192,
+//     D = 128: 1 head 74 -> 50 us, 2 heads 76 -> 62 us.
+//   * Otherwise a pair is cut into ceil(work / (f . fair share)) parts, the fair share being the
+//     whole problem's work over the SMs and f the best of a few values in a simulation of the
+//     launch (below); no cut at all is one of the candidates.  Measured at S = 8192, D = 128
+//     (without -> with cuts): 3 heads 111 -> 79 us, 4 heads 113 -> 87, 5 heads 102 -> 99,
+//     6 heads 123 -> 118, 8 heads 150 -> 128, 10 heads 152 -> 150; from 12 heads on nothing is cut.
+//   * Without a workspace nothing is cut: pairs where there are at least two per SM (or exactly
+//     one wave of them), the single-tile kernel otherwise.
+static int fill_pair_schedule(PairSchedule* schedule, int tile_begin, int q_tiles, const uint8_t* parts_of,
+                              int* work_of);
+struct AttnFwdPlan {
+  bool pairs, split, pairs_without_split;
+  uint8_t parts_of[kMaxPairs];
+};
+static AttnFwdPlan attn_fwd_plan_uncached(int batch, int seq, int heads, int tile_begin, int q_tiles, int sms) {
+  AttnFwdPlan plan{};
+  const int all_tiles = (seq + kBM - 1) / kBM;
+  const bool whole = tile_begin == 0 && q_tiles == all_tiles;
+  // a partial range runs as pairs only when it starts on a pair and ends on one (or at the end)
+  const bool pairable = tile_begin % 2 == 0 && (q_tiles % 2 == 0 || tile_begin + q_tiles == all_tiles);
+  const long long units = static_cast<long long>(heads) * batch;
+  const int n_pairs = (q_tiles + 1) / 2;
+  const long long pair_units = n_pairs * units;
+  for (int i = 0; i < kMaxPairs; ++i) plan.parts_of[i] = 1;
+  // Pairs also win when they fit the SMs in one wave and the single tiles would not (measured at
+  // B 16, H 6, S 256, D 64: 16.3 against 20.5 us).
+  const bool one_wave_of_pairs = pair_units <= sms && static_cast<long long>(q_tiles) * units > sms;
+  plan.pairs_without_split = q_tiles >= 2 && pairable && (pair_units >= 2LL * sms || one_wave_of_pairs);
+  plan.pairs = q_tiles >= 2 && pairable && n_pairs <= kMaxPairItems;
+  plan.pairs_without_split = plan.pairs_without_split && n_pairs <= kMaxPairItems;
+  if (!plan.pairs || !whole || n_pairs > kMaxPairs || q_tiles < 8) {
+    plan.pairs = plan.pairs_without_split;
+    return plan;
+  }
+  if (static_cast<long long>(q_tiles) * units <= sms) {
+    const int parts = pair_units * 2 >= 2LL * sms ? 2 : 4;
+    for (int i = 0; i < n_pairs; ++i) plan.parts_of[i] = static_cast<uint8_t>(parts);
+    plan.split = true;
+    return plan;
+  }
+  long long total = 0;
+  for (int i = 0; i < n_pairs; ++i) total += (2 * i + 1) + (2 * i + 1 < q_tiles ? 2 * i + 2 : 0);
+  const double fair = static_cast<double>(total) * units / sms;
+  // A pair is cut into ceil(work / (f . fair share)) parts; f is chosen by simulating the launch
+  // (CTAs in schedule order onto the earliest free SM) with a CTA costing its key blocks plus a
+  // fixed 11 blocks' worth of set-up and epilogue (13 when it writes partials), which reproduces
+  // the measured times of 3 to 8 heads at S = 8192 within a few per cent.  Cutting at the fair
+  // share itself leaves a second wave of half-length CTAs behind a first wave of full-length ones;
+  // a somewhat finer cut fills the tail better, a much finer one pays too many fixed costs.
+  // f = 0 stands for no cut at all; a plan with cuts also pays for the merge kernel (about 11 blocks).
+  static const double kCuts[] = {0.0, 1.0, 0.85, 0.7, 0.6, 0.5};
+  double best_time = 0.0;
+  bool first = true;
+  for (double f : kCuts) {
+    uint8_t parts_of[kMaxPairs];
+    bool any = false;
+    for (int i = 0; i < n_pairs; ++i) {
+      const int work = (2 * i + 1) + (2 * i + 1 < q_tiles ? 2 * i + 2 : 0);
+      const int parts = f > 0.0 ? static_cast<int>((work + f * fair - 1e-9) / (f * fair)) : 1;
+      parts_of[i] = static_cast<uint8_t>(parts < 1 ? 1 : (parts > 4 ? 4 : parts));
+      any = any || parts_of[i] > 1;
+    }
+    if (!any && f > 0.0) continue;
+    PairSchedule schedule;
+    int work_of[kMaxPairItems];
+    const int items = fill_pair_schedule(&schedule, tile_begin, q_tiles, parts_of, work_of);
+    // earliest-free-SM simulation, CTAs in launch order: item-major, (sequence, head) fastest
+    double free_at[256];
+    const int machines = sms < 256 ? sms : 256;
+    for (int m = 0; m < machines; ++m) free_at[m] = 0.0;
+    auto place = [&](double cost) {
+      for (long long u = 0; u < units; ++u) {
+        int at = 0;
+        for (int m = 1; m < machines; ++m)
+          if (free_at[m] < free_at[at]) at = m;
+        free_at[at] += cost;
+      }
+    };
+    if (f == 0.0 && !plan.pairs_without_split) {
+      // what runs without cuts here is the single-tile kernel: a key block costs 1.4 times as much
+      // without the second tile to alternate with (5 heads at S = 8192: 102 us)
+      for (int t = q_tiles - 1; t >= 0; --t) place(1.4 * (t + 1) + 11.0);
+    } else {
+      for (int i = 0; i < items; ++i) place(work_of[i] + ((schedule.meta[i] >> 4) > 1 ? 13.0 : 11.0));
+    }
+    double time = any ? 11.0 : 0.0;
+    for (int m = 0; m < machines; ++m) time = free_at[m] > time ? free_at[m] + (any ? 11.0 : 0.0) : time;
+    if (first || time < best_time) {
+      first = false;
+      best_time = time;
+      plan.split = any;
+      for (int i = 0; i < kMaxPairs; ++i) plan.parts_of[i] = i < n_pairs ? parts_of[i] : 1;
+    }
+  }
+  if (!plan.split) plan.pairs = plan.pairs_without_split;
+  return plan;
+}
+
+// The plan of a shape is computed once (the simulation above costs tens of microseconds).
+static AttnFwdPlan attn_fwd_plan(int batch, int seq, int heads, int tile_begin, int q_tiles, int sms) {
+  struct Entry { int key[6]; AttnFwdPlan plan; };
+  static std::mutex mutex;
+  static Entry cache[16];
+  static int used = 0, next = 0;
+  const int key[6] = {batch, seq, heads, tile_begin, q_tiles, sms};
+  std::lock_guard<std::mutex> lock(mutex);
+  for (int i = 0; i < used; ++i)
+    if (memcmp(cache[i].key, key, sizeof(key)) == 0) return cache[i].plan;
+  Entry& e = cache[next];
+  memcpy(e.key, key, sizeof(key));
+  e.plan = attn_fwd_plan_uncached(batch, seq, heads, tile_begin, q_tiles, sms);
+  next = (next + 1) % 16;
+  used = used < 16 ? used + 1 : 16;
+  return e.plan;
+}
+
+// Items of pairs [tile_begin / 2, ...) sorted by length, longest first; returns their number.
+static int fill_pair_schedule(PairSchedule* schedule, int tile_begin, int q_tiles, const uint8_t* parts_of,
+                              int* work_of) {
+  const int first = tile_begin / 2, last = (tile_begin + q_tiles + 1) / 2;   // pairs [first, last)
+  struct Item { int work, pair, part, parts; };
+  Item items[kMaxPairItems];
+  int n = 0;
+  for (int pair = last - 1; pair >= first && n < kMaxPairItems; --pair) {
+    const int parts = parts_of != nullptr && pair < kMaxPairs ? parts_of[pair] : 1;
+    const int blocks = 2 * pair + 2;
+    const int chunk = (blocks + parts - 1) / parts;
+    for (int part = 0; part < parts && n < kMaxPairItems; ++part) {
+      const int lo = part * chunk, hi = lo + chunk < blocks ? lo + chunk : blocks;
+      // key blocks of the two tiles inside [lo, hi): tile 2p has 2p + 1 of them, tile 2p + 1 has 2p + 2
+      const int a0 = (hi < blocks - 1 ? hi : blocks - 1) - lo, a1 = hi - lo;
+      items[n++] = Item{(a0 > 0 ? a0 : 0) + (a1 > 0 ? a1 : 0), pair, part, parts};
+    }
+  }
+  for (int i = 1; i < n; ++i) {   // insertion sort, stable, descending by work
+    const Item x = items[i];
+    int j = i - 1;
+    for (; j >= 0 && items[j].work < x.work; --j) items[j + 1] = items[j];
+    items[j + 1] = x;
+  }
+  for (int i = 0; i < n; ++i) {
+    schedule->pair[i] = static_cast<uint16_t>(items[i].pair);
+    schedule->meta[i] = static_cast<uint8_t>(items[i].part | (items[i].parts << 4));
+    if (work_of != nullptr) work_of[i] = items[i].work;
+  }
+  for (int i = 0; i < kMaxPairs; ++i) schedule->parts_of[i] = parts_of != nullptr ? parts_of[i] : 1;
+  return n;
+}
+
+// Bytes of scratch attn_fwd_tc can use for this shape, 0 when it would not cut any pair.
+size_t attn_fwd_tc_split_workspace_bytes(int batch, int seq, int heads, int head_dim) {
+  int sms = 148, device = 0;
+  if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const AttnFwdPlan plan = attn_fwd_plan(batch, seq, heads, 0, (seq + kBM - 1) / kBM, sms);
+  return plan.split ? attn_fwd_tc_workspace_bytes(batch, seq, heads, head_dim) : 0;
+}
+
 // Partials of the key/value-split mode: a float4 record and D floats per (part, token, head), 4 parts.
 size_t attn_fwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim) {
   const size_t units = static_cast<size_t>(batch) * seq * heads;
@@ -874,7 +1107,6 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
   const int q_tiles = a.tile_count > 0 ? a.tile_count : all_tiles;
   if (tile_begin < 0 || tile_begin + q_tiles > all_tiles) return cudaErrorInvalidValue;
   p.tile_end = tile_begin + q_tiles;
-  const bool whole = q_tiles == all_tiles;
   const size_t tile = static_cast<size_t>(a.head_dim / 64) * kSlabBytes;
   cudaError_t e;
   if (a.head_dim != 128 && a.head_dim != 64) return cudaErrorInvalidValue;
@@ -888,43 +1120,36 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
     if (cudaGetDevice(&device) == cudaSuccess)
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   }
-  // a partial range runs as pairs only when it starts on a pair and ends on one (or at the end)
-  const bool pairable = tile_begin % 2 == 0 && (q_tiles % 2 == 0 || p.tile_end == all_tiles);
-  const long long pair_units = static_cast<long long>((q_tiles + 1) / 2) * a.heads * a.batch;
-  // With a workspace, a shape that cannot even fill the SMs with single tiles (one or two heads of
-  // a long prompt) is made finer by cutting every pair's key range into parts, combined by
-  // attn_fwd_merge.  Measured at S = 8192, D = 128: 1 head 74 -> 50 us, 2 heads 76 -> 62 us, but
-  // 3 heads 77 -> 95 us and 5 heads 103 -> 114 us (the per-CTA prologue/epilogue outweighs the
-  // better balance), hence the threshold.
-  int splits = 1;
-  if (whole && a.workspace != nullptr && q_tiles >= 8 && static_cast<long long>(q_tiles) * a.heads * a.batch <= sms)
-    splits = pair_units * 2 >= 2LL * sms ? 2 : 4;
-  p.splits = splits;
+  const AttnFwdPlan plan = attn_fwd_plan(a.batch, a.seq, a.heads, tile_begin, q_tiles, sms);
+  const bool split = plan.split && a.workspace != nullptr;
+  p.split_pairs = split ? 1 : 0;
   p.part_o = nullptr;
   p.part_m = nullptr;
-  if (splits > 1) {
+  if (split) {
     const size_t tokens = static_cast<size_t>(a.batch) * a.seq;
     p.part_m = static_cast<float4*>(a.workspace);
     p.part_o = reinterpret_cast<float*>(p.part_m + 4 * tokens * a.heads);
   }
-  // Pairs also win when they fit the SMs in one wave and the single tiles would not (measured at
-  // B 16, H 6, S 256, D 64: 16.3 against 20.5 us).
-  const bool one_wave_of_pairs = pair_units <= sms && static_cast<long long>(q_tiles) * a.heads * a.batch > sms;
-  if (q_tiles >= 2 && pairable && (pair_units >= 2LL * sms || splits > 1 || one_wave_of_pairs)) {
+  if (plan.pairs && (split || !plan.split || plan.pairs_without_split)) {
     // two query tiles per CTA in ping-pong
-    const dim3 grid(a.heads * a.batch, ((q_tiles + 1) / 2) * splits);
+    PairSchedule schedule;
+    const int items = fill_pair_schedule(&schedule, tile_begin, q_tiles, split ? plan.parts_of : nullptr, nullptr);
+    const dim3 grid(a.heads * a.batch, items);
     const size_t smem = 1024 + tile * (2 + 2 * kStages) + sizeof(PairBarriers);
     auto kernel = a.head_dim == 128 ? attn_fwd_sm100_pair<128> : attn_fwd_sm100_pair<64>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    kernel<<<grid, kThreadsPair, smem, stream>>>(map_q, map_k, map_v, p);
-    if (splits > 1) {
+    kernel<<<grid, kThreadsPair, smem, stream>>>(map_q, map_k, map_v, p, schedule);
+    if (split) {
       e = cudaGetLastError();
       if (e != cudaSuccess) return e;
-      const long long rows = static_cast<long long>(a.batch) * a.seq * a.heads;
+      int first_pair = 0;
+      while (first_pair < kMaxPairs && plan.parts_of[first_pair] <= 1) ++first_pair;
+      const int first_token = first_pair * 2 * kBM;
+      const long long rows = static_cast<long long>(a.batch) * (a.seq - first_token) * a.heads;
       const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
-      if (a.head_dim == 128) attn_fwd_merge<128><<<blocks, 256, 0, stream>>>(p, a.batch);
-      else attn_fwd_merge<64><<<blocks, 256, 0, stream>>>(p, a.batch);
+      if (a.head_dim == 128) attn_fwd_merge<128><<<blocks, 256, 0, stream>>>(p, a.batch, first_token, schedule);
+      else attn_fwd_merge<64><<<blocks, 256, 0, stream>>>(p, a.batch, first_token, schedule);
     }
   } else {
     const dim3 grid(a.heads * a.batch, q_tiles);

@@ -279,7 +279,7 @@ int pluto_gqa_prefill_bwd(pluto_stream_t stream, const void* q, const void* k, c
 
 size_t pluto_gqa_prefill_fwd_workspace_bytes(int batch, int seq, int q_heads, int head_dim) {
   if (batch <= 0 || seq <= 0 || q_heads <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
-  return pluto::attn_fwd_tc_workspace_bytes(batch, seq, q_heads, head_dim);
+  return pluto::attn_fwd_tc_split_workspace_bytes(batch, seq, q_heads, head_dim);
 }
 
 size_t pluto_gqa_prefill_bwd_workspace_bytes(int batch, int seq, int q_heads, int head_dim, int dtype) {

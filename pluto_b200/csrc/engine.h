@@ -127,6 +127,8 @@ struct AttnFwdArgs {
 };
 cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& args);
 size_t attn_fwd_tc_workspace_bytes(int batch, int seq, int heads, int head_dim);
+// ... or 0 when the launch plan for this shape cuts no tile pair (the scratch would not be used)
+size_t attn_fwd_tc_split_workspace_bytes(int batch, int seq, int heads, int head_dim);
 bool make_token_map(CUtensorMap* map, const void* base, int cols, int seq, int batch,
                     size_t token_stride, int box_rows);
 

@@ -279,12 +279,14 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         if gate.stride(3) != 1 or gate.stride(0) != T * gate.stride(1):
             raise _invalid("attention gate must have a contiguous head dimension and batch")
         gts, ghs = gate.stride(1), gate.stride(2)
-    # one or two heads of a long prompt cannot fill the GPU with query tiles: give the kernel
-    # scratch for its key/value split; pass `workspace` to reuse one across calls
+    # a few heads of a long prompt cannot load the SMs evenly with whole query tiles: the kernel
+    # then cuts the longest tile pairs along their keys and needs scratch for the partial results
+    # (the query returns 0 for shapes it would not cut); pass `workspace` to reuse one across calls
     L = _capi.lib()
     ws_ptr, ws_bytes = None, 0
-    if D in (64, 128) and T >= 1024 and B * Hq * ((T + 127) // 128) <= 148:
+    if D in (64, 128):
         ws_bytes = L.pluto_gqa_prefill_fwd_workspace_bytes(B, T, Hq, D)
+    if ws_bytes > 0:
         if workspace is None or workspace.numel() < ws_bytes + 16:
             workspace = torch.empty((ws_bytes + 16,), dtype=torch.uint8, device=q.device)
         ws_ptr = (workspace.data_ptr() + 15) // 16 * 16
