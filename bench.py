@@ -400,8 +400,22 @@ def gdn_leg(ranks, peaks, batch=2, tokens=16384, heads=16, dim=128):
         "prefill_tflops_per_gpu": tflops,
         "prefill_roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                              "frac": tflops / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
-                             "note": "dense chunked count (11.53 MFLOP per chunk and head); the kernel is bound "
-                                     "by the chain of dependent chunk steps, not by the tensor pipe"},
+                             "note": "dense chunked count (11.53 MFLOP per chunk and head); the kernels are bound "
+                                     "by latency inside the chunk-parallel prepare CTA and by the chain of "
+                                     "dependent chunk steps, not by the tensor pipe"},
+        # the memory view: q, k, v in and the output out are the algorithmic bytes; the chunk records
+        # (91136 B per chunk and head, written by the prepare kernel and read by the scan) are traffic
+        # of this design
+        "prefill_hbm": {"algorithmic_bytes_per_gpu": 4 * batch * tokens * local * dim * 2,
+                        "algorithmic_gbs": 4 * batch * tokens * local * dim * 2 / (prefill_ms * 1e-3) / 1e9,
+                        "with_records_bytes_per_gpu": (4 * batch * tokens * local * dim * 2 +
+                                                       2 * batch * local * ((tokens + 63) // 64) * 91136),
+                        "with_records_gbs": (4 * batch * tokens * local * dim * 2 +
+                                             2 * batch * local * ((tokens + 63) // 64) * 91136) /
+                                            (prefill_ms * 1e-3) / 1e9,
+                        "frac_of_measured_hbm": (4 * batch * tokens * local * dim * 2 +
+                                                 2 * batch * local * ((tokens + 63) // 64) * 91136) /
+                                                (prefill_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},
         "step_in_cuda_graph_us": graph_ms * 1e3 / 256,
         "step_state_gbs_per_gpu": state_bytes / (graph_ms * 1e-3 / 256) / 1e9,
         "fused_256_step_launch_us": fused_ms * 1e3, "fused_us_per_token": fused_ms * 1e3 / 256,

@@ -223,7 +223,9 @@ int pluto_qk_prepare_bwd(pluto_stream_t stream, const void* x, size_t x_token_st
  * with page(b, t) = block_table ? block_table[b * max_blocks + t / page_size] : b.
  * One contiguous [capacity, kv_heads, head_dim] region per sequence is block_table = NULL,
  * page_size = capacity, page_stride = capacity * kv_heads * head_dim,
- * token_stride = kv_heads * head_dim.  The position counter stays with the caller. */
+ * token_stride = kv_heads * head_dim.  The position counter stays with the caller.
+ * A shard of KV heads [h0, h0 + n) of a wider cache is addressed in place: k_base / v_base advanced
+ * by h0 * head_dim elements, kv_heads = n in the call, token_stride left at the full row. */
 typedef struct pluto_kv_cache {
   void* k_base;
   void* v_base;

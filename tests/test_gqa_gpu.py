@@ -275,10 +275,13 @@ def test_host_memory_prefill_by_token_chunks_matches_device_prefill():
     assert _capi.kernel_status() == 0
 
 
-@pytest.mark.parametrize("shape", [(2048, 4, 2, 128), (3000, 5, 1, 128), (2304, 6, 6, 64), (9000, 2, 1, 128)])
+@pytest.mark.parametrize("shape", [(2048, 4, 2, 128), (3000, 5, 1, 128), (2304, 6, 6, 64), (9000, 2, 1, 128),
+                                   (4096, 6, 2, 128), (5000, 4, 4, 64)])
 def test_key_value_split_prefill_matches_oracle_and_unsplit_kernel(shape):
-    """Few (sequence, head) units for a long prompt: with a workspace every query-tile pair is cut
-    along the keys into 2 or 4 parts and merged.  Checked against the CPU oracle on sampled rows
+    """Few (sequence, head) units for a long prompt: with a workspace query-tile pairs are cut along
+    the keys into 2 to 4 parts and merged -- every pair when there are no more tiles than SMs, only
+    the pairs above the per-SM fair share otherwise (the last two shapes: a schedule that mixes cut
+    and whole pairs).  Checked against the CPU oracle on sampled rows
     (first rows, rows around tile and part boundaries, last rows) and against the same call without
     a workspace; gate, fp32 core and statistics included."""
     import torch
@@ -314,3 +317,23 @@ def test_key_value_split_prefill_matches_oracle_and_unsplit_kernel(shape):
         ref = oracle.from_bf16_bits(want["out"])[rows[0]:rows[1]]
         assert np.abs(got - ref).max() <= 2e-2, rows
         assert np.abs(split["core"].cpu().numpy()[0, rows[0]:rows[1]] - want["core"][rows[0]:rows[1]]).max() <= 8e-3
+
+
+def test_decode_over_a_shard_of_kv_heads_in_place():
+    """A head shard of a wider cache needs no copy: advance k_base / v_base to the shard's first KV
+    head, pass the shard's head count and leave token_stride at the full row.  KV heads 2..3 of an
+    8-head bf16 cache (TMA path: lengths and capacity multiples of 16) and of an fp32 cache (plain
+    loads) give bit for bit what a materialised copy of the shard gives."""
+    batch, hkv, group, d, cap = 3, 8, 5, 128, 1024
+    gen = torch.Generator(device="cuda").manual_seed(41)
+    lens = torch.tensor([1024, 528, 16], dtype=torch.int32, device="cuda")
+    for dtype in (torch.bfloat16, torch.float32):
+        k_pool = (torch.randn(batch, cap, hkv, d, device="cuda", generator=gen) * 0.5).to(dtype)
+        v_pool = (torch.randn(batch, cap, hkv, d, device="cuda", generator=gen) * 0.5).to(dtype)
+        q = (torch.randn(batch, 2 * group, d, device="cuda", generator=gen) * 0.5).bfloat16()
+        in_place = gqa_decode(q, k_pool[:, :, 2:4], v_pool[:, :, 2:4], lens, cap)
+        copied = gqa_decode(q, k_pool[:, :, 2:4].contiguous(), v_pool[:, :, 2:4].contiguous(), lens, cap)
+        torch.cuda.synchronize()
+        assert _capi.kernel_status() == 0
+        assert torch.equal(in_place, copied), dtype
+        assert torch.isfinite(in_place.float()).all()
