@@ -27,10 +27,12 @@
 #include "engine.h"
 #include "gdn_records.cuh"
 
+#include <mutex>
+
 namespace pluto {
 // gdn_chunked.cu / gdn_scan_sm100.cu
 cudaError_t gdn_chunked_with_states(cudaStream_t stream, const GdnArgs& a, void* records, float* state_dump,
-                                    uint32_t* status);
+                                    uint32_t* status, cudaEvent_t after_prepare);
 cudaError_t gdn_scan_bwd_launch(cudaStream_t stream, const void* dcore_bf16, const void* records, int batch,
                                 int tokens, int value_heads, int chunks, float* dstate_dump, uint32_t* status);
 namespace {
@@ -806,6 +808,30 @@ __global__ void __launch_bounds__(256) transpose_128_kernel(const float* __restr
   }
 }
 
+// A second stream per device: the reverse scan needs the forward's records but not its states, so
+// it runs beside the forward scan (both fill only sequences x heads SMs), with the bf16 copy of the
+// output gradient made there too; the caller's stream joins before the transposes.
+struct BwdLanes {
+  cudaStream_t aux = nullptr;
+  cudaEvent_t forked = nullptr, prepared = nullptr, aux_done = nullptr;
+  bool ok = false;
+  std::mutex enqueue;
+};
+BwdLanes g_bwd_lanes[64];
+std::once_flag g_bwd_once[64];
+BwdLanes* bwd_lanes_for_current_device() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+  std::call_once(g_bwd_once[device], [device] {
+    BwdLanes& l = g_bwd_lanes[device];
+    l.ok = cudaStreamCreateWithFlags(&l.aux, cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&l.forked, cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&l.prepared, cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&l.aux_done, cudaEventDisableTiming) == cudaSuccess;
+  });
+  return g_bwd_lanes[device].ok ? &g_bwd_lanes[device] : nullptr;
+}
+
 size_t align_up(size_t n) { return (n + 1023) / 1024 * 1024; }
 
 }  // namespace
@@ -862,13 +888,19 @@ cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& a, float* dq_out, f
   a.qk_partials = reinterpret_cast<float*>(base + l.qk_partials);
   a.scalar_partials = reinterpret_cast<float*>(base + l.scalar_partials);
 
+  BwdLanes* lanes = bwd_lanes_for_current_device();
+  if (lanes == nullptr) return cudaErrorInitializationError;
+  std::lock_guard<std::mutex> lock(lanes->enqueue);
   cudaError_t e = gdn_gates(stream, a.a_in, a.b_in, a.a_log, a.dt_bias, a.ab_is_bf16,
                             static_cast<long long>(a.batch) * a.tokens, a.value_heads, a.round, g, beta);
   if (e != cudaSuccess) return e;
-  const size_t count = rows * kLD;
-  cast_to_bf16_kernel<<<static_cast<unsigned>((count / 4 + 255) / 256 + 1), 256, 0, stream>>>(a.dcore, dcore16, count);
-  e = cudaGetLastError();
+  // second stream: the output gradient as bf16 now, the reverse scan once the records are there
+  e = cudaEventRecord(lanes->forked, stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(lanes->aux, lanes->forked, 0);
   if (e != cudaSuccess) return e;
+  const size_t count = rows * kLD;
+  cast_to_bf16_kernel<<<static_cast<unsigned>((count / 4 + 255) / 256 + 1), 256, 0, lanes->aux>>>(a.dcore, dcore16, count);
+  e = cudaGetLastError();
   // forward: records and the state at every chunk's start (from a zero state, as the layer's
   // sequence mode runs); its outputs are not needed
   GdnArgs f{};
@@ -880,17 +912,25 @@ cudaError_t gdn_bwd_chunked(cudaStream_t stream, GdnBwdArgs& a, float* dq_out, f
   f.batch = a.batch; f.tokens = a.tokens; f.key_heads = a.key_heads; f.value_heads = a.value_heads;
   f.key_dim = kLD; f.value_dim = kLD;
   f.normalize_qk = 1; f.q_scale = 1.0f; f.round = a.round;
-  // the scan reads its initial state from and leaves its final state in f.state: the start of the
-  // state-gradient area is free until the reverse scan runs
-  f.state = dstates;
-  e = cudaMemsetAsync(dstates, 0, static_cast<size_t>(a.batch) * a.value_heads * kLD * kLD * sizeof(float), stream);
-  if (e != cudaSuccess) return e;
-  e = gdn_chunked_with_states(stream, f, base + l.records, states, status);
-  if (e != cudaSuccess) return e;
-  e = gdn_scan_bwd_launch(stream, dcore16, base + l.records, a.batch, a.tokens, a.value_heads, chunks, dstates, status);
-  if (e != cudaSuccess) return e;
+  // the scan reads its initial state from and leaves its final state in f.state: the transposed
+  // state-gradient area is free until the transposes run
+  f.state = dstates_t;
+  if (e == cudaSuccess)
+    e = cudaMemsetAsync(dstates_t, 0, static_cast<size_t>(a.batch) * a.value_heads * kLD * kLD * sizeof(float), stream);
+  if (e == cudaSuccess) e = gdn_chunked_with_states(stream, f, base + l.records, states, status, lanes->prepared);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(lanes->aux, lanes->prepared, 0);
+  if (e == cudaSuccess)
+    e = gdn_scan_bwd_launch(lanes->aux, dcore16, base + l.records, a.batch, a.tokens, a.value_heads, chunks, dstates, status);
+  // (joined even after a failed launch, so that nothing of this call is left running unordered)
+  cudaError_t joined = cudaEventRecord(lanes->aux_done, lanes->aux);
   const unsigned matrices = static_cast<unsigned>(a.batch) * a.value_heads * chunks;
-  transpose_128_kernel<<<matrices, 256, 0, stream>>>(states, states_t);
+  if (e == cudaSuccess && joined == cudaSuccess) {
+    transpose_128_kernel<<<matrices, 256, 0, stream>>>(states, states_t);   // (needs the forward only)
+    e = cudaGetLastError();
+  }
+  if (joined == cudaSuccess) joined = cudaStreamWaitEvent(stream, lanes->aux_done, 0);
+  if (e != cudaSuccess) return e;
+  if (joined != cudaSuccess) return joined;
   transpose_128_kernel<<<matrices, 256, 0, stream>>>(dstates, dstates_t);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;

@@ -91,14 +91,17 @@ int gdn_piece_pairs(const GdnArgs& a, int pairs) {
   return per_piece;
 }
 
+// after_prepare (optional): recorded on `stream` behind the last prepare launch -- what only needs
+// the records (the reverse scan of the backward pass) can start there, beside the scan.
 cudaError_t gdn_prepare_and_scan(cudaStream_t stream, const GdnArgs& a, uint8_t* records, int chunks,
-                                 float* state_dump, uint32_t* status) {
+                                 float* state_dump, uint32_t* status, cudaEvent_t after_prepare = nullptr) {
   CUtensorMap maps[3];
   if (!gdn_prepare_sm100_maps(a, maps)) return cudaErrorInvalidValue;
   const int pairs = (chunks + 1) / 2;
   const int per_piece = gdn_piece_pairs(a, pairs);
   if (per_piece >= pairs) {
     cudaError_t e = gdn_prepare_sm100_launch(stream, maps, a, records, 0, pairs, chunks, status);
+    if (e == cudaSuccess && after_prepare != nullptr) e = cudaEventRecord(after_prepare, stream);
     if (e != cudaSuccess) return e;
     return gdn_scan_launch(stream, a, records, 0, chunks, chunks, state_dump, status);
   }
@@ -111,6 +114,7 @@ cudaError_t gdn_prepare_and_scan(cudaStream_t stream, const GdnArgs& a, uint8_t*
     const int n = min(per_piece, pairs - first);
     e = gdn_prepare_sm100_launch(stream, maps, a, records, first, n, chunks, status);
     if (e == cudaSuccess) e = cudaEventRecord(l->prepared[piece], stream);
+    if (e == cudaSuccess && after_prepare != nullptr && first + per_piece >= pairs) e = cudaEventRecord(after_prepare, stream);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(l->scan, l->prepared[piece], 0);
     if (e == cudaSuccess)
       e = gdn_scan_launch(l->scan, a, records, first * 2, min(n * 2, chunks - first * 2), chunks, state_dump, status);
@@ -761,9 +765,10 @@ cudaError_t gdn_chunked(cudaStream_t stream, const GdnArgs& a, void* workspace, 
 // well: the forward half of the chunked backward pass.  `records` is 1024-byte aligned and holds
 // gdn_chunked_workspace_bytes(...) bytes.
 cudaError_t gdn_chunked_with_states(cudaStream_t stream, const GdnArgs& a, void* records, float* state_dump,
-                                    uint32_t* status) {
+                                    uint32_t* status, cudaEvent_t after_prepare) {
   if (!gdn_prepare_sm100_supported(a)) return cudaErrorInvalidValue;
-  return gdn_prepare_and_scan(stream, a, static_cast<uint8_t*>(records), (a.tokens + kC - 1) / kC, state_dump, status);
+  return gdn_prepare_and_scan(stream, a, static_cast<uint8_t*>(records), (a.tokens + kC - 1) / kC, state_dump, status,
+                              after_prepare);
 }
 
 }  // namespace pluto
