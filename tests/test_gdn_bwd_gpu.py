@@ -142,7 +142,7 @@ def test_frozen_parameters_and_contracts():
         frozen.bwd([torch.zeros((t, vh * vd), dtype=torch.float32, device="cuda")], fwd.state)
 
 
-@pytest.mark.parametrize("shape", [(1, 320, 1, 2), (2, 333, 2, 4), (1, 1100, 1, 1)])
+@pytest.mark.parametrize("shape", [(1, 320, 1, 2), (2, 333, 2, 4), (1, 1100, 1, 1), (1, 256, 1, 1), (3, 257, 1, 2)])
 def test_chunk_parallel_recurrence_backward_matches_the_token_sequential_kernel(shape):
     """pluto_gdn_recurrence_bwd takes the chunk-parallel path for bf16 activations at width 128 from
     256 tokens on, the token-sequential kernel otherwise.  The same values given once as bf16 and
