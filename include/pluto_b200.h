@@ -225,7 +225,13 @@ int pluto_qk_prepare_bwd(pluto_stream_t stream, const void* x, size_t x_token_st
  * page_size = capacity, page_stride = capacity * kv_heads * head_dim,
  * token_stride = kv_heads * head_dim.  The position counter stays with the caller.
  * A shard of KV heads [h0, h0 + n) of a wider cache is addressed in place: k_base / v_base advanced
- * by h0 * head_dim elements, kv_heads = n in the call, token_stride left at the full row. */
+ * by h0 * head_dim elements, kv_heads = n in the call, token_stride left at the full row.
+ * Separately allocated per-sequence caches (the reference's one KeyValueCache object per
+ * sequence) are passed as two device arrays of base pointers, k_bases / v_bases [batch]: token t of
+ * sequence b, kv head h then starts at element t * token_stride + h * head_dim of k_bases[b]; no
+ * block table, page_size = the sequences' capacity, k_base / v_base / page_stride unused.  Decode
+ * over pointer arrays runs on the plain-load kernel (one pool or a block table is what the
+ * tensor-map path addresses). */
 typedef struct pluto_kv_cache {
   void* k_base;
   void* v_base;
@@ -237,6 +243,8 @@ typedef struct pluto_kv_cache {
   int dtype;           /* PLUTO_BF16 or PLUTO_FP32 */
   int num_pages;       /* pages in the pool when block_table is used (0 = unknown: decode then
                           takes its plain-load path); ignored without a block table */
+  const void* const* k_bases; /* device arrays [batch] of per-sequence base pointers, or both NULL */
+  const void* const* v_bases;
 } pluto_kv_cache;
 
 /* Per-head RMSNorm(1+w) -> bf16 rounding -> split-half partial RoPE of queries and keys, and the

@@ -84,7 +84,7 @@ class KvCacheStruct(C.Structure):
     """struct pluto_kv_cache of include/pluto_b200.h."""
     _fields_ = [("k_base", _vp), ("v_base", _vp), ("block_table", _vp), ("max_blocks", _i),
                 ("page_size", _i), ("page_stride", _sz), ("token_stride", _sz), ("dtype", _i),
-                ("num_pages", _i)]
+                ("num_pages", _i), ("k_bases", _vp), ("v_bases", _vp)]
 
 _lib = None
 

@@ -330,12 +330,14 @@ namespace {
 bool dtype_ok(int d) { return d == PLUTO_FP32 || d == PLUTO_BF16; }
 
 int check_cache(const pluto_kv_cache* cache, int kv_heads, int head_dim) {
-  if (!cache || !cache->k_base || !cache->v_base)
+  const bool separate = cache && (cache->k_bases || cache->v_bases);
+  if (!cache || (separate ? (!cache->k_bases || !cache->v_bases || cache->block_table)
+                          : (!cache->k_base || !cache->v_base)))
     return fail(PLUTO_E_INVALID, "attention requires non-null device pointers");
   if (!dtype_ok(cache->dtype)) return fail(PLUTO_E_INVALID, "attention cache has an unknown dtype");
   if (cache->page_size <= 0 || (cache->block_table && cache->max_blocks <= 0) ||
       cache->token_stride < static_cast<size_t>(kv_heads) * head_dim ||
-      cache->page_stride < cache->token_stride)
+      (!separate && cache->page_stride < cache->token_stride))
     return fail(PLUTO_E_INVALID, "attention cache shape or capacity does not match parameters");
   return PLUTO_OK;
 }
@@ -363,6 +365,8 @@ int fill_decode(pluto::DecodeArgs* a, const void* q, int q_dtype, const pluto_kv
   a->q_is_bf16 = q_dtype == PLUTO_BF16;
   a->k_base = cache->k_base;
   a->v_base = cache->v_base;
+  a->k_bases = cache->k_bases;
+  a->v_bases = cache->v_bases;
   a->kv_is_bf16 = cache->dtype == PLUTO_BF16;
   a->block_table = cache->block_table;
   a->max_blocks = cache->max_blocks;
@@ -416,6 +420,7 @@ int pluto_qk_prepare(pluto_stream_t stream, const void* q_in, const void* k_in, 
   a.q_norm = q_norm; a.k_norm = k_norm; a.positions = positions;
   a.q_out = q_out; a.q_out_is_bf16 = q_out_dtype == PLUTO_BF16;
   a.k_cache = cache->k_base; a.v_cache = cache->v_base; a.kv_is_bf16 = cache->dtype == PLUTO_BF16;
+  a.k_bases = cache->k_bases; a.v_bases = cache->v_bases;
   a.block_table = cache->block_table; a.max_blocks = cache->max_blocks;
   a.page_size = cache->page_size; a.page_stride = cache->page_stride;
   a.token_stride = cache->token_stride;

@@ -145,6 +145,8 @@ struct DecodeArgs {
   size_t gate_token, gate_head;
   const void* k_base;
   const void* v_base;
+  const void* const* k_bases;   // optional device arrays [batch] of per-sequence bases: sequence b's token
+  const void* const* v_bases;   // t then starts at t * token_stride of k_bases[b] (no pages)
   int kv_is_bf16;
   const int32_t* block_table;
   int max_blocks, page_size;
@@ -188,6 +190,8 @@ struct PrepareArgs {
   int q_out_is_bf16;
   void* k_cache;            // cache addressing as in DecodeArgs
   void* v_cache;
+  const void* const* k_bases;   // optional per-sequence base pointers (then k_cache / v_cache are unused)
+  const void* const* v_bases;
   int kv_is_bf16;
   const int32_t* block_table;
   int max_blocks, page_size;

@@ -44,8 +44,14 @@ __device__ __forceinline__ int bounded_length(const DecodeArgs& a, int b, uint32
   return length;
 }
 
-__device__ __forceinline__ const char* kv_row(const DecodeArgs& a, const void* base, int b, int t,
+__device__ __forceinline__ const char* kv_row(const DecodeArgs& a, bool value, int b, int t,
                                               int kv_head, size_t element) {
+  const void* base = value ? a.v_base : a.k_base;
+  if (a.k_bases != nullptr) {   // separately allocated sequences
+    const void* own = (value ? a.v_bases : a.k_bases)[b];
+    return static_cast<const char*>(own) +
+           (static_cast<size_t>(t) * a.token_stride + static_cast<size_t>(kv_head) * a.head_dim) * element;
+  }
   int page = a.block_table ? a.block_table[static_cast<size_t>(b) * a.max_blocks + t / a.page_size]
                            : b;
   if (a.block_table && a.num_pages > 0 && (page < 0 || page >= a.num_pages)) {
@@ -343,8 +349,8 @@ __global__ void __launch_bounds__(128) gqa_decode_generic(DecodeArgs a) {
   }
   float m = -INFINITY, l = 0.0f;
   for (int t = begin + warp; t < end; t += 4) {
-    const char* kr = kv_row(a, a.k_base, b, t, kv_head, element);
-    const char* vr = kv_row(a, a.v_base, b, t, kv_head, element);
+    const char* kr = kv_row(a, false, b, t, kv_head, element);
+    const char* vr = kv_row(a, true, b, t, kv_head, element);
     float dot = 0.0f, v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -500,7 +506,7 @@ __global__ void __launch_bounds__(256) gqa_decode_probs(DecodeArgs a, float* pro
   const size_t q0 = (static_cast<size_t>(b) * a.q_heads + head) * D;
   float local_max = -INFINITY;
   for (int t = threadIdx.x; t < length; t += 256) {
-    const char* kr = kv_row(a, a.k_base, b, t, kv_head, element);
+    const char* kr = kv_row(a, false, b, t, kv_head, element);
     float dot = 0.0f;
     for (int d = 0; d < D; ++d) {
       const float kx = a.kv_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(kr)[d])
@@ -570,7 +576,7 @@ bool make_pool_map(CUtensorMap* map, const void* base, const DecodeArgs& a, int 
 bool gqa_decode_uses_tensor_cores(const DecodeArgs& a) {
   const int group = a.q_heads / a.kv_heads;
   const int pages = a.block_table ? a.num_pages : a.batch;
-  return a.kv_is_bf16 && (a.head_dim == 64 || a.head_dim == 128) && group <= 16 &&
+  return a.k_bases == nullptr && a.kv_is_bf16 && (a.head_dim == 64 || a.head_dim == 128) && group <= 16 &&
          (a.round || a.q_is_bf16) && a.token_stride % 8 == 0 && a.page_stride % 8 == 0 &&
          a.page_size % 16 == 0 && pages > 0 &&
          (reinterpret_cast<uintptr_t>(a.k_base) & 15u) == 0 &&

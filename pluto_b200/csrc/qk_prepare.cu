@@ -48,7 +48,13 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(PrepareArgs a) {
 
   // destination row: queries are dense [B, T, Hq, D]; keys/values go to the cache layout
   size_t kv_off = 0;
-  if (!is_query) {
+  void* k_dst = a.k_cache;
+  void* v_dst = a.v_cache;
+  if (!is_query && a.k_bases != nullptr) {   // separately allocated sequences
+    k_dst = const_cast<void*>(a.k_bases[b]);
+    v_dst = const_cast<void*>(a.v_bases[b]);
+    kv_off = static_cast<size_t>(position) * a.token_stride + static_cast<size_t>(h) * D;
+  } else if (!is_query) {
     const int page = a.block_table ? a.block_table[static_cast<size_t>(b) * a.max_blocks + position / a.page_size] : b;
     kv_off = static_cast<size_t>(page) * a.page_stride +
              static_cast<size_t>(position % a.page_size) * a.token_stride + static_cast<size_t>(h) * D;
@@ -70,9 +76,9 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(PrepareArgs a) {
     if (is_query) {
       store_out(a.q_out, (static_cast<size_t>(token) * a.q_heads + h) * D + c, a.q_out_is_bf16, result);
     } else {
-      store_out(a.k_cache, kv_off + c, a.kv_is_bf16, result);
+      store_out(k_dst, kv_off + c, a.kv_is_bf16, result);
       const float value = load_in(a.v_in, (static_cast<size_t>(token) * a.kv_heads + h) * D + c, a.in_is_bf16);
-      store_out(a.v_cache, kv_off + c, a.kv_is_bf16, rnd(value, a.round));
+      store_out(v_dst, kv_off + c, a.kv_is_bf16, rnd(value, a.round));
     }
   }
 }

@@ -409,6 +409,39 @@ def kv_layout(k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: Optional[
     return s
 
 
+def gqa_decode_separate_caches(q: torch.Tensor, caches, seq_lens: torch.Tensor, *,
+                               round_to_bfloat16: bool = True, want_lse: bool = False):
+    """Batched decode over independently allocated per-sequence caches (one KeyValueCache object
+    per sequence, as the reference keeps them, src/llm/key_value_cache.h:25-57): the cache
+    descriptor carries two device arrays of base pointers instead of one pool.  q [B,Hq,D];
+    `caches` B KeyValueCache objects of equal shape and dtype; seq_lens int32 [B]."""
+    B, Hq, D = q.shape
+    first = caches[0]
+    if len(caches) != B or any(c.keys().shape != first.keys().shape or c.keys().dtype != first.keys().dtype
+                               for c in caches):
+        raise _invalid("one cache per sequence, all of one shape and dtype")
+    capacity, Hkv = first.capacity(), first.key_value_heads()
+    k_bases = torch.tensor([c.keys().data_ptr() for c in caches], dtype=torch.int64, device=q.device)
+    v_bases = torch.tensor([c.values().data_ptr() for c in caches], dtype=torch.int64, device=q.device)
+    layout = _capi.KvCacheStruct()
+    layout.k_base = layout.v_base = layout.block_table = None
+    layout.max_blocks, layout.page_size = 0, capacity
+    layout.page_stride = layout.token_stride = Hkv * D
+    layout.page_stride *= capacity
+    layout.dtype = 1 if first.keys().dtype == torch.bfloat16 else 0
+    layout.num_pages = 0
+    layout.k_bases, layout.v_bases = k_bases.data_ptr(), v_bases.data_ptr()
+    L = _capi.lib()
+    out = torch.empty_like(q)
+    nbytes = L.pluto_gqa_decode_workspace_bytes(B, Hq, Hkv, D, capacity)
+    ws = _workspace(q.device, nbytes)
+    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if want_lse else None
+    check(L.pluto_gqa_decode(_stream(), _ptr(q), _dt(q), None, 0, 0, 0, C_byref(layout), _ptr(seq_lens),
+                             capacity, _ptr(out), _dt(out), _ptr(lse), _ptr(ws), ws.numel(), B, Hq, Hkv, D,
+                             int(round_to_bfloat16)))
+    return (out, lse) if want_lse else out
+
+
 def _dt(t: torch.Tensor) -> int:
     if t.dtype == torch.bfloat16:
         return 1

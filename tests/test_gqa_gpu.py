@@ -11,6 +11,7 @@ from conftest import sine_values
 from gpu_util import bf16_bits, near, to_device_bf16
 from pluto_b200 import PlutoStatusError, _capi
 from pluto_b200.layers import (CachedAttentionStep, FullAttentionParameters, KeyValueCache,
+                               gqa_decode_separate_caches,
                                gqa_decode, gqa_prefill)
 
 pytestmark = pytest.mark.gpu
@@ -337,3 +338,39 @@ def test_decode_over_a_shard_of_kv_heads_in_place():
         assert _capi.kernel_status() == 0
         assert torch.equal(in_place, copied), dtype
         assert torch.isfinite(in_place.float()).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_decode_over_separately_allocated_caches(dtype):
+    """The reference keeps one KeyValueCache object per sequence (key_value_cache.h:25-57).  A batch
+    of independently allocated caches is decoded through device arrays of base pointers in the cache
+    descriptor, with no pooling copy: same result as the decode over a pool holding the same rows
+    (the pool takes the tensor-map kernel for bf16, the pointer arrays the plain-load kernel, so
+    the two agree to bf16 resolution, and exactly for the fp32 cache where both take plain loads),
+    and each sequence against the CPU oracle."""
+    batch, hq, hkv, d, cap = 4, 10, 2, 128, 512
+    gen = torch.Generator(device="cuda").manual_seed(43)
+    lens = torch.tensor([512, 333, 16, 1], dtype=torch.int32, device="cuda")
+    caches = [KeyValueCache.Create(cap, hkv, d, dtype) for _ in range(batch)]
+    spacer = [torch.empty(1000 + 37 * i, device="cuda") for i in range(batch)]   # keep the allocations apart
+    for c in caches:
+        c.keys().copy_((torch.randn(cap, hkv, d, device="cuda", generator=gen) * 0.5).to(dtype))
+        c.values().copy_((torch.randn(cap, hkv, d, device="cuda", generator=gen) * 0.5).to(dtype))
+    q = (torch.randn(batch, hq, d, device="cuda", generator=gen) * 0.5).bfloat16()
+    out, lse = gqa_decode_separate_caches(q, caches, lens, want_lse=True)
+    pool_k = torch.stack([c.keys() for c in caches])
+    pool_v = torch.stack([c.values() for c in caches])
+    pooled, pooled_lse = gqa_decode(q, pool_k, pool_v, lens, cap, want_lse=True)
+    torch.cuda.synchronize()
+    assert _capi.kernel_status() == 0
+    del spacer
+    if dtype == torch.float32:
+        assert torch.equal(out, pooled) and torch.equal(lse, pooled_lse)
+    else:
+        assert (out.float() - pooled.float()).abs().max().item() <= 2e-2
+        assert (lse - pooled_lse).abs().max().item() <= 1e-3
+    kb = [bf16_bits(c.keys().bfloat16()[:int(n)]) for c, n in zip(caches, lens.tolist())]
+    vb = [bf16_bits(c.values().bfloat16()[:int(n)]) for c, n in zip(caches, lens.tolist())]
+    if dtype == torch.bfloat16:
+        want = oracle.gqa_decode_batch(bf16_bits(q), kb, vb, lens.cpu().numpy(), threads=4)
+        assert np.abs(oracle.from_bf16_bits(bf16_bits(out)) - oracle.from_bf16_bits(want)).max() <= 2e-2
