@@ -374,3 +374,50 @@ def test_decode_over_separately_allocated_caches(dtype):
     if dtype == torch.bfloat16:
         want = oracle.gqa_decode_batch(bf16_bits(q), kb, vb, lens.cpu().numpy(), threads=4)
         assert np.abs(oracle.from_bf16_bits(bf16_bits(out)) - oracle.from_bf16_bits(want)).max() <= 2e-2
+
+
+def test_prepare_appends_into_separately_allocated_caches():
+    """pluto_qk_prepare with per-sequence base pointers writes each sequence's new key / value rows
+    at its own position of its own allocation: bit for bit the rows the pool form writes, and
+    nothing else in the caches changes."""
+    import ctypes
+
+    from pluto_b200.layers import kv_layout
+    batch, hq, hkv, d, cap, rotary = 3, 4, 2, 64, 48, 32
+    gen = torch.Generator(device="cuda").manual_seed(47)
+    q_gate = (torch.randn(batch, 1, hq, 2, d, device="cuda", generator=gen) * 0.5).bfloat16()
+    k_in = (torch.randn(batch, 1, hkv, d, device="cuda", generator=gen) * 0.5).bfloat16()
+    v_in = (torch.randn(batch, 1, hkv, d, device="cuda", generator=gen) * 0.5).bfloat16()
+    q_norm = torch.randn(d, device="cuda", generator=gen) * 0.1
+    k_norm = torch.randn(d, device="cuda", generator=gen) * 0.1
+    positions = torch.tensor([0, 17, 47], dtype=torch.int32, device="cuda")
+    L = _capi.lib()
+    P = lambda x: ctypes.c_void_p(x.data_ptr())
+
+    def run(layout):
+        q_out = torch.empty(batch, 1, hq, d, dtype=torch.bfloat16, device="cuda")
+        _capi.check(L.pluto_qk_prepare(None, P(q_gate), P(k_in), P(v_in), 1, 2 * hq * d, 2 * d, P(q_norm), P(k_norm),
+                                       P(positions), P(q_out), 1, ctypes.byref(layout), batch, 1, hq, hkv, d, rotary,
+                                       1e-6, 1.0e6, 1))
+        torch.cuda.synchronize()
+        return q_out
+
+    pool_k = torch.full((batch, cap, hkv, d), 7.0, dtype=torch.bfloat16, device="cuda")
+    pool_v = torch.full_like(pool_k, 7.0)
+    q_pool = run(kv_layout(pool_k, pool_v, None, cap, cap * hkv * d, hkv * d))
+    caches = [KeyValueCache.Create(cap, hkv, d) for _ in range(batch)]
+    for c in caches:
+        c.keys().fill_(7.0)
+        c.values().fill_(7.0)
+    k_bases = torch.tensor([c.keys().data_ptr() for c in caches], dtype=torch.int64, device="cuda")
+    v_bases = torch.tensor([c.values().data_ptr() for c in caches], dtype=torch.int64, device="cuda")
+    layout = _capi.KvCacheStruct()
+    layout.page_size, layout.token_stride, layout.page_stride, layout.dtype = cap, hkv * d, cap * hkv * d, 1
+    layout.k_bases, layout.v_bases = k_bases.data_ptr(), v_bases.data_ptr()
+    q_separate = run(layout)
+    assert _capi.kernel_status() == 0
+    assert torch.equal(q_pool, q_separate)
+    for b, c in enumerate(caches):
+        assert torch.equal(c.keys(), pool_k[b]) and torch.equal(c.values(), pool_v[b])
+        row = int(positions[b])
+        assert not torch.equal(c.keys()[row], torch.full_like(c.keys()[row], 7.0))
