@@ -538,6 +538,8 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       const float c = sm.cdec[t], f = sm.iq[t] * q_scale;
       float qv[4], scaled[4], rs = 0.0f;
       to_array(qraw[i], qv);
+      // (this thread's piece of q^, kept for the last products: big[1] is free since U)
+      *reinterpret_cast<float4*>(sm.big[1] + t * kLP + c0) = make_float4(qv[0] * f, qv[1] * f, qv[2] * f, qv[3] * f);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         scaled[j] = acc[i][j] * c;
@@ -587,6 +589,9 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       rows[i] = rs;
     }
     add_rows(sm.dbeta, rows, 1.0f);
+    // (this thread's piece of v, for R below: big[3] is free since the last ring product)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(sm.big[3] + (r0 + i) * kLP + c0) = vraw[i];
     __syncthreads();   // every read of dU is done (and dW is complete)
     store_dense(sm.big[4], l, acc);
   }
@@ -612,15 +617,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     store_dense(sm.big[2], l, acc);
   }
   // ---- dA = -mask(X1 U'^T + X2 W^T) = -mask(R T^T),  R = X1 (beta . v)^T + X2 (beta c . k^)^T: U' and W
-  //      need not be kept.  v is staged again (big[3]); R -> sq[1] (M is dead)
-  for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
-    const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
-    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (t < count)
-      v = load_any4(a.v, (token0 + t) * a.v_token + static_cast<size_t>(h) * kLD + c4 * 4, a.in_is_bf16);
-    *reinterpret_cast<float4*>(sm.big[3] + t * kLP + c4 * 4) = v;
-  }
-  __syncthreads();
+  //      need not be kept (v came into big[3] with X1, the barrier after X2 covers it); R -> sq[1] (M is dead)
   {
     float from_v[4][2], from_k[4][2];
     zero(from_v);
@@ -636,17 +633,6 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       }
   }
   __syncthreads();
-  // q^ is staged again (big[1]) while the last [64 x 64] products run
-  for (int idx = tid; idx < kLC * (kLD / 4); idx += kLThreads) {
-    const int t = idx / (kLD / 4), c4 = idx % (kLD / 4);
-    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (t < count) {
-      const float f = sm.iq[t] * q_scale;
-      v = load_any4(a.q, (token0 + t) * a.qk_token + static_cast<size_t>(kh) * kLD + c4 * 4, a.in_is_bf16);
-      v = make_float4(v.x * f, v.y * f, v.z * f, v.w * f);
-    }
-    *reinterpret_cast<float4*>(sm.big[1] + t * kLP + c4 * 4) = v;
-  }
   {
     float acc[4][2], g[4][2];
     zero(acc);
@@ -686,7 +672,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     for (int g = 0; g < 16; ++g) total += sm.part[g][tid];
     sm.part[0][tid] = total;
   }
-  // ---- dk^ = stashed + beta c . X2 + (dG + dG^T) k^ + dH^T q^;  dq^ = stashed + dH k^
+  // ---- dk^ = stashed + beta c . X2 + (dG + dG^T) k^ + dH^T q^;  dq^ = stashed + dH k^   (q^ in big[1] since dQc)
   float dk_acc[4][4], dq_acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
