@@ -234,6 +234,53 @@ __device__ __forceinline__ void nn_ring(const float* A, int pa, const float* __r
   from_pairs(pair, acc);
 }
 
+// Two products against the same streamed matrix in one pass: acc1 += A1 Bg, acc2 += A2 Bg.
+__device__ __forceinline__ void nn_ring2(const float* A1, const float* A2, int pa, const float* __restrict__ Bg,
+                                         float* ring, const Lane& l, int tid, float (&acc1)[4][4],
+                                         float (&acc2)[4][4]) {
+  constexpr int kStageRows = 16, kStages = kLD / kStageRows, kStageFloats = kStageRows * kLD;
+  uint64_t pair1[4][2], pair2[4][2];
+  to_pairs(acc1, pair1);
+  to_pairs(acc2, pair2);
+#pragma unroll
+  for (int s = 0; s < kRingStages - 1; ++s) {
+    cp_async16(ring + s * kStageFloats + tid * 4, Bg + s * kStageFloats + tid * 4);
+    cp_async_commit();
+  }
+#pragma unroll 1
+  for (int s = 0; s < kStages; ++s) {
+    cp_async_wait<kRingStages - 2>();
+    __syncthreads();
+    const int ahead = s + kRingStages - 1;
+    if (ahead < kStages)
+      cp_async16(ring + (ahead % kRingStages) * kStageFloats + tid * 4, Bg + ahead * kStageFloats + tid * 4);
+    cp_async_commit();
+    const float* Bs = ring + (s % kRingStages) * kStageFloats;
+#pragma unroll 2
+    for (int k = 0; k < kStageRows; k += 4) {
+      float4 a1[4], a2[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a1[i] = lds4(A1 + (l.r0 + i) * pa + s * kStageRows + k);
+        a2[i] = lds4(A2 + (l.r0 + i) * pa + s * kStageRows + k);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const float4 bv = lds4(Bs + (k + kk) * kLD + l.c0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          dense_step(comp(a1[i], kk), bv, pair1[i]);
+          dense_step(comp(a2[i], kk), bv, pair2[i]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  from_pairs(pair1, acc1);
+  from_pairs(pair2, acc2);
+}
+
 template <int N>
 __device__ __forceinline__ void zero(float (&acc)[4][N]) {
 #pragma unroll
@@ -521,16 +568,23 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     }
     store_dense(sm.big[4], l, acc);
   }
-  // ---- dQc = dO S_0^T: dq^ += c . dQc, db += rows(dQc . c q^)
+  // ---- dQc = dO S_0^T: dq^ += c . dQc, db += rows(dQc . c q^);  dW = -dU S_0^T -> big[2] in the same pass
+  //      over S_0^T (dU is complete: the pass starts with a barrier; dO is read for the last time)
   {
     float4 qraw[4];   // requested before the product, used after it
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       qraw[i] = r0 + i < count ? load_any4(a.q, (token0 + r0 + i) * a.qk_token + static_cast<size_t>(kh) * kLD + c0, a.in_is_bf16)
                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    float acc[4][4];
+    float acc[4][4], dw[4][4];
     zero(acc);
-    nn_ring(sm.big[2], kLP, S0t, sm.big[3], l, tid, acc);
+    zero(dw);
+    nn_ring2(sm.big[2], sm.big[4], kLP, S0t, sm.big[3], l, tid, acc, dw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dw[i][j] = -dw[i][j];
+    store_dense(sm.big[2], l, dw);
     float rows[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -551,17 +605,6 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       rows[i] = rs;
     }
     add_rows(sm.db, rows, 1.0f);
-  }
-  // ---- dW = -dU S_0^T -> big[2]   (dU is complete and dO no longer needed: barriers inside nn_ring)
-  {
-    float acc[4][4];
-    zero(acc);
-    nn_ring(sm.big[4], kLP, S0t, sm.big[3], l, tid, acc);
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = -acc[i][j];
-    store_dense(sm.big[2], l, acc);
   }
   // ---- X1 = T^T dU: dv = beta . X1, dbeta += rows(X1 . v); X1 replaces dU
   {
