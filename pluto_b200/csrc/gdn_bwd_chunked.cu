@@ -185,6 +185,98 @@ __device__ __forceinline__ void tn_smem(const float* A, int pa, const float* B, 
   from_pairs(pair, acc);
 }
 
+// Pairs of products that share an operand, in one pass (the shared fragments are loaded once):
+// acc1[i][j] += sum_k A1[r0+i][k] B[..][k], acc2 likewise with A2          (two A B^T, strided columns)
+template <int K>
+__device__ __forceinline__ void nt_smem2(const float* A1, const float* A2, int pa, const float* B, int pb,
+                                         const Lane& l, float (&acc1)[4][2], float (&acc2)[4][2]) {
+  uint64_t p1[4][2], p2[4][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) p1[i][j] = p2[i][j] = f2_pack(0.0f, 0.0f);
+#pragma unroll 2
+  for (int k = 0; k < K; k += 4) {
+    float4 a1[4], a2[4], b[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      a1[i] = lds4(A1 + (l.r0 + i) * pa + k);
+      a2[i] = lds4(A2 + (l.r0 + i) * pa + k);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) b[j] = lds4(B + (l.cg + 16 * j + 32 * l.ch) * pb + k);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint64_t b01 = f2_pack(b[j].x, b[j].y), b23 = f2_pack(b[j].z, b[j].w);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        p1[i][j] = f2_fma(f2_pack(a1[i].x, a1[i].y), b01, p1[i][j]);
+        p1[i][j] = f2_fma(f2_pack(a1[i].z, a1[i].w), b23, p1[i][j]);
+        p2[i][j] = f2_fma(f2_pack(a2[i].x, a2[i].y), b01, p2[i][j]);
+        p2[i][j] = f2_fma(f2_pack(a2[i].z, a2[i].w), b23, p2[i][j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float lo, hi;
+      f2_unpack(p1[i][j], lo, hi);
+      acc1[i][j] += lo + hi;
+      f2_unpack(p2[i][j], lo, hi);
+      acc2[i][j] += lo + hi;
+    }
+}
+// acc1 += A1 B, acc2 += A2 B                                                (two A B, dense columns)
+template <int K>
+__device__ __forceinline__ void nn_smem2(const float* A1, const float* A2, int pa, const float* B, int pb,
+                                         const Lane& l, float (&acc1)[4][4], float (&acc2)[4][4]) {
+  uint64_t p1[4][2], p2[4][2];
+  to_pairs(acc1, p1);
+  to_pairs(acc2, p2);
+#pragma unroll 2
+  for (int k = 0; k < K; k += 4) {
+    float4 a1[4], a2[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      a1[i] = lds4(A1 + (l.r0 + i) * pa + k);
+      a2[i] = lds4(A2 + (l.r0 + i) * pa + k);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const float4 bv = lds4(B + (k + kk) * pb + l.c0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        dense_step(comp(a1[i], kk), bv, p1[i]);
+        dense_step(comp(a2[i], kk), bv, p2[i]);
+      }
+    }
+  }
+  from_pairs(p1, acc1);
+  from_pairs(p2, acc2);
+}
+// acc1 += A^T B1, acc2 += A^T B2                                            (two A^T B, dense columns)
+template <int K>
+__device__ __forceinline__ void tn_smem2(const float* A, int pa, const float* B1, const float* B2, int pb,
+                                         const Lane& l, float (&acc1)[4][4], float (&acc2)[4][4]) {
+  uint64_t p1[4][2], p2[4][2];
+  to_pairs(acc1, p1);
+  to_pairs(acc2, p2);
+#pragma unroll 4
+  for (int k = 0; k < K; ++k) {
+    const float4 a = lds4(A + k * pa + l.r0);
+    const float4 b1 = lds4(B1 + k * pb + l.c0), b2 = lds4(B2 + k * pb + l.c0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      dense_step(comp(a, i), b1, p1[i]);
+      dense_step(comp(a, i), b2, p2[i]);
+    }
+  }
+  from_pairs(p1, acc1);
+  from_pairs(p2, acc2);
+}
+
 __device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
 }
@@ -395,8 +487,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     float g[4][2], hh[4][2];
     zero(g);
     zero(hh);
-    nt_smem<kLD>(Kh, kLP, Kh, kLP, l, g);
-    nt_smem<kLD>(sm.big[1], kLP, Kh, kLP, l, hh);
+    nt_smem2<kLD>(Kh, sm.big[1], kLP, Kh, kLP, l, g, hh);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -734,8 +825,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
       dk_acc[i][j] = sk_[j] + bc * x2[j];
     }
   }
-  nn_smem<kLC>(sm.sq[1], kLQ, nullptr, Kh, kLP, l, dk_acc);
-  nn_smem<kLC>(sm.sq[0], kLQ, nullptr, Kh, kLP, l, dq_acc);
+  nn_smem2<kLC>(sm.sq[1], sm.sq[0], kLQ, Kh, kLP, l, dk_acc, dq_acc);
   tn_smem<kLC>(sm.sq[0], kLQ, sm.big[1], kLP, l, dk_acc);
 
   // ---- through the normalisations: per-token partials in the layout of the gather kernels (one
