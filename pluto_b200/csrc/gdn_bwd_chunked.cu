@@ -698,58 +698,51 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     add_rows(sm.db, rows, 1.0f);
   }
   // ---- X1 = T^T dU: dv = beta . X1, dbeta += rows(X1 . v); X1 replaces dU
+  //      X2 = T^T dW: dk^ += beta c . X2 (at the end), dbeta += rows(X2 . c k^), db += rows(X2 . beta c k^);
+  //      X2 replaces dW.  One pass over T for both.
   {
     float4 vraw[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       vraw[i] = r0 + i < count ? load_any4(a.v, (token0 + r0 + i) * a.v_token + static_cast<size_t>(h) * kLD + c0, a.in_is_bf16)
                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    float acc[4][4];
+    float acc[4][4], acc2[4][4];
     zero(acc);
-    tn_smem<kLC>(Tm, kLQ, sm.big[4], kLP, l, acc);
-    float rows[4];
+    zero(acc2);
+    __syncthreads();   // dW (stored after the pass over S_0^T) is complete
+    tn_smem2<kLC>(Tm, kLQ, sm.big[4], sm.big[2], kLP, l, acc, acc2);
+    float rows[4], rows_beta[4], rows_b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int t = r0 + i;
-      float vv[4], rs = 0.0f;
+      float vv[4], kv[4], rs = 0.0f, rs2 = 0.0f;
       to_array(vraw[i], vv);
+      to_array(lds4(Kh + t * kLP + c0), kv);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) rs = fmaf(acc[i][j], vv[j], rs);
+      for (int j = 0; j < 4; ++j) {
+        rs = fmaf(acc[i][j], vv[j], rs);
+        rs2 = fmaf(acc2[i][j], kv[j], rs2);
+      }
       if (t < count) {
         const float be = sm.beta[t];
         *reinterpret_cast<float4*>(a.dv_out + (token0 + t) * a.dv_token + static_cast<size_t>(h) * kLD + c0) =
             make_float4(be * acc[i][0], be * acc[i][1], be * acc[i][2], be * acc[i][3]);
       }
       rows[i] = rs;
+      rows_beta[i] = rs2 * sm.cdec[t];
+      rows_b[i] = rows_beta[i] * sm.beta[t];
     }
     add_rows(sm.dbeta, rows, 1.0f);
+    add_rows(sm.dbeta, rows_beta, 1.0f);
+    add_rows(sm.db, rows_b, 1.0f);
     // (this thread's piece of v, for R below: big[3] is free since the last ring product)
 #pragma unroll
     for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(sm.big[3] + (r0 + i) * kLP + c0) = vraw[i];
-    __syncthreads();   // every read of dU is done (and dW is complete)
+    __syncthreads();   // every read of dU and dW is done
     store_dense(sm.big[4], l, acc);
+    store_dense(sm.big[2], l, acc2);
   }
-  // ---- X2 = T^T dW: dk^ += beta c . X2 (at the end), dbeta += rows(X2 . c k^), db += rows(X2 . beta c k^); X2 replaces dW
-  {
-    float acc[4][4];
-    zero(acc);
-    tn_smem<kLC>(Tm, kLQ, sm.big[2], kLP, l, acc);
-    float rows_beta[4], rows_b[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int t = r0 + i;
-      float kv[4], rs = 0.0f;
-      to_array(lds4(Kh + t * kLP + c0), kv);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) rs = fmaf(acc[i][j], kv[j], rs);
-      rows_beta[i] = rs * sm.cdec[t];
-      rows_b[i] = rows_beta[i] * sm.beta[t];
-    }
-    add_rows(sm.dbeta, rows_beta, 1.0f);
-    add_rows(sm.db, rows_b, 1.0f);
-    __syncthreads();   // every read of dW is done
-    store_dense(sm.big[2], l, acc);
-  }
+  __syncthreads();
   // ---- dA = -mask(X1 U'^T + X2 W^T) = -mask(R T^T),  R = X1 (beta . v)^T + X2 (beta c . k^)^T: U' and W
   //      need not be kept (v came into big[3] with X1, the barrier after X2 covers it); R -> sq[1] (M is dead)
   {
