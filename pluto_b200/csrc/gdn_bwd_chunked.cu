@@ -284,93 +284,160 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// acc[i][j] += sum_k A[r0+i][k] Bg[k][c0+j]  with Bg a [128 x 128] matrix in global memory.  Its
-// rows pass through a ring in shared memory, sixteen rows (8 KB, one 16-byte asynchronous copy per
-// thread) per stage and kRingStages - 1 stages in flight, so the products never wait for memory; all
-// 512 threads call this together.  `ring` holds kRingStages * 2048 floats and is free again on return.
-constexpr int kRingStages = 4;
-__device__ __forceinline__ void nn_ring(const float* A, int pa, const float* __restrict__ Bg, float* ring,
-                                        const Lane& l, int tid, float (&acc)[4][4]) {
-  constexpr int kStageRows = 16, kStages = kLD / kStageRows, kStageFloats = kStageRows * kLD;
-  uint64_t pair[4][2];
-  to_pairs(acc, pair);
-#pragma unroll
-  for (int s = 0; s < kRingStages - 1; ++s) {
-    cp_async16(ring + s * kStageFloats + tid * 4, Bg + s * kStageFloats + tid * 4);
-    cp_async_commit();
-  }
-#pragma unroll 1
-  for (int s = 0; s < kStages; ++s) {
-    cp_async_wait<kRingStages - 2>();
-    __syncthreads();   // stage s has landed for every thread; the slot refilled below was read in step s - 1
-    const int ahead = s + kRingStages - 1;
-    if (ahead < kStages)
-      cp_async16(ring + (ahead % kRingStages) * kStageFloats + tid * 4, Bg + ahead * kStageFloats + tid * 4);
-    cp_async_commit();
-    const float* Bs = ring + (s % kRingStages) * kStageFloats;
-#pragma unroll 2
-    for (int k = 0; k < kStageRows; k += 4) {
-      float4 a[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = lds4(A + (l.r0 + i) * pa + s * kStageRows + k);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const float4 bv = lds4(Bs + (k + kk) * kLD + l.c0);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dense_step(comp(a[i], kk), bv, pair[i]);
-      }
-    }
-  }
-  cp_async_wait<0>();
-  __syncthreads();
-  from_pairs(pair, acc);
-}
+__device__ __forceinline__ void to_array(const float4& v, float (&x)[4]) { x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w; }
 
-// Two products against the same streamed matrix in one pass: acc1 += A1 Bg, acc2 += A2 Bg.
-__device__ __forceinline__ void nn_ring2(const float* A1, const float* A2, int pa, const float* __restrict__ Bg,
-                                         float* ring, const Lane& l, int tid, float (&acc1)[4][4],
-                                         float (&acc2)[4][4]) {
-  constexpr int kStageRows = 16, kStages = kLD / kStageRows, kStageFloats = kStageRows * kLD;
-  uint64_t pair1[4][2], pair2[4][2];
-  to_pairs(acc1, pair1);
-  to_pairs(acc2, pair2);
+// ---- products on the tensor cores -----------------------------------------------------------------
+// fp32 operands as bf16 high part + bf16 remainder, three mma.sync products per pair of fragments
+// (high x high, high x remainder, remainder x high; the remainder x remainder term is 2^-16 of
+// the product), fp32 accumulation.  The results go to a matrix in shared memory, from where the
+// threads pick up their usual tiles.
+__device__ __forceinline__ void split_pair(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  hi = pack_bf16(x0, x1);
+  lo = pack_bf16(x0 - bf16_lo(hi), x1 - bf16_hi(hi));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+constexpr int kMmaRingPitch = 132;                       // floats per staged row: conflict-free fragment loads
+constexpr int kMmaStageFloats = 16 * kMmaRingPitch;      // 16 rows = one k step; 4 stages = one [64 x 132] buffer
+// A fragment (16 rows x 16 k) of a row-major fp32 matrix, split
+__device__ __forceinline__ void load_a_fragment(const float* A, int pa, int m0, int k0, int g, int t,
+                                                uint32_t (&hi)[4], uint32_t (&lo)[4]) {
+  const float2 x0 = *reinterpret_cast<const float2*>(A + (m0 + g) * pa + k0 + 2 * t);
+  const float2 x1 = *reinterpret_cast<const float2*>(A + (m0 + g + 8) * pa + k0 + 2 * t);
+  const float2 x2 = *reinterpret_cast<const float2*>(A + (m0 + g) * pa + k0 + 2 * t + 8);
+  const float2 x3 = *reinterpret_cast<const float2*>(A + (m0 + g + 8) * pa + k0 + 2 * t + 8);
+  split_pair(x0.x, x0.y, hi[0], lo[0]);
+  split_pair(x1.x, x1.y, hi[1], lo[1]);
+  split_pair(x2.x, x2.y, hi[2], lo[2]);
+  split_pair(x3.x, x3.y, hi[3], lo[3]);
+}
+// out1 = A1 Bg (and out2 = sign2 A2 Bg when kTwo) for a [128 x 128] matrix Bg in global memory, whose
+// rows pass through `ring` ([4 stages][16 rows][132] floats, one 16-byte asynchronous copy per thread
+// and stage, three stages in flight).  Warp w owns the 16 x 32 block (rows 16 (w / 4), columns
+// 32 (w % 4)) of the [64 x 128] results.  out2 may be the matrix A1 lives in: the results are
+// written after the last read of the operands.  All 512 threads call this together; on return the
+// results are visible to every thread and the ring is free.
+template <bool kTwo>
+__device__ __forceinline__ void nn_ring_mma(const float* A1, const float* A2, int pa, const float* __restrict__ Bg,
+                                            float* ring, int tid, float* out1, float* out2, float sign2) {
+  const int warp = tid >> 5, lane = tid & 31;
+  const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 32, g = lane >> 2, t = lane & 3;
+  float c1[4][4], c2[4][4];
 #pragma unroll
-  for (int s = 0; s < kRingStages - 1; ++s) {
-    cp_async16(ring + s * kStageFloats + tid * 4, Bg + s * kStageFloats + tid * 4);
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c1[i][j] = c2[i][j] = 0.0f;
+  const int row = tid >> 5, c4 = tid & 31;   // this thread's 16 bytes of a stage
+  auto issue = [&](int s) {
+    cp_async16(ring + (s % 4) * kMmaStageFloats + row * kMmaRingPitch + c4 * 4, Bg + (s * 16 + row) * kLD + c4 * 4);
+  };
+#pragma unroll
+  for (int s = 0; s < 3; ++s) {
+    issue(s);
     cp_async_commit();
   }
 #pragma unroll 1
-  for (int s = 0; s < kStages; ++s) {
-    cp_async_wait<kRingStages - 2>();
-    __syncthreads();
-    const int ahead = s + kRingStages - 1;
-    if (ahead < kStages)
-      cp_async16(ring + (ahead % kRingStages) * kStageFloats + tid * 4, Bg + ahead * kStageFloats + tid * 4);
+  for (int s = 0; s < kLD / 16; ++s) {
+    cp_async_wait<2>();
+    __syncthreads();   // stage s has landed for every thread; the slot refilled below was read in step s - 1
+    if (s + 3 < kLD / 16) issue(s + 3);
     cp_async_commit();
-    const float* Bs = ring + (s % kRingStages) * kStageFloats;
-#pragma unroll 2
-    for (int k = 0; k < kStageRows; k += 4) {
-      float4 a1[4], a2[4];
+    const float* Bs = ring + (s % 4) * kMmaStageFloats;
+    uint32_t a1h[4], a1l[4], a2h[4], a2l[4];
+    load_a_fragment(A1, pa, m0, s * 16, g, t, a1h, a1l);
+    if (kTwo) load_a_fragment(A2, pa, m0, s * 16, g, t, a2h, a2l);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        a1[i] = lds4(A1 + (l.r0 + i) * pa + s * kStageRows + k);
-        a2[i] = lds4(A2 + (l.r0 + i) * pa + s * kStageRows + k);
-      }
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const float4 bv = lds4(Bs + (k + kk) * kLD + l.c0);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          dense_step(comp(a1[i], kk), bv, pair1[i]);
-          dense_step(comp(a2[i], kk), bv, pair2[i]);
-        }
+    for (int nt = 0; nt < 4; ++nt) {
+      const float* col = Bs + n0 + nt * 8 + g;
+      uint32_t bh0, bl0, bh1, bl1;
+      split_pair(col[(2 * t) * kMmaRingPitch], col[(2 * t + 1) * kMmaRingPitch], bh0, bl0);
+      split_pair(col[(2 * t + 8) * kMmaRingPitch], col[(2 * t + 9) * kMmaRingPitch], bh1, bl1);
+      mma16816(c1[nt], a1h, bh0, bh1);
+      mma16816(c1[nt], a1h, bl0, bl1);
+      mma16816(c1[nt], a1l, bh0, bh1);
+      if (kTwo) {
+        mma16816(c2[nt], a2h, bh0, bh1);
+        mma16816(c2[nt], a2h, bl0, bl1);
+        mma16816(c2[nt], a2l, bh0, bh1);
       }
     }
   }
   cp_async_wait<0>();
-  __syncthreads();
-  from_pairs(pair1, acc1);
-  from_pairs(pair2, acc2);
+  __syncthreads();   // every operand read is done
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int col = n0 + nt * 8 + 2 * t;
+    *reinterpret_cast<float2*>(out1 + (m0 + g) * kLP + col) = make_float2(c1[nt][0], c1[nt][1]);
+    *reinterpret_cast<float2*>(out1 + (m0 + g + 8) * kLP + col) = make_float2(c1[nt][2], c1[nt][3]);
+    if (kTwo) {
+      *reinterpret_cast<float2*>(out2 + (m0 + g) * kLP + col) = make_float2(sign2 * c2[nt][0], sign2 * c2[nt][1]);
+      *reinterpret_cast<float2*>(out2 + (m0 + g + 8) * kLP + col) = make_float2(sign2 * c2[nt][2], sign2 * c2[nt][3]);
+    }
+  }
+  __syncthreads();   // the results are there for every thread
+}
+// out1 = A1 B^T (and out2 = A2 B^T when kTwo) for [64 x K] matrices in shared memory, the same way;
+// warp w owns the 16 x 16 block (rows 16 (w / 4), columns 16 (w % 4)) of the [64 x 64] results, which
+// go to matrices of pitch kLQ.  The caller synchronises before the results are read.
+template <int K, bool kTwo>
+__device__ __forceinline__ void nt_mma(const float* A1, const float* A2, int pa, const float* B, int pb, int tid,
+                                       float* out1, float* out2) {
+  const int warp = tid >> 5, lane = tid & 31;
+  const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 16, g = lane >> 2, t = lane & 3;
+  float c1[2][4], c2[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c1[i][j] = c2[i][j] = 0.0f;
+#pragma unroll 2
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    uint32_t a1h[4], a1l[4], a2h[4], a2l[4];
+    load_a_fragment(A1, pa, m0, k0, g, t, a1h, a1l);
+    if (kTwo) load_a_fragment(A2, pa, m0, k0, g, t, a2h, a2l);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float* rowp = B + (n0 + nt * 8 + g) * pb + k0 + 2 * t;
+      const float2 y0 = *reinterpret_cast<const float2*>(rowp), y1 = *reinterpret_cast<const float2*>(rowp + 8);
+      uint32_t bh0, bl0, bh1, bl1;
+      split_pair(y0.x, y0.y, bh0, bl0);
+      split_pair(y1.x, y1.y, bh1, bl1);
+      mma16816(c1[nt], a1h, bh0, bh1);
+      mma16816(c1[nt], a1h, bl0, bl1);
+      mma16816(c1[nt], a1l, bh0, bh1);
+      if (kTwo) {
+        mma16816(c2[nt], a2h, bh0, bh1);
+        mma16816(c2[nt], a2h, bl0, bl1);
+        mma16816(c2[nt], a2l, bh0, bh1);
+      }
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    const int col = n0 + nt * 8 + 2 * t;
+    *reinterpret_cast<float2*>(out1 + (m0 + g) * kLQ + col) = make_float2(c1[nt][0], c1[nt][1]);
+    *reinterpret_cast<float2*>(out1 + (m0 + g + 8) * kLQ + col) = make_float2(c1[nt][2], c1[nt][3]);
+    if (kTwo) {
+      *reinterpret_cast<float2*>(out2 + (m0 + g) * kLQ + col) = make_float2(c2[nt][0], c2[nt][1]);
+      *reinterpret_cast<float2*>(out2 + (m0 + g + 8) * kLQ + col) = make_float2(c2[nt][2], c2[nt][3]);
+    }
+  }
+}
+// this thread's 4 x 2 tile (strided columns) of a [64 x 64] matrix of pitch kLQ
+__device__ __forceinline__ void load_strided(const float* src, const Lane& l, float (&acc)[4][2]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) acc[i][j] = src[(l.r0 + i) * kLQ + l.cg + 16 * j + 32 * l.ch];
+}
+// this thread's 4 x 4 tile of a [64 x 128] matrix
+__device__ __forceinline__ void load_dense(const float* src, const Lane& l, float (&acc)[4][4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) to_array(lds4(src + (l.r0 + i) * kLP + l.c0), acc[i]);
 }
 
 template <int N>
@@ -386,7 +453,6 @@ __device__ __forceinline__ void store_dense(float* dst, const Lane& l, const flo
   for (int i = 0; i < 4; ++i)
     *reinterpret_cast<float4*>(dst + (l.r0 + i) * kLP + l.c0) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
 }
-__device__ __forceinline__ void to_array(const float4& v, float (&x)[4]) { x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w; }
 
 struct LocalArgs {
   GdnBwdArgs a;
@@ -485,9 +551,10 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   // ---- A (transposed, for the substitution) -> sq[0];  M -> sq[1]
   {
     float g[4][2], hh[4][2];
-    zero(g);
-    zero(hh);
-    nt_smem2<kLD>(Kh, sm.big[1], kLP, Kh, kLP, l, g, hh);
+    nt_mma<kLD, true>(Kh, sm.big[1], kLP, Kh, kLP, tid, sm.big[3], sm.big[4]);   // (big[3], big[4] are still free)
+    __syncthreads();
+    load_strided(sm.big[3], l, g);
+    load_strided(sm.big[4], l, hh);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -554,8 +621,8 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   // ---- U = U' - W S_0 -> big[4]
   {
     float acc[4][4];
-    zero(acc);
-    nn_ring(sm.big[1], kLP, S0, sm.big[2], l, tid, acc);   // (v in big[2] is dead: U' is complete)
+    nn_ring_mma<false>(sm.big[1], nullptr, kLP, S0, sm.big[2], tid, sm.big[4], nullptr, 0.0f);   // (v in big[2] is dead: U' is complete)
+    load_dense(sm.big[4], l, acc);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float4 up = lds4(sm.big[3] + (r0 + i) * kLP + c0);
@@ -585,8 +652,9 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   // ---- dM = mask(dO U^T): M-bar = dM . M into db, dH = dM . ratio -> sq[0]
   {
     float acc[4][2];
-    zero(acc);
-    nt_smem<kLD>(sm.big[2], kLP, sm.big[4], kLP, l, acc);
+    nt_mma<kLD, false>(sm.big[2], nullptr, kLP, sm.big[4], kLP, tid, sm.big[1], nullptr);   // (W in big[1] is dead)
+    __syncthreads();
+    load_strided(sm.big[1], l, acc);
     float rows[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cols[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -622,8 +690,8 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   // ---- dKt = U dS^T (dense columns = keys)
   {
     float acc[4][4];
-    zero(acc);
-    nn_ring(sm.big[4], kLP, dSt, sm.big[3], l, tid, acc);   // (W and U' are dead from here on: big[1], big[3])
+    nn_ring_mma<false>(sm.big[4], nullptr, kLP, dSt, sm.big[3], tid, sm.big[1], nullptr, 0.0f);   // (W and U' are dead from here on: big[1], big[3])
+    load_dense(sm.big[1], l, acc);
     float rows[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -650,7 +718,9 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     zero(acc);
     zero(from_state);
     tn_smem<kLC>(Mm, kLQ, sm.big[2], kLP, l, acc);
-    nn_ring(Kh, kLP, dS, sm.big[3], l, tid, from_state);
+    __syncthreads();   // every thread has its dKt tile out of big[1]
+    nn_ring_mma<false>(Kh, nullptr, kLP, dS, sm.big[3], tid, sm.big[1], nullptr, 0.0f);
+    load_dense(sm.big[1], l, from_state);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float f = gamma / sm.cdec[r0 + i];
@@ -667,15 +737,10 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
     for (int i = 0; i < 4; ++i)
       qraw[i] = r0 + i < count ? load_any4(a.q, (token0 + r0 + i) * a.qk_token + static_cast<size_t>(kh) * kLD + c0, a.in_is_bf16)
                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    float acc[4][4], dw[4][4];
-    zero(acc);
-    zero(dw);
-    nn_ring2(sm.big[2], sm.big[4], kLP, S0t, sm.big[3], l, tid, acc, dw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) dw[i][j] = -dw[i][j];
-    store_dense(sm.big[2], l, dw);
+    float acc[4][4];
+    __syncthreads();   // every thread has its tile of the dU product's state term out of big[1]; dU is stored
+    nn_ring_mma<true>(sm.big[2], sm.big[4], kLP, S0t, sm.big[3], tid, sm.big[1], sm.big[2], -1.0f);
+    load_dense(sm.big[1], l, acc);
     float rows[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
