@@ -427,6 +427,71 @@ __device__ __forceinline__ void nt_mma(const float* A1, const float* A2, int pa,
     }
   }
 }
+// out1 (+)= op(A) diag(sc1) B1  (and out2 = op(A) diag(sc2) B2 when kTwoB) for A [64 x K] (or, kTransA,
+// stored [K x 64]) and B [K x 128] in shared memory; sc: optional factor per k.  Warp blocks and result
+// matrices as nn_ring_mma; kAccumulate adds to what out1 holds.  No barrier inside.
+template <int K, bool kTransA, bool kTwoB, bool kAccumulate>
+__device__ __forceinline__ void nn_mma(const float* A, int pa, const float* B1, const float* sc1, const float* B2,
+                                       const float* sc2, int pb, int tid, float* out1, float* out2) {
+  const int warp = tid >> 5, lane = tid & 31;
+  const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 32, g = lane >> 2, t = lane & 3;
+  float c1[4][4], c2[4][4];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int col = n0 + nt * 8 + 2 * t;
+    float2 lo = make_float2(0.0f, 0.0f), hi = make_float2(0.0f, 0.0f);
+    if (kAccumulate) {
+      lo = *reinterpret_cast<const float2*>(out1 + (m0 + g) * kLP + col);
+      hi = *reinterpret_cast<const float2*>(out1 + (m0 + g + 8) * kLP + col);
+    }
+    c1[nt][0] = lo.x; c1[nt][1] = lo.y; c1[nt][2] = hi.x; c1[nt][3] = hi.y;
+    c2[nt][0] = c2[nt][1] = c2[nt][2] = c2[nt][3] = 0.0f;
+  }
+#pragma unroll 2
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    uint32_t ah[4], al[4];
+    if (kTransA) {
+      const float* colp = A + m0 + g;
+      split_pair(colp[(k0 + 2 * t) * pa], colp[(k0 + 2 * t + 1) * pa], ah[0], al[0]);
+      split_pair(colp[(k0 + 2 * t) * pa + 8], colp[(k0 + 2 * t + 1) * pa + 8], ah[1], al[1]);
+      split_pair(colp[(k0 + 2 * t + 8) * pa], colp[(k0 + 2 * t + 9) * pa], ah[2], al[2]);
+      split_pair(colp[(k0 + 2 * t + 8) * pa + 8], colp[(k0 + 2 * t + 9) * pa + 8], ah[3], al[3]);
+    } else {
+      load_a_fragment(A, pa, m0, k0, g, t, ah, al);
+    }
+    float s1[4] = {1.0f, 1.0f, 1.0f, 1.0f}, s2[4] = {1.0f, 1.0f, 1.0f, 1.0f};   // factors of rows 2t, 2t+1, 2t+8, 2t+9
+    if (sc1 != nullptr) { s1[0] = sc1[k0 + 2 * t]; s1[1] = sc1[k0 + 2 * t + 1]; s1[2] = sc1[k0 + 2 * t + 8]; s1[3] = sc1[k0 + 2 * t + 9]; }
+    if (kTwoB && sc2 != nullptr) { s2[0] = sc2[k0 + 2 * t]; s2[1] = sc2[k0 + 2 * t + 1]; s2[2] = sc2[k0 + 2 * t + 8]; s2[3] = sc2[k0 + 2 * t + 9]; }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const float* col = B1 + k0 * pb + n0 + nt * 8 + g;
+      uint32_t bh0, bl0, bh1, bl1;
+      split_pair(col[(2 * t) * pb] * s1[0], col[(2 * t + 1) * pb] * s1[1], bh0, bl0);
+      split_pair(col[(2 * t + 8) * pb] * s1[2], col[(2 * t + 9) * pb] * s1[3], bh1, bl1);
+      mma16816(c1[nt], ah, bh0, bh1);
+      mma16816(c1[nt], ah, bl0, bl1);
+      mma16816(c1[nt], al, bh0, bh1);
+      if (kTwoB) {
+        const float* col2 = B2 + k0 * pb + n0 + nt * 8 + g;
+        split_pair(col2[(2 * t) * pb] * s2[0], col2[(2 * t + 1) * pb] * s2[1], bh0, bl0);
+        split_pair(col2[(2 * t + 8) * pb] * s2[2], col2[(2 * t + 9) * pb] * s2[3], bh1, bl1);
+        mma16816(c2[nt], ah, bh0, bh1);
+        mma16816(c2[nt], ah, bl0, bl1);
+        mma16816(c2[nt], al, bh0, bh1);
+      }
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int col = n0 + nt * 8 + 2 * t;
+    *reinterpret_cast<float2*>(out1 + (m0 + g) * kLP + col) = make_float2(c1[nt][0], c1[nt][1]);
+    *reinterpret_cast<float2*>(out1 + (m0 + g + 8) * kLP + col) = make_float2(c1[nt][2], c1[nt][3]);
+    if (kTwoB) {
+      *reinterpret_cast<float2*>(out2 + (m0 + g) * kLP + col) = make_float2(c2[nt][0], c2[nt][1]);
+      *reinterpret_cast<float2*>(out2 + (m0 + g + 8) * kLP + col) = make_float2(c2[nt][2], c2[nt][3]);
+    }
+  }
+}
 // this thread's 4 x 2 tile (strided columns) of a [64 x 64] matrix of pitch kLQ
 __device__ __forceinline__ void load_strided(const float* src, const Lane& l, float (&acc)[4][2]) {
 #pragma unroll
@@ -608,15 +673,7 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   const float* Mm = sm.sq[1];
 
   // ---- W = T (beta c . k^) -> big[1] (the queries are read again later);  U' = T (beta . v) -> big[3]
-  {
-    float acc[4][4];
-    zero(acc);
-    nn_smem<kLC>(Tm, kLQ, sm.part[0], Kh, kLP, l, acc);
-    store_dense(sm.big[1], l, acc);
-    zero(acc);
-    nn_smem<kLC>(Tm, kLQ, sm.beta, sm.big[2], kLP, l, acc);
-    store_dense(sm.big[3], l, acc);
-  }
+  nn_mma<kLC, false, true, false>(Tm, kLQ, Kh, sm.part[0], sm.big[2], sm.beta, kLP, tid, sm.big[1], sm.big[3]);
   __syncthreads();
   // ---- U = U' - W S_0 -> big[4]
   {
@@ -715,11 +772,9 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   // ---- dU = M^T dO + Kt dS -> big[4]   (every read of U is done: nn_ring ends with a barrier)
   {
     float acc[4][4], from_state[4][4];
-    zero(acc);
-    zero(from_state);
-    tn_smem<kLC>(Mm, kLQ, sm.big[2], kLP, l, acc);
-    __syncthreads();   // every thread has its dKt tile out of big[1]
-    nn_ring_mma<false>(Kh, nullptr, kLP, dS, sm.big[3], tid, sm.big[1], nullptr, 0.0f);
+    nn_mma<kLC, true, false, false>(Mm, kLQ, sm.big[2], nullptr, nullptr, nullptr, kLP, tid, sm.big[4], nullptr);   // M^T dO (U is dead)
+    nn_ring_mma<false>(Kh, nullptr, kLP, dS, sm.big[3], tid, sm.big[1], nullptr, 0.0f);   // (starts with a barrier: the dKt tiles are out of big[1])
+    load_dense(sm.big[4], l, acc);
     load_dense(sm.big[1], l, from_state);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
