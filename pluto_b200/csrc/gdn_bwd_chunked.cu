@@ -492,6 +492,47 @@ __device__ __forceinline__ void nn_mma(const float* A, int pa, const float* B1, 
     }
   }
 }
+// out (+)= A (diag(f) B)^T with f[n] = fa[n] (* fb[n] when given): row n of B scaled; otherwise as nt_mma.
+template <int K, bool kAccumulate>
+__device__ __forceinline__ void nt_mma_scaled(const float* A, int pa, const float* B, int pb, const float* fa,
+                                              const float* fb, int tid, float* out) {
+  const int warp = tid >> 5, lane = tid & 31;
+  const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 16, g = lane >> 2, t = lane & 3;
+  float c[2][4], f[2];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    const int n = n0 + nt * 8 + g, col = n0 + nt * 8 + 2 * t;
+    f[nt] = fa[n] * (fb != nullptr ? fb[n] : 1.0f);
+    float2 lo = make_float2(0.0f, 0.0f), hi = make_float2(0.0f, 0.0f);
+    if (kAccumulate) {
+      lo = *reinterpret_cast<const float2*>(out + (m0 + g) * kLQ + col);
+      hi = *reinterpret_cast<const float2*>(out + (m0 + g + 8) * kLQ + col);
+    }
+    c[nt][0] = lo.x; c[nt][1] = lo.y; c[nt][2] = hi.x; c[nt][3] = hi.y;
+  }
+#pragma unroll 2
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    uint32_t ah[4], al[4];
+    load_a_fragment(A, pa, m0, k0, g, t, ah, al);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float* rowp = B + (n0 + nt * 8 + g) * pb + k0 + 2 * t;
+      const float2 y0 = *reinterpret_cast<const float2*>(rowp), y1 = *reinterpret_cast<const float2*>(rowp + 8);
+      uint32_t bh0, bl0, bh1, bl1;
+      split_pair(y0.x * f[nt], y0.y * f[nt], bh0, bl0);
+      split_pair(y1.x * f[nt], y1.y * f[nt], bh1, bl1);
+      mma16816(c[nt], ah, bh0, bh1);
+      mma16816(c[nt], ah, bl0, bl1);
+      mma16816(c[nt], al, bh0, bh1);
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    const int col = n0 + nt * 8 + 2 * t;
+    *reinterpret_cast<float2*>(out + (m0 + g) * kLQ + col) = make_float2(c[nt][0], c[nt][1]);
+    *reinterpret_cast<float2*>(out + (m0 + g + 8) * kLQ + col) = make_float2(c[nt][2], c[nt][3]);
+  }
+}
 // this thread's 4 x 2 tile (strided columns) of a [64 x 64] matrix of pitch kLQ
 __device__ __forceinline__ void load_strided(const float* src, const Lane& l, float (&acc)[4][2]) {
 #pragma unroll
@@ -865,28 +906,16 @@ __global__ void __launch_bounds__(kLThreads, 1) gdn_bwd_chunk_local(LocalArgs la
   __syncthreads();
   // ---- dA = -mask(X1 U'^T + X2 W^T) = -mask(R T^T),  R = X1 (beta . v)^T + X2 (beta c . k^)^T: U' and W
   //      need not be kept (v came into big[3] with X1, the barrier after X2 covers it); R -> sq[1] (M is dead)
-  {
-    float from_v[4][2], from_k[4][2];
-    zero(from_v);
-    zero(from_k);
-    nt_smem<kLD>(sm.big[4], kLP, sm.big[3], kLP, l, from_v);
-    nt_smem<kLD>(sm.big[2], kLP, Kh, kLP, l, from_k);
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int s2 = l.cg + 16 * j + 32 * l.ch;
-        sm.sq[1][(r0 + i) * kLQ + s2] = sm.beta[s2] * fmaf(sm.cdec[s2], from_k[i][j], from_v[i][j]);
-      }
-  }
+  nt_mma_scaled<kLD, false>(sm.big[4], kLP, sm.big[3], kLP, sm.beta, nullptr, tid, sm.sq[1]);
+  nt_mma_scaled<kLD, true>(sm.big[2], kLP, Kh, kLP, sm.beta, sm.cdec, tid, sm.sq[1]);   // (same lanes, same elements)
   __syncthreads();
   {
     float acc[4][2], g[4][2];
-    zero(acc);
-    zero(g);
-    nt_smem<kLC>(sm.sq[1], kLQ, Tm, kLQ, l, acc);
-    nt_smem<kLD>(Kh, kLP, Kh, kLP, l, g);
+    nt_mma<kLC, false>(sm.sq[1], nullptr, kLQ, Tm, kLQ, tid, sm.big[3], nullptr);   // R T^T (v and X1 are dead)
+    nt_mma<kLD, false>(Kh, nullptr, kLP, Kh, kLP, tid, sm.big[4], nullptr);        // G once more
     __syncthreads();   // every read of R is done: dG + dG^T goes over it
+    load_strided(sm.big[3], l, acc);
+    load_strided(sm.big[4], l, g);
     float rows_beta[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rows_b[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cols[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < 4; ++i)
