@@ -76,53 +76,18 @@ __device__ __forceinline__ float row_sum16(float v) {
   return v;
 }
 
-// 512 threads = 16 warps.  Warp w covers the column half ch = w & 1 of the row groups 2 (w >> 1) and
-// 2 (w >> 1) + 1 (one per half warp): thread (rg, ch, cg) owns rows rg*4 .. +3 and
-//   "dense"   columns ch*64 + cg*4 .. +3   where the B operand is read along its rows (the 16 lanes
-//             of a row group read 256 contiguous bytes per 16-byte load, the two row groups of a
-//             warp the same ones),
-//   "strided" columns cg + 16 j + 32 ch (j < 2) of a [64 x 64] result whose B operand is read along
-//             k: with row pitches of 132 / 68 floats those lanes fall into different banks too.
-// All products run on two-lane fp32 FMAs.
+// 512 threads = 16 warps.  The epilogues and the short products (64 contraction steps, two-lane
+// fp32 FMAs) use a tile per thread: warp w covers the column half ch = w & 1 of the row groups
+// 2 (w >> 1) and 2 (w >> 1) + 1 (one per half warp); thread (rg, ch, cg) owns rows rg*4 .. +3 and
+//   "dense"   columns ch*64 + cg*4 .. +3 of a [64 x 128] matrix (the 16 lanes of a row group read
+//             256 contiguous bytes per 16-byte load, the two row groups of a warp the same ones),
+//   "strided" columns cg + 16 j + 32 ch (j < 2) of a [64 x 64] matrix (row pitches of 132 / 68
+//             floats keep those lanes in different banks).
+// The long products (128 contraction steps) run on mma.sync in warp blocks of their own and hand
+// their results to these tiles through shared memory.
 struct Lane {
   int rg, ch, cg, r0, c0;   // c0: first dense column
 };
-
-// acc[i][j] += sum_k A[r0+i][k] B[cg+16j+32ch][k]     (A B^T, [64 x 64] result, strided columns)
-template <int K>
-__device__ __forceinline__ void nt_smem(const float* A, int pa, const float* B, int pb, const Lane& l,
-                                        float (&acc)[4][2]) {
-  uint64_t part[4][2];   // (even k, odd k) partial sums of every accumulator
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 2; ++j) part[i][j] = f2_pack(0.0f, 0.0f);
-#pragma unroll 2
-  for (int k = 0; k < K; k += 4) {
-    float4 a[4], b[2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = lds4(A + (l.r0 + i) * pa + k);
-#pragma unroll
-    for (int j = 0; j < 2; ++j) b[j] = lds4(B + (l.cg + 16 * j + 32 * l.ch) * pb + k);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint64_t a01 = f2_pack(a[i].x, a[i].y), a23 = f2_pack(a[i].z, a[i].w);
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        part[i][j] = f2_fma(a01, f2_pack(b[j].x, b[j].y), part[i][j]);
-        part[i][j] = f2_fma(a23, f2_pack(b[j].z, b[j].w), part[i][j]);
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      float lo, hi;
-      f2_unpack(part[i][j], lo, hi);
-      acc[i][j] += lo + hi;
-    }
-}
 
 __device__ __forceinline__ void to_pairs(const float (&acc)[4][4], uint64_t (&pair)[4][2]) {
 #pragma unroll
@@ -143,32 +108,6 @@ __device__ __forceinline__ void dense_step(float av, const float4& bv, uint64_t 
   pair[1] = f2_fma(av2, f2_pack(bv.z, bv.w), pair[1]);
 }
 
-// acc[i][j] += sum_k A[r0+i][k] scale[k] B[k][c0+j]   (A B, [64 x 128] result, dense columns)
-template <int K>
-__device__ __forceinline__ void nn_smem(const float* A, int pa, const float* scale, const float* B, int pb,
-                                        const Lane& l, float (&acc)[4][4]) {
-  uint64_t pair[4][2];
-  to_pairs(acc, pair);
-#pragma unroll 2
-  for (int k = 0; k < K; k += 4) {
-    float4 a[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = lds4(A + (l.r0 + i) * pa + k);
-    if (scale != nullptr) {
-      const float4 s = lds4(scale + k);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { a[i].x *= s.x; a[i].y *= s.y; a[i].z *= s.z; a[i].w *= s.w; }
-    }
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      const float4 bv = lds4(B + (k + kk) * pb + l.c0);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) dense_step(comp(a[i], kk), bv, pair[i]);
-    }
-  }
-  from_pairs(pair, acc);
-}
-
 // acc[i][j] += sum_k A[k][r0+i] B[k][c0+j]       (A^T B, dense columns)
 template <int K>
 __device__ __forceinline__ void tn_smem(const float* A, int pa, const float* B, int pb, const Lane& l,
@@ -186,48 +125,6 @@ __device__ __forceinline__ void tn_smem(const float* A, int pa, const float* B, 
 }
 
 // Pairs of products that share an operand, in one pass (the shared fragments are loaded once):
-// acc1[i][j] += sum_k A1[r0+i][k] B[..][k], acc2 likewise with A2          (two A B^T, strided columns)
-template <int K>
-__device__ __forceinline__ void nt_smem2(const float* A1, const float* A2, int pa, const float* B, int pb,
-                                         const Lane& l, float (&acc1)[4][2], float (&acc2)[4][2]) {
-  uint64_t p1[4][2], p2[4][2];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 2; ++j) p1[i][j] = p2[i][j] = f2_pack(0.0f, 0.0f);
-#pragma unroll 2
-  for (int k = 0; k < K; k += 4) {
-    float4 a1[4], a2[4], b[2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      a1[i] = lds4(A1 + (l.r0 + i) * pa + k);
-      a2[i] = lds4(A2 + (l.r0 + i) * pa + k);
-    }
-#pragma unroll
-    for (int j = 0; j < 2; ++j) b[j] = lds4(B + (l.cg + 16 * j + 32 * l.ch) * pb + k);
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint64_t b01 = f2_pack(b[j].x, b[j].y), b23 = f2_pack(b[j].z, b[j].w);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        p1[i][j] = f2_fma(f2_pack(a1[i].x, a1[i].y), b01, p1[i][j]);
-        p1[i][j] = f2_fma(f2_pack(a1[i].z, a1[i].w), b23, p1[i][j]);
-        p2[i][j] = f2_fma(f2_pack(a2[i].x, a2[i].y), b01, p2[i][j]);
-        p2[i][j] = f2_fma(f2_pack(a2[i].z, a2[i].w), b23, p2[i][j]);
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      float lo, hi;
-      f2_unpack(p1[i][j], lo, hi);
-      acc1[i][j] += lo + hi;
-      f2_unpack(p2[i][j], lo, hi);
-      acc2[i][j] += lo + hi;
-    }
-}
 // acc1 += A1 B, acc2 += A2 B                                                (two A B, dense columns)
 template <int K>
 __device__ __forceinline__ void nn_smem2(const float* A1, const float* A2, int pa, const float* B, int pb,
