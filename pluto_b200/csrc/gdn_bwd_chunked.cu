@@ -6,7 +6,9 @@
 // the tensor cores (gdn_scan_sm100.cu): the forward scan leaves the state S_0 at the start of every
 // chunk, the reverse scan the gradient dS_C at the end of every chunk.  Given those two, a chunk's
 // gradients depend on nothing outside it, and gdn_bwd_chunk_local below computes all chunks in
-// parallel, one CTA per (sequence, head, chunk), in fp32 on the CUDA cores.
+// parallel, one CTA per (sequence, head, chunk), with fp32-level accuracy: its long products on
+// mma.sync with every operand split into a bf16 high part and remainder, the short ones and all
+// element-wise work in fp32 on the CUDA cores.
 //
 // Chunk algebra (t, s index the chunk's tokens; b_t = running sum of log decay, c = exp(b),
 // gamma = c_C; k^, q^ the normalised keys and scaled normalised queries):
