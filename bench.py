@@ -890,7 +890,7 @@ def _gdn_bptt_only(time_ms):
     vn = torch.randn(bb, tt, hh, dd, device="cuda").bfloat16()
     out = _gdn_bptt(time_ms, qn, kn, vn, bb, tt, hh, dd, None, None, None)
     out["gated_delta_net"]["workload"] = "batch 1, 8 heads, d_k = d_v = 128, seq 4096"
-    del out["gated_delta_net"]["recurrence_bwd_fp32_tflops"]
+    del out["gated_delta_net"]["recurrence_bwd_tflops"]
     return out
 
 
@@ -948,9 +948,10 @@ def _gdn_bptt(time_ms, qn, kn, vn, bb, tt, hh, dd, pre_ms, step_ms, graph_ms):
     bptt_ms = time_ms(bptt, steps=3, warmup=2)
     entry = {"workload": "batch 2, 16 heads, d_k = d_v = 128, seq 16384",
              "recurrence_bwd_ms": bptt_ms, "recurrence_bwd_workspace_gb": ws_bytes / 1e9,
-             "recurrence_bwd_note": "chunk-parallel: two tcgen05 scans + one fp32 CTA per 64-token chunk "
-                                    "(about 215 GFLOP of fp32 products)",
-             "recurrence_bwd_fp32_tflops": 215.0e9 / (bptt_ms * 1e-3) / 1e12}
+             "recurrence_bwd_note": "chunk-parallel: two tcgen05 scans + one CTA per 64-token chunk (about 215 GFLOP "
+                                    "of products at fp32-level accuracy: mma.sync on bf16 high part + remainder "
+                                    "for the long ones, fp32 FMAs for the short ones)",
+             "recurrence_bwd_tflops": 215.0e9 / (bptt_ms * 1e-3) / 1e12}
     if pre_ms is not None:
         entry.update({
             "prefill_ms": pre_ms, "prefill_tflops_chunked_count": 94.49e9 / (pre_ms * 1e-3) / 1e12,
