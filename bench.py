@@ -580,10 +580,14 @@ def run_engine(args):
         # with an L2 flush between them, hence against the burst figure
         per_rank_flop = FLOP_PER_STEP / world
         achieved = per_rank_flop / (ms * 1e-3) / 1e12
+        # which kernel the launch plan picks: cut tile pairs + merge when a workspace is in use, whole
+        # pairs from two pairs per SM on, single tiles below that
         pairs_per_sm = shard.q_heads * (SEQ // 256) / 148.0
+        kernel = ("attn_fwd_sm100_pair<128> + attn_fwd_merge<128>" if step_state["workspace"] is not None
+                  else "attn_fwd_sm100_pair<128>" if pairs_per_sm >= 2 else "attn_fwd_sm100<128>")
         line["roofline"] = {
             "bound": "tensor",
-            "kernel": "attn_fwd_sm100_pair<128>" if pairs_per_sm >= 2 else "attn_fwd_sm100<128>",
+            "kernel": kernel,
             "achieved": achieved,
             "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
             "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
@@ -591,8 +595,10 @@ def run_engine(args):
             "algorithmic_flop_per_launch": per_rank_flop,
         }
         if world == 1 and not args.no_extras:
-            line["sustained"] = sustained_leg(ranks, step, peaks)
+            # (the seconds-long leg last: it leaves the GPU hot and power-capped, which would colour the
+            # burst-timed secondary figures)
             line["other_workloads"] = other_workloads(peaks, skip=("decode", "gdn"))
+            line["sustained"] = sustained_leg(ranks, step, peaks)
             cores = os.cpu_count() or 1
             heads = min(Q_HEADS, cores)
             seconds, flop, kind = cpu_reference_sample(4096, heads, cores)
