@@ -20,6 +20,8 @@
 // TMEM budgets (<= 256 columns for head width 64) let two CTAs share an SM, so one CTA's
 // exponentials overlap the other's MMAs.  All copies are tiled TMA loads without multicast; all
 // waits are bounded.
+#include <type_traits>
+
 #include "common.cuh"
 #include "engine.h"
 
@@ -29,7 +31,8 @@ namespace {
 constexpr int kRowTile = 128;   // rows owned by a CTA (TMEM lanes)
 constexpr int kColTile = 64;    // opposite-side rows consumed per step
 constexpr int kBwdStages = 4;
-constexpr int kBwdThreads = 256;
+constexpr int kRowGroups = 2;   // warpgroups of row threads; group g takes columns [32 g, 32 g + 32) of a step
+constexpr int kBwdThreads = 64 + 128 * kRowGroups;   // warp 0 loads, warp 1 issues MMAs, then the row warps
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
@@ -37,8 +40,15 @@ struct BwdParams {
   int group;                  // query heads per key/value head
   int q_col0, k_col0, v_col0; // column of head 0 inside a token row of the q / k / v tensor maps
   float scale, scale_log2;
-  const float4* stats;   // [(b*H+h) * seq_pad + s] = (max*log2e, 1/l, delta, 0); zero past seq
-  int seq_pad;
+  // Row statistics, one float4 per pair of rows: [(b*H+h) * seq_pad/2 + s/2] = (x_even, x_odd,
+  // delta_even, delta_odd) with x = -(max*log2e + log2 l), so that P = exp2(s*scale*log2e + x);
+  // the two-lane arithmetic of the dK/dV pass takes both halves as they lie.  Past the sequence
+  // end x = -1e30 (P = 0) and delta = 0.
+  const float* stats;
+  int seq_pad;   // even
+  const __nv_bfloat16* q;        // query rows as the dQ pass reads them itself: token stride q_token
+  const __nv_bfloat16* d_out16;  // upstream gradient rounded to bf16, [token, head, D]
+  size_t q_token;
   float *dq, *dk, *dv;   // fp32; token strides dq_token / dkv_token elements, head stride D
   size_t dq_token, dkv_token;
   uint32_t* status;
@@ -54,7 +64,7 @@ template <int D>
 __global__ void __launch_bounds__(256)
 attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d_out,  // out may be null
               const float* __restrict__ maxima, const float* __restrict__ normalizers,
-              __nv_bfloat16* __restrict__ d_out_bf16, float4* __restrict__ stats,
+              __nv_bfloat16* __restrict__ d_out_bf16, float* __restrict__ stats,
               float* __restrict__ deltas, int batch, int seq, int seq_pad, int heads) {
   constexpr int kLanes = D / 8;              // lanes per row
   constexpr int kRowsPerWarp = 32 / kLanes;
@@ -95,21 +105,27 @@ attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d
         const size_t stat = (static_cast<size_t>(b) * heads + h) * seq + t;
         if (out != nullptr) deltas[stat] = part;   // otherwise the caller's deltas are the input
         else part = deltas[stat];
-        stats[(static_cast<size_t>(b) * heads + h) * seq_pad + t] =
-            make_float4(maxima[stat] * kLog2e, 1.0f / normalizers[stat], part, 0.0f);
+        // P = exp2(s*scale*log2e + x): the division by l is folded into the exponent
+        float* record = stats + ((static_cast<size_t>(b) * heads + h) * seq_pad + (t & ~1)) * 2 + (t & 1);
+        record[0] = -(maxima[stat] * kLog2e + log2f(normalizers[stat]));
+        record[2] = part;
       }
     }
   }
-  // records of the padding past the sequence end read as zero
+  // records of the padding past the sequence end: probability 0, delta 0
   const int pad = seq_pad - seq;
   const long long n_pad = static_cast<long long>(batch) * heads * pad;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_pad;
-       i += static_cast<long long>(gridDim.x) * blockDim.x)
-    stats[(i / pad) * seq_pad + seq + i % pad] = make_float4(0.f, 0.f, 0.f, 0.f);
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = seq + i % pad;
+    float* record = stats + ((i / pad) * seq_pad + (t & ~1ll)) * 2 + (t & 1);
+    record[0] = -1.0e30f;
+    record[2] = 0.0f;
+  }
 }
 
 struct DqBarriers {
-  uint64_t qdo_full, k_full[kBwdStages], v_full[kBwdStages], kv_empty[kBwdStages];
+  uint64_t rows_ready, k_full[kBwdStages], v_full[kBwdStages], kv_empty[kBwdStages];
   uint64_t s_full[2], ds_full[2], dq_done;
   uint32_t tmem_base;
 };
@@ -119,28 +135,29 @@ struct DqBarriers {
 // ---------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, D == 64 ? 2 : 1)
-attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
-                  const __grid_constant__ CUtensorMap map_k64,
-                  const __grid_constant__ CUtensorMap map_v64,
-                  const __grid_constant__ CUtensorMap map_do128, BwdParams p) {
+attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
+                  const __grid_constant__ CUtensorMap map_v64, BwdParams p) {
   constexpr int kSlabs = D / 64;
-  constexpr int kRowTileBytes = kSlabs * kRowTile * 128;   // [128 x D] bf16
   constexpr int kColTileBytes = kSlabs * kColTile * 128;   // [64 x D] bf16
-  // Head width 128 (one CTA per SM): two (S, dP) buffers of 64 + 64 columns, then dQ; the MMA warp
-  // computes step j+1's S and dP while the row threads turn step j's into dS.  Head width 64: one
-  // buffer and 256 columns, so that two CTAs share an SM and overlap each other instead.
+  // The CTA's own Q and dO rows live in TMEM (D / 2 columns each, two bf16 per column) as the A
+  // operands of S = Q K^T and dP = dO V^T: an A operand in shared memory would be fetched again by
+  // every MMA (4 KB against the 2 KB of a 64-key B operand), and shared-memory bandwidth, not the
+  // tensor pipe, then sets the pace.  Head width 128 (one CTA per SM): then two (S, dP) buffers of
+  // 64 + 64 columns and dQ, 512 columns in all; the MMA warp computes step j+1's S and dP while the
+  // row threads turn step j's into dS.  Head width 64: one buffer and 256 columns, so that two
+  // CTAs share an SM and overlap each other instead.
   constexpr bool kPipe = D == 128;
   constexpr uint32_t kTmemCols = kPipe ? 512 : 256;
-  constexpr uint32_t kColS = 0, kColDP = 64, kBuf = kPipe ? 128 : 0, kColDQ = kPipe ? 256 : 128;
+  constexpr uint32_t kColQ = 0, kColDO = D / 2, kFirstBuf = D;
+  constexpr uint32_t kColS = 0, kColDP = 64, kBuf = kPipe ? 128 : 0;
+  constexpr uint32_t kColDQ = kFirstBuf + (kPipe ? 256 : 128);
   constexpr uint32_t kIdescS = umma_idesc_bf16(kRowTile, kColTile, false);
   constexpr uint32_t kIdescDQ = umma_idesc_bf16(kRowTile, D, true);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* q_smem = smem;
-  uint8_t* do_smem = q_smem + kRowTileBytes;
-  uint8_t* k_smem = do_smem + kRowTileBytes;
+  uint8_t* k_smem = smem;
   uint8_t* v_smem = k_smem + kBwdStages * kColTileBytes;
   DqBarriers* bar = reinterpret_cast<DqBarriers*>(v_smem + kBwdStages * kColTileBytes);
 
@@ -152,7 +169,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
   const int n_steps = min(2 * q_tile + 2, col_tiles);   // key tiles that hold a visible key
 
   if (threadIdx.x == 0) {
-    mbar_init(&bar->qdo_full, 1);
+    mbar_init(&bar->rows_ready, 4 * kRowGroups);
     for (int s = 0; s < kBwdStages; ++s) {
       mbar_init(&bar->k_full[s], 1);
       mbar_init(&bar->v_full[s], 1);
@@ -160,7 +177,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bar->s_full[s], 1);
-      mbar_init(&bar->ds_full[s], 4);   // one arrival per warp
+      mbar_init(&bar->ds_full[s], 4 * kRowGroups);   // one arrival per row warp
     }
     mbar_init(&bar->dq_done, 1);
     mbar_fence_init();
@@ -182,17 +199,8 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&map_q128);
       tma_prefetch_desc(&map_k64);
       tma_prefetch_desc(&map_v64);
-      tma_prefetch_desc(&map_do128);
-      mbar_expect_tx(&bar->qdo_full, 2 * kRowTileBytes);
-      for (int s = 0; s < kSlabs; ++s) {
-        tma_load_3d(q_smem + s * kRowTile * 128, &map_q128, p.q_col0 + head * D + s * 64,
-                    q_tile * kRowTile, batch, &bar->qdo_full);
-        tma_load_3d(do_smem + s * kRowTile * 128, &map_do128, head * D + s * 64, q_tile * kRowTile,
-                    batch, &bar->qdo_full);
-      }
       bool ok = true;
       for (int j = 0; j < n_steps && ok; ++j) {
         const int st = j % kBwdStages, use = j / kBwdStages;
@@ -207,7 +215,6 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
                       p.v_col0 + kv_head * D + s * 64, j * kColTile, batch, &bar->v_full[st]);
         }
       }
-      mbar_wait(&bar->qdo_full, 0, p.status, 51);
       for (int j = max(0, n_steps - kBwdStages); j < n_steps; ++j) {
         mbar_wait(&bar->k_full[j % kBwdStages], (j / kBwdStages) & 1, p.status, 52);
         mbar_wait(&bar->v_full[j % kBwdStages], (j / kBwdStages) & 1, p.status, 53);
@@ -216,9 +223,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
   } else if (warp == 1) {
     {
       // The whole warp walks the schedule (uniform control flow); one elected lane issues.
-      bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->qdo_full, 0, p.status, 54));
-      const uint64_t q_desc = umma_desc_sw128(smem_u32(q_smem), 16, 1024);
-      const uint64_t do_desc = umma_desc_sw128(smem_u32(do_smem), 16, 1024);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->rows_ready, 0, p.status, 54));
       auto issue_scores = [&](int j) -> bool {   // S(j) = Q K_j^T, dP(j) = dO V_j^T into buffer j & 1
         const int st = j % kBwdStages;
         if (!__all_sync(0xffffffffu,
@@ -229,18 +234,16 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
         if (elect_one()) {
           const uint64_t k_desc = umma_desc_sw128(smem_u32(k_smem + st * kColTileBytes), 16, 1024);
           const uint64_t v_desc = umma_desc_sw128(smem_u32(v_smem + st * kColTileBytes), 16, 1024);
-          const uint32_t buf = tmem + (j & 1) * kBuf;
+          const uint32_t buf = tmem + kFirstBuf + (j & 1) * kBuf;
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
+          for (int ks = 0; ks < D / 16; ++ks) {   // 16 channels = 8 TMEM columns of the A operand
             const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
-            umma_ss(buf + kColS, q_desc + a_off, k_desc + b_off, kIdescS, ks > 0);
+            umma_ts(buf + kColS, tmem + kColQ + ks * 8, k_desc + b_off, kIdescS, ks > 0);
           }
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t a_off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
             const uint32_t b_off = ((ks / 4) * kColTile * 128 + (ks % 4) * 32) >> 4;
-            umma_ss(buf + kColDP, do_desc + a_off, v_desc + b_off, kIdescS, ks > 0);
+            umma_ts(buf + kColDP, tmem + kColDO + ks * 8, v_desc + b_off, kIdescS, ks > 0);
           }
           tc_commit(&bar->s_full[j & 1]);
         }
@@ -260,8 +263,8 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
           const uint64_t k_mn = umma_desc_sw128(smem_u32(k_smem + st * kColTileBytes), kColTile * 128, 1024);
 #pragma unroll
           for (int ks = 0; ks < kColTile / 16; ++ks)   // dQ += dS K: 16 keys per step, K MN-major
-            umma_ts(tmem + kColDQ, tmem + (j & 1) * kBuf + kColS + ks * 8, k_mn + ks * (2048 >> 4),
-                    kIdescDQ, j > 0 || ks > 0);
+            umma_ts(tmem + kColDQ, tmem + kFirstBuf + (j & 1) * kBuf + kColS + (ks >> 1) * 32 + (ks & 1) * 8,
+                    k_mn + ks * (2048 >> 4), kIdescDQ, j > 0 || ks > 0);
           tc_commit(&bar->kv_empty[st]);
         }
         __syncwarp();
@@ -270,40 +273,81 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
       if (ok && elect_one()) tc_commit(&bar->dq_done);
       __syncwarp();
     }
-  } else if (warp >= 4) {
-    const int quarter = warp & 3, row = quarter * 32 + lane;
+  } else if (warp >= 2) {
+    // Row threads: TMEM lane quarter = warp % 4; warps 2..5 are group 0, warps 6..9 group 1.
+    const int group = (warp - 2) >> 2, quarter = warp & 3, row = quarter * 32 + lane;
     const int query = q_tile * kRowTile + row;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const float4 st4 = p.stats[(static_cast<size_t>(batch) * p.heads + head) * p.seq_pad +
-                               min(query, p.seq_pad - 1)];
-    const float neg_m = -st4.x, inv_l = st4.y, delta = st4.z;
+    const int stat_row = min(query, p.seq_pad - 1);
+    const float* record = p.stats + ((static_cast<size_t>(batch) * p.heads + head) * p.seq_pad +
+                                     (stat_row & ~1)) * 2 + (stat_row & 1);
+    const float shift = record[0], delta = record[2];
+    // dS here is P (dP - delta) without the softmax scale: dQ is scaled once when it is written.
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
+    const uint64_t shift2 = f2_pack(shift, shift), delta2 = f2_pack(delta, delta);
+    {
+      // group 0 brings the Q rows into TMEM, group 1 the dO rows: one row of D bf16 per thread
+      const __nv_bfloat16* src =
+          group == 0 ? p.q + (static_cast<size_t>(batch) * p.seq + min(query, p.seq - 1)) * p.q_token +
+                           p.q_col0 + head * D
+                     : p.d_out16 + ((static_cast<size_t>(batch) * p.seq + min(query, p.seq - 1)) * p.heads +
+                                    head) * D;
+      const uint32_t dst = tmem + lane_base + (group == 0 ? kColQ : kColDO);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint4 v = *reinterpret_cast<const uint4*>(src + c * 64 + i * 8);
+          if (query >= p.seq) v = make_uint4(0u, 0u, 0u, 0u);
+          w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+        tmem_st32(dst + c * 32, w);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->rows_ready);
+    }
     bool ok = true;
     for (int j = 0; j < n_steps && ok; ++j) {
-      const uint32_t buf = tmem + (j & 1) * kBuf;
+      const uint32_t buf = tmem + kFirstBuf + (j & 1) * kBuf + lane_base + group * 32;
       ok = mbar_wait(&bar->s_full[j & 1], (j >> 1) & 1, p.status, 58);
       if (!ok) break;
       tc_fence_after();
       const bool masked = (j + 1) * kColTile - 1 > q_tile * kRowTile;  // tile may cross the diagonal
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t s[32], dp[32], packed[16];
-        tmem_ld32(buf + lane_base + kColS + half * 32, s);
-        tmem_ld32(buf + lane_base + kColDP + half * 32, dp);
-        tmem_wait_ld();
+      const int key0 = j * kColTile + group * 32;
+      uint32_t s[32], dp[32], packed[16];
+#ifdef BWD_EXP_NOROW
+      if (lane == 0) mbar_arrive(&bar->ds_full[j & 1]);
+      continue;
+#endif
+      tmem_ld32(buf + kColS, s);
+      tmem_ld32(buf + kColDP, dp);
+      tmem_wait_ld();
+      auto build = [&](auto masked_tag) {
+#ifdef BWD_EXP_NOMATH
+        for (int i = 0; i < 16; ++i) packed[i] = s[2 * i] ^ dp[2 * i + 1];
+        return;
+#endif
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int key = j * kColTile + half * 32 + i + e;
-            float pr = fast_exp2(fmaf(__uint_as_float(s[i + e]), p.scale_log2, neg_m)) * inv_l;
-            if (masked && key > query) pr = 0.0f;
-            ds[e] = pr * (__uint_as_float(dp[i + e]) - delta) * p.scale;
+          float p0, p1, d0, d1;
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), scale2, shift2), p0, p1);
+          p0 = fast_exp2(p0);
+          p1 = fast_exp2(p1);
+          if (decltype(masked_tag)::value) {
+            if (key0 + i > query) p0 = 0.0f;
+            if (key0 + i + 1 > query) p1 = 0.0f;
           }
-          packed[i / 2] = pack_bf16(ds[0], ds[1]);
+          const uint64_t t2 = f2_sub(f2_pack(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), delta2);
+          f2_unpack(f2_mul(f2_pack(p0, p1), t2), d0, d1);
+          packed[i / 2] = pack_bf16(d0, d1);
         }
-        tmem_st16(buf + lane_base + kColS + half * 16, packed);
-      }
+      };
+      if (masked) build(std::true_type{});
+      else build(std::false_type{});
+      tmem_st16(buf + kColS, packed);   // over the first half of this group's own S columns
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -314,14 +358,16 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_q128,
       tc_fence_after();
       float* dst = p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = group; c < D / 32; c += kRowGroups) {
         uint32_t o[32];
         tmem_ld32(tmem + lane_base + kColDQ + c * 32, o);
         tmem_wait_ld();
         if (query < p.seq) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+            *reinterpret_cast<float4*>(dst + c * 32 + i) =
+                make_float4(__uint_as_float(o[i]) * p.scale, __uint_as_float(o[i + 1]) * p.scale,
+                            __uint_as_float(o[i + 2]) * p.scale, __uint_as_float(o[i + 3]) * p.scale);
         }
       }
     }
@@ -352,8 +398,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
   constexpr int kSlabs = D / 64;
   constexpr int kRowTileBytes = kSlabs * kRowTile * 128;
   constexpr int kColTileBytes = kSlabs * kColTile * 128;
-  constexpr int kStatsBytes = kColTile * 16;
-  constexpr int kStageBytes = 2 * kColTileBytes + kStatsBytes;   // Q_i, dO_i, stats
+  constexpr int kStatsBytes = kColTile * 8;
+  constexpr int kStageBytes = 2 * kColTileBytes + 1024;   // Q_i, dO_i, stats (tiles stay 1024-byte aligned)
   // as in the dQ kernel: two (S^T, dP^T) buffers for head width 128 (256 + 2 D = 512 columns),
   // one buffer and 256 columns for head width 64
   constexpr bool kPipe = D == 128;
@@ -388,7 +434,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bar->s_full[s], 1);
-      mbar_init(&bar->ds_full[s], 4);   // one arrival per warp
+      mbar_init(&bar->ds_full[s], 4 * kRowGroups);   // one arrival per row warp
     }
     mbar_init(&bar->done, 1);
     mbar_fence_init();
@@ -401,8 +447,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
-  const float4* stats_group =
-      p.stats + (static_cast<size_t>(batch) * p.heads + kv_head * p.group) * p.seq_pad;
+  const float* stats_group =
+      p.stats + (static_cast<size_t>(batch) * p.heads + kv_head * p.group) * p.seq_pad * 2;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -425,7 +471,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
         if (use > 0) ok = mbar_wait(&bar->q_empty[st], (use - 1) & 1, p.status, 60);
         if (!ok) break;
         uint8_t* dst = stage_smem + st * kStageBytes;
-        mbar_expect_tx(&bar->q_full[st], kStageBytes);
+        mbar_expect_tx(&bar->q_full[st], 2 * kColTileBytes + kStatsBytes);
         for (int s = 0; s < kSlabs; ++s) {
           tma_load_3d(dst + s * kColTile * 128, &map_q64, p.q_col0 + head * D + s * 64,
                       tile * kColTile, batch, &bar->q_full[st]);
@@ -433,7 +479,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
                       tile * kColTile, batch, &bar->q_full[st]);
         }
         bulk_load(dst + 2 * kColTileBytes,
-                  stats_group + static_cast<size_t>(in_group) * p.seq_pad + tile * kColTile,
+                  stats_group + (static_cast<size_t>(in_group) * p.seq_pad + tile * kColTile) * 2,
                   kStatsBytes, &bar->q_full[st]);
       }
       mbar_wait(&bar->kv_full, 0, p.status, 61);
@@ -487,10 +533,9 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
           const uint32_t buf = tmem + (i & 1) * kBuf;
 #pragma unroll
           for (int ks = 0; ks < kColTile / 16; ++ks) {   // 16 queries per step, operands MN-major
-            umma_ts(tmem + kColDV, buf + kColS + ks * 8, do_mn + ks * (2048 >> 4), kIdescAcc,
-                    i > 0 || ks > 0);
-            umma_ts(tmem + kColDK, buf + kColDP + ks * 8, q_mn + ks * (2048 >> 4), kIdescAcc,
-                    i > 0 || ks > 0);
+            const uint32_t col = (ks >> 1) * 32 + (ks & 1) * 8;   // where the row group left these 16 queries
+            umma_ts(tmem + kColDV, buf + kColS + col, do_mn + ks * (2048 >> 4), kIdescAcc, i > 0 || ks > 0);
+            umma_ts(tmem + kColDK, buf + kColDP + col, q_mn + ks * (2048 >> 4), kIdescAcc, i > 0 || ks > 0);
           }
           tc_commit(&bar->q_empty[st]);
         }
@@ -500,44 +545,60 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
       if (ok && elect_one()) tc_commit(&bar->done);
       __syncwarp();
     }
-  } else if (warp >= 4) {
-    const int quarter = warp & 3, row = quarter * 32 + lane;
+  } else if (warp >= 2) {
+    const int group = (warp - 2) >> 2, quarter = warp & 3, row = quarter * 32 + lane;
     const int key = k_tile * kRowTile + row;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
     bool ok = true;
     for (int i = 0; i < n_steps && ok; ++i) {
       const int st = i % kBwdStages, tile = first + i % per_head;
-      const uint32_t buf = tmem + (i & 1) * kBuf;
+      const uint32_t buf = tmem + (i & 1) * kBuf + lane_base + group * 32;
       ok = mbar_wait(&bar->s_full[i & 1], (i >> 1) & 1, p.status, 66) &&
            mbar_wait(&bar->q_full[st], (i / kBwdStages) & 1, p.status, 68);  // stats landed (acquire)
       if (!ok) break;
       tc_fence_after();
-      const float4* st4 = reinterpret_cast<const float4*>(stage_smem + st * kStageBytes + 2 * kColTileBytes);
+      const uint32_t pair_stats = smem_u32(stage_smem + st * kStageBytes + 2 * kColTileBytes) + group * 256;
       const bool masked = tile * kColTile < k_tile * kRowTile + kRowTile;  // some query may precede a key
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t s[32], dp[32], pp[16], dsp[16];
-        tmem_ld32(buf + lane_base + kColS + half * 32, s);
-        tmem_ld32(buf + lane_base + kColDP + half * 32, dp);
-        tmem_wait_ld();
+      const int query0 = tile * kColTile + group * 32;
+      uint32_t s[32], dp[32], pp[16], dsp[16];
+#ifdef BWD_EXP_NOROW
+      if (lane == 0) mbar_arrive(&bar->ds_full[i & 1]);
+      continue;
+#endif
+      tmem_ld32(buf + kColS, s);
+      tmem_ld32(buf + kColDP, dp);
+      tmem_wait_ld();
+      // dS^T here is P^T (dP^T - delta) without the softmax scale: dK is scaled once when it is written.
+      auto build = [&](auto masked_tag) {
+#ifdef BWD_EXP_NOMATH
+        for (int c = 0; c < 16; ++c) { pp[c] = s[2 * c] ^ dp[2 * c + 1]; dsp[c] = s[2 * c + 1] ^ dp[2 * c]; }
+        return;
+#endif
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float pr[2], ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float4 q4 = st4[half * 32 + c + e];   // same address for the whole warp
-            const int query = tile * kColTile + half * 32 + c + e;
-            pr[e] = fast_exp2(fmaf(__uint_as_float(s[c + e]), p.scale_log2, -q4.x)) * q4.y;
-            if (masked && query < key) pr[e] = 0.0f;
-            ds[e] = pr[e] * (__uint_as_float(dp[c + e]) - q4.z) * p.scale;
+          const float4 q4 = lds_f32x4(pair_stats + c * 8);   // same address for the whole warp
+          float p0, p1, d0, d1;
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2,
+                           f2_pack(q4.x, q4.y)), p0, p1);
+          p0 = fast_exp2(p0);
+          p1 = fast_exp2(p1);
+          if (decltype(masked_tag)::value) {
+            if (query0 + c < key) p0 = 0.0f;
+            if (query0 + c + 1 < key) p1 = 0.0f;
           }
-          pp[c / 2] = pack_bf16(pr[0], pr[1]);
-          dsp[c / 2] = pack_bf16(ds[0], ds[1]);
+          const uint64_t t2 = f2_sub(f2_pack(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])),
+                                     f2_pack(q4.z, q4.w));
+          f2_unpack(f2_mul(f2_pack(p0, p1), t2), d0, d1);
+          pp[c / 2] = pack_bf16(p0, p1);
+          dsp[c / 2] = pack_bf16(d0, d1);
         }
-        // P^T over the consumed part of S^T, dS^T over the consumed part of dP^T
-        tmem_st16(buf + lane_base + kColS + half * 16, pp);
-        tmem_st16(buf + lane_base + kColDP + half * 16, dsp);
-      }
+      };
+      if (masked) build(std::true_type{});
+      else build(std::false_type{});
+      // P^T and dS^T over the first half of this group's own S^T and dP^T columns
+      tmem_st16(buf + kColS, pp);
+      tmem_st16(buf + kColDP, dsp);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -548,23 +609,24 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
       tc_fence_after();
       const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
+      for (int idx = group; idx < 2 * (D / 32); idx += kRowGroups) {
+        const int which = idx / (D / 32), c = idx % (D / 32);   // 0: dV, 1: dK
+        const float factor = which == 0 ? 1.0f : p.scale;
+        uint32_t o[32];
+        if (n_steps > 0) {
+          tmem_ld32(tmem + lane_base + (which == 0 ? kColDV : kColDK) + c * 32, o);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          if (n_steps > 0) {
-            tmem_ld32(tmem + lane_base + (which == 0 ? kColDV : kColDK) + c * 32, o);
-            tmem_wait_ld();
-          } else {
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (key < p.seq) {
+          float* out = (which == 0 ? p.dv : p.dk) + dst + c * 32;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = 0u;
-          }
-          if (key < p.seq) {
-            float* out = (which == 0 ? p.dv : p.dk) + dst + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<uint4*>(out + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
-          }
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(out + i) =
+                make_float4(__uint_as_float(o[i]) * factor, __uint_as_float(o[i + 1]) * factor,
+                            __uint_as_float(o[i + 2]) * factor, __uint_as_float(o[i + 3]) * factor);
         }
       }
     }
@@ -578,16 +640,15 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
 }
 
 struct BwdMaps {
-  CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64;
+  CUtensorMap q64, k128, k64, v128, v64, do64;
 };
 
 template <int D>
 cudaError_t launch_bwd_tc(cudaStream_t stream, const BwdMaps& m, const BwdParams& p, int batch) {
   constexpr int kSlabs = D / 64;
-  const size_t dq_smem = 1024 + 2 * kSlabs * kRowTile * 128 + 2 * kBwdStages * kSlabs * kColTile * 128 +
-                         sizeof(DqBarriers);
+  const size_t dq_smem = 1024 + 2 * kBwdStages * kSlabs * kColTile * 128 + sizeof(DqBarriers);
   const size_t dkv_smem = 1024 + 2 * kSlabs * kRowTile * 128 +
-                          kBwdStages * (2 * kSlabs * kColTile * 128 + kColTile * 16) + sizeof(DkvBarriers);
+                          kBwdStages * (2 * kSlabs * kColTile * 128 + 1024) + sizeof(DkvBarriers);
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(dq_smem));
   if (e != cudaSuccess) return e;
@@ -605,7 +666,7 @@ cudaError_t launch_bwd_tc(cudaStream_t stream, const BwdMaps& m, const BwdParams
   config.numAttrs = 1;
   config.gridDim = dim3(p.heads * batch, tiles);
   config.dynamicSmemBytes = dq_smem;
-  e = cudaLaunchKernelEx(&config, attn_bwd_dq_sm100<D>, m.q128, m.k64, m.v64, m.do128, p);
+  e = cudaLaunchKernelEx(&config, attn_bwd_dq_sm100<D>, m.k64, m.v64, p);
   if (e != cudaSuccess) return e;
   config.gridDim = dim3((p.heads / p.group) * batch, tiles);
   config.dynamicSmemBytes = dkv_smem;
@@ -626,7 +687,7 @@ cudaError_t gqa_bwd_tc(cudaStream_t stream, const GqaBwdTcArgs& a) {
   const int seq_pad = (a.seq + kColTile - 1) / kColTile * kColTile + kColTile;
   const size_t do_bytes = (static_cast<size_t>(a.batch) * a.seq * E * 2 + 255) / 256 * 256;
   auto* do_bf16 = static_cast<__nv_bfloat16*>(a.workspace);
-  auto* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.workspace) + do_bytes);
+  auto* stats = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + do_bytes);
   {
     const long long n_rows = static_cast<long long>(a.batch) * a.seq * a.q_heads;
     const long long rows_per_cta = 8 * (32 / (D / 8)) * 2;   // 8 warps, two steps each
@@ -638,13 +699,11 @@ cudaError_t gqa_bwd_tc(cudaStream_t stream, const GqaBwdTcArgs& a) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   BwdMaps m;
-  if (!make_token_map(&m.q128, a.q, a.q_cols, a.seq, a.batch, a.q_token, kRowTile) ||
-      !make_token_map(&m.q64, a.q, a.q_cols, a.seq, a.batch, a.q_token, kColTile) ||
+  if (!make_token_map(&m.q64, a.q, a.q_cols, a.seq, a.batch, a.q_token, kColTile) ||
       !make_token_map(&m.k128, a.k, a.kv_cols, a.seq, a.batch, a.kv_token, kRowTile) ||
       !make_token_map(&m.k64, a.k, a.kv_cols, a.seq, a.batch, a.kv_token, kColTile) ||
       !make_token_map(&m.v128, a.v, a.kv_cols, a.seq, a.batch, a.kv_token, kRowTile) ||
       !make_token_map(&m.v64, a.v, a.kv_cols, a.seq, a.batch, a.kv_token, kColTile) ||
-      !make_token_map(&m.do128, do_bf16, E, a.seq, a.batch, E, kRowTile) ||
       !make_token_map(&m.do64, do_bf16, E, a.seq, a.batch, E, kColTile))
     return cudaErrorInvalidValue;
   BwdParams p;
@@ -658,6 +717,9 @@ cudaError_t gqa_bwd_tc(cudaStream_t stream, const GqaBwdTcArgs& a) {
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
   p.scale_log2 = p.scale * kLog2e;
   p.stats = stats;
+  p.q = static_cast<const __nv_bfloat16*>(a.q);
+  p.d_out16 = do_bf16;
+  p.q_token = a.q_token;
   p.seq_pad = seq_pad;
   p.dq = a.dq;
   p.dk = a.dk;
