@@ -45,6 +45,10 @@ struct BwdParams {
   // the two-lane arithmetic of the dK/dV pass takes both halves as they lie.  Past the sequence
   // end x = -1e30 (P = 0) and delta = 0.
   const float* stats;
+  // The same two values as plain arrays, [(b*H+h) * seq_pad + s] each, for the passes that fetch
+  // them at different times.
+  const float* shifts;
+  const float* deltas_pad;
   int seq_pad;   // even
   const __nv_bfloat16* q;        // query rows as the dQ pass reads them itself: token stride q_token
   const __nv_bfloat16* d_out16;  // upstream gradient rounded to bf16, [token, head, D]
@@ -65,6 +69,7 @@ __global__ void __launch_bounds__(256)
 attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d_out,  // out may be null
               const float* __restrict__ maxima, const float* __restrict__ normalizers,
               __nv_bfloat16* __restrict__ d_out_bf16, float* __restrict__ stats,
+              float* __restrict__ shifts, float* __restrict__ deltas_pad,
               float* __restrict__ deltas, int batch, int seq, int seq_pad, int heads) {
   constexpr int kLanes = D / 8;              // lanes per row
   constexpr int kRowsPerWarp = 32 / kLanes;
@@ -107,8 +112,11 @@ attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d
         else part = deltas[stat];
         // P = exp2(s*scale*log2e + x): the division by l is folded into the exponent
         float* record = stats + ((static_cast<size_t>(b) * heads + h) * seq_pad + (t & ~1)) * 2 + (t & 1);
-        record[0] = -(maxima[stat] * kLog2e + log2f(normalizers[stat]));
+        const float shift = -(maxima[stat] * kLog2e + log2f(normalizers[stat]));
+        record[0] = shift;
         record[2] = part;
+        shifts[(static_cast<size_t>(b) * heads + h) * seq_pad + t] = shift;
+        deltas_pad[(static_cast<size_t>(b) * heads + h) * seq_pad + t] = part;
       }
     }
   }
@@ -121,6 +129,8 @@ attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d
     float* record = stats + ((i / pad) * seq_pad + (t & ~1ll)) * 2 + (t & 1);
     record[0] = -1.0e30f;
     record[2] = 0.0f;
+    shifts[(i / pad) * seq_pad + t] = -1.0e30f;
+    deltas_pad[(i / pad) * seq_pad + t] = 0.0f;
   }
 }
 
@@ -377,6 +387,263 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dQ for head width 128 in steps of 128 keys.
+//
+// An MMA of 64 columns takes as long as one of 128 on this tensor pipe, so the passes for head
+// width 128 consume 128 opposite-side rows per step.  All 512 TMEM columns are then in use (Q and
+// dO as A operands 64 + 64, S 128, dP 128, dQ 128) and nothing is double-buffered; the pipe is
+// kept busy by the order of work instead:
+//   row threads, step j    phase 1: S(j) -> registers, release the S columns, P = exp2(...)
+//                          phase 2: dP(j) -> registers, dS = P (dP - delta) over the dP columns
+//   tensor pipe            dQ(j) after phase 2 of step j, then dP(j+1), then S(j+2)
+// so that phase 1 of step j+1 runs beside dQ(j) and dP(j+1), and S(j+2) beside phase 2.
+// Sixteen row warps: group g (warps 2+4g .. 5+4g) takes key columns [32 g, 32 g + 32) of a step.
+// ---------------------------------------------------------------------------------------------
+constexpr int kWideGroups = 4;
+constexpr int kWideThreads = 64 + 128 * kWideGroups;
+constexpr int kWideKStages = 4, kWideVStages = 3;
+constexpr int kWideTileBytes = 2 * kRowTile * 128;   // [128 x 128] bf16, two 64-channel slabs
+
+struct DqWideBarriers {
+  uint64_t rows_ready, k_full[kWideKStages], k_empty[kWideKStages], v_full[kWideVStages], v_empty[kWideVStages];
+  uint64_t s_full, dp_full, s_free, stored, dq_done;
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(kWideThreads, 1)
+attn_bwd_dq128_sm100(const __grid_constant__ CUtensorMap map_k128,
+                     const __grid_constant__ CUtensorMap map_v128, BwdParams p) {
+  constexpr int D = 128;
+  constexpr uint32_t kColQ = 0, kColDO = 64, kColS = 128, kColDP = 256, kColDQ = 384;
+  constexpr uint32_t kIdescS = umma_idesc_bf16(kRowTile, kRowTile, false);
+  constexpr uint32_t kIdescDQ = umma_idesc_bf16(kRowTile, D, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* k_smem = smem;
+  uint8_t* v_smem = k_smem + kWideKStages * kWideTileBytes;
+  DqWideBarriers* bar = reinterpret_cast<DqWideBarriers*>(v_smem + kWideVStages * kWideTileBytes);
+
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  const int q_tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
+  const int kv_head = head / p.group;
+  const int n_steps = min(q_tile + 1, (p.seq + kRowTile - 1) / kRowTile);   // key tiles with a visible key
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->rows_ready, 4 * kWideGroups);
+    for (int s = 0; s < kWideKStages; ++s) {
+      mbar_init(&bar->k_full[s], 1);
+      mbar_init(&bar->k_empty[s], 1);
+    }
+    for (int s = 0; s < kWideVStages; ++s) {
+      mbar_init(&bar->v_full[s], 1);
+      mbar_init(&bar->v_empty[s], 1);
+    }
+    mbar_init(&bar->s_full, 1);
+    mbar_init(&bar->dp_full, 1);
+    mbar_init(&bar->s_free, 4 * kWideGroups);
+    mbar_init(&bar->stored, 4 * kWideGroups);
+    mbar_init(&bar->dq_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  pdl_wait();   // the prep kernel's records and bf16 gradient are read below
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_k128);
+      tma_prefetch_desc(&map_v128);
+      bool ok = true;
+      for (int j = 0; j < n_steps && ok; ++j) {
+        const int ks = j % kWideKStages, vs = j % kWideVStages;
+        if (j >= kWideKStages) ok = mbar_wait(&bar->k_empty[ks], (j / kWideKStages - 1) & 1, p.status, 70);
+        if (!ok) break;
+        mbar_expect_tx(&bar->k_full[ks], kWideTileBytes);
+        for (int s = 0; s < 2; ++s)
+          tma_load_3d(k_smem + ks * kWideTileBytes + s * kRowTile * 128, &map_k128,
+                      p.k_col0 + kv_head * D + s * 64, j * kRowTile, batch, &bar->k_full[ks]);
+        if (j >= kWideVStages) ok = mbar_wait(&bar->v_empty[vs], (j / kWideVStages - 1) & 1, p.status, 71);
+        if (!ok) break;
+        mbar_expect_tx(&bar->v_full[vs], kWideTileBytes);
+        for (int s = 0; s < 2; ++s)
+          tma_load_3d(v_smem + vs * kWideTileBytes + s * kRowTile * 128, &map_v128,
+                      p.v_col0 + kv_head * D + s * 64, j * kRowTile, batch, &bar->v_full[vs]);
+      }
+      // no copy may still be in flight when the CTA leaves
+      for (int j = max(0, n_steps - kWideKStages); j < n_steps; ++j)
+        mbar_wait(&bar->k_full[j % kWideKStages], (j / kWideKStages) & 1, p.status, 72);
+      for (int j = max(0, n_steps - kWideVStages); j < n_steps; ++j)
+        mbar_wait(&bar->v_full[j % kWideVStages], (j / kWideVStages) & 1, p.status, 73);
+    }
+  } else if (warp == 1) {
+    // The whole warp walks the schedule (uniform control flow); one elected lane issues.
+    auto issue_s = [&](int j) -> bool {   // S(j) = Q K_j^T
+      const int st = j % kWideKStages;
+      if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[st], (j / kWideKStages) & 1, p.status, 74))) return false;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t k_desc = umma_desc_sw128(smem_u32(k_smem + st * kWideTileBytes), 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_ts(tmem + kColS, tmem + kColQ + ks * 8,
+                  k_desc + (((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4), kIdescS, ks > 0);
+        tc_commit(&bar->s_full);
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_dp = [&](int j) -> bool {   // dP(j) = dO V_j^T
+      const int st = j % kWideVStages;
+      if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full[st], (j / kWideVStages) & 1, p.status, 75))) return false;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t v_desc = umma_desc_sw128(smem_u32(v_smem + st * kWideTileBytes), 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          umma_ts(tmem + kColDP, tmem + kColDO + ks * 8,
+                  v_desc + (((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4), kIdescS, ks > 0);
+        tc_commit(&bar->dp_full);
+        tc_commit(&bar->v_empty[st]);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->rows_ready, 0, p.status, 76));
+    if (ok) ok = issue_s(0);
+    if (ok) ok = issue_dp(0);
+    if (ok && n_steps > 1) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_free, 0, p.status, 77));
+      if (ok) ok = issue_s(1);
+    }
+    for (int j = 0; j < n_steps && ok; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->stored, j & 1, p.status, 78));
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const int st = j % kWideKStages;
+        const uint64_t k_mn = umma_desc_sw128(smem_u32(k_smem + st * kWideTileBytes), kRowTile * 128, 1024);
+#pragma unroll
+        for (int ks = 0; ks < kRowTile / 16; ++ks)   // dQ += dS K: 16 keys per instruction, K MN-major
+          umma_ts(tmem + kColDQ, tmem + kColDP + (ks >> 1) * 32 + (ks & 1) * 8, k_mn + ks * (2048 >> 4),
+                  kIdescDQ, j > 0 || ks > 0);
+        tc_commit(&bar->k_empty[st]);
+      }
+      __syncwarp();
+      if (j + 1 < n_steps) ok = issue_dp(j + 1);   // the pipe runs in order: dQ(j) has read dS(j) by then
+      if (ok && j + 2 < n_steps) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_free, (j + 1) & 1, p.status, 79));
+        if (ok) ok = issue_s(j + 2);
+      }
+    }
+    if (ok && elect_one()) tc_commit(&bar->dq_done);
+    __syncwarp();
+  } else {
+    const int group = (warp - 2) >> 2, quarter = warp & 3, row = quarter * 32 + lane;
+    const int query = q_tile * kRowTile + row;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const int stat_row = min(query, p.seq_pad - 1);
+    const float* record = p.stats + ((static_cast<size_t>(batch) * p.heads + head) * p.seq_pad +
+                                     (stat_row & ~1)) * 2 + (stat_row & 1);
+    const float shift = record[0], delta = record[2];
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
+    const uint64_t shift2 = f2_pack(shift, shift), delta2 = f2_pack(delta, delta);
+    {
+      // groups 0, 1 bring the two 64-channel halves of the Q rows into TMEM, groups 2, 3 those of dO
+      const size_t token = static_cast<size_t>(batch) * p.seq + min(query, p.seq - 1);
+      const __nv_bfloat16* src = (group < 2 ? p.q + token * p.q_token + p.q_col0 + head * D
+                                            : p.d_out16 + (token * p.heads + head) * D) + (group & 1) * 64;
+      uint32_t w[32];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint4 v = *reinterpret_cast<const uint4*>(src + i * 8);
+        if (query >= p.seq) v = make_uint4(0u, 0u, 0u, 0u);
+        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+      }
+      tmem_st32(tmem + lane_base + (group < 2 ? kColQ : kColDO) + (group & 1) * 32, w);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->rows_ready);
+    }
+    bool ok = true;
+    for (int j = 0; j < n_steps && ok; ++j) {
+      const uint32_t cols = tmem + lane_base + group * 32;
+      const int key0 = j * kRowTile + group * 32;
+      uint32_t s[32], dp[32], packed[16];
+      ok = mbar_wait(&bar->s_full, j & 1, p.status, 80);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld32(cols + kColS, s);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->s_free);
+      const bool masked = j == q_tile;   // the step on the diagonal
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float p0, p1;
+        f2_unpack(f2_fma(f2_pack(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), scale2, shift2), p0, p1);
+        p0 = fast_exp2(p0);
+        p1 = fast_exp2(p1);
+        if (masked) {
+          if (key0 + i > query) p0 = 0.0f;
+          if (key0 + i + 1 > query) p1 = 0.0f;
+        }
+        s[i] = __float_as_uint(p0);
+        s[i + 1] = __float_as_uint(p1);
+      }
+      ok = mbar_wait(&bar->dp_full, j & 1, p.status, 81);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld32(cols + kColDP, dp);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float d0, d1;
+        const uint64_t t2 = f2_sub(f2_pack(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), delta2);
+        f2_unpack(f2_mul(f2_pack(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), t2), d0, d1);
+        packed[i / 2] = pack_bf16(d0, d1);
+      }
+      tmem_st16(cols + kColDP, packed);   // dS over the first half of this group's own dP columns
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->stored);
+    }
+    if (ok) ok = mbar_wait(&bar->dq_done, 0, p.status, 82);
+    if (ok) {
+      tc_fence_after();
+      float* dst = p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D + group * 32;
+      uint32_t o[32];
+      tmem_ld32(tmem + lane_base + kColDQ + group * 32, o);
+      tmem_wait_ld();
+      if (query < p.seq) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(dst + i) =
+              make_float4(__uint_as_float(o[i]) * p.scale, __uint_as_float(o[i + 1]) * p.scale,
+                          __uint_as_float(o[i + 2]) * p.scale, __uint_as_float(o[i + 3]) * p.scale);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
   }
 }
 
@@ -639,8 +906,311 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// dK, dV for head width 128 in steps of 128 queries: grid (key tiles of 128, kv heads, batch).
+//
+// With 64-query steps the S^T and dP^T instructions re-read their 128-row A operand (the K or V
+// tile, 4 KB per instruction) from shared memory for 64 columns of output, and shared-memory
+// bandwidth held them to two thirds of the tensor pipe's rate; 128 columns per instruction halve
+// that traffic.  All 512 TMEM columns are in use (S^T 128, dP^T 128, dV 128, dK 128) with no
+// second buffer, so, as in the wide dQ pass, the order of work keeps the pipe busy:
+//   row threads, step i    phase 1: S^T(i) -> registers, release its columns, P^T = exp2(...)
+//                          phase 2: dP^T(i) -> registers; dS^T and P^T (bf16) over the dP^T columns
+//   tensor pipe            dV(i), dK(i) after phase 2 of step i, then dP^T(i+1), then S^T(i+2)
+// Group g of the sixteen row warps takes query columns [32 g, 32 g + 32) of a step and leaves
+// dS^T in the first 16 and P^T in the last 16 of its own dP^T columns.
+// Shared memory is used to the last kilobyte (K, V, three Q stages, two dO stages, the row
+// statistics: the shifts travel with the Q stages because phase 1 needs them early, the deltas
+// with the dO stages), so there is no slack for aligning the base: a base off the 1024-byte
+// boundary is reported through the status word and the CTA returns.
+// ---------------------------------------------------------------------------------------------
+constexpr int kWideQStages = 3, kWideDoStages = 2;
+constexpr int kWideStatBytes = kRowTile * 4;   // one float per query of a step
+
+struct DkvWideBarriers {
+  uint64_t kv_full, q_full[kWideQStages], q_empty[kWideQStages], do_full[kWideDoStages], do_empty[kWideDoStages];
+  uint64_t s_full, dp_full, s_free, stored, done;
+  uint32_t tmem_base;
+};
+constexpr int kDkvWideSmem = (2 + kWideQStages + kWideDoStages) * kWideTileBytes +
+                             (kWideQStages + kWideDoStages) * kWideStatBytes + 256;
+static_assert(sizeof(DkvWideBarriers) <= 256, "barrier block");
+static_assert(kDkvWideSmem <= 232448, "dynamic shared memory of one CTA");
+
+__global__ void __launch_bounds__(kWideThreads, 1)
+attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
+                      const __grid_constant__ CUtensorMap map_v128,
+                      const __grid_constant__ CUtensorMap map_q128,
+                      const __grid_constant__ CUtensorMap map_do128, BwdParams p) {
+  constexpr int D = 128;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
+  constexpr uint32_t kIdescS = umma_idesc_bf16(kRowTile, kRowTile, false);
+  constexpr uint32_t kIdescAcc = umma_idesc_bf16(kRowTile, D, true);
+
+  extern __shared__ uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {   // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0) report_status(p.status, 83, kBadSmemBase);
+    return;
+  }
+  uint8_t* k_smem = smem;
+  uint8_t* v_smem = k_smem + kWideTileBytes;
+  uint8_t* q_ring = v_smem + kWideTileBytes;
+  uint8_t* do_ring = q_ring + kWideQStages * kWideTileBytes;
+  uint8_t* shift_ring = do_ring + kWideDoStages * kWideTileBytes;
+  uint8_t* delta_ring = shift_ring + kWideQStages * kWideStatBytes;
+  DkvWideBarriers* bar = reinterpret_cast<DkvWideBarriers*>(delta_ring + kWideDoStages * kWideStatBytes);
+
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  const int kv_heads = p.heads / p.group;
+  const int k_tile = blockIdx.y, kv_head = blockIdx.x % kv_heads, batch = blockIdx.x / kv_heads;
+  const int tiles = (p.seq + kRowTile - 1) / kRowTile;
+  const int per_head = tiles - k_tile;        // query tiles that can see these keys
+  const int n_steps = per_head * p.group;     // heads of the group one after the other
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->kv_full, 1);
+    for (int s = 0; s < kWideQStages; ++s) {
+      mbar_init(&bar->q_full[s], 1);
+      mbar_init(&bar->q_empty[s], 1);
+    }
+    for (int s = 0; s < kWideDoStages; ++s) {
+      mbar_init(&bar->do_full[s], 1);
+      mbar_init(&bar->do_empty[s], 1);
+    }
+    mbar_init(&bar->s_full, 1);
+    mbar_init(&bar->dp_full, 1);
+    mbar_init(&bar->s_free, 4 * kWideGroups);
+    mbar_init(&bar->stored, 4 * kWideGroups);
+    mbar_init(&bar->done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bar->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  const size_t stat_group = (static_cast<size_t>(batch) * p.heads + kv_head * p.group) * p.seq_pad;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_k128);
+      tma_prefetch_desc(&map_v128);
+      tma_prefetch_desc(&map_q128);
+      tma_prefetch_desc(&map_do128);
+      mbar_expect_tx(&bar->kv_full, 2 * kWideTileBytes);
+      for (int s = 0; s < 2; ++s) {
+        tma_load_3d(k_smem + s * kRowTile * 128, &map_k128, p.k_col0 + kv_head * D + s * 64,
+                    k_tile * kRowTile, batch, &bar->kv_full);
+        tma_load_3d(v_smem + s * kRowTile * 128, &map_v128, p.v_col0 + kv_head * D + s * 64,
+                    k_tile * kRowTile, batch, &bar->kv_full);
+      }
+      bool ok = true;
+      for (int i = 0; i < n_steps && ok; ++i) {
+        const int qs = i % kWideQStages, ds = i % kWideDoStages;
+        const int in_group = i / per_head, tile = k_tile + i % per_head;
+        const int head = kv_head * p.group + in_group;
+        const size_t stat = stat_group + static_cast<size_t>(in_group) * p.seq_pad + tile * kRowTile;
+        if (i >= kWideQStages) ok = mbar_wait(&bar->q_empty[qs], (i / kWideQStages - 1) & 1, p.status, 84);
+        if (!ok) break;
+        mbar_expect_tx(&bar->q_full[qs], kWideTileBytes + kWideStatBytes);
+        for (int s = 0; s < 2; ++s)
+          tma_load_3d(q_ring + qs * kWideTileBytes + s * kRowTile * 128, &map_q128,
+                      p.q_col0 + head * D + s * 64, tile * kRowTile, batch, &bar->q_full[qs]);
+        bulk_load(shift_ring + qs * kWideStatBytes, p.shifts + stat, kWideStatBytes, &bar->q_full[qs]);
+        if (i >= kWideDoStages) ok = mbar_wait(&bar->do_empty[ds], (i / kWideDoStages - 1) & 1, p.status, 85);
+        if (!ok) break;
+        mbar_expect_tx(&bar->do_full[ds], kWideTileBytes + kWideStatBytes);
+        for (int s = 0; s < 2; ++s)
+          tma_load_3d(do_ring + ds * kWideTileBytes + s * kRowTile * 128, &map_do128, head * D + s * 64,
+                      tile * kRowTile, batch, &bar->do_full[ds]);
+        bulk_load(delta_ring + ds * kWideStatBytes, p.deltas_pad + stat, kWideStatBytes, &bar->do_full[ds]);
+      }
+      // no copy may still be in flight when the CTA leaves
+      mbar_wait(&bar->kv_full, 0, p.status, 86);
+      for (int i = max(0, n_steps - kWideQStages); i < n_steps; ++i)
+        mbar_wait(&bar->q_full[i % kWideQStages], (i / kWideQStages) & 1, p.status, 87);
+      for (int i = max(0, n_steps - kWideDoStages); i < n_steps; ++i)
+        mbar_wait(&bar->do_full[i % kWideDoStages], (i / kWideDoStages) & 1, p.status, 88);
+    }
+  } else if (warp == 1) {
+    const uint64_t k_desc = umma_desc_sw128(smem_u32(k_smem), 16, 1024);
+    const uint64_t v_desc = umma_desc_sw128(smem_u32(v_smem), 16, 1024);
+    auto issue_s = [&](int i) -> bool {   // S^T(i) = K Q_i^T
+      const int st = i % kWideQStages;
+      if (!__all_sync(0xffffffffu, mbar_wait(&bar->q_full[st], (i / kWideQStages) & 1, p.status, 89))) return false;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t q_desc = umma_desc_sw128(smem_u32(q_ring + st * kWideTileBytes), 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
+          umma_ss(tmem + kColS, k_desc + off, q_desc + off, kIdescS, ks > 0);
+        }
+        tc_commit(&bar->s_full);
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_dp = [&](int i) -> bool {   // dP^T(i) = V dO_i^T
+      const int st = i % kWideDoStages;
+      if (!__all_sync(0xffffffffu, mbar_wait(&bar->do_full[st], (i / kWideDoStages) & 1, p.status, 90))) return false;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t do_desc = umma_desc_sw128(smem_u32(do_ring + st * kWideTileBytes), 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = ((ks / 4) * kRowTile * 128 + (ks % 4) * 32) >> 4;
+          umma_ss(tmem + kColDP, v_desc + off, do_desc + off, kIdescS, ks > 0);
+        }
+        tc_commit(&bar->dp_full);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->kv_full, 0, p.status, 91));
+    if (ok && n_steps > 0) ok = issue_s(0);
+    if (ok && n_steps > 0) ok = issue_dp(0);
+    if (ok && n_steps > 1) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_free, 0, p.status, 92));
+      if (ok) ok = issue_s(1);
+    }
+    for (int i = 0; i < n_steps && ok; ++i) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar->stored, i & 1, p.status, 93));
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t do_mn = umma_desc_sw128(smem_u32(do_ring + (i % kWideDoStages) * kWideTileBytes),
+                                               kRowTile * 128, 1024);
+        const uint64_t q_mn = umma_desc_sw128(smem_u32(q_ring + (i % kWideQStages) * kWideTileBytes),
+                                              kRowTile * 128, 1024);
+#pragma unroll
+        for (int ks = 0; ks < kRowTile / 16; ++ks) {   // 16 queries per instruction, operands MN-major
+          const uint32_t col = tmem + kColDP + (ks >> 1) * 32 + (ks & 1) * 8;   // dS^T; P^T 16 columns on
+          umma_ts(tmem + kColDV, col + 16, do_mn + ks * (2048 >> 4), kIdescAcc, i > 0 || ks > 0);
+          umma_ts(tmem + kColDK, col, q_mn + ks * (2048 >> 4), kIdescAcc, i > 0 || ks > 0);
+        }
+        tc_commit(&bar->q_empty[i % kWideQStages]);
+        tc_commit(&bar->do_empty[i % kWideDoStages]);
+      }
+      __syncwarp();
+      if (i + 1 < n_steps) ok = issue_dp(i + 1);   // the pipe runs in order: the products above have read by then
+      if (ok && i + 2 < n_steps) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_free, (i + 1) & 1, p.status, 94));
+        if (ok) ok = issue_s(i + 2);
+      }
+    }
+    if (ok && elect_one()) tc_commit(&bar->done);
+    __syncwarp();
+  } else {
+    const int group = (warp - 2) >> 2, quarter = warp & 3, row = quarter * 32 + lane;
+    const int key = k_tile * kRowTile + row;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t cols = tmem + lane_base + group * 32;
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
+    bool ok = true;
+    for (int i = 0; i < n_steps && ok; ++i) {
+      const int tile = k_tile + i % per_head;
+      const int query0 = tile * kRowTile + group * 32;
+      const bool masked = tile == k_tile;   // the step on the diagonal: a query may precede a key
+      uint32_t s[32], pp[16];
+      ok = mbar_wait(&bar->s_full, i & 1, p.status, 95) &&
+           mbar_wait(&bar->q_full[i % kWideQStages], (i / kWideQStages) & 1, p.status, 96);   // shifts landed
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld32(cols + kColS, s);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->s_free);
+      const uint32_t shifts = smem_u32(shift_ring + (i % kWideQStages) * kWideStatBytes) + group * 128;
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
+        float p0, p1;
+        f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2,
+                         lds_b64(shifts + c * 4)), p0, p1);   // same address for the whole warp
+        p0 = fast_exp2(p0);
+        p1 = fast_exp2(p1);
+        if (masked) {
+          if (query0 + c < key) p0 = 0.0f;
+          if (query0 + c + 1 < key) p1 = 0.0f;
+        }
+        s[c] = __float_as_uint(p0);
+        s[c + 1] = __float_as_uint(p1);
+        pp[c / 2] = pack_bf16(p0, p1);
+      }
+      ok = mbar_wait(&bar->dp_full, i & 1, p.status, 97) &&
+           mbar_wait(&bar->do_full[i % kWideDoStages], (i / kWideDoStages) & 1, p.status, 98);   // deltas landed
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t deltas = smem_u32(delta_ring + (i % kWideDoStages) * kWideStatBytes) + group * 128;
+      // dS^T here is P^T (dP^T - delta) without the softmax scale: dK is scaled once when it is written.
+      uint32_t dp_lo[16], dp_hi[16], ds_lo[8], ds_hi[8];
+      tmem_ld16(cols + kColDP, dp_lo);
+      tmem_ld16(cols + kColDP + 16, dp_hi);
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 16; c += 2) {
+        float d0, d1;
+        const uint64_t t2 = f2_sub(f2_pack(__uint_as_float(dp_lo[c]), __uint_as_float(dp_lo[c + 1])),
+                                   lds_b64(deltas + c * 4));
+        f2_unpack(f2_mul(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), t2), d0, d1);
+        ds_lo[c / 2] = pack_bf16(d0, d1);
+      }
+      tmem_st8(cols + kColDP, ds_lo);
+#pragma unroll
+      for (int c = 0; c < 16; c += 2) {
+        float d0, d1;
+        const uint64_t t2 = f2_sub(f2_pack(__uint_as_float(dp_hi[c]), __uint_as_float(dp_hi[c + 1])),
+                                   lds_b64(deltas + (16 + c) * 4));
+        f2_unpack(f2_mul(f2_pack(__uint_as_float(s[16 + c]), __uint_as_float(s[16 + c + 1])), t2), d0, d1);
+        ds_hi[c / 2] = pack_bf16(d0, d1);
+      }
+      tmem_st8(cols + kColDP + 8, ds_hi);
+      tmem_st16(cols + kColDP + 16, pp);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->stored);
+    }
+    if (ok && n_steps > 0) ok = mbar_wait(&bar->done, 0, p.status, 99);
+    if (ok) {
+      tc_fence_after();
+      const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D + group * 32;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
+        const float factor = which == 0 ? 1.0f : p.scale;
+        uint32_t o[32];
+        if (n_steps > 0) {
+          tmem_ld32(tmem + lane_base + (which == 0 ? kColDV : kColDK) + group * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (key < p.seq) {
+          float* out = (which == 0 ? p.dv : p.dk) + dst;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(out + i) =
+                make_float4(__uint_as_float(o[i]) * factor, __uint_as_float(o[i + 1]) * factor,
+                            __uint_as_float(o[i + 2]) * factor, __uint_as_float(o[i + 3]) * factor);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 struct BwdMaps {
-  CUtensorMap q64, k128, k64, v128, v64, do64;
+  CUtensorMap q128, q64, k128, k64, v128, v64, do128, do64;
 };
 
 template <int D>
@@ -649,11 +1219,20 @@ cudaError_t launch_bwd_tc(cudaStream_t stream, const BwdMaps& m, const BwdParams
   const size_t dq_smem = 1024 + 2 * kBwdStages * kSlabs * kColTile * 128 + sizeof(DqBarriers);
   const size_t dkv_smem = 1024 + 2 * kSlabs * kRowTile * 128 +
                           kBwdStages * (2 * kSlabs * kColTile * 128 + 1024) + sizeof(DkvBarriers);
-  cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(dq_smem));
+  const size_t dq_wide_smem = 1024 + (kWideKStages + kWideVStages) * kWideTileBytes + sizeof(DqWideBarriers);
+  cudaError_t e;
+  if constexpr (D == 128)
+    e = cudaFuncSetAttribute(attn_bwd_dq128_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(dq_wide_smem));
+  else
+    e = cudaFuncSetAttribute(attn_bwd_dq_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(dq_smem));
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(attn_bwd_dkv_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(dkv_smem));
+  if constexpr (D == 128)
+    e = cudaFuncSetAttribute(attn_bwd_dkv128_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvWideSmem);
+  else
+    e = cudaFuncSetAttribute(attn_bwd_dkv_sm100<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(dkv_smem));
   if (e != cudaSuccess) return e;
   const int tiles = (p.seq + kRowTile - 1) / kRowTile;
   cudaLaunchAttribute attribute;
@@ -665,12 +1244,24 @@ cudaError_t launch_bwd_tc(cudaStream_t stream, const BwdMaps& m, const BwdParams
   config.attrs = &attribute;
   config.numAttrs = 1;
   config.gridDim = dim3(p.heads * batch, tiles);
-  config.dynamicSmemBytes = dq_smem;
-  e = cudaLaunchKernelEx(&config, attn_bwd_dq_sm100<D>, m.k64, m.v64, p);
+  if constexpr (D == 128) {
+    config.blockDim = dim3(kWideThreads);
+    config.dynamicSmemBytes = dq_wide_smem;
+    e = cudaLaunchKernelEx(&config, attn_bwd_dq128_sm100, m.k128, m.v128, p);
+  } else {
+    config.dynamicSmemBytes = dq_smem;
+    e = cudaLaunchKernelEx(&config, attn_bwd_dq_sm100<D>, m.k64, m.v64, p);
+  }
   if (e != cudaSuccess) return e;
   config.gridDim = dim3((p.heads / p.group) * batch, tiles);
-  config.dynamicSmemBytes = dkv_smem;
-  return cudaLaunchKernelEx(&config, attn_bwd_dkv_sm100<D>, m.k128, m.v128, m.q64, m.do64, p);
+  if constexpr (D == 128) {
+    config.dynamicSmemBytes = kDkvWideSmem;
+    return cudaLaunchKernelEx(&config, attn_bwd_dkv128_sm100, m.k128, m.v128, m.q128, m.do128, p);
+  } else {
+    config.blockDim = dim3(kBwdThreads);
+    config.dynamicSmemBytes = dkv_smem;
+    return cudaLaunchKernelEx(&config, attn_bwd_dkv_sm100<D>, m.k128, m.v128, m.q64, m.do64, p);
+  }
 }
 
 }  // namespace
@@ -687,19 +1278,26 @@ cudaError_t gqa_bwd_tc(cudaStream_t stream, const GqaBwdTcArgs& a) {
   const int seq_pad = (a.seq + kColTile - 1) / kColTile * kColTile + kColTile;
   const size_t do_bytes = (static_cast<size_t>(a.batch) * a.seq * E * 2 + 255) / 256 * 256;
   auto* do_bf16 = static_cast<__nv_bfloat16*>(a.workspace);
+  // 16 bytes per (sequence, head, padded row): 8 of pair records, then the two plain arrays
   auto* stats = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + do_bytes);
+  const size_t stat_rows = static_cast<size_t>(a.batch) * a.q_heads * seq_pad;
+  float* shifts = stats + 2 * stat_rows;
+  float* deltas_pad = stats + 3 * stat_rows;
   {
     const long long n_rows = static_cast<long long>(a.batch) * a.seq * a.q_heads;
     const long long rows_per_cta = 8 * (32 / (D / 8)) * 2;   // 8 warps, two steps each
     const unsigned blocks = static_cast<unsigned>(std::min<long long>((n_rows + rows_per_cta - 1) / rows_per_cta, 148 * 8));
     auto prep = D == 128 ? attn_bwd_prep<128> : attn_bwd_prep<64>;
     prep<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.out), a.d_out, a.maxima, a.normalizers,
-                                     do_bf16, stats, a.deltas, a.batch, a.seq, seq_pad, a.q_heads);
+                                     do_bf16, stats, shifts, deltas_pad, a.deltas, a.batch, a.seq, seq_pad,
+                                     a.q_heads);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   BwdMaps m;
-  if (!make_token_map(&m.q64, a.q, a.q_cols, a.seq, a.batch, a.q_token, kColTile) ||
+  if (!make_token_map(&m.q128, a.q, a.q_cols, a.seq, a.batch, a.q_token, kRowTile) ||
+      !make_token_map(&m.do128, do_bf16, E, a.seq, a.batch, E, kRowTile) ||
+      !make_token_map(&m.q64, a.q, a.q_cols, a.seq, a.batch, a.q_token, kColTile) ||
       !make_token_map(&m.k128, a.k, a.kv_cols, a.seq, a.batch, a.kv_token, kRowTile) ||
       !make_token_map(&m.k64, a.k, a.kv_cols, a.seq, a.batch, a.kv_token, kColTile) ||
       !make_token_map(&m.v128, a.v, a.kv_cols, a.seq, a.batch, a.kv_token, kRowTile) ||
@@ -717,6 +1315,8 @@ cudaError_t gqa_bwd_tc(cudaStream_t stream, const GqaBwdTcArgs& a) {
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
   p.scale_log2 = p.scale * kLog2e;
   p.stats = stats;
+  p.shifts = shifts;
+  p.deltas_pad = deltas_pad;
   p.q = static_cast<const __nv_bfloat16*>(a.q);
   p.d_out16 = do_bf16;
   p.q_token = a.q_token;
