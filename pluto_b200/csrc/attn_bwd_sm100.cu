@@ -134,8 +134,30 @@ attn_bwd_prep(const __nv_bfloat16* __restrict__ out, const float* __restrict__ d
   }
 }
 
+// One row of a TMA-written [rows x 64 bf16] slab (128-byte swizzle) into 32 registers: the 16-byte
+// chunk c of row r lies at chunk position c ^ (r & 7).
+__device__ __forceinline__ void load_swizzled_row(uint32_t slab, int row, uint32_t (&w)[32]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 v = lds_b32x4(slab + row * 128 + ((c ^ (row & 7)) << 4));
+    w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
+  }
+}
+
+// 32 accumulator columns of one row, scaled, into the row's slot of a staging tile in shared
+// memory.  The tiles leave as one linear bulk copy per row: a thread writing its own row to global
+// memory touches 32 different lines per warp instruction, which cost 4 to 5 us per CTA.
+__device__ __forceinline__ void stage_columns(uint32_t slot, const uint32_t (&o)[32], float factor) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4)
+    sts_b32x4(slot + i * 4, __float_as_uint(__uint_as_float(o[i]) * factor),
+              __float_as_uint(__uint_as_float(o[i + 1]) * factor),
+              __float_as_uint(__uint_as_float(o[i + 2]) * factor),
+              __float_as_uint(__uint_as_float(o[i + 3]) * factor));
+}
+
 struct DqBarriers {
-  uint64_t rows_ready, k_full[kBwdStages], v_full[kBwdStages], kv_empty[kBwdStages];
+  uint64_t qdo_full, rows_ready, k_full[kBwdStages], v_full[kBwdStages], kv_empty[kBwdStages];
   uint64_t s_full[2], ds_full[2], dq_done;
   uint32_t tmem_base;
 };
@@ -146,7 +168,10 @@ struct DqBarriers {
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, D == 64 ? 2 : 1)
 attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
-                  const __grid_constant__ CUtensorMap map_v64, BwdParams p) {
+                  const __grid_constant__ CUtensorMap map_v64,
+                  const __grid_constant__ CUtensorMap map_q128,
+                  const __grid_constant__ CUtensorMap map_do128, BwdParams p) {
+  static_assert(D == 64, "the staging below fits head width 64; head width 128 has its own pass");
   constexpr int kSlabs = D / 64;
   constexpr int kColTileBytes = kSlabs * kColTile * 128;   // [64 x D] bf16
   // The CTA's own Q and dO rows live in TMEM (D / 2 columns each, two bf16 per column) as the A
@@ -179,6 +204,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
   const int n_steps = min(2 * q_tile + 2, col_tiles);   // key tiles that hold a visible key
 
   if (threadIdx.x == 0) {
+    mbar_init(&bar->qdo_full, 1);
     mbar_init(&bar->rows_ready, 4 * kRowGroups);
     for (int s = 0; s < kBwdStages; ++s) {
       mbar_init(&bar->k_full[s], 1);
@@ -211,9 +237,19 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
     if (lane == 0) {
       tma_prefetch_desc(&map_k64);
       tma_prefetch_desc(&map_v64);
+      tma_prefetch_desc(&map_q128);
+      tma_prefetch_desc(&map_do128);
+      // The CTA's Q and dO rows pass through the last two stages of the K and V rings on their way
+      // into TMEM; those stages take key tiles only after the row threads have read them.
+      mbar_expect_tx(&bar->qdo_full, 2 * kRowTile * 128);
+      tma_load_3d(k_smem + 2 * kColTileBytes, &map_q128, p.q_col0 + head * D, q_tile * kRowTile, batch,
+                  &bar->qdo_full);
+      tma_load_3d(v_smem + 2 * kColTileBytes, &map_do128, head * D, q_tile * kRowTile, batch, &bar->qdo_full);
       bool ok = true;
       for (int j = 0; j < n_steps && ok; ++j) {
         const int st = j % kBwdStages, use = j / kBwdStages;
+        if (j == 2) ok = mbar_wait(&bar->rows_ready, 0, p.status, 51);
+        if (!ok) break;
         if (use > 0) ok = mbar_wait(&bar->kv_empty[st], (use - 1) & 1, p.status, 50);
         if (!ok) break;
         mbar_expect_tx(&bar->k_full[st], kColTileBytes);
@@ -297,23 +333,10 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
     const uint64_t shift2 = f2_pack(shift, shift), delta2 = f2_pack(delta, delta);
     {
       // group 0 brings the Q rows into TMEM, group 1 the dO rows: one row of D bf16 per thread
-      const __nv_bfloat16* src =
-          group == 0 ? p.q + (static_cast<size_t>(batch) * p.seq + min(query, p.seq - 1)) * p.q_token +
-                           p.q_col0 + head * D
-                     : p.d_out16 + ((static_cast<size_t>(batch) * p.seq + min(query, p.seq - 1)) * p.heads +
-                                    head) * D;
-      const uint32_t dst = tmem + lane_base + (group == 0 ? kColQ : kColDO);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t w[32];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          uint4 v = *reinterpret_cast<const uint4*>(src + c * 64 + i * 8);
-          if (query >= p.seq) v = make_uint4(0u, 0u, 0u, 0u);
-          w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-        }
-        tmem_st32(dst + c * 32, w);
-      }
+      uint32_t w[32];
+      mbar_wait(&bar->qdo_full, 0, p.status, 53);
+      load_swizzled_row(smem_u32(group == 0 ? k_smem : v_smem) + 2 * kColTileBytes, row, w);
+      tmem_st32(tmem + lane_base + (group == 0 ? kColQ : kColDO), w);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -364,22 +387,24 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
       if (lane == 0) mbar_arrive(&bar->ds_full[j & 1]);
     }
     if (ok) ok = mbar_wait(&bar->dq_done, 0, p.status, 59);
+    // dQ leaves through the K ring (every key tile has been consumed by now): [128 rows x D] fp32
     if (ok) {
       tc_fence_after();
-      float* dst = p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D;
 #pragma unroll
       for (int c = group; c < D / 32; c += kRowGroups) {
         uint32_t o[32];
         tmem_ld32(tmem + lane_base + kColDQ + c * 32, o);
         tmem_wait_ld();
-        if (query < p.seq) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<float4*>(dst + c * 32 + i) =
-                make_float4(__uint_as_float(o[i]) * p.scale, __uint_as_float(o[i + 1]) * p.scale,
-                            __uint_as_float(o[i + 2]) * p.scale, __uint_as_float(o[i + 3]) * p.scale);
-        }
+        stage_columns(smem_u32(k_smem) + row * (D * 4) + c * 128, o, p.scale);
       }
+    }
+    fence_proxy_async();
+    named_barrier_sync(1, 128 * kRowGroups);   // every row thread gets here, whatever `ok` says
+    if (ok && group == 0 && query < p.seq) {
+      bulk_store(p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D,
+                 k_smem + row * (D * 4), D * 4);
+      bulk_store_commit();
+      bulk_store_wait_read();
     }
   }
   tc_fence_before();
@@ -409,14 +434,16 @@ constexpr int kWideKStages = 4, kWideVStages = 3;
 constexpr int kWideTileBytes = 2 * kRowTile * 128;   // [128 x 128] bf16, two 64-channel slabs
 
 struct DqWideBarriers {
-  uint64_t rows_ready, k_full[kWideKStages], k_empty[kWideKStages], v_full[kWideVStages], v_empty[kWideVStages];
+  uint64_t qdo_full, rows_ready, k_full[kWideKStages], k_empty[kWideKStages], v_full[kWideVStages], v_empty[kWideVStages];
   uint64_t s_full, dp_full, s_free, stored, dq_done;
   uint32_t tmem_base;
 };
 
 __global__ void __launch_bounds__(kWideThreads, 1)
 attn_bwd_dq128_sm100(const __grid_constant__ CUtensorMap map_k128,
-                     const __grid_constant__ CUtensorMap map_v128, BwdParams p) {
+                     const __grid_constant__ CUtensorMap map_v128,
+                     const __grid_constant__ CUtensorMap map_q128,
+                     const __grid_constant__ CUtensorMap map_do128, BwdParams p) {
   constexpr int D = 128;
   constexpr uint32_t kColQ = 0, kColDO = 64, kColS = 128, kColDP = 256, kColDQ = 384;
   constexpr uint32_t kIdescS = umma_idesc_bf16(kRowTile, kRowTile, false);
@@ -435,6 +462,7 @@ attn_bwd_dq128_sm100(const __grid_constant__ CUtensorMap map_k128,
   const int n_steps = min(q_tile + 1, (p.seq + kRowTile - 1) / kRowTile);   // key tiles with a visible key
 
   if (threadIdx.x == 0) {
+    mbar_init(&bar->qdo_full, 1);
     mbar_init(&bar->rows_ready, 4 * kWideGroups);
     for (int s = 0; s < kWideKStages; ++s) {
       mbar_init(&bar->k_full[s], 1);
@@ -466,9 +494,22 @@ attn_bwd_dq128_sm100(const __grid_constant__ CUtensorMap map_k128,
     if (lane == 0) {
       tma_prefetch_desc(&map_k128);
       tma_prefetch_desc(&map_v128);
+      tma_prefetch_desc(&map_q128);
+      tma_prefetch_desc(&map_do128);
+      // The CTA's Q and dO rows pass through the last stage of the K and of the V ring on their way
+      // into TMEM; those stages take key tiles only after the row threads have read them.
+      mbar_expect_tx(&bar->qdo_full, 2 * kWideTileBytes);
+      for (int s = 0; s < 2; ++s) {
+        tma_load_3d(k_smem + (kWideKStages - 1) * kWideTileBytes + s * kRowTile * 128, &map_q128,
+                    p.q_col0 + head * D + s * 64, q_tile * kRowTile, batch, &bar->qdo_full);
+        tma_load_3d(v_smem + (kWideVStages - 1) * kWideTileBytes + s * kRowTile * 128, &map_do128,
+                    head * D + s * 64, q_tile * kRowTile, batch, &bar->qdo_full);
+      }
       bool ok = true;
       for (int j = 0; j < n_steps && ok; ++j) {
         const int ks = j % kWideKStages, vs = j % kWideVStages;
+        if (j == kWideVStages - 1) ok = mbar_wait(&bar->rows_ready, 0, p.status, 69);
+        if (!ok) break;
         if (j >= kWideKStages) ok = mbar_wait(&bar->k_empty[ks], (j / kWideKStages - 1) & 1, p.status, 70);
         if (!ok) break;
         mbar_expect_tx(&bar->k_full[ks], kWideTileBytes);
@@ -562,16 +603,11 @@ attn_bwd_dq128_sm100(const __grid_constant__ CUtensorMap map_k128,
     const uint64_t shift2 = f2_pack(shift, shift), delta2 = f2_pack(delta, delta);
     {
       // groups 0, 1 bring the two 64-channel halves of the Q rows into TMEM, groups 2, 3 those of dO
-      const size_t token = static_cast<size_t>(batch) * p.seq + min(query, p.seq - 1);
-      const __nv_bfloat16* src = (group < 2 ? p.q + token * p.q_token + p.q_col0 + head * D
-                                            : p.d_out16 + (token * p.heads + head) * D) + (group & 1) * 64;
       uint32_t w[32];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        uint4 v = *reinterpret_cast<const uint4*>(src + i * 8);
-        if (query >= p.seq) v = make_uint4(0u, 0u, 0u, 0u);
-        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-      }
+      mbar_wait(&bar->qdo_full, 0, p.status, 68);
+      load_swizzled_row(smem_u32(group < 2 ? k_smem + (kWideKStages - 1) * kWideTileBytes
+                                           : v_smem + (kWideVStages - 1) * kWideTileBytes) +
+                            (group & 1) * kRowTile * 128, row, w);
       tmem_st32(tmem + lane_base + (group < 2 ? kColQ : kColDO) + (group & 1) * 32, w);
       tmem_wait_st();
       tc_fence_before();
@@ -624,19 +660,21 @@ attn_bwd_dq128_sm100(const __grid_constant__ CUtensorMap map_k128,
       if (lane == 0) mbar_arrive(&bar->stored);
     }
     if (ok) ok = mbar_wait(&bar->dq_done, 0, p.status, 82);
+    // dQ leaves through the K ring (every key tile has been consumed by now): [128 rows x 128] fp32
     if (ok) {
       tc_fence_after();
-      float* dst = p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D + group * 32;
       uint32_t o[32];
       tmem_ld32(tmem + lane_base + kColDQ + group * 32, o);
       tmem_wait_ld();
-      if (query < p.seq) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          *reinterpret_cast<float4*>(dst + i) =
-              make_float4(__uint_as_float(o[i]) * p.scale, __uint_as_float(o[i + 1]) * p.scale,
-                          __uint_as_float(o[i + 2]) * p.scale, __uint_as_float(o[i + 3]) * p.scale);
-      }
+      stage_columns(smem_u32(k_smem) + row * (D * 4) + group * 128, o, p.scale);
+    }
+    fence_proxy_async();
+    named_barrier_sync(1, 128 * kWideGroups);   // every row thread gets here, whatever `ok` says
+    if (ok && group == 0 && query < p.seq) {
+      bulk_store(p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D,
+                 k_smem + row * (D * 4), D * 4);
+      bulk_store_commit();
+      bulk_store_wait_read();
     }
   }
   tc_fence_before();
@@ -667,6 +705,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
   constexpr int kColTileBytes = kSlabs * kColTile * 128;
   constexpr int kStatsBytes = kColTile * 8;
   constexpr int kStageBytes = 2 * kColTileBytes + 1024;   // Q_i, dO_i, stats (tiles stay 1024-byte aligned)
+  static_assert(D == 64, "the staging below fits head width 64; head width 128 has its own pass");
+  static_assert(kBwdStages * kStageBytes >= 2 * kRowTile * D * 4, "the output tiles are staged in the ring");
   // as in the dQ kernel: two (S^T, dP^T) buffers for head width 128 (256 + 2 D = 512 columns),
   // one buffer and 256 columns for head width 64
   constexpr bool kPipe = D == 128;
@@ -872,13 +912,13 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
       if (lane == 0) mbar_arrive(&bar->ds_full[i & 1]);
     }
     if (ok && n_steps > 0) ok = mbar_wait(&bar->done, 0, p.status, 67);
+    // dV and dK leave through the stage ring (every stage has been consumed by now): two
+    // [128 rows x D] fp32 tiles
     if (ok) {
       tc_fence_after();
-      const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D;
 #pragma unroll
       for (int idx = group; idx < 2 * (D / 32); idx += kRowGroups) {
         const int which = idx / (D / 32), c = idx % (D / 32);   // 0: dV, 1: dK
-        const float factor = which == 0 ? 1.0f : p.scale;
         uint32_t o[32];
         if (n_steps > 0) {
           tmem_ld32(tmem + lane_base + (which == 0 ? kColDV : kColDK) + c * 32, o);
@@ -887,15 +927,17 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
-        if (key < p.seq) {
-          float* out = (which == 0 ? p.dv : p.dk) + dst + c * 32;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<float4*>(out + i) =
-                make_float4(__uint_as_float(o[i]) * factor, __uint_as_float(o[i + 1]) * factor,
-                            __uint_as_float(o[i + 2]) * factor, __uint_as_float(o[i + 3]) * factor);
-        }
+        stage_columns(smem_u32(stage_smem) + which * (kRowTile * D * 4) + row * (D * 4) + c * 128, o,
+                      which == 0 ? 1.0f : p.scale);
       }
+    }
+    fence_proxy_async();
+    named_barrier_sync(1, 128 * kRowGroups);   // every row thread gets here, whatever `ok` says
+    if (ok && key < p.seq && group < 2) {   // group 0 sends the dV rows, group 1 the dK rows
+      const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D;
+      bulk_store((group == 0 ? p.dv : p.dk) + dst, stage_smem + group * (kRowTile * D * 4) + row * (D * 4), D * 4);
+      bulk_store_commit();
+      bulk_store_wait_read();
     }
   }
   tc_fence_before();
@@ -1176,12 +1218,12 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
       if (lane == 0) mbar_arrive(&bar->stored);
     }
     if (ok && n_steps > 0) ok = mbar_wait(&bar->done, 0, p.status, 99);
+    // dV leaves through the Q ring and dK through the dO ring (every stage has been consumed by
+    // now): two [128 rows x 128] fp32 tiles
     if (ok) {
       tc_fence_after();
-      const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D + group * 32;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
-        const float factor = which == 0 ? 1.0f : p.scale;
         uint32_t o[32];
         if (n_steps > 0) {
           tmem_ld32(tmem + lane_base + (which == 0 ? kColDV : kColDK) + group * 32, o);
@@ -1190,15 +1232,17 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
-        if (key < p.seq) {
-          float* out = (which == 0 ? p.dv : p.dk) + dst;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<float4*>(out + i) =
-                make_float4(__uint_as_float(o[i]) * factor, __uint_as_float(o[i + 1]) * factor,
-                            __uint_as_float(o[i + 2]) * factor, __uint_as_float(o[i + 3]) * factor);
-        }
+        stage_columns(smem_u32(which == 0 ? q_ring : do_ring) + row * (D * 4) + group * 128, o,
+                      which == 0 ? 1.0f : p.scale);
       }
+    }
+    fence_proxy_async();
+    named_barrier_sync(1, 128 * kWideGroups);   // every row thread gets here, whatever `ok` says
+    if (ok && key < p.seq && group < 2) {   // group 0 sends the dV rows, group 1 the dK rows
+      const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D;
+      bulk_store((group == 0 ? p.dv : p.dk) + dst, (group == 0 ? q_ring : do_ring) + row * (D * 4), D * 4);
+      bulk_store_commit();
+      bulk_store_wait_read();
     }
   }
   tc_fence_before();
@@ -1247,10 +1291,10 @@ cudaError_t launch_bwd_tc(cudaStream_t stream, const BwdMaps& m, const BwdParams
   if constexpr (D == 128) {
     config.blockDim = dim3(kWideThreads);
     config.dynamicSmemBytes = dq_wide_smem;
-    e = cudaLaunchKernelEx(&config, attn_bwd_dq128_sm100, m.k128, m.v128, p);
+    e = cudaLaunchKernelEx(&config, attn_bwd_dq128_sm100, m.k128, m.v128, m.q128, m.do128, p);
   } else {
     config.dynamicSmemBytes = dq_smem;
-    e = cudaLaunchKernelEx(&config, attn_bwd_dq_sm100<D>, m.k64, m.v64, p);
+    e = cudaLaunchKernelEx(&config, attn_bwd_dq_sm100<D>, m.k64, m.v64, m.q128, m.do128, p);
   }
   if (e != cudaSuccess) return e;
   config.gridDim = dim3((p.heads / p.group) * batch, tiles);

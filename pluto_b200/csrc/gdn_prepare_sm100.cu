@@ -56,17 +56,6 @@ struct PrepSmall {
   uint32_t tmem_base;
 };
 
-// Linear bulk copy shared -> global (both 16-byte aligned, size a multiple of 16); the issuing
-// thread later commits and waits for the group before the shared memory may be reused or freed.
-__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
-               "r"(smem_u32(smem_src)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
 
 // The fp32 scratch holds, per chunk, first A TRANSPOSED ([s][t] with the even rows t before the odd
 // ones: the substitution's two threads per column own the even and the odd rows and read four of
