@@ -146,7 +146,10 @@ __device__ __forceinline__ void load_swizzled_row(uint32_t slab, int row, uint32
 
 // 32 accumulator columns of one row, scaled, into the row's slot of a staging tile in shared
 // memory.  The tiles leave as one linear bulk copy per row: a thread writing its own row to global
-// memory touches 32 different lines per warp instruction, which cost 4 to 5 us per CTA.
+// memory touches 32 different lines per warp instruction, which cost 4 to 5 us per CTA.  Rows
+// are kStagePad bytes apart beyond their length, so that the 16-byte stores of a warp (one row
+// per lane) spread over the banks.
+constexpr int kStagePad = 16;
 __device__ __forceinline__ void stage_columns(uint32_t slot, const uint32_t (&o)[32], float factor) {
 #pragma unroll
   for (int i = 0; i < 32; i += 4)
@@ -387,7 +390,9 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
       if (lane == 0) mbar_arrive(&bar->ds_full[j & 1]);
     }
     if (ok) ok = mbar_wait(&bar->dq_done, 0, p.status, 59);
-    // dQ leaves through the K ring (every key tile has been consumed by now): [128 rows x D] fp32
+    // dQ leaves through the K and V rings, which lie one behind the other (every key tile has been
+    // consumed by now): [128 rows x D] fp32
+    static_assert(2 * kBwdStages * kColTileBytes >= kRowTile * (D * 4 + kStagePad), "staging tile");
     if (ok) {
       tc_fence_after();
 #pragma unroll
@@ -395,14 +400,14 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap map_k64,
         uint32_t o[32];
         tmem_ld32(tmem + lane_base + kColDQ + c * 32, o);
         tmem_wait_ld();
-        stage_columns(smem_u32(k_smem) + row * (D * 4) + c * 128, o, p.scale);
+        stage_columns(smem_u32(k_smem) + row * (D * 4 + kStagePad) + c * 128, o, p.scale);
       }
     }
     fence_proxy_async();
     named_barrier_sync(1, 128 * kRowGroups);   // every row thread gets here, whatever `ok` says
     if (ok && group == 0 && query < p.seq) {
       bulk_store(p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D,
-                 k_smem + row * (D * 4), D * 4);
+                 k_smem + row * (D * 4 + kStagePad), D * 4);
       bulk_store_commit();
       bulk_store_wait_read();
     }
@@ -666,13 +671,13 @@ attn_bwd_dq128_sm100(const __grid_constant__ CUtensorMap map_k128,
       uint32_t o[32];
       tmem_ld32(tmem + lane_base + kColDQ + group * 32, o);
       tmem_wait_ld();
-      stage_columns(smem_u32(k_smem) + row * (D * 4) + group * 128, o, p.scale);
+      stage_columns(smem_u32(k_smem) + row * (D * 4 + kStagePad) + group * 128, o, p.scale);
     }
     fence_proxy_async();
     named_barrier_sync(1, 128 * kWideGroups);   // every row thread gets here, whatever `ok` says
     if (ok && group == 0 && query < p.seq) {
       bulk_store(p.dq + (static_cast<size_t>(batch) * p.seq + query) * p.dq_token + head * D,
-                 k_smem + row * (D * 4), D * 4);
+                 k_smem + row * (D * 4 + kStagePad), D * 4);
       bulk_store_commit();
       bulk_store_wait_read();
     }
@@ -706,7 +711,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
   constexpr int kStatsBytes = kColTile * 8;
   constexpr int kStageBytes = 2 * kColTileBytes + 1024;   // Q_i, dO_i, stats (tiles stay 1024-byte aligned)
   static_assert(D == 64, "the staging below fits head width 64; head width 128 has its own pass");
-  static_assert(kBwdStages * kStageBytes >= 2 * kRowTile * D * 4, "the output tiles are staged in the ring");
+  constexpr int kStageTile = kRowTile * (D * 4 + kStagePad);   // one staged output tile
+  static_assert(kBwdStages * kStageBytes >= 2 * kStageTile, "the output tiles are staged in the ring");
   // as in the dQ kernel: two (S^T, dP^T) buffers for head width 128 (256 + 2 D = 512 columns),
   // one buffer and 256 columns for head width 64
   constexpr bool kPipe = D == 128;
@@ -927,7 +933,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
-        stage_columns(smem_u32(stage_smem) + which * (kRowTile * D * 4) + row * (D * 4) + c * 128, o,
+        stage_columns(smem_u32(stage_smem) + which * kStageTile + row * (D * 4 + kStagePad) + c * 128, o,
                       which == 0 ? 1.0f : p.scale);
       }
     }
@@ -935,7 +941,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap map_k128,
     named_barrier_sync(1, 128 * kRowGroups);   // every row thread gets here, whatever `ok` says
     if (ok && key < p.seq && group < 2) {   // group 0 sends the dV rows, group 1 the dK rows
       const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D;
-      bulk_store((group == 0 ? p.dv : p.dk) + dst, stage_smem + group * (kRowTile * D * 4) + row * (D * 4), D * 4);
+      bulk_store((group == 0 ? p.dv : p.dk) + dst, stage_smem + group * kStageTile + row * (D * 4 + kStagePad),
+                 D * 4);
       bulk_store_commit();
       bulk_store_wait_read();
     }
@@ -1218,8 +1225,10 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
       if (lane == 0) mbar_arrive(&bar->stored);
     }
     if (ok && n_steps > 0) ok = mbar_wait(&bar->done, 0, p.status, 99);
-    // dV leaves through the Q ring and dK through the dO ring (every stage has been consumed by
-    // now): two [128 rows x 128] fp32 tiles
+    // dV and dK leave through the Q and dO rings, which lie one behind the other (every stage has
+    // been consumed by now): two [128 rows x 128] fp32 tiles
+    constexpr int kStageTile = kRowTile * (D * 4 + kStagePad);
+    static_assert((kWideQStages + kWideDoStages) * kWideTileBytes >= 2 * kStageTile, "staging tiles");
     if (ok) {
       tc_fence_after();
 #pragma unroll
@@ -1232,7 +1241,7 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
-        stage_columns(smem_u32(which == 0 ? q_ring : do_ring) + row * (D * 4) + group * 128, o,
+        stage_columns(smem_u32(q_ring) + which * kStageTile + row * (D * 4 + kStagePad) + group * 128, o,
                       which == 0 ? 1.0f : p.scale);
       }
     }
@@ -1240,7 +1249,7 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
     named_barrier_sync(1, 128 * kWideGroups);   // every row thread gets here, whatever `ok` says
     if (ok && key < p.seq && group < 2) {   // group 0 sends the dV rows, group 1 the dK rows
       const size_t dst = (static_cast<size_t>(batch) * p.seq + key) * p.dkv_token + kv_head * D;
-      bulk_store((group == 0 ? p.dv : p.dk) + dst, (group == 0 ? q_ring : do_ring) + row * (D * 4), D * 4);
+      bulk_store((group == 0 ? p.dv : p.dk) + dst, q_ring + group * kStageTile + row * (D * 4 + kStagePad), D * 4);
       bulk_store_commit();
       bulk_store_wait_read();
     }
