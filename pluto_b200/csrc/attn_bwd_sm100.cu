@@ -1056,26 +1056,49 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
         tma_load_3d(v_smem + s * kRowTile * 128, &map_v128, p.v_col0 + kv_head * D + s * 64,
                     k_tile * kRowTile, batch, &bar->kv_full);
       }
+      // The two rings advance independently: each copy starts as soon as its own stage is free.
+      // (Pulling tiles into L2 two steps ahead was measured without effect.)
       bool ok = true;
-      for (int i = 0; i < n_steps && ok; ++i) {
-        const int qs = i % kWideQStages, ds = i % kWideDoStages;
-        const int in_group = i / per_head, tile = k_tile + i % per_head;
-        const int head = kv_head * p.group + in_group;
-        const size_t stat = stat_group + static_cast<size_t>(in_group) * p.seq_pad + tile * kRowTile;
-        if (i >= kWideQStages) ok = mbar_wait(&bar->q_empty[qs], (i / kWideQStages - 1) & 1, p.status, 84);
-        if (!ok) break;
-        mbar_expect_tx(&bar->q_full[qs], kWideTileBytes + kWideStatBytes);
-        for (int s = 0; s < 2; ++s)
-          tma_load_3d(q_ring + qs * kWideTileBytes + s * kRowTile * 128, &map_q128,
-                      p.q_col0 + head * D + s * 64, tile * kRowTile, batch, &bar->q_full[qs]);
-        bulk_load(shift_ring + qs * kWideStatBytes, p.shifts + stat, kWideStatBytes, &bar->q_full[qs]);
-        if (i >= kWideDoStages) ok = mbar_wait(&bar->do_empty[ds], (i / kWideDoStages - 1) & 1, p.status, 85);
-        if (!ok) break;
-        mbar_expect_tx(&bar->do_full[ds], kWideTileBytes + kWideStatBytes);
-        for (int s = 0; s < 2; ++s)
-          tma_load_3d(do_ring + ds * kWideTileBytes + s * kRowTile * 128, &map_do128, head * D + s * 64,
-                      tile * kRowTile, batch, &bar->do_full[ds]);
-        bulk_load(delta_ring + ds * kWideStatBytes, p.deltas_pad + stat, kWideStatBytes, &bar->do_full[ds]);
+      int qi = 0, di = 0;
+      uint32_t spins = 0;
+      const uint64_t start = global_timer_ns();
+      while ((qi < n_steps || di < n_steps) && ok) {
+        bool progress = false;
+        if (qi < n_steps && (qi < kWideQStages ||
+                             mbar_test(&bar->q_empty[qi % kWideQStages], (qi / kWideQStages - 1) & 1))) {
+          const int qs = qi % kWideQStages, in_group = qi / per_head, tile = k_tile + qi % per_head;
+          const int head = kv_head * p.group + in_group;
+          mbar_expect_tx(&bar->q_full[qs], kWideTileBytes + kWideStatBytes);
+          for (int s = 0; s < 2; ++s)
+            tma_load_3d(q_ring + qs * kWideTileBytes + s * kRowTile * 128, &map_q128,
+                        p.q_col0 + head * D + s * 64, tile * kRowTile, batch, &bar->q_full[qs]);
+          bulk_load(shift_ring + qs * kWideStatBytes,
+                    p.shifts + stat_group + static_cast<size_t>(in_group) * p.seq_pad + tile * kRowTile,
+                    kWideStatBytes, &bar->q_full[qs]);
+          ++qi;
+          progress = true;
+        }
+        if (di < n_steps && (di < kWideDoStages ||
+                             mbar_test(&bar->do_empty[di % kWideDoStages], (di / kWideDoStages - 1) & 1))) {
+          const int ds = di % kWideDoStages, in_group = di / per_head, tile = k_tile + di % per_head;
+          const int head = kv_head * p.group + in_group;
+          mbar_expect_tx(&bar->do_full[ds], kWideTileBytes + kWideStatBytes);
+          for (int s = 0; s < 2; ++s)
+            tma_load_3d(do_ring + ds * kWideTileBytes + s * kRowTile * 128, &map_do128, head * D + s * 64,
+                        tile * kRowTile, batch, &bar->do_full[ds]);
+          bulk_load(delta_ring + ds * kWideStatBytes,
+                    p.deltas_pad + stat_group + static_cast<size_t>(in_group) * p.seq_pad + tile * kRowTile,
+                    kWideStatBytes, &bar->do_full[ds]);
+          ++di;
+          progress = true;
+        }
+        if (!progress && (++spins & 0x3ffu) == 0) {   // bounded like every other wait
+          if (*reinterpret_cast<volatile uint32_t*>(p.status) != 0) ok = false;
+          else if (global_timer_ns() - start > kWaitLimitNs) {
+            report_status(p.status, 84, kWaitTimeout);
+            ok = false;
+          }
+        }
       }
       // no copy may still be in flight when the CTA leaves
       mbar_wait(&bar->kv_full, 0, p.status, 86);
@@ -1135,14 +1158,20 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
                                                kRowTile * 128, 1024);
         const uint64_t q_mn = umma_desc_sw128(smem_u32(q_ring + (i % kWideQStages) * kWideTileBytes),
                                               kRowTile * 128, 1024);
+        // 16 queries per instruction, operands MN-major; dS^T starts at `col`, P^T 16 columns on.
+        // dV goes first: the dO ring is the shorter one, and its stage is free after these.
 #pragma unroll
-        for (int ks = 0; ks < kRowTile / 16; ++ks) {   // 16 queries per instruction, operands MN-major
-          const uint32_t col = tmem + kColDP + (ks >> 1) * 32 + (ks & 1) * 8;   // dS^T; P^T 16 columns on
+        for (int ks = 0; ks < kRowTile / 16; ++ks) {
+          const uint32_t col = tmem + kColDP + (ks >> 1) * 32 + (ks & 1) * 8;
           umma_ts(tmem + kColDV, col + 16, do_mn + ks * (2048 >> 4), kIdescAcc, i > 0 || ks > 0);
+        }
+        tc_commit(&bar->do_empty[i % kWideDoStages]);
+#pragma unroll
+        for (int ks = 0; ks < kRowTile / 16; ++ks) {
+          const uint32_t col = tmem + kColDP + (ks >> 1) * 32 + (ks & 1) * 8;
           umma_ts(tmem + kColDK, col, q_mn + ks * (2048 >> 4), kIdescAcc, i > 0 || ks > 0);
         }
         tc_commit(&bar->q_empty[i % kWideQStages]);
-        tc_commit(&bar->do_empty[i % kWideDoStages]);
       }
       __syncwarp();
       if (i + 1 < n_steps) ok = issue_dp(i + 1);   // the pipe runs in order: the products above have read by then
