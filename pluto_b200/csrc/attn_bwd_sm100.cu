@@ -8,18 +8,22 @@
 //     P = exp(s*scale - max) / l,   dP = dO V^T,   dS = P (dP - delta) scale,   delta = sum dO.O
 //     dQ = dS K                     dK = dS^T Q,                                dV = P^T dO
 //
-//   attn_bwd_prep        delta per row (fp32, from the stored O like the reference), the upstream
-//                        gradient rounded to bf16 for the tensor cores, and a padded per-row
-//                        record (max*log2e, 1/l, delta) the other two kernels fetch.
-//   attn_bwd_dq_sm100    one CTA per 128-query tile; per 64-key step: S and dP by tcgen05.mma into
-//                        TMEM, one thread per query row turns them into dS (bf16, written over S in
-//                        TMEM), dQ += dS K with dS as the TMEM operand and K MN-major from smem.
-//   attn_bwd_dkv_sm100   one CTA per 128-key tile; per 64-query step: S^T = K Q^T and dP^T = V dO^T,
-//                        one thread per key row builds P^T and dS^T, then dV += P^T dO and
-//                        dK += dS^T Q.
-// TMEM budgets (<= 256 columns for head width 64) let two CTAs share an SM, so one CTA's
-// exponentials overlap the other's MMAs.  All copies are tiled TMA loads without multicast; all
-// waits are bounded.
+//   attn_bwd_prep          delta per row (fp32, from the stored O like the reference), the upstream
+//                          gradient rounded to bf16 for the tensor cores, and per-row statistics
+//                          x = -(max*log2e + log2 l) (so that P = exp2(s*scale*log2e + x)) and delta.
+//   attn_bwd_dq_sm100      head width 64, one CTA per 128-query tile, two CTAs per SM; per 64-key step:
+//                          S and dP by tcgen05.mma into TMEM (the CTA's Q and dO rows are TMEM A
+//                          operands), the row threads turn them into dS (bf16, written over S in
+//                          TMEM), dQ += dS K with dS as the TMEM operand and K MN-major from smem.
+//   attn_bwd_dkv_sm100     head width 64, one CTA per 128-key tile; per 64-query step: S^T = K Q^T and
+//                          dP^T = V dO^T, the row threads build P^T and dS^T, then dV += P^T dO and
+//                          dK += dS^T Q.
+//   attn_bwd_dq128_sm100,  head width 128 in steps of 128 opposite-side rows (an N64 instruction costs
+//   attn_bwd_dkv128_sm100  more than half an N128 one); all 512 TMEM columns single-buffered, four
+//                          warpgroups of row threads working in two phases; see above each kernel.
+// dS carries no softmax scale: dQ and dK are scaled once when they are written.  The Q/dO rows of a
+// dQ CTA arrive by TMA and every gradient tile leaves as bulk copies of rows staged in shared
+// memory.  All copies are tiled TMA loads without multicast; all waits are bounded.
 #include <type_traits>
 
 #include "common.cuh"
