@@ -667,34 +667,55 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
     const bool any = n_tiles > jb;             // this part holds key blocks of this tile
     if (ok && any) ok = mbar_wait(&bar->pv_done[x], (n_tiles - 1 - jb) & 1, p.status, 22);
     if (parts > 1 && blocks_of[x] > 0) {   // (uniform over the warpgroup: the other branch holds a barrier)
-      if (ok) {
-      // unnormalised partial of this part: accumulator and sums are relative to m_used
-      if (any) tc_fence_after();
+      // Unnormalised partial of this part (accumulator and sums are relative to m_used), staged like
+      // the normalised rows below: fp32 rows go through this tile's query buffer half a row at a
+      // time (16-byte chunk c of row r at chunk position c ^ (r & (chunks - 1))), and the warpgroup
+      // copies each half out with 16 threads per row.
+      constexpr int kRoundCols = kTileBytes / (kBM * 4);   // fp32 columns of a row per round: 64 (D 128) or 32
+      constexpr int kChunks = kRoundCols / 4;              // 16-byte chunks per row and round
+      uint8_t* stage = q_smem + x * kTileBytes;
       const bool live = query < p.seq;
-      const size_t token = static_cast<size_t>(batch) * p.seq + query;
       const size_t tokens = static_cast<size_t>(gridDim.x / p.heads) * p.seq;
-      float* dst = p.part_o + ((static_cast<size_t>(part) * tokens + token) * p.heads + head) * D;
+      float* dst_tile = p.part_o + ((static_cast<size_t>(part) * tokens + static_cast<size_t>(batch) * p.seq +
+                                     static_cast<size_t>(q_tile) * kBM) * p.heads + head) * D;
+      const int t128 = threadIdx.x - (4 + 4 * x) * 32;
+      if (ok && any) tc_fence_after();
+#pragma unroll 1
+      for (int round = 0; round < D / kRoundCols; ++round) {
+        if (ok) {
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        if (any) {
-          tmem_ld32(o_addr + c * 32, o);
-          tmem_wait_ld();
-        } else {
+          for (int c = 0; c < kRoundCols / 32; ++c) {
+            uint32_t o[32];
+            if (any) {
+              tmem_ld32(o_addr + round * kRoundCols + c * 32, o);
+              tmem_wait_ld();
+            } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
+              for (int i = 0; i < 32; ++i) o[i] = 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint4*>(stage + row * (kRoundCols * 4) + (((c * 8 + i) ^ (row & (kChunks - 1))) * 16)) =
+                  make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          }
         }
-        if (live) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+        // all 128 threads of this tile's warpgroup, whatever their waits returned
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");
+        if (ok) {
+#pragma unroll 4
+          for (int e = t128; e < kBM * kChunks; e += 128) {
+            const int r = e / kChunks, piece = e % kChunks;
+            if (q_tile * kBM + r < p.seq)
+              *reinterpret_cast<uint4*>(dst_tile + static_cast<size_t>(r) * p.heads * D + round * kRoundCols + piece * 4) =
+                  *reinterpret_cast<const uint4*>(stage + r * (kRoundCols * 4) + ((piece ^ (r & (kChunks - 1))) * 16));
+          }
         }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");   // the next round reuses the buffer
       }
-      if (live)
+      if (ok && live)
         p.part_m[((static_cast<size_t>(part) * (gridDim.x / p.heads) + batch) * p.heads + head) * p.seq + query] =
             make_float4(any ? m_used * p.scale_log2 : -INFINITY, any ? m_true * p.scale_log2 : -INFINITY,
                         any ? l : 0.0f, 0.0f);
-      }
     } else if (any) {
       // The normalised rows leave through shared memory: each thread writes its row, as bf16, into
       // this tile's query buffer (free: the tile's last Q K^T has completed) in the swizzled slab
