@@ -54,7 +54,10 @@ const char* pluto_last_error(void);
 const char* pluto_build_info(void);
 
 /* Diagnostic: reads (and optionally clears) the device status word that kernels set when one of
- * their bounded waits ran out.  SYNCHRONISES the device.  *value == 0 means healthy. */
+ * their bounded waits ran out.  SYNCHRONISES the device.  *value == 0 means healthy; otherwise
+ * (site << 8) | kind with kind 1 = a bounded wait ran out, 2 = a device-side sequence length lay
+ * outside the declared bound, 3 = a block-table entry lay outside the page pool, 4 = a kernel found
+ * its dynamic shared memory off the boundary it needs (it returns without computing). */
 int pluto_kernel_status(uint32_t* value /* host */, int clear);
 
 /* Diagnostic with no counterpart in the reference: proves on the running GPU that a bounded wait
