@@ -195,7 +195,9 @@ def test_future_tokens_and_other_sequences_cannot_matter(bf16):
     assert np.all(new_g[cut:] == 0.0)
 
 
-@pytest.mark.parametrize("shape", [(300, 2, 128, 2), (1024, 2, 256, 1), (65, 3, 192, 2)])
+@pytest.mark.parametrize("shape", [(300, 2, 128, 2), (1024, 2, 256, 1), (65, 3, 192, 2),
+                                   # head width 128 in one, three and five 128-row steps, several sequences
+                                   (100, 1, 128, 3), (330, 2, 256, 2), (640, 1, 128, 2)])
 def test_tensor_core_backward_matches_exact_backward(shape):
     """bf16, head width 64/128: the tcgen05 backward against the exact fp32 backward kernels on
     the same saved state (max-abs 2e-2), and bit-identical across repeated runs."""
