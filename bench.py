@@ -202,15 +202,23 @@ class Ranks:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
-    def timed(self, fn, steps, warmup, flush=True):
+    def timed(self, fn, steps, warmup, flush=True, hold=True):
         """Mean device time per step in ms: CUDA events around each step, L2 flushed between
-        steps (outside the events), barrier + synchronize either side, max over ranks."""
+        steps (outside the events), barrier + synchronize either side, max over ranks.
+
+        With `hold` the stream is first occupied by a sleep kernel while the host enqueues the
+        steps, so the events bracket device work only: a step of two short launches is otherwise
+        stretched by whatever the host needs between them (measured: 99 against 104 us on an idle
+        host, far more with eight ranks sharing its cores).  Calls that synchronise inside
+        (the end-to-end leg) or meet other ranks (the gather) are timed without it."""
         torch = self.torch
         for _ in range(warmup):
             fn()
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         self.barrier()
+        if hold:
+            torch.cuda._sleep(min(steps * 400_000, 400_000_000))   # ~0.2 ms of device time per step
         for i in range(steps):
             if flush:
                 self.flush.fill_(i & 0xFF)
@@ -274,7 +282,7 @@ def copy_floor_ms(ranks, q_host, k_host, v_host, out_host, steps=5):
                 out_host[:, t0:t0 + count].copy_(out_dev[:, t0:t0 + count], non_blocking=True)
         main.wait_stream(d2h)
 
-    return ranks.timed(step, steps, 2)
+    return ranks.timed(step, steps, 2, hold=False)
 
 
 def decode_leg(ranks, peaks, steps=20, batch=64, capacity=32768):
@@ -436,7 +444,7 @@ def allgather_leg(ranks, prefill_out, decode_out):
         rows, cols = local.shape
         scratch = torch.empty((ranks.world * rows, cols), dtype=local.dtype, device="cuda")
         full = torch.empty((rows, ranks.world * cols), dtype=local.dtype, device="cuda")
-        ms = ranks.timed(lambda: allgather_heads(local, comm=comm, out=full, scratch=scratch), 10, 3)
+        ms = ranks.timed(lambda: allgather_heads(local, comm=comm, out=full, scratch=scratch), 10, 3, hold=False)
         # check: this rank's own columns come back where they belong
         mine = full[:, ranks.rank * cols:(ranks.rank + 1) * cols]
         if not torch.equal(mine, local):
@@ -523,7 +531,7 @@ def run_engine(args):
     with ClockSampler(ranks.local_rank) as sampler:
         time.sleep(0.3)  # let the sampler take its first readings before the timed region
         ms = ranks.timed(step, args.steps, max(args.warmup, 3))
-        e2e_ms = ranks.timed(e2e_step, max(3, min(args.steps, 10)), 3)
+        e2e_ms = ranks.timed(e2e_step, max(3, min(args.steps, 10)), 3, hold=False)
     clocks = sampler.summary()
     status = _capi.kernel_status()
     if status != 0:
@@ -563,6 +571,8 @@ def run_engine(args):
                    "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": HEAD_DIM,
                    "parallelism": f"kv-head shard x{world} (no collective)",
                    "l2": "256 MiB buffer written between timed steps",
+                   "timing": "CUDA events around each step; a sleep kernel holds the stream while the host "
+                             "enqueues the steps, so host launch gaps are outside the events (not for e2e)",
                    "flop_per_step": FLOP_PER_STEP},
         "e2e": {"value": FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
