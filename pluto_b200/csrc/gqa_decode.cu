@@ -102,6 +102,7 @@ gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                                              ~static_cast<uintptr_t>(1023));
   DecodeBarriers* bar = reinterpret_cast<DecodeBarriers*>(smem + kDecodeStages * kStageBytes);
 
+  pdl_launch_dependents();   // the merge may be placed as SMs free up; it waits for this grid itself
   const int split = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
   const int length = bounded_length(a, b, 36);
   const int begin = split * a.split_tokens;
@@ -329,6 +330,7 @@ gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 // token row in flight, each lane owning head_dim/32 (<= 8) channels.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) gqa_decode_generic(DecodeArgs a) {
+  pdl_launch_dependents();
   const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
   const int length = bounded_length(a, b, 37);
   const int begin = split * a.split_tokens;
@@ -410,6 +412,7 @@ constexpr int kMergeThreads = 128;
 constexpr int kMergeSplits = 1024;   // chunk weights held in shared memory per pass
 
 __global__ void __launch_bounds__(kMergeThreads) gqa_decode_merge(DecodeArgs a) {
+  pdl_wait();   // the chunk kernel's partials are complete and visible from here on
   const int head = blockIdx.x, b = blockIdx.y, D = a.head_dim;
   const int length = bounded_length(a, b, 38);
   const int splits = (length + a.split_tokens - 1) / a.split_tokens;   // <= a.splits
@@ -611,8 +614,18 @@ cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
-  gqa_decode_merge<<<dim3(a.q_heads, a.batch), kMergeThreads, 0, stream>>>(a);
-  return cudaGetLastError();
+  // The merge is launched with programmatic stream serialisation: its CTAs are placed while the
+  // chunk kernel's last CTAs still run, and wait for that grid before they read a partial.
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(a.q_heads, a.batch);
+  config.blockDim = dim3(kMergeThreads);
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, gqa_decode_merge, a);
 }
 
 cudaError_t gqa_decode_probabilities(cudaStream_t stream, const DecodeArgs& a, float* probs,
