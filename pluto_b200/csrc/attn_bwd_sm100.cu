@@ -1069,7 +1069,7 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
       while ((qi < n_steps || di < n_steps) && ok) {
         bool progress = false;
         if (qi < n_steps && (qi < kWideQStages ||
-                             mbar_test(&bar->q_empty[qi % kWideQStages], (qi / kWideQStages - 1) & 1))) {
+                             mbar_poll(&bar->q_empty[qi % kWideQStages], (qi / kWideQStages - 1) & 1))) {
           const int qs = qi % kWideQStages, in_group = qi / per_head, tile = k_tile + qi % per_head;
           const int head = kv_head * p.group + in_group;
           mbar_expect_tx(&bar->q_full[qs], kWideTileBytes + kWideStatBytes);
@@ -1083,7 +1083,7 @@ attn_bwd_dkv128_sm100(const __grid_constant__ CUtensorMap map_k128,
           progress = true;
         }
         if (di < n_steps && (di < kWideDoStages ||
-                             mbar_test(&bar->do_empty[di % kWideDoStages], (di / kWideDoStages - 1) & 1))) {
+                             mbar_poll(&bar->do_empty[di % kWideDoStages], (di / kWideDoStages - 1) & 1))) {
           const int ds = di % kWideDoStages, in_group = di / per_head, tile = k_tile + di % per_head;
           const int head = kv_head * p.group + in_group;
           mbar_expect_tx(&bar->do_full[ds], kWideTileBytes + kWideStatBytes);

@@ -66,6 +66,20 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-suspending form of the test (try_wait may park the thread for a while before it answers):
+// for a thread that polls several barriers in turn.
+__device__ __forceinline__ bool mbar_poll(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Default time limit for any single wait: far above any legitimate kernel duration here
 // (milliseconds), far below a watchdog.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
