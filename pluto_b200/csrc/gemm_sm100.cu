@@ -238,6 +238,249 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same product on pairs of SMs: a cluster of two CTAs owns a 256 x 256 output tile and issues
+// tcgen05.mma.cta_group::2 (M 256, N 256, K 16).  Each CTA stages its own 128 rows of A and its own
+// 128 columns of B (16 KB + 16 KB per K step of 64 instead of 16 KB + 32 KB), so a CTA pulls a third
+// less through L2 and its shared memory per MMA cycle; every CTA keeps the 256 accumulator columns
+// of its 128 rows in its own TMEM and drains them itself.  All loads are plain tiled TMA loads (no
+// multicast); CTA 1's loads complete on CTA 0's `full` barrier, the MMA warp of CTA 0 issues for
+// both and its commits arrive on both CTAs' barriers.
+// ------------------------------------------------------------------------------------------------
+constexpr int kPairTile = 256, kPairStages = 6;
+constexpr int kPairABytes = kTile * kBK * 2;   // 16 KB: this CTA's 128 rows of A
+constexpr int kPairBBytes = kTile * kBK * 2;   // 16 KB: this CTA's 128 columns of B
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu; // clears the CTA-of-the-pair bit of a shared::cluster address
+
+struct PairGemmBarriers {
+  uint64_t full[kPairStages], empty[kPairStages], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+};
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Tiled TMA load of the CTA's own operand part; the bytes are counted on the barrier at `mbar_addr`,
+// a shared::cluster address (CTA 0's barrier for both CTAs of the pair).
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                                 uint32_t mbar_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(map), "r"(mbar_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair once every MMA
+// issued so far has completed.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t mbar_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(mbar_addr) : "memory");
+}
+
+constexpr uint32_t gemm_idesc_pair(int format, bool a_mn, bool b_mn) {
+  return (1u << 4) | (static_cast<uint32_t>(format) << 7) | (static_cast<uint32_t>(format) << 10) |
+         (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
+         (static_cast<uint32_t>(kPairTile >> 3) << 17) | (static_cast<uint32_t>(kPairTile >> 4) << 24);
+}
+
+__device__ __forceinline__ void pair_tile_origin(int tile, int m_tiles, int n_tiles, int& m0, int& n0) {
+  const int band = tile / (kBand * m_tiles);
+  const int width = min(kBand, n_tiles - band * kBand);
+  const int within = tile - band * kBand * m_tiles;
+  m0 = (within / width) * kPairTile;
+  n0 = (band * kBand + within % width) * kPairTile;
+}
+
+// map_b: for K-major B a box of 128 n-rows, for MN-major B the 64 x 64 slab box.  p.idesc is unused
+// here (pair_idesc carries M = 256).
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_sm100_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                GemmParams p, uint32_t pair_idesc) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* a_smem = smem;
+  uint8_t* b_smem = smem + kPairStages * kPairABytes;
+  PairGemmBarriers* bar = reinterpret_cast<PairGemmBarriers*>(b_smem + kPairStages * kPairBBytes);
+  const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
+  const int rank = static_cast<int>(cluster_cta_rank());   // 0 issues the MMAs
+  const int cluster = blockIdx.x / 2, clusters = gridDim.x / 2;
+  const int m_tiles = (p.M + kPairTile - 1) / kPairTile, n_tiles = (p.N + kPairTile - 1) / kPairTile;
+  const int tiles = m_tiles * n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&bar->full[s], 1);
+      mbar_init(&bar->empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar->acc_full[s], 1);
+      mbar_init(&bar->acc_empty[s], 8);   // one arrival per epilogue warp of both CTAs (used in CTA 0)
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {   // the same warp of both CTAs, together
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
+                 "r"(2 * kPairTile)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();   // both CTAs' barriers exist before either touches the other's
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      bool ok = true;
+      int it = 0;
+      for (int tile = cluster; tile < tiles && ok; tile += clusters) {
+        int m0, n0;
+        pair_tile_origin(tile, m_tiles, n_tiles, m0, n0);
+        m0 += rank * kTile;   // this CTA's rows of A
+        n0 += rank * kTile;   // this CTA's columns of B
+        for (int kt = 0; kt < p.k_tiles && ok; ++kt, ++it) {
+          const int st = it % kPairStages, use = it / kPairStages;
+          if (use > 0) ok = mbar_wait(&bar->empty[st], (use - 1) & 1, p.status, 75);
+          if (!ok) break;
+          if (rank == 0) mbar_expect_tx(&bar->full[st], 2 * (kPairABytes + kPairBBytes));   // both CTAs' bytes
+          const uint32_t full_addr = smem_u32(&bar->full[st]) & kPeerBitMask;
+          uint8_t* a_dst = a_smem + st * kPairABytes;
+          uint8_t* b_dst = b_smem + st * kPairBBytes;
+          const int ka = (kt % p.a_wrap) * kBK, half = kt / p.a_wrap, kb = (kt % p.b_wrap) * kBK;
+          if (A_MN) {
+            for (int h = 0; h < kTile / 64; ++h)
+              tma_load_3d_pair(a_dst + h * kSlab, &map_a, m0 + 64 * h, ka, half, full_addr);
+          } else {
+            tma_load_3d_pair(a_dst, &map_a, ka, m0, half, full_addr);
+          }
+          if (B_MN) {
+            for (int h = 0; h < kTile / 64; ++h)
+              tma_load_3d_pair(b_dst + h * kSlab, &map_b, n0 + 64 * h, kb, 0, full_addr);
+          } else {
+            tma_load_3d_pair(b_dst, &map_b, kb, n0, 0, full_addr);
+          }
+        }
+      }
+      // every stage this CTA filled has been consumed: its last `empty` phases have completed
+      for (int back = max(0, it - kPairStages); back < it && ok; ++back)
+        ok = mbar_wait(&bar->empty[back % kPairStages], (back / kPairStages) & 1, p.status, 76);
+    }
+  } else if (warp == 1 && rank == 0) {
+    bool ok = true;
+    int it = 0, local = 0;
+    for (int tile = cluster; tile < tiles && ok; tile += clusters, ++local) {
+      const int buf = local & 1, use = local >> 1;
+      if (use > 0)   // both CTAs' epilogues have drained this accumulator's previous tile
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->acc_empty[buf], (use - 1) & 1, p.status, 77));
+      if (!ok) break;
+      tc_fence_after();
+      for (int kt = 0; kt < p.k_tiles && ok; ++kt, ++it) {
+        const int st = it % kPairStages;
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar->full[st], (it / kPairStages) & 1, p.status, 78));
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+          const uint32_t a_addr = smem_u32(a_smem + st * kPairABytes);
+          const uint32_t b_addr = smem_u32(b_smem + st * kPairBBytes);
+          const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr, kSlab, 1024) : umma_desc_sw128(a_addr, 16, 1024);
+          const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr, kSlab, 1024) : umma_desc_sw128(b_addr, 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < kBK / 16; ++ks)
+            umma_ss_pair(tmem + buf * kPairTile, a_desc + ks * ((A_MN ? 2048 : 32) >> 4),
+                         b_desc + ks * ((B_MN ? 2048 : 32) >> 4), pair_idesc, kt > 0 || ks > 0);
+          tc_commit_pair(&bar->empty[st]);
+          if (kt + 1 == p.k_tiles) tc_commit_pair(&bar->acc_full[buf]);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp >= 4) {
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const bool vec = (p.ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
+    int local = 0;
+    for (int tile = cluster; tile < tiles; tile += clusters, ++local) {
+      const int buf = local & 1;
+      int m0, n0;
+      pair_tile_origin(tile, m_tiles, n_tiles, m0, n0);
+      if (!mbar_wait(&bar->acc_full[buf], (local >> 1) & 1, p.status, 79)) break;
+      tc_fence_after();
+      const int m = m0 + rank * kTile + row;
+#pragma unroll 2
+      for (int c = 0; c < kPairTile / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld32(tmem + lane_base + buf * kPairTile + c * 32, acc);
+        tmem_wait_ld();
+        const int n_base = n0 + c * 32;
+        if (m >= p.M || n_base >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = __uint_as_float(acc[i]);
+          if (p.bias != nullptr && n_base + i < p.N) v[i] += p.bias[n_base + i];
+        }
+        if (p.c_kind == 0) {
+          float* dst = static_cast<float*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
+          if (p.c_accumulate) {
+            for (int i = 0; i < 32 && n_base + i < p.N; ++i) v[i] += dst[i];
+          }
+          if (vec && n_base + 32 <= p.N) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          } else {
+            for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = v[i];
+          }
+        } else {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
+          if (p.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(p.c) % 16 == 0 && n_base + 32 <= p.N) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8)
+              *reinterpret_cast<uint4*>(dst + i) =
+                  make_uint4(pack_bf16(v[i], v[i + 1]), pack_bf16(v[i + 2], v[i + 3]),
+                             pack_bf16(v[i + 4], v[i + 5]), pack_bf16(v[i + 6], v[i + 7]));
+          } else {
+            for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(smem_u32(&bar->acc_empty[buf]) & kPeerBitMask);   // CTA 0's barrier
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();   // neither CTA leaves while the other may still signal it or read its tiles
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * kPairTile) : "memory");
+  }
+}
+
 // src [rows, cols] (fp32 or bf16) -> dst [rows_p, cols_p] 2-byte (bf16 or fp16), zero padded.
 // grid (cols_p / 8 / 256 rounded up, rows_p): a thread converts 8 consecutive columns.
 template <typename In, bool kHalf>
@@ -320,17 +563,31 @@ __global__ void bias_final_kernel(const float* __restrict__ partial, int chunks,
 
 int pad128(int v) { return (v + 127) / 128 * 128; }
 
+// b_pair: the B operand's map for the two-SM kernel (K-major B: boxes of 128 rows; MN-major B: the
+// same slab map as `b`), or null to keep the call on the one-SM kernel.
 template <bool A_MN, bool B_MN>
 cudaError_t launch_gemm(cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b,
-                        const GemmParams& p) {
+                        const GemmParams& p, const CUtensorMap* b_pair = nullptr) {
+  int sms = 148, device = 0;
+  if (cudaGetDevice(&device) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const int pair_tiles = ((p.N + kPairTile - 1) / kPairTile) * ((p.M + kPairTile - 1) / kPairTile);
+  if (b_pair != nullptr && pair_tiles >= sms / 2) {   // enough 256 x 256 tiles to occupy every pair of SMs
+    const size_t pair_smem = 1024 + kPairStages * (kPairABytes + kPairBBytes) + sizeof(PairGemmBarriers);
+    cudaError_t e = cudaFuncSetAttribute(gemm_sm100_pair<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(pair_smem));
+    if (e != cudaSuccess) return e;
+    const uint32_t format = (p.idesc >> 7) & 7u;
+    const int clusters = std::min(pair_tiles, sms / 2);
+    gemm_sm100_pair<A_MN, B_MN><<<2 * clusters, kGemmThreads, pair_smem, stream>>>(
+        a, *b_pair, p, gemm_idesc_pair(static_cast<int>(format), A_MN, B_MN));
+    return cudaGetLastError();
+  }
   const size_t smem = 1024 + kGemmStages * (kABytes + kBBytes) + sizeof(GemmBarriers);
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   const int tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kTile - 1) / kTile);
-  int sms = 148, device = 0;
-  if (cudaGetDevice(&device) == cudaSuccess)
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   gemm_sm100<A_MN, B_MN><<<std::min(tiles, sms), kGemmThreads, smem, stream>>>(a, b, p);
   return cudaGetLastError();
 }
@@ -395,7 +652,7 @@ cudaError_t dense_fwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
     return cudaErrorInvalidValue;
   GemmParams p{rows, out, i / kBK, i / kBK, i / kBK, 0, gemm_idesc(half ? 0 : 1, false, true), bias, y,
                static_cast<size_t>(out), x_is_bf16 ? 1 : 0, status};
-  return launch_gemm<false, true>(stream, ma, mb, p);
+  return launch_gemm<false, true>(stream, ma, mb, p, &mb);
 }
 
 // dy fp32 [rows, out]; dx fp32 [rows, in]; dw fp32 [in, out]; db fp32 [out] (all overwritten)
@@ -415,18 +672,20 @@ cudaError_t dense_bwd(cudaStream_t stream, const void* x, bool x_is_bf16, const 
   const int format = half ? 0 : 1;
   CUtensorMap ma, mb;
   // dX[rows, in] = dY[rows][out] (K-major) * W^T: B(k, n) = W[n][k], memory [in][out] = K-major
-  if (!make_token_map(&ma, gc, o, r, 1, o, kTile) || !make_token_map(&mb, wc, o, i, 1, o, kTileN))
+  CUtensorMap mb_pair;
+  if (!make_token_map(&ma, gc, o, r, 1, o, kTile) || !make_token_map(&mb, wc, o, i, 1, o, kTileN) ||
+      !make_token_map(&mb_pair, wc, o, i, 1, o, kTile))
     return cudaErrorInvalidValue;
   GemmParams pdx{rows, in, o / kBK, o / kBK, o / kBK, 0, gemm_idesc(format, false, false), nullptr, dx,
                  static_cast<size_t>(in), 0, status};
-  e = launch_gemm<false, false>(stream, ma, mb, pdx);
+  e = launch_gemm<false, false>(stream, ma, mb, pdx, &mb_pair);
   if (e != cudaSuccess) return e;
   // dW[in, out] = X^T dY: A(m, k) = X[k][m], memory [rows][in] = MN-major; B = dY [rows][out] MN-major
   if (!operand_map(&ma, xo, kBK) || !make_token_map(&mb, gc, o, r, 1, o, kBK))
     return cudaErrorInvalidValue;
   GemmParams pdw{in, out, r / kBK, r / kBK, r / kBK, 0, gemm_idesc(format, true, true), nullptr, dw,
                  static_cast<size_t>(out), 0, status};
-  e = launch_gemm<true, true>(stream, ma, mb, pdw);
+  e = launch_gemm<true, true>(stream, ma, mb, pdw, &mb);
   if (e != cudaSuccess) return e;
   float* partial = reinterpret_cast<float*>(gc + 2 * static_cast<size_t>(r) * o);
   bias_partial_kernel<<<dim3((out + 127) / 128, kBiasChunks), 256, 0, stream>>>(dy, rows, out, partial);
@@ -524,12 +783,13 @@ cudaError_t block_linear_fwd(cudaStream_t stream, const void* weight, const void
   cudaError_t e = bf16_operand(stream, x, tokens, in, xc, &xo);
   if (e == cudaSuccess) e = bf16_operand(stream, weight, out, in, wc, &wo);
   if (e != cudaSuccess) return e;
-  CUtensorMap ma, mb;
-  if (!operand_map(&ma, xo, kTile) || !operand_map(&mb, wo, kTileN)) return cudaErrorInvalidValue;
+  CUtensorMap ma, mb, mb_pair;
+  if (!operand_map(&ma, xo, kTile) || !operand_map(&mb, wo, kTileN) || !operand_map(&mb_pair, wo, kTile))
+    return cudaErrorInvalidValue;
   const int k_tiles = static_cast<int>(i / kBK);
   GemmParams p{tokens, out, k_tiles, k_tiles, k_tiles, 0, gemm_idesc(1, false, false), nullptr, y,
                static_cast<size_t>(out), y_is_fp32 ? 0 : 1, status};
-  return launch_gemm<false, false>(stream, ma, mb, p);
+  return launch_gemm<false, false>(stream, ma, mb, p, &mb_pair);
 }
 
 cudaError_t block_linear_bwd(cudaStream_t stream, const void* weight, const void* x, const float* dy,
@@ -557,7 +817,7 @@ cudaError_t block_linear_bwd(cudaStream_t stream, const void* weight, const void
   const int ko = static_cast<int>(o / kBK), kt = static_cast<int>(t / kBK);
   GemmParams pdx{tokens, in, 2 * ko, ko, ko, 0, gemm_idesc(1, false, true), nullptr, dx,
                  static_cast<size_t>(in), 0, status};
-  e = launch_gemm<false, true>(stream, ma, mb, pdx);
+  e = launch_gemm<false, true>(stream, ma, mb, pdx, &mb);
   if (e != cudaSuccess || d_weight == nullptr) return e;
   // dW[out, in] += dY^T X: A(m = r, k = t) = dY[t][r]: MN-major halves over tokens; B = X MN-major
   if (!make_token_map(&ma, gc, static_cast<int>(o), static_cast<int>(t), 2, o, kBK) ||
@@ -565,7 +825,7 @@ cudaError_t block_linear_bwd(cudaStream_t stream, const void* weight, const void
     return cudaErrorInvalidValue;
   GemmParams pdw{out, in, 2 * kt, kt, kt, 1, gemm_idesc(1, true, true), nullptr, d_weight,
                  static_cast<size_t>(in), 0, status};
-  return launch_gemm<true, true>(stream, ma, mb, pdw);
+  return launch_gemm<true, true>(stream, ma, mb, pdw, &mb);
 }
 
 cudaError_t dequantize_matrix(cudaStream_t stream, const void* input, int storage, const float* scales,

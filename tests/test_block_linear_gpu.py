@@ -64,7 +64,8 @@ def test_linear_masks_tail_tiles_and_produces_repeatable_gradients():
         weight.Deactivate()
 
 
-@pytest.mark.parametrize("tokens,cols,rows", [(200, 264, 136), (1000, 1024, 2304), (77, 5120, 300)])
+@pytest.mark.parametrize("tokens,cols,rows", [(200, 264, 136), (1000, 1024, 2304), (77, 5120, 300),
+                                              (2500, 2304, 2104)])   # two-SM kernel, ragged tiles
 def test_random_values_match_oracle_with_fp32_gradients(tokens, cols, rows):
     rng = np.random.default_rng(tokens)
     x = oracle.round_bf16(rng.standard_normal((tokens, cols)).astype(np.float32))

@@ -43,7 +43,9 @@ def test_rectangular_projection_uses_distinct_input_and_output_widths():
 
 @pytest.mark.parametrize("rows,in_dim,out_dim,dtype", [
     (300, 200, 136, DataType.BF16), (513, 768, 2304, DataType.BF16), (100, 77, 53, DataType.FP16),
-    (1024, 1024, 1024, DataType.FP16), (64, 3000, 130, DataType.BF16)])
+    (1024, 1024, 1024, DataType.FP16), (64, 3000, 130, DataType.BF16),
+    # every product large enough for the two-SM kernel (at least 74 tiles of 256 x 256), ragged edges
+    (2500, 2300, 2100, DataType.BF16), (2340, 2200, 2500, DataType.FP16)])
 def test_forward_and_backward_match_oracle(rows, in_dim, out_dim, dtype):
     rng = np.random.default_rng(rows + in_dim)
     bf16 = dtype == DataType.BF16
