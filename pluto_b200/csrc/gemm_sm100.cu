@@ -17,7 +17,9 @@
 //   MN-major  (m or n contiguous: W for the forward, X and dY for dW), read as 64-wide slabs.
 // One persistent CTA per SM walks its output tiles: warp 0 issues the TMA loads, warp 1 the MMA
 // schedule with one elected issuing lane into one of two TMEM accumulators, warps 4-7 move the
-// other accumulator to global memory (one row per thread) adding the bias.  All waits are bounded.
+// other accumulator to global memory (one row per thread) adding the bias.  Products with at least
+// one 256 x 256 tile per pair of SMs run the same schedule on clusters of two CTAs
+// (gemm_sm100_pair, tcgen05.mma.cta_group::2).  All waits are bounded.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
