@@ -217,8 +217,9 @@ class Ranks:
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         self.barrier()
-        if hold:
-            torch.cuda._sleep(min(steps * 400_000, 400_000_000))   # ~0.2 ms of device time per step
+        sleep = getattr(torch.cuda, "_sleep", None)
+        if hold and sleep is not None:
+            sleep(min(steps * 400_000, 400_000_000))   # ~0.2 ms of device time per step
         for i in range(steps):
             if flush:
                 self.flush.fill_(i & 0xFF)
