@@ -695,8 +695,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              *reinterpret_cast<uint4*>(stage + row * (kRoundCols * 4) + (((c * 8 + i) ^ (row & (kChunks - 1))) * 16)) =
-                  make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              sts_b32x4(smem_u32(stage) + row * (kRoundCols * 4) + (((c * 8 + i) ^ (row & (kChunks - 1))) * 16),
+                        o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
           }
         }
         // all 128 threads of this tile's warpgroup, whatever their waits returned
@@ -707,7 +707,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
             const int r = e / kChunks, piece = e % kChunks;
             if (q_tile * kBM + r < p.seq)
               *reinterpret_cast<uint4*>(dst_tile + static_cast<size_t>(r) * p.heads * D + round * kRoundCols + piece * 4) =
-                  *reinterpret_cast<const uint4*>(stage + r * (kRoundCols * 4) + ((piece ^ (r & (kChunks - 1))) * 16));
+                  lds_b32x4(smem_u32(stage) + r * (kRoundCols * 4) + ((piece ^ (r & (kChunks - 1))) * 16));
           }
         }
         asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");   // the next round reuses the buffer
@@ -760,11 +760,12 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
             }
             w[i / 2] = pack_bf16(a, b);
           }
-          uint8_t* slab_row = stage + (c / 2) * kSlabBytes + row * 128;
+          // (st.shared by address: a store through the generic `stage` pointer took four times as long)
+          const uint32_t slab_row = smem_u32(stage) + (c / 2) * kSlabBytes + row * 128;
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<uint4*>(slab_row + ((((c & 1) * 4 + i) ^ (row & 7)) * 16)) =
-                make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            sts_b32x4(slab_row + ((((c & 1) * 4 + i) ^ (row & 7)) * 16), w[4 * i], w[4 * i + 1], w[4 * i + 2],
+                      w[4 * i + 3]);
         }
       }
       // all 128 threads of this tile's warpgroup, whatever their waits returned (`any` is uniform)
@@ -777,8 +778,8 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
           const int r = e / kPieces, piece = e % kPieces;
           const int q_row = q_tile * kBM + r;
           if (q_row < p.seq) {
-            const uint4 v = *reinterpret_cast<const uint4*>(stage + (piece / 8) * kSlabBytes + r * 128 +
-                                                            (((piece & 7) ^ (r & 7)) * 16));
+            const uint4 v = lds_b32x4(smem_u32(stage) + (piece / 8) * kSlabBytes + r * 128 +
+                                      (((piece & 7) ^ (r & 7)) * 16));
             *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(batch) * p.seq + q_row) * p.out_token +
                                       head * p.out_head + piece * 8) = v;
           }
