@@ -210,9 +210,9 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, 
         arithmetic_sync();   // the previous chunk's rows have left the tile
         if (ok) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            reinterpret_cast<__nv_bfloat16*>(out_tile)[(half * 32 + i) * kGdnSliceCols + jl] =
-                __float2bfloat16_rn(__uint_as_float(o[i]));
+          for (int i = 0; i < 32; ++i)   // (st.shared by address: `out_tile` is a generic pointer to the compiler)
+            sts_b16(smem_u32(out_tile) + ((half * 32 + i) * kGdnSliceCols + jl) * 2,
+                    __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(o[i]))));
         }
         arithmetic_sync();
         if (ok) {
@@ -225,7 +225,7 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, 
               const size_t off = ((static_cast<size_t>(b) * a.tokens + t) * a.value_heads + h) * dv +
                                  slice * kGdnSliceCols + piece * 8;
               *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + off) =
-                  *reinterpret_cast<const uint4*>(out_tile + row * (kGdnSliceCols * 2) + piece * 16);
+                  lds_b32x4(smem_u32(out_tile) + row * (kGdnSliceCols * 2) + piece * 16);
             }
           }
         }
@@ -249,7 +249,7 @@ gdn_scan_sm100(GdnArgs a, const uint8_t* __restrict__ records, int first_chunk, 
       ok = __all_sync(0xffffffffu, ok && mbar_wait(&bar->full[st], (c / kScanStages) & 1, status, 57));   // gamma is in the record
       if (ok) {
         tc_fence_after();
-        const float gamma = *reinterpret_cast<const float*>(smem + st * kStageBytes + GdnRecord::kGM);
+        const float gamma = lds_f32(smem_u32(smem) + st * kStageBytes + GdnRecord::kGM);
         uint32_t s[2][32], packed[32];
         tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
         tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
@@ -429,7 +429,7 @@ gdn_scan_bwd_sm100(const __grid_constant__ CUtensorMap map_do, int value_heads,
       ok = __all_sync(0xffffffffu, ok && mbar_wait(&bar->full[st], (n / kRevStages) & 1, status, 49));
       if (ok) {
         tc_fence_after();
-        const float gamma = *reinterpret_cast<const float*>(smem + st * kRevStageBytes + kRevGm);
+        const float gamma = lds_f32(smem_u32(smem) + st * kRevStageBytes + kRevGm);
         uint32_t s[2][32], packed[32];
         tmem_ld32(tmem + lane_base + kColState + half * 64, s[0]);
         tmem_ld32(tmem + lane_base + kColState + half * 64 + 32, s[1]);
