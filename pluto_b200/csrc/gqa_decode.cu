@@ -205,8 +205,8 @@ gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         // V rows first.  Only the last tile of a sequence takes this path.
         for (int r = max(live, warp * 16); r < (warp + 1) * 16; ++r)
           for (int c = lane; c < kHalves * 8; c += 32)
-            *reinterpret_cast<uint4*>(smem + st * kStageBytes + kTileBytes + (c / 8) * kHalfBytes +
-                                      r * 128 + (c % 8) * 16) = make_uint4(0, 0, 0, 0);
+            sts_b32x4(smem_u32(smem) + st * kStageBytes + kTileBytes + (c / 8) * kHalfBytes + r * 128 +
+                          (c % 8) * 16, 0u, 0u, 0u, 0u);
         fence_proxy_async();
         __syncwarp();
       }
@@ -282,38 +282,42 @@ gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   }
   __syncthreads();  // every stage consumed, every copy landed: the ring can be reused as scratch
 
-  // ---- merge the four warps' partial softmax states through shared memory
-  float* scratch = reinterpret_cast<float*>(smem);              // [warps][16][D]
-  float* scratch_ml = scratch + kConsumerWarps * 16 * D;        // [warps][16][2]
+  // ---- merge the four warps' partial softmax states through shared memory (ld.shared / st.shared
+  // by address: `smem` went through alignment arithmetic and is a generic pointer to the compiler)
+  const uint32_t scratch = smem_u32(smem);                               // fp32 [warps][16][D]
+  const uint32_t scratch_ml = scratch + kConsumerWarps * 16 * D * 4;     // fp32 [warps][16][2]
   if (warp < kConsumerWarps) {
     const int r0 = lane / 4;
 #pragma unroll
     for (int nb = 0; nb < D / 8; ++nb) {
       const int col = nb * 8 + (lane % 4) * 2;
-      scratch[(warp * 16 + r0) * D + col] = o[nb][0];
-      scratch[(warp * 16 + r0) * D + col + 1] = o[nb][1];
-      scratch[(warp * 16 + r0 + 8) * D + col] = o[nb][2];
-      scratch[(warp * 16 + r0 + 8) * D + col + 1] = o[nb][3];
+      sts_f32(scratch + ((warp * 16 + r0) * D + col) * 4, o[nb][0]);
+      sts_f32(scratch + ((warp * 16 + r0) * D + col + 1) * 4, o[nb][1]);
+      sts_f32(scratch + ((warp * 16 + r0 + 8) * D + col) * 4, o[nb][2]);
+      sts_f32(scratch + ((warp * 16 + r0 + 8) * D + col + 1) * 4, o[nb][3]);
     }
     if (lane % 4 == 0) {
-      scratch_ml[(warp * 16 + r0) * 2] = m_run[0];
-      scratch_ml[(warp * 16 + r0) * 2 + 1] = l_run[0];
-      scratch_ml[(warp * 16 + r0 + 8) * 2] = m_run[1];
-      scratch_ml[(warp * 16 + r0 + 8) * 2 + 1] = l_run[1];
+      sts_f32(scratch_ml + ((warp * 16 + r0) * 2) * 4, m_run[0]);
+      sts_f32(scratch_ml + ((warp * 16 + r0) * 2 + 1) * 4, l_run[0]);
+      sts_f32(scratch_ml + ((warp * 16 + r0 + 8) * 2) * 4, m_run[1]);
+      sts_f32(scratch_ml + ((warp * 16 + r0 + 8) * 2 + 1) * 4, l_run[1]);
     }
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < group * D; idx += kDecodeThreads) {
     const int r = idx / D, d = idx % D;
-    float m_tot = -INFINITY;
+    float m_w[kConsumerWarps], m_tot = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) m_tot = fmaxf(m_tot, scratch_ml[(w * 16 + r) * 2]);
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      m_w[w] = lds_f32(scratch_ml + ((w * 16 + r) * 2) * 4);
+      m_tot = fmaxf(m_tot, m_w[w]);
+    }
     float acc = 0.0f, l_tot = 0.0f;
 #pragma unroll
     for (int w = 0; w < kConsumerWarps; ++w) {
-      const float f = fast_exp2(scratch_ml[(w * 16 + r) * 2] - m_tot);
-      acc += scratch[(w * 16 + r) * D + d] * f;
-      l_tot += scratch_ml[(w * 16 + r) * 2 + 1] * f;
+      const float f = fast_exp2(m_w[w] - m_tot);
+      acc += lds_f32(scratch + ((w * 16 + r) * D + d) * 4) * f;
+      l_tot += lds_f32(scratch_ml + ((w * 16 + r) * 2 + 1) * 4) * f;
     }
     const size_t head = static_cast<size_t>(b) * a.q_heads + static_cast<size_t>(kv_head) * group + r;
     const size_t slot = head * a.splits + split;
