@@ -378,7 +378,8 @@ int fill_decode(pluto::DecodeArgs* a, const void* q, int q_dtype, const pluto_kv
   a->seq_lens = seq_lens;
   a->batch = batch; a->q_heads = q_heads; a->kv_heads = kv_heads; a->head_dim = head_dim;
   a->split_tokens = decode_split_tokens(batch, kv_heads, max_seq_len);
-  a->splits = (max_seq_len + a->split_tokens - 1) / a->split_tokens;
+  a->splits = pluto::decode_chunk_count(max_seq_len, a->split_tokens);
+  if (a->splits > 65535) return fail(PLUTO_E_INVALID, "max_seq_len exceeds what one decode launch can split");
   a->scale = 1.0f / sqrtf(static_cast<float>(head_dim));
   a->status = pluto::kernel_status_word();
   if (!a->status) return fail(PLUTO_E_INTERNAL, "kernel status word unavailable");
@@ -435,7 +436,7 @@ size_t pluto_gqa_decode_workspace_bytes(int batch, int q_heads, int kv_heads, in
                                         int max_seq_len) {
   if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || max_seq_len <= 0) return 0;
   const int s = decode_split_tokens(batch, kv_heads, max_seq_len);
-  const size_t splits = static_cast<size_t>((max_seq_len + s - 1) / s);
+  const size_t splits = static_cast<size_t>(pluto::decode_chunk_count(max_seq_len, s));
   return static_cast<size_t>(batch) * q_heads * splits * (head_dim + 2) * sizeof(float);
 }
 

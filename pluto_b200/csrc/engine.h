@@ -165,6 +165,26 @@ struct DecodeArgs {
   int round;
   uint32_t* status;
 };
+// Chunks of the split-KV decode.  A sequence is cut into chunks of `split_tokens` tokens, except
+// that its first split_tokens tokens form four chunks of a quarter each; the kernels run the
+// chunks in decreasing index order, so that these short ones fill the end of the launch, where
+// whole-length chunks would leave most SMs waiting for the last few.  (One KV head of 64 sequences:
+// 4.1 waves of equal chunks cost 5.)  split_tokens is a multiple of 256.
+__host__ __device__ inline int decode_chunk_begin(int s, int split_tokens) {
+  return s < 4 ? s * (split_tokens / 4) : (s - 3) * split_tokens;
+}
+__host__ __device__ inline int decode_chunk_tokens(int s, int split_tokens) {
+  return s < 4 ? split_tokens / 4 : split_tokens;
+}
+__host__ __device__ inline int decode_chunk_count(int length, int split_tokens) {   // chunks with a token
+  if (length <= 0) return 0;
+  return length <= split_tokens ? (length + split_tokens / 4 - 1) / (split_tokens / 4)
+                                : 3 + (length + split_tokens - 1) / split_tokens;
+}
+__host__ __device__ inline long long decode_chunk_capacity(int splits, int split_tokens) {   // tokens `splits` chunks hold
+  return splits < 4 ? static_cast<long long>(splits) * (split_tokens / 4)
+                    : static_cast<long long>(splits - 3) * split_tokens;
+}
 bool gqa_decode_uses_tensor_cores(const DecodeArgs& args);
 // Floats of the (max, sum) section at the start of the decode workspace; the accumulators
 // [batch, q_heads, splits, head_dim] follow it.  Always an even count, so a workspace aligned to

@@ -32,11 +32,11 @@ constexpr int kConsumerWarps = 4;  // 16 tokens of every tile each
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
 
 // Sequence length as the kernels use it: the device value clamped into what the host sized the
-// grid and the workspace for, [0, splits * split_tokens].  A value outside is a caller error; it
+// grid and the workspace for, [0, decode_chunk_capacity(splits, split_tokens)].  A value outside is a caller error; it
 // is reported through the status word and the launch stays inside its buffers.
 __device__ __forceinline__ int bounded_length(const DecodeArgs& a, int b, uint32_t site) {
   const int length = a.seq_lens[b];
-  const long long limit = static_cast<long long>(a.splits) * a.split_tokens;
+  const long long limit = decode_chunk_capacity(a.splits, a.split_tokens);
   if (length < 0 || length > limit) {
     report_status(a.status, site, kBadLength);
     return length < 0 ? 0 : static_cast<int>(limit);
@@ -88,7 +88,7 @@ struct DecodeBarriers {
   uint64_t empty[kDecodeStages];
 };
 
-// grid (splits, kv_heads, batch).  Partials: acc [B, Hq, splits, D], ml [B, Hq, splits, 2].
+// grid (kv_heads, batch, splits), chunks in decreasing index order.  Partials: acc [B, Hq, splits, D], ml [B, Hq, splits, 2].
 template <int D>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
 gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -103,11 +103,13 @@ gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   DecodeBarriers* bar = reinterpret_cast<DecodeBarriers*>(smem + kDecodeStages * kStageBytes);
 
   pdl_launch_dependents();   // the merge may be placed as SMs free up; it waits for this grid itself
-  const int split = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
+  // chunks in decreasing index order, (KV head, sequence) fastest: the four short chunks of every
+  // sequence are the last CTAs of the launch
+  const int split = gridDim.z - 1 - blockIdx.z, kv_head = blockIdx.x, b = blockIdx.y;
   const int length = bounded_length(a, b, 36);
-  const int begin = split * a.split_tokens;
+  const int begin = decode_chunk_begin(split, a.split_tokens);
   if (begin >= length) return;  // whole CTA leaves before touching any barrier
-  const int end = min(length, begin + a.split_tokens);
+  const int end = min(length, begin + decode_chunk_tokens(split, a.split_tokens));
   const int tiles = (end - begin + kTile - 1) / kTile;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int group = a.q_heads / a.kv_heads;
@@ -330,16 +332,16 @@ gqa_decode_tc(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------------------------
-// Exact fp32 kernel with the same split structure: grid (splits, q_heads, batch), one warp per
+// Exact fp32 kernel with the same split structure: grid (q_heads, batch, splits), one warp per
 // token row in flight, each lane owning head_dim/32 (<= 8) channels.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) gqa_decode_generic(DecodeArgs a) {
   pdl_launch_dependents();
-  const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  const int split = gridDim.z - 1 - blockIdx.z, head = blockIdx.x, b = blockIdx.y;
   const int length = bounded_length(a, b, 37);
-  const int begin = split * a.split_tokens;
+  const int begin = decode_chunk_begin(split, a.split_tokens);
   if (begin >= length) return;
-  const int end = min(length, begin + a.split_tokens);
+  const int end = min(length, begin + decode_chunk_tokens(split, a.split_tokens));
   const int D = a.head_dim, kv_head = head / (a.q_heads / a.kv_heads);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const size_t element = a.kv_is_bf16 ? 2 : 4;
@@ -419,7 +421,7 @@ __global__ void __launch_bounds__(kMergeThreads) gqa_decode_merge(DecodeArgs a) 
   pdl_wait();   // the chunk kernel's partials are complete and visible from here on
   const int head = blockIdx.x, b = blockIdx.y, D = a.head_dim;
   const int length = bounded_length(a, b, 38);
-  const int splits = (length + a.split_tokens - 1) / a.split_tokens;   // <= a.splits
+  const int splits = decode_chunk_count(length, a.split_tokens);   // <= a.splits
   if (length <= 0) {
     // nothing to attend to (a caller error: lengths are >= 1): zeros, not 0/0
     for (int d = threadIdx.x; d < D; d += kMergeThreads) {
@@ -593,7 +595,7 @@ bool gqa_decode_uses_tensor_cores(const DecodeArgs& a) {
 cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args) {
   DecodeArgs a = args;
   if (gqa_decode_uses_tensor_cores(a)) {
-    const dim3 grid(a.splits, a.kv_heads, a.batch);
+    const dim3 grid(a.kv_heads, a.batch, a.splits);
     cudaError_t e;
     a.box_rows = a.page_size % kTile == 0 ? kTile : 16;
     const int pages = a.block_table ? a.num_pages : a.batch;
@@ -614,7 +616,7 @@ cudaError_t gqa_decode(cudaStream_t stream, const DecodeArgs& args) {
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   } else {
-    gqa_decode_generic<<<dim3(a.splits, a.q_heads, a.batch), 128, 0, stream>>>(a);
+    gqa_decode_generic<<<dim3(a.q_heads, a.batch, a.splits), 128, 0, stream>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
