@@ -297,14 +297,14 @@ int pluto_gqa_decode(pluto_stream_t stream, const void* q, int q_dtype, const vo
  * cudaMalloc (and the stream-ordered allocators) to loaded libraries, decode loops that must not
  * contend for an allocator lock.  It has no counterpart in the reference, whose CachedAttentionStep
  * allocates its scratch with a stream-ordered Buffer on every token.  The split-KV partials live
- * in a 24 MiB area inside the library image (pluto_gqa_decode_builtin_scratch_bytes()).  Arguments,
+ * in a 32 MiB area inside the library image (pluto_gqa_decode_builtin_scratch_bytes()).  Arguments,
  * results and kernels are those of pluto_gqa_decode minus the workspace pair.
  *   - A call whose pluto_gqa_decode_workspace_bytes(...) exceeds the area returns
  *     PLUTO_E_EXHAUSTED with the two sizes in pluto_last_error(); nothing is launched.
  *   - The entry point itself calls no cudaMalloc/cudaFree or allocating library routine.  The
  *     area is a static device array: the CUDA runtime gives it memory when it loads this
  *     library's device code on a GPU, which with lazy module loading (the default) happens at the
- *     first call on that GPU, not when the process loads the .so; the GPU then holds the 24 MiB
+ *     first call on that GPU, not when the process loads the .so; the GPU then holds the 32 MiB
  *     until the process exits.  So make ONE warm-up call per device at start-up -- before the HBM
  *     plan is committed and before any stream capture: that call loads the device code, looks up
  *     the area's device address (cudaGetSymbolAddress, with that device current) and the status

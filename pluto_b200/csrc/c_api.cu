@@ -811,7 +811,7 @@ extern "C" int pluto_interleave_heads(pluto_stream_t stream, const void* gathere
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-constexpr size_t kBuiltInScratchBytes = 24u << 20;  // 24 MiB per GPU that loads the library
+constexpr size_t kBuiltInScratchBytes = 32u << 20;  // 32 MiB per GPU that loads the library
 static __device__ __align__(256) unsigned char g_builtin_decode_scratch[kBuiltInScratchBytes];
 
 constexpr int kMaxScratchDevices = 64;

@@ -676,7 +676,7 @@ def gqa_decode_noalloc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     """`gqa_decode` for callers that may not allocate device memory (a fixed, fully committed
     memory plan; a sandbox that forbids cudaMalloc to plugins; a decode loop that must stay off
     the allocator lock).  Nothing is allocated here or in the library: `out` comes from the
-    caller and the split-KV partials use the 24 MiB area built into the library, which every
+    caller and the split-KV partials use the 32 MiB area built into the library, which every
     call shares -- keep calls on one stream.  Raises ResourceExhausted when the shape needs more
     scratch than the area holds."""
     B, Hq, D = q.shape

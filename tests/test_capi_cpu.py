@@ -80,7 +80,8 @@ def test_cached_attention_argument_validation(engine):
     mismatch = _code(engine, L.pluto_gqa_decode, None, 16, 1, None, 0, 0, 0, ref, 16, 8, 16, 1, None,
                      16, 1 << 20, 1, 4, 2, 4, 1)
     assert mismatch[0] == "InvalidArgument" and "cache shape" in mismatch[1]
-    assert L.pluto_gqa_decode_workspace_bytes(64, 40, 8, 128, 32768) == 64 * 40 * 16 * 130 * 4
+    # 16 chunks of 2048 tokens, the first of them as four short ones: 19 partials per head
+    assert L.pluto_gqa_decode_workspace_bytes(64, 40, 8, 128, 32768) == 64 * 40 * 19 * 130 * 4
     odd_rotary = _code(engine, L.pluto_qk_prepare, None, 16, 16, 16, 0, 8, 4, 16, 16, None, 16, 0, ref,
                        1, 1, 2, 1, 4, 3, 1e-6, 1e4, 1)
     assert odd_rotary[0] == "InvalidArgument"

@@ -6,7 +6,7 @@ run that stops at the first failure has already exercised everything else.
 Who needs it: hosts that cannot allocate device memory when attention runs -- a server whose HBM
 plan is fixed and fully committed at start-up, a sandbox that forbids cudaMalloc to loaded
 plugins, a decode loop that must not wait on an allocator lock.  The entry point keeps its
-split-KV scratch in a 24 MiB area inside the library; the test drives it through the C ABI and
+split-KV scratch in a 32 MiB area inside the library; the test drives it through the C ABI and
 requires the same bytes as pluto_gqa_decode with a caller workspace, on two calls in a row whose
 shapes differ (so anything left in the area by the first call would show in the second).
 """
@@ -33,7 +33,7 @@ def make_case(seed, batch, q_heads, kv_heads, dim, max_len):
 
 
 def test_noalloc_decode_matches_workspace_decode_twice_in_a_row():
-    assert _capi.lib().pluto_gqa_decode_builtin_scratch_bytes() == 24 << 20
+    assert _capi.lib().pluto_gqa_decode_builtin_scratch_bytes() == 32 << 20
     # two different shapes back to back: long ragged sequences, then short ones with other heads
     for seed, shape in ((1, (3, 40, 8, 128, 5000)), (2, (5, 10, 2, 128, 700))):
         q, k, v, lens = make_case(seed, *shape)
@@ -93,14 +93,14 @@ def test_noalloc_decode_rejects_shapes_beyond_the_built_in_area():
     before = out.clone()
     layout = kv_layout(k, v, None, k.shape[1], k.stride(0), k.stride(1))
     L = _capi.lib()
-    # claim a batch/context whose partials need more than 24 MiB; rejected before any launch
+    # claim a batch/context whose partials need more than 32 MiB; rejected before any launch
     need = L.pluto_gqa_decode_workspace_bytes(64, 40, 8, 128, 1 << 20)
-    assert need > 24 << 20
+    assert need > 32 << 20
     with pytest.raises(PlutoStatusError) as info:
         _capi.check(L.pluto_gqa_decode_noalloc(
             torch.cuda.current_stream().cuda_stream, q.data_ptr(), 1, None, 0, 0, 0,
             C_byref(layout), lens.data_ptr(), 1 << 20, out.data_ptr(), 1, None, 64, 40, 8, 128, 1))
     assert info.value.code == "ResourceExhausted"
-    assert str(need) in info.value.message and str(24 << 20) in info.value.message
+    assert str(need) in info.value.message and str(32 << 20) in info.value.message
     torch.cuda.synchronize()
     assert torch.equal(out, before)
