@@ -74,6 +74,85 @@ __device__ __forceinline__ void tile_origin(int tile, int m_tiles, int n_tiles, 
   n0 = (band * kBand + within % width) * kTileN;
 }
 
+// One epilogue warp's 32 rows x 256 columns of an accumulator to global memory, adding the bias.
+// Each thread holds a row (that is how tcgen05.ld delivers it), and a thread writing its own row
+// makes every store instruction of the warp touch 32 lines; so full, aligned 32-column blocks pass
+// through a 4 KB per-warp staging tile (16-byte chunk c of row r at position c ^ (r & 7), or
+// c ^ ((r >> 1) & 3) for 64-byte bf16 rows) and leave with 8 (fp32) or 4 (bf16) lanes per row.
+// Ragged or unaligned blocks keep the row-per-thread stores.
+constexpr int kDrainStageBytes = 4 * 32 * 32 * 4;   // four epilogue warps
+__device__ __forceinline__ void drain_accumulator(uint32_t acc_tmem, int m0_warp, int lane, int n0,
+                                                  const GemmParams& p, uint32_t stage) {
+  const bool vec = (p.ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
+  const bool vec16 = p.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(p.c) % 16 == 0;
+  const int m = m0_warp + lane;
+#pragma unroll 2
+  for (int c = 0; c < kTileN / 32; ++c) {
+    uint32_t acc[32];
+    tmem_ld32(acc_tmem + c * 32, acc);
+    tmem_wait_ld();
+    const int n_base = n0 + c * 32;
+    if (m0_warp >= p.M || n_base >= p.N) continue;   // (uniform over the warp)
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      v[i] = __uint_as_float(acc[i]);
+      if (p.bias != nullptr && n_base + i < p.N) v[i] += p.bias[n_base + i];
+    }
+    const bool full = n_base + 32 <= p.N;
+    if (p.c_kind == 0 && vec && full) {
+      float* block = static_cast<float*>(p.c) + static_cast<size_t>(m0_warp) * p.ldc + n_base;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        sts_b32x4(stage + lane * 128 + ((i ^ (lane & 7)) << 4), __float_as_uint(v[4 * i]),
+                  __float_as_uint(v[4 * i + 1]), __float_as_uint(v[4 * i + 2]), __float_as_uint(v[4 * i + 3]));
+      __syncwarp();
+#pragma unroll
+      for (int pass = 0; pass < 8; ++pass) {
+        const int r = pass * 4 + lane / 8, piece = lane % 8;
+        const uint4 raw = lds_b32x4(stage + r * 128 + ((piece ^ (r & 7)) << 4));
+        if (m0_warp + r < p.M) {
+          float4* dst = reinterpret_cast<float4*>(block + static_cast<size_t>(r) * p.ldc + piece * 4);
+          float4 out = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z),
+                                   __uint_as_float(raw.w));
+          if (p.c_accumulate) {
+            const float4 old = *dst;
+            out.x += old.x; out.y += old.y; out.z += old.z; out.w += old.w;
+          }
+          *dst = out;
+        }
+      }
+      __syncwarp();
+    } else if (p.c_kind == 1 && vec16 && full) {
+      __nv_bfloat16* block = static_cast<__nv_bfloat16*>(p.c) + static_cast<size_t>(m0_warp) * p.ldc + n_base;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        sts_b32x4(stage + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4), pack_bf16(v[8 * i], v[8 * i + 1]),
+                  pack_bf16(v[8 * i + 2], v[8 * i + 3]), pack_bf16(v[8 * i + 4], v[8 * i + 5]),
+                  pack_bf16(v[8 * i + 6], v[8 * i + 7]));
+      __syncwarp();
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        const int r = pass * 8 + lane / 4, piece = lane % 4;
+        const uint4 raw = lds_b32x4(stage + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4));
+        if (m0_warp + r < p.M) *reinterpret_cast<uint4*>(block + static_cast<size_t>(r) * p.ldc + piece * 8) = raw;
+      }
+      __syncwarp();
+    } else if (m < p.M) {
+      if (p.c_kind == 0) {
+        float* dst = static_cast<float*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
+        if (p.c_accumulate) {
+          for (int i = 0; i < 32 && n_base + i < p.N; ++i) v[i] += dst[i];
+        }
+        for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = v[i];
+      } else {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
+        for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+      }
+    }
+  }
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -83,7 +162,8 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* a_smem = smem;
   uint8_t* b_smem = smem + kGemmStages * kABytes;
-  GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(b_smem + kGemmStages * kBBytes);
+  uint8_t* drain_stage = b_smem + kGemmStages * kBBytes;
+  GemmBarriers* bar = reinterpret_cast<GemmBarriers*>(drain_stage + kDrainStageBytes);
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   const int m_tiles = (p.M + kTile - 1) / kTile, n_tiles = (p.N + kTileN - 1) / kTileN;
   const int tiles = m_tiles * n_tiles;
@@ -177,9 +257,8 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
     }
   } else if (warp >= 4) {
-    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const int quarter = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const bool vec = (p.ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
     int local = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
@@ -187,45 +266,8 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       tile_origin(tile, m_tiles, n_tiles, m0, n0);
       if (!mbar_wait(&bar->acc_full[buf], (local >> 1) & 1, p.status, 73)) break;
       tc_fence_after();
-      const int m = m0 + row;
-#pragma unroll 2
-      for (int c = 0; c < kTileN / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld32(tmem + lane_base + buf * kTileN + c * 32, acc);
-        tmem_wait_ld();
-        const int n_base = n0 + c * 32;
-        if (m >= p.M || n_base >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          v[i] = __uint_as_float(acc[i]);
-          if (p.bias != nullptr && n_base + i < p.N) v[i] += p.bias[n_base + i];
-        }
-        if (p.c_kind == 0) {
-          float* dst = static_cast<float*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
-          if (p.c_accumulate) {
-            for (int i = 0; i < 32 && n_base + i < p.N; ++i) v[i] += dst[i];
-          }
-          if (vec && n_base + 32 <= p.N) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-          } else {
-            for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = v[i];
-          }
-        } else {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
-          if (p.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(p.c) % 16 == 0 && n_base + 32 <= p.N) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8)
-              *reinterpret_cast<uint4*>(dst + i) =
-                  make_uint4(pack_bf16(v[i], v[i + 1]), pack_bf16(v[i + 2], v[i + 3]),
-                             pack_bf16(v[i + 4], v[i + 5]), pack_bf16(v[i + 6], v[i + 7]));
-          } else {
-            for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
-          }
-        }
-      }
+      drain_accumulator(tmem + lane_base + buf * kTileN, m0 + quarter * 32, lane, n0, p,
+                        smem_u32(drain_stage) + quarter * (kDrainStageBytes / 4));
       // the accumulator has been read into registers by every lane of this warp
       tc_fence_before();
       __syncwarp();
@@ -324,7 +366,8 @@ gemm_sm100_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* a_smem = smem;
   uint8_t* b_smem = smem + kPairStages * kPairABytes;
-  PairGemmBarriers* bar = reinterpret_cast<PairGemmBarriers*>(b_smem + kPairStages * kPairBBytes);
+  uint8_t* drain_stage = b_smem + kPairStages * kPairBBytes;
+  PairGemmBarriers* bar = reinterpret_cast<PairGemmBarriers*>(drain_stage + kDrainStageBytes);
   const int warp = uniform_warp_index(), lane = threadIdx.x % 32;
   const int rank = static_cast<int>(cluster_cta_rank());   // 0 issues the MMAs
   const int cluster = blockIdx.x / 2, clusters = gridDim.x / 2;
@@ -421,9 +464,8 @@ gemm_sm100_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
   } else if (warp >= 4) {
-    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const int quarter = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const bool vec = (p.ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
     int local = 0;
     for (int tile = cluster; tile < tiles; tile += clusters, ++local) {
       const int buf = local & 1;
@@ -431,45 +473,8 @@ gemm_sm100_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       pair_tile_origin(tile, m_tiles, n_tiles, m0, n0);
       if (!mbar_wait(&bar->acc_full[buf], (local >> 1) & 1, p.status, 79)) break;
       tc_fence_after();
-      const int m = m0 + rank * kTile + row;
-#pragma unroll 2
-      for (int c = 0; c < kPairTile / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld32(tmem + lane_base + buf * kPairTile + c * 32, acc);
-        tmem_wait_ld();
-        const int n_base = n0 + c * 32;
-        if (m >= p.M || n_base >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          v[i] = __uint_as_float(acc[i]);
-          if (p.bias != nullptr && n_base + i < p.N) v[i] += p.bias[n_base + i];
-        }
-        if (p.c_kind == 0) {
-          float* dst = static_cast<float*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
-          if (p.c_accumulate) {
-            for (int i = 0; i < 32 && n_base + i < p.N; ++i) v[i] += dst[i];
-          }
-          if (vec && n_base + 32 <= p.N) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-          } else {
-            for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = v[i];
-          }
-        } else {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<size_t>(m) * p.ldc + n_base;
-          if (p.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(p.c) % 16 == 0 && n_base + 32 <= p.N) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8)
-              *reinterpret_cast<uint4*>(dst + i) =
-                  make_uint4(pack_bf16(v[i], v[i + 1]), pack_bf16(v[i + 2], v[i + 3]),
-                             pack_bf16(v[i + 4], v[i + 5]), pack_bf16(v[i + 6], v[i + 7]));
-          } else {
-            for (int i = 0; i < 32 && n_base + i < p.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
-          }
-        }
-      }
+      drain_accumulator(tmem + lane_base + buf * kPairTile, m0 + rank * kTile + quarter * 32, lane, n0, p,
+                        smem_u32(drain_stage) + quarter * (kDrainStageBytes / 4));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(smem_u32(&bar->acc_empty[buf]) & kPeerBitMask);   // CTA 0's barrier
@@ -575,7 +580,8 @@ cudaError_t launch_gemm(cudaStream_t stream, const CUtensorMap& a, const CUtenso
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   const int pair_tiles = ((p.N + kPairTile - 1) / kPairTile) * ((p.M + kPairTile - 1) / kPairTile);
   if (b_pair != nullptr && pair_tiles >= sms / 2) {   // enough 256 x 256 tiles to occupy every pair of SMs
-    const size_t pair_smem = 1024 + kPairStages * (kPairABytes + kPairBBytes) + sizeof(PairGemmBarriers);
+    const size_t pair_smem =
+        1024 + kPairStages * (kPairABytes + kPairBBytes) + kDrainStageBytes + sizeof(PairGemmBarriers);
     cudaError_t e = cudaFuncSetAttribute(gemm_sm100_pair<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(pair_smem));
     if (e != cudaSuccess) return e;
@@ -585,7 +591,7 @@ cudaError_t launch_gemm(cudaStream_t stream, const CUtensorMap& a, const CUtenso
         a, *b_pair, p, gemm_idesc_pair(static_cast<int>(format), A_MN, B_MN));
     return cudaGetLastError();
   }
-  const size_t smem = 1024 + kGemmStages * (kABytes + kBBytes) + sizeof(GemmBarriers);
+  const size_t smem = 1024 + kGemmStages * (kABytes + kBBytes) + kDrainStageBytes + sizeof(GemmBarriers);
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
