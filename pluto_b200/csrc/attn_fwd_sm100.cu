@@ -404,6 +404,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
   // index slowest, so every head's longest pairs start first and the shortest ones fill the tail
   // (longest-processing-time-first over the whole grid, not per head).
   // blockIdx.y indexes the schedule (pairs below the launch's range are not in it).
+  pdl_launch_dependents();   // a merge kernel behind this launch may be placed as SMs free up
   const int pair = schedule.pair[blockIdx.y];
   const int part = schedule.meta[blockIdx.y] & 15, parts = schedule.meta[blockIdx.y] >> 4;
   const int head = blockIdx.x % p.heads, batch = blockIdx.x / p.heads;
@@ -810,6 +811,7 @@ attn_fwd_sm100_pair(const __grid_constant__ CUtensorMap map_q,
 template <int D>
 __global__ void __launch_bounds__(256) attn_fwd_merge(FwdParams p, int batch, int first_token,
                                                       const __grid_constant__ PairSchedule schedule) {
+  pdl_wait();   // the pair kernel's partials are complete and visible from here on
   // rows (token, head) of the tokens from first_token on (the first token of the first pair that
   // was cut: the plan cuts the long pairs, i.e. the late ones)
   constexpr int kPer = D / 32;
@@ -1170,8 +1172,19 @@ cudaError_t attn_fwd_tc(cudaStream_t stream, const AttnFwdArgs& a) {
       const int first_token = first_pair * 2 * kBM;
       const long long rows = static_cast<long long>(a.batch) * (a.seq - first_token) * a.heads;
       const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
-      if (a.head_dim == 128) attn_fwd_merge<128><<<blocks, 256, 0, stream>>>(p, a.batch, first_token, schedule);
-      else attn_fwd_merge<64><<<blocks, 256, 0, stream>>>(p, a.batch, first_token, schedule);
+      // launched with programmatic stream serialisation: its CTAs are placed while the pair
+      // kernel's last CTAs still run and wait for that grid before they read a partial
+      cudaLaunchAttribute attribute;
+      attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attribute.val.programmaticStreamSerializationAllowed = 1;
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3(blocks);
+      config.blockDim = dim3(256);
+      config.stream = stream;
+      config.attrs = &attribute;
+      config.numAttrs = 1;
+      if (a.head_dim == 128) return cudaLaunchKernelEx(&config, attn_fwd_merge<128>, p, a.batch, first_token, schedule);
+      return cudaLaunchKernelEx(&config, attn_fwd_merge<64>, p, a.batch, first_token, schedule);
     }
   } else {
     const dim3 grid(a.heads * a.batch, q_tiles);
