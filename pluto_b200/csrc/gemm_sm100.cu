@@ -187,6 +187,10 @@ gemm_sm100(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
+  // Launched with programmatic stream serialisation: everything above ran beside the kernel
+  // before (an operand cast, or the previous product); its results are read only from here on.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -395,6 +399,8 @@ gemm_sm100_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   cluster_sync_all();   // both CTAs' barriers exist before either touches the other's
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
+  pdl_wait();   // (as in the one-SM kernel: the set-up above ran beside the kernel before)
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -493,6 +499,7 @@ gemm_sm100_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 template <typename In, bool kHalf>
 __global__ void __launch_bounds__(256)
 cast_pad_kernel(const In* __restrict__ src, uint16_t* __restrict__ dst, int rows, int cols, int cols_p) {
+  pdl_launch_dependents();   // the product behind this cast may set itself up meanwhile
   const int r = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (c >= cols_p) return;
@@ -587,17 +594,35 @@ cudaError_t launch_gemm(cudaStream_t stream, const CUtensorMap& a, const CUtenso
     if (e != cudaSuccess) return e;
     const uint32_t format = (p.idesc >> 7) & 7u;
     const int clusters = std::min(pair_tiles, sms / 2);
-    gemm_sm100_pair<A_MN, B_MN><<<2 * clusters, kGemmThreads, pair_smem, stream>>>(
-        a, *b_pair, p, gemm_idesc_pair(static_cast<int>(format), A_MN, B_MN));
-    return cudaGetLastError();
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * clusters);
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = pair_smem;
+    config.stream = stream;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, gemm_sm100_pair<A_MN, B_MN>, a, *b_pair, p,
+                              gemm_idesc_pair(static_cast<int>(format), A_MN, B_MN));
   }
   const size_t smem = 1024 + kGemmStages * (kABytes + kBBytes) + kDrainStageBytes + sizeof(GemmBarriers);
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   const int tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kTile - 1) / kTile);
-  gemm_sm100<A_MN, B_MN><<<std::min(tiles, sms), kGemmThreads, smem, stream>>>(a, b, p);
-  return cudaGetLastError();
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(std::min(tiles, sms));
+  config.blockDim = dim3(kGemmThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, gemm_sm100<A_MN, B_MN>, a, b, p);
 }
 
 template <typename In>
@@ -720,6 +745,7 @@ namespace {
 __global__ void __launch_bounds__(256)
 split_pad_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, int rows, int cols,
                  int rows_p, int cols_p) {
+  pdl_launch_dependents();   // the product behind this split may set itself up meanwhile
   const int r = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (c >= cols_p) return;
