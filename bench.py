@@ -623,8 +623,10 @@ def run_engine(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_sm100_pair<128> launch on this
-# workload, from the ncu capture summarised in profiles/attn_fwd_sm100_pair_d128_gqa_prefill_8192.md.
-TRAFFIC_BYTES_PER_LAUNCH = 164.5e6
+# workload, from the ncu captures summarised in profiles/attn_fwd_sm100_pair_d128_gqa_prefill_8192.md
+# (117.5 + 47 MB in the first, 117.7 + 49.8 MB in the latest: part of the output is still in L2 when
+# the launch ends).
+TRAFFIC_BYTES_PER_LAUNCH = 167.5e6
 
 
 def other_workloads(peaks, only=None, decode_batch=64, steps_scale=1.0, skip=()):
